@@ -1,0 +1,620 @@
+/*
+ * CPU oracle for the cudabackend hot path — TEST INFRASTRUCTURE ONLY.
+ * See oracle.h for what each function restates and how parity is pinned.
+ * Nothing here is part of the shipped library.
+ */
+#include "oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------ */
+/* half-precision scalar types                                        */
+/* ------------------------------------------------------------------ */
+
+static inline uint32_t f32_bits(float x) { uint32_t u; memcpy(&u, &x, 4); return u; }
+static inline float bits_f32(uint32_t u) { float x; memcpy(&x, &u, 4); return x; }
+
+/* bfloat16.go:30-39: NaN/Inf keep their top 16 bits; everything else gets
+ * 0x7FFF + lsb added before the shift (round to nearest, ties to even). */
+uint16_t orc_bf16_from_f32(float x) {
+  uint32_t b = f32_bits(x);
+  if ((b & 0x7F800000u) == 0x7F800000u) return (uint16_t)(b >> 16);
+  b += 0x7FFFu + ((b >> 16) & 1u);
+  return (uint16_t)(b >> 16);
+}
+float orc_bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
+
+void orc_bf16_from_f32_n(const float* in, uint16_t* out, size_t n) {
+  for (size_t i = 0; i < n; i++) out[i] = orc_bf16_from_f32(in[i]);
+}
+void orc_bf16_to_f32_n(const uint16_t* in, float* out, size_t n) {
+  for (size_t i = 0; i < n; i++) out[i] = orc_bf16_to_f32(in[i]);
+}
+
+/* float16.go:103-165: IEEE binary16 with round-to-nearest-even, overflow to
+ * infinity, gradual underflow, flush below 2^-25. */
+uint16_t orc_f16_from_f32(float x) {
+  uint32_t b = f32_bits(x);
+  uint16_t sign = (uint16_t)((b >> 16) & 0x8000u);
+  int e = (int)((b >> 23) & 0xFFu);
+  uint32_t man = b & 0x007FFFFFu;
+  if (e == 0xFF) {
+    if (man == 0) return (uint16_t)(sign | 0x7C00u);
+    return (uint16_t)(sign | 0x7C00u | (uint16_t)(man >> 13) | 1u);
+  }
+  e -= 127;
+  if (e > 15) return (uint16_t)(sign | 0x7C00u);
+  if (e < -24) return sign;
+  if (e < -14) {
+    man |= 0x00800000u;
+    unsigned shift = (unsigned)(14 - e);
+    man >>= (shift - 1);
+    man = (man & 1u) ? (man >> 1) + 1u : (man >> 1);
+    return (uint16_t)(sign | (uint16_t)man);
+  }
+  uint16_t re = (uint16_t)((e + 15) << 10);
+  uint16_t rm = (uint16_t)(man >> 13);
+  if (man & 0x1000u) {
+    if ((man & 0x0FFFu) != 0 || (rm & 1u)) {
+      rm++;
+      if (rm & 0x0400u) {
+        rm = 0;
+        re = (uint16_t)(re + 0x0400u);
+        if (re >= 0x7C00u) return (uint16_t)(sign | 0x7C00u);
+      }
+    }
+  }
+  return (uint16_t)(sign | re | rm);
+}
+
+float orc_f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  int e = (h & 0x7C00u) >> 10;
+  uint32_t man = h & 0x03FFu;
+  if (e == 0x1F) return bits_f32(sign | 0x7F800000u | (man << 13));
+  if (e == 0) {
+    if (man == 0) return bits_f32(sign);
+    while ((man & 0x0400u) == 0) { man <<= 1; e--; }
+    e++;
+    man &= 0x03FFu;
+  }
+  return bits_f32(sign | ((uint32_t)(e - 15 + 127) << 23) | (man << 13));
+}
+
+int orc_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------ */
+/* activations (dense.go:176-205, gelu.go:113-118)                    */
+/* ------------------------------------------------------------------ */
+
+void orc_activation_f32(float* d, size_t n, int activation) {
+  switch (activation) {
+    case ORC_ACT_NONE: break;
+    case ORC_ACT_GELU: {
+      const float inv_sqrt2 = (float)(1.0 / sqrt(2.0));
+      for (size_t i = 0; i < n; i++) {
+        float x = d[i];
+        float h = x * 0.5f;
+        d[i] = h * (1.0f + (float)erf((double)(x * inv_sqrt2)));
+      }
+      break;
+    }
+    case ORC_ACT_RELU:
+      for (size_t i = 0; i < n; i++) if (d[i] < 0) d[i] = 0;
+      break;
+    case ORC_ACT_SILU:
+      for (size_t i = 0; i < n; i++) {
+        float x = d[i];
+        d[i] = x / (1.0f + (float)exp((double)(-x)));
+      }
+      break;
+    case ORC_ACT_HARDSWISH: {
+      const float sixth = (float)(1.0 / 6.0);
+      for (size_t i = 0; i < n; i++) {
+        float x = d[i];
+        float g = x * sixth + 0.5f;
+        if (g < 0.0f) g = 0.0f;
+        if (g > 1.0f) g = 1.0f;
+        d[i] = x * g;
+      }
+      break;
+    }
+    case ORC_ACT_TANH:
+      for (size_t i = 0; i < n; i++) d[i] = (float)tanh((double)d[i]);
+      break;
+    default: break;
+  }
+}
+
+/* ------------------------------------------------------------------ */
+/* fused quantized dense, Linear scheme, int8/uint8 weights           */
+/* ------------------------------------------------------------------ */
+
+/* One reference work unit: row m, columns [n0,n1)  (quantizeddense.go:617-649).
+ * Order of operations per element: bias first, then k ascending,
+ * out += (x * float(w)) * s            (symmetric)
+ * out += x * (float(w) * s + zp)       (with zero points)
+ * every operation rounded to f32 on its own. */
+static void qdense_unit(const float* x, const int8_t* ws, const uint8_t* wu,
+                        const float* scales, const float* zps, const float* bias,
+                        float* out, int64_t m, int64_t n0, int64_t n1,
+                        int64_t K, int64_t N, int64_t bs, int64_t nblk) {
+  float* o = out + m * N;
+  for (int64_t n = n0; n < n1; n++) o[n] = bias ? bias[n] : 0.0f;
+  for (int64_t k = 0; k < K; k++) {
+    const float xv = x[m * K + k];
+    const float* srow = scales + k * nblk;
+    const float* zrow = zps ? zps + k * nblk : NULL;
+    int64_t blk = n0 / bs;
+    int64_t next = (blk + 1) * bs;
+    for (int64_t n = n0; n < n1; n++) {
+      if (n >= next) { blk++; next += bs; }
+      const float wf = ws ? (float)ws[k * N + n] : (float)wu[k * N + n];
+      if (zrow) {
+        float dq = wf * srow[blk];
+        dq = dq + zrow[blk];
+        float p = xv * dq;
+        o[n] = o[n] + p;
+      } else {
+        float p = xv * wf;
+        p = p * srow[blk];
+        o[n] = o[n] + p;
+      }
+    }
+  }
+}
+
+void orc_qdense_linear(const float* x, const void* w, int w_unsigned,
+                       const float* scales, const float* zero_points,
+                       const float* bias, float* out,
+                       int64_t M, int64_t K, int64_t N, int64_t block_size,
+                       int activation, int threads) {
+  const int8_t* ws = w_unsigned ? NULL : (const int8_t*)w;
+  const uint8_t* wu = w_unsigned ? (const uint8_t*)w : NULL;
+  const int64_t nblk = (N + block_size - 1) / block_size;
+  const int64_t min_chunk = 4096; /* geluMinParallelizeChunk, gelu.go:90 */
+  if (threads <= 1 || M * K * N <= min_chunk) {
+    for (int64_t m = 0; m < M; m++)
+      qdense_unit(x, ws, wu, scales, zero_points, bias, out, m, 0, N, K, N, block_size, nblk);
+  } else if (M > 1) {
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+    for (int64_t m = 0; m < M; m++)
+      qdense_unit(x, ws, wu, scales, zero_points, bias, out, m, 0, N, K, N, block_size, nblk);
+  } else {
+    int64_t tile = min_chunk / K;
+    if (tile < 1) tile = 1;
+    const int64_t ntiles = (N + tile - 1) / tile;
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 16)
+    for (int64_t t = 0; t < ntiles; t++) {
+      int64_t n0 = t * tile, n1 = n0 + tile;
+      if (n1 > N) n1 = N;
+      qdense_unit(x, ws, wu, scales, zero_points, bias, out, 0, n0, n1, K, N, block_size, nblk);
+    }
+  }
+  /* the reference applies the activation single-threaded over the whole output */
+  orc_activation_f32(out, (size_t)(M * N), activation);
+}
+
+/* ------------------------------------------------------------------ */
+/* DotGeneral                                                         */
+/* ------------------------------------------------------------------ */
+
+static int is_float_dtype(int d) { return d == ORC_F16 || d == ORC_F32 || d == ORC_F64 || d == ORC_BF16; }
+static int is_half_dtype(int d) { return d == ORC_F16 || d == ORC_BF16; }
+static int is_int_dtype(int d) { return d >= ORC_I8 && d <= ORC_U64; }
+
+static size_t dtype_size(int d) {
+  switch (d) {
+    case ORC_BOOL: case ORC_I8: case ORC_U8: return 1;
+    case ORC_I16: case ORC_U16: case ORC_F16: case ORC_BF16: return 2;
+    case ORC_I32: case ORC_U32: case ORC_F32: return 4;
+    case ORC_I64: case ORC_U64: case ORC_F64: return 8;
+    default: return 0;
+  }
+}
+
+static double load_as_double(const void* p, int d, int64_t i) {
+  switch (d) {
+    case ORC_F64: return ((const double*)p)[i];
+    case ORC_F32: return (double)((const float*)p)[i];
+    case ORC_BF16: return (double)orc_bf16_to_f32(((const uint16_t*)p)[i]);
+    case ORC_F16: return (double)orc_f16_to_f32(((const uint16_t*)p)[i]);
+    case ORC_I8: return (double)((const int8_t*)p)[i];
+    case ORC_U8: return (double)((const uint8_t*)p)[i];
+    case ORC_I16: return (double)((const int16_t*)p)[i];
+    case ORC_U16: return (double)((const uint16_t*)p)[i];
+    case ORC_I32: return (double)((const int32_t*)p)[i];
+    case ORC_U32: return (double)((const uint32_t*)p)[i];
+    case ORC_I64: return (double)((const int64_t*)p)[i];
+    case ORC_U64: return (double)((const uint64_t*)p)[i];
+    default: return 0.0;
+  }
+}
+
+static int64_t load_as_i64(const void* p, int d, int64_t i) {
+  switch (d) {
+    case ORC_I8: return ((const int8_t*)p)[i];
+    case ORC_U8: return ((const uint8_t*)p)[i];
+    case ORC_I16: return ((const int16_t*)p)[i];
+    case ORC_U16: return ((const uint16_t*)p)[i];
+    case ORC_I32: return ((const int32_t*)p)[i];
+    case ORC_U32: return ((const uint32_t*)p)[i];
+    case ORC_I64: return ((const int64_t*)p)[i];
+    case ORC_U64: return (int64_t)((const uint64_t*)p)[i];
+    default: return 0;
+  }
+}
+
+/* value -> value rounded to float dtype d (as a double). */
+static double round_to_dtype(double v, int d) {
+  switch (d) {
+    case ORC_F64: return v;
+    case ORC_F32: return (double)(float)v;
+    case ORC_BF16: return (double)orc_bf16_to_f32(orc_bf16_from_f32((float)v));
+    case ORC_F16: return (double)orc_f16_to_f32(orc_f16_from_f32((float)v));
+    default: return v;
+  }
+}
+
+static void store_float(void* p, int d, int64_t i, double v) {
+  switch (d) {
+    case ORC_F64: ((double*)p)[i] = v; break;
+    case ORC_F32: ((float*)p)[i] = (float)v; break;
+    case ORC_BF16: ((uint16_t*)p)[i] = orc_bf16_from_f32((float)v); break;
+    case ORC_F16: ((uint16_t*)p)[i] = orc_f16_from_f32((float)v); break;
+    default: break;
+  }
+}
+
+static void store_int(void* p, int d, int64_t i, int64_t v) {
+  switch (d) {
+    case ORC_I8: ((int8_t*)p)[i] = (int8_t)v; break;
+    case ORC_U8: ((uint8_t*)p)[i] = (uint8_t)v; break;
+    case ORC_I16: ((int16_t*)p)[i] = (int16_t)v; break;
+    case ORC_U16: ((uint16_t*)p)[i] = (uint16_t)v; break;
+    case ORC_I32: ((int32_t*)p)[i] = (int32_t)v; break;
+    case ORC_U32: ((uint32_t*)p)[i] = (uint32_t)v; break;
+    case ORC_I64: ((int64_t*)p)[i] = v; break;
+    case ORC_U64: ((uint64_t*)p)[i] = (uint64_t)v; break;
+    default: break;
+  }
+}
+
+/* Offsets (in elements) of every multi-index over `axes` (row-major in the
+ * order the axes are listed). Returns count; *offs malloc'ed. */
+static int64_t axis_offsets(const int64_t* dims, const int64_t* strides,
+                            const int* axes, int n_axes, int64_t** offs) {
+  int64_t count = 1;
+  for (int i = 0; i < n_axes; i++) count *= dims[axes[i]];
+  *offs = (int64_t*)malloc(sizeof(int64_t) * (size_t)(count > 0 ? count : 1));
+  for (int64_t lin = 0; lin < count; lin++) {
+    int64_t rem = lin, off = 0;
+    for (int i = n_axes - 1; i >= 0; i--) {
+      int64_t d = dims[axes[i]];
+      off += (rem % d) * strides[axes[i]];
+      rem /= d;
+    }
+    (*offs)[lin] = off;
+  }
+  return count;
+}
+
+int orc_dot_general(int in_dtype, const void* lhs, int lhs_rank, const int64_t* lhs_dims,
+                    const int* lhs_contract, const int* lhs_batch,
+                    const void* rhs, int rhs_rank, const int64_t* rhs_dims,
+                    const int* rhs_contract, const int* rhs_batch,
+                    int n_contract, int n_batch,
+                    int acc_dtype, int out_dtype, void* out, int acc_f64) {
+  if (lhs_rank > 16 || rhs_rank > 16 || dtype_size(in_dtype) == 0) return -1;
+  if (out_dtype == 0) out_dtype = in_dtype;
+  for (int i = 0; i < n_contract; i++)
+    if (lhs_dims[lhs_contract[i]] != rhs_dims[rhs_contract[i]]) return -1;
+  for (int i = 0; i < n_batch; i++)
+    if (lhs_dims[lhs_batch[i]] != rhs_dims[rhs_batch[i]]) return -1;
+
+  /* dtype the normalised op computes in (dot.go:207-217, :340-372) */
+  int comp = in_dtype;      /* dtype inputs are (re)rounded to */
+  int acc = in_dtype;       /* accumulation dtype */
+  if (is_half_dtype(in_dtype)) acc = ORC_F32;
+  if (acc_dtype != 0 && acc_dtype != in_dtype && acc_dtype != acc) {
+    comp = acc_dtype;
+    acc = is_half_dtype(acc_dtype) ? ORC_F32 : acc_dtype;
+  }
+  const int float_path = is_float_dtype(comp);
+  if (float_path != is_float_dtype(in_dtype) && !is_int_dtype(in_dtype)) return -2;
+
+  int64_t ls[16], rs[16];
+  { int64_t s = 1; for (int i = lhs_rank - 1; i >= 0; i--) { ls[i] = s; s *= lhs_dims[i]; } }
+  { int64_t s = 1; for (int i = rhs_rank - 1; i >= 0; i--) { rs[i] = s; s *= rhs_dims[i]; } }
+  int lcross[16], rcross[16], nlc = 0, nrc = 0;
+  for (int a = 0; a < lhs_rank; a++) {
+    int used = 0;
+    for (int i = 0; i < n_contract; i++) used |= (lhs_contract[i] == a);
+    for (int i = 0; i < n_batch; i++) used |= (lhs_batch[i] == a);
+    if (!used) lcross[nlc++] = a;
+  }
+  for (int a = 0; a < rhs_rank; a++) {
+    int used = 0;
+    for (int i = 0; i < n_contract; i++) used |= (rhs_contract[i] == a);
+    for (int i = 0; i < n_batch; i++) used |= (rhs_batch[i] == a);
+    if (!used) rcross[nrc++] = a;
+  }
+  int64_t *lb, *rb, *lc, *rc, *lk, *rk;
+  const int64_t nB = axis_offsets(lhs_dims, ls, lhs_batch, n_batch, &lb);
+  axis_offsets(rhs_dims, rs, rhs_batch, n_batch, &rb);
+  const int64_t nM = axis_offsets(lhs_dims, ls, lcross, nlc, &lc);
+  const int64_t nN = axis_offsets(rhs_dims, rs, rcross, nrc, &rc);
+  const int64_t nK = axis_offsets(lhs_dims, ls, lhs_contract, n_contract, &lk);
+  axis_offsets(rhs_dims, rs, rhs_contract, n_contract, &rk);
+
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t b = 0; b < nB; b++) {
+    for (int64_t i = 0; i < nM; i++) {
+      for (int64_t j = 0; j < nN; j++) {
+        const int64_t lo = lb[b] + lc[i], ro = rb[b] + rc[j];
+        const int64_t oi = (b * nM + i) * nN + j;
+        if (float_path) {
+          double result;
+          if (acc_f64 || acc == ORC_F64) {
+            double s = 0.0;
+            for (int64_t c = 0; c < nK; c++) {
+              double a = round_to_dtype(load_as_double(lhs, in_dtype, lo + lk[c]), comp);
+              double bb = round_to_dtype(load_as_double(rhs, in_dtype, ro + rk[c]), comp);
+              s += a * bb;
+            }
+            result = s;
+          } else {
+            float s = 0.0f;
+            for (int64_t c = 0; c < nK; c++) {
+              float a = (float)round_to_dtype(load_as_double(lhs, in_dtype, lo + lk[c]), comp);
+              float bb = (float)round_to_dtype(load_as_double(rhs, in_dtype, ro + rk[c]), comp);
+              float p = a * bb;
+              s = s + p;
+            }
+            result = (double)s;
+          }
+          if (is_float_dtype(out_dtype)) store_float(out, out_dtype, oi, result);
+          else store_int(out, out_dtype, oi, (int64_t)result);
+        } else {
+          int64_t s = 0;
+          for (int64_t c = 0; c < nK; c++)
+            s += load_as_i64(lhs, in_dtype, lo + lk[c]) * load_as_i64(rhs, in_dtype, ro + rk[c]);
+          if (is_float_dtype(out_dtype)) store_float(out, out_dtype, oi, (double)s);
+          else store_int(out, out_dtype, oi, s);
+        }
+      }
+    }
+  }
+  free(lb); free(rb); free(lc); free(rc); free(lk); free(rk);
+  return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* scaled dot-product attention                                       */
+/* ------------------------------------------------------------------ */
+
+/* sdpaComputeMaskStrides, sdpa.go:309-329 */
+static void mask_strides(int rank, const int64_t* d, int64_t* bstride, int64_t* hstride) {
+  *bstride = 0; *hstride = 0;
+  if (rank == 3) {
+    if (d[0] > 1) *bstride = d[1] * d[2];
+  } else if (rank == 4) {
+    if (d[0] > 1) *bstride = d[1] * d[2] * d[3];
+    if (d[1] > 1) *hstride = d[2] * d[3];
+  }
+}
+
+/* One (batch, kv head) group: sdpaGeneric, sdpa.go:373-519. */
+static void sdpa_group(const float* q, const float* k, const float* v,
+                       int64_t q_off, int64_t kv_off, int64_t q_seq_stride, int64_t kv_seq_stride,
+                       int64_t q_group_stride,
+                       const float* add_mask, const uint8_t* bool_mask, int64_t mask_group_stride,
+                       const float* add_bias, int64_t bias_group_stride,
+                       float* scores, float* out,
+                       int64_t group, int64_t S, int64_t Skv, int64_t D, float scale, int causal,
+                       int64_t q_limit, int64_t kv_limit) {
+  for (int64_t g = 0; g < group; g++) {
+    const int64_t gq = q_off + g * q_group_stride;
+    for (int64_t qi = 0; qi < S; qi++) {
+      const int64_t row = gq + qi * q_seq_stride;
+      if (qi >= q_limit) {               /* padded query row -> zeros */
+        for (int64_t d = 0; d < D; d++) out[row + d] = 0.0f;
+        continue;
+      }
+      float* sc = scores + (g * S + qi) * Skv;
+      const int64_t mrow = g * mask_group_stride + qi * Skv;
+      const int64_t brow = g * bias_group_stride + qi * Skv;
+      int64_t live = Skv < kv_limit ? Skv : kv_limit;
+      if (causal && qi + 1 < live) live = qi + 1;
+      float row_max = -INFINITY;
+      for (int64_t j = 0; j < Skv; j++) sc[j] = 0.0f;
+      for (int64_t j = 0; j < live; j++) {
+        if (bool_mask && !bool_mask[mrow + j]) continue;
+        float dot = 0.0f;
+        const float* kr = k + kv_off + j * kv_seq_stride;
+        for (int64_t d = 0; d < D; d++) {
+          float p = q[row + d] * kr[d];
+          dot = dot + p;
+        }
+        float s = dot * scale;
+        if (add_bias) s = s + add_bias[brow + j];
+        if (add_mask) s = s + add_mask[mrow + j];
+        sc[j] = s;
+        if (s > row_max) row_max = s;
+      }
+      float sum = 0.0f;
+      for (int64_t j = 0; j < live; j++) {
+        if (bool_mask && !bool_mask[mrow + j]) continue;
+        sc[j] = (float)exp((double)(sc[j] - row_max));
+        sum = sum + sc[j];
+      }
+      const float inv = (sum != 0.0f) ? 1.0f / sum : 0.0f;  /* all-masked row -> zeros */
+      for (int64_t j = 0; j < live; j++) {
+        if (bool_mask && !bool_mask[mrow + j]) sc[j] = 0.0f;
+        else sc[j] = sc[j] * inv;
+      }
+      for (int64_t d = 0; d < D; d++) {
+        float acc = 0.0f;
+        for (int64_t j = 0; j < live; j++) {
+          if (bool_mask && !bool_mask[mrow + j]) continue;
+          float p = sc[j] * v[kv_off + j * kv_seq_stride + d];
+          acc = acc + p;
+        }
+        out[row + d] = acc;
+      }
+    }
+  }
+}
+
+static void sdpa_impl(const float* q, const float* k, const float* v,
+                      const void* mask, int mask_is_bool, int mask_rank, const int64_t* mask_dims,
+                      const float* bias, int bias_rank, const int64_t* bias_dims,
+                      const int32_t* q_len, const int32_t* kv_len, float* out,
+                      int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t Skv, int64_t D,
+                      int bshd, double scale, int causal,
+                      int64_t b0, int64_t b1, int64_t h0, int64_t h1) {
+  const int64_t group = Hq / Hkv;
+  int64_t q_seq, kv_seq, q_head, kv_head, q_batch, kv_batch;
+  if (bshd) {   /* [B,S,H,D], sdpa.go:554-566 */
+    q_seq = Hq * D; kv_seq = Hkv * D; q_head = D; kv_head = D;
+    q_batch = S * Hq * D; kv_batch = Skv * Hkv * D;
+  } else {      /* [B,H,S,D], sdpa.go:567-578 */
+    q_seq = D; kv_seq = D; q_head = S * D; kv_head = Skv * D;
+    q_batch = Hq * S * D; kv_batch = Hkv * Skv * D;
+  }
+  int64_t mb = 0, mh = 0, bb = 0, bh = 0;
+  if (mask) mask_strides(mask_rank, mask_dims, &mb, &mh);
+  if (bias) mask_strides(bias_rank, bias_dims, &bb, &bh);
+  float* scores = (float*)malloc(sizeof(float) * (size_t)(group * S * Skv > 0 ? group * S * Skv : 1));
+  for (int64_t b = b0; b < b1; b++) {
+    int64_t q_limit = S, kv_limit = Skv;
+    if (q_len) { int64_t l = q_len[b]; q_limit = l < 0 ? 0 : (l > S ? S : l); }
+    if (kv_len) { int64_t l = kv_len[b]; kv_limit = l < 0 ? 0 : (l > Skv ? Skv : l); }
+    for (int64_t h = h0; h < h1; h++) {
+      const int64_t q_off = b * q_batch + h * group * q_head;
+      const int64_t kv_off = b * kv_batch + h * kv_head;
+      const float* am = NULL; const uint8_t* bm = NULL; int64_t mgs = 0;
+      if (mask) {
+        const int64_t off = b * mb + h * group * mh;
+        if (mh > 0 && group > 1) mgs = mh;
+        if (mask_is_bool) bm = (const uint8_t*)mask + off; else am = (const float*)mask + off;
+      }
+      const float* ab = NULL; int64_t bgs = 0;
+      if (bias) {
+        ab = bias + b * bb + h * group * bh;
+        if (bh > 0 && group > 1) bgs = bh;
+      }
+      sdpa_group(q, k, v, q_off, kv_off, q_seq, kv_seq, q_head, am, bm, mgs, ab, bgs,
+                 scores, out, group, S, Skv, D, (float)scale, causal, q_limit, kv_limit);
+    }
+  }
+  free(scores);
+}
+
+void orc_sdpa_f32(const float* q, const float* k, const float* v,
+                  const void* mask, int mask_is_bool, int mask_rank, const int64_t* mask_dims,
+                  const float* bias, int bias_rank, const int64_t* bias_dims,
+                  const int32_t* q_len, const int32_t* kv_len, float* out,
+                  int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t Skv, int64_t D,
+                  int bshd, double scale, int causal) {
+  if (scale == 0.0) scale = 1.0 / sqrt((double)D);   /* sdpa.go:155-158 */
+  sdpa_impl(q, k, v, mask, mask_is_bool, mask_rank, mask_dims, bias, bias_rank, bias_dims,
+            q_len, kv_len, out, B, Hq, Hkv, S, Skv, D, bshd, scale, causal, 0, B, 0, Hkv);
+}
+
+void orc_sdpa_f32_slice(const float* q, const float* k, const float* v, float* out,
+                        int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t Skv, int64_t D,
+                        int bshd, double scale, int causal,
+                        int64_t b0, int64_t b1, int64_t h0, int64_t h1) {
+  if (scale == 0.0) scale = 1.0 / sqrt((double)D);
+  sdpa_impl(q, k, v, NULL, 0, 0, NULL, NULL, 0, NULL, NULL, NULL, out,
+            B, Hq, Hkv, S, Skv, D, bshd, scale, causal, b0, b1, h0, h1);
+}
+
+/* ------------------------------------------------------------------ */
+/* blocked f32 GEMM (timed CPU baseline for DotGeneral)               */
+/* ------------------------------------------------------------------ */
+
+#define GB_MR 4
+#define GB_NR 32
+#define GB_KC 128
+#define GB_MC 24
+#define GB_NC 512
+
+/* Register-tile update: acc[MR][NR] += Apanel[kc][MR] (x) Bpanel[kc][NR].
+ * Cloned per ISA so the prebuilt library runs on whatever host it lands on. */
+__attribute__((target_clones("avx512f", "avx2,fma", "default")))
+static void gb_micro(const float* ap, const float* bp, float* c, int64_t ldc, int64_t kc,
+                     int64_t mr, int64_t nr, int overwrite) {
+  float acc[GB_MR][GB_NR];
+  for (int i = 0; i < GB_MR; i++)
+    for (int j = 0; j < GB_NR; j++) acc[i][j] = 0.0f;
+  for (int64_t p = 0; p < kc; p++) {
+    const float* a = ap + p * GB_MR;
+    const float* b = bp + p * GB_NR;
+    for (int i = 0; i < GB_MR; i++) {
+      const float av = a[i];
+      for (int j = 0; j < GB_NR; j++) acc[i][j] += av * b[j];
+    }
+  }
+  for (int64_t i = 0; i < mr; i++)
+    for (int64_t j = 0; j < nr; j++) {
+      if (overwrite) c[i * ldc + j] = acc[i][j];
+      else c[i * ldc + j] += acc[i][j];
+    }
+}
+
+void orc_gemm_f32_blocked(const float* A, const float* B, float* C,
+                          int64_t M, int64_t K, int64_t N, int threads) {
+  if (threads < 1) threads = 1;
+  const int64_t n_jc = (N + GB_NC - 1) / GB_NC;
+#pragma omp parallel num_threads(threads)
+  {
+    float* bpack = (float*)aligned_alloc(64, sizeof(float) * GB_KC * GB_NC);
+    float* apack = (float*)aligned_alloc(64, sizeof(float) * GB_KC * (GB_MC + GB_MR));
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t jc_i = 0; jc_i < n_jc; jc_i++) {
+      const int64_t jc = jc_i * GB_NC;
+      const int64_t nc = (N - jc) < GB_NC ? (N - jc) : GB_NC;
+      for (int64_t pc = 0; pc < K; pc += GB_KC) {
+        const int64_t kc = (K - pc) < GB_KC ? (K - pc) : GB_KC;
+        /* pack rhs panel: [ceil(nc/NR)][kc][NR], zero padded */
+        for (int64_t jr = 0; jr < nc; jr += GB_NR) {
+          float* dst = bpack + (jr / GB_NR) * kc * GB_NR;
+          for (int64_t p = 0; p < kc; p++)
+            for (int64_t j = 0; j < GB_NR; j++)
+              dst[p * GB_NR + j] = (jr + j < nc) ? B[(pc + p) * N + jc + jr + j] : 0.0f;
+        }
+        for (int64_t ic = 0; ic < M; ic += GB_MC) {
+          const int64_t mc = (M - ic) < GB_MC ? (M - ic) : GB_MC;
+          for (int64_t ir = 0; ir < mc; ir += GB_MR) {
+            float* dst = apack + (ir / GB_MR) * kc * GB_MR;
+            for (int64_t p = 0; p < kc; p++)
+              for (int64_t i = 0; i < GB_MR; i++)
+                dst[p * GB_MR + i] = (ir + i < mc) ? A[(ic + ir + i) * K + pc + p] : 0.0f;
+          }
+          for (int64_t jr = 0; jr < nc; jr += GB_NR)
+            for (int64_t ir = 0; ir < mc; ir += GB_MR) {
+              const int64_t mr = (mc - ir) < GB_MR ? (mc - ir) : GB_MR;
+              const int64_t nr = (nc - jr) < GB_NR ? (nc - jr) : GB_NR;
+              gb_micro(apack + (ir / GB_MR) * kc * GB_MR, bpack + (jr / GB_NR) * kc * GB_NR,
+                       C + (ic + ir) * N + jc + jr, N, kc, mr, nr, pc == 0);
+            }
+        }
+      }
+    }
+    free(bpack);
+    free(apack);
+  }
+}

@@ -1,0 +1,299 @@
+"""ctypes/numpy front end of the CPU oracle — TEST INFRASTRUCTURE ONLY.
+
+Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may
+import this module; the product package never does.  See oracle.h for which
+reference function each entry point restates and how parity is pinned
+(FusedQuantizedDense: parity unpinned — the reference has no asserting test).
+
+Half-precision arrays travel as ``np.uint16`` bit patterns together with an
+explicit dtype code (the codes of gomlx/compute dtypes/dtype_enum.go:18-120).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+BOOL, I8, I16, I32, I64, U8, U16, U32, U64, F16, F32, F64, BF16 = range(1, 14)
+ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
+
+_NP_OF = {BOOL: np.bool_, I8: np.int8, I16: np.int16, I32: np.int32, I64: np.int64,
+          U8: np.uint8, U16: np.uint16, U32: np.uint32, U64: np.uint64,
+          F16: np.uint16, F32: np.float32, F64: np.float64, BF16: np.uint16}
+
+
+def build(force: bool = False) -> None:
+    """Compile liboracle.so / liboracle_fast.so with the Makefile beside this file."""
+    need = force or not all(os.path.exists(os.path.join(HERE, n))
+                            for n in ("liboracle.so", "liboracle_fast.so"))
+    if need:
+        subprocess.run(["make", "-C", HERE, "-s"] + (["-B"] if force else []), check=True)
+
+
+_libs: dict = {}
+
+
+def lib(fast: bool = False):
+    name = "liboracle_fast.so" if fast else "liboracle.so"
+    if name not in _libs:
+        path = os.path.join(HERE, name)
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.orc_bf16_from_f32_n.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_bf16_to_f32_n.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_f16_from_f32.argtypes = [C.c_float]
+        L.orc_f16_from_f32.restype = C.c_uint16
+        L.orc_f16_to_f32.argtypes = [C.c_uint16]
+        L.orc_f16_to_f32.restype = C.c_float
+        L.orc_qdense_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_int, C.c_int]
+        L.orc_activation_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_int]
+        L.orc_dot_general.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.orc_dot_general.restype = C.c_int
+        L.orc_sdpa_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_int, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                   C.c_int, C.c_double, C.c_int]
+        L.orc_sdpa_f32_slice.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                         C.c_int, C.c_double, C.c_int,
+                                         C.c_int64, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_gemm_f32_blocked.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_int64, C.c_int64, C.c_int64, C.c_int]
+        L.orc_max_threads.restype = C.c_int
+        _libs[name] = L
+    return _libs[name]
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+# ---------------------------------------------------------------- half types
+def bf16_from_f32(a) -> np.ndarray:
+    a = _c(a, np.float32)
+    out = np.empty(a.shape, np.uint16)
+    lib().orc_bf16_from_f32_n(_p(a), _p(out), a.size)
+    return out
+
+
+def bf16_to_f32(a) -> np.ndarray:
+    a = _c(a, np.uint16)
+    out = np.empty(a.shape, np.float32)
+    lib().orc_bf16_to_f32_n(_p(a), _p(out), a.size)
+    return out
+
+
+def f16_from_f32(a) -> np.ndarray:
+    a = _c(a, np.float32)
+    L = lib()
+    return np.array([L.orc_f16_from_f32(float(v)) for v in a.ravel()], np.uint16).reshape(a.shape)
+
+
+def f16_to_f32(a) -> np.ndarray:
+    a = _c(a, np.uint16)
+    L = lib()
+    return np.array([L.orc_f16_to_f32(int(v)) for v in a.ravel()], np.float32).reshape(a.shape)
+
+
+def to_f32(a, dtype: int) -> np.ndarray:
+    if dtype == BF16:
+        return bf16_to_f32(a)
+    if dtype == F16:
+        return np.asarray(a, np.uint16).view(np.float16).astype(np.float32)
+    return np.asarray(a).astype(np.float32)
+
+
+def from_f32(a, dtype: int) -> np.ndarray:
+    if dtype == BF16:
+        return bf16_from_f32(a)
+    if dtype == F16:
+        return np.asarray(a, np.float32).astype(np.float16).view(np.uint16)
+    return np.asarray(a).astype(_NP_OF[dtype])
+
+
+# ---------------------------------------------------------------- quantized dense
+def expand_scales(scales, layout: str, K: int, N: int, group: int = 0) -> np.ndarray:
+    """Compact scale layouts -> the reference form ``[K, N]`` with BlockSize = 1.
+
+    ``layout``: "channel" (``[N]``, one scale per output column) or "kgroup"
+    (``[K/group, N]``, one scale per `group` consecutive input rows and column).
+    The expanded tensor makes the reference arithmetic element-wise identical.
+    """
+    s = np.asarray(scales, np.float32)
+    if layout == "channel":
+        return np.ascontiguousarray(np.broadcast_to(s.reshape(1, N), (K, N)))
+    if layout == "kgroup":
+        return np.ascontiguousarray(np.repeat(s.reshape(-1, N), group, axis=0)[:K])
+    raise ValueError(layout)
+
+
+def qdense_linear(x, w, scales, zero_points=None, bias=None, block_size: int = 1,
+                  activation: int = ACT_NONE, threads: int = 1, fast: bool = False) -> np.ndarray:
+    """Reference FusedQuantizedDense, Linear scheme (quantizeddense.go:616-650)."""
+    x = _c(x, np.float32)
+    K = x.shape[-1]
+    M = x.size // K if K else 0
+    w = np.ascontiguousarray(w)
+    assert w.dtype in (np.int8, np.uint8) and w.shape[0] == K
+    N = w.shape[1]
+    nblk = (N + block_size - 1) // block_size
+    scales = _c(scales, np.float32)
+    assert scales.shape == (K, nblk), (scales.shape, (K, nblk))
+    zp = None if zero_points is None else _c(zero_points, np.float32)
+    b = None if bias is None else _c(bias, np.float32)
+    out = np.empty(x.shape[:-1] + (N,), np.float32)
+    lib(fast).orc_qdense_linear(_p(x), _p(w), int(w.dtype == np.uint8), _p(scales), _p(zp), _p(b),
+                                _p(out), M, K, N, block_size, activation, threads)
+    return out
+
+
+def activation_f64(y: np.ndarray, activation: int) -> np.ndarray:
+    """Mathematical definition of the activations in float64 (an independent check)."""
+    from math import erf
+    y = np.asarray(y, np.float64)
+    if activation == ACT_NONE:
+        return y
+    if activation == ACT_RELU:
+        return np.maximum(y, 0)
+    if activation == ACT_SILU:
+        return y / (1.0 + np.exp(-y))
+    if activation == ACT_TANH:
+        return np.tanh(y)
+    if activation == ACT_HARDSWISH:
+        return y * np.clip(y / 6.0 + 0.5, 0, 1)
+    if activation == ACT_GELU:
+        return y * 0.5 * (1.0 + np.vectorize(erf)(y / np.sqrt(2.0)))
+    raise ValueError(activation)
+
+
+def qdense_decomposed(x, w, scales, zero_points=None, bias=None, block_size: int = 1,
+                      activation: int = ACT_NONE) -> np.ndarray:
+    """The reference's decomposed formulation (benchmarks.go:510-545) in float64:
+    dequantise the weights, matmul, add bias, activation.  Independent of the
+    fused loop order, so it cross-checks the restatement above."""
+    x = np.asarray(x, np.float64)
+    w = np.asarray(w)
+    K, N = w.shape
+    cols = np.arange(N) // block_size
+    wd = w.astype(np.float64) * np.asarray(scales, np.float64)[:, cols]
+    if zero_points is not None:
+        wd = wd + np.asarray(zero_points, np.float64)[:, cols]
+    y = x.reshape(-1, K) @ wd
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)[None, :]
+    return activation_f64(y, activation).reshape(x.shape[:-1] + (N,))
+
+
+# ---------------------------------------------------------------- DotGeneral
+def dot_output_dims(lhs_dims, lhs_contract, lhs_batch, rhs_dims, rhs_contract, rhs_batch):
+    """shapeinference/dotgeneral.go:99-147: batch..., lhs cross..., rhs cross..."""
+    out = [lhs_dims[a] for a in lhs_batch]
+    out += [d for a, d in enumerate(lhs_dims) if a not in lhs_contract and a not in lhs_batch]
+    out += [d for a, d in enumerate(rhs_dims) if a not in rhs_contract and a not in rhs_batch]
+    return out
+
+
+def dot_general(lhs, lhs_contract, lhs_batch, rhs, rhs_contract, rhs_batch, in_dtype: int,
+                acc_dtype: int = 0, out_dtype: int = 0, acc_f64: bool = False) -> np.ndarray:
+    lhs = _c(lhs, _NP_OF[in_dtype])
+    rhs = _c(rhs, _NP_OF[in_dtype])
+    od = out_dtype or in_dtype
+    dims = dot_output_dims(list(lhs.shape), list(lhs_contract), list(lhs_batch),
+                           list(rhs.shape), list(rhs_contract), list(rhs_batch))
+    out = np.empty(dims, _NP_OF[od])
+    ld = np.array(lhs.shape, np.int64)
+    rd = np.array(rhs.shape, np.int64)
+    lc = np.array(list(lhs_contract), np.int32)
+    lb = np.array(list(lhs_batch), np.int32)
+    rc = np.array(list(rhs_contract), np.int32)
+    rb = np.array(list(rhs_batch), np.int32)
+    rcode = lib().orc_dot_general(in_dtype, _p(lhs), lhs.ndim, _p(ld), _p(lc), _p(lb),
+                                  _p(rhs), rhs.ndim, _p(rd), _p(rc), _p(rb),
+                                  len(lc), len(lb), acc_dtype, od, _p(out), int(acc_f64))
+    if rcode != 0:
+        raise ValueError(f"orc_dot_general failed: {rcode}")
+    return out
+
+
+def gemm_f32_blocked(a, b, threads: int) -> np.ndarray:
+    a = _c(a, np.float32)
+    b = _c(b, np.float32)
+    out = np.empty((a.shape[0], b.shape[1]), np.float32)
+    lib(True).orc_gemm_f32_blocked(_p(a), _p(b), _p(out), a.shape[0], a.shape[1], b.shape[1], threads)
+    return out
+
+
+# ---------------------------------------------------------------- SDPA
+def sdpa(q, k, v, mask=None, bias=None, q_len=None, kv_len=None, layout: str = "BHSD",
+         scale: float = 0.0, causal: bool = False, fast: bool = False) -> np.ndarray:
+    """Reference fused SDPA on float32 (sdpa.go:373-636)."""
+    q = _c(q, np.float32)
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    bshd = int(layout == "BSHD")
+    if bshd:
+        B, S, Hq, D = q.shape
+        Skv, Hkv = k.shape[1], k.shape[2]
+    else:
+        B, Hq, S, D = q.shape
+        Hkv, Skv = k.shape[1], k.shape[2]
+    m = md = None
+    mbool = 0
+    if mask is not None:
+        mask = np.asarray(mask)
+        if bshd and mask.ndim == 4:       # sdpa.go:259-274: [B,S,H,Skv] -> [B,H,S,Skv]
+            mask = mask.transpose(0, 2, 1, 3)
+        mbool = int(mask.dtype == np.bool_)
+        m = np.ascontiguousarray(mask, np.uint8 if mbool else np.float32)
+        md = np.array(m.shape, np.int64)
+    bs = bd = None
+    if bias is not None:
+        bias = np.asarray(bias, np.float32)
+        if bshd and bias.ndim == 4:
+            bias = bias.transpose(0, 2, 1, 3)
+        bs = np.ascontiguousarray(bias)
+        bd = np.array(bs.shape, np.int64)
+    ql = None if q_len is None else _c(q_len, np.int32)
+    kl = None if kv_len is None else _c(kv_len, np.int32)
+    out = np.empty_like(q)
+    lib(fast).orc_sdpa_f32(_p(q), _p(k), _p(v), _p(m), mbool, 0 if m is None else m.ndim, _p(md),
+                           _p(bs), 0 if bs is None else bs.ndim, _p(bd), _p(ql), _p(kl), _p(out),
+                           B, Hq, Hkv, S, Skv, D, bshd, float(scale), int(causal))
+    return out
+
+
+def sdpa_slice(q, k, v, b0, b1, h0, h1, layout="BHSD", scale=0.0, causal=False) -> np.ndarray:
+    """Only batches [b0,b1) and kv heads [h0,h1) are computed (others left zero)."""
+    q = _c(q, np.float32)
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    bshd = int(layout == "BSHD")
+    if bshd:
+        B, S, Hq, D = q.shape
+        Skv, Hkv = k.shape[1], k.shape[2]
+    else:
+        B, Hq, S, D = q.shape
+        Hkv, Skv = k.shape[1], k.shape[2]
+    out = np.zeros_like(q)
+    lib(True).orc_sdpa_f32_slice(_p(q), _p(k), _p(v), _p(out), B, Hq, Hkv, S, Skv, D, bshd,
+                                 float(scale), int(causal), b0, b1, h0, h1)
+    return out

@@ -1,0 +1,213 @@
+"""CPU tests that pin the oracle: the reference's own known-answer vectors
+(tests/golden/, transcribed from the reference's asserting tests) and, for the
+quantized dense op the reference never asserts, hand-computed cases plus the
+reference's decomposed formulation."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.helpers import ACT, DT, as_f64, load_golden, max_abs_normalised, qdense_inputs, tensor
+
+DOT = load_golden("backendtest_dotgeneral.json")["cases"]
+SDPA = load_golden("backendtest_sdpa.json")["cases"]
+DENSE = load_golden("backendtest_dense_epilogue.json")["cases"]
+
+
+# ---------------------------------------------------------------- bf16 / f16
+def test_bf16_known_answers():
+    # dtypes/bfloat16/bfloat16_test.go:10-60
+    for v in [0, 1, -1, 0.5, 1.5, 100, 1000, np.inf, -np.inf]:
+        assert orc.bf16_to_f32(orc.bf16_from_f32(np.float32(v))) == np.float32(v)
+    assert orc.bf16_to_f32(orc.bf16_from_f32(np.float32(65504))) == 65536
+    assert np.isnan(orc.bf16_to_f32(orc.bf16_from_f32(np.float32(np.nan))))
+    assert orc.bf16_from_f32(np.float32(1.0)) == 0x3F80
+    # ties to even: 1 + 2^-8 is halfway between 0x3F80 and 0x3F81 -> even (0x3F80)
+    assert orc.bf16_from_f32(np.float32(1.0 + 2.0 ** -8)) == 0x3F80
+    assert orc.bf16_from_f32(np.float32(1.0 + 3 * 2.0 ** -8)) == 0x3F82
+
+
+def test_f16_matches_ieee():
+    rng = np.random.default_rng(1)
+    v = np.concatenate([rng.standard_normal(2000).astype(np.float32) * 100,
+                        np.float32([0, -0.0, 65504, 65520, 1e-8, 6.2e-5, np.inf, -np.inf])])
+    with np.errstate(over="ignore"):
+        want = v.astype(np.float16).view(np.uint16)
+    assert np.array_equal(orc.f16_from_f32(v), want)
+    assert np.array_equal(orc.f16_to_f32(want), want.view(np.float16).astype(np.float32))
+    # The reference's FromFloat32 shifts subnormal results by (14 - exp) bits
+    # (dtypes/float16/float16.go:131-143), which flushes them to zero; the
+    # restatement keeps that behaviour.  Subnormal *inputs* still widen exactly.
+    assert orc.f16_from_f32(np.float32([6.0e-5]))[0] == 0
+    sub = np.uint16([0x0001, 0x03FF, 0x8200])
+    assert np.array_equal(orc.f16_to_f32(sub), sub.view(np.float16).astype(np.float32))
+
+
+# ---------------------------------------------------------------- DotGeneral
+@pytest.mark.parametrize("case", DOT, ids=[c["name"] for c in DOT])
+def test_dot_general_golden(case):
+    code = DT[case["dtype"]]
+    lhs = tensor(case["lhs"], case["dtype"])
+    rhs = tensor(case["rhs"], case["dtype"])
+    acc = DT[case["acc"]] if "acc" in case else 0
+    out = DT[case["out"]] if "out" in case else 0
+    got = orc.dot_general(lhs, case["lhs_contract"], case["lhs_batch"],
+                          rhs, case["rhs_contract"], case["rhs_batch"], code, acc, out)
+    assert list(got.shape) == case["want"]["shape"]
+    g = as_f64(got, out or code).ravel()
+    w = np.array(case["want"]["data"], np.float64)
+    if case["cmp"] == "equal":
+        assert np.array_equal(g, w)
+    else:
+        assert np.max(np.abs(g - w)) <= case["tol"]
+
+
+def test_dot_general_f64_very_large():
+    # support/backendtest/dotgeneral.go:132-159: out[0,0,0] = sum_{i<384} (i+1)*1e-5 = 0.7392
+    lhs = (np.arange(16 * 13 * 384, dtype=np.float64) + 1.0) * 1e-5
+    lhs = lhs.reshape(16, 13, 384)
+    rhs = np.ones((384, 1536), np.float64)
+    got = orc.dot_general(lhs, [2], [], rhs, [0], [], orc.F64)
+    assert got.shape == (16, 13, 1536)
+    assert abs(got[0, 0, 0] - 0.7392) < 1e-4
+
+
+def transposed_large_inputs():
+    """Inputs and f64 reference of support/backendtest/dotgeneral.go:499-560."""
+    g_idx = np.arange(4 * 32 * 8 * 2, dtype=np.float64).reshape(4, 32, 8, 2, 1)
+    lhs = np.broadcast_to((g_idx.astype(np.float32) * np.float32(0.0001)), (4, 32, 8, 2, 256))
+    lhs = np.ascontiguousarray(lhs, np.float32)
+    rhs = (np.arange(4 * 32 * 8 * 256).astype(np.float32) * np.float32(0.0001)).reshape(4, 32, 8, 256)
+    want = np.einsum("bqhgd,bkhd->bhqgk", lhs.astype(np.float64), rhs.astype(np.float64)).astype(np.float32)
+    return lhs, rhs, want
+
+
+def check_transposed_large(got, want):
+    diff = np.abs(want.astype(np.float64) - got.astype(np.float64))
+    ok = (diff <= 0.5) | ((np.abs(want) > 0) & (diff / np.maximum(np.abs(want), 1e-30) < 0.03))
+    assert ok.all()
+
+
+def test_dot_general_transposed_large():
+    lhs, rhs, want = transposed_large_inputs()
+    got = orc.dot_general(lhs, [4], [0, 2], rhs, [3], [0, 2], orc.F32)
+    assert got.shape == (4, 8, 32, 2, 32)
+    check_transposed_large(got, want)
+
+
+def test_dot_general_dtype_sweep():
+    # dotgeneral.go:444-497: iota(16) . iota(16) = 1240 for every supported combination
+    for name in ("f32", "f64", "bf16", "f16"):
+        code = DT[name]
+        v = orc.from_f32(np.arange(16, dtype=np.float32), code) if code in (orc.BF16, orc.F16) \
+            else np.arange(16).astype({orc.F32: np.float32, orc.F64: np.float64}[code])
+        for out in (0, orc.F32, orc.F64):
+            got = orc.dot_general(v, [0], [], v, [0], [], code, 0, out)
+            assert float(as_f64(got, out or code).ravel()[0]) == 1240.0
+
+
+# ---------------------------------------------------------------- SDPA
+@pytest.mark.parametrize("case", SDPA, ids=[c["name"] for c in SDPA])
+def test_sdpa_golden(case):
+    code = DT[case["dtype"]]
+    up = lambda key: as_f64(tensor(case[key], case["dtype"]), code).astype(np.float32)
+    mask = tensor(case["mask"], "bool") if "mask" in case else None
+    bias = up("bias") if "bias" in case else None
+    got = orc.sdpa(up("q"), up("k"), up("v"), mask=mask, bias=bias,
+                   q_len=case.get("q_len"), kv_len=case.get("kv_len"),
+                   layout=case["layout"], scale=case["scale"], causal=case["causal"])
+    if code in (orc.BF16, orc.F16):      # half inputs: upcast, f32 arithmetic, round to the half type
+        got = orc.to_f32(orc.from_f32(got, code), code)
+    want = np.array(case["want"]["data"], np.float64).reshape(case["want"]["shape"])
+    assert np.max(np.abs(got - want)) <= case["tol"]
+
+
+def test_sdpa_gqa_matches_numpy():
+    rng = np.random.default_rng(7)
+    B, Hq, Hkv, S, Skv, D = 2, 4, 2, 5, 7, 8
+    q = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32)
+    bias = rng.standard_normal((B, Hq, S, Skv), dtype=np.float32)
+    got = orc.sdpa(q, k, v, bias=bias, scale=0.0, causal=False)
+    kk = np.repeat(k, Hq // Hkv, axis=1).astype(np.float64)
+    vv = np.repeat(v, Hq // Hkv, axis=1).astype(np.float64)
+    s = np.einsum("bhsd,bhtd->bhst", q.astype(np.float64), kk) / np.sqrt(D) + bias
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bhst,bhtd->bhsd", p, vv)
+    assert max_abs_normalised(got, want) < 1e-5
+    # BSHD gives the same numbers in the other layout
+    got2 = orc.sdpa(q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3),
+                    bias=bias.transpose(0, 2, 1, 3), layout="BSHD")
+    assert np.array_equal(got2.transpose(0, 2, 1, 3), got)
+
+
+# ---------------------------------------------------------------- quantized dense
+@pytest.mark.parametrize("case", DENSE, ids=[c["name"] for c in DENSE])
+def test_dense_epilogue_golden(case):
+    """fusedops.go:178-212 pins bias-then-activation; with unit scales the
+    quantized op must reproduce those numbers exactly."""
+    x = tensor(case["x"], "f32")
+    w = tensor(case["w"], "i8")
+    K, N = w.shape
+    got = orc.qdense_linear(x, w, np.ones((K, N), np.float32), None,
+                            np.array(case["bias"], np.float32), 1, ACT[case["activation"]])
+    assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
+
+
+def test_qdense_hand_computed():
+    # K=2, N=4, BlockSize=2, power-of-two scales: every product is exact.
+    x = np.float32([[1, 2], [-3, 0.5]])
+    w = np.int8([[1, -2, 3, 4], [5, 6, -7, 8]])
+    s = np.float32([[0.5, 2.0], [0.25, 1.0]])          # [K, N/2]
+    bias = np.float32([1, 1, -1, 0])
+    want = np.float32([[1 + 0.5 + 2.5, 1 - 1 + 3, -1 + 6 - 14, 8 + 16],
+                       [1 - 1.5 + 0.625, 1 + 3 + 0.75, -1 - 18 - 3.5, -24 + 4]])
+    got = orc.qdense_linear(x, w, s, None, bias, 2, orc.ACT_NONE)
+    assert np.array_equal(got, want)
+    zp = np.float32([[1, 0], [0, -1]])
+    want_zp = want + np.float32([[1, 1, -2, -2], [-3, -3, -0.5, -0.5]])
+    assert np.array_equal(orc.qdense_linear(x, w, s, zp, bias, 2, orc.ACT_NONE), want_zp)
+    # uint8 weights
+    wu = np.uint8([[200, 0, 3, 4], [5, 255, 7, 8]])
+    got_u = orc.qdense_linear(x, wu, s, None, None, 2, orc.ACT_RELU)
+    want_u = np.maximum(x.astype(np.float64) @ (wu.astype(np.float64) * s[:, [0, 0, 1, 1]]), 0)
+    assert np.array_equal(got_u, want_u.astype(np.float32))
+
+
+@pytest.mark.parametrize("act", list(ACT))
+@pytest.mark.parametrize("block", [1, 3, 16, 40])
+def test_qdense_matches_decomposed(act, block):
+    K, N, M = 96, 40, 5
+    x, w, s, b = qdense_inputs(11 + block, M, K, N, scale_layout="ref", block_size=block)
+    rng = np.random.default_rng(5)
+    zp = rng.uniform(-0.05, 0.05, size=s.shape).astype(np.float32)
+    for z in (None, zp):
+        got = orc.qdense_linear(x, w, s, z, b, block, ACT[act])
+        want = orc.qdense_decomposed(x, w, s, z, b, block, ACT[act])
+        assert max_abs_normalised(got, want) < 1e-5
+
+
+def test_qdense_thread_split_is_bit_identical():
+    for M in (1, 3):
+        x, w, s, b = qdense_inputs(3, M, 256, 300, scale_layout="ref", block_size=7)
+        one = orc.qdense_linear(x, w, s, None, b, 7, orc.ACT_SILU, threads=1)
+        many = orc.qdense_linear(x, w, s, None, b, 7, orc.ACT_SILU, threads=4)
+        fast = orc.qdense_linear(x, w, s, None, b, 7, orc.ACT_SILU, threads=4, fast=True)
+        assert np.array_equal(one, many) and np.array_equal(one, fast)
+
+
+def test_expand_scales_layouts():
+    s = np.arange(6, dtype=np.float32).reshape(2, 3)
+    e = orc.expand_scales(s, "kgroup", 4, 3, group=2)
+    assert e.shape == (4, 3) and np.array_equal(e[0], e[1]) and np.array_equal(e[2], s[1])
+    c = orc.expand_scales(np.float32([1, 2, 3]), "channel", 4, 3)
+    assert c.shape == (4, 3) and np.array_equal(c[3], [1, 2, 3])
+
+
+def test_blocked_gemm_baseline_is_a_gemm():
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((70, 300), dtype=np.float32)
+    b = rng.standard_normal((300, 530), dtype=np.float32)
+    got = orc.gemm_f32_blocked(a, b, threads=2)
+    assert max_abs_normalised(got, a.astype(np.float64) @ b.astype(np.float64)) < 1e-5
