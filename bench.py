@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: decode-shaped int8 quantized dense on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m 16] [--impl reference]
+
+Workload (BASELINE config 3): x bf16 [M, 4096], W int8 [4096, 14336], group-128
+float32 scales along K, SiLU, output bf16.  One *step* runs the projection for
+LAYERS distinct weight matrices (LAYERS x 58.7 MB > the 126 MB L2, so every
+launch streams its weights from HBM).  With N GPUs the projection is sharded
+along N (each rank holds columns [r*N/g, (r+1)*N/g) of every layer; x is
+replicated) and the per-rank output slices are all-gathered once per step.
+
+Prints ONE JSON line (rank 0).  `value` = algorithmic bytes of the whole job per
+second with inputs resident in HBM; `e2e` = the same metric with the per-step
+activations copied from pinned host memory and the results copied back inside
+the timed region (weights stay resident, as model parameters do).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM, N_DIM, GROUP = 4096, 14336, 128
+LAYERS = 8
+METRIC = "int8 quantized-dense GB/s & TFLOP/s vs roofline (1/2/4/8 B200) vs gobackend AVX"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
+# (profiles/); None until a capture of the current kernel exists.
+NCU_TRAFFIC_BYTES = {1: None, 4: None, 16: None}
+
+
+def algorithmic_bytes(M: int, n_cols: int) -> int:
+    """int8 W + f32 group scales + bf16 x + bf16 out for one launch over n_cols columns."""
+    return K_DIM * n_cols + 4 * (K_DIM // GROUP) * n_cols + 2 * M * K_DIM + 2 * M * n_cols
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+                for name, val in zip(names, r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        # the busiest samples are the ones taken under load
+        under = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(under) if under else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_layer(seed: int, M: int, cols: slice):
+    """Seeded synthetic weights of one layer, restricted to this rank's columns."""
+    rng = np.random.default_rng(seed)
+    w = rng.integers(-127, 128, size=(K_DIM, N_DIM), dtype=np.int8)
+    s = rng.uniform(0.001, 0.02, size=(K_DIM // GROUP, N_DIM)).astype(np.float32)
+    return np.ascontiguousarray(w[:, cols]), np.ascontiguousarray(s[:, cols])
+
+
+def cpu_baseline(M: int, seconds: float = 12.0):
+    """The oracle port (the reference's scalar loop nest with its row / N-tile parallel split)
+    timed on the host cores over repeated launches of one layer."""
+    from oracle import oracle as orc
+    orc.build()
+    threads = orc.max_threads()
+    rng = np.random.default_rng(1)
+    x = orc.bf16_to_f32(orc.bf16_from_f32(rng.standard_normal((M, K_DIM), dtype=np.float32)))
+    w, s = make_layer(100, M, slice(0, N_DIM))
+    se = orc.expand_scales(s, "kgroup", K_DIM, N_DIM, GROUP)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        orc.qdense_linear(x, w, se, None, None, 1, orc.ACT_SILU, threads=threads, fast=True)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el > seconds or reps >= 50:
+            break
+    gbs = reps * algorithmic_bytes(M, N_DIM) / el / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} launches of one 4096x14336 layer at M={M} (f32 x, reference scale layout expanded), {el:.1f} s",
+            "ms_per_launch": el / reps * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    M = args.m
+    from oracle import oracle as orc
+    orc.build()
+    threads = orc.max_threads()
+    rng = np.random.default_rng(1)
+    x = orc.bf16_to_f32(orc.bf16_from_f32(rng.standard_normal((M, K_DIM), dtype=np.float32)))
+    w, s = make_layer(100, M, slice(0, N_DIM))
+    se = orc.expand_scales(s, "kgroup", K_DIM, N_DIM, GROUP)
+    run = lambda: orc.qdense_linear(x, w, se, None, None, 1, orc.ACT_SILU, threads=threads, fast=True)
+    for _ in range(min(args.warmup, 2)):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    el = time.perf_counter() - t0
+    val = args.steps * algorithmic_bytes(M, N_DIM) / el / 1e9
+    sample = f"each step = 1 of the {LAYERS} layers of a step (one 4096x14336 launch at M={M}) on {threads} host threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded)",
+        "config": {"workload": f"config3 decode quantized dense M={M} K={K_DIM} N={N_DIM} int8 W group-{GROUP} scales SiLU; "
+                               "reference arithmetic (oracle port of gobackend's scalar kernel; no Go toolchain on this image)",
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--m", type=int, default=16, help="decode batch (tokens per launch): 1, 4 or 16")
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    g = world
+    assert N_DIM % (g * 128) == 0, "shards must be whole column tiles"
+
+    from compute_b200 import device as dv
+    from oracle import oracle as orc   # bf16 helpers + cpu_baseline only; never on the measured path
+    dv.init()
+    dev = local
+    M = args.m
+    n_loc = N_DIM // g
+    cols = slice(rank * n_loc, (rank + 1) * n_loc)
+
+    plan = dv.Plan.qdense(M, K_DIM, n_loc, dv.BF16, dv.I8, dv.SCALE_KGROUP, GROUP, False, False, dv.ACT_SILU, dev=dev)
+    ws = plan.new_workspace()
+    stream = dv.Stream(dev)
+    rng = np.random.default_rng(7)
+    x_host = dv.PinnedHost((LAYERS, M, K_DIM), np.uint16)
+    x_host.array[...] = orc.bf16_from_f32(rng.standard_normal((LAYERS, M, K_DIM), dtype=np.float32))
+    y_host = dv.PinnedHost((LAYERS, M, n_loc), np.uint16)
+    w_dev, s_dev = [], []
+    for layer in range(LAYERS):
+        w, s = make_layer(100 + layer, M, cols)
+        w_dev.append(dv.DeviceMem.from_numpy(w, dev))
+        s_dev.append(dv.DeviceMem.from_numpy(s, dev))
+    x_dev = dv.DeviceMem.from_numpy(x_host.array, dev)
+    y_dev = dv.DeviceMem(LAYERS * M * n_loc * 2, dev)
+    x_stride, y_stride = M * K_DIM * 2, M * n_loc * 2
+    wsp = ws.ptr if ws else None
+
+    gather = None
+    if dist is not None:
+        import torch
+        y_all = torch.empty((g, LAYERS * M * n_loc), dtype=torch.bfloat16, device=f"cuda:{local}")
+        y_loc = torch.empty((LAYERS * M * n_loc,), dtype=torch.bfloat16, device=f"cuda:{local}")
+        y_dev_ptr = y_loc.data_ptr()
+        tstream = torch.cuda.current_stream()
+
+        class _S:            # launch on torch's stream so NCCL orders after the kernels
+            handle = tstream.cuda_stream
+        stream_l = _S()
+
+        def gather():
+            dist.all_gather_into_tensor(y_all.view(-1), y_loc)
+    else:
+        y_dev_ptr = y_dev.ptr
+        stream_l = stream
+
+    def step(copy: bool):
+        for layer in range(LAYERS):
+            xp = x_dev.ptr + layer * x_stride
+            if copy:
+                dv.check(dv._lib.load().cb_h2d(dev, xp, x_host.ptr + layer * x_stride, x_stride, stream_l.handle))
+            plan.launch([xp, w_dev[layer].ptr, s_dev[layer].ptr], [y_dev_ptr + layer * y_stride], wsp, stream_l)
+        if gather:
+            gather()
+        if copy:
+            dv.check(dv._lib.load().cb_d2h(dev, y_host.ptr, y_dev_ptr, LAYERS * y_stride, stream_l.handle))
+
+    def sync():
+        dv.check(dv._lib.load().cb_stream_sync(dev, stream_l.handle))
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+
+    def barrier():
+        sync()
+        if dist is not None:
+            dist.barrier()
+            sync()
+
+    def timed(copy: bool, steps: int):
+        e0, e1 = dv.Event(dev), dv.Event(dev)
+        barrier()
+        e0.record(stream_l)
+        for _ in range(steps):
+            step(copy)
+        e1.record(stream_l)
+        sync()
+        ms = e0.elapsed_ms(e1)
+        barrier()
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], device=f"cuda:{local}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        step(False)
+    sync()
+    plan.check_status(wsp)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = timed(False, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    plan.check_status(wsp)
+    for _ in range(3):
+        step(True)
+    ms_e2e = timed(True, args.steps)
+
+    bytes_launch = algorithmic_bytes(M, n_loc)
+    job_bytes_step = LAYERS * (algorithmic_bytes(M, N_DIM) if g == 1 else g * bytes_launch)
+    flops_step = LAYERS * 2 * M * K_DIM * N_DIM
+    value = job_bytes_step * args.steps / (ms * 1e-3) / 1e9
+    e2e = job_bytes_step * args.steps / (ms_e2e * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    launch_us = ms * 1e3 / (args.steps * LAYERS)       # includes the per-step gather when g > 1
+    achieved = bytes_launch / (launch_us * 1e-6) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    out = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": g, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 activations x int8 weights, f32 accumulate", "data": "synthetic (seeded)",
+        "config": {"workload": f"config3 decode quantized dense: x bf16 [{M},{K_DIM}], W int8 [{K_DIM},{N_DIM}], "
+                               f"group-{GROUP} f32 scales along K, SiLU, bf16 out; {LAYERS} distinct layers per step",
+                   "M": M, "K": K_DIM, "N": N_DIM, "layers_per_step": LAYERS,
+                   "parallelism": f"N-sharded x{g}, one all-gather per step" if g > 1 else "single GPU",
+                   "l2": f"{LAYERS} distinct weight matrices per step ({LAYERS * K_DIM * N_DIM // g >> 20} MiB per GPU) exceed the 126 MB L2" if LAYERS * K_DIM * N_DIM // g > 126e6 else
+                         "per-GPU weights of a step fit in L2 at this shard count; launches may be served from L2",
+                   "kernel": plan.kernel_name, "grid": [plan.blocks, plan.threads], "dyn_smem": plan.dyn_smem},
+        "tflops": flops_step * args.steps / (ms * 1e-3) / 1e12,
+        "gpu_launches": LAYERS * args.steps,
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * x_stride, "d2h_bytes_per_step": LAYERS * y_stride,
+                "ms_per_step": ms_e2e / args.steps,
+                "note": "activations H2D from pinned memory and results D2H every step; weights resident as device buffers"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(M) if g == 1 else None, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": bytes_launch, "us_per_launch": launch_us,
+                     "frac_of_nominal_8TBs": achieved / 8000.0},
+        "clocks": clocks,
+    }
+    if g == 1 and not args.no_extra:
+        extra = {}
+        for m_other in (1, 4, 16):
+            if m_other == M:
+                continue
+            p2 = dv.Plan.qdense(m_other, K_DIM, N_DIM, dv.BF16, dv.I8, dv.SCALE_KGROUP, GROUP, False, False, dv.ACT_SILU, dev=dev)
+            ws2 = p2.new_workspace()
+            e0, e1 = dv.Event(dev), dv.Event(dev)
+            reps = max(args.steps // 2, 5)
+            for it in range(reps + 3):
+                if it == 3:
+                    e0.record(stream)
+                for layer in range(LAYERS):
+                    p2.launch([x_dev.ptr, w_dev[layer].ptr, s_dev[layer].ptr], [y_dev.ptr], ws2.ptr, stream)
+            e1.record(stream)
+            stream.sync()
+            us = e0.elapsed_ms(e1) * 1e3 / (reps * LAYERS)
+            b = algorithmic_bytes(m_other, N_DIM)
+            extra[f"M={m_other}"] = {"us_per_launch": us, "GB/s": b / us / 1e3, "frac_of_measured_hbm": b / us / 1e3 / peak,
+                                     "kernel": p2.kernel_name}
+        out["other_decode_batches"] = extra
+    if g == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline(M)
+    print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

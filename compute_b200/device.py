@@ -1,0 +1,269 @@
+"""Thin object layer over the C ABI: device memory, streams, events and plans."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import DotDesc, QDenseDesc, SdpaDesc, check
+
+# dtype codes of gomlx/compute dtypes/dtype_enum.go (also cb_dtype in cudabackend.h)
+INVALID, BOOL, I8, I16, I32, I64, U8, U16, U32, U64, F16, F32, F64, BF16 = range(14)
+F8E5M2, F8E4M3FN = 19, 20
+DTYPE_SIZE = {BOOL: 1, I8: 1, U8: 1, I16: 2, U16: 2, F16: 2, BF16: 2, I32: 4, U32: 4, F32: 4,
+              I64: 8, U64: 8, F64: 8, F8E5M2: 1, F8E4M3FN: 1}
+# numpy carrier of each dtype; half types travel as uint16 bit patterns
+NP_CARRIER = {BOOL: np.bool_, I8: np.int8, U8: np.uint8, I16: np.int16, U16: np.uint16,
+              F16: np.uint16, BF16: np.uint16, I32: np.int32, U32: np.uint32, F32: np.float32,
+              I64: np.int64, U64: np.uint64, F64: np.float64}
+
+ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
+SCALE_REF, SCALE_CHANNEL, SCALE_KGROUP = range(3)
+QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL = range(4)
+DOT_AUTO, DOT_GENERIC, DOT_TCGEN05 = range(3)
+SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH = range(3)
+LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
+MASK_NONE, MASK_BOOL, MASK_ADDITIVE = range(3)
+
+
+def init() -> int:
+    """Number of visible CUDA devices; raises BackendError when there is none."""
+    n = C.c_int(0)
+    check(_lib.load().cb_init(C.byref(n)))
+    return n.value
+
+
+def device_description(dev: int = 0) -> str:
+    buf = C.create_string_buffer(256)
+    check(_lib.load().cb_device_desc(dev, buf, 256))
+    return buf.value.decode()
+
+
+def sm_count(dev: int = 0) -> int:
+    n = C.c_int(0)
+    check(_lib.load().cb_device_sm_count(dev, C.byref(n)))
+    return n.value
+
+
+class Stream:
+    def __init__(self, dev: int = 0):
+        self.dev = dev
+        h = C.c_void_p()
+        check(_lib.load().cb_stream_create(dev, C.byref(h)))
+        self.handle = h
+
+    def sync(self) -> None:
+        check(_lib.load().cb_stream_sync(self.dev, self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.load().cb_stream_destroy(self.dev, self.handle)
+            self.handle = None
+
+
+class Event:
+    def __init__(self, dev: int = 0):
+        self.dev = dev
+        h = C.c_void_p()
+        check(_lib.load().cb_event_create(dev, C.byref(h)))
+        self.handle = h
+
+    def record(self, stream: Optional[Stream]) -> None:
+        check(_lib.load().cb_event_record(self.dev, self.handle, stream.handle if stream else None))
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float(0)
+        check(_lib.load().cb_event_elapsed_ms(self.handle, stop.handle, C.byref(ms)))
+        return ms.value
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.load().cb_event_destroy(self.dev, self.handle)
+            self.handle = None
+
+
+class DeviceMem:
+    """A device allocation owned by this object."""
+
+    def __init__(self, nbytes: int, dev: int = 0):
+        self.dev = dev
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        check(_lib.load().cb_alloc(dev, self.nbytes, C.byref(p)))
+        self.ptr = p.value
+
+    @classmethod
+    def from_numpy(cls, a: np.ndarray, dev: int = 0, stream: Optional[Stream] = None) -> "DeviceMem":
+        a = np.ascontiguousarray(a)
+        m = cls(a.nbytes, dev)
+        m.upload(a, stream)
+        return m
+
+    def upload(self, a: np.ndarray, stream: Optional[Stream] = None) -> None:
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        check(_lib.load().cb_h2d(self.dev, self.ptr, a.ctypes.data, a.nbytes, stream.handle if stream else None))
+
+    def download(self, shape, np_dtype, stream: Optional[Stream] = None) -> np.ndarray:
+        out = np.empty(shape, np_dtype)
+        assert out.nbytes <= self.nbytes
+        check(_lib.load().cb_d2h(self.dev, out.ctypes.data, self.ptr, out.nbytes, stream.handle if stream else None))
+        return out
+
+    def zero(self, stream: Optional[Stream] = None) -> None:
+        check(_lib.load().cb_memset(self.dev, self.ptr, 0, self.nbytes, stream.handle if stream else None))
+
+    def free(self) -> None:
+        if self.ptr:
+            _lib.load().cb_free(self.dev, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class PinnedHost:
+    """Page-locked host buffer exposed as a numpy array (for timed H2D / D2H copies)."""
+
+    def __init__(self, shape, np_dtype):
+        self.shape = tuple(shape)
+        self.dtype = np.dtype(np_dtype)
+        n = int(np.prod(self.shape)) * self.dtype.itemsize
+        p = C.c_void_p()
+        check(_lib.load().cb_host_alloc(max(n, 1), C.byref(p)))
+        self.ptr = p.value
+        self.nbytes = n
+        buf = (C.c_uint8 * max(n, 1)).from_address(self.ptr)
+        self.array = np.frombuffer(buf, dtype=self.dtype, count=int(np.prod(self.shape))).reshape(self.shape)
+
+    def free(self) -> None:
+        if self.ptr:
+            self.array = None
+            _lib.load().cb_host_free(self.ptr)
+            self.ptr = None
+
+
+class Plan:
+    """An immutable launch plan: kernel variant, grid and workspace size, chosen by shape and dtype."""
+
+    def __init__(self, handle: C.c_void_p, dev: int):
+        self.handle = handle
+        self.dev = dev
+        lib = _lib.load()
+        n = C.c_size_t(0)
+        check(lib.cb_plan_workspace_bytes(handle, C.byref(n)))
+        self.workspace_bytes = n.value
+        self.kernel_name = lib.cb_plan_kernel_name(handle).decode()
+        b, t, s = C.c_int(0), C.c_int(0), C.c_int(0)
+        check(lib.cb_plan_grid(handle, C.byref(b), C.byref(t), C.byref(s)))
+        self.blocks, self.threads, self.dyn_smem = b.value, t.value, s.value
+
+    # --- constructors ------------------------------------------------------
+    @classmethod
+    def qdense(cls, M, K, N, x_dtype=F32, w_dtype=I8, scale_layout=SCALE_REF, block_size=1,
+               has_zero_point=False, has_bias=False, activation=ACT_NONE, variant=QDENSE_AUTO, dev=0) -> "Plan":
+        d = QDenseDesc(M, K, N, x_dtype, w_dtype, scale_layout, block_size, int(has_zero_point),
+                       int(has_bias), activation, variant)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_qdense(dev, C.byref(d), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def dot(cls, B, M, N, K, in_dtype=F32, out_dtype=INVALID, rhs_transposed=False, variant=DOT_AUTO, dev=0) -> "Plan":
+        d = DotDesc(B, M, N, K, int(rhs_transposed), in_dtype, out_dtype, variant)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_dot(dev, C.byref(d), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def sdpa(cls, B, Hq, Hkv, S, Skv, D, dtype=F32, layout=LAYOUT_BHSD, scale=0.0, causal=False,
+             mask_kind=MASK_NONE, mask_dims: Sequence[int] = (), has_seq_lens=False,
+             bias_dims: Sequence[int] = (), variant=SDPA_AUTO, dev=0) -> "Plan":
+        d = SdpaDesc()
+        d.B, d.Hq, d.Hkv, d.S, d.Skv, d.D = B, Hq, Hkv, S, Skv, D
+        d.layout, d.dtype, d.scale, d.causal = layout, dtype, float(scale), int(causal)
+        d.mask_kind, d.mask_rank = mask_kind, len(mask_dims)
+        for i, v in enumerate(list(mask_dims)[:4]):
+            d.mask_dims[i] = v
+        d.has_seq_lens = int(has_seq_lens)
+        d.bias_rank = len(bias_dims)
+        for i, v in enumerate(list(bias_dims)[:4]):
+            d.bias_dims[i] = v
+        d.variant = variant
+        if len(mask_dims) > 4 or len(bias_dims) > 4:
+            raise _lib.BackendError(_lib.ERR_INVALID_ARG, "mask/bias must have rank 2, 3, or 4")
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_sdpa(dev, C.byref(d), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def copy(cls, dtype, n, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_copy(dev, dtype, n, C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def convert(cls, from_dtype, to_dtype, n, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_convert(dev, from_dtype, to_dtype, n, C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def iota(cls, dtype, dims, axis, dev=0) -> "Plan":
+        arr = (C.c_int64 * max(len(dims), 1))(*dims)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_iota(dev, dtype, len(dims), arr, axis, C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def slice(cls, dtype, dims, starts, limits, strides=None, dev=0) -> "Plan":
+        r = len(dims)
+        mk = lambda v: (C.c_int64 * max(r, 1))(*v)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_slice(dev, dtype, r, mk(dims), mk(starts), mk(limits),
+                                        mk(strides if strides is not None else [1] * r), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def transpose(cls, dtype, dims, perm, dev=0) -> "Plan":
+        r = len(dims)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_transpose(dev, dtype, r, (C.c_int64 * max(r, 1))(*dims),
+                                            (C.c_int32 * max(r, 1))(*perm), C.byref(h)))
+        return cls(h, dev)
+
+    # --- execution -----------------------------------------------------------
+    def new_workspace(self) -> Optional[DeviceMem]:
+        """Allocates and prepares a workspace for this plan (None when it needs none)."""
+        if self.workspace_bytes == 0:
+            return None
+        ws = DeviceMem(self.workspace_bytes, self.dev)
+        check(_lib.load().cb_plan_prepare_workspace(self.handle, ws.ptr, None))
+        check(_lib.load().cb_stream_sync(self.dev, None))
+        return ws
+
+    def launch(self, inputs: Sequence[int], outputs: Sequence[int], workspace: Optional[int] = None,
+               stream: Optional[Stream] = None) -> None:
+        ins = (C.c_void_p * max(len(inputs), 1))(*inputs)
+        outs = (C.c_void_p * max(len(outputs), 1))(*outputs)
+        check(_lib.load().cb_launch(self.handle, ins, len(inputs), outs, len(outputs), workspace,
+                                    stream.handle if stream else None))
+
+    def check_status(self, workspace: Optional[int]) -> None:
+        check(_lib.load().cb_plan_check_status(self.handle, workspace))
+
+    def destroy(self) -> None:
+        if self.handle:
+            _lib.load().cb_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

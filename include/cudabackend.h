@@ -1,0 +1,183 @@
+/*
+ * libcudabackend — C ABI of the B200 (sm_100a) backend for gomlx/compute's
+ * inference hot path: FusedQuantizedDense, DotGeneral, FusedScaledDotProductAttention.
+ *
+ * This is the boundary a cgo shim binds (one C call per Backend / Executable
+ * step).  Plain pointers and sizes only; every function returns CB_OK (0) or a
+ * cb_status code and leaves a message for cb_last_error() (thread-local).  No
+ * C++ exception crosses the boundary and the library never calls back into the
+ * host language.  All `void*` data arguments are DEVICE pointers on `dev`
+ * unless the parameter name starts with `host_`.
+ *
+ * Each group below cites the interface of the reference it replaces
+ * (paths relative to the gomlx/compute repository).
+ */
+#ifndef CUDABACKEND_H
+#define CUDABACKEND_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  CB_OK = 0,
+  CB_ERR_INVALID_ARG = 1,     /* ordinary Go `error` at build/execute time            */
+  CB_ERR_NOT_IMPLEMENTED = 2, /* maps to compute.ErrNotImplemented (compute.go:104-115) */
+  CB_ERR_OOM = 3,
+  CB_ERR_CUDA = 4,
+  CB_ERR_TIMEOUT = 5,         /* a bounded device-side wait gave up                    */
+  CB_ERR_NO_DEVICE = 6
+} cb_status;
+
+/* Element types: numeric codes of dtypes/dtype_enum.go:18-120. */
+typedef enum {
+  CB_INVALID = 0, CB_BOOL = 1, CB_I8 = 2, CB_I16 = 3, CB_I32 = 4, CB_I64 = 5,
+  CB_U8 = 6, CB_U16 = 7, CB_U32 = 8, CB_U64 = 9, CB_F16 = 10, CB_F32 = 11,
+  CB_F64 = 12, CB_BF16 = 13, CB_F8E5M2 = 19, CB_F8E4M3FN = 20
+} cb_dtype;
+
+/* compute.ActivationType (fused_ops.go:280-289). */
+typedef enum { CB_ACT_NONE = 0, CB_ACT_GELU = 1, CB_ACT_RELU = 2, CB_ACT_SILU = 3,
+               CB_ACT_HARDSWISH = 4, CB_ACT_TANH = 5 } cb_activation;
+
+typedef void* cb_stream;          /* a cudaStream_t; NULL = the device's default stream */
+typedef struct cb_plan cb_plan;   /* immutable after creation; safe to launch from many threads */
+
+/* ---- process / device (Backend: compute.go:68-102; gobackend.New, internal/gobackend/gobackend.go:58-104) */
+int cb_init(int* n_devices);                            /* Backend.NumDevices                   */
+int cb_device_desc(int dev, char* buf, size_t buf_len); /* Backend.DeviceDescription            */
+int cb_device_sm_count(int dev, int* n_sm);
+const char* cb_last_error(void);
+const char* cb_status_name(int status);
+
+/* ---- buffers (DataInterface.BufferFromFlatData / Buffer.ToFlatData / Finalize / CopyToDevice:
+ *      buffer.go:12-61; gobackend buffers.go:117-180, :387-417).  Copies with a NULL stream are
+ *      synchronous; with a stream they are ordered on it (host memory should then be pinned). */
+int cb_alloc(int dev, size_t bytes, void** dptr);
+int cb_free(int dev, void* dptr);
+int cb_memset(int dev, void* dptr, int value, size_t bytes, cb_stream stream);
+int cb_h2d(int dev, void* dst, const void* host_src, size_t bytes, cb_stream stream);
+int cb_d2h(int dev, void* host_dst, const void* src, size_t bytes, cb_stream stream);
+int cb_d2d(int dst_dev, void* dst, int src_dev, const void* src, size_t bytes, cb_stream stream);
+int cb_host_alloc(size_t bytes, void** host_ptr);       /* pinned host memory */
+int cb_host_free(void* host_ptr);
+
+/* ---- streams / events (replace the goroutine pool of internal/gobackend/workerspool) */
+int cb_stream_create(int dev, cb_stream* stream);
+int cb_stream_sync(int dev, cb_stream stream);
+int cb_stream_destroy(int dev, cb_stream stream);
+typedef void* cb_event;
+int cb_event_create(int dev, cb_event* ev);
+int cb_event_record(int dev, cb_event ev, cb_stream stream);
+int cb_event_elapsed_ms(cb_event start, cb_event stop, float* ms);  /* syncs on stop */
+int cb_event_destroy(int dev, cb_event ev);
+
+/* ---- FusedQuantizedDense, Linear scheme, 8-bit weights
+ *      (FusedOps.FusedQuantizedDense fused_ops.go:413-435; builder/executor
+ *       internal/gobackend/fusedops/quantizeddense.go:58-142, :330-418, :616-650;
+ *       activation epilogue fusedops/dense.go:176-205).
+ * y[M,N] = act( x[M,K] @ dequant(W[K,N]) + bias[N] ),  dequant = w*scale (+ zero_point).
+ * Launch inputs, in the reference's node-input order: x, weights, scales, zero_points?, bias?. */
+typedef enum {
+  CB_SCALE_REF = 0,     /* the reference layout: scales [K, ceil(N/block_size)], block along N  */
+  CB_SCALE_CHANNEL = 1, /* compact extension: scales [N], one per output channel               */
+  CB_SCALE_KGROUP = 2   /* compact extension: scales [ceil(K/block_size), N], groups along K   */
+} cb_scale_layout;
+
+typedef enum {
+  CB_QDENSE_AUTO = 0,
+  CB_QDENSE_GENERIC = 1,    /* CUDA-core kernel in the reference's (m,k,n) summation order       */
+  CB_QDENSE_DECODE_MMA = 2, /* M <= 16 stream-K kernel: TMA-staged int8 tiles, bf16 mma, fp32 acc */
+  CB_QDENSE_PREFILL = 3     /* large-M tensor-core kernel                                        */
+} cb_qdense_variant;
+
+typedef struct {
+  int64_t M, K, N;
+  int32_t x_dtype;        /* CB_F32 (the reference's only type) or CB_BF16 (extension); out has the same type */
+  int32_t w_dtype;        /* CB_I8 or CB_U8 */
+  int32_t scale_layout;   /* cb_scale_layout */
+  int64_t block_size;     /* REF: columns per scale; KGROUP: rows per scale; CHANNEL: ignored */
+  int32_t has_zero_point; /* zero points share the scale layout (f32) */
+  int32_t has_bias;       /* bias [N] f32 */
+  int32_t activation;     /* cb_activation */
+  int32_t variant;        /* cb_qdense_variant; AUTO selects by shape and dtype */
+} cb_qdense_desc;
+
+int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);
+
+/* ---- DotGeneral in normalised form (StandardOps.DotGeneral standard_ops.go:338-363;
+ *      normalisation and dtype rules internal/gobackend/dot/dot.go:165-285; kernels dot/matmul/*).
+ * out[B,M,N] = lhs[B,M,K] x rhs, rhs = [B,K,N] (rhs_transposed = 0) or [B,N,K] (= 1).
+ * Half inputs accumulate in f32.  Launch inputs: lhs, rhs. */
+typedef enum {
+  CB_DOT_AUTO = 0,
+  CB_DOT_GENERIC = 1,   /* CUDA-core tiled kernel, every supported dtype                       */
+  CB_DOT_TCGEN05 = 2    /* tcgen05 / TMEM / TMA kernel (bf16, f16; f32 via 3-way bf16 split)   */
+} cb_dot_variant;
+
+typedef struct {
+  int64_t B, M, N, K;
+  int32_t rhs_transposed;
+  int32_t in_dtype;      /* f32, f64, bf16, f16, i32, i64 */
+  int32_t out_dtype;     /* dtype stored; CB_INVALID = in_dtype */
+  int32_t variant;       /* cb_dot_variant */
+} cb_dot_desc;
+
+int cb_plan_dot(int dev, const cb_dot_desc* desc, cb_plan** plan);
+
+/* ---- FusedScaledDotProductAttention (fused_ops.go:349-378, :245-277;
+ *      internal/gobackend/fusedops/sdpa.go:98-210, :221-329, :373-636).
+ * Launch inputs, in the reference's node-input order: q, k, v, mask?, q_len?, kv_len?, bias?. */
+typedef enum { CB_LAYOUT_BHSD = 0, CB_LAYOUT_BSHD = 1 } cb_attn_layout;
+typedef enum { CB_MASK_NONE = 0, CB_MASK_BOOL = 1, CB_MASK_ADDITIVE = 2 } cb_mask_kind;
+typedef enum { CB_SDPA_AUTO = 0, CB_SDPA_GENERIC = 1, CB_SDPA_FLASH = 2 } cb_sdpa_variant;
+
+typedef struct {
+  int64_t B, Hq, Hkv, S, Skv, D;
+  int32_t layout;          /* cb_attn_layout */
+  int32_t dtype;           /* f32, f64, bf16, f16 (mask/bias additive values share it) */
+  double  scale;           /* 0 = 1/sqrt(D) */
+  int32_t causal;
+  int32_t mask_kind;       /* cb_mask_kind */
+  int32_t mask_rank;       /* 2..4 */
+  int64_t mask_dims[4];    /* as given by the caller (BSHD rank-4 masks are [B,S,H,Skv]) */
+  int32_t has_seq_lens;    /* q_len, kv_len: int32 [B] */
+  int32_t bias_rank;       /* 0 = none, else 2..4 */
+  int64_t bias_dims[4];
+  int32_t variant;         /* cb_sdpa_variant */
+} cb_sdpa_desc;
+
+int cb_plan_sdpa(int dev, const cb_sdpa_desc* desc, cb_plan** plan);
+
+/* ---- helper ops the DotGeneral path and its compliance tests need
+ *      (internal/gobackend/ops: reshape.go, slice.go, iota.go, convertdtype.go, transpose.go). */
+int cb_plan_copy(int dev, int32_t dtype, int64_t n_elements, cb_plan** plan);          /* Reshape */
+int cb_plan_convert(int dev, int32_t from, int32_t to, int64_t n_elements, cb_plan** plan);
+int cb_plan_iota(int dev, int32_t dtype, int32_t rank, const int64_t* dims, int32_t axis, cb_plan** plan);
+int cb_plan_slice(int dev, int32_t dtype, int32_t rank, const int64_t* dims, const int64_t* starts,
+                  const int64_t* limits, const int64_t* strides, cb_plan** plan);
+int cb_plan_transpose(int dev, int32_t dtype, int32_t rank, const int64_t* dims,
+                      const int32_t* permutation, cb_plan** plan);
+
+/* ---- plans ("compile-time kernel selection by shape and dtype": created in Builder.Compile,
+ *      builder.go:29-82; launched from Executable.Execute, executable.go:10-37) */
+int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes);
+/* Scratch memory is caller-owned.  A freshly allocated workspace must be prepared once
+ * (this zeroes the arrival counters some kernels keep in it); launches leave it prepared. */
+int cb_plan_prepare_workspace(const cb_plan* plan, void* workspace, cb_stream stream);
+const char* cb_plan_kernel_name(const cb_plan* plan);
+int cb_plan_grid(const cb_plan* plan, int* blocks, int* threads, int* dyn_smem_bytes);
+int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
+              void* const* outputs, int n_outputs, void* workspace, cb_stream stream);
+/* After a stream sync: reads the status word a kernel with bounded waits keeps in its
+ * workspace; CB_ERR_TIMEOUT if a wait gave up.  CB_OK for plans without such waits. */
+int cb_plan_check_status(const cb_plan* plan, const void* workspace);
+int cb_plan_destroy(cb_plan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

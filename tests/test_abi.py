@@ -1,0 +1,52 @@
+"""CPU checks of the drop-in boundary: the shared library loads, exports every symbol the
+header declares, and plans (shape/dtype kernel selection) can be built without a GPU."""
+import os
+import re
+
+import pytest
+
+import compute_b200 as cb
+from compute_b200 import _lib, device as dv
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "cudabackend.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = cb.load_library()
+    names = header_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/cudabackend.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) <= set(names)
+
+
+def test_plans_select_kernels_by_shape_and_dtype():
+    p = dv.Plan.qdense(1, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, activation=dv.ACT_SILU)
+    assert p.kernel_name == "qdense_decode_bf16_m8_i8" and p.workspace_bytes > 0
+    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_m16_i8")
+    # the reference's own scale layout and zero points go to the reference-order kernel
+    assert dv.Plan.qdense(1, 4096, 14336, dv.F32, dv.I8, dv.SCALE_REF, 128).kernel_name.startswith("qdense_generic")
+    assert dv.Plan.qdense(4, 64, 64, dv.F32, dv.U8, dv.SCALE_CHANNEL, has_zero_point=True).kernel_name == "qdense_generic_f32_u8"
+    assert dv.Plan.dot(1, 3, 5, 7, dv.F64).kernel_name.startswith("dot_generic_Float64")
+    assert dv.Plan.sdpa(1, 4, 2, 5, 7, 8, dv.F32, causal=True).kernel_name.startswith("sdpa_")
+
+
+def test_error_mapping():
+    with pytest.raises(cb.ErrNotImplemented):
+        dv.Plan.sdpa(1, 1, 1, 2, 2, 8, dv.F8E4M3FN)
+    with pytest.raises(cb.BackendError) as e:
+        dv.Plan.sdpa(1, 3, 2, 2, 2, 8, dv.F32)
+    assert "divisible" in str(e.value) and not isinstance(e.value, cb.ErrNotImplemented)
+    with pytest.raises(cb.BackendError):
+        dv.Plan.sdpa(1, 1, 1, 2, 2, 1, dv.F32, bias_dims=(2,))
+    with pytest.raises(cb.BackendError):
+        dv.Plan.sdpa(1, 1, 1, 2, 2, 1, dv.F32, bias_dims=(2, 3))
+    with pytest.raises(cb.ErrNotImplemented):
+        dv.Plan.dot(1, 2, 2, 2, dv.BOOL)

@@ -1,0 +1,87 @@
+"""GPU parity of the normalised DotGeneral kernels ([B,M,K] x [B,K,N] or [B,N,K]) against the
+CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from compute_b200 import ErrNotImplemented, device as dv, ops
+from oracle import oracle as orc
+from tests.helpers import DT, as_f64, max_abs_normalised
+
+pytestmark = pytest.mark.gpu
+TOL = {"f32": 1e-4, "f64": 1e-12, "bf16": 2e-2, "f16": 2e-2}
+
+
+def make(seed, shape, dtype, sigma=1.0):
+    a = (np.random.default_rng(seed).standard_normal(shape) * sigma).astype(np.float32)
+    code = DT[dtype]
+    if code in (orc.BF16, orc.F16):
+        return orc.from_f32(a, code)
+    return a.astype(np.float64 if code == orc.F64 else np.float32)
+
+
+def oracle_dot(lhs, rhs, code, transposed, out=0):
+    rc = [2] if transposed else [1]
+    return orc.dot_general(lhs, [2], [0], rhs, rc, [0], code, 0, out, acc_f64=True)
+
+
+@pytest.mark.parametrize("variant", [dv.DOT_GENERIC, dv.DOT_AUTO])
+@pytest.mark.parametrize("dtype", ["f32", "f64", "bf16", "f16"])
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("B,M,N,K", [(1, 1, 1, 1), (3, 5, 7, 9), (2, 65, 130, 33), (1, 128, 256, 192), (4, 200, 72, 264)])
+def test_dot_matches_oracle(B, M, N, K, transposed, dtype, variant):
+    code = DT[dtype]
+    lhs = make(1, (B, M, K), dtype)
+    rhs = make(2, (B, N, K) if transposed else (B, K, N), dtype)
+    want = as_f64(oracle_dot(lhs, rhs, code, transposed), code)
+    got = ops.dot_normalised(lhs, rhs, in_dtype=code, rhs_transposed=transposed, variant=variant)
+    assert got.shape == (B, M, N)
+    assert max_abs_normalised(as_f64(got, code), want) < TOL[dtype]
+
+
+def test_dot_output_dtypes_and_ints():
+    lhs = make(1, (1, 4, 6), "bf16")
+    rhs = make(2, (1, 6, 5), "bf16")
+    got = ops.dot_normalised(lhs, rhs, in_dtype=dv.BF16, out_dtype=dv.F32)
+    want = oracle_dot(lhs, rhs, orc.BF16, False, orc.F32)
+    assert got.dtype == np.float32 and max_abs_normalised(got, want) < 1e-6
+    a = np.arange(24, dtype=np.int32).reshape(1, 4, 6)
+    b = np.arange(30, dtype=np.int32).reshape(1, 6, 5) - 7
+    assert np.array_equal(ops.dot_normalised(a, b, in_dtype=dv.I32)[0], a[0] @ b[0])
+    a64, b64 = a.astype(np.int64), b.astype(np.int64)
+    assert np.array_equal(ops.dot_normalised(a64, b64, in_dtype=dv.I64)[0], a64[0] @ b64[0])
+    with pytest.raises(ErrNotImplemented):
+        dv.Plan.dot(1, 2, 2, 2, dv.I32, dv.F32)
+
+
+def check_rows(got, lhs, rhs, code, rows, tol):
+    """Oracle (f64 accumulation) on a sample of output rows of a large product."""
+    sub = np.ascontiguousarray(lhs[:, rows, :])
+    want = as_f64(oracle_dot(sub, rhs, code, False), code)
+    assert max_abs_normalised(as_f64(got[:, rows, :], code), want) < tol
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_config2_gemm_4096(dtype):
+    """A[4096,4096] x B[4096,4096], entries ~ N(0, 1/sqrt(K)); sampled rows against the oracle."""
+    code = DT[dtype]
+    lhs = make(0x5EED0002, (1, 4096, 4096), dtype, 1.0 / 64)
+    rhs = make(0x5EED0012, (1, 4096, 4096), dtype, 1.0 / 64)
+    got = ops.dot_normalised(lhs, rhs, in_dtype=code)
+    check_rows(got, lhs, rhs, code, [0, 1, 127, 128, 2049, 4095], TOL[dtype])
+    # linearity in the left operand: (A1 + A2) B == A1 B + A2 B, over the full output
+    if dtype == "f32":
+        lhs2 = make(7, (1, 4096, 4096), dtype, 1.0 / 64)
+        s = ops.dot_normalised(lhs + lhs2, rhs, in_dtype=code).astype(np.float64)
+        t = got.astype(np.float64) + ops.dot_normalised(lhs2, rhs, in_dtype=code)
+        assert max_abs_normalised(s, t) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_config2_batched(dtype):
+    """[32,512,128] x [32,128,512], batch axis 0."""
+    code = DT[dtype]
+    lhs = make(3, (32, 512, 128), dtype, 128 ** -0.5)
+    rhs = make(4, (32, 128, 512), dtype, 128 ** -0.5)
+    got = ops.dot_normalised(lhs, rhs, in_dtype=code)
+    want = as_f64(oracle_dot(lhs, rhs, code, False), code)
+    assert max_abs_normalised(as_f64(got, code), want) < TOL[dtype]

@@ -1,0 +1,116 @@
+"""GPU parity of FusedScaledDotProductAttention: the reference's known-answer cases and
+seeded comparisons against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from compute_b200 import BackendError, ErrNotImplemented, device as dv, ops
+from oracle import oracle as orc
+from tests.helpers import DT, as_f64, load_golden, max_abs_normalised, tensor
+
+pytestmark = pytest.mark.gpu
+G = load_golden("backendtest_sdpa.json")
+LAYOUT = {"BHSD": dv.LAYOUT_BHSD, "BSHD": dv.LAYOUT_BSHD}
+
+
+@pytest.mark.parametrize("variant", [dv.SDPA_GENERIC, dv.SDPA_AUTO])
+@pytest.mark.parametrize("case", G["cases"], ids=[c["name"] for c in G["cases"]])
+def test_sdpa_known_answers(case, variant):
+    code = DT[case["dtype"]]
+    t = lambda key: tensor(case[key], case["dtype"])
+    mask = tensor(case["mask"], "bool") if "mask" in case else None
+    bias = t("bias") if "bias" in case else None
+    ql = np.array(case["q_len"], np.int32) if "q_len" in case else None
+    kl = np.array(case["kv_len"], np.int32) if "kv_len" in case else None
+    got = ops.sdpa(t("q"), t("k"), t("v"), dtype=code, layout=LAYOUT[case["layout"]], scale=case["scale"],
+                   causal=case["causal"], mask=mask, q_len=ql, kv_len=kl, bias=bias, variant=variant)
+    want = np.array(case["want"]["data"], np.float64).reshape(case["want"]["shape"])
+    assert np.max(np.abs(as_f64(got, code) - want)) <= case["tol"]
+
+
+@pytest.mark.parametrize("case", G["error_cases"], ids=[c["name"] for c in G["error_cases"]])
+def test_sdpa_rejected_requests(case):
+    q, k, v = (tensor(case[n], "f32") for n in ("q", "k", "v"))
+    kwargs = dict(scale=1.0)
+    if "bias" in case:
+        kwargs["bias"] = tensor(case["bias"], "f32")
+    if "q_len" in case:
+        dt = np.int64 if case.get("seq_len_dtype") == "i64" else np.int32
+        kwargs["q_len"] = np.array(case["q_len"], dt)
+        kwargs["kv_len"] = np.array(case["kv_len"], dt)
+    if case["error"] == "not_implemented":
+        with pytest.raises(ErrNotImplemented):
+            dv.Plan.sdpa(1, 1, 1, 2, 2, 1, dv.F8E4M3FN, causal=True, scale=1.0)
+    else:
+        with pytest.raises(BackendError) as e:
+            ops.sdpa(q, k, v, **kwargs)
+        assert not isinstance(e.value, ErrNotImplemented)
+
+
+def random_case(seed, B, Hq, Hkv, S, Skv, D):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((B, Hq, S, D), dtype=np.float32),
+            rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32),
+            rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32), rng)
+
+
+@pytest.mark.parametrize("layout", ["BHSD", "BSHD"])
+@pytest.mark.parametrize("variant", [dv.SDPA_GENERIC, dv.SDPA_AUTO])
+def test_sdpa_matches_oracle_f32(layout, variant):
+    B, Hq, Hkv, S, Skv, D = 2, 6, 2, 37, 53, 24
+    q, k, v, rng = random_case(3, B, Hq, Hkv, S, Skv, D)
+    bias = rng.standard_normal((B, Hq, S, Skv), dtype=np.float32)
+    bmask = rng.random((S, Skv)) > 0.3
+    bmask[5, :] = False                      # an all-masked row must give zeros
+    amask = np.where(rng.random((B, 1, S, Skv)) > 0.2, 0.0, -1e9).astype(np.float32)
+    ql = np.array([S, 20], np.int32)
+    kl = np.array([Skv - 3, 999], np.int32)
+    tr = (lambda a: np.ascontiguousarray(a.transpose(0, 2, 1, 3))) if layout == "BSHD" else (lambda a: a)
+    for kw in (dict(causal=True), dict(bias=bias), dict(mask=bmask, causal=True), dict(mask=amask, bias=bias),
+               dict(q_len=ql, kv_len=kl, causal=True), dict(scale=0.37)):
+        okw = dict(kw)
+        gkw = dict(kw)
+        for name in ("bias", "mask"):
+            if name in kw and kw[name].ndim == 4:
+                gkw[name] = tr(kw[name])
+                okw[name] = tr(kw[name])
+        want = orc.sdpa(tr(q), tr(k), tr(v), layout=layout, **okw)
+        got = ops.sdpa(tr(q), tr(k), tr(v), dtype=dv.F32, layout=LAYOUT[layout], variant=variant, **gkw)
+        assert max_abs_normalised(got, want) < 1e-4, kw.keys()
+        if "mask" in kw and kw["mask"].dtype == np.bool_:
+            row = got[:, :, 5, :] if layout == "BHSD" else got[:, 5, :, :]
+            assert np.all(row == 0)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f64"])
+def test_sdpa_other_dtypes(dtype):
+    B, Hq, Hkv, S, Skv, D = 1, 4, 4, 19, 19, 16
+    q, k, v, _ = random_case(5, B, Hq, Hkv, S, Skv, D)
+    code = DT[dtype]
+    if dtype == "f64":
+        got = ops.sdpa(q.astype(np.float64), k.astype(np.float64), v.astype(np.float64), dtype=dv.F64, causal=True)
+        want = orc.sdpa(q, k, v, causal=True)
+        assert max_abs_normalised(got, want) < 1e-5
+        return
+    qh, kh, vh = (orc.from_f32(a, code) for a in (q, k, v))
+    want = orc.sdpa(orc.to_f32(qh, code), orc.to_f32(kh, code), orc.to_f32(vh, code), causal=True)
+    got = ops.sdpa(qh, kh, vh, dtype=code, causal=True)
+    assert max_abs_normalised(orc.to_f32(got, code), want) < 2e-2
+
+
+def test_sdpa_config4_slice():
+    """B=8, 32 query / 8 kv heads, head_dim 128, seq 2048, bf16, causal: one (batch, kv head)
+    group of the full configuration against the oracle, the rest through a checksum identity
+    (with V = ones every output element is exactly 1)."""
+    B, Hq, Hkv, S, D = 8, 32, 8, 2048, 128
+    rng = np.random.default_rng(0x5EED0004)
+    q = orc.bf16_from_f32(rng.standard_normal((B, Hq, S, D), dtype=np.float32))
+    k = orc.bf16_from_f32(rng.standard_normal((B, Hkv, S, D), dtype=np.float32))
+    v = orc.bf16_from_f32(rng.standard_normal((B, Hkv, S, D), dtype=np.float32))
+    got = ops.sdpa(q, k, v, dtype=dv.BF16, causal=True)
+    b, h = 3, 5
+    qs = orc.bf16_to_f32(q[b:b + 1, 4 * h:4 * h + 4])
+    want = orc.sdpa(qs, orc.bf16_to_f32(k[b:b + 1, h:h + 1]), orc.bf16_to_f32(v[b:b + 1, h:h + 1]), causal=True, fast=True)
+    assert max_abs_normalised(orc.bf16_to_f32(got[b:b + 1, 4 * h:4 * h + 4]), want) < 2e-2
+    ones = orc.bf16_from_f32(np.ones((B, Hkv, S, D), np.float32))
+    got1 = orc.bf16_to_f32(ops.sdpa(q, k, ones, dtype=dv.BF16, causal=True))
+    assert np.max(np.abs(got1 - 1.0)) < 2e-2
