@@ -11,13 +11,16 @@
 //    scales).  W is streamed exactly once: a stream-K partition gives every SM
 //    the same number of [64 x 128] int8 chunks, an elected producer thread
 //    keeps a ring of TMA loads (128B-swizzled) in flight, consumer warps
-//    convert int8 -> bf16 in registers (exact) and feed mma.sync with x as the
-//    8-wide operand, accumulate in f32, apply the per-group scale per chunk,
+//    convert int8 -> f16 in registers (exact) and feed mma.sync with x (rows
+//    pre-scaled by an exact power of two, then f16) as the 8-wide operand,
+//    accumulate in f32, apply the per-group scale per chunk,
 //    reduce across warps in shared memory and across SMs through a small
 //    workspace with per-tile arrival counters (deterministic order).
 #include "common.cuh"
 
+#include <stdlib.h>
 #include <string.h>
+#include <atomic>
 #include <mutex>
 
 namespace cb {
@@ -81,379 +84,462 @@ qdense_generic_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const 
 // ---------------------------------------------------------------------------
 // decode kernel
 // ---------------------------------------------------------------------------
-constexpr int QD_TILE_N = 128;                 // columns per chunk = one swizzled 128-byte row
+constexpr int QD_TILE_N = 64;                  // columns per tile
 constexpr int QD_CHUNK_K = 64;                 // rows per chunk
-constexpr int QD_STAGE_BYTES = QD_TILE_N * QD_CHUNK_K;
-constexpr int QD_CONSUMERS = 8;                // consumer warps (two warpgroups)
-constexpr int QD_THREADS = (QD_CONSUMERS + 4) * 32;   // + one producer warpgroup (one lane works)
+constexpr int QD_PITCH = 80;                   // shared-memory row pitch: 64 data bytes + 16 pad (conflict-free 8-byte reads)
+constexpr int QD_STAGE_BYTES = QD_CHUNK_K * QD_PITCH;
+constexpr int QD_WARPS = 16;
+constexpr int QD_THREADS = QD_WARPS * 32;
+constexpr int QD_DEPTH = 2;                    // chunks each warp keeps in flight
 constexpr int QD_WS_HEADER = 64;               // status words live in the first 64 bytes
-constexpr unsigned long long QD_WAIT_NS = 1000000000ull;   // every barrier wait gives up after 1 s
-
-enum { QD_ERR_FULL_WAIT = 1, QD_ERR_EMPTY_WAIT = 2 };
 
 struct QdParams {
   const void* x;
+  const uint8_t* w;
   const float* scales;
   const float* bias;
   void* out;
-  unsigned* status;     // [0] error code, [1] detail
-  unsigned* counters;   // per column tile
-  float* partials;      // [grid][2][MT*8*128]
+  unsigned* status;     // [0] error code, [1] detail (reserved; this kernel has no device-side waits)
+  unsigned* counters;   // arrivals per stream-K tile
+  float* partials;      // [grid][2][MT*8*64]
   int M, K, N;
   int n_tiles, cpt;     // column tiles, chunks per tile
-  long long total;      // n_tiles * cpt
+  int sk_tiles;         // tiles [0, sk_tiles) are split across CTAs; the rest are owned whole
+  int dp_per_cta;       // whole tiles per CTA
+  long long sk_total;   // sk_tiles * cpt
   int scale_group;      // rows per scale row; 0 = one scale per column
   int activation;
-  int stages;
+  int debug_skip;       // diagnostics: 1 = stream the weights but skip the math
+  unsigned long long* dbg;   // diagnostics: per-CTA phase timestamps (16 per CTA) or NULL
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false once QD_WAIT_NS elapsed without the phase completing.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; i++)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > QD_WAIT_NS) return false;
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Byte `b` of `word` (already biased to unsigned) -> exact f32 integer value.
-// 0x4B0000uu is 2^23 + uu; subtracting the magic removes 2^23 and the +128 bias.
-template <int B>
-__device__ __forceinline__ float byte_to_f32(uint32_t word, float magic) {
-  return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540 + B)) - magic;
+// int8 -> f16, exact.  0x64uu is the f16 number 1024 + uu, so two bytes dropped under
+// 0x64 high bytes and reduced by 1024 (+128 for the sign bias) are the weights as f16x2.
+// X and Y are the same four columns of two consecutive k rows; H[b] = {X.b, Y.b} as f16x2.
+__device__ __forceinline__ void bytes_to_f16x2(uint32_t X, uint32_t Y, uint32_t bias, uint32_t (&H)[4]) {
+  const uint32_t ra = __byte_perm(X, Y, 0x5140);   // X.0 Y.0 X.1 Y.1
+  const uint32_t rb = __byte_perm(X, Y, 0x7362);   // X.2 Y.2 X.3 Y.3
+  uint32_t h[4];
+  h[0] = __byte_perm(ra, 0x64646464u, 0x4140);
+  h[1] = __byte_perm(ra, 0x64646464u, 0x4342);
+  h[2] = __byte_perm(rb, 0x64646464u, 0x4140);
+  h[3] = __byte_perm(rb, 0x64646464u, 0x4342);
+#pragma unroll
+  for (int b = 0; b < 4; b++) {
+    __half2 v = __hsub2(*reinterpret_cast<__half2*>(&h[b]), *reinterpret_cast<const __half2*>(&bias));
+    H[b] = *reinterpret_cast<uint32_t*>(&v);
+  }
 }
-// Two exact small-integer floats -> packed bf16x2 (their upper halves; no rounding happens).
-__device__ __forceinline__ uint32_t pack_hi16(float lo, float hi) {
-  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
-}
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Activation operand of one k-step and row tile.  Rows are pre-multiplied by a power of
+// two (exact) that brings the row's largest magnitude to [2^14, 2^15), so the f16
+// conversion cannot overflow and keeps every value within 2^-28 of the row maximum.
 template <typename XT> struct XFrag;
-// bf16 activations: one operand register pair per k-step and row tile.
 template <> struct XFrag<__nv_bfloat16> {
-  static constexpr int SPLITS = 1;
-  uint32_t b0[1], b1[1];
+  static constexpr int SPLITS = 1;     // bf16 has 8 significant bits: one f16 term is exact
+  uint32_t raw[2];
   __device__ __forceinline__ void load(const void* x, int64_t row_off, int k, bool ok) {
     const uint16_t* p = reinterpret_cast<const uint16_t*>(x) + row_off + k;
-    b0[0] = ok ? *reinterpret_cast<const uint32_t*>(p) : 0u;
-    b1[0] = ok ? *reinterpret_cast<const uint32_t*>(p + 8) : 0u;
+    raw[0] = ok ? __ldg(reinterpret_cast<const uint32_t*>(p)) : 0u;
+    raw[1] = ok ? __ldg(reinterpret_cast<const uint32_t*>(p + 8)) : 0u;
+  }
+  __device__ __forceinline__ void operands(float mul, uint32_t (&b0)[1], uint32_t (&b1)[1]) const {
+    b0[0] = pack_f16x2(__uint_as_float(raw[0] << 16) * mul, __uint_as_float(raw[0] & 0xFFFF0000u) * mul);
+    b1[0] = pack_f16x2(__uint_as_float(raw[1] << 16) * mul, __uint_as_float(raw[1] & 0xFFFF0000u) * mul);
   }
 };
-// f32 activations: split every value into three bf16 terms (hi + mid + lo carries
-// all 24 significand bits), so the products with the exact bf16 weights are exact.
 template <> struct XFrag<float> {
-  static constexpr int SPLITS = 3;
-  uint32_t b0[3], b1[3];
-  __device__ __forceinline__ static void split(float a, float b, uint32_t* out, int stride) {
-    float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
-    float ar = a - ah, br = b - bh;
-    float am = __bfloat162float(__float2bfloat16_rn(ar)), bm = __bfloat162float(__float2bfloat16_rn(br));
-    float al = ar - am, bl = br - bm;
-    out[0] = pack_hi16(ah, bh);
-    out[stride] = pack_hi16(am, bm);
-    out[2 * stride] = pack_bf16x2(al, bl);
-  }
+  static constexpr int SPLITS = 2;     // hi + lo f16 terms carry 22 significant bits
+  float2 raw[2];
   __device__ __forceinline__ void load(const void* x, int64_t row_off, int k, bool ok) {
     const float* p = reinterpret_cast<const float*>(x) + row_off + k;
-    float2 lo = ok ? *reinterpret_cast<const float2*>(p) : make_float2(0.f, 0.f);
-    float2 hi = ok ? *reinterpret_cast<const float2*>(p + 8) : make_float2(0.f, 0.f);
-    split(lo.x, lo.y, b0, 1);
-    split(hi.x, hi.y, b1, 1);
+    raw[0] = ok ? __ldg(reinterpret_cast<const float2*>(p)) : make_float2(0.f, 0.f);
+    raw[1] = ok ? __ldg(reinterpret_cast<const float2*>(p + 8)) : make_float2(0.f, 0.f);
+  }
+  __device__ __forceinline__ static void split(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 hf = __half22float2(h);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = pack_f16x2(a - hf.x, b - hf.y);
+  }
+  __device__ __forceinline__ void operands(float mul, uint32_t (&b0)[2], uint32_t (&b1)[2]) const {
+    split(raw[0].x * mul, raw[0].y * mul, b0[0], b0[1]);
+    split(raw[1].x * mul, raw[1].y * mul, b1[0], b1[1]);
   }
 };
+
+// Per-row power-of-two multiplier from the row's largest magnitude (biased exponent E):
+// 2^(141-E) puts the maximum in [2^14, 2^15).  Zero / denormal rows and non-finite rows
+// are left unscaled (non-finite values then propagate as inf/NaN, as in f32 arithmetic).
+__device__ __forceinline__ float row_multiplier(uint32_t biased_exp) {
+  if (biased_exp == 0u || biased_exp == 255u) return 1.0f;
+  int e = 268 - (int)biased_exp;
+  e = e > 254 ? 254 : e;
+  return __uint_as_float((uint32_t)e << 23);
+}
+
+// Work list of one CTA: first its share of the stream-K region (chunks of tiles that are
+// split across CTAs, so their cross-CTA sums finish early), then the tiles it owns whole.
+struct QdSched {
+  unsigned c0;         // first stream-K chunk of this CTA (chunk counts fit 32 bits: checked at plan time)
+  int n_sk, n_local;   // stream-K chunks, all chunks
+  unsigned cpt;
+  int sk_tiles, G, cta;
+  __device__ __forceinline__ void coords(int i, int& tile, int& kc) const {
+    if (i < n_sk) {
+      const unsigned ch = c0 + (unsigned)i;
+      const unsigned q = ch / cpt;
+      tile = (int)q;
+      kc = (int)(ch - q * cpt);
+    } else {
+      const unsigned j = (unsigned)(i - n_sk);
+      const unsigned q = j / cpt;
+      tile = sk_tiles + (int)q * G + cta;
+      kc = (int)(j - q * cpt);
+    }
+  }
+};
+
+// One warp copies a [64 x 64] int8 chunk into its own stage with 16-byte cp.async
+// (zero-filled outside the matrix) and closes the group.
+__device__ __forceinline__ void issue_chunk_copy(const QdParams& p, const QdSched& sc, int i, uint8_t* stage, int lane) {
+  if (i < sc.n_local) {
+    int tile, kc;
+    sc.coords(i, tile, kc);
+    const int k0 = kc * QD_CHUNK_K, colbase = tile * QD_TILE_N;
+    // lane -> (row lane/4 of each group of 8 rows, 16-byte piece lane%4)
+    const int r0 = lane >> 2, q = lane & 3;
+    const uint8_t* src = p.w + (int64_t)(k0 + r0) * p.N + colbase + 16 * q;
+    const uint32_t dst = smem_u32(stage + r0 * QD_PITCH + 16 * q);
+    const int64_t step = (int64_t)8 * p.N;
+    if (k0 + QD_CHUNK_K <= p.K && colbase + QD_TILE_N <= p.N) {
+#pragma unroll
+      for (int it = 0; it < 8; it++)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + it * 8 * QD_PITCH), "l"(src + it * step) : "memory");
+    } else {      // edge chunk: zero-fill what lies outside the matrix
+      const bool col_ok = colbase + 16 * q < p.N;
+#pragma unroll
+      for (int it = 0; it < 8; it++) {
+        const bool ok = col_ok && (k0 + r0 + 8 * it < p.K);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + it * 8 * QD_PITCH),
+                     "l"(ok ? src + it * step : p.w), "r"(ok ? 16 : 0) : "memory");
+      }
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <typename XT, int MT>
+__device__ __forceinline__ void fetch_chunk_inputs(const QdParams& p, int tile, int kc, int g, int t, float (&sc)[8],
+                                                   XFrag<XT> (&xf)[4][MT]) {
+  const int k0 = kc * QD_CHUNK_K, colbase = tile * QD_TILE_N;
+  const int srow = p.scale_group ? k0 / p.scale_group : 0;
+  const float* sp = p.scales + (int64_t)srow * p.N + colbase + 8 * g;
+  const bool ok = colbase + 8 * g < p.N;     // N is a multiple of 16
+#pragma unroll
+  for (int q = 0; q < 2; q++) {
+    float4 v = ok ? __ldg(reinterpret_cast<const float4*>(sp) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
+  }
+#pragma unroll
+  for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+      const int m = mt * 8 + g, k = k0 + 16 * ks + 2 * t;
+      xf[ks][mt].load(p.x, (int64_t)m * p.K, k, m < p.M && k0 + 16 * ks < p.K);
+    }
+}
 
 template <typename XT, int MT, bool WUNSIGNED>
 __global__ void __launch_bounds__(QD_THREADS, 1)
-qdense_decode_kernel(const __grid_constant__ CUtensorMap tmap, const QdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr int RED_FLOATS = MT * 8 * QD_TILE_N;   // one [rows x 128] partial tile
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* ring = base;
-  float* red = reinterpret_cast<float*>(base + (size_t)p.stages * QD_STAGE_BYTES);
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + QD_CONSUMERS * RED_FLOATS);
-  uint64_t* empty = full + p.stages;
+qdense_decode_kernel(const QdParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr int RED_FLOATS = MT * 8 * QD_TILE_N;   // one [rows x 64] partial tile
+  uint8_t* ring = smem_raw;
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)QD_WARPS * QD_DEPTH * QD_STAGE_BYTES);
   __shared__ unsigned s_flag;
-  __shared__ unsigned s_failed;
+  __shared__ unsigned s_rowmax[16];
+  __shared__ float s_mul[16], s_inv[16];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int G = gridDim.x, cta = blockIdx.x;
-  const long long c0 = (long long)cta * p.total / G;
-  const long long c1 = (long long)(cta + 1) * p.total / G;
-  const int n_local = (int)(c1 - c0);
+  QdSched sched;
+  sched.cpt = (unsigned)p.cpt; sched.sk_tiles = p.sk_tiles; sched.G = G; sched.cta = cta;
+  // the stream-K region is shared by the first Gsk CTAs (all of them unless it is tiny)
+  const int Gsk = (int)min((long long)G, p.sk_total);
+  sched.c0 = cta < Gsk ? (unsigned)((long long)cta * p.sk_total / Gsk) : 0u;
+  sched.n_sk = cta < Gsk ? (int)((long long)(cta + 1) * p.sk_total / Gsk - sched.c0) : 0;
+  sched.n_local = sched.n_sk + p.dp_per_cta * p.cpt;
+  const int n_local = sched.n_local;
 
-  if (tid == 0) {
-    for (int s = 0; s < p.stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    s_failed = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
+  int dbg_n = 0;
+#define QD_STAMP() do { if (p.dbg && tid == 0 && dbg_n < 16) p.dbg[cta * 16 + dbg_n++] = global_ns(); } while (0)
+  QD_STAMP();
+
+  // start streaming before anything else: the first QD_DEPTH chunks of every warp
+  uint8_t* my_ring = ring + (size_t)warp * QD_DEPTH * QD_STAGE_BYTES;
+#pragma unroll
+  for (int d = 0; d < QD_DEPTH; d++) issue_chunk_copy(p, sched, warp + d * QD_WARPS, my_ring + d * QD_STAGE_BYTES, lane);
+
+  // Row maxima of x (every CTA computes the same values, so partial sums of different
+  // CTAs share one scaling); one warp per row, all loads of a row issued together.
+  if (tid < 16) s_rowmax[tid] = 0;
   __syncthreads();
-
-  if (warp >= QD_CONSUMERS) {
-    // ---------------- producer warpgroup: keep the TMA ring full ---------
-    // Registers move from this warpgroup to the two consumer warpgroups
-    // (384 x 168 = 128 x 40 + 256 x 232).
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == QD_CONSUMERS && lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
-      for (int i = 0; i < n_local; i++) {
-        const int s = i % p.stages;
-        if (i >= p.stages) {
-          if (!mbar_wait_bounded(&empty[s], (uint32_t)((i / p.stages - 1) & 1))) {
-            atomicExch(&p.status[0], (unsigned)QD_ERR_EMPTY_WAIT);
-            atomicExch(&p.status[1], (unsigned)i);
-            atomicExch(&s_failed, 1u);
-            break;
+  {
+    constexpr int PER16 = 16 / (int)sizeof(XT);             // elements per 16-byte load
+    const int vec_per_row = p.K / PER16;
+    for (int m = warp; m < p.M; m += QD_WARPS) {
+      uint32_t mx = 0;
+      const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const XT*>(p.x) + (int64_t)m * p.K);
+      for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 8) {
+        uint4 q[8];      // eight independent loads in flight per lane
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const int v = v0 + u * 32 + lane;
+          q[u] = v < vec_per_row ? __ldg(row + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (sizeof(XT) == 2) {
+            const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) mx = max(mx, max((w[e] & 0x7FFFu) << 16, w[e] & 0x7FFF0000u));
+          } else {
+            mx = max(max(mx, q[u].x & 0x7FFFFFFFu), max(max(q[u].y & 0x7FFFFFFFu, q[u].z & 0x7FFFFFFFu), q[u].w & 0x7FFFFFFFu));
           }
         }
-        if (*reinterpret_cast<volatile unsigned*>(&s_failed)) break;
-        const long long chunk = c0 + i;
-        const int ct = (int)(chunk / p.cpt), kc = (int)(chunk % p.cpt);
-        mbar_expect_tx(&full[s], QD_STAGE_BYTES);
-        tma_load_2d(ring + (size_t)s * QD_STAGE_BYTES, &tmap, ct * QD_TILE_N, kc * QD_CHUNK_K, &full[s]);
       }
-    }
-    return;   // consumers only use named barrier 1 from here on
-  }
-
-  // -------------------- consumers -------------------------------------
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-  const int g = lane >> 2, t = lane & 3;
-  const float magic = WUNSIGNED ? 8388608.0f : 8388736.0f;
-  float tot[8][MT][4];
 #pragma unroll
-  for (int j = 0; j < 8; j++)
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) s_rowmax[m] = mx;
+    }
+    __syncthreads();
+    if (tid < 16) {
+      const float mul = row_multiplier(s_rowmax[tid] >> 23);
+      s_mul[tid] = mul;
+      s_inv[tid] = 1.0f / mul;
+    }
+    __syncthreads();
+  }
+  QD_STAMP();
+  float mul[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; mt++) mul[mt] = s_mul[mt * 8 + g];
+  const uint32_t wbias = WUNSIGNED ? 0x64006400u : 0x64806480u;   // f16x2 1024 / 1152
+
+  float tot[4][MT][4];
+#pragma unroll
+  for (int j = 0; j < 4; j++)
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
       for (int c = 0; c < 4; c++) tot[j][mt][c] = 0.0f;
 
-  bool failed = false;
+  // scales and activations of the warp's next chunk are fetched one chunk ahead
+  float sc_next[8];
+  XFrag<XT> xf_next[4][MT];
+  if (warp < n_local) {
+    int tile, kc;
+    sched.coords(warp, tile, kc);
+    fetch_chunk_inputs<XT, MT>(p, tile, kc, g, t, sc_next, xf_next);
+  }
+
+  int n_done = 0;        // chunks this warp has consumed (selects its ring stage)
   int seg_begin = 0;
   while (seg_begin < n_local) {
-    const long long first_chunk = c0 + seg_begin;
-    const int ct = (int)(first_chunk / p.cpt);
-    const long long tile_begin = (long long)ct * p.cpt, tile_end = tile_begin + p.cpt;
-    const int seg_end = (int)min((long long)n_local, tile_end - c0);
-    const int colbase = ct * QD_TILE_N;
+    int tile, kc0;
+    sched.coords(seg_begin, tile, kc0);
+    const int seg_end = seg_begin < sched.n_sk ? min(sched.n_sk, seg_begin + p.cpt - kc0) : seg_begin + p.cpt;
+    const int colbase = tile * QD_TILE_N;
 
     // first local chunk index >= seg_begin that belongs to this warp
-    int i = seg_begin + ((warp - seg_begin) % QD_CONSUMERS + QD_CONSUMERS) % QD_CONSUMERS;
-    for (; i < seg_end; i += QD_CONSUMERS) {
-      const int s = i % p.stages;
-      const int kc = (int)((c0 + i) % p.cpt);
-      const int k0 = kc * QD_CHUNK_K;
-      // scales of this chunk's group for the thread's 16 columns
-      float sc[16];
-      {
-        const int srow = p.scale_group ? k0 / p.scale_group : 0;
-        const float* sp = p.scales + (int64_t)srow * p.N + colbase + 16 * g;
-        const bool ok = colbase + 16 * g < p.N;     // N is a multiple of 16
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          float4 v = ok ? __ldg(reinterpret_cast<const float4*>(sp) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-          sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
-        }
-      }
-      // activation operands for the four k-steps of the chunk
+    int i = seg_begin + ((warp - seg_begin) % QD_WARPS + QD_WARPS) % QD_WARPS;
+    for (; i < seg_end; i += QD_WARPS, n_done++) {
+      uint8_t* stage = my_ring + (n_done % QD_DEPTH) * QD_STAGE_BYTES;
+      float sc[8];
       XFrag<XT> xf[4][MT];
+#pragma unroll
+      for (int q = 0; q < 8; q++) sc[q] = sc_next[q];
 #pragma unroll
       for (int ks = 0; ks < 4; ks++)
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
-          const int m = mt * 8 + g, k = k0 + 16 * ks + 2 * t;
-          xf[ks][mt].load(p.x, (int64_t)m * p.K, k, m < p.M && k0 + 16 * ks < p.K);
-        }
-      if (!failed && !mbar_wait_bounded(&full[s], (uint32_t)((i / p.stages) & 1))) {
-        failed = true;
-        atomicExch(&p.status[0], (unsigned)QD_ERR_FULL_WAIT);
-        atomicExch(&p.status[1], (unsigned)i);
-        atomicExch(&s_failed, 1u);
+        for (int mt = 0; mt < MT; mt++) xf[ks][mt] = xf_next[ks][mt];
+      if (i + QD_WARPS < n_local) {
+        int tn, kn;
+        sched.coords(i + QD_WARPS, tn, kn);
+        fetch_chunk_inputs<XT, MT>(p, tn, kn, g, t, sc_next, xf_next);
       }
-      if (failed) continue;
+      // this warp's copy of chunk i is the oldest of its QD_DEPTH open groups
+      asm volatile("cp.async.wait_group %0;" ::"n"(QD_DEPTH - 1) : "memory");
+      __syncwarp();
 
-      float acc[8][MT][4];
+      float acc[4][MT][4];
 #pragma unroll
-      for (int j = 0; j < 8; j++)
+      for (int j = 0; j < 4; j++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
 #pragma unroll
           for (int c = 0; c < 4; c++) acc[j][mt][c] = 0.0f;
 
-      const uint8_t* stage = ring + (size_t)s * QD_STAGE_BYTES;
+      if (!p.debug_skip) {
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++) {
-        // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step: exactly the k indices the mma
-        // fragment assigns to lane t; the 128B swizzle makes the loads conflict-free.
-        uint32_t L[4][4];
+        for (int ks = 0; ks < 4; ks++) {
+          // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step: exactly the k indices the mma
+          // fragment assigns to lane t; the 80-byte pitch makes the loads conflict-free.
+          uint32_t L[4][2];
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-          const int row = 16 * ks + 2 * t + (r & 1) + 8 * (r >> 1);
-          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((g ^ (row & 7)) << 4));
-          L[r][0] = v.x; L[r][1] = v.y; L[r][2] = v.z; L[r][3] = v.w;
-          if (!WUNSIGNED) {
+          for (int r = 0; r < 4; r++) {
+            const int row = 16 * ks + 2 * t + (r & 1) + 8 * (r >> 1);
+            const uint2 v = *reinterpret_cast<const uint2*>(stage + row * QD_PITCH + 8 * g);
+            L[r][0] = v.x; L[r][1] = v.y;
+            if (!WUNSIGNED) { L[r][0] ^= 0x80808080u; L[r][1] ^= 0x80808080u; }
+          }
+          uint32_t xb0[MT][XFrag<XT>::SPLITS], xb1[MT][XFrag<XT>::SPLITS];
 #pragma unroll
-            for (int q = 0; q < 4; q++) L[r][q] ^= 0x80808080u;
+          for (int mt = 0; mt < MT; mt++) xf[ks][mt].operands(mul[mt], xb0[mt], xb1[mt]);
+          // H*[b]: columns b (lo) and 4+b (hi) of the thread's 8, for k rows (2t,2t+1) and (2t+8,2t+9)
+          uint32_t Hlo01[4], Hhi01[4], Hlo23[4], Hhi23[4];
+          bytes_to_f16x2(L[0][0], L[1][0], wbias, Hlo01);
+          bytes_to_f16x2(L[0][1], L[1][1], wbias, Hhi01);
+          bytes_to_f16x2(L[2][0], L[3][0], wbias, Hlo23);
+          bytes_to_f16x2(L[2][1], L[3][1], wbias, Hhi23);
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            const uint32_t a[4] = {Hlo01[b], Hhi01[b], Hlo23[b], Hhi23[b]};
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+              for (int sp = 0; sp < XFrag<XT>::SPLITS; sp++)
+                mma_f16_16816(acc[b][mt], a, xb0[mt][sp], xb1[mt][sp]);
           }
         }
-#pragma unroll
-        for (int qh = 0; qh < 2; qh++) {
-#define QD_BYTE_STEP(B)                                                                             \
-  {                                                                                                 \
-    uint32_t a[4];                                                                                  \
-    a[0] = pack_hi16(byte_to_f32<B>(L[0][qh], magic), byte_to_f32<B>(L[1][qh], magic));             \
-    a[1] = pack_hi16(byte_to_f32<B>(L[0][2 + qh], magic), byte_to_f32<B>(L[1][2 + qh], magic));     \
-    a[2] = pack_hi16(byte_to_f32<B>(L[2][qh], magic), byte_to_f32<B>(L[3][qh], magic));             \
-    a[3] = pack_hi16(byte_to_f32<B>(L[2][2 + qh], magic), byte_to_f32<B>(L[3][2 + qh], magic));     \
-    _Pragma("unroll") for (int mt = 0; mt < MT; mt++) {                                             \
-      _Pragma("unroll") for (int sp = 0; sp < XFrag<XT>::SPLITS; sp++)                              \
-          mma_bf16_16816(acc[4 * qh + B][mt], a, xf[ks][mt].b0[sp], xf[ks][mt].b1[sp]);             \
-    }                                                                                               \
-  }
-          QD_BYTE_STEP(0) QD_BYTE_STEP(1) QD_BYTE_STEP(2) QD_BYTE_STEP(3)
-#undef QD_BYTE_STEP
-        }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);   // stage may be refilled
+      __syncwarp();     // every lane is done reading the stage: refill it
+      issue_chunk_copy(p, sched, i + QD_DEPTH * QD_WARPS, stage, lane);
 
-      // column of acc[j][*][0..1] is 16g+j, of acc[j][*][2..3] is 16g+8+j
+      // column of acc[b][*][0..1] is 8g+b, of acc[b][*][2..3] is 8g+4+b
 #pragma unroll
-      for (int j = 0; j < 8; j++)
+      for (int b = 0; b < 4; b++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
-          tot[j][mt][0] = fmaf(acc[j][mt][0], sc[j], tot[j][mt][0]);
-          tot[j][mt][1] = fmaf(acc[j][mt][1], sc[j], tot[j][mt][1]);
-          tot[j][mt][2] = fmaf(acc[j][mt][2], sc[8 + j], tot[j][mt][2]);
-          tot[j][mt][3] = fmaf(acc[j][mt][3], sc[8 + j], tot[j][mt][3]);
+          tot[b][mt][0] = fmaf(acc[b][mt][0], sc[b], tot[b][mt][0]);
+          tot[b][mt][1] = fmaf(acc[b][mt][1], sc[b], tot[b][mt][1]);
+          tot[b][mt][2] = fmaf(acc[b][mt][2], sc[4 + b], tot[b][mt][2]);
+          tot[b][mt][3] = fmaf(acc[b][mt][3], sc[4 + b], tot[b][mt][3]);
         }
     }
+    QD_STAMP();
 
     // ---- cross-warp reduction of this segment -------------------------
     float* mine = red + warp * RED_FLOATS;
 #pragma unroll
-    for (int j = 0; j < 8; j++)
+    for (int b = 0; b < 4; b++)
 #pragma unroll
       for (int mt = 0; mt < MT; mt++) {
         const int m = mt * 8 + 2 * t;
-        mine[m * QD_TILE_N + 16 * g + j] = tot[j][mt][0];
-        mine[(m + 1) * QD_TILE_N + 16 * g + j] = tot[j][mt][1];
-        mine[m * QD_TILE_N + 16 * g + 8 + j] = tot[j][mt][2];
-        mine[(m + 1) * QD_TILE_N + 16 * g + 8 + j] = tot[j][mt][3];
-        tot[j][mt][0] = tot[j][mt][1] = tot[j][mt][2] = tot[j][mt][3] = 0.0f;
+        mine[m * QD_TILE_N + 8 * g + b] = tot[b][mt][0];
+        mine[(m + 1) * QD_TILE_N + 8 * g + b] = tot[b][mt][1];
+        mine[m * QD_TILE_N + 8 * g + 4 + b] = tot[b][mt][2];
+        mine[(m + 1) * QD_TILE_N + 8 * g + 4 + b] = tot[b][mt][3];
+        tot[b][mt][0] = tot[b][mt][1] = tot[b][mt][2] = tot[b][mt][3] = 0.0f;
       }
-    asm volatile("bar.sync 1, %0;" ::"n"(QD_CONSUMERS * 32) : "memory");
+    __syncthreads();
 
-    constexpr int PER_THREAD = RED_FLOATS / (QD_CONSUMERS * 32);
+    constexpr int PER_THREAD = RED_FLOATS / QD_THREADS;
     float sum[PER_THREAD];
 #pragma unroll
     for (int e = 0; e < PER_THREAD; e++) {
-      const int idx = tid + e * QD_CONSUMERS * 32;
+      const int idx = tid + e * QD_THREADS;
       float v = 0.0f;
 #pragma unroll
-      for (int w = 0; w < QD_CONSUMERS; w++) v += red[w * RED_FLOATS + idx];
+      for (int w = 0; w < QD_WARPS; w++) v += red[w * RED_FLOATS + idx];
       sum[e] = v;
     }
 
-    const bool whole_tile = (first_chunk == tile_begin) && (c0 + seg_end == tile_end);
+    const bool whole_tile = (kc0 == 0) && (seg_end - seg_begin == p.cpt);
     bool finalize = whole_tile;
     if (!whole_tile) {
       // partial tile: park the CTA's sum, then see whether every contributor has arrived
-      const int slot = (first_chunk > tile_begin) ? 0 : 1;
+      const long long tile_begin = (long long)tile * p.cpt, tile_end = tile_begin + p.cpt;
+      const int slot = (kc0 > 0) ? 0 : 1;
       float* dst = p.partials + ((size_t)cta * 2 + slot) * RED_FLOATS;
 #pragma unroll
-      for (int e = 0; e < PER_THREAD; e++) dst[tid + e * QD_CONSUMERS * 32] = sum[e];
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(QD_CONSUMERS * 32) : "memory");
-      const int cf = (int)(((tile_begin + 1) * G - 1) / p.total);
-      const int cl = (int)((tile_end * G - 1) / p.total);
+      for (int e = 0; e < PER_THREAD; e++) dst[tid + e * QD_THREADS] = sum[e];
+      __syncthreads();
+      const int cf = (int)(((tile_begin + 1) * Gsk - 1) / p.sk_total);
+      const int cl = (int)((tile_end * Gsk - 1) / p.sk_total);
       if (tid == 0) {
-        const unsigned old = atomicAdd(&p.counters[ct], 1u);
-        const unsigned last = (old == (unsigned)(cl - cf)) ? 1u : 0u;
-        if (last) p.counters[ct] = 0;      // leave the workspace prepared for the next launch
-        s_flag = last;
         __threadfence();
+        const unsigned old = atomicAdd(&p.counters[tile], 1u);
+        const unsigned last = (old == (unsigned)(cl - cf)) ? 1u : 0u;
+        if (last) p.counters[tile] = 0;      // leave the workspace prepared for the next launch
+        __threadfence();
+        s_flag = last;
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(QD_CONSUMERS * 32) : "memory");
+      __syncthreads();
       finalize = (s_flag != 0);
       if (finalize) {
 #pragma unroll
         for (int e = 0; e < PER_THREAD; e++) sum[e] = 0.0f;
         for (int c = cf; c <= cl; c++) {       // fixed order: results do not depend on arrival order
-          const long long cs = (long long)c * p.total / G;
+          const long long cs = (long long)c * p.sk_total / Gsk;
           const float* src = p.partials + ((size_t)c * 2 + (cs > tile_begin ? 0 : 1)) * RED_FLOATS;
 #pragma unroll
-          for (int e = 0; e < PER_THREAD; e++) sum[e] += __ldcg(src + tid + e * QD_CONSUMERS * 32);
+          for (int e = 0; e < PER_THREAD; e++) sum[e] += __ldcg(src + tid + e * QD_THREADS);
         }
       }
     }
-    if (finalize && !*reinterpret_cast<volatile unsigned*>(&s_failed)) {
+    if (finalize) {
 #pragma unroll
       for (int e = 0; e < PER_THREAD; e++) {
-        const int idx = tid + e * QD_CONSUMERS * 32;
+        const int idx = tid + e * QD_THREADS;
         const int m = idx / QD_TILE_N, col = colbase + idx % QD_TILE_N;
         if (m < p.M && col < p.N) {
-          float v = sum[e];
+          float v = sum[e] * s_inv[m];           // undo the row's power-of-two scaling (exact)
           if (p.bias) v += __ldg(p.bias + col);
           v = apply_activation(v, p.activation);
           Scalar<XT>::store(reinterpret_cast<XT*>(p.out), (int64_t)m * p.N + col, v);
         }
       }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(QD_CONSUMERS * 32) : "memory");   // red[] is reused
+    __syncthreads();   // red[] and s_flag are reused by the next segment
+    QD_STAMP();
     seg_begin = seg_end;
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+#undef QD_STAMP
 }
 
 // ---------------------------------------------------------------------------
 // planning and launch
 // ---------------------------------------------------------------------------
-static int decode_stages(int mt) { return mt == 1 ? 24 : 20; }
 static size_t decode_smem(int mt) {
-  return 1024 + (size_t)decode_stages(mt) * QD_STAGE_BYTES + (size_t)QD_CONSUMERS * mt * 8 * QD_TILE_N * 4 +
-         (size_t)2 * decode_stages(mt) * 8;
+  return (size_t)QD_WARPS * QD_DEPTH * QD_STAGE_BYTES + (size_t)QD_WARPS * mt * 8 * QD_TILE_N * 4;
+}
+
+// Tiles split across CTAs (stream-K) and tiles owned whole, for `tiles` column tiles on `grid` CTAs.
+static void decode_schedule(long long tiles, int grid, int* sk_tiles, int* dp_per_cta) {
+  *dp_per_cta = (int)(tiles / grid);
+  *sk_tiles = (int)(tiles - (long long)*dp_per_cta * grid);
 }
 
 static bool decode_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -466,6 +552,7 @@ static bool decode_eligible(const cb_qdense_desc& d, std::string* why) {
   if (d.scale_layout == CB_SCALE_KGROUP && (d.block_size <= 0 || d.block_size % QD_CHUNK_K != 0))
     return no("K-group size must be a multiple of 64");
   if (d.K > (1 << 30) || d.N > (1 << 30)) return no("dimension too large");
+  if (((d.K + QD_CHUNK_K - 1) / QD_CHUNK_K) * ((d.N + QD_TILE_N - 1) / QD_TILE_N) >= (1ll << 31)) return no("too many chunks");
   return true;
 }
 
@@ -506,13 +593,12 @@ int qdense_plan(cb_plan* p) {
   const int mt = d.M <= 8 ? 1 : 2;
   const long long n_tiles = (d.N + QD_TILE_N - 1) / QD_TILE_N;
   const long long cpt = (d.K + QD_CHUNK_K - 1) / QD_CHUNK_K;
-  const long long total = n_tiles * cpt;
-  p->blocks = (int)std::min<long long>(p->n_sm, total);
+  p->blocks = (int)std::min<long long>(p->n_sm, n_tiles * cpt);
   p->threads = QD_THREADS;
   p->dyn_smem = (int)decode_smem(mt);
   p->counter_bytes = (QD_WS_HEADER + (size_t)n_tiles * 4 + 255) & ~(size_t)255;
-  p->workspace_bytes = p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4;
-  p->has_status = true;
+  p->workspace_bytes = p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4 + (size_t)p->blocks * 16 * 8;
+  p->has_status = false;
   p->name = std::string("qdense_decode_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (mt == 1 ? "_m8" : "_m16") +
             (d.w_dtype == CB_U8 ? "_u8" : "_i8");
   return CB_OK;
@@ -533,81 +619,49 @@ static int launch_generic(const cb_plan* p, const void* const* in, void* const* 
   return CB_OK;
 }
 
-// Encoded tensor maps are cached per (device, weights pointer, shape): a resident
-// weight matrix is encoded once, not on every launch.
-struct MapCacheEntry { int dev; const void* w; int64_t K, N; CUtensorMap map; };
-static std::mutex g_map_mu;
-static MapCacheEntry g_map_cache[64];
-static int g_map_next = 0, g_map_count = 0;
-
-static int weight_tensor_map(int dev, const void* w, int64_t K, int64_t N, CUtensorMap* out) {
-  std::lock_guard<std::mutex> lock(g_map_mu);
-  for (int i = 0; i < g_map_count; i++) {
-    const MapCacheEntry& e = g_map_cache[i];
-    if (e.dev == dev && e.w == w && e.K == K && e.N == N) { *out = e.map; return CB_OK; }
-  }
-  encode_tiled_fn enc = tensor_map_encoder();
-  if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  if ((reinterpret_cast<uintptr_t>(w) & 15) != 0)
-    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: weights must be 16-byte aligned");
-  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
-  cuuint64_t strides[1] = {(cuuint64_t)N};
-  cuuint32_t box[2] = {QD_TILE_N, QD_CHUNK_K};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  MapCacheEntry& e = g_map_cache[g_map_next];
-  e.dev = dev; e.w = w; e.K = K; e.N = N; e.map = m;
-  g_map_next = (g_map_next + 1) % 64;
-  if (g_map_count < 64) g_map_count++;
-  *out = m;
-  return CB_OK;
-}
-
 template <typename XT, int MT, bool WU>
-static int launch_decode_t(const cb_plan* p, const CUtensorMap& map, const QdParams& prm, cudaStream_t s) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  // The attribute is per device; setting it again is cheap and keeps multi-GPU processes correct.
-  attr_err = cudaFuncSetAttribute(qdense_decode_kernel<XT, MT, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize, p->dyn_smem);
-  (void)once;
-  CB_CUDA(attr_err);
-  qdense_decode_kernel<XT, MT, WU><<<p->blocks, QD_THREADS, p->dyn_smem, s>>>(map, prm);
+static int launch_decode_t(const cb_plan* p, const QdParams& prm, cudaStream_t s) {
+  // The attribute is per device: set it once for each device this process launches on.
+  static std::atomic<bool> configured[64];
+  if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(qdense_decode_kernel<XT, MT, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize, p->dyn_smem));
+    if (p->dev < 64) configured[p->dev].store(true, std::memory_order_release);
+  }
+  qdense_decode_kernel<XT, MT, WU><<<p->blocks, QD_THREADS, p->dyn_smem, s>>>(prm);
   CB_CUDA(cudaGetLastError());
   return CB_OK;
 }
 
 static int launch_decode(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
-  CUtensorMap map;
-  CB_TRY(weight_tensor_map(p->dev, in[1], d.K, d.N, &map));
   QdParams prm;
   memset(&prm, 0, sizeof(prm));
   prm.x = in[0];
+  prm.w = (const uint8_t*)in[1];
   prm.scales = (const float*)in[2];
   prm.bias = d.has_bias ? (const float*)in[3] : nullptr;
   prm.out = out[0];
   uint8_t* w8 = (uint8_t*)ws;
+  const int mt = d.M <= 8 ? 1 : 2;
   prm.status = (unsigned*)w8;
   prm.counters = (unsigned*)(w8 + QD_WS_HEADER);
   prm.partials = (float*)(w8 + p->counter_bytes);
   prm.M = (int)d.M; prm.K = (int)d.K; prm.N = (int)d.N;
   prm.n_tiles = (int)((d.N + QD_TILE_N - 1) / QD_TILE_N);
   prm.cpt = (int)((d.K + QD_CHUNK_K - 1) / QD_CHUNK_K);
-  prm.total = (long long)prm.n_tiles * prm.cpt;
+  decode_schedule(prm.n_tiles, p->blocks, &prm.sk_tiles, &prm.dp_per_cta);
+  prm.sk_total = (long long)prm.sk_tiles * prm.cpt;
   prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
   prm.activation = d.activation;
-  const int mt = d.M <= 8 ? 1 : 2;
-  prm.stages = decode_stages(mt);
-  if ((reinterpret_cast<uintptr_t>(in[0]) & 7) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
-    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x must be 8-byte and scales 16-byte aligned");
+  { const char* e = getenv("CB_QDENSE_DEBUG_SKIP"); prm.debug_skip = (e && e[0] == '1') ? 1 : 0; }
+  { const char* e = getenv("CB_QDENSE_DEBUG_STAMPS");
+    prm.dbg = (e && e[0] == '1') ? (unsigned long long*)(w8 + p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4) : nullptr; }
+  if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
 #define QD_DISPATCH(XT)                                                                       \
-  (mt == 1 ? (wu ? launch_decode_t<XT, 1, true>(p, map, prm, s) : launch_decode_t<XT, 1, false>(p, map, prm, s)) \
-           : (wu ? launch_decode_t<XT, 2, true>(p, map, prm, s) : launch_decode_t<XT, 2, false>(p, map, prm, s)))
+  (mt == 1 ? (wu ? launch_decode_t<XT, 1, true>(p, prm, s) : launch_decode_t<XT, 1, false>(p, prm, s)) \
+           : (wu ? launch_decode_t<XT, 2, true>(p, prm, s) : launch_decode_t<XT, 2, false>(p, prm, s)))
   return bf ? QD_DISPATCH(__nv_bfloat16) : QD_DISPATCH(float);
 #undef QD_DISPATCH
 }
