@@ -6,7 +6,7 @@ package is the host-side mirror of the reference's Backend / Builder / Function 
 Executable / Buffer interface over that ABI.  There is no CPU fallback: importing
 works without a GPU (plans can be built), running anything needs one.
 """
-from . import device
+from . import backend, device
 from ._lib import BackendError, ErrNotImplemented, load as load_library
 
-__all__ = ["device", "BackendError", "ErrNotImplemented", "load_library"]
+__all__ = ["backend", "device", "BackendError", "ErrNotImplemented", "load_library"]

@@ -1,0 +1,552 @@
+"""Host-side mirror of gomlx/compute's Backend / Builder / Function / Executable / Buffer
+interface (compute.go, builder.go, function.go, executable.go, buffer.go of the
+reference) for the accelerated path.  Method names and argument meaning follow
+the reference so that tests read like its own; the work happens in
+libcudabackend (include/cudabackend_graph.h).  Ops outside the path raise
+ErrNotImplemented, as a Go backend embedding notimplemented.Function would.
+
+Host data are numpy arrays; bfloat16 / float16 travel as uint16 bit patterns
+with an explicit dtype (compute_b200.device.BF16 / F16).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _lib, device as dv
+from ._lib import BackendError, ErrNotImplemented, check
+
+# compute.OpType values used by Capabilities (optype.go)
+OP_PARAMETER, OP_CONSTANT, OP_DOT_GENERAL = 1, 2, 32
+OP_FUSED_SDPA, OP_FUSED_QUANTIZED_DENSE = 120, 123
+OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 120: "FusedScaledDotProductAttention",
+            123: "FusedQuantizedDense"}
+
+# compute.QuantizationScheme (fused_ops.go:81-98)
+QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
+# compute.AttentionAxesLayout (fused_ops.go:6-16)
+LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
+
+
+class _SdpaOptions(C.Structure):
+    _fields_ = [("quantized_matmuls", C.c_int), ("query_seq_len", C.c_void_p), ("key_value_seq_len", C.c_void_p),
+                ("bias", C.c_void_p), ("scale", C.c_double), ("causal", C.c_int), ("mask", C.c_void_p)]
+
+
+_GRAPH_SIGNATURES = {
+    "cbg_backend_new": ([C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_backend_name": ([C.c_void_p], C.c_char_p),
+    "cbg_backend_description": ([C.c_void_p], C.c_char_p),
+    "cbg_backend_num_devices": ([C.c_void_p], C.c_int),
+    "cbg_backend_device_description": ([C.c_void_p, C.c_int, C.c_char_p, C.c_size_t], C.c_int),
+    "cbg_backend_capabilities": ([C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int32), C.POINTER(C.c_int)], C.c_int),
+    "cbg_backend_finalize": ([C.c_void_p], C.c_int),
+    "cbg_backend_is_finalized": ([C.c_void_p], C.c_int),
+    "cbg_backend_free": ([C.c_void_p], C.c_int),
+    "cbg_buffer_from_flat": ([C.c_void_p, C.c_int, C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_buffer_shape": ([C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
+    "cbg_buffer_device_num": ([C.c_void_p, C.POINTER(C.c_int)], C.c_int),
+    "cbg_buffer_to_flat": ([C.c_void_p, C.c_void_p, C.c_size_t], C.c_int),
+    "cbg_buffer_copy_to_device": ([C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_buffer_device_ptr": ([C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_buffer_finalize": ([C.c_void_p], C.c_int),
+    "cbg_builder_new": ([C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_builder_main": ([C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_builder_distributed_spmd": ([C.c_void_p, C.c_int], C.c_int),
+    "cbg_builder_device_assignment": ([C.c_void_p, C.POINTER(C.c_int), C.c_int], C.c_int),
+    "cbg_builder_compile": ([C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_builder_free": ([C.c_void_p], C.c_int),
+    "cbg_fn_parameter": ([C.c_void_p, C.c_char_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_constant": ([C.c_void_p, C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_shape": ([C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
+    "cbg_fn_return": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int], C.c_int),
+    "cbg_fn_dot_general": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.c_int, C.c_void_p,
+                            C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int32, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_reshape": ([C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_slice": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_iota": ([C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_convert_dtype": ([C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_transpose": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                      C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_sdpa": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(_SdpaOptions), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_not_implemented": ([C.c_void_p, C.c_char_p], C.c_int),
+    "cbg_exec_num_inputs": ([C.c_void_p], C.c_int),
+    "cbg_exec_num_outputs": ([C.c_void_p], C.c_int),
+    "cbg_exec_input_info": ([C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
+    "cbg_exec_output_info": ([C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
+    "cbg_exec_kernel_names": ([C.c_void_p, C.c_char_p, C.c_size_t], C.c_int),
+    "cbg_exec_execute": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_uint8), C.c_int, C.POINTER(C.c_void_p), C.c_int], C.c_int),
+    "cbg_exec_finalize": ([C.c_void_p], C.c_int),
+}
+_glib = None
+
+
+def _g():
+    global _glib
+    if _glib is None:
+        lib = _lib.load()
+        for name, (args, res) in _GRAPH_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = res
+        _glib = lib
+    return _glib
+
+
+def _i64(vals):
+    vals = list(vals)
+    return (C.c_int64 * max(len(vals), 1))(*vals)
+
+
+def _ints(vals):
+    vals = list(vals or [])
+    return (C.c_int * max(len(vals), 1))(*vals)
+
+
+@dataclass(frozen=True)
+class Shape:
+    """shapes.Shape: dtype + dimensions."""
+    dtype: int
+    dimensions: Tuple[int, ...] = ()
+
+    def rank(self) -> int:
+        return len(self.dimensions)
+
+    def size(self) -> int:
+        return int(np.prod(self.dimensions, dtype=np.int64)) if self.dimensions else 1
+
+
+def make_shape(dtype: int, *dims: int) -> Shape:
+    return Shape(dtype, tuple(int(d) for d in dims))
+
+
+def _read_shape(fn, handle) -> Shape:
+    dt, rk, dims = C.c_int32(0), C.c_int(0), (C.c_int64 * 8)()
+    check(fn(handle, C.byref(dt), C.byref(rk), dims))
+    return Shape(dt.value, tuple(dims[i] for i in range(rk.value)))
+
+
+@dataclass
+class Capabilities:
+    """compute.Capabilities (capabilities.go:12-39)."""
+    Operations: dict = field(default_factory=dict)
+    DTypes: dict = field(default_factory=dict)
+    Functions: bool = False
+    DynamicAxes: bool = False
+    PreferConstantsForVariables: bool = False
+
+
+@dataclass
+class DotGeneralConfig:
+    """compute.DotGeneralConfig (standard_ops.go:91-111); 0 = InvalidDType = unset."""
+    AccumulatorDType: int = 0
+    OutputDType: int = 0
+
+
+@dataclass
+class Quantization:
+    """compute.Quantization (fused_ops.go:204-234).  BlockAxis=1 is the reference layout
+    (Scale [K, ceil(N/BlockSize)]); BlockAxis=0 is this backend's extension
+    (Scale [ceil(K/BlockSize), N]; BlockSize=K gives per-output-channel scales)."""
+    Scheme: int = QUANT_LINEAR
+    Scale: Optional["Value"] = None
+    ZeroPoint: Optional["Value"] = None
+    BlockAxis: int = 1
+    BlockSize: int = 1
+    GGMLType: int = 0
+
+
+@dataclass
+class ScaledDotProductAttentionConfig:
+    """compute.ScaledDotProductAttentionConfig (fused_ops.go:245-277)."""
+    QuantizedMatmuls: bool = False
+    QuerySeqLen: Optional["Value"] = None
+    KeyValueSeqLen: Optional["Value"] = None
+    Bias: Optional["Value"] = None
+    Scale: float = 0.0
+    Causal: bool = False
+    Mask: Optional["Value"] = None
+
+
+class Value:
+    """compute.Value: an opaque node of a function under construction."""
+
+    def __init__(self, handle, fn: "Function"):
+        self.handle = handle
+        self.fn = fn
+
+
+class Buffer:
+    """compute.Buffer (buffer.go:12-42)."""
+
+    def __init__(self, handle, backend: "Backend"):
+        self.handle = handle
+        self._backend = backend
+
+    def Backend(self) -> "Backend":
+        return self._backend
+
+    def Shape(self) -> Shape:
+        return _read_shape(_g().cbg_buffer_shape, self.handle)
+
+    def DeviceNum(self) -> int:
+        d = C.c_int(0)
+        check(_g().cbg_buffer_device_num(self.handle, C.byref(d)))
+        return d.value
+
+    def ToFlatData(self, flat: np.ndarray) -> None:
+        """Copies the buffer into `flat` (exact size), like Buffer.ToFlatData."""
+        if not flat.flags["C_CONTIGUOUS"]:
+            raise BackendError(_lib.ERR_INVALID_ARG, "Buffer.ToFlatData: flat must be contiguous")
+        check(_g().cbg_buffer_to_flat(self.handle, flat.ctypes.data, flat.nbytes))
+
+    def ToNumpy(self) -> np.ndarray:
+        s = self.Shape()
+        out = np.empty(s.dimensions, dv.NP_CARRIER[s.dtype])
+        self.ToFlatData(out)
+        return out
+
+    def CopyToDevice(self, device_num: int) -> "Buffer":
+        h = C.c_void_p()
+        check(_g().cbg_buffer_copy_to_device(self.handle, device_num, C.byref(h)))
+        return Buffer(h, self._backend)
+
+    def DevicePtr(self) -> int:
+        p = C.c_void_p()
+        check(_g().cbg_buffer_device_ptr(self.handle, C.byref(p)))
+        return p.value
+
+    def Data(self):
+        raise BackendError(_lib.ERR_INVALID_ARG, "Buffer.Data: the cuda backend has no shared (host-visible) buffers")
+
+    def Finalize(self) -> None:
+        if self.handle:
+            _g().cbg_buffer_finalize(self.handle)
+            self.handle = None
+
+
+class Function:
+    """compute.Function (function.go:23-134): graph building.  Only the ops of the
+    accelerated path exist; the rest raise ErrNotImplemented."""
+
+    def __init__(self, handle, builder: "Builder"):
+        self.handle = handle
+        self._builder = builder
+
+    def Builder(self) -> "Builder":
+        return self._builder
+
+    def Name(self) -> str:
+        return "main"
+
+    def _v(self, h) -> Value:
+        return Value(h, self)
+
+    def Parameter(self, name: str, shape: Shape, sharding=None) -> Value:
+        if sharding is not None:
+            raise ErrNotImplemented(_lib.ERR_NOT_IMPLEMENTED, "Parameter: sharding specs are not implemented by the cuda backend")
+        h = C.c_void_p()
+        check(_g().cbg_fn_parameter(self.handle, name.encode(), shape.dtype, shape.rank(), _i64(shape.dimensions), C.byref(h)))
+        return self._v(h)
+
+    def Constant(self, flat, *dims: int, dtype: Optional[int] = None) -> Value:
+        a = np.ascontiguousarray(flat)
+        if dtype is None:
+            rev = {np.dtype(v): k for k, v in dv.NP_CARRIER.items() if k not in (dv.F16, dv.BF16, dv.U16)}
+            rev[np.dtype(np.uint16)] = dv.U16
+            dtype = rev[a.dtype]
+        h = C.c_void_p()
+        n = int(np.prod(dims, dtype=np.int64)) if dims else 1
+        if a.size != n:
+            raise BackendError(_lib.ERR_INVALID_ARG, f"Constant: flat has {a.size} elements, dimensions {list(dims)} need {n}")
+        check(_g().cbg_fn_constant(self.handle, a.ctypes.data, dtype, len(dims), _i64(dims), C.byref(h)))
+        return self._v(h)
+
+    def Shape(self, value: Value) -> Shape:
+        return _read_shape(_g().cbg_fn_shape, value.handle)
+
+    def Return(self, outputs: Sequence[Value], shardings=None) -> None:
+        arr = (C.c_void_p * max(len(outputs), 1))(*[o.handle for o in outputs])
+        check(_g().cbg_fn_return(self.handle, arr, len(outputs)))
+
+    # ---- StandardOps on the path
+    def DotGeneral(self, lhs: Value, lhsContractingAxes, lhsBatchAxes, rhs: Value, rhsContractingAxes, rhsBatchAxes,
+                   config: Optional[DotGeneralConfig] = None) -> Value:
+        config = config or DotGeneralConfig()
+        lc, lb = list(lhsContractingAxes or []), list(lhsBatchAxes or [])
+        rc, rb = list(rhsContractingAxes or []), list(rhsBatchAxes or [])
+        if len(lc) != len(rc):
+            raise BackendError(_lib.ERR_INVALID_ARG, f"DotGeneral number of contracting axes for lhs ({len(lc)}) doesn't match rhs ({len(rc)})")
+        if len(lb) != len(rb):
+            raise BackendError(_lib.ERR_INVALID_ARG, f"DotGeneral number of batch axes for lhs ({len(lb)}) doesn't match rhs ({len(rb)})")
+        h = C.c_void_p()
+        check(_g().cbg_fn_dot_general(self.handle, lhs.handle, _ints(lc), len(lc), _ints(lb), len(lb), rhs.handle,
+                                      _ints(rc), _ints(rb), config.AccumulatorDType, config.OutputDType, C.byref(h)))
+        return self._v(h)
+
+    def Reshape(self, x: Value, *dims: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_reshape(self.handle, x.handle, len(dims), _i64(dims), C.byref(h)))
+        return self._v(h)
+
+    def Slice(self, x: Value, starts, limits, strides=None) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_slice(self.handle, x.handle, _i64(starts), _i64(limits),
+                                _i64(strides) if strides is not None else None, C.byref(h)))
+        return self._v(h)
+
+    def Iota(self, shape: Shape, iotaAxis: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_iota(self.handle, shape.dtype, shape.rank(), _i64(shape.dimensions), iotaAxis, C.byref(h)))
+        return self._v(h)
+
+    def ConvertDType(self, x: Value, dtype: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_convert_dtype(self.handle, x.handle, dtype, C.byref(h)))
+        return self._v(h)
+
+    def Transpose(self, x: Value, *permutation: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_transpose(self.handle, x.handle, _ints(permutation), C.byref(h)))
+        return self._v(h)
+
+    # ---- FusedOps on the path
+    def FusedQuantizedDense(self, x: Value, weights: Value, bias: Optional[Value], weightsQuantization: Quantization,
+                            activation: int = dv.ACT_NONE) -> Value:
+        q = weightsQuantization
+        if q is None:
+            raise BackendError(_lib.ERR_INVALID_ARG, "FusedQuantizedDense: weightsQuantization must not be nil")
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_quantized_dense(
+            self.handle, x.handle, weights.handle, bias.handle if bias is not None else None, q.Scheme,
+            q.Scale.handle if q.Scale is not None else None, q.ZeroPoint.handle if q.ZeroPoint is not None else None,
+            q.BlockAxis, q.BlockSize, activation, C.byref(h)))
+        return self._v(h)
+
+    def FusedScaledDotProductAttention(self, query: Value, key: Value, value: Value, axesLayout: int = LAYOUT_BHSD,
+                                       options: Optional[ScaledDotProductAttentionConfig] = None):
+        """Returns (output, statesForVJP); statesForVJP is empty (no fused backward)."""
+        o = None
+        if options is not None:
+            hv = lambda v: v.handle if v is not None else None
+            o = _SdpaOptions(int(options.QuantizedMatmuls), hv(options.QuerySeqLen), hv(options.KeyValueSeqLen),
+                             hv(options.Bias), float(options.Scale), int(options.Causal), hv(options.Mask))
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_sdpa(self.handle, query.handle, key.handle, value.handle, axesLayout,
+                                     C.byref(o) if o is not None else None, C.byref(h)))
+        return self._v(h), []
+
+    def FusedScaledDotProductAttentionVJP(self, *args, **kwargs):
+        return self._not_implemented("FusedScaledDotProductAttentionVJP")
+
+    # ---- everything else: notimplemented
+    def _not_implemented(self, op: str):
+        check(_g().cbg_fn_not_implemented(self.handle, op.encode()))
+
+    def __getattr__(self, name: str):
+        # Any other op of the interface (Neg, Add, FusedSoftmax, AllReduce, While, ...).
+        if name and name[0].isupper():
+            def stub(*args, **kwargs):
+                return self._not_implemented(name)
+            return stub
+        raise AttributeError(name)
+
+
+class Executable:
+    """compute.Executable (executable.go:10-37)."""
+
+    def __init__(self, handle, backend: "Backend"):
+        self.handle = handle
+        self._backend = backend
+
+    def Inputs(self) -> Tuple[List[str], List[Shape]]:
+        names, shapes = [], []
+        for i in range(_g().cbg_exec_num_inputs(self.handle)):
+            nm = C.create_string_buffer(256)
+            dt, rk, dims = C.c_int32(0), C.c_int(0), (C.c_int64 * 8)()
+            check(_g().cbg_exec_input_info(self.handle, i, nm, 256, C.byref(dt), C.byref(rk), dims))
+            names.append(nm.value.decode())
+            shapes.append(Shape(dt.value, tuple(dims[j] for j in range(rk.value))))
+        return names, shapes
+
+    def Outputs(self) -> List[Shape]:
+        out = []
+        for i in range(_g().cbg_exec_num_outputs(self.handle)):
+            dt, rk, dims = C.c_int32(0), C.c_int(0), (C.c_int64 * 8)()
+            check(_g().cbg_exec_output_info(self.handle, i, C.byref(dt), C.byref(rk), dims))
+            out.append(Shape(dt.value, tuple(dims[j] for j in range(rk.value))))
+        return out
+
+    def KernelNames(self) -> List[str]:
+        buf = C.create_string_buffer(4096)
+        check(_g().cbg_exec_kernel_names(self.handle, buf, 4096))
+        return [s for s in buf.value.decode().split("\n") if s]
+
+    def Execute(self, inputs: Sequence[Buffer], donate: Optional[Sequence[bool]] = None, defaultDevice: int = 0) -> List[Buffer]:
+        n_in = len(inputs)
+        ins = (C.c_void_p * max(n_in, 1))(*[b.handle if b is not None else None for b in inputs])
+        don = None
+        if donate is not None:
+            if len(donate) != n_in:
+                raise BackendError(_lib.ERR_INVALID_ARG, f"Execute: donate has {len(donate)} entries for {n_in} inputs")
+            don = (C.c_uint8 * max(n_in, 1))(*[1 if d else 0 for d in donate])
+        n_out_max = max(_g().cbg_exec_num_outputs(self.handle) * max(self._backend.NumDevices(), 1), 1)
+        outs = (C.c_void_p * n_out_max)()
+        check(_g().cbg_exec_execute(self.handle, ins, n_in, don, defaultDevice, outs, n_out_max))
+        if donate is not None:
+            for b, d in zip(inputs, donate):
+                if d:
+                    b._donated = True
+        return [Buffer(C.c_void_p(outs[i]), self._backend) for i in range(n_out_max) if outs[i]]
+
+    def Finalize(self) -> None:
+        if self.handle:
+            _g().cbg_exec_finalize(self.handle)
+            self.handle = None
+
+
+class Builder:
+    """compute.Builder (builder.go:29-82)."""
+
+    def __init__(self, handle, backend: "Backend", name: str):
+        self.handle = handle
+        self._backend = backend
+        self._name = name
+        self._main = None
+
+    def Name(self) -> str:
+        return self._name
+
+    def Main(self) -> Function:
+        if self._main is None:
+            h = C.c_void_p()
+            check(_g().cbg_builder_main(self.handle, C.byref(h)))
+            self._main = Function(h, self)
+        return self._main
+
+    def NewFunction(self, name: str):
+        raise ErrNotImplemented(_lib.ERR_NOT_IMPLEMENTED, "NewFunction: functions/closures are not implemented by the cuda backend")
+
+    def OpShape(self, value: Value) -> Shape:
+        return _read_shape(_g().cbg_fn_shape, value.handle)
+
+    def DistributedSPMD(self, numDevices: int) -> None:
+        check(_g().cbg_builder_distributed_spmd(self.handle, numDevices))
+
+    def DistributedAutoSharding(self, *meshes) -> None:
+        raise ErrNotImplemented(_lib.ERR_NOT_IMPLEMENTED, "DistributedAutoSharding is not implemented by the cuda backend")
+
+    def DeviceAssignment(self, *devices: int) -> None:
+        check(_g().cbg_builder_device_assignment(self.handle, _ints(devices), len(devices)))
+
+    def Compile(self) -> Executable:
+        h = C.c_void_p()
+        check(_g().cbg_builder_compile(self.handle, C.byref(h)))
+        return Executable(h, self._backend)
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _g().cbg_builder_free(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+class Backend:
+    """compute.Backend (compute.go:68-102) + DataInterface (buffer.go:46-61)."""
+
+    def __init__(self, config: str = ""):
+        h = C.c_void_p()
+        check(_g().cbg_backend_new(config.encode(), C.byref(h)))
+        self.handle = h
+
+    def Name(self) -> str:
+        return _g().cbg_backend_name(self.handle).decode()
+
+    def String(self) -> str:
+        return self.Name()
+
+    def Description(self) -> str:
+        return _g().cbg_backend_description(self.handle).decode()
+
+    def NumDevices(self) -> int:
+        return _g().cbg_backend_num_devices(self.handle)
+
+    def DeviceDescription(self, deviceNum: int) -> str:
+        buf = C.create_string_buffer(256)
+        check(_g().cbg_backend_device_description(self.handle, deviceNum, buf, 256))
+        return buf.value.decode()
+
+    def Capabilities(self) -> Capabilities:
+        ops, dts = (C.c_int32 * 32)(), (C.c_int32 * 32)()
+        no, nd = C.c_int(32), C.c_int(32)
+        check(_g().cbg_backend_capabilities(self.handle, ops, C.byref(no), dts, C.byref(nd)))
+        return Capabilities(Operations={ops[i]: True for i in range(no.value)},
+                            DTypes={dts[i]: True for i in range(nd.value)})
+
+    def Builder(self, name: str) -> Builder:
+        h = C.c_void_p()
+        check(_g().cbg_builder_new(self.handle, name.encode(), C.byref(h)))
+        return Builder(h, self, name)
+
+    # ---- DataInterface
+    def BufferFromFlatData(self, deviceNum: int, flat: np.ndarray, shape: Shape) -> Buffer:
+        a = np.ascontiguousarray(flat, dv.NP_CARRIER.get(shape.dtype))
+        if a.size != shape.size():
+            raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} elements, shape needs {shape.size()}")
+        h = C.c_void_p()
+        check(_g().cbg_buffer_from_flat(self.handle, deviceNum, a.ctypes.data, shape.dtype, shape.rank(),
+                                        _i64(shape.dimensions), C.byref(h)))
+        return Buffer(h, self)
+
+    def HasSharedBuffers(self) -> bool:
+        return False
+
+    def NewSharedBuffer(self, deviceNum: int, shape: Shape):
+        raise BackendError(_lib.ERR_INVALID_ARG, "NewSharedBuffer: the cuda backend has no shared buffers")
+
+    def Finalize(self) -> None:
+        if self.handle:
+            check(_g().cbg_backend_finalize(self.handle))
+
+    def IsFinalized(self) -> bool:
+        return bool(_g().cbg_backend_is_finalized(self.handle))
+
+
+def New(config: str = "") -> Backend:
+    """compute.NewWithConfig("cuda:<config>")."""
+    return Backend(config)
+
+
+def exec_graph(backend: Backend, inputs: Sequence[Tuple[np.ndarray, int]], build_fn, default_device: int = 0):
+    """The reference's testutil.Exec helper (support/testutil/exec.go:14-76): one parameter per
+    input (array, dtype), build, compile, execute, and return the outputs as numpy arrays."""
+    builder = backend.Builder("test")
+    fn = builder.Main()
+    params, bufs = [], []
+    for i, (arr, dtype) in enumerate(inputs):
+        arr = np.asarray(arr)
+        shape = make_shape(dtype, *arr.shape)
+        params.append(fn.Parameter(f"x{i}", shape))
+        bufs.append(backend.BufferFromFlatData(default_device, arr, shape))
+    outs = build_fn(fn, params)
+    if isinstance(outs, Value):
+        outs = [outs]
+    fn.Return(list(outs))
+    exe = builder.Compile()
+    try:
+        results = exe.Execute(bufs, None, default_device)
+        arrays = [r.ToNumpy() for r in results]
+        shapes = [r.Shape() for r in results]
+        for r in results:
+            r.Finalize()
+    finally:
+        for b in bufs:
+            b.Finalize()
+        exe.Finalize()
+    return arrays, shapes

@@ -13,7 +13,7 @@ OUT = os.path.join(HERE, "libcudabackend.so")
 OBJ = os.path.join(HERE, "build")
 
 SOURCES = ["runtime.cu", "qdense.cu", "dot.cu", "dot_generic.cu", "gemm_tcgen05.cu",
-           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "helper_ops.cu"]
+           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "helper_ops.cu", "graph.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-DCB_BUILDING"]
@@ -37,6 +37,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "cudabackend.h"))
+    headers.append(os.path.join(HERE, "..", "include", "cudabackend_graph.h"))
     headers.append(os.path.abspath(__file__))
     cc = nvcc()
     # gcc 13 from the system; an unrelated CC in the environment must not leak into nvcc

@@ -1,0 +1,121 @@
+/*
+ * libcudabackend — host-side graph layer: a C-handle rendering of gomlx/compute's
+ * Backend / Builder / Function / Executable / Buffer interfaces for the accelerated
+ * path (FusedQuantizedDense, DotGeneral, FusedScaledDotProductAttention and the
+ * helper ops around them).  It is written in C++ inside the library (no Go toolchain
+ * exists where this was built) and keeps the reference's method names, argument
+ * meaning and error behaviour; every other op of the interface is not implemented
+ * and reports CB_ERR_NOT_IMPLEMENTED, the equivalent of embedding
+ * notimplemented.Function (notimplemented/function.go:13).
+ *
+ * Conventions: as in cudabackend.h (status codes, cb_last_error()).  `host_*`
+ * pointers are host memory; handles are opaque and owned by the caller until the
+ * matching *_finalize / *_free call.  A Builder/Function is single-threaded; an
+ * Executable may be executed from several threads at once (executable.go:10-37).
+ */
+#ifndef CUDABACKEND_GRAPH_H
+#define CUDABACKEND_GRAPH_H
+
+#include "cudabackend.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cbg_backend cbg_backend;   /* compute.Backend   (compute.go:68-102)     */
+typedef struct cbg_builder cbg_builder;   /* compute.Builder   (builder.go:29-82)      */
+typedef struct cbg_function cbg_function; /* compute.Function  (function.go:23-134)    */
+typedef struct cbg_value cbg_value;       /* compute.Value     (builder.go:12)         */
+typedef struct cbg_exec cbg_exec;         /* compute.Executable(executable.go:10-37)   */
+typedef struct cbg_buffer cbg_buffer;     /* compute.Buffer    (buffer.go:12-42)       */
+
+/* ---- Backend.  config: "" or comma-separated keys, e.g. "devices=0,fallback_only"
+ *      (the role of gobackend.New's config string, internal/gobackend/gobackend.go:58-104).
+ *      fallback_only forces the generic kernels (like ForceSmallVariant in the reference's tests). */
+int cbg_backend_new(const char* config, cbg_backend** backend);          /* compute.NewWithConfig("cuda:<config>") */
+const char* cbg_backend_name(const cbg_backend* b);                       /* Backend.Name        */
+const char* cbg_backend_description(const cbg_backend* b);                /* Backend.Description */
+int cbg_backend_num_devices(const cbg_backend* b);                        /* Backend.NumDevices  */
+int cbg_backend_device_description(const cbg_backend* b, int dev, char* buf, size_t n);
+/* Backend.Capabilities (capabilities.go:12-39): op codes are optype.go values, dtypes cb_dtype. */
+int cbg_backend_capabilities(const cbg_backend* b, int32_t* ops, int* n_ops, int32_t* dtypes, int* n_dtypes);
+int cbg_backend_finalize(cbg_backend* b);                                 /* Backend.Finalize    */
+int cbg_backend_is_finalized(const cbg_backend* b);
+int cbg_backend_free(cbg_backend* b);                                     /* drops the handle itself */
+
+/* ---- DataInterface / Buffer (buffer.go:12-61).  BufferFromFlatData copies host data. */
+int cbg_buffer_from_flat(cbg_backend* b, int dev, const void* host_flat, int32_t dtype, int rank,
+                         const int64_t* dims, cbg_buffer** buffer);
+int cbg_buffer_shape(const cbg_buffer* buf, int32_t* dtype, int* rank, int64_t* dims /* up to 8 */);
+int cbg_buffer_device_num(const cbg_buffer* buf, int* dev);
+int cbg_buffer_to_flat(const cbg_buffer* buf, void* host_flat, size_t n_bytes);   /* Buffer.ToFlatData */
+int cbg_buffer_copy_to_device(const cbg_buffer* buf, int dev, cbg_buffer** out);  /* Buffer.CopyToDevice */
+int cbg_buffer_device_ptr(const cbg_buffer* buf, void** dptr);            /* extension: raw device pointer */
+int cbg_buffer_finalize(cbg_buffer* buf);                                  /* Buffer.Finalize; frees the handle */
+
+/* ---- Builder */
+int cbg_builder_new(cbg_backend* b, const char* name, cbg_builder** builder);   /* Backend.Builder */
+int cbg_builder_main(cbg_builder* bld, cbg_function** fn);                       /* Builder.Main    */
+int cbg_builder_distributed_spmd(cbg_builder* bld, int num_devices);             /* Builder.DistributedSPMD */
+int cbg_builder_device_assignment(cbg_builder* bld, const int* devices, int n);  /* Builder.DeviceAssignment */
+int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec);                      /* Builder.Compile */
+int cbg_builder_free(cbg_builder* bld);   /* values and functions of the builder die with it */
+
+/* ---- Function: graph building */
+int cbg_fn_parameter(cbg_function* f, const char* name, int32_t dtype, int rank, const int64_t* dims, cbg_value** v);
+int cbg_fn_constant(cbg_function* f, const void* host_flat, int32_t dtype, int rank, const int64_t* dims, cbg_value** v);
+int cbg_fn_shape(const cbg_value* v, int32_t* dtype, int* rank, int64_t* dims /* up to 8 */);   /* Function.Shape */
+int cbg_fn_return(cbg_function* f, cbg_value* const* outputs, int n);
+
+/* StandardOps.DotGeneral (standard_ops.go:338-363); acc/out dtype 0 = unset (DotGeneralConfig, :91-111). */
+int cbg_fn_dot_general(cbg_function* f, cbg_value* lhs, const int* lhs_contract, int n_contract,
+                       const int* lhs_batch, int n_batch, cbg_value* rhs, const int* rhs_contract,
+                       const int* rhs_batch, int32_t acc_dtype, int32_t out_dtype, cbg_value** v);
+int cbg_fn_reshape(cbg_function* f, cbg_value* x, int rank, const int64_t* dims, cbg_value** v);
+int cbg_fn_slice(cbg_function* f, cbg_value* x, const int64_t* starts, const int64_t* limits,
+                 const int64_t* strides, cbg_value** v);
+int cbg_fn_iota(cbg_function* f, int32_t dtype, int rank, const int64_t* dims, int axis, cbg_value** v);
+int cbg_fn_convert_dtype(cbg_function* f, cbg_value* x, int32_t dtype, cbg_value** v);
+int cbg_fn_transpose(cbg_function* f, cbg_value* x, const int* permutation, cbg_value** v);
+
+/* FusedOps.FusedQuantizedDense (fused_ops.go:413-435) with compute.Quantization (:204-234).
+ * scheme: 0 Linear, 1 NF4, 2 GGML (only Linear is built).  block_axis 1 is the reference
+ * layout scales [K, ceil(N/block_size)]; block_axis 0 is this backend's extension, scales
+ * [ceil(K/block_size), N] (block_size = K gives one scale per output channel). */
+int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias /* or NULL */,
+                                 int scheme, cbg_value* scale, cbg_value* zero_point /* or NULL */,
+                                 int block_axis, int64_t block_size, int activation, cbg_value** v);
+
+/* FusedOps.FusedScaledDotProductAttention (fused_ops.go:349-378) with
+ * ScaledDotProductAttentionConfig (:245-277); NULL values = unset. */
+typedef struct {
+  int quantized_matmuls;          /* optimisation hint; ignored (computed in float) */
+  cbg_value* query_seq_len;
+  cbg_value* key_value_seq_len;
+  cbg_value* bias;
+  double scale;                   /* 0 = 1/sqrt(head_dim) */
+  int causal;
+  cbg_value* mask;
+} cbg_sdpa_options;
+int cbg_fn_fused_sdpa(cbg_function* f, cbg_value* query, cbg_value* key, cbg_value* value, int axes_layout,
+                      const cbg_sdpa_options* options /* or NULL */, cbg_value** output);
+
+/* Any other op of the interface, by OpType name (e.g. "Neg", "FusedSoftmax", "AllReduce"):
+ * returns CB_ERR_NOT_IMPLEMENTED with the reference's wording. */
+int cbg_fn_not_implemented(cbg_function* f, const char* op_name);
+
+/* ---- Executable.  inputs: one buffer per parameter (device-major under SPMD,
+ * executable.go:33-35); donate may be NULL.  outputs must hold cbg_exec_num_outputs handles. */
+int cbg_exec_num_inputs(const cbg_exec* e);
+int cbg_exec_num_outputs(const cbg_exec* e);
+int cbg_exec_input_info(const cbg_exec* e, int i, char* name, size_t name_len, int32_t* dtype, int* rank, int64_t* dims);
+int cbg_exec_output_info(const cbg_exec* e, int i, int32_t* dtype, int* rank, int64_t* dims);
+int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n);      /* launch plan, one kernel per line */
+int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const uint8_t* donate,
+                     int default_device, cbg_buffer** outputs, int n_outputs);
+int cbg_exec_finalize(cbg_exec* e);                                        /* Executable.Finalize; frees the handle */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -11,10 +11,10 @@ from compute_b200 import _lib, device as dv
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def header_symbols():
-    text = open(os.path.join(ROOT, "include", "cudabackend.h")).read()
+def header_symbols(name="cudabackend.h", prefix="cb_"):
+    text = open(os.path.join(ROOT, "include", name)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(cb_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(" + prefix + r"[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
@@ -25,6 +25,12 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), f"{n} declared in include/cudabackend.h but not exported"
         assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
     assert set(_lib.SIGNATURES) <= set(names)
+    from compute_b200 import backend as be
+    gnames = header_symbols("cudabackend_graph.h", "cbg_")
+    assert len(gnames) >= 40
+    for n in gnames:
+        assert hasattr(lib, n), f"{n} declared in include/cudabackend_graph.h but not exported"
+        assert n in be._GRAPH_SIGNATURES, f"{n} has no ctypes signature"
 
 
 def test_plans_select_kernels_by_shape_and_dtype():

@@ -1,0 +1,272 @@
+"""The reference's compliance cases for the accelerated path, replayed through the host-side
+mirror of its Backend / Builder / Function / Executable / Buffer interface
+(support/backendtest/dotgeneral.go, exec.go, fusedops.go of gomlx/compute)."""
+import numpy as np
+import pytest
+
+from compute_b200 import BackendError, ErrNotImplemented, backend as be, device as dv
+from oracle import oracle as orc
+from tests.helpers import ACT, DT, as_f64, load_golden, max_abs_normalised, qdense_inputs, tensor
+from tests.test_oracle import check_transposed_large, transposed_large_inputs
+
+pytestmark = pytest.mark.gpu
+DOT = load_golden("backendtest_dotgeneral.json")["cases"]
+SDPA = load_golden("backendtest_sdpa.json")
+
+
+@pytest.fixture(scope="module", params=["", "fallback_only"])
+def backend(request):
+    b = be.New(request.param)
+    yield b
+    b.Finalize()
+
+
+def test_backend_identity(backend):
+    assert backend.Name() == "cuda" and backend.NumDevices() >= 1
+    assert "B200" in backend.Description() or "cuda:0" in backend.Description()
+    caps = backend.Capabilities()
+    for op in (be.OP_PARAMETER, be.OP_CONSTANT, be.OP_DOT_GENERAL, be.OP_FUSED_QUANTIZED_DENSE, be.OP_FUSED_SDPA):
+        assert caps.Operations.get(op)
+    assert caps.DTypes.get(dv.BF16) and caps.DTypes.get(dv.F64) and not caps.Functions
+    assert not backend.HasSharedBuffers()
+
+
+# ---------------------------------------------------------------- DotGeneral (dotgeneral.go)
+@pytest.mark.parametrize("case", DOT, ids=[c["name"] for c in DOT])
+def test_dot_general_known_answers(backend, case):
+    code = DT[case["dtype"]]
+    cfg = be.DotGeneralConfig(DT[case["acc"]] if "acc" in case else 0, DT[case["out"]] if "out" in case else 0)
+    ins = [(tensor(case["lhs"], case["dtype"]), code), (tensor(case["rhs"], case["dtype"]), code)]
+    (got,), (shape,) = be.exec_graph(backend, ins, lambda f, p: f.DotGeneral(
+        p[0], case["lhs_contract"], case["lhs_batch"], p[1], case["rhs_contract"], case["rhs_batch"], cfg))
+    assert list(shape.dimensions) == case["want"]["shape"]
+    assert shape.dtype == (cfg.OutputDType or code)
+    g = as_f64(got, shape.dtype).ravel()
+    w = np.array(case["want"]["data"], np.float64)
+    if case["cmp"] == "equal":
+        assert np.array_equal(g, w)
+    else:
+        assert np.max(np.abs(g - w)) <= case["tol"]
+
+
+def test_dot_general_shape_inference(backend):
+    # dotgeneral.go:25-58: Function.Shape before compiling
+    f = backend.Builder("DotGeneral Test").Main()
+    lhs = f.Parameter("lhs", be.make_shape(dv.F32, 2, 3, 4, 5))
+    rhs = f.Parameter("rhs", be.make_shape(dv.F32, 5, 1, 2, 3))
+    out = f.DotGeneral(lhs, [1], [3, 0], rhs, [3], [0, 2])
+    assert f.Shape(out) == be.make_shape(dv.F32, 5, 2, 4, 1)
+
+
+def test_dot_general_f64_very_large_with_constants_and_slice(backend):
+    # dotgeneral.go:132-159
+    def build(f, _):
+        lhs = f.Constant((np.arange(16 * 13 * 384, dtype=np.float64) + 1.0) * 1e-5, 16, 13, 384)
+        rhs = f.Constant(np.ones(384 * 1536, np.float64), 384, 1536)
+        out = f.DotGeneral(lhs, [2], None, rhs, [0], None)
+        return f.Slice(out, [0, 0, 0], [1, 1, 1], [1, 1, 1])
+    (got,), (shape,) = be.exec_graph(backend, [], build)
+    assert shape == be.make_shape(dv.F64, 1, 1, 1)
+    assert abs(got[0, 0, 0] - 0.7392) < 1e-4
+
+
+def test_dot_general_dtype_sweep(backend):
+    # dotgeneral.go:444-497: iota(16) . iota(16); unsupported combinations must say so
+    floats = [dv.F16, dv.F32, dv.F64, dv.BF16]
+    for in_dt in floats:
+        for acc in floats + [0]:
+            for out in floats + [0]:
+                def build(f, _):
+                    a = f.Iota(be.make_shape(in_dt, 16), 0)
+                    b = f.Iota(be.make_shape(in_dt, 16), 0)
+                    return f.DotGeneral(a, [0], None, b, [0], None, be.DotGeneralConfig(acc, out))
+                try:
+                    (got,), (shape,) = be.exec_graph(backend, [], build)
+                except ErrNotImplemented:
+                    continue
+                assert shape.dtype == (out or in_dt)
+                assert float(as_f64(got, shape.dtype).ravel()[0]) == 1240.0
+
+
+def test_dot_general_transposed_large(backend):
+    # dotgeneral.go:499-599
+    lhs, rhs, want = transposed_large_inputs()
+    def build(f, p):
+        l = f.Reshape(p[0], 4, 32, 8, 2, 256)
+        r = f.Reshape(p[1], 4, 32, 8, 256)
+        return f.Reshape(f.DotGeneral(l, [4], [0, 2], r, [3], [0, 2]), 65536)
+    (got,), _ = be.exec_graph(backend, [(lhs.ravel(), dv.F32), (rhs.ravel(), dv.F32)], build)
+    check_transposed_large(got.reshape(want.shape), want)
+
+
+def test_dot_general_validation(backend):
+    f = backend.Builder("bad").Main()
+    a = f.Parameter("a", be.make_shape(dv.F32, 2, 3))
+    b = f.Parameter("b", be.make_shape(dv.F32, 4, 5))
+    c = f.Parameter("c", be.make_shape(dv.F64, 3, 5))
+    with pytest.raises(BackendError):   # contracting dimensions do not match
+        f.DotGeneral(a, [1], [], b, [0], [])
+    with pytest.raises(BackendError):   # same dtype required
+        f.DotGeneral(a, [1], [], c, [0], [])
+    with pytest.raises(BackendError):   # axis out of bounds
+        f.DotGeneral(a, [2], [], b, [0], [])
+    with pytest.raises(BackendError):   # axis used twice
+        f.DotGeneral(a, [1], [1], b, [0], [0])
+    with pytest.raises(ErrNotImplemented):
+        f.Neg(a)
+    with pytest.raises(ErrNotImplemented):
+        f.AllReduce([a], 0, [[0]])
+
+
+# ---------------------------------------------------------------- Exec protocol (exec.go)
+def test_exec_protocol(backend):
+    builder = backend.Builder("passthrough")
+    f = builder.Main()
+    x = f.Parameter("x", be.make_shape(dv.F32, 2, 2))
+    y = f.Parameter("y", be.make_shape(dv.I32, 3))
+    f.Return([x, y, f.Reshape(x, 4)])
+    exe = builder.Compile()
+    names, shapes = exe.Inputs()
+    assert names == ["x", "y"] and shapes[0] == be.make_shape(dv.F32, 2, 2)
+    assert exe.Outputs()[2] == be.make_shape(dv.F32, 4)
+    bx = backend.BufferFromFlatData(0, np.float32([[1, 2], [3, 4]]), be.make_shape(dv.F32, 2, 2))
+    by = backend.BufferFromFlatData(0, np.int32([7, 8, 9]), be.make_shape(dv.I32, 3))
+    outs = exe.Execute([bx, by], None, 0)
+    assert np.array_equal(outs[0].ToNumpy(), [[1, 2], [3, 4]]) and np.array_equal(outs[1].ToNumpy(), [7, 8, 9])
+    assert np.array_equal(outs[2].ToNumpy(), [1, 2, 3, 4])
+    assert outs[0].DevicePtr() != bx.DevicePtr()          # outputs are new buffers
+    # exec.go:72-111: wrong number of inputs, wrong shape, wrong dtype
+    with pytest.raises(BackendError):
+        exe.Execute([bx], None, 0)
+    wrong_shape = backend.BufferFromFlatData(0, np.zeros(3, np.float32), be.make_shape(dv.F32, 3))
+    with pytest.raises(BackendError):
+        exe.Execute([wrong_shape, by], None, 0)
+    wrong_dtype = backend.BufferFromFlatData(0, np.zeros((2, 2), np.int32), be.make_shape(dv.I32, 2, 2))
+    with pytest.raises(BackendError):
+        exe.Execute([wrong_dtype, by], None, 0)
+    # donation: the donated buffer becomes invalid and a later Finalize must not fail (exec.go:143-147)
+    outs2 = exe.Execute([bx, by], [True, False], 0)
+    assert np.array_equal(outs2[0].ToNumpy(), [[1, 2], [3, 4]])
+    with pytest.raises(BackendError):
+        bx.ToNumpy()
+    bx.Finalize()
+    # exact-size ToFlatData
+    with pytest.raises(BackendError):
+        outs[1].ToFlatData(np.zeros(2, np.int32))
+    for b in outs + outs2 + [by, wrong_shape, wrong_dtype]:
+        b.Finalize()
+    exe.Finalize()
+    with pytest.raises(BackendError):   # a compiled builder cannot be reused
+        builder.Compile()
+
+
+# ---------------------------------------------------------------- FusedQuantizedDense
+@pytest.mark.parametrize("layout", ["ref", "channel", "kgroup"])
+def test_fused_quantized_dense_through_api(backend, layout):
+    M, K, N, G = 4, 256, 320, 64
+    block = {"ref": 16, "channel": K, "kgroup": G}[layout]
+    x, w, s, b = qdense_inputs(5, M, K, N, scale_layout=layout if layout != "channel" else "channel", group=G, block_size=block)
+    s_api = s.reshape(1, N) if layout == "channel" else s
+    def build(f, p):
+        q = be.Quantization(be.QUANT_LINEAR, p[2], None, 1 if layout == "ref" else 0, block)
+        return f.FusedQuantizedDense(p[0], p[1], p[3], q, dv.ACT_SILU)
+    (got,), (shape,) = be.exec_graph(backend, [(x.reshape(2, 2, K), dv.F32), (w, dv.I8), (s_api, dv.F32), (b, dv.F32)], build)
+    assert shape == be.make_shape(dv.F32, 2, 2, N)
+    se = s if layout == "ref" else orc.expand_scales(s, layout, K, N, G)
+    want = orc.qdense_linear(x, w, se, None, b, block if layout == "ref" else 1, orc.ACT_SILU)
+    assert max_abs_normalised(got.reshape(M, N), want) < 1e-4
+
+
+def test_fused_quantized_dense_validation(backend):
+    f = backend.Builder("qd").Main()
+    x = f.Parameter("x", be.make_shape(dv.F32, 2, 32))
+    x16 = f.Parameter("x16", be.make_shape(dv.F16, 2, 32))
+    w = f.Parameter("w", be.make_shape(dv.I8, 32, 48))
+    w_bad = f.Parameter("wb", be.make_shape(dv.I8, 16, 48))
+    s = f.Parameter("s", be.make_shape(dv.F32, 32, 3))
+    q = lambda **kw: be.Quantization(**{**dict(Scheme=be.QUANT_LINEAR, Scale=s, BlockAxis=1, BlockSize=16), **kw})
+    assert f.Shape(f.FusedQuantizedDense(x, w, None, q())) == be.make_shape(dv.F32, 2, 48)
+    with pytest.raises(BackendError) as e:     # quantizeddense.go:93: x must be float32
+        f.FusedQuantizedDense(x16, w, None, q())
+    assert not isinstance(e.value, ErrNotImplemented)
+    with pytest.raises(BackendError):          # :104 weights must be [K, N]
+        f.FusedQuantizedDense(x, w_bad, None, q())
+    with pytest.raises(BackendError):          # :111 scales must be [K, numBlocks]
+        f.FusedQuantizedDense(x, w, None, q(BlockSize=8))
+    with pytest.raises(BackendError):          # :123 only Axis=1 (and this backend's Axis=0)
+        f.FusedQuantizedDense(x, w, None, q(BlockAxis=2))
+    for scheme in (be.QUANT_NF4, be.QUANT_GGML):
+        with pytest.raises(ErrNotImplemented):
+            f.FusedQuantizedDense(x, w, None, q(Scheme=scheme))
+
+
+# ---------------------------------------------------------------- SDPA (fusedops.go, sdpa_direct_test.go)
+@pytest.mark.parametrize("case", SDPA["cases"], ids=[c["name"] for c in SDPA["cases"]])
+def test_sdpa_known_answers_through_api(backend, case):
+    code = DT[case["dtype"]]
+    ins = [(tensor(case[k], case["dtype"]), code) for k in ("q", "k", "v")]
+    names = []
+    if "mask" in case:
+        ins.append((tensor(case["mask"], "bool"), dv.BOOL)); names.append("mask")
+    if "q_len" in case:
+        ins.append((np.array(case["q_len"], np.int32), dv.I32)); names.append("q_len")
+        ins.append((np.array(case["kv_len"], np.int32), dv.I32)); names.append("kv_len")
+    if "bias" in case:
+        ins.append((tensor(case["bias"], case["dtype"]), code)); names.append("bias")
+    def build(f, p):
+        extra = dict(zip(names, p[3:]))
+        cfg = be.ScaledDotProductAttentionConfig(
+            QuantizedMatmuls=case.get("quantized_matmuls", False), QuerySeqLen=extra.get("q_len"),
+            KeyValueSeqLen=extra.get("kv_len"), Bias=extra.get("bias"), Scale=case["scale"], Causal=case["causal"],
+            Mask=extra.get("mask"))
+        out, states = f.FusedScaledDotProductAttention(p[0], p[1], p[2], {"BHSD": 0, "BSHD": 1}[case["layout"]], cfg)
+        assert states == []
+        return out
+    (got,), _ = be.exec_graph(backend, ins, build)
+    want = np.array(case["want"]["data"], np.float64).reshape(case["want"]["shape"])
+    assert np.max(np.abs(as_f64(got, code) - want)) <= case["tol"]
+
+
+@pytest.mark.parametrize("case", SDPA["error_cases"], ids=[c["name"] for c in SDPA["error_cases"]])
+def test_sdpa_rejected_through_api(backend, case):
+    f = backend.Builder("sdpa-bad").Main()
+    q = f.Parameter("q", be.make_shape(dv.F32, 1, 1, 2, 1))
+    opts = be.ScaledDotProductAttentionConfig(Scale=1.0)
+    if "bias" in case:
+        opts.Bias = f.Parameter("bias", be.make_shape(dv.F32, *case["bias"]["shape"]))
+    if "q_len" in case:
+        dt = dv.I64 if case.get("seq_len_dtype") == "i64" else dv.I32
+        opts.QuerySeqLen = f.Parameter("ql", be.make_shape(dt, 1))
+        opts.KeyValueSeqLen = f.Parameter("kl", be.make_shape(dt, 1))
+    if case["error"] == "not_implemented":
+        with pytest.raises(ErrNotImplemented):     # float8 operands cannot even be produced
+            q8 = f.ConvertDType(q, dv.F8E4M3FN)
+            f.FusedScaledDotProductAttention(q8, q8, q8, 0, be.ScaledDotProductAttentionConfig(Scale=1.0, Causal=True))
+    else:
+        with pytest.raises(BackendError) as e:
+            f.FusedScaledDotProductAttention(q, q, q, 0, opts)
+        assert not isinstance(e.value, ErrNotImplemented)
+    with pytest.raises(BackendError):              # QuerySeqLen without KeyValueSeqLen
+        f.FusedScaledDotProductAttention(q, q, q, 0, be.ScaledDotProductAttentionConfig(QuerySeqLen=q))
+
+
+def test_decoder_style_graph(backend):
+    """Several ops in one Executable: quantized dense -> reshape to heads -> SDPA -> DotGeneral."""
+    rng = np.random.default_rng(4)
+    B, S, H, D, E = 2, 8, 4, 16, 64
+    x = rng.standard_normal((B * S, E), dtype=np.float32)
+    w = rng.integers(-127, 128, size=(E, 3 * H * D), dtype=np.int8)
+    sc = rng.uniform(0.001, 0.02, size=(1, 3 * H * D)).astype(np.float32)
+    wo = rng.standard_normal((H * D, E), dtype=np.float32) * 0.1
+    def build(f, p):
+        qkv = f.FusedQuantizedDense(p[0], p[1], None, be.Quantization(be.QUANT_LINEAR, p[2], None, 0, E))
+        qkv = f.Reshape(qkv, B, S, 3, H, D)
+        parts = [f.Reshape(f.Slice(qkv, [0, 0, i, 0, 0], [B, S, i + 1, H, D]), B, S, H, D) for i in range(3)]
+        att, _ = f.FusedScaledDotProductAttention(parts[0], parts[1], parts[2], be.LAYOUT_BSHD,
+                                                  be.ScaledDotProductAttentionConfig(Causal=True))
+        return f.DotGeneral(f.Reshape(att, B * S, H * D), [1], [], p[3], [0], [])
+    (got,), _ = be.exec_graph(backend, [(x, dv.F32), (w, dv.I8), (sc, dv.F32), (wo, dv.F32)], build)
+    qkv = orc.qdense_linear(x, w, orc.expand_scales(sc[0], "channel", E, 3 * H * D), None, None, 1).reshape(B, S, 3, H, D)
+    att = orc.sdpa(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], layout="BSHD", causal=True)
+    want = att.reshape(B * S, H * D).astype(np.float64) @ wo.astype(np.float64)
+    assert max_abs_normalised(got, want) < 1e-4
