@@ -1,15 +1,404 @@
-// Flash-style tensor-core attention (placeholder until the kernel lands).
-#include "common.cuh"
+// FusedScaledDotProductAttention, flash-style on the 5th-generation tensor cores:
+// bf16 / f16, head_dim 128, causal or full, GQA, BHSD and BSHD, no mask / bias / sequence
+// lengths (those go to the generic kernel).  Softmax is online, in f32, over the
+// reference's definition (internal/gobackend/fusedops/sdpa.go:373-519): row max, exp,
+// sum, normalise, P.V — evaluated blockwise, so the [S, Skv] scores never exist in memory.
+//
+// One CTA owns two 128-row query tiles of one (batch, query head) and walks the key/value
+// blocks of 128 rows:
+//   warp 8      TMA producer: Q once, K and V blocks into two-stage rings (128B swizzle)
+//   warp 9      MMA issuer:  S_t = Q_t K^T (tcgen05.mma, smem x smem -> TMEM) and
+//               O_t += P_t V (P_t read from TMEM, V from smem as the MN-major operand)
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: tcgen05.ld of S, scale, causal mask,
+//               running max and sum, exp2, P written back over S as packed 16-bit
+// The two tiles alternate on the tensor core, so one tile's softmax overlaps the other's
+// matrix products.  O stays in TMEM and is rescaled only when a row maximum grows by more
+// than 2^8 (the stale maximum is used consistently for P and the row sum, so the result is
+// exact up to rounding).  Every wait is bounded; TMEM is always released.
+#include "tc_common.cuh"
+
+#include <atomic>
+#include <math.h>
+#include <string.h>
 
 namespace cb {
 
-bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why) {
-  if (why) *why = "not built yet";
-  return false;
+using namespace tc;
+
+constexpr int FA_BM = 128, FA_BN = 128, FA_D = 128;
+constexpr int FA_TILE_BYTES = 128 * FA_D * 2;      // 32 KB: two 64-column halves of 16 KB
+constexpr int FA_HALF_BYTES = 128 * 128;           // 16 KB
+constexpr int FA_THREADS = 320;
+constexpr int FA_SMEM = 1024 + 6 * FA_TILE_BYTES + 256;   // Q0 Q1 K0 K1 V0 V1
+constexpr int FA_TMEM_COLS = 512;                  // S0 S1 O0 O1, 128 columns each
+constexpr float FA_RESCALE_THRESHOLD = 8.0f;       // log2 units
+
+struct FaParams {
+  void* out;
+  unsigned* status;
+  int B, Hq, Hkv, S, Skv;
+  int bshd, causal, ab_format;
+  float scale_log2;        // scale * log2(e)
+  int q_pairs;             // ceil(S / 256)
+};
+
+__device__ __forceinline__ void fa_fail(const FaParams& p, unsigned* s_failed, unsigned code, unsigned detail) {
+  atomicExch(&p.status[0], code);
+  atomicExch(&p.status[1], detail);
+  atomicExch(s_failed, 1u);
 }
-int sdpa_flash_plan(cb_plan* p) { return fail(CB_ERR_NOT_IMPLEMENTED, "flash attention kernel is not built yet"); }
+
+// one [128 rows x 128 columns] tile = two TMA boxes of 64 columns
+__device__ __forceinline__ void fa_load_tile(uint8_t* dst, const CUtensorMap* map, int bshd, int row0, int head, int b, uint64_t* bar) {
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    if (bshd) tma_load_4d(dst + h * FA_HALF_BYTES, map, 64 * h, head, row0, b, bar);
+    else tma_load_4d(dst + h * FA_HALF_BYTES, map, 64 * h, row0, head, b, bar);
+  }
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
+  extern __shared__ uint8_t fa_smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = base;                              // [2 tiles]
+  uint8_t* sK = base + 2 * FA_TILE_BYTES;          // [2 stages]
+  uint8_t* sV = base + 4 * FA_TILE_BYTES;          // [2 stages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * FA_TILE_BYTES);
+  uint64_t* q_full = bars;            // [1]
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2] per tile: scores ready
+  uint64_t* p_full = bars + 11;       // [2] per tile: probabilities written
+  uint64_t* o_done = bars + 13;       // [2] per tile: P.V of a block finished
+  __shared__ uint32_t s_tmem;
+  __shared__ unsigned s_failed;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heavy (late, causal) query tiles first
+  const int pair = p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs);
+  const int h = (int)((blockIdx.x / p.q_pairs) % p.Hq);
+  const int b = (int)(blockIdx.x / ((long long)p.q_pairs * p.Hq));
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = pair * 2 * FA_BM;
+  const int nb_all = (p.Skv + FA_BN - 1) / FA_BN;
+  int nb[2];
+#pragma unroll
+  for (int t = 0; t < 2; t++) {
+    const int qt = q0 + t * FA_BM;
+    int n = nb_all;
+    if (p.causal) n = min(n, (min(qt + FA_BM, p.S) + FA_BN - 1) / FA_BN);   // blocks with kv <= last row of the tile
+    if (qt >= p.S) n = 0;
+    nb[t] = n;
+  }
+  const int nb_max = max(nb[0], nb[1]);
+
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4); mbar_init(&o_done[s], 1);
+    }
+    s_failed = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) tmem_alloc(&s_tmem, FA_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+
+  if (warp == 8) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+      mbar_expect_tx(q_full, 2 * FA_TILE_BYTES);
+      fa_load_tile(sQ, &tm_q, p.bshd, q0, h, b, q_full);
+      fa_load_tile(sQ + FA_TILE_BYTES, &tm_q, p.bshd, q0 + FA_BM, h, b, q_full);
+      for (int j = 0; j < nb_max; j++) {
+        const int s = j & 1;
+        if (j >= 2 && !mbar_wait(&k_empty[s], (uint32_t)((j / 2 - 1) & 1))) { fa_fail(p, &s_failed, 1, (unsigned)j); break; }
+        mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
+        fa_load_tile(sK + s * FA_TILE_BYTES, &tm_k, p.bshd, j * FA_BN, hk, b, &k_full[s]);
+        if (j >= 2 && !mbar_wait(&v_empty[s], (uint32_t)((j / 2 - 1) & 1))) { fa_fail(p, &s_failed, 2, (unsigned)j); break; }
+        mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
+        fa_load_tile(sV + s * FA_TILE_BYTES, &tm_v, p.bshd, j * FA_BN, hk, b, &v_full[s]);
+        if (*(volatile unsigned*)&s_failed) break;
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && nb_max > 0) {
+      const uint32_t idesc_qk = idesc_f16(FA_BM, FA_BN, p.ab_format, 0, 0);   // A, B K-major
+      const uint32_t idesc_pv = idesc_f16(FA_BM, FA_D, p.ab_format, 0, 1);    // B (V) MN-major
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) fa_fail(p, &s_failed, 3, 0);
+      auto issue_qk = [&](int t, int s) {   // S_t = Q_t K_s^T
+        const uint32_t d = tmem_base + (uint32_t)(t * 128);
+#pragma unroll
+        for (int kk = 0; kk < FA_D / 16; kk++) {
+          const uint32_t off = (uint32_t)((kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32);
+          umma_f16(d, smem_desc_sw128(q_addr + t * FA_TILE_BYTES + off, 16, 1024),
+                   smem_desc_sw128(k_addr + s * FA_TILE_BYTES + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int s, bool accumulate) {   // O_t (+)= P_t V_s
+        const uint32_t d = tmem_base + (uint32_t)(256 + t * 128);
+        const uint32_t a = tmem_base + (uint32_t)(t * 128);
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; kk++)
+          umma_f16_ts(d, a + (uint32_t)(kk * 8), smem_desc_sw128(v_addr + s * FA_TILE_BYTES + kk * 16 * 128, FA_HALF_BYTES, 1024),
+                      idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+        umma_commit(&o_done[t]);
+      };
+      if (ok) {
+        // block 0 scores
+        ok = mbar_wait(&k_full[0], 0);
+        if (!ok) fa_fail(p, &s_failed, 4, 0);
+        if (ok) {
+          tc_fence_after();
+          for (int t = 0; t < 2; t++) if (nb[t] > 0) issue_qk(t, 0);
+          umma_commit(&k_empty[0]);
+        }
+      }
+      for (int j = 0; j < nb_max && ok; j++) {
+        const int s = j & 1, sn = (j + 1) & 1;
+        bool k_next_ready = false;
+        for (int t = 0; t < 2 && ok; t++) {
+          if (j < nb[t]) {
+            if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { fa_fail(p, &s_failed, 5, (unsigned)(j * 2 + t)); ok = false; break; }
+            if (t == 0 || j >= nb[0]) {
+              if (!mbar_wait(&v_full[s], (uint32_t)((j / 2) & 1))) { fa_fail(p, &s_failed, 6, (unsigned)j); ok = false; break; }
+            }
+            tc_fence_after();
+            issue_pv(t, s, j > 0);
+          }
+          if (j + 1 < nb[t]) {
+            if (!k_next_ready) {
+              if (!mbar_wait(&k_full[sn], (uint32_t)(((j + 1) / 2) & 1))) { fa_fail(p, &s_failed, 7, (unsigned)j); ok = false; break; }
+              k_next_ready = true;
+              tc_fence_after();
+            }
+            issue_qk(t, sn);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[s]);
+        if (k_next_ready) umma_commit(&k_empty[sn]);
+      }
+    }
+  } else {
+    // ------------------------------ softmax warpgroups ------------------------
+    const int t = warp >> 2;                 // tile of this warpgroup
+    const int wq = warp & 3;                 // TMEM lane quarter of this warp
+    const int row = q0 + t * FA_BM + wq * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
+    const uint32_t s_addr = lane_base + (uint32_t)(t * 128);
+    const uint32_t o_addr = lane_base + (uint32_t)(256 + t * 128);
+    float m_used = -INFINITY, l = 0.0f;
+    bool failed = false;
+    for (int j = 0; j < nb[t]; j++) {
+      if (!mbar_wait(&s_full[t], (uint32_t)(j & 1))) { failed = true; fa_fail(p, &s_failed, 8, (unsigned)(j * 2 + t)); break; }
+      if (*(volatile unsigned*)&s_failed) { failed = true; break; }
+      tc_fence_after();
+      const int kv0 = j * FA_BN;
+      const bool need_mask = (p.causal && kv0 + FA_BN - 1 > row) || (kv0 + FA_BN > p.Skv);
+      const int kv_limit = p.causal ? min(p.Skv, row + 1) : p.Skv;   // first masked kv index
+      // pass 1: block maximum of the scaled scores
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          float x = __uint_as_float(r[i]) * p.scale_log2;
+          if (need_mask && kv0 + c * 32 + i >= kv_limit) x = -INFINITY;
+          m_blk = fmaxf(m_blk, x);
+        }
+      }
+      float m_new = fmaxf(m_used, m_blk);
+      if (m_new == -INFINITY) m_new = 0.0f;          // nothing attendable so far
+      const bool first = (j == 0);
+      const bool grow = !first && (m_new > m_used + FA_RESCALE_THRESHOLD);
+      if (first) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        // rescale the running output and sum to the new maximum (whole warp: TMEM access is collective)
+        const float alpha = exp2f(m_used - m_new);
+        l *= alpha;
+        m_used = m_new;
+#pragma unroll 1
+        for (int c = 0; c < 4; c++) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(o_addr + (uint32_t)(c * 32), r);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: probabilities, row sum, P over S as packed 16-bit pairs
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32], pk[16];
+        tmem_ld32(s_addr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(r[i]) * p.scale_log2 - m_used;
+          float x1 = __uint_as_float(r[i + 1]) * p.scale_log2 - m_used;
+          if (need_mask) {
+            if (kv0 + c * 32 + i >= kv_limit) x0 = -INFINITY;
+            if (kv0 + c * 32 + i + 1 >= kv_limit) x1 = -INFINITY;
+          }
+          const float p0 = exp2f(x0), p1 = exp2f(x1);
+          l += p0 + p1;
+          if (p.ab_format == 1) {
+            pk[i >> 1] = (uint32_t)f32_to_bf16_bits(p0) | ((uint32_t)f32_to_bf16_bits(p1) << 16);
+          } else {
+            __half2 hh = __floats2half2_rn(p0, p1);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+        }
+        tmem_st16(s_addr + (uint32_t)(c * 16), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    // epilogue: O / l
+    if (!failed && nb[t] > 0) {
+      if (!mbar_wait(&o_done[t], (uint32_t)((nb[t] - 1) & 1))) { failed = true; fa_fail(p, &s_failed, 9, (unsigned)t); }
+    }
+    if (!failed && nb[t] > 0 && !*(volatile unsigned*)&s_failed) {
+      tc_fence_after();
+      const float inv = l != 0.0f ? 1.0f / l : 0.0f;
+      OT* out = reinterpret_cast<OT*>(p.out);
+      const int rr = min(row, p.S - 1);
+      OT* orow = p.bshd ? out + (((size_t)b * p.S + rr) * p.Hq + h) * FA_D : out + (((size_t)b * p.Hq + h) * p.S + rr) * FA_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld32(o_addr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        if (row < p.S) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const float a0 = __uint_as_float(r[8 * q + 2 * i]) * inv, a1 = __uint_as_float(r[8 * q + 2 * i + 1]) * inv;
+              if (p.ab_format == 1) w[i] = (uint32_t)f32_to_bf16_bits(a0) | ((uint32_t)f32_to_bf16_bits(a1) << 16);
+              else { __half2 hh = __floats2half2_rn(a0, a1); w[i] = *reinterpret_cast<uint32_t*>(&hh); }
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FA_TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// planning and launch
+// ---------------------------------------------------------------------------
+bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why) {
+  auto no = [&](const char* m) { if (why) *why = m; return false; };
+  if (d.dtype != CB_BF16 && d.dtype != CB_F16) return no("dtype must be bfloat16 or float16");
+  if (d.D != FA_D) return no("head_dim must be 128");
+  if (d.mask_kind != CB_MASK_NONE || d.bias_rank > 0 || d.has_seq_lens) return no("mask, bias and sequence lengths use the generic kernel");
+  if (d.B < 1 || d.S < 1 || d.Skv < 1) return no("empty operand");
+  if (d.S < 128 || d.Skv < 128) return no("sequence too short for the tensor-core tile");
+  if (d.S > (1 << 24) || d.Skv > (1 << 24) || d.B * d.Hq * ((d.S + 255) / 256) > 0x7fffffffLL) return no("dimension too large");
+  return true;
+}
+
+int sdpa_flash_plan(cb_plan* p) {
+  const cb_sdpa_desc& d = p->sdpa;
+  p->blocks = (int)(d.B * d.Hq * ((d.S + 255) / 256));
+  p->threads = FA_THREADS;
+  p->dyn_smem = FA_SMEM;
+  p->counter_bytes = 64;
+  p->workspace_bytes = 64;
+  p->has_status = true;
+  p->name = std::string("sdpa_flash_") + dtype_name(d.dtype) + (d.causal ? "_causal" : "_full") + (d.layout == CB_LAYOUT_BSHD ? "_bshd" : "_bhsd");
+  return CB_OK;
+}
+
+// [B,H,S,D] (BHSD) or [B,S,H,D] (BSHD) as a 4-D tensor map with boxes of 128 rows x 64 columns
+static int encode_qkv(CUtensorMap* m, const void* ptr, int bshd, int64_t B, int64_t H, int64_t S) {
+  encode_tiled_fn enc = tensor_map_encoder();
+  if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(CB_ERR_INVALID_ARG, "flash attention: operands must be 16-byte aligned");
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  dims[0] = FA_D;
+  if (bshd) { dims[1] = (cuuint64_t)H; dims[2] = (cuuint64_t)S; box[1] = 1; box[2] = 128; }
+  else { dims[1] = (cuuint64_t)S; dims[2] = (cuuint64_t)H; box[1] = 128; box[2] = 1; }
+  dims[3] = (cuuint64_t)B;
+  box[0] = 64; box[3] = 1;
+  strides[0] = FA_D * 2;
+  strides[1] = strides[0] * dims[1];
+  strides[2] = strides[1] * dims[2];
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return CB_OK;
+}
+
+template <typename OT>
+static int launch_t(const cb_plan* p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& prm, cudaStream_t s) {
+  static std::atomic<bool> configured[64];
+  if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(sdpa_flash_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
+    if (p->dev < 64) configured[p->dev].store(true, std::memory_order_release);
+  }
+  sdpa_flash_kernel<OT><<<p->blocks, FA_THREADS, FA_SMEM, s>>>(tq, tk, tv, prm);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
 int sdpa_flash_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  return fail(CB_ERR_NOT_IMPLEMENTED, "flash attention kernel is not built yet");
+  const cb_sdpa_desc& d = p->sdpa;
+  const int bshd = d.layout == CB_LAYOUT_BSHD ? 1 : 0;
+  CUtensorMap tq, tk, tv;
+  CB_TRY(encode_qkv(&tq, in[0], bshd, d.B, d.Hq, d.S));
+  CB_TRY(encode_qkv(&tk, in[1], bshd, d.B, d.Hkv, d.Skv));
+  CB_TRY(encode_qkv(&tv, in[2], bshd, d.B, d.Hkv, d.Skv));
+  if (reinterpret_cast<uintptr_t>(out[0]) & 15) return fail(CB_ERR_INVALID_ARG, "flash attention: output must be 16-byte aligned");
+  FaParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.out = out[0];
+  prm.status = (unsigned*)ws;
+  prm.B = (int)d.B; prm.Hq = (int)d.Hq; prm.Hkv = (int)d.Hkv; prm.S = (int)d.S; prm.Skv = (int)d.Skv;
+  prm.bshd = bshd;
+  prm.causal = d.causal;
+  prm.ab_format = d.dtype == CB_BF16 ? 1 : 0;
+  const double scale = d.scale != 0.0 ? d.scale : 1.0 / sqrt((double)d.D);
+  prm.scale_log2 = (float)(scale * 1.4426950408889634);
+  prm.q_pairs = (int)((d.S + 255) / 256);
+  return d.dtype == CB_BF16 ? launch_t<__nv_bfloat16>(p, tq, tk, tv, prm, s) : launch_t<__half>(p, tq, tk, tv, prm, s);
 }
 
 }  // namespace cb
