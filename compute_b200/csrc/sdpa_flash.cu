@@ -48,6 +48,21 @@ __device__ __forceinline__ void fa_fail(const FaParams& p, unsigned* s_failed, u
   atomicExch(s_failed, 1u);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// two f32 -> packed bf16x2 (format 1) or f16x2 (format 0), round to nearest even
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi, int ab_format) {
+  if (ab_format == 1) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // one [128 rows x 128 columns] tile = two TMA boxes of 64 columns
 __device__ __forceinline__ void fa_load_tile(uint8_t* dst, const CUtensorMap* map, int bshd, int row0, int head, int b, uint64_t* bar) {
 #pragma unroll
@@ -206,6 +221,9 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t o_addr = lane_base + (uint32_t)(256 + t * 128);
     float m_used = -INFINITY, l = 0.0f;
     bool failed = false;
+    const bool pos_scale = p.scale_log2 >= 0.0f;
+    // a masked score: the value that scales to -inf-like (never the row extreme, exp2 gives 0)
+    const uint32_t neg_biggest = __float_as_uint(pos_scale ? -INFINITY : INFINITY);
     for (int j = 0; j < nb[t]; j++) {
       if (!mbar_wait(&s_full[t], (uint32_t)(j & 1))) { failed = true; fa_fail(p, &s_failed, 8, (unsigned)(j * 2 + t)); break; }
       if (*(volatile unsigned*)&s_failed) { failed = true; break; }
@@ -213,20 +231,26 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int kv0 = j * FA_BN;
       const bool need_mask = (p.causal && kv0 + FA_BN - 1 > row) || (kv0 + FA_BN > p.Skv);
       const int kv_limit = p.causal ? min(p.Skv, row + 1) : p.Skv;   // first masked kv index
-      // pass 1: block maximum of the scaled scores
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; c++) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
+      // the whole score row of this block lives in registers: one TMEM read, one pass for the
+      // maximum, one for the probabilities
+      uint32_t sr[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          float x = __uint_as_float(r[i]) * p.scale_log2;
-          if (need_mask && kv0 + c * 32 + i >= kv_limit) x = -INFINITY;
-          m_blk = fmaxf(m_blk, x);
-        }
+      for (int c = 0; c < 4; c++) tmem_ld32(s_addr + (uint32_t)(c * 32), sr[c]);
+      tmem_ld_wait();
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (kv0 + c * 32 + i >= kv_limit) sr[c][i] = neg_biggest;   // -inf after scaling either way
       }
+      // max of scale*s = scale*max(s) for a positive scale, scale*min(s) for a negative one
+      float ext = __uint_as_float(sr[0][0]);
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int i = 0; i < 32; i++) ext = pos_scale ? fmaxf(ext, __uint_as_float(sr[c][i])) : fminf(ext, __uint_as_float(sr[c][i]));
+      const float m_blk = ext * p.scale_log2;
       float m_new = fmaxf(m_used, m_blk);
       if (m_new == -INFINITY) m_new = 0.0f;          // nothing attendable so far
       const bool first = (j == 0);
@@ -235,7 +259,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         // rescale the running output and sum to the new maximum (whole warp: TMEM access is collective)
-        const float alpha = exp2f(m_used - m_new);
+        const float alpha = fast_exp2(m_used - m_new);
         l *= alpha;
         m_used = m_new;
 #pragma unroll 1
@@ -249,31 +273,22 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         tmem_st_wait();
       }
-      // pass 2: probabilities, row sum, P over S as packed 16-bit pairs
-#pragma unroll 1
+      // probabilities, row sum, P over S as packed 16-bit pairs
+      float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
       for (int c = 0; c < 4; c++) {
-        uint32_t r[32], pk[16];
-        tmem_ld32(s_addr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
+        uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(r[i]) * p.scale_log2 - m_used;
-          float x1 = __uint_as_float(r[i + 1]) * p.scale_log2 - m_used;
-          if (need_mask) {
-            if (kv0 + c * 32 + i >= kv_limit) x0 = -INFINITY;
-            if (kv0 + c * 32 + i + 1 >= kv_limit) x1 = -INFINITY;
-          }
-          const float p0 = exp2f(x0), p1 = exp2f(x1);
-          l += p0 + p1;
-          if (p.ab_format == 1) {
-            pk[i >> 1] = (uint32_t)f32_to_bf16_bits(p0) | ((uint32_t)f32_to_bf16_bits(p1) << 16);
-          } else {
-            __half2 hh = __floats2half2_rn(p0, p1);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-          }
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_used));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_used));
+          l0 += p0;
+          l1 += p1;
+          pk[i >> 1] = pack16x2(p0, p1, p.ab_format);
         }
         tmem_st16(s_addr + (uint32_t)(c * 16), pk);
       }
+      l += l0 + l1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -301,8 +316,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 4; i++) {
               const float a0 = __uint_as_float(r[8 * q + 2 * i]) * inv, a1 = __uint_as_float(r[8 * q + 2 * i + 1]) * inv;
-              if (p.ab_format == 1) w[i] = (uint32_t)f32_to_bf16_bits(a0) | ((uint32_t)f32_to_bf16_bits(a1) << 16);
-              else { __half2 hh = __floats2half2_rn(a0, a1); w[i] = *reinterpret_cast<uint32_t*>(&hh); }
+              w[i] = pack16x2(a0, a1, p.ab_format);
             }
             *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
