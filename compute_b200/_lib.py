@@ -70,6 +70,8 @@ SIGNATURES = {
     "cb_event_elapsed_ms": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_float)], C.c_int),
     "cb_event_destroy": ([C.c_int, C.c_void_p], C.c_int),
     "cb_plan_qdense": ([C.c_int, C.POINTER(QDenseDesc), C.POINTER(C.c_void_p)], C.c_int),
+    "cb_qdense_decode_static": ([C.c_int, C.POINTER(QDenseDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_dot": ([C.c_int, C.POINTER(DotDesc), C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_sdpa": ([C.c_int, C.POINTER(SdpaDesc), C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_copy": ([C.c_int, C.c_int32, C.c_int64, C.POINTER(C.c_void_p)], C.c_int),

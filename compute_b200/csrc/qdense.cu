@@ -674,4 +674,104 @@ int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   return wu ? launch_generic<float, uint8_t>(p, in, out, s) : launch_generic<float, int8_t>(p, in, out, s);
 }
 
+
+// ---------------------------------------------------------------------------
+// Decode kernel without any allocation: the scratch lives in the library image.
+// ---------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory at the moment they need a
+// projection: an inference server that has handed every byte of HBM to its own arena, a
+// plugin running inside another framework's stream callback or graph-replay window, a
+// process whose allocator is locked down after start-up.  For them the stream-K scratch
+// (arrival counters + parked partial tiles) is a fixed array in device memory that every
+// GPU loading the library holds until the process exits.
+constexpr size_t QD_STATIC_SCRATCH_BYTES = 2u << 20;   // 2 MiB per device
+static __device__ __align__(256) unsigned char g_qd_static_scratch[QD_STATIC_SCRATCH_BYTES];
+
+// In host code `g_qd_static_scratch` is only a handle for the runtime, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, per device.
+static std::mutex g_qd_static_mu;
+static void* g_qd_static_ptr[64];
+
+static int qd_static_scratch(int dev, void** ptr) {
+  if (dev < 0 || dev >= 64) return fail(CB_ERR_INVALID_ARG, "device %d out of range for the static scratch", dev);
+  std::lock_guard<std::mutex> l(g_qd_static_mu);
+  if (!g_qd_static_ptr[dev]) {
+    void* p = nullptr;
+    CB_CUDA(cudaGetSymbolAddress(&p, g_qd_static_scratch));   // `dev` is current: set_device ran just before
+    g_qd_static_ptr[dev] = p;
+  }
+  *ptr = g_qd_static_ptr[dev];
+  return CB_OK;
+}
+
+template <typename XT, int MT, bool WU>
+static int launch_decode_static_t(int dev, int blocks, int dyn_smem, const QdParams& prm, cudaStream_t s) {
+  static std::atomic<bool> configured[64];
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(qdense_decode_kernel<XT, MT, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem));
+    configured[dev].store(true, std::memory_order_release);
+  }
+  qdense_decode_kernel<XT, MT, WU><<<blocks, QD_THREADS, dyn_smem, s>>>(prm);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
 }  // namespace cb
+
+extern "C" int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, const void* x, const void* weights,
+                                       const void* scales, const void* bias, void* out, cb_stream stream) {
+  using namespace cb;
+  clear_error();
+  if (!desc || !x || !weights || !scales || !out) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: NULL argument");
+  const cb_qdense_desc& d = *desc;
+  std::string why;
+  if (d.x_dtype != CB_F32 && d.x_dtype != CB_BF16) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: x must be float32 or bfloat16");
+  if (d.w_dtype != CB_I8 && d.w_dtype != CB_U8) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: weights must be int8 or uint8");
+  if (!decode_eligible(d, &why)) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: %s", why.c_str());
+  if (d.has_bias && !bias) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: bias is NULL");
+  CB_TRY(set_device(dev));
+  const int mt = d.M <= 8 ? 1 : 2;
+  const long long n_tiles = (d.N + QD_TILE_N - 1) / QD_TILE_N;
+  const long long cpt = (d.K + QD_CHUNK_K - 1) / QD_CHUNK_K;
+  int n_sm = sm_count(dev);
+  if (n_sm <= 0) n_sm = 148;
+  const int blocks = (int)std::min<long long>(n_sm, n_tiles * cpt);
+  const size_t counter_bytes = (QD_WS_HEADER + (size_t)n_tiles * 4 + 255) & ~(size_t)255;
+  const size_t need = counter_bytes + (size_t)blocks * 2 * mt * 8 * QD_TILE_N * 4;
+  if (need > QD_STATIC_SCRATCH_BYTES)
+    return fail(CB_ERR_INVALID_ARG,
+                "cb_qdense_decode_static: this shape needs %zu bytes of scratch, the built-in scratch holds %zu "
+                "(use cb_plan_qdense with a caller-owned workspace)", need, QD_STATIC_SCRATCH_BYTES);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(weights) & 15) || (reinterpret_cast<uintptr_t>(scales) & 15))
+    return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: x, weights and scales must be 16-byte aligned");
+  void* scratch = nullptr;
+  CB_TRY(qd_static_scratch(dev, &scratch));
+  cudaStream_t s = (cudaStream_t)stream;
+  // The array keeps whatever the previous call left: the arrival counters must start at zero.
+  CB_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, s));
+  QdParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.x = x;
+  prm.w = (const uint8_t*)weights;
+  prm.scales = (const float*)scales;
+  prm.bias = d.has_bias ? (const float*)bias : nullptr;
+  prm.out = out;
+  uint8_t* w8 = (uint8_t*)scratch;
+  prm.status = (unsigned*)w8;
+  prm.counters = (unsigned*)(w8 + QD_WS_HEADER);
+  prm.partials = (float*)(w8 + counter_bytes);
+  prm.M = (int)d.M; prm.K = (int)d.K; prm.N = (int)d.N;
+  prm.n_tiles = (int)n_tiles;
+  prm.cpt = (int)cpt;
+  decode_schedule(prm.n_tiles, blocks, &prm.sk_tiles, &prm.dp_per_cta);
+  prm.sk_total = (long long)prm.sk_tiles * prm.cpt;
+  prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
+  prm.activation = d.activation;
+  const int smem = (int)decode_smem(mt);
+  const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
+#define QD_DISPATCH(XT)                                                                                     \
+  (mt == 1 ? (wu ? launch_decode_static_t<XT, 1, true>(dev, blocks, smem, prm, s) : launch_decode_static_t<XT, 1, false>(dev, blocks, smem, prm, s)) \
+           : (wu ? launch_decode_static_t<XT, 2, true>(dev, blocks, smem, prm, s) : launch_decode_static_t<XT, 2, false>(dev, blocks, smem, prm, s)))
+  return bf ? QD_DISPATCH(__nv_bfloat16) : QD_DISPATCH(float);
+#undef QD_DISPATCH
+}

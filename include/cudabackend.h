@@ -90,7 +90,7 @@ typedef enum {
 typedef enum {
   CB_QDENSE_AUTO = 0,
   CB_QDENSE_GENERIC = 1,    /* CUDA-core kernel in the reference's (m,k,n) summation order       */
-  CB_QDENSE_DECODE_MMA = 2, /* M <= 16 stream-K kernel: TMA-staged int8 tiles, bf16 mma, fp32 acc */
+  CB_QDENSE_DECODE_MMA = 2, /* M <= 16 stream-K kernel: cp.async-staged int8 tiles, f16 mma, f32 acc */
   CB_QDENSE_PREFILL = 3     /* large-M tensor-core kernel                                        */
 } cb_qdense_variant;
 
@@ -107,6 +107,19 @@ typedef struct {
 } cb_qdense_desc;
 
 int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);
+
+/* No counterpart in the reference: a decode-shaped (M <= 16, compact scales) quantized dense
+ * for callers that cannot allocate device memory when they launch — a server that gave all of
+ * HBM to its own arena, a plugin inside another framework's callback, a process whose allocator
+ * is frozen after start-up.  It runs the same kernel as the CB_QDENSE_DECODE_MMA plan, with the
+ * stream-K scratch in a 2 MiB array that is part of the library image (every GPU that loads the
+ * library holds it until exit).  It allocates nothing; shapes whose scratch would exceed the
+ * array are rejected with CB_ERR_INVALID_ARG — use a plan with a caller-owned workspace then.
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture.  All calls share the one array per device: calls that overlap on the GPU
+ * (different streams, threads or processes sharing a context) race and give wrong results. */
+int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, const void* x, const void* weights,
+                            const void* scales, const void* bias /* or NULL */, void* out, cb_stream stream);
 
 /* ---- DotGeneral in normalised form (StandardOps.DotGeneral standard_ops.go:338-363;
  *      normalisation and dtype rules internal/gobackend/dot/dot.go:165-285; kernels dot/matmul/*).
