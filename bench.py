@@ -110,6 +110,54 @@ def make_layer(seed: int, M: int, cols: slice):
     return np.ascontiguousarray(w[:, cols]), np.ascontiguousarray(s[:, cols])
 
 
+def other_kernels(dv, dev, stream):
+    """The tensor-core rows of the path, timed alone (CUDA events, inputs resident): DotGeneral
+    4096^3 bf16 (config 2) and causal SDPA B=8, 32/8 heads, D=128, S=2048 bf16 (config 4)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tpeak = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        tpeak = 1590.0
+    rng = np.random.default_rng(3)
+
+    def rand_bf16(n):
+        a = (rng.standard_normal(n, dtype=np.float32) * 0.05).view(np.uint32) >> 16
+        return dv.DeviceMem.from_numpy(a.astype(np.uint16), dev)
+
+    def time_plan(plan, ins, outs, reps):
+        ws = plan.new_workspace()
+        e0, e1 = dv.Event(dev), dv.Event(dev)
+        for it in range(reps + 3):
+            if it == 3:
+                e0.record(stream)
+            plan.launch(ins, outs, ws.ptr if ws else None, stream)
+        e1.record(stream)
+        stream.sync()
+        plan.check_status(ws.ptr if ws else None)
+        return e0.elapsed_ms(e1) * 1e3 / reps
+
+    res = {}
+    n = 4096
+    a, b, c = rand_bf16(n * n), rand_bf16(n * n), dv.DeviceMem(n * n * 2, dev)
+    plan = dv.Plan.dot(1, n, n, n, dv.BF16, dev=dev)
+    us = time_plan(plan, [a.ptr, b.ptr], [c.ptr], 20)
+    tf = 2.0 * n ** 3 / us / 1e6
+    res["dot_general_4096_bf16"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": tf, "frac_of_measured_bf16_peak": tf / tpeak}
+    for m in (a, b, c):
+        m.free()
+    B, Hq, Hkv, S, D = 8, 32, 8, 2048, 128
+    q, k, v = rand_bf16(B * Hq * S * D), rand_bf16(B * Hkv * S * D), rand_bf16(B * Hkv * S * D)
+    o = dv.DeviceMem(B * Hq * S * D * 2, dev)
+    plan = dv.Plan.sdpa(B, Hq, Hkv, S, S, D, dv.BF16, causal=True, dev=dev)
+    us = time_plan(plan, [q.ptr, k.ptr, v.ptr], [o.ptr], 10)
+    tf = 4.0 * B * Hq * D * (S * (S + 1) / 2) / us / 1e6
+    res["sdpa_causal_b8_h32_8_s2048_d128_bf16"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": tf,
+                                                     "frac_of_measured_bf16_peak": tf / tpeak}
+    for m in (q, k, v, o):
+        m.free()
+    return res
+
+
 def cpu_baseline(M: int, seconds: float = 12.0):
     """The oracle port (the reference's scalar loop nest with its row / N-tile parallel split)
     timed on the host cores over repeated launches of one layer."""
@@ -237,14 +285,14 @@ def main():
         stream_l = stream
 
     def step(copy: bool):
+        if copy:      # this step's activations: one pinned-host -> device copy
+            dv.check(dv._lib.load().cb_h2d(dev, x_dev.ptr, x_host.ptr, LAYERS * x_stride, stream_l.handle))
         for layer in range(LAYERS):
-            xp = x_dev.ptr + layer * x_stride
-            if copy:
-                dv.check(dv._lib.load().cb_h2d(dev, xp, x_host.ptr + layer * x_stride, x_stride, stream_l.handle))
-            plan.launch([xp, w_dev[layer].ptr, s_dev[layer].ptr], [y_dev_ptr + layer * y_stride], wsp, stream_l)
+            plan.launch([x_dev.ptr + layer * x_stride, w_dev[layer].ptr, s_dev[layer].ptr],
+                        [y_dev_ptr + layer * y_stride], wsp, stream_l)
         if gather:
             gather()
-        if copy:
+        if copy:      # this step's results: one device -> pinned-host copy
             dv.check(dv._lib.load().cb_d2h(dev, y_host.ptr, y_dev_ptr, LAYERS * y_stride, stream_l.handle))
 
     def sync():
@@ -348,6 +396,7 @@ def main():
             extra[f"M={m_other}"] = {"us_per_launch": us, "GB/s": b / us / 1e3, "frac_of_measured_hbm": b / us / 1e3 / peak,
                                      "kernel": p2.kernel_name}
         out["other_decode_batches"] = extra
+        out["other_path_kernels"] = other_kernels(dv, dev, stream)
     if g == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(M)
     print(json.dumps(out))

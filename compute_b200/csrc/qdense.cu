@@ -87,10 +87,10 @@ qdense_generic_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const 
 constexpr int QD_TILE_N = 64;                  // columns per tile
 constexpr int QD_CHUNK_K = 64;                 // rows per chunk
 constexpr int QD_PITCH = 80;                   // shared-memory row pitch: 64 data bytes + 16 pad (conflict-free 8-byte reads)
-constexpr int QD_STAGE_BYTES = QD_CHUNK_K * QD_PITCH;
+constexpr int QD_STEP_BYTES = 16 * QD_PITCH;    // copy unit: one k-step (16 rows)
+constexpr int QD_RING_STEPS = 8;               // k-steps in each warp's ring: one in use, seven in flight
 constexpr int QD_WARPS = 16;
 constexpr int QD_THREADS = QD_WARPS * 32;
-constexpr int QD_DEPTH = 2;                    // chunks each warp keeps in flight
 constexpr int QD_WS_HEADER = 64;               // status words live in the first 64 bytes
 
 struct QdParams {
@@ -126,22 +126,18 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// int8 -> f16, exact.  0x64uu is the f16 number 1024 + uu, so two bytes dropped under
-// 0x64 high bytes and reduced by 1024 (+128 for the sign bias) are the weights as f16x2.
+// int8 -> f16 without arithmetic.  0x64uu is the f16 number 1024 + uu, so two bytes dropped
+// under 0x64 high bytes are the (biased) weights plus a constant: w + 1152 for int8 (bytes
+// xor 0x80), w + 1024 for uint8, both exact.  The constant is taken out again per chunk as
+// constant * sum_k x, which one extra MMA against an all-ones operand provides.
 // X and Y are the same four columns of two consecutive k rows; H[b] = {X.b, Y.b} as f16x2.
-__device__ __forceinline__ void bytes_to_f16x2(uint32_t X, uint32_t Y, uint32_t bias, uint32_t (&H)[4]) {
+__device__ __forceinline__ void bytes_to_f16x2(uint32_t X, uint32_t Y, uint32_t (&H)[4]) {
   const uint32_t ra = __byte_perm(X, Y, 0x5140);   // X.0 Y.0 X.1 Y.1
   const uint32_t rb = __byte_perm(X, Y, 0x7362);   // X.2 Y.2 X.3 Y.3
-  uint32_t h[4];
-  h[0] = __byte_perm(ra, 0x64646464u, 0x4140);
-  h[1] = __byte_perm(ra, 0x64646464u, 0x4342);
-  h[2] = __byte_perm(rb, 0x64646464u, 0x4140);
-  h[3] = __byte_perm(rb, 0x64646464u, 0x4342);
-#pragma unroll
-  for (int b = 0; b < 4; b++) {
-    __half2 v = __hsub2(*reinterpret_cast<__half2*>(&h[b]), *reinterpret_cast<const __half2*>(&bias));
-    H[b] = *reinterpret_cast<uint32_t*>(&v);
-  }
+  H[0] = __byte_perm(ra, 0x64646464u, 0x4140);
+  H[1] = __byte_perm(ra, 0x64646464u, 0x4342);
+  H[2] = __byte_perm(rb, 0x64646464u, 0x4140);
+  H[3] = __byte_perm(rb, 0x64646464u, 0x4342);
 }
 
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
@@ -156,10 +152,9 @@ template <typename XT> struct XFrag;
 template <> struct XFrag<__nv_bfloat16> {
   static constexpr int SPLITS = 1;     // bf16 has 8 significant bits: one f16 term is exact
   uint32_t raw[2];
-  __device__ __forceinline__ void load(const void* x, int64_t row_off, int k, bool ok) {
-    const uint16_t* p = reinterpret_cast<const uint16_t*>(x) + row_off + k;
-    raw[0] = ok ? __ldg(reinterpret_cast<const uint32_t*>(p)) : 0u;
-    raw[1] = ok ? __ldg(reinterpret_cast<const uint32_t*>(p + 8)) : 0u;
+  __device__ __forceinline__ void load(const uint8_t* ptr) {     // elements k, k+1 and k+8, k+9
+    raw[0] = __ldg(reinterpret_cast<const uint32_t*>(ptr));
+    raw[1] = __ldg(reinterpret_cast<const uint32_t*>(ptr + 16));
   }
   __device__ __forceinline__ void operands(float mul, uint32_t (&b0)[1], uint32_t (&b1)[1]) const {
     b0[0] = pack_f16x2(__uint_as_float(raw[0] << 16) * mul, __uint_as_float(raw[0] & 0xFFFF0000u) * mul);
@@ -169,10 +164,9 @@ template <> struct XFrag<__nv_bfloat16> {
 template <> struct XFrag<float> {
   static constexpr int SPLITS = 2;     // hi + lo f16 terms carry 22 significant bits
   float2 raw[2];
-  __device__ __forceinline__ void load(const void* x, int64_t row_off, int k, bool ok) {
-    const float* p = reinterpret_cast<const float*>(x) + row_off + k;
-    raw[0] = ok ? __ldg(reinterpret_cast<const float2*>(p)) : make_float2(0.f, 0.f);
-    raw[1] = ok ? __ldg(reinterpret_cast<const float2*>(p + 8)) : make_float2(0.f, 0.f);
+  __device__ __forceinline__ void load(const uint8_t* ptr) {     // elements k, k+1 and k+8, k+9
+    raw[0] = __ldg(reinterpret_cast<const float2*>(ptr));
+    raw[1] = __ldg(reinterpret_cast<const float2*>(ptr + 32));
   }
   __device__ __forceinline__ static void split(float a, float b, uint32_t& hi, uint32_t& lo) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -218,64 +212,14 @@ struct QdSched {
   }
 };
 
-// One warp copies a [64 x 64] int8 chunk into its own stage with 16-byte cp.async
-// (zero-filled outside the matrix) and closes the group.
-__device__ __forceinline__ void issue_chunk_copy(const QdParams& p, const QdSched& sc, int i, uint8_t* stage, int lane) {
-  if (i < sc.n_local) {
-    int tile, kc;
-    sc.coords(i, tile, kc);
-    const int k0 = kc * QD_CHUNK_K, colbase = tile * QD_TILE_N;
-    // lane -> (row lane/4 of each group of 8 rows, 16-byte piece lane%4)
-    const int r0 = lane >> 2, q = lane & 3;
-    const uint8_t* src = p.w + (int64_t)(k0 + r0) * p.N + colbase + 16 * q;
-    const uint32_t dst = smem_u32(stage + r0 * QD_PITCH + 16 * q);
-    const int64_t step = (int64_t)8 * p.N;
-    if (k0 + QD_CHUNK_K <= p.K && colbase + QD_TILE_N <= p.N) {
-#pragma unroll
-      for (int it = 0; it < 8; it++)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + it * 8 * QD_PITCH), "l"(src + it * step) : "memory");
-    } else {      // edge chunk: zero-fill what lies outside the matrix
-      const bool col_ok = colbase + 16 * q < p.N;
-#pragma unroll
-      for (int it = 0; it < 8; it++) {
-        const bool ok = col_ok && (k0 + r0 + 8 * it < p.K);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + it * 8 * QD_PITCH),
-                     "l"(ok ? src + it * step : p.w), "r"(ok ? 16 : 0) : "memory");
-      }
-    }
-  }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-
-template <typename XT, int MT>
-__device__ __forceinline__ void fetch_chunk_inputs(const QdParams& p, int tile, int kc, int g, int t, float (&sc)[8],
-                                                   XFrag<XT> (&xf)[4][MT]) {
-  const int k0 = kc * QD_CHUNK_K, colbase = tile * QD_TILE_N;
-  const int srow = p.scale_group ? k0 / p.scale_group : 0;
-  const float* sp = p.scales + (int64_t)srow * p.N + colbase + 8 * g;
-  const bool ok = colbase + 8 * g < p.N;     // N is a multiple of 16
-#pragma unroll
-  for (int q = 0; q < 2; q++) {
-    float4 v = ok ? __ldg(reinterpret_cast<const float4*>(sp) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-    sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
-  }
-#pragma unroll
-  for (int ks = 0; ks < 4; ks++)
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
-      const int m = mt * 8 + g, k = k0 + 16 * ks + 2 * t;
-      xf[ks][mt].load(p.x, (int64_t)m * p.K, k, m < p.M && k0 + 16 * ks < p.K);
-    }
-}
-
 template <typename XT, int MT, bool WUNSIGNED>
 __global__ void __launch_bounds__(QD_THREADS, 1)
 qdense_decode_kernel(const QdParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   constexpr int RED_FLOATS = MT * 8 * QD_TILE_N;   // one [rows x 64] partial tile
   uint8_t* ring = smem_raw;
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)QD_WARPS * QD_DEPTH * QD_STAGE_BYTES);
-  __shared__ unsigned s_flag;
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)QD_WARPS * QD_RING_STEPS * QD_STEP_BYTES);
+  __shared__ unsigned s_last[2];
   __shared__ unsigned s_rowmax[16];
   __shared__ float s_mul[16], s_inv[16];
 
@@ -290,15 +234,50 @@ qdense_decode_kernel(const QdParams p) {
   sched.n_sk = cta < Gsk ? (int)((long long)(cta + 1) * p.sk_total / Gsk - sched.c0) : 0;
   sched.n_local = sched.n_sk + p.dp_per_cta * p.cpt;
   const int n_local = sched.n_local;
+  const int ksteps_tile = p.K / 16;                      // k-steps (16 rows) per column tile
+  const int gsteps = p.scale_group ? p.scale_group / 16 : 0;   // k-steps per scale group (0: one scale per column)
 
   int dbg_n = 0;
 #define QD_STAMP() do { if (p.dbg && tid == 0 && dbg_n < 16) p.dbg[cta * 16 + dbg_n++] = global_ns(); } while (0)
   QD_STAMP();
 
-  // start streaming before anything else: the first QD_DEPTH chunks of every warp
-  uint8_t* my_ring = ring + (size_t)warp * QD_DEPTH * QD_STAGE_BYTES;
-#pragma unroll
-  for (int d = 0; d < QD_DEPTH; d++) issue_chunk_copy(p, sched, warp + d * QD_WARPS, my_ring + d * QD_STAGE_BYTES, lane);
+  // ---- copy cursor: walks this warp's k-steps through all segments, QD_RING_STEPS ahead of the math.
+  // Within a segment (one column tile, a run of chunks) the 16 warps take contiguous, equal shares
+  // of the k-steps, so they reach the segment's reduction together.
+  int cp_ks = 0, cp_end = 0, cp_next_seg = 0;   // next / end k-step of the share, next segment's first chunk
+  const uint8_t* cp_src = p.w;                   // this lane's source address for the next k-step
+  uint32_t cp_size = 16;                         // 0 for column pieces outside the matrix (zero fill)
+  auto seg_share = [&](int seg_begin, int& tile, int& s0, int& s1) {   // this warp's k-steps [s0,s1) of a segment
+    int kc0;
+    sched.coords(seg_begin, tile, kc0);
+    const int seg_end = seg_begin < sched.n_sk ? min(sched.n_sk, seg_begin + p.cpt - kc0) : seg_begin + p.cpt;
+    const int a = kc0 * 4, b = min(ksteps_tile, (kc0 + seg_end - seg_begin) * 4);
+    s0 = a + (b - a) * warp / QD_WARPS;
+    s1 = a + (b - a) * (warp + 1) / QD_WARPS;
+    return seg_end;
+  };
+  auto cp_issue = [&](uint8_t* slot) {           // copy one k-step (16 rows x 64 bytes), or close an empty group
+    while (cp_ks >= cp_end && cp_next_seg < n_local) {
+      int tile;
+      cp_next_seg = seg_share(cp_next_seg, tile, cp_ks, cp_end);
+      const int col = tile * QD_TILE_N + 16 * (lane & 3);
+      cp_size = col < p.N ? 16u : 0u;
+      cp_src = p.w + (size_t)(cp_ks * 16 + (lane >> 2)) * p.N + (cp_size ? col : 0);
+    }
+    if (cp_ks < cp_end) {
+      const uint32_t dst = smem_u32(slot + (lane >> 2) * QD_PITCH + 16 * (lane & 3));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(cp_src), "r"(cp_size) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 8 * QD_PITCH), "l"(cp_src + (size_t)8 * p.N), "r"(cp_size) : "memory");
+      cp_src += (size_t)16 * p.N;
+      cp_ks++;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // start streaming before anything else
+  uint8_t* my_ring = ring + (size_t)warp * QD_RING_STEPS * QD_STEP_BYTES;
+#pragma unroll 1
+  for (int d = 0; d < QD_RING_STEPS; d++) cp_issue(my_ring + d * QD_STEP_BYTES);
+  QD_STAMP();   // [1] first copies issued
 
   // Row maxima of x (every CTA computes the same values, so partial sums of different
   // CTAs share one scaling); one warp per row, all loads of a row issued together.
@@ -340,11 +319,17 @@ qdense_decode_kernel(const QdParams p) {
     }
     __syncthreads();
   }
-  QD_STAMP();
+  QD_STAMP();   // [2] prologue done
+
   float mul[MT];
+  const uint8_t* xrow[MT];   // this lane's x operands; rows past M read row M-1 with weight 0
 #pragma unroll
-  for (int mt = 0; mt < MT; mt++) mul[mt] = s_mul[mt * 8 + g];
-  const uint32_t wbias = WUNSIGNED ? 0x64006400u : 0x64806480u;   // f16x2 1024 / 1152
+  for (int mt = 0; mt < MT; mt++) {
+    const int m = mt * 8 + g;
+    mul[mt] = m < p.M ? s_mul[m] : 0.0f;
+    xrow[mt] = reinterpret_cast<const uint8_t*>(p.x) + ((size_t)min(m, p.M - 1) * p.K + 2 * t) * sizeof(XT);
+  }
+  const float wbias = WUNSIGNED ? 1024.0f : 1152.0f;   // constant carried by the converted weights
 
   float tot[4][MT][4];
 #pragma unroll
@@ -354,98 +339,110 @@ qdense_decode_kernel(const QdParams p) {
 #pragma unroll
       for (int c = 0; c < 4; c++) tot[j][mt][c] = 0.0f;
 
-  // scales and activations of the warp's next chunk are fetched one chunk ahead
-  float sc_next[8];
-  XFrag<XT> xf_next[4][MT];
-  if (warp < n_local) {
-    int tile, kc;
-    sched.coords(warp, tile, kc);
-    fetch_chunk_inputs<XT, MT>(p, tile, kc, g, t, sc_next, xf_next);
-  }
-
-  int n_done = 0;        // chunks this warp has consumed (selects its ring stage)
+  int n_done = 0;        // k-steps this warp has consumed (selects its ring slot)
+  int pend_tile[2], n_pend = 0;       // split tiles whose arrival ticket is checked at the end
+  unsigned pend_ticket[2] = {0u, 0u}; // meaningful in thread 0 only
   int seg_begin = 0;
   while (seg_begin < n_local) {
-    int tile, kc0;
-    sched.coords(seg_begin, tile, kc0);
-    const int seg_end = seg_begin < sched.n_sk ? min(sched.n_sk, seg_begin + p.cpt - kc0) : seg_begin + p.cpt;
+    int tile, ks0, ks1;
+    const int seg_end = seg_share(seg_begin, tile, ks0, ks1);
+    int kc0;
+    { int tt; sched.coords(seg_begin, tt, kc0); }
     const int colbase = tile * QD_TILE_N;
+    const bool cols_ok = colbase + 8 * g < p.N;     // N is a multiple of 16
 
-    // first local chunk index >= seg_begin that belongs to this warp
-    int i = seg_begin + ((warp - seg_begin) % QD_WARPS + QD_WARPS) % QD_WARPS;
-    for (; i < seg_end; i += QD_WARPS, n_done++) {
-      uint8_t* stage = my_ring + (n_done % QD_DEPTH) * QD_STAGE_BYTES;
+    // blocks of up to 8 k-steps that stay inside one scale group
+    for (int ks = ks0; ks < ks1;) {
+      int cnt = min(8, ks1 - ks);
+      if (gsteps) cnt = min(cnt, gsteps - ks % gsteps);
+      // scales of the block's group for the thread's 8 columns, x operands of its k-steps
       float sc[8];
-      XFrag<XT> xf[4][MT];
+      {
+        const float* sp = p.scales + (size_t)(gsteps ? ks / gsteps : 0) * p.N + colbase + 8 * g;
 #pragma unroll
-      for (int q = 0; q < 8; q++) sc[q] = sc_next[q];
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++)
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++) xf[ks][mt] = xf_next[ks][mt];
-      if (i + QD_WARPS < n_local) {
-        int tn, kn;
-        sched.coords(i + QD_WARPS, tn, kn);
-        fetch_chunk_inputs<XT, MT>(p, tn, kn, g, t, sc_next, xf_next);
-      }
-      // this warp's copy of chunk i is the oldest of its QD_DEPTH open groups
-      asm volatile("cp.async.wait_group %0;" ::"n"(QD_DEPTH - 1) : "memory");
-      __syncwarp();
-
-      float acc[4][MT][4];
-#pragma unroll
-      for (int j = 0; j < 4; j++)
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-          for (int c = 0; c < 4; c++) acc[j][mt][c] = 0.0f;
-
-      if (!p.debug_skip) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-          // rows 2t, 2t+1, 2t+8, 2t+9 of this k-step: exactly the k indices the mma
-          // fragment assigns to lane t; the 80-byte pitch makes the loads conflict-free.
-          uint32_t L[4][2];
-#pragma unroll
-          for (int r = 0; r < 4; r++) {
-            const int row = 16 * ks + 2 * t + (r & 1) + 8 * (r >> 1);
-            const uint2 v = *reinterpret_cast<const uint2*>(stage + row * QD_PITCH + 8 * g);
-            L[r][0] = v.x; L[r][1] = v.y;
-            if (!WUNSIGNED) { L[r][0] ^= 0x80808080u; L[r][1] ^= 0x80808080u; }
-          }
-          uint32_t xb0[MT][XFrag<XT>::SPLITS], xb1[MT][XFrag<XT>::SPLITS];
-#pragma unroll
-          for (int mt = 0; mt < MT; mt++) xf[ks][mt].operands(mul[mt], xb0[mt], xb1[mt]);
-          // H*[b]: columns b (lo) and 4+b (hi) of the thread's 8, for k rows (2t,2t+1) and (2t+8,2t+9)
-          uint32_t Hlo01[4], Hhi01[4], Hlo23[4], Hhi23[4];
-          bytes_to_f16x2(L[0][0], L[1][0], wbias, Hlo01);
-          bytes_to_f16x2(L[0][1], L[1][1], wbias, Hhi01);
-          bytes_to_f16x2(L[2][0], L[3][0], wbias, Hlo23);
-          bytes_to_f16x2(L[2][1], L[3][1], wbias, Hhi23);
-#pragma unroll
-          for (int b = 0; b < 4; b++) {
-            const uint32_t a[4] = {Hlo01[b], Hhi01[b], Hlo23[b], Hhi23[b]};
-#pragma unroll
-            for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-              for (int sp = 0; sp < XFrag<XT>::SPLITS; sp++)
-                mma_f16_16816(acc[b][mt], a, xb0[mt][sp], xb1[mt][sp]);
-          }
+        for (int q = 0; q < 2; q++) {
+          const float4 v = cols_ok ? __ldg(reinterpret_cast<const float4*>(sp) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+          sc[4 * q] = v.x; sc[4 * q + 1] = v.y; sc[4 * q + 2] = v.z; sc[4 * q + 3] = v.w;
         }
       }
-      __syncwarp();     // every lane is done reading the stage: refill it
-      issue_chunk_copy(p, sched, i + QD_DEPTH * QD_WARPS, stage, lane);
+      XFrag<XT> xf[8][MT];
+#pragma unroll
+      for (int s = 0; s < 8; s++)
+        if (s < cnt) {
+#pragma unroll
+          for (int mt = 0; mt < MT; mt++) xf[s][mt].load(xrow[mt] + (size_t)(ks + s) * 16 * sizeof(XT));
+        }
 
+      float acc[4][MT][4], xsum[MT][4];     // xsum: sum_k x of the block, per row, from the all-ones MMA
+#pragma unroll
+      for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          xsum[mt][c] = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[j][mt][c] = 0.0f;
+        }
+
+#pragma unroll
+      for (int s = 0; s < 8; s++) {
+        if (s < cnt) {
+          // the k-step about to be used is the oldest of this warp's open copy groups
+          uint8_t* slot = my_ring + (n_done % QD_RING_STEPS) * QD_STEP_BYTES;
+          asm volatile("cp.async.wait_group %0;" ::"n"(QD_RING_STEPS - 1) : "memory");
+          __syncwarp();
+          if (!p.debug_skip) {
+            // rows 2t, 2t+1, 2t+8, 2t+9: exactly the k indices the mma fragment assigns to lane t;
+            // the 80-byte pitch makes the loads conflict-free.
+            uint32_t L[4][2];
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+              const int row = 2 * t + (r & 1) + 8 * (r >> 1);
+              const uint2 v = *reinterpret_cast<const uint2*>(slot + row * QD_PITCH + 8 * g);
+              L[r][0] = v.x; L[r][1] = v.y;
+              if (!WUNSIGNED) { L[r][0] ^= 0x80808080u; L[r][1] ^= 0x80808080u; }
+            }
+            uint32_t xb0[MT][XFrag<XT>::SPLITS], xb1[MT][XFrag<XT>::SPLITS];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) xf[s][mt].operands(mul[mt], xb0[mt], xb1[mt]);
+            // H*[b]: columns b (lo) and 4+b (hi) of the thread's 8, for k rows (2t,2t+1) and (2t+8,2t+9)
+            uint32_t Hlo01[4], Hhi01[4], Hlo23[4], Hhi23[4];
+            bytes_to_f16x2(L[0][0], L[1][0], Hlo01);
+            bytes_to_f16x2(L[0][1], L[1][1], Hhi01);
+            bytes_to_f16x2(L[2][0], L[3][0], Hlo23);
+            bytes_to_f16x2(L[2][1], L[3][1], Hhi23);
+            {
+              const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};   // f16 1.0
+#pragma unroll
+              for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int sp = 0; sp < XFrag<XT>::SPLITS; sp++) mma_f16_16816(xsum[mt], ones, xb0[mt][sp], xb1[mt][sp]);
+            }
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+              const uint32_t a[4] = {Hlo01[b], Hhi01[b], Hlo23[b], Hhi23[b]};
+#pragma unroll
+              for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int sp = 0; sp < XFrag<XT>::SPLITS; sp++)
+                  mma_f16_16816(acc[b][mt], a, xb0[mt][sp], xb1[mt][sp]);
+            }
+          }
+          __syncwarp();     // every lane is done reading the slot: refill it
+          cp_issue(slot);
+          n_done++;
+        }
+      }
       // column of acc[b][*][0..1] is 8g+b, of acc[b][*][2..3] is 8g+4+b
 #pragma unroll
       for (int b = 0; b < 4; b++)
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
-          tot[b][mt][0] = fmaf(acc[b][mt][0], sc[b], tot[b][mt][0]);
-          tot[b][mt][1] = fmaf(acc[b][mt][1], sc[b], tot[b][mt][1]);
-          tot[b][mt][2] = fmaf(acc[b][mt][2], sc[4 + b], tot[b][mt][2]);
-          tot[b][mt][3] = fmaf(acc[b][mt][3], sc[4 + b], tot[b][mt][3]);
+          tot[b][mt][0] = fmaf(fmaf(-wbias, xsum[mt][0], acc[b][mt][0]), sc[b], tot[b][mt][0]);
+          tot[b][mt][1] = fmaf(fmaf(-wbias, xsum[mt][1], acc[b][mt][1]), sc[b], tot[b][mt][1]);
+          tot[b][mt][2] = fmaf(fmaf(-wbias, xsum[mt][2], acc[b][mt][2]), sc[4 + b], tot[b][mt][2]);
+          tot[b][mt][3] = fmaf(fmaf(-wbias, xsum[mt][3], acc[b][mt][3]), sc[4 + b], tot[b][mt][3]);
         }
+      ks += cnt;
     }
     QD_STAMP();
 
@@ -463,6 +460,7 @@ qdense_decode_kernel(const QdParams p) {
         tot[b][mt][0] = tot[b][mt][1] = tot[b][mt][2] = tot[b][mt][3] = 0.0f;
       }
     __syncthreads();
+    QD_STAMP();   // after deposit barrier
 
     constexpr int PER_THREAD = RED_FLOATS / QD_THREADS;
     float sum[PER_THREAD];
@@ -485,28 +483,14 @@ qdense_decode_kernel(const QdParams p) {
 #pragma unroll
       for (int e = 0; e < PER_THREAD; e++) dst[tid + e * QD_THREADS] = sum[e];
       __syncthreads();
-      const int cf = (int)(((tile_begin + 1) * Gsk - 1) / p.sk_total);
-      const int cl = (int)((tile_end * Gsk - 1) / p.sk_total);
+      // Arrive on the tile's counter now, look at the ticket only when the CTA has finished all
+      // its chunks: by then every contributor has parked its sum, and nobody waits in between.
+      pend_tile[n_pend] = tile;
       if (tid == 0) {
         __threadfence();
-        const unsigned old = atomicAdd(&p.counters[tile], 1u);
-        const unsigned last = (old == (unsigned)(cl - cf)) ? 1u : 0u;
-        if (last) p.counters[tile] = 0;      // leave the workspace prepared for the next launch
-        __threadfence();
-        s_flag = last;
+        pend_ticket[n_pend] = atomicAdd(&p.counters[tile], 1u);
       }
-      __syncthreads();
-      finalize = (s_flag != 0);
-      if (finalize) {
-#pragma unroll
-        for (int e = 0; e < PER_THREAD; e++) sum[e] = 0.0f;
-        for (int c = cf; c <= cl; c++) {       // fixed order: results do not depend on arrival order
-          const long long cs = (long long)c * p.sk_total / Gsk;
-          const float* src = p.partials + ((size_t)c * 2 + (cs > tile_begin ? 0 : 1)) * RED_FLOATS;
-#pragma unroll
-          for (int e = 0; e < PER_THREAD; e++) sum[e] += __ldcg(src + tid + e * QD_THREADS);
-        }
-      }
+      n_pend++;
     }
     if (finalize) {
 #pragma unroll
@@ -521,11 +505,70 @@ qdense_decode_kernel(const QdParams p) {
         }
       }
     }
-    __syncthreads();   // red[] and s_flag are reused by the next segment
+    __syncthreads();   // red[] is reused by the next segment
     QD_STAMP();
     seg_begin = seg_end;
   }
   asm volatile("cp.async.wait_all;" ::: "memory");
+
+  // ---- split tiles this CTA contributed to: the last arriver sums the parked partials ----
+  if (tid == 0) {
+    __threadfence();     // the tickets came back long ago; order the reads below after them
+    for (int i = 0; i < 2; i++) {
+      unsigned last = 0u;
+      if (i < n_pend) {
+        const int tile = pend_tile[i];
+        const long long tile_begin = (long long)tile * p.cpt, tile_end = tile_begin + p.cpt;
+        const int cf = (int)(((tile_begin + 1) * Gsk - 1) / p.sk_total);
+        const int cl = (int)((tile_end * Gsk - 1) / p.sk_total);
+        last = (pend_ticket[i] == (unsigned)(cl - cf)) ? 1u : 0u;
+        if (last) p.counters[tile] = 0;      // leave the workspace prepared for the next launch
+      }
+      s_last[i] = last;
+    }
+  }
+  __syncthreads();
+  for (int i = 0; i < n_pend; i++) {
+    if (s_last[i] == 0) continue;
+    const int tile = pend_tile[i];
+    const long long tile_begin = (long long)tile * p.cpt, tile_end = tile_begin + p.cpt;
+    const int cf = (int)(((tile_begin + 1) * Gsk - 1) / p.sk_total);
+    const int cl = (int)((tile_end * Gsk - 1) / p.sk_total);
+    constexpr int PER_THREAD = RED_FLOATS / QD_THREADS;
+    float sum[PER_THREAD];
+#pragma unroll
+    for (int e = 0; e < PER_THREAD; e++) sum[e] = 0.0f;
+    for (int c0 = cf; c0 <= cl; c0 += 4) {   // fixed order: results do not depend on arrival order
+      float v[4][PER_THREAD];                // four contributors' loads in flight together
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int c = min(c0 + u, cl);
+        const long long cs = (long long)c * p.sk_total / Gsk;
+        const float* src = p.partials + ((size_t)c * 2 + (cs > tile_begin ? 0 : 1)) * RED_FLOATS;
+#pragma unroll
+        for (int e = 0; e < PER_THREAD; e++) v[u][e] = __ldcg(src + tid + e * QD_THREADS);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+        if (c0 + u <= cl) {
+#pragma unroll
+          for (int e = 0; e < PER_THREAD; e++) sum[e] += v[u][e];
+        }
+    }
+    const int colbase = tile * QD_TILE_N;
+#pragma unroll
+    for (int e = 0; e < PER_THREAD; e++) {
+      const int idx = tid + e * QD_THREADS;
+      const int m = idx / QD_TILE_N, col = colbase + idx % QD_TILE_N;
+      if (m < p.M && col < p.N) {
+        float v = sum[e] * s_inv[m];
+        if (p.bias) v += __ldg(p.bias + col);
+        v = apply_activation(v, p.activation);
+        Scalar<XT>::store(reinterpret_cast<XT*>(p.out), (int64_t)m * p.N + col, v);
+      }
+    }
+  }
+  QD_STAMP();
 #undef QD_STAMP
 }
 
@@ -533,7 +576,7 @@ qdense_decode_kernel(const QdParams p) {
 // planning and launch
 // ---------------------------------------------------------------------------
 static size_t decode_smem(int mt) {
-  return (size_t)QD_WARPS * QD_DEPTH * QD_STAGE_BYTES + (size_t)QD_WARPS * mt * 8 * QD_TILE_N * 4;
+  return (size_t)QD_WARPS * QD_RING_STEPS * QD_STEP_BYTES + (size_t)QD_WARPS * mt * 8 * QD_TILE_N * 4;
 }
 
 // Tiles split across CTAs (stream-K) and tiles owned whole, for `tiles` column tiles on `grid` CTAs.
