@@ -145,6 +145,38 @@ def other_kernels(dv, dev, stream):
     res["dot_general_4096_bf16"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": tf, "frac_of_measured_bf16_peak": tf / tpeak}
     for m in (a, b, c):
         m.free()
+    # the same product on float32 operands (three bf16 planes each, six plane products)
+    af = dv.DeviceMem.from_numpy(rng.standard_normal(n * n, dtype=np.float32) * 0.05, dev)
+    bf = dv.DeviceMem.from_numpy(rng.standard_normal(n * n, dtype=np.float32) * 0.05, dev)
+    cf = dv.DeviceMem(n * n * 4, dev)
+    plan = dv.Plan.dot(1, n, n, n, dv.F32, dev=dev)
+    us = time_plan(plan, [af.ptr, bf.ptr], [cf.ptr], 10)
+    res["dot_general_4096_f32"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": 2.0 * n ** 3 / us / 1e6,
+                                   "note": "f32-accurate result from 6 bf16 plane products; includes the two split launches"}
+    for m in (af, bf, cf):
+        m.free()
+    # batched [32,512,128] x [32,128,512] bf16
+    a, b, c = rand_bf16(32 * 512 * 128), rand_bf16(32 * 128 * 512), dv.DeviceMem(32 * 512 * 512 * 2, dev)
+    plan = dv.Plan.dot(32, 512, 512, 128, dv.BF16, dev=dev)
+    us = time_plan(plan, [a.ptr, b.ptr], [c.ptr], 50)
+    res["dot_general_batched_32x512x128x512_bf16"] = {"kernel": plan.kernel_name, "us": us,
+                                                      "GB/s": (2 * 32 * 512 * 128 * 2 + 32 * 512 * 512 * 2) / us / 1e3}
+    for m in (a, b, c):
+        m.free()
+    # prefill-shaped quantized dense: 4 x 512 tokens through the 4096 x 14336 projection, per-channel scales
+    Mp = 2048
+    x = rand_bf16(Mp * K_DIM)
+    w = dv.DeviceMem.from_numpy(rng.integers(-127, 128, size=K_DIM * N_DIM, dtype=np.int8), dev)
+    sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=N_DIM).astype(np.float32), dev)
+    y = dv.DeviceMem(Mp * N_DIM * 2, dev)
+    plan = dv.Plan.qdense(Mp, K_DIM, N_DIM, dv.BF16, dv.I8, dv.SCALE_CHANNEL, 0, False, False, dv.ACT_SILU, dev=dev)
+    us = time_plan(plan, [x.ptr, w.ptr, sc.ptr], [y.ptr], 10)
+    tf = 2.0 * Mp * K_DIM * N_DIM / us / 1e6
+    res["quantized_dense_prefill_2048x4096x14336_bf16"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": tf,
+                                                          "frac_of_measured_bf16_peak": tf / tpeak,
+                                                          "note": "includes expanding the int8 weights to bf16"}
+    for m in (x, w, sc, y):
+        m.free()
     B, Hq, Hkv, S, D = 8, 32, 8, 2048, 128
     q, k, v = rand_bf16(B * Hq * S * D), rand_bf16(B * Hkv * S * D), rand_bf16(B * Hkv * S * D)
     o = dv.DeviceMem(B * Hq * S * D * 2, dev)

@@ -38,6 +38,23 @@ def test_dot_matches_oracle(B, M, N, K, transposed, dtype, variant):
     assert max_abs_normalised(as_f64(got, code), want) < TOL[dtype]
 
 
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("B,M,N,K", [(1, 128, 256, 192), (4, 200, 72, 264), (2, 65, 136, 40), (1, 300, 520, 1024)])
+def test_dot_f32_on_tensor_cores(B, M, N, K, transposed):
+    """float32 operands as three bf16 planes each, six plane products in one f32 accumulator."""
+    lhs = make(11, (B, M, K), "f32")
+    rhs = make(12, (B, N, K) if transposed else (B, K, N), "f32")
+    want = oracle_dot(lhs, rhs, orc.F32, transposed).astype(np.float64)
+    got, plan = ops.dot_normalised(lhs, rhs, in_dtype=dv.F32, rhs_transposed=transposed, variant=dv.DOT_TCGEN05,
+                                   return_plan=True)
+    assert plan.kernel_name.startswith("gemm_tcgen05_Float32_Float32")
+    assert max_abs_normalised(got.astype(np.float64), want) < 2e-6
+    # non-finite inputs propagate as in IEEE arithmetic
+    lhs[0, 3, 5] = np.inf
+    got = ops.dot_normalised(lhs, rhs, in_dtype=dv.F32, rhs_transposed=transposed, variant=dv.DOT_TCGEN05)
+    assert not np.isfinite(got[0, 3]).all() and np.isfinite(got[0, 4]).all()
+
+
 def test_dot_output_dtypes_and_ints():
     lhs = make(1, (1, 4, 6), "bf16")
     rhs = make(2, (1, 6, 5), "bf16")

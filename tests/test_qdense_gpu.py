@@ -68,9 +68,15 @@ def test_config1_reference_cpu_case():
     got, plan = ops.quantized_dense(x, w, s, None, b, scale_layout=dv.SCALE_CHANNEL, return_plan=True)
     want = oracle_compact(x, w, s, b, "channel", 0, orc.ACT_NONE)
     assert max_abs_normalised(got, want) < F32_TOL
-    # the same numbers through the reference's own scale layout (expanded [K,N], BlockSize=1)
-    got_ref = ops.quantized_dense(x, w, orc.expand_scales(s, "channel", 1024, 1024), None, b, block_size=1)
+    assert plan.kernel_name.startswith("qdense_prefill_tcgen05_f32")
+    # the same numbers through the reference's own scale layout (expanded [K,N], BlockSize=1):
+    # identical bits from the kernel that keeps the reference's summation order, and within
+    # tolerance from the tensor-core path the planner picks for this size
+    sref = orc.expand_scales(s, "channel", 1024, 1024)
+    got_ref = ops.quantized_dense(x, w, sref, None, b, block_size=1, variant=dv.QDENSE_GENERIC)
     assert np.array_equal(got_ref, want)
+    got_auto = ops.quantized_dense(x, w, sref, None, b, block_size=1)
+    assert max_abs_normalised(got_auto, want) < 1e-5
 
 
 # ------------------------------------------------------------- decode kernel
@@ -154,6 +160,66 @@ def test_decode_linearity_property():
     lhs = run(2.0 * x1 + x2)
     rhs = 2.0 * run(x1) + run(x2)
     assert max_abs_normalised(lhs, rhs) < 1e-5
+
+
+# ------------------------------------------------------------- prefill kernel
+PREFILL_SHAPES = [
+    # M, K, N, layout, block/group, zero points
+    (17, 64, 72, "channel", 0, False),       # smallest M beyond the decode kernel, ragged tiles
+    (130, 200, 264, "kgroup", 40, False),
+    (300, 512, 520, "ref", 16, True),
+    (257, 1024, 1024, "kgroup", 128, False),
+    (64, 320, 136, "ref", 1, False),
+]
+
+
+@pytest.mark.parametrize("M,K,N,layout,block,with_zp", PREFILL_SHAPES)
+@pytest.mark.parametrize("x_dtype", ["f32", "bf16"])
+def test_prefill_matches_oracle(M, K, N, layout, block, with_zp, x_dtype):
+    if layout == "ref":
+        x, w, s, b = qdense_inputs(M + K + N, M, K, N, x_dtype=x_dtype, scale_layout="ref", block_size=block)
+        full, sl = s, dv.SCALE_REF
+    else:
+        x, w, s, b = qdense_inputs(M + K + N, M, K, N, x_dtype=x_dtype, scale_layout=layout, group=block)
+        full, sl = orc.expand_scales(s, layout, K, N, block), (dv.SCALE_CHANNEL if layout == "channel" else dv.SCALE_KGROUP)
+    zp = np.random.default_rng(5).uniform(-0.05, 0.05, size=s.shape).astype(np.float32) if with_zp else None
+    want = orc.qdense_linear(x, w, full, zp, b, block if layout == "ref" else 1, orc.ACT_GELU, threads=orc.max_threads())
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    got, plan = ops.quantized_dense(xin, w, s, zp, b, x_dtype=dv.BF16 if x_dtype == "bf16" else dv.F32, scale_layout=sl,
+                                    block_size=block, activation=dv.ACT_GELU, variant=dv.QDENSE_PREFILL, return_plan=True)
+    assert plan.kernel_name.startswith("qdense_prefill_tcgen05_" + x_dtype)
+    if x_dtype == "bf16":
+        assert max_abs_normalised(orc.bf16_to_f32(got), want) < BF16_TOL
+        assert max_abs_normalised(orc.bf16_to_f32(got), orc.bf16_to_f32(orc.bf16_from_f32(want))) < 2.0 ** -7
+    else:
+        assert max_abs_normalised(got, want) < 1e-5
+
+
+def test_prefill_uint8_all_activations():
+    x, w, s, b = qdense_inputs(77, 40, 256, 264, scale_layout="channel", unsigned=True)
+    for act in ACT.values():
+        got = ops.quantized_dense(x, w, s, None, b, scale_layout=dv.SCALE_CHANNEL, activation=act, variant=dv.QDENSE_PREFILL)
+        want = oracle_compact(x, w, s, b, "channel", 0, act)
+        assert max_abs_normalised(got, want) < F32_TOL
+
+
+@pytest.mark.parametrize("layout,group", [("channel", 0), ("kgroup", 128)])
+def test_prefill_llama_projection_full_size(layout, group):
+    """Prefill batch 4 x 512 tokens through the 4096 x 14336 projection, bf16 activations; a sample of
+    rows against the oracle, and the rows the decode kernel computes agree with it."""
+    M, K, N = 2048, 4096, 14336
+    x, w, s, _ = qdense_inputs(0x5EED0005, M, K, N, x_dtype="bf16", scale_layout=layout, group=group, bias=False)
+    xb = orc.bf16_from_f32(x)
+    sl = dv.SCALE_CHANNEL if layout == "channel" else dv.SCALE_KGROUP
+    got, plan = ops.quantized_dense(xb, w, s, None, None, x_dtype=dv.BF16, scale_layout=sl, block_size=group,
+                                    activation=dv.ACT_SILU, return_plan=True)
+    assert plan.kernel_name.startswith("qdense_prefill_tcgen05_bf16")
+    rows = [0, 127, 128, 1000, 2047]
+    want = oracle_compact(np.ascontiguousarray(x[rows]), w, s, None, layout, group, orc.ACT_SILU)
+    assert max_abs_normalised(orc.bf16_to_f32(got[rows]), want) < BF16_TOL
+    dec = ops.quantized_dense(np.ascontiguousarray(xb[rows]), w, s, None, None, x_dtype=dv.BF16, scale_layout=sl,
+                              block_size=group, activation=dv.ACT_SILU)
+    assert max_abs_normalised(orc.bf16_to_f32(dec), orc.bf16_to_f32(got[rows])) < 2.0 ** -7
 
 
 # ------------------------------------------------------------- validation / errors
