@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libcudabackend.so")
 OBJ = os.path.join(HERE, "build")
 
-SOURCES = ["runtime.cu", "qdense.cu", "qdense_prefill.cu", "dot.cu", "dot_generic.cu", "gemm_tcgen05.cu",
+SOURCES = ["runtime.cu", "qdense.cu", "qdense_prefill.cu", "qdense_decode_tc.cu", "dot.cu", "dot_generic.cu", "gemm_tcgen05.cu",
            "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "helper_ops.cu", "graph.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",

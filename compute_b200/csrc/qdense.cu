@@ -602,6 +602,9 @@ static bool decode_eligible(const cb_qdense_desc& d, std::string* why) {
 bool qdense_prefill_eligible(const cb_qdense_desc& d, std::string* why);
 int qdense_prefill_plan(cb_plan* p);
 int qdense_prefill_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why);
+int qdense_decode_tc_plan(cb_plan* p);
+int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 
 int qdense_plan(cb_plan* p) {
   cb_qdense_desc& d = p->qd;
@@ -622,13 +625,15 @@ int qdense_plan(cb_plan* p) {
   int variant = d.variant;
   std::string why;
   const bool can_decode = decode_eligible(d, &why);
-  std::string why_prefill;
+  std::string why_prefill, why_tc;
+  const bool can_decode_tc = qdense_decode_tc_eligible(d, &why_tc);
   const bool can_prefill = qdense_prefill_eligible(d, &why_prefill);
   if (variant == CB_QDENSE_AUTO) {
     // decode shapes stream W once; beyond 16 rows the tensor-core GEMM wins as soon as the
     // problem is large enough to pay for expanding the weights (small ones stay on the
     // CUDA-core kernel, which also keeps the reference's summation order)
-    if (can_decode) variant = CB_QDENSE_DECODE_MMA;
+    if (can_decode_tc) variant = CB_QDENSE_DECODE_TC;
+    else if (can_decode) variant = CB_QDENSE_DECODE_MMA;
     else if (can_prefill && d.M > 16 && (double)d.M * d.K * d.N >= 64.0 * 1024 * 1024) variant = CB_QDENSE_PREFILL;
     else variant = CB_QDENSE_GENERIC;
   }
@@ -636,8 +641,13 @@ int qdense_plan(cb_plan* p) {
     return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense decode kernel: %s", why.c_str());
   if (variant == CB_QDENSE_PREFILL && !can_prefill)
     return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense prefill kernel: %s", why_prefill.c_str());
+  if (variant == CB_QDENSE_DECODE_TC && !can_decode_tc)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense tensor-core decode kernel: %s", why_tc.c_str());
+  if (variant < CB_QDENSE_AUTO || variant > CB_QDENSE_DECODE_TC)
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown kernel variant %d", variant);
   p->variant = variant;
   if (variant == CB_QDENSE_PREFILL) return qdense_prefill_plan(p);
+  if (variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_plan(p);
 
   if (variant == CB_QDENSE_GENERIC) {
     p->blocks = (int)(((d.N + QG_COLS - 1) / QG_COLS) * ((d.M + QG_ROWS - 1) / QG_ROWS));
@@ -727,6 +737,7 @@ int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   const cb_qdense_desc& d = p->qd;
   if (p->variant == CB_QDENSE_DECODE_MMA) return launch_decode(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_PREFILL) return qdense_prefill_launch(p, in, out, ws, s);
+  if (p->variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_launch(p, in, out, ws, s);
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
   if (bf) return wu ? launch_generic<__nv_bfloat16, uint8_t>(p, in, out, s) : launch_generic<__nv_bfloat16, int8_t>(p, in, out, s);
   return wu ? launch_generic<float, uint8_t>(p, in, out, s) : launch_generic<float, int8_t>(p, in, out, s);

@@ -1,0 +1,600 @@
+// FusedQuantizedDense for decode shapes (M <= 16) on the integer tensor cores:
+//   y[M,N] = act( x[M,K] @ (W[K,N] * scale) + bias[N] ),  W int8/uint8, compact scales
+// (reference semantics: internal/gobackend/fusedops/quantizeddense.go:330-418 of gomlx/compute).
+//
+// The op is bound by reading W once from HBM, so the kernel spends no instruction on the
+// weights: TMA lands [128 k x 128 n] byte tiles of W in shared memory and tcgen05.mma kind::i8
+// consumes them in place as the MN-major operand.  The activations become the other operand by
+// writing each row in fixed point: x[m,k] = unit[m] * (d0 + 128 d1 + 16384 d2) with signed
+// base-128 digits (unit[m] a power of two chosen from the row maximum, 20 bits below it; exact
+// for bfloat16 values within 2^-13 of the row maximum, and 2^-21 of the row maximum otherwise
+// and for float32).  The digits of all rows form a [3*MB x K] int8 matrix (MB rows per digit),
+// so one MMA of shape (128 n) x (3*MB) x (32 k) yields the three digit sums of 128 output
+// columns, exactly, in s32 tensor memory.  Epilogue threads (one per output column) turn a
+// finished 128-k unit into f32, recombine the digits, multiply by the scale of that K group
+// and add it to their running totals.
+//
+//   qdense_xdigits_kernel   x -> digits + per-row exponents (one CTA per row, a few microseconds)
+//   qdense_decode_tc_kernel persistent, one CTA per SM over a balanced contiguous range of
+//                           (n tile, k unit) pairs:
+//       warp 8   TMA producer: W tile + digit tile + the unit's 128 scales into an 8-stage ring
+//                (the first weight tiles are requested before the digit kernel has finished)
+//       warp 9   MMA issuer: 4 MMAs (K = 32) per unit into one of 8 TMEM accumulators
+//       warps 0-7 epilogue as above, two groups of four warps on alternate units; a tile whose
+//                units are split between CTAs is finished by the CTA that arrives last, summing
+//                the parked partial tiles in CTA order (deterministic: the result does not
+//                depend on which CTA finishes)
+// All mbarrier waits are bounded; a timeout sets the status word and TMEM is always freed.
+#include "tc_common.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <stdlib.h>
+#include <string.h>
+
+namespace cb {
+
+using namespace tc;
+
+constexpr int QT_TILE_N = 128;
+constexpr int QT_UNIT_K = 128;
+constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
+constexpr int QT_STAGES = 8;
+constexpr int QT_THREADS = 320;                       // warps 0-7 epilogue, 8 TMA, 9 MMA
+constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9;
+constexpr int QT_TMEM_COLS = 512;
+constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
+constexpr int QT_SC_BYTES = QT_TILE_N * 4;
+constexpr int QT_HEADER = 256;                          // status words, then arrival counters
+
+struct QtParams {
+  const float* scales;
+  const float* bias;
+  void* out;
+  unsigned* status;
+  unsigned* counters;       // one per n tile, zero between launches
+  const int* row_exp;       // [16] exponent of unit[m]
+  const unsigned* row_bad;  // [16] non-zero when the row holds a non-finite value
+  float* partials;          // [grid][2][MB][128]
+  int M, K, N;
+  int n_tiles, units_per_tile;
+  long long total_units;
+  int scale_group;          // 0: one scale per column; else rows of the K group
+  int activation;
+  int out_bf16;
+  uint32_t idesc;
+  unsigned long long* dbg;  // timing diagnosis only: 8 time stamps per CTA, or null
+  int debug_no_mma;         // timing diagnosis only: the MMA warp issues commits but no MMA
+  int debug_linear;         // timing diagnosis only: weight tiles are read as contiguous 16 KB blocks
+};
+
+// ---------------------------------------------------------------------------
+// x -> digits
+// ---------------------------------------------------------------------------
+constexpr int QX_THREADS = 512;
+
+// 8 consecutive elements of a row as floats (K is a multiple of 16, rows are 16-byte aligned)
+__device__ __forceinline__ void qx_load8(const __nv_bfloat16* row, int k, float (&v)[8]) {
+  const uint4 r = *reinterpret_cast<const uint4*>(row + k);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ void qx_load8(const float* row, int k, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(row + k), b = *reinterpret_cast<const float4*>(row + k + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(QX_THREADS)
+qdense_xdigits_kernel(const XT* __restrict__ x, int K, int MB, int8_t* __restrict__ digits, int* __restrict__ row_exp,
+                      unsigned* __restrict__ row_bad) {
+  // the kernel that consumes the digits may start its own set-up now; it waits for this grid
+  // to finish before it reads them
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ float s_max[QX_THREADS / 32];
+  __shared__ unsigned s_bad[QX_THREADS / 32];
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const XT* row = x + (size_t)m * K;
+  float amax = 0.0f;
+  unsigned bad = 0;
+  for (int k = tid * 8; k < K; k += QX_THREADS * 8) {
+    float v[8];
+    qx_load8(row, k, v);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const float a = fabsf(v[e]);
+      if (!(a <= 3.0e38f)) bad = 1;          // inf or NaN
+      else amax = fmaxf(amax, a);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+  }
+  if ((tid & 31) == 0) { s_max[tid >> 5] = amax; s_bad[tid >> 5] = bad; }
+  __syncthreads();
+  amax = s_max[0]; bad = s_bad[0];
+#pragma unroll
+  for (int i = 1; i < QX_THREADS / 32; i++) { amax = fmaxf(amax, s_max[i]); bad |= s_bad[i]; }
+  int ex = 0;
+  (void)frexpf(amax, &ex);                 // amax < 2^ex
+  const int shift = 20 - ex;               // |x| * 2^shift <= 2^20
+  if (tid == 0) { row_exp[m] = -shift; row_bad[m] = bad; }
+  // 2^shift as two factors that are always normal floats (shift lies in [-108, 169])
+  const int sh1 = shift / 2, sh2 = shift - sh1;
+  const float p1 = __int_as_float((127 + sh1) << 23), p2 = __int_as_float((127 + sh2) << 23);
+  int8_t* d0 = digits + (size_t)(0 * MB + m) * K;
+  int8_t* d1 = digits + (size_t)(1 * MB + m) * K;
+  int8_t* d2 = digits + (size_t)(2 * MB + m) * K;
+  for (int k = tid * 8; k < K; k += QX_THREADS * 8) {
+    float v[8];
+    qx_load8(row, k, v);
+    uint32_t w0[2] = {0, 0}, w1[2] = {0, 0}, w2[2] = {0, 0};
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const float f = (fabsf(v[e]) <= 3.0e38f) ? v[e] : 0.0f;
+      const int q = __float2int_rn(f * p1 * p2);
+      const int a = ((q + 64) & 127) - 64;
+      const int q1 = (q - a) >> 7;
+      const int b = ((q1 + 64) & 127) - 64;
+      const int c = (q1 - b) >> 7;
+      w0[e >> 2] |= (uint32_t)(a & 0xFF) << (8 * (e & 3));
+      w1[e >> 2] |= (uint32_t)(b & 0xFF) << (8 * (e & 3));
+      w2[e >> 2] |= (uint32_t)(c & 0xFF) << (8 * (e & 3));
+    }
+    *reinterpret_cast<uint2*>(d0 + k) = make_uint2(w0[0], w0[1]);
+    *reinterpret_cast<uint2*>(d1 + k) = make_uint2(w1[0], w1[1]);
+    *reinterpret_cast<uint2*>(d2 + k) = make_uint2(w2[0], w2[1]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// schedule helpers (the same arithmetic on every CTA)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ long long qt_first_unit(long long total, int grid, int cta) {
+  return (total * cta) / grid;
+}
+// the CTA whose range [first(c), first(c+1)) holds unit u
+__device__ __forceinline__ int qt_cta_of(long long total, int grid, long long u) {
+  int c = (int)(((u + 1) * grid - 1) / total);
+  if (c >= grid) c = grid - 1;
+  while (c > 0 && qt_first_unit(total, grid, c) > u) c--;
+  while (c + 1 < grid && qt_first_unit(total, grid, c + 1) <= u) c++;
+  return c;
+}
+
+__device__ __forceinline__ void qt_fail(const QtParams& p, unsigned code, unsigned detail) {
+  atomicExch(&p.status[0], code);
+  atomicExch(&p.status[1], detail);
+}
+
+// act(v[m]) -> out[m, n] for the rows that exist.  The activation is chosen once, outside the
+// row loop, so the MB rows are independent instruction streams; for 16-bit outputs SiLU uses
+// the hardware exp and reciprocal (error far below one unit of the output).
+template <int MB, int ACT, bool BF16>
+__device__ __forceinline__ void qt_store_rows_act(const float* v, void* out, int M, int N, int n) {
+#pragma unroll
+  for (int m = 0; m < MB; m++) {
+    float y;
+    if (ACT == CB_ACT_SILU && BF16) y = __fdividef(v[m], 1.0f + __expf(-v[m]));
+    else y = apply_activation(v[m], ACT);
+    if (m < M) {
+      if (BF16) reinterpret_cast<uint16_t*>(out)[(size_t)m * N + n] = f32_to_bf16_bits(y);
+      else reinterpret_cast<float*>(out)[(size_t)m * N + n] = y;
+    }
+  }
+}
+template <int MB, bool BF16>
+__device__ __forceinline__ void qt_store_rows(const float* v, int act, void* out, int M, int N, int n) {
+  switch (act) {
+    case CB_ACT_GELU: qt_store_rows_act<MB, CB_ACT_GELU, BF16>(v, out, M, N, n); break;
+    case CB_ACT_RELU: qt_store_rows_act<MB, CB_ACT_RELU, BF16>(v, out, M, N, n); break;
+    case CB_ACT_SILU: qt_store_rows_act<MB, CB_ACT_SILU, BF16>(v, out, M, N, n); break;
+    case CB_ACT_HARDSWISH: qt_store_rows_act<MB, CB_ACT_HARDSWISH, BF16>(v, out, M, N, n); break;
+    case CB_ACT_TANH: qt_store_rows_act<MB, CB_ACT_TANH, BF16>(v, out, M, N, n); break;
+    default: qt_store_rows_act<MB, CB_ACT_NONE, BF16>(v, out, M, N, n); break;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------
+template <int NB>      // MMA N extent: 3 digit planes of MB = NB / 3 rows (16 -> 5, 32 -> 10, 48 -> 16)
+__global__ void __launch_bounds__(QT_THREADS, 1)
+qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_s, const QtParams p) {
+  constexpr int MB = NB / 3;
+  constexpr int X_BYTES = NB * QT_UNIT_K;
+  constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
+  constexpr int NBUF = 8;
+  static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
+  static_assert(QT_SC_SLOTS >= QT_STAGES + NBUF, "a scale slot must outlive its stage and its accumulator");
+  extern __shared__ uint8_t qt_smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qt_smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + QT_STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                       // [QT_STAGES] TMA -> MMA
+  uint64_t* empty = bars + QT_STAGES;          // [QT_STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * QT_STAGES;   // [NBUF] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> MMA
+  float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
+  float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
+  __shared__ uint32_t s_tmem;
+  __shared__ unsigned s_failed;
+  __shared__ unsigned s_last;
+  __shared__ float s_unit[16][2];     // unit[m] as two normal factors
+  __shared__ unsigned s_bad[16];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#define QT_STAMP(i) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 8 + (i)] = global_ns(); } while (0)
+  if (tid == 0) QT_STAMP(0);
+  const int G = p.units_per_tile;
+  const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
+  const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
+  const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
+
+  // The producer thread owns the stage barriers: it sets them up itself and starts the weight
+  // stream at once.  Weights do not depend on the digit kernel, so with a programmatic dependent
+  // launch the first QT_STAGES tiles are already in flight while that kernel still runs.
+  int early = 0;
+  if (warp == QT_TMA_WARP && lane == 0) {
+    for (int s = 0; s < QT_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_w);
+    early = n_units < QT_STAGES ? n_units : QT_STAGES;
+    int tile = tile0, g = g0;
+    for (int it = 0; it < early; it++) {
+      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES);
+      if (p.debug_linear) tma_load_2d(base + it * STAGE_BYTES, &tmap_w, 0, (int)((u0 + it) * 128), &full[it]);
+      else tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
+      if (++g == G) { g = 0; tile++; }
+    }
+    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmap_s);
+  }
+  if (tid == 0) {
+    for (int b = 0; b < NBUF; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    s_failed = 0;
+    fence_barrier_init();
+  }
+  if (warp == QT_MMA_WARP) tmem_alloc(&s_tmem, QT_TMEM_COLS);
+  // from here on the outputs of the digit kernel are read
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid < 16) {
+    const int e = p.row_exp[tid], e1 = e / 2, e2 = e - e1;       // e lies in [-169, 108]
+    s_unit[tid][0] = __int_as_float((127 + e1) << 23);
+    s_unit[tid][1] = __int_as_float((127 + e2) << 23);
+    s_bad[tid] = p.row_bad[tid];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+  if (tid == 0) QT_STAMP(1);
+
+  if (warp == QT_TMA_WARP) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int tile = tile0, g = g0;
+      for (int it = 0; it < n_units && !*(volatile unsigned*)&s_failed; it++) {
+        const int s = it % QT_STAGES;
+        uint8_t* sw = base + s * STAGE_BYTES;
+
+        if (it >= early) {
+          if (!mbar_wait(&empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
+          if (p.debug_linear) tma_load_2d(sw, &tmap_w, 0, (int)((u0 + it) * 128), &full[s]);
+          else tma_load_2d(sw, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
+        }
+        // The 128 scales of the unit ride along: their slot is reused QT_SC_SLOTS units later, by
+        // which time the epilogue of this unit has read them (it does so before it releases the
+        // accumulator, which the MMA of unit it+8 waits for, which this loop's unit it+16 waits for).
+        const int srow = p.scale_group ? (g * QT_UNIT_K) / p.scale_group : 0;
+        tma_load_2d(sw + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);              // [NB rows][128 k]
+        tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+        if (++g == G) { g = 0; tile++; }
+      }
+    }
+  } else if (warp == QT_MMA_WARP) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      for (int it = 0; it < n_units && !*(volatile unsigned*)&s_failed; it++) {
+        const int s = it % QT_STAGES, buf = it % NBUF;
+        if (it >= NBUF && !mbar_wait(&acc_empty[buf], (uint32_t)((it / NBUF - 1) & 1))) { qt_fail(p, 2, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        if (!mbar_wait(&full[s], (uint32_t)((it / QT_STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        tc_fence_after();
+        const uint32_t sw = smem_u32(base + s * STAGE_BYTES), sx = sw + QT_W_BYTES;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NB);
+#pragma unroll
+        for (int j = 0; j < QT_UNIT_K / 32; j++) {
+          // W: MN-major, 128 n bytes per k row, 8-row groups 1024 bytes apart, 32 k rows per MMA
+          const uint64_t da = smem_desc_sw128(sw + j * 32 * 128, QT_W_BYTES, 1024);
+          // digits: K-major, 128 k bytes per row, 8-row groups 1024 bytes apart, 32 bytes per MMA
+          const uint64_t db = smem_desc_sw128(sx + j * 32, 16, 1024);
+          if (!p.debug_no_mma) umma_i8(d_tmem, da, db, p.idesc, j > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 0-7) ----------------------
+    // Two groups of four warps take alternate units, so that one group's TMEM load and barrier
+    // round trips hide behind the other's arithmetic.  Each thread owns one output column of the
+    // tile (TMEM lane) and keeps MB running totals; at the end of the CTA's share of a tile the
+    // second group hands its totals to the first through shared memory.
+    const int grp = warp >> 2, quarter = warp & 3;
+    const int nl = quarter * 32 + lane;             // column within the tile = TMEM lane
+    const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float tot[MB];
+#pragma unroll
+    for (int m = 0; m < MB; m++) tot[m] = 0.0f;
+    bool failed = false;
+    int tile = tile0, g = g0;
+    for (int it = 0; it < n_units; it++) {
+      // After a timeout this group stops touching the pipeline but keeps walking the units, so that
+      // the barriers below still see every thread (the status word reports the failure).
+      if ((it & 1) == grp && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
+      if ((it & 1) == grp && !failed) {
+        const int buf = it % NBUF;
+        tc_fence_after();
+        uint32_t acc[NB];
+#pragma unroll
+        for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
+        const float sc = sc_slots[(it % QT_SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        // s32 -> f32 through the 1.5 * 2^23 offset (|sum| < 2^22), digits recombined, group scale applied
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+          const float f0 = __uint_as_float(acc[m] + 0x4B400000u) - 12582912.0f;
+          const float f1 = __uint_as_float(acc[MB + m] + 0x4B400000u) - 12582912.0f;
+          const float f2 = __uint_as_float(acc[2 * MB + m] + 0x4B400000u) - 12582912.0f;
+          tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)), sc, tot[m]);
+        }
+      }
+      const bool tile_ends = (g == G - 1);
+      const bool final_seg = it + 1 == n_units;
+      if (tile_ends || it + 1 == n_units) {
+        // ---- end of this CTA's share of the tile ----
+        if (tid == 0 && final_seg) QT_STAMP(2);
+        if (grp == 1) {
+#pragma unroll
+          for (int m = 0; m < MB; m++) s_merge[m * QT_TILE_N + nl] = tot[m];
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (grp == 0) {
+#pragma unroll
+          for (int m = 0; m < MB; m++) tot[m] += s_merge[m * QT_TILE_N + nl];
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");      // s_merge may be rewritten
+        if (grp == 0) {
+          const int n = tile * QT_TILE_N + nl;
+          const bool whole = tile_ends && (it >= g);          // the tile's first unit is ours too
+          bool write = true;
+          if (!whole) {
+            // park the partial tile, count the arrival; the last CTA to arrive sums all of them in CTA order
+            const int slot = (tile == tile0) ? 0 : 1;         // first or last share of this CTA's range
+            float* mine = p.partials + ((size_t)(blockIdx.x * 2 + slot) * MB) * QT_TILE_N;
+#pragma unroll
+            for (int m = 0; m < MB; m++) mine[m * QT_TILE_N + nl] = tot[m];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tid == 0 && final_seg) QT_STAMP(5);
+            const long long tile_first = (long long)tile * G;
+            const int c_first = qt_cta_of(p.total_units, gridDim.x, tile_first);
+            const int c_last = qt_cta_of(p.total_units, gridDim.x, tile_first + G - 1);
+            if (tid == 0) {
+              __threadfence();      // after the barrier: cumulative over the partial tile the group just wrote
+              const unsigned old = atomicAdd(&p.counters[tile], 1u);
+              s_last = (old == (unsigned)(c_last - c_first)) ? 1u : 0u;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            write = s_last != 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // s_last is rewritten at the next shared tile
+            if (tid == 0 && final_seg) QT_STAMP(6);
+            if (write) {
+              __threadfence();
+#pragma unroll
+              for (int m = 0; m < MB; m++) tot[m] = 0.0f;
+              for (int c = c_first; c <= c_last; c++) {
+                const int cslot = (qt_first_unit(p.total_units, gridDim.x, c) / G == tile) ? 0 : 1;
+                const float* theirs = p.partials + ((size_t)(c * 2 + cslot) * MB) * QT_TILE_N;
+#pragma unroll
+                for (int m = 0; m < MB; m++) tot[m] += __ldcg(theirs + m * QT_TILE_N + nl);
+              }
+              if (tid == 0) p.counters[tile] = 0;     // the workspace stays ready for the next launch
+              if (tid == 0 && final_seg) QT_STAMP(7);
+            }
+          }
+          if (write && n < p.N) {
+            const float bias = p.bias ? __ldg(p.bias + n) : 0.0f;
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+              float v = tot[m] * s_unit[m][0] * s_unit[m][1];
+              if (s_bad[m]) v = __int_as_float(0x7FC00000);
+              tot[m] = v + bias;
+            }
+            if (p.out_bf16) qt_store_rows<MB, true>(tot, p.activation, p.out, p.M, p.N, n);
+            else qt_store_rows<MB, false>(tot, p.activation, p.out, p.M, p.N, n);
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < MB; m++) tot[m] = 0.0f;
+      }
+      if (++g == G) { g = 0; tile++; }
+    }
+    if (tid == 0) QT_STAMP(3);
+    if (failed) { qt_fail(p, 4, 0); atomicExch(&s_failed, 1u); }
+  }
+  // every role ends here; TMEM is released by the warp that allocated it
+  tc_fence_before();
+  __syncthreads();
+  if (warp == QT_MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, QT_TMEM_COLS);
+  }
+  if (tid == 0) QT_STAMP(4);
+#undef QT_STAMP
+}
+
+// ---------------------------------------------------------------------------
+// planning and launch
+// ---------------------------------------------------------------------------
+static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
+static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
+static int qt_smem(int nb) {
+  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + (nb / 3) * QT_TILE_N * 4;
+}
+
+bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
+  auto no = [&](const char* m) { if (why) *why = m; return false; };
+  if (d.M < 1 || d.M > 16) return no("M must be in [1,16]");
+  if (d.has_zero_point) return no("zero points are handled by the generic kernel");
+  if (d.scale_layout == CB_SCALE_REF) return no("reference [K, N/block] scales are handled by the generic kernel");
+  if (d.K < 16 || d.K % 16 != 0) return no("K must be a positive multiple of 16");
+  if (d.N < 16 || d.N % 16 != 0) return no("N must be a positive multiple of 16");
+  if (d.scale_layout == CB_SCALE_KGROUP && (d.block_size <= 0 || d.block_size % QT_UNIT_K != 0))
+    return no("K-group size must be a multiple of 128");
+  if (d.K > (1 << 30) || d.N > (1 << 30)) return no("dimension too large");
+  return true;
+}
+
+struct QtLayout {
+  int nb, mb, n_tiles, units_per_tile;
+  long long total_units;
+  size_t off_counters, off_rows, off_digits, counter_bytes, off_partials, off_stamps, total;
+};
+
+static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
+  QtLayout l;
+  l.nb = qt_nb(d.M);
+  l.mb = l.nb / 3;
+  l.n_tiles = (int)((d.N + QT_TILE_N - 1) / QT_TILE_N);
+  l.units_per_tile = (int)((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
+  l.total_units = (long long)l.n_tiles * l.units_per_tile;
+  l.off_counters = QT_HEADER;
+  l.off_rows = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
+  l.off_digits = l.off_rows + 256;                             // 16 exponents + 16 flags
+  l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
+  l.off_partials = l.counter_bytes;
+  l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
+  l.total = l.off_stamps + (size_t)blocks * 8 * 8;
+  return l;
+}
+
+int qdense_decode_tc_plan(cb_plan* p) {
+  const cb_qdense_desc& d = p->qd;
+  const long long units = ((d.N + QT_TILE_N - 1) / QT_TILE_N) * ((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
+  p->blocks = (int)std::min<long long>(p->n_sm, units);
+  const QtLayout l = qt_layout(d, p->blocks);
+  p->threads = QT_THREADS;
+  p->dyn_smem = qt_smem(l.nb);
+  p->counter_bytes = l.counter_bytes;
+  p->workspace_bytes = l.total;
+  p->has_status = true;
+  p->name = std::string("qdense_decode_tc_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + "_n" + std::to_string(l.nb) +
+            (d.w_dtype == CB_U8 ? "_u8" : "_i8");
+  return CB_OK;
+}
+
+// bytes == 1: a byte matrix in 128-byte swizzled tiles; bytes == 4: rows of floats, not swizzled
+static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0, uint64_t d1, uint32_t b0, uint32_t b1) {
+  encode_tiled_fn enc = tensor_map_encoder();
+  if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {d0, d1};
+  cuuint64_t strides[1] = {d0 * (uint64_t)bytes};
+  cuuint32_t box[2] = {b0, b1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr),
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   bytes == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return CB_OK;
+}
+
+template <int NB>
+static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const QtParams& prm, bool overlap, cudaStream_t s) {
+  static std::atomic<bool> configured[64];
+  if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB)));
+    if (p->dev < 64) configured[p->dev].store(true, std::memory_order_release);
+  }
+  // programmatic dependent launch: this grid may be scheduled while the digit kernel still runs
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)p->blocks);
+  cfg.blockDim = dim3(QT_THREADS);
+  cfg.dynamicSmemBytes = (size_t)qt_smem(NB);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, prm));
+  return CB_OK;
+}
+
+int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const cb_qdense_desc& d = p->qd;
+  if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
+  const QtLayout l = qt_layout(d, p->blocks);
+  uint8_t* w8 = (uint8_t*)ws;
+  int* row_exp = (int*)(w8 + l.off_rows);
+  unsigned* row_bad = (unsigned*)(w8 + l.off_rows + 64);
+  int8_t* digits = (int8_t*)(w8 + l.off_digits);
+
+  // timing diagnosis only: CB_QDENSE_DEBUG_SKIP=4 leaves out the digit kernel, =5 the main kernel;
+  // CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
+  const char* env_skip = getenv("CB_QDENSE_DEBUG_SKIP");
+  const char* env_stamps = getenv("CB_QDENSE_DEBUG_STAMPS");
+  const int skip = env_skip ? env_skip[0] - '0' : 0;
+  if (skip == 4) {
+  } else if (d.x_dtype == CB_BF16)
+    qdense_xdigits_kernel<__nv_bfloat16><<<(unsigned)d.M, QX_THREADS, 0, s>>>((const __nv_bfloat16*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad);
+  else
+    qdense_xdigits_kernel<float><<<(unsigned)d.M, QX_THREADS, 0, s>>>((const float*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad);
+  CB_CUDA(cudaGetLastError());
+
+  CUtensorMap tw, tx, ts;
+  const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
+  CB_TRY(qt_encode_2d(&tw, in[1], 1, (uint64_t)d.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
+  CB_TRY(qt_encode_2d(&tx, digits, 1, (uint64_t)d.K, (uint64_t)l.nb, QT_UNIT_K, (uint32_t)l.nb));
+  CB_TRY(qt_encode_2d(&ts, in[2], 4, (uint64_t)d.N, scale_rows, QT_TILE_N, 1));
+  QtParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.scales = (const float*)in[2];
+  prm.bias = d.has_bias ? (const float*)in[3] : nullptr;
+  prm.out = out[0];
+  prm.status = (unsigned*)w8;
+  prm.counters = (unsigned*)(w8 + l.off_counters);
+  prm.row_exp = row_exp;
+  prm.row_bad = row_bad;
+  prm.partials = (float*)(w8 + l.off_partials);
+  prm.M = (int)d.M; prm.K = (int)d.K; prm.N = (int)d.N;
+  prm.n_tiles = l.n_tiles;
+  prm.units_per_tile = l.units_per_tile;
+  prm.total_units = l.total_units;
+  prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
+  prm.activation = d.activation;
+  prm.out_bf16 = d.x_dtype == CB_BF16 ? 1 : 0;
+  prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
+  prm.debug_no_mma = (skip == 6 || skip == 7) ? 1 : 0;
+  prm.debug_linear = skip == 7 ? 1 : 0;
+  if (skip == 7) CB_TRY(qt_encode_2d(&tw, in[1], 1, 128, (uint64_t)(d.N * d.K / 128), 128, 128));
+  if (skip == 5) return CB_OK;
+  prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
+  switch (l.nb) {
+    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, skip != 4, s);
+    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, skip != 4, s);
+    default: return qt_launch_t<48>(p, tw, tx, ts, prm, skip != 4, s);
+  }
+}
+
+}  // namespace cb

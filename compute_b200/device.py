@@ -21,7 +21,7 @@ NP_CARRIER = {BOOL: np.bool_, I8: np.int8, U8: np.uint8, I16: np.int16, U16: np.
 
 ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
 SCALE_REF, SCALE_CHANNEL, SCALE_KGROUP = range(3)
-QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL = range(4)
+QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL, QDENSE_DECODE_TC = range(5)
 DOT_AUTO, DOT_GENERIC, DOT_TCGEN05 = range(3)
 SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH = range(3)
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1

@@ -91,7 +91,8 @@ typedef enum {
   CB_QDENSE_AUTO = 0,
   CB_QDENSE_GENERIC = 1,    /* CUDA-core kernel in the reference's (m,k,n) summation order       */
   CB_QDENSE_DECODE_MMA = 2, /* M <= 16 stream-K kernel: cp.async-staged int8 tiles, f16 mma, f32 acc */
-  CB_QDENSE_PREFILL = 3     /* large-M tensor-core kernel                                        */
+  CB_QDENSE_PREFILL = 3,    /* M > 16: weights expanded to bf16 planes, tcgen05 GEMM, fused epilogue */
+  CB_QDENSE_DECODE_TC = 4   /* M <= 16: TMA-fed tcgen05 kind::i8 on the raw weight bytes, x as int8 digits */
 } cb_qdense_variant;
 
 typedef struct {

@@ -35,8 +35,12 @@ def test_library_exports_every_declared_symbol():
 
 def test_plans_select_kernels_by_shape_and_dtype():
     p = dv.Plan.qdense(1, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, activation=dv.ACT_SILU)
-    assert p.kernel_name == "qdense_decode_bf16_m8_i8" and p.workspace_bytes > 0
-    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_m16_i8")
+    assert p.kernel_name == "qdense_decode_tc_bf16_n16_i8" and p.workspace_bytes > 0
+    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n48_i8")
+    # K groups finer than the 128-row tensor-core unit stay on the mma.sync decode kernel; M > 16 is prefill
+    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 64).kernel_name == "qdense_decode_bf16_m16_i8"
+    assert dv.Plan.qdense(2048, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_CHANNEL).kernel_name == "qdense_prefill_tcgen05_bf16_i8"
+    assert dv.Plan.dot(1, 4096, 4096, 4096, dv.F32).kernel_name == "gemm_tcgen05_Float32_Float32_nn"
     # the reference's own scale layout and zero points go to the reference-order kernel
     assert dv.Plan.qdense(1, 4096, 14336, dv.F32, dv.I8, dv.SCALE_REF, 128).kernel_name.startswith("qdense_generic")
     assert dv.Plan.qdense(4, 64, 64, dv.F32, dv.U8, dv.SCALE_CHANNEL, has_zero_point=True).kernel_name == "qdense_generic_f32_u8"
