@@ -397,7 +397,8 @@ def main():
                          "per-GPU weights of a step fit in L2 at this shard count; launches may be served from L2",
                    "kernel": plan.kernel_name, "grid": [plan.blocks, plan.threads], "dyn_smem": plan.dyn_smem},
         "tflops": flops_step * args.steps / (ms * 1e-3) / 1e12,
-        "gpu_launches": LAYERS * args.steps,
+        # the tensor-core decode plan launches two kernels per call: the activation digit kernel and the main kernel
+        "gpu_launches": LAYERS * args.steps * (2 if plan.kernel_name.startswith("qdense_decode_tc") else 1),
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * x_stride, "d2h_bytes_per_step": LAYERS * y_stride,
                 "ms_per_step": ms_e2e / args.steps,
                 "note": "activations H2D from pinned memory and results D2H every step; weights resident as device buffers"},

@@ -17,9 +17,11 @@
 //   qdense_xdigits_kernel   x -> digits + per-row exponents (one CTA per row, a few microseconds)
 //   qdense_decode_tc_kernel persistent, one CTA per SM over a balanced contiguous range of
 //                           (n tile, k unit) pairs:
-//       warp 8   TMA producer: W tile + digit tile + the unit's 128 scales into an 8-stage ring
-//                (the first weight tiles are requested before the digit kernel has finished)
-//       warp 9   MMA issuer: 4 MMAs (K = 32) per unit into one of 8 TMEM accumulators
+//       warp 8   TMA producer: weight tiles into an 8-stage ring (the first ones are requested
+//                before the digit kernel has finished)
+//       warp 10  TMA producer: the digit tile and the 128 scales of each unit
+//       warps 9, 11  MMA issuers on alternate units: 4 MMAs (K = 32) per unit into one of 8 TMEM
+//                accumulators
 //       warps 0-7 epilogue as above, two groups of four warps on alternate units; a tile whose
 //                units are split between CTAs is finished by the CTA that arrives last, summing
 //                the parked partial tiles in CTA order (deterministic: the result does not
@@ -40,8 +42,8 @@ constexpr int QT_TILE_N = 128;
 constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
 constexpr int QT_STAGES = 8;
-constexpr int QT_THREADS = 320;                       // warps 0-7 epilogue, 8 TMA, 9 MMA
-constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9;
+constexpr int QT_THREADS = 384;                       // warps 0-7 epilogue, 8 weight TMA, 9 and 11 MMA, 10 side TMA
+constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;
 constexpr int QT_TMEM_COLS = 512;
 constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
@@ -66,6 +68,8 @@ struct QtParams {
   unsigned long long* dbg;  // timing diagnosis only: 8 time stamps per CTA, or null
   int debug_no_mma;         // timing diagnosis only: the MMA warp issues commits but no MMA
   int debug_linear;         // timing diagnosis only: weight tiles are read as contiguous 16 KB blocks
+  int debug_no_epi;         // timing diagnosis only: the epilogue releases accumulators without reading them
+  int debug_w_only;         // timing diagnosis only: only the weight tiles are loaded
 };
 
 // ---------------------------------------------------------------------------
@@ -89,9 +93,12 @@ template <typename XT>
 __global__ void __launch_bounds__(QX_THREADS)
 qdense_xdigits_kernel(const XT* __restrict__ x, int K, int MB, int8_t* __restrict__ digits, int* __restrict__ row_exp,
                       unsigned* __restrict__ row_bad) {
-  // the kernel that consumes the digits may start its own set-up now; it waits for this grid
-  // to finish before it reads them
+  // The kernel that consumes the digits may start its own set-up now; it waits for this grid to
+  // finish before it reads them.  This grid in turn may have been scheduled while the kernel
+  // before it in the stream (which may produce x, and may still read the digit buffer) was
+  // running: it waits for that kernel to finish before it touches either.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float s_max[QX_THREADS / 32];
   __shared__ unsigned s_bad[QX_THREADS / 32];
   const int m = blockIdx.x, tid = threadIdx.x;
@@ -208,27 +215,35 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int MB = NB / 3;
   constexpr int X_BYTES = NB * QT_UNIT_K;
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
-  constexpr int NBUF = 8;
+  constexpr int NBUF = QT_STAGES;
   static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
   static_assert(QT_SC_SLOTS >= QT_STAGES + NBUF, "a scale slot must outlive its stage and its accumulator");
   extern __shared__ uint8_t qt_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qt_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + QT_STAGES * STAGE_BYTES);
+  // Stage s and accumulator s travel together (QT_STAGES == NBUF): a unit's stage is refilled once
+  // the epilogue has read its accumulator, so the MMA thread waits on one barrier per unit and
+  // commits once, which keeps its serial loop short.
   uint64_t* full = bars;                       // [QT_STAGES] TMA -> MMA
-  uint64_t* empty = bars + QT_STAGES;          // [QT_STAGES] MMA -> TMA
-  uint64_t* acc_full = bars + 2 * QT_STAGES;   // [NBUF] MMA -> epilogue
-  uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> MMA
+  uint64_t* acc_full = bars + QT_STAGES;       // [NBUF] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> TMA producers
   float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
   float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
   __shared__ unsigned s_last;
+  __shared__ long long s_trace[32][6];    // timing diagnosis only (one CTA, when stamps are on)
+#define QT_TRACE(it, j) do { if (p.dbg && blockIdx.x == 74 && (it) < 32) s_trace[it][j] = clock64(); } while (0)
   __shared__ float s_unit[16][2];     // unit[m] as two normal factors
   __shared__ unsigned s_bad[16];
 
+  // Lets a following digit kernel of this library be scheduled early (it waits for this grid to
+  // finish before it reads or writes anything); kernels launched the ordinary way are unaffected.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #define QT_STAMP(i) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 8 + (i)] = global_ns(); } while (0)
   if (tid == 0) QT_STAMP(0);
+  if (tid == 0 && p.dbg && blockIdx.x == 74) { p.dbg[(size_t)gridDim.x * 8 + 194] = clock64(); p.dbg[(size_t)gridDim.x * 8 + 195] = global_ns(); }
   const int G = p.units_per_tile;
   const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
   const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
@@ -239,13 +254,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   // launch the first QT_STAGES tiles are already in flight while that kernel still runs.
   int early = 0;
   if (warp == QT_TMA_WARP && lane == 0) {
-    for (int s = 0; s < QT_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < QT_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
     fence_barrier_init();
     prefetch_tensormap(&tmap_w);
     early = n_units < QT_STAGES ? n_units : QT_STAGES;
     int tile = tile0, g = g0;
     for (int it = 0; it < early; it++) {
-      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES);
+      mbar_expect_tx(&full[it], p.debug_w_only ? QT_W_BYTES : STAGE_BYTES + QT_SC_BYTES);
       if (p.debug_linear) tma_load_2d(base + it * STAGE_BYTES, &tmap_w, 0, (int)((u0 + it) * 128), &full[it]);
       else tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
       if (++g == G) { g = 0; tile++; }
@@ -254,7 +269,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     prefetch_tensormap(&tmap_s);
   }
   if (tid == 0) {
-    for (int b = 0; b < NBUF; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < NBUF; b++) mbar_init(&acc_full[b], 1);
     s_failed = 0;
     fence_barrier_init();
   }
@@ -274,48 +289,72 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   if (tid == 0) QT_STAMP(1);
 
   if (warp == QT_TMA_WARP) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ TMA producer: weights ----------------------
+    // One thread can issue a copy roughly every 50 ns and a unit needs three, so the weight
+    // tiles and the two small side loads have an issuing thread each (in different warps).
     if (lane == 0) {
       int tile = tile0, g = g0;
-      for (int it = 0; it < n_units && !*(volatile unsigned*)&s_failed; it++) {
-        const int s = it % QT_STAGES;
-        uint8_t* sw = base + s * STAGE_BYTES;
-
+      for (int it = 0; it < n_units; it++) {
         if (it >= early) {
-          if (!mbar_wait(&empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
-          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
-          if (p.debug_linear) tma_load_2d(sw, &tmap_w, 0, (int)((u0 + it) * 128), &full[s]);
-          else tma_load_2d(sw, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
+          const int s = it % QT_STAGES;
+          if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          mbar_expect_tx(&full[s], p.debug_w_only ? QT_W_BYTES : STAGE_BYTES + QT_SC_BYTES);
+          if (p.debug_linear) tma_load_2d(base + s * STAGE_BYTES, &tmap_w, 0, (int)((u0 + it) * 128), &full[s]);
+          else tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
         }
-        // The 128 scales of the unit ride along: their slot is reused QT_SC_SLOTS units later, by
-        // which time the epilogue of this unit has read them (it does so before it releases the
-        // accumulator, which the MMA of unit it+8 waits for, which this loop's unit it+16 waits for).
-        const int srow = p.scale_group ? (g * QT_UNIT_K) / p.scale_group : 0;
-        tma_load_2d(sw + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);              // [NB rows][128 k]
-        tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+        QT_TRACE(it, 0);
         if (++g == G) { g = 0; tile++; }
       }
     }
-  } else if (warp == QT_MMA_WARP) {
-    // ------------------------------ MMA issuer --------------------------------
+  } else if (warp == QT_SIDE_WARP) {
+    // ------------------------------ TMA producer: digits and scales ------------
+    // Their bytes count towards the same stage barrier; the weight producer announces the total.
+    // The 128 scales of a unit sit in a slot that is reused QT_SC_SLOTS units later, by which time
+    // the epilogue of this unit has read them (it does so before it releases the accumulator,
+    // which the MMA of unit it+8 waits for, which the stage reuse of unit it+16 waits for).
+    if (lane == 0 && !p.debug_w_only) {
+      const int gpr = p.scale_group ? p.scale_group / QT_UNIT_K : 0;    // units per scale row
+      int tile = tile0, g = g0;
+      int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
+      for (int it = 0; it < n_units; it++) {
+        const int s = it % QT_STAGES;
+        if (it >= QT_STAGES) {
+          if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        }
+        tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
+        tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+        QT_TRACE(it, 1);
+        if (gpr && ++sub == gpr) { sub = 0; srow++; }
+        if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
+      }
+    }
+  } else if (warp == QT_MMA_WARP || warp == QT_MMA2_WARP) {
+    // ------------------------------ MMA issuers -------------------------------
+    // Issuing a unit (one wait, four MMAs, one commit) costs a single thread several hundred
+    // cycles, about what the unit's bytes take to arrive: two threads take alternate units.
     if (lane == 0) {
-      for (int it = 0; it < n_units && !*(volatile unsigned*)&s_failed; it++) {
-        const int s = it % QT_STAGES, buf = it % NBUF;
-        if (it >= NBUF && !mbar_wait(&acc_empty[buf], (uint32_t)((it / NBUF - 1) & 1))) { qt_fail(p, 2, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+      const int mine = warp == QT_MMA_WARP ? 0 : 1;
+      // W: MN-major, 128 n bytes per k row, 8-row groups 1024 bytes apart, 32 k rows (4096 bytes) per MMA.
+      // digits: K-major, 128 k bytes per row, 8-row groups 1024 bytes apart, 32 bytes per MMA.
+      // The address field of a descriptor counts 16-byte units, so stepping is an add.
+      const uint64_t da0 = smem_desc_sw128(smem_u32(base), QT_W_BYTES, 1024);
+      const uint64_t db0 = smem_desc_sw128(smem_u32(base) + QT_W_BYTES, 16, 1024);
+      const uint32_t idesc = p.idesc;
+      const bool no_mma = p.debug_no_mma != 0;
+      for (int it = mine; it < n_units; it += 2) {
+        const int s = it % QT_STAGES;
         if (!mbar_wait(&full[s], (uint32_t)((it / QT_STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
         tc_fence_after();
-        const uint32_t sw = smem_u32(base + s * STAGE_BYTES), sx = sw + QT_W_BYTES;
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NB);
+        QT_TRACE(it, 2);
+        const uint64_t da = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(s * NB);
+        if (!no_mma) {
 #pragma unroll
-        for (int j = 0; j < QT_UNIT_K / 32; j++) {
-          // W: MN-major, 128 n bytes per k row, 8-row groups 1024 bytes apart, 32 k rows per MMA
-          const uint64_t da = smem_desc_sw128(sw + j * 32 * 128, QT_W_BYTES, 1024);
-          // digits: K-major, 128 k bytes per row, 8-row groups 1024 bytes apart, 32 bytes per MMA
-          const uint64_t db = smem_desc_sw128(sx + j * 32, 16, 1024);
-          if (!p.debug_no_mma) umma_i8(d_tmem, da, db, p.idesc, j > 0 ? 1u : 0u);
+          for (int j = 0; j < QT_UNIT_K / 32; j++)
+            umma_i8(d_tmem, da + (uint64_t)((j * 32 * 128) >> 4), db + (uint64_t)((j * 32) >> 4), idesc, j > 0 ? 1u : 0u);
         }
-        umma_commit(&empty[s]);
-        umma_commit(&acc_full[buf]);
+        umma_commit(&acc_full[s]);
+        QT_TRACE(it, 3);
       }
     }
   } else {
@@ -336,9 +375,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       // After a timeout this group stops touching the pipeline but keeps walking the units, so that
       // the barriers below still see every thread (the status word reports the failure).
       if ((it & 1) == grp && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
-      if ((it & 1) == grp && !failed) {
+      if ((it & 1) == grp && !failed && p.debug_no_epi) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[it % NBUF]);
+      } else if ((it & 1) == grp && !failed) {
         const int buf = it % NBUF;
         tc_fence_after();
+        if (quarter == 0 && lane == 0) QT_TRACE(it, 4);
         uint32_t acc[NB];
 #pragma unroll
         for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
@@ -355,6 +398,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           const float f2 = __uint_as_float(acc[2 * MB + m] + 0x4B400000u) - 12582912.0f;
           tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)), sc, tot[m]);
         }
+        if (quarter == 0 && lane == 0) QT_TRACE(it, 5);
       }
       const bool tile_ends = (g == G - 1);
       const bool final_seg = it + 1 == n_units;
@@ -438,6 +482,12 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     tmem_dealloc(tmem_base, QT_TMEM_COLS);
   }
   if (tid == 0) QT_STAMP(4);
+  if (p.dbg && blockIdx.x == 74) {
+    __syncthreads();
+    for (int i = tid; i < 32 * 6; i += QT_THREADS) p.dbg[(size_t)gridDim.x * 8 + i] = (unsigned long long)s_trace[i / 6][i % 6];
+    if (tid == 0) { p.dbg[(size_t)gridDim.x * 8 + 192] = clock64(); p.dbg[(size_t)gridDim.x * 8 + 193] = global_ns(); }
+  }
+#undef QT_TRACE
 #undef QT_STAMP
 }
 
@@ -482,7 +532,7 @@ static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
   l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
   l.off_partials = l.counter_bytes;
   l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
-  l.total = l.off_stamps + (size_t)blocks * 8 * 8;
+  l.total = l.off_stamps + (size_t)blocks * 8 * 8 + 256 * 8;
   return l;
 }
 
@@ -555,12 +605,22 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   const char* env_skip = getenv("CB_QDENSE_DEBUG_SKIP");
   const char* env_stamps = getenv("CB_QDENSE_DEBUG_STAMPS");
   const int skip = env_skip ? env_skip[0] - '0' : 0;
-  if (skip == 4) {
-  } else if (d.x_dtype == CB_BF16)
-    qdense_xdigits_kernel<__nv_bfloat16><<<(unsigned)d.M, QX_THREADS, 0, s>>>((const __nv_bfloat16*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad);
-  else
-    qdense_xdigits_kernel<float><<<(unsigned)d.M, QX_THREADS, 0, s>>>((const float*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad);
-  CB_CUDA(cudaGetLastError());
+  if (skip != 4) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)d.M);
+    cfg.blockDim = dim3(QX_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (d.x_dtype == CB_BF16)
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad));
+    else
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad));
+  }
 
   CUtensorMap tw, tx, ts;
   const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
@@ -585,7 +645,9 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   prm.activation = d.activation;
   prm.out_bf16 = d.x_dtype == CB_BF16 ? 1 : 0;
   prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
-  prm.debug_no_mma = (skip == 6 || skip == 7) ? 1 : 0;
+  prm.debug_no_mma = (skip >= 6 && skip <= 9) ? 1 : 0;
+  prm.debug_no_epi = (skip == 8 || skip == 9) ? 1 : 0;
+  prm.debug_w_only = skip == 9 ? 1 : 0;
   prm.debug_linear = skip == 7 ? 1 : 0;
   if (skip == 7) CB_TRY(qt_encode_2d(&tw, in[1], 1, 128, (uint64_t)(d.N * d.K / 128), 128, 128));
   if (skip == 5) return CB_OK;
