@@ -1,0 +1,98 @@
+"""Runs one kernel of the library on a named synthetic case and prints its device time.
+
+    python -m compute_b200.run_case gemm --dtype bf16 --b 1 --m 4096 --n 4096 --k 4096
+    python -m compute_b200.run_case sdpa --b 8 --hq 32 --hkv 8 --s 2048 --d 128 --causal
+    python -m compute_b200.run_case qdense --m 16            # decode (M <= 16) or prefill (M > 16)
+
+A small stand-alone driver for timing or profiling a single plan (inputs are seeded random
+data resident on the device; time is taken with CUDA events on the launching stream).  The
+profile summaries of this repository were captured from these commands.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+from . import device as dv
+
+
+def _bf16(rng, n, sigma=0.05):
+    a = (rng.standard_normal(n, dtype=np.float32) * sigma).view(np.uint32) >> 16
+    return a.astype(np.uint16)
+
+
+def _time(plan, ins, outs, dev, stream, reps, warmup):
+    ws = plan.new_workspace()
+    e0, e1 = dv.Event(dev), dv.Event(dev)
+    for it in range(reps + warmup):
+        if it == warmup:
+            e0.record(stream)
+        plan.launch(ins, outs, ws.ptr if ws else None, stream)
+    e1.record(stream)
+    stream.sync()
+    plan.check_status(ws.ptr if ws else None)
+    return e0.elapsed_ms(e1) * 1e3 / reps
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=["gemm", "sdpa", "qdense"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--b", type=int, default=1)
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--s", type=int, default=2048)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--layout", default="kgroup", choices=["channel", "kgroup"])
+    ap.add_argument("--group", type=int, default=128)
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dev", type=int, default=0)
+    a = ap.parse_args()
+    dev = a.dev
+    dv.init()
+    stream = dv.Stream(dev)
+    rng = np.random.default_rng(1)
+    out = {"case": a.case}
+    if a.case == "gemm":
+        code = dv.BF16 if a.dtype == "bf16" else dv.F32
+        size = 2 if a.dtype == "bf16" else 4
+        mk = (lambda n: _bf16(rng, n)) if a.dtype == "bf16" else (lambda n: rng.standard_normal(n, dtype=np.float32) * np.float32(0.05))
+        lhs = dv.DeviceMem.from_numpy(mk(a.b * a.m * a.k), dev)
+        rhs = dv.DeviceMem.from_numpy(mk(a.b * a.k * a.n), dev)
+        res = dv.DeviceMem(a.b * a.m * a.n * size, dev)
+        plan = dv.Plan.dot(a.b, a.m, a.n, a.k, code, dev=dev)
+        us = _time(plan, [lhs.ptr, rhs.ptr], [res.ptr], dev, stream, a.reps, a.warmup)
+        out.update(kernel=plan.kernel_name, us=us, tflops=2.0 * a.b * a.m * a.n * a.k / us / 1e6)
+    elif a.case == "sdpa":
+        q = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hq * a.s * a.d, 1.0), dev)
+        k = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
+        v = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
+        o = dv.DeviceMem(a.b * a.hq * a.s * a.d * 2, dev)
+        plan = dv.Plan.sdpa(a.b, a.hq, a.hkv, a.s, a.s, a.d, dv.BF16, causal=a.causal, dev=dev)
+        us = _time(plan, [q.ptr, k.ptr, v.ptr], [o.ptr], dev, stream, a.reps, a.warmup)
+        pairs = a.s * (a.s + 1) / 2 if a.causal else a.s * a.s
+        out.update(kernel=plan.kernel_name, us=us, tflops=4.0 * a.b * a.hq * a.d * pairs / us / 1e6)
+    else:
+        K, N = a.k, a.n if a.n != 4096 else 14336
+        code = dv.BF16 if a.dtype == "bf16" else dv.F32
+        x = dv.DeviceMem.from_numpy(_bf16(rng, a.m * K, 1.0) if a.dtype == "bf16" else rng.standard_normal(a.m * K, dtype=np.float32), dev)
+        w = dv.DeviceMem.from_numpy(rng.integers(-127, 128, size=K * N, dtype=np.int8), dev)
+        rows = 1 if a.layout == "channel" else -(-K // a.group)
+        sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=rows * N).astype(np.float32), dev)
+        y = dv.DeviceMem(a.m * N * (2 if a.dtype == "bf16" else 4), dev)
+        plan = dv.Plan.qdense(a.m, K, N, code, dv.I8, dv.SCALE_CHANNEL if a.layout == "channel" else dv.SCALE_KGROUP,
+                              a.group, False, False, dv.ACT_SILU, dev=dev)
+        us = _time(plan, [x.ptr, w.ptr, sc.ptr], [y.ptr], dev, stream, a.reps, a.warmup)
+        out.update(kernel=plan.kernel_name, us=us, weight_GBps=K * N / us / 1e3, tflops=2.0 * a.m * K * N / us / 1e6)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
