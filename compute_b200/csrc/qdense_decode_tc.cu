@@ -66,10 +66,6 @@ struct QtParams {
   int out_bf16;
   uint32_t idesc;
   unsigned long long* dbg;  // timing diagnosis only: 8 time stamps per CTA, or null
-  int debug_no_mma;         // timing diagnosis only: the MMA warp issues commits but no MMA
-  int debug_linear;         // timing diagnosis only: weight tiles are read as contiguous 16 KB blocks
-  int debug_no_epi;         // timing diagnosis only: the epilogue releases accumulators without reading them
-  int debug_w_only;         // timing diagnosis only: only the weight tiles are loaded
 };
 
 // ---------------------------------------------------------------------------
@@ -232,8 +228,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
   __shared__ unsigned s_last;
-  __shared__ long long s_trace[32][6];    // timing diagnosis only (one CTA, when stamps are on)
-#define QT_TRACE(it, j) do { if (p.dbg && blockIdx.x == 74 && (it) < 32) s_trace[it][j] = clock64(); } while (0)
   __shared__ float s_unit[16][2];     // unit[m] as two normal factors
   __shared__ unsigned s_bad[16];
 
@@ -243,7 +237,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #define QT_STAMP(i) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 8 + (i)] = global_ns(); } while (0)
   if (tid == 0) QT_STAMP(0);
-  if (tid == 0 && p.dbg && blockIdx.x == 74) { p.dbg[(size_t)gridDim.x * 8 + 194] = clock64(); p.dbg[(size_t)gridDim.x * 8 + 195] = global_ns(); }
   const int G = p.units_per_tile;
   const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
   const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
@@ -260,9 +253,8 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     early = n_units < QT_STAGES ? n_units : QT_STAGES;
     int tile = tile0, g = g0;
     for (int it = 0; it < early; it++) {
-      mbar_expect_tx(&full[it], p.debug_w_only ? QT_W_BYTES : STAGE_BYTES + QT_SC_BYTES);
-      if (p.debug_linear) tma_load_2d(base + it * STAGE_BYTES, &tmap_w, 0, (int)((u0 + it) * 128), &full[it]);
-      else tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
+      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES);
+      tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
       if (++g == G) { g = 0; tile++; }
     }
     prefetch_tensormap(&tmap_x);
@@ -274,18 +266,21 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     fence_barrier_init();
   }
   if (warp == QT_MMA_WARP) tmem_alloc(&s_tmem, QT_TMEM_COLS);
-  // from here on the outputs of the digit kernel are read
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (tid < 16) {
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+  // Everything above (and the weight stream) overlaps the kernels before this one in the stream.
+  // The threads that read what those kernels produce (digits, row exponents) or write what they may
+  // still use (output, workspace) wait for them here; the weight producer and the MMA issuers,
+  // which touch only weights, shared memory and tensor memory, do not.
+  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid < 16) {        // read long before the first tile is finished (shared-memory barriers lie in between)
     const int e = p.row_exp[tid], e1 = e / 2, e2 = e - e1;       // e lies in [-169, 108]
     s_unit[tid][0] = __int_as_float((127 + e1) << 23);
     s_unit[tid][1] = __int_as_float((127 + e2) << 23);
     s_bad[tid] = p.row_bad[tid];
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = s_tmem;
   if (tid == 0) QT_STAMP(1);
 
   if (warp == QT_TMA_WARP) {
@@ -298,11 +293,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (it >= early) {
           const int s = it % QT_STAGES;
           if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
-          mbar_expect_tx(&full[s], p.debug_w_only ? QT_W_BYTES : STAGE_BYTES + QT_SC_BYTES);
-          if (p.debug_linear) tma_load_2d(base + s * STAGE_BYTES, &tmap_w, 0, (int)((u0 + it) * 128), &full[s]);
-          else tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
+          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
+          tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
         }
-        QT_TRACE(it, 0);
         if (++g == G) { g = 0; tile++; }
       }
     }
@@ -312,7 +305,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     // The 128 scales of a unit sit in a slot that is reused QT_SC_SLOTS units later, by which time
     // the epilogue of this unit has read them (it does so before it releases the accumulator,
     // which the MMA of unit it+8 waits for, which the stage reuse of unit it+16 waits for).
-    if (lane == 0 && !p.debug_w_only) {
+    if (lane == 0) {
       const int gpr = p.scale_group ? p.scale_group / QT_UNIT_K : 0;    // units per scale row
       int tile = tile0, g = g0;
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
@@ -323,7 +316,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
         tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
-        QT_TRACE(it, 1);
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
       }
@@ -340,21 +332,16 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const uint64_t da0 = smem_desc_sw128(smem_u32(base), QT_W_BYTES, 1024);
       const uint64_t db0 = smem_desc_sw128(smem_u32(base) + QT_W_BYTES, 16, 1024);
       const uint32_t idesc = p.idesc;
-      const bool no_mma = p.debug_no_mma != 0;
       for (int it = mine; it < n_units; it += 2) {
         const int s = it % QT_STAGES;
         if (!mbar_wait(&full[s], (uint32_t)((it / QT_STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
         tc_fence_after();
-        QT_TRACE(it, 2);
         const uint64_t da = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
         const uint32_t d_tmem = tmem_base + (uint32_t)(s * NB);
-        if (!no_mma) {
 #pragma unroll
-          for (int j = 0; j < QT_UNIT_K / 32; j++)
-            umma_i8(d_tmem, da + (uint64_t)((j * 32 * 128) >> 4), db + (uint64_t)((j * 32) >> 4), idesc, j > 0 ? 1u : 0u);
-        }
+        for (int j = 0; j < QT_UNIT_K / 32; j++)
+          umma_i8(d_tmem, da + (uint64_t)((j * 32 * 128) >> 4), db + (uint64_t)((j * 32) >> 4), idesc, j > 0 ? 1u : 0u);
         umma_commit(&acc_full[s]);
-        QT_TRACE(it, 3);
       }
     }
   } else {
@@ -375,13 +362,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       // After a timeout this group stops touching the pipeline but keeps walking the units, so that
       // the barriers below still see every thread (the status word reports the failure).
       if ((it & 1) == grp && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
-      if ((it & 1) == grp && !failed && p.debug_no_epi) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[it % NBUF]);
-      } else if ((it & 1) == grp && !failed) {
+      if ((it & 1) == grp && !failed) {
         const int buf = it % NBUF;
         tc_fence_after();
-        if (quarter == 0 && lane == 0) QT_TRACE(it, 4);
         uint32_t acc[NB];
 #pragma unroll
         for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
@@ -398,7 +381,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           const float f2 = __uint_as_float(acc[2 * MB + m] + 0x4B400000u) - 12582912.0f;
           tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)), sc, tot[m]);
         }
-        if (quarter == 0 && lane == 0) QT_TRACE(it, 5);
       }
       const bool tile_ends = (g == G - 1);
       const bool final_seg = it + 1 == n_units;
@@ -443,11 +425,18 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
               __threadfence();
 #pragma unroll
               for (int m = 0; m < MB; m++) tot[m] = 0.0f;
-              for (int c = c_first; c <= c_last; c++) {
-                const int cslot = (qt_first_unit(p.total_units, gridDim.x, c) / G == tile) ? 0 : 1;
-                const float* theirs = p.partials + ((size_t)(c * 2 + cslot) * MB) * QT_TILE_N;
+              // two contributors per round, their loads in flight together; summed in CTA order
+              for (int c = c_first; c <= c_last; c += 2) {
+                const bool two = c + 1 <= c_last;
+                const int slot_a = (qt_first_unit(p.total_units, gridDim.x, c) / G == tile) ? 0 : 1;
+                const int slot_b = (two && qt_first_unit(p.total_units, gridDim.x, c + 1) / G == tile) ? 0 : 1;
+                const float* pa = p.partials + ((size_t)(c * 2 + slot_a) * MB) * QT_TILE_N + nl;
+                const float* pb = p.partials + ((size_t)((two ? c + 1 : c) * 2 + slot_b) * MB) * QT_TILE_N + nl;
+                float va[MB], vb[MB];
 #pragma unroll
-                for (int m = 0; m < MB; m++) tot[m] += __ldcg(theirs + m * QT_TILE_N + nl);
+                for (int m = 0; m < MB; m++) { va[m] = __ldcg(pa + m * QT_TILE_N); vb[m] = __ldcg(pb + m * QT_TILE_N); }
+#pragma unroll
+                for (int m = 0; m < MB; m++) { tot[m] += va[m]; if (two) tot[m] += vb[m]; }
               }
               if (tid == 0) p.counters[tile] = 0;     // the workspace stays ready for the next launch
               if (tid == 0 && final_seg) QT_STAMP(7);
@@ -482,12 +471,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     tmem_dealloc(tmem_base, QT_TMEM_COLS);
   }
   if (tid == 0) QT_STAMP(4);
-  if (p.dbg && blockIdx.x == 74) {
-    __syncthreads();
-    for (int i = tid; i < 32 * 6; i += QT_THREADS) p.dbg[(size_t)gridDim.x * 8 + i] = (unsigned long long)s_trace[i / 6][i % 6];
-    if (tid == 0) { p.dbg[(size_t)gridDim.x * 8 + 192] = clock64(); p.dbg[(size_t)gridDim.x * 8 + 193] = global_ns(); }
-  }
-#undef QT_TRACE
 #undef QT_STAMP
 }
 
@@ -532,7 +515,7 @@ static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
   l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
   l.off_partials = l.counter_bytes;
   l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
-  l.total = l.off_stamps + (size_t)blocks * 8 * 8 + 256 * 8;
+  l.total = l.off_stamps + (size_t)blocks * 8 * 8;
   return l;
 }
 
@@ -600,12 +583,9 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   unsigned* row_bad = (unsigned*)(w8 + l.off_rows + 64);
   int8_t* digits = (int8_t*)(w8 + l.off_digits);
 
-  // timing diagnosis only: CB_QDENSE_DEBUG_SKIP=4 leaves out the digit kernel, =5 the main kernel;
-  // CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
-  const char* env_skip = getenv("CB_QDENSE_DEBUG_SKIP");
+  // timing diagnosis only: CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
   const char* env_stamps = getenv("CB_QDENSE_DEBUG_STAMPS");
-  const int skip = env_skip ? env_skip[0] - '0' : 0;
-  if (skip != 4) {
+  {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)d.M);
@@ -645,17 +625,11 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   prm.activation = d.activation;
   prm.out_bf16 = d.x_dtype == CB_BF16 ? 1 : 0;
   prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
-  prm.debug_no_mma = (skip >= 6 && skip <= 9) ? 1 : 0;
-  prm.debug_no_epi = (skip == 8 || skip == 9) ? 1 : 0;
-  prm.debug_w_only = skip == 9 ? 1 : 0;
-  prm.debug_linear = skip == 7 ? 1 : 0;
-  if (skip == 7) CB_TRY(qt_encode_2d(&tw, in[1], 1, 128, (uint64_t)(d.N * d.K / 128), 128, 128));
-  if (skip == 5) return CB_OK;
   prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
   switch (l.nb) {
-    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, skip != 4, s);
-    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, skip != 4, s);
-    default: return qt_launch_t<48>(p, tw, tx, ts, prm, skip != 4, s);
+    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, true, s);
+    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, true, s);
+    default: return qt_launch_t<48>(p, tw, tx, ts, prm, true, s);
   }
 }
 

@@ -252,6 +252,24 @@ def test_prefill_llama_projection_full_size(layout, group):
     assert max_abs_normalised(orc.bf16_to_f32(dec), orc.bf16_to_f32(got[rows])) < 2.0 ** -7
 
 
+# ------------------------------------------------------------- dequantisation, bit for bit
+@pytest.mark.parametrize("variant,rows", [(dv.QDENSE_GENERIC, 16), (dv.QDENSE_DECODE_MMA, 16), (dv.QDENSE_DECODE_TC, 16),
+                                          (dv.QDENSE_PREFILL, 64)])
+@pytest.mark.parametrize("unsigned", [False, True])
+def test_dequantised_weights_are_bit_exact(variant, rows, unsigned):
+    """One-hot activations read the dequantised weights back through each kernel: out[m, n] = 1 * W[m, n] * s[n]
+    must equal float32(W) * s bit for bit (the integer -> float conversion and the scale product are exact
+    operations in every kernel's arithmetic)."""
+    K, N = 256, 384
+    _, w, s, _ = qdense_inputs(5, rows, K, N, scale_layout="channel", bias=False, unsigned=unsigned)
+    x = np.zeros((rows, K), np.float32)
+    pick = np.random.default_rng(6).choice(K, size=rows, replace=False)
+    x[np.arange(rows), pick] = 1.0
+    got = ops.quantized_dense(x, w, s, None, None, scale_layout=dv.SCALE_CHANNEL, variant=variant)
+    want = w[pick].astype(np.float32) * s[None, :]
+    assert np.array_equal(got, want)
+
+
 # ------------------------------------------------------------- validation / errors
 def test_validation_errors():
     x, w, s, b = qdense_inputs(1, 2, 32, 32, scale_layout="ref", block_size=1)
