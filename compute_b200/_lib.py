@@ -67,6 +67,7 @@ SIGNATURES = {
     "cb_stream_destroy": ([C.c_int, C.c_void_p], C.c_int),
     "cb_event_create": ([C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cb_event_record": ([C.c_int, C.c_void_p, C.c_void_p], C.c_int),
+    "cb_stream_wait_event": ([C.c_int, C.c_void_p, C.c_void_p], C.c_int),
     "cb_event_elapsed_ms": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_float)], C.c_int),
     "cb_event_destroy": ([C.c_int, C.c_void_p], C.c_int),
     "cb_plan_qdense": ([C.c_int, C.POINTER(QDenseDesc), C.POINTER(C.c_void_p)], C.c_int),

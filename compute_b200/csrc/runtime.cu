@@ -218,6 +218,12 @@ int cb_event_record(int dev, cb_event ev, cb_stream stream) {
   return CB_OK;
 }
 
+int cb_stream_wait_event(int dev, cb_stream stream, cb_event ev) {
+  CB_TRY(set_device(dev));
+  CB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0));
+  return CB_OK;
+}
+
 int cb_event_elapsed_ms(cb_event start, cb_event stop, float* ms) {
   clear_error();
   CB_CUDA(cudaEventSynchronize((cudaEvent_t)stop));

@@ -57,6 +57,10 @@ class Stream:
     def sync(self) -> None:
         check(_lib.load().cb_stream_sync(self.dev, self.handle))
 
+    def wait_event(self, event: "Event") -> None:
+        """Work submitted to this stream from now on starts after `event` has completed."""
+        check(_lib.load().cb_stream_wait_event(self.dev, self.handle, event.handle))
+
     def close(self) -> None:
         if self.handle:
             _lib.load().cb_stream_destroy(self.dev, self.handle)

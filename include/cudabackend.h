@@ -72,6 +72,8 @@ int cb_stream_destroy(int dev, cb_stream stream);
 typedef void* cb_event;
 int cb_event_create(int dev, cb_event* ev);
 int cb_event_record(int dev, cb_event ev, cb_stream stream);
+int cb_stream_wait_event(int dev, cb_stream stream, cb_event ev);  /* later work on `stream` waits for `ev`: copies and launches of
+                                                                       different Execute calls overlap across streams */
 int cb_event_elapsed_ms(cb_event start, cb_event stop, float* ms);  /* syncs on stop */
 int cb_event_destroy(int dev, cb_event ev);
 
