@@ -140,6 +140,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
 
+  // The next kernel in the stream, if it was launched for programmatic dependent launch, may be
+  // scheduled while this grid drains (such kernels wait before they touch global memory).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kblocks = (p.K + GT_BK - 1) / GT_BK;
 
@@ -154,6 +157,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
+  // Set-up above overlaps the tail of the kernel before this one; its outputs (possibly this
+  // kernel's operands) and the memory it may still read are touched only after it has finished.
+  if (warp != GT_MMA_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == GT_TMA_WARP) {
     // ------------------------------ TMA producer ------------------------------
@@ -295,6 +301,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 split_f32_planes_kernel(const float* __restrict__ src, uint16_t* __restrict__ planes, size_t n, int n_planes) {
+  // the GEMM that consumes the planes may set itself up meanwhile; it waits for this grid before it loads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
   for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
     float v[4];
@@ -381,8 +389,18 @@ static int launch_t(int dev, int blocks, const CUtensorMap& ta, const CUtensorMa
     CB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM));
     if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  gemm_tcgen05_kernel<OT><<<blocks, GT_THREADS, GT_SMEM, s>>>(ta, tb, prm);
-  CB_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(GT_THREADS);
+  cfg.dynamicSmemBytes = GT_SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<OT>, ta, tb, prm));
   return CB_OK;
 }
 

@@ -29,6 +29,8 @@ template <bool WUNSIGNED, int NPLANES, bool RAW>
 __global__ void __launch_bounds__(256)
 qdense_planes_kernel(const uint8_t* __restrict__ w, const float* __restrict__ scales, const float* __restrict__ zps,
                      uint16_t* __restrict__ planes, int64_t K, int64_t N, int layout, int64_t block, int rows_per_cta) {
+  // the GEMM that consumes the planes may set itself up meanwhile; it waits for this grid before it loads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t n = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (n >= N) return;
   const int64_t nblk = (layout == CB_SCALE_REF) ? (N + block - 1) / block : 0;
