@@ -298,23 +298,19 @@ def main():
     x_stride, y_stride = M * K_DIM * 2, M * n_loc * 2
     wsp = ws.ptr if ws else None
 
+    # Multi-GPU: the kernels and the all-gather of the column shards run on this library's own stream and
+    # communicator (cb_comm_*, NCCL); torch.distributed only hands out the communicator id and the barriers.
     gather = None
+    y_dev_ptr = y_dev.ptr
+    stream_l = stream
     if dist is not None:
-        import torch
-        y_all = torch.empty((g, LAYERS * M * n_loc), dtype=torch.bfloat16, device=f"cuda:{local}")
-        y_loc = torch.empty((LAYERS * M * n_loc,), dtype=torch.bfloat16, device=f"cuda:{local}")
-        y_dev_ptr = y_loc.data_ptr()
-        tstream = torch.cuda.current_stream()
-
-        class _S:            # launch on torch's stream so NCCL orders after the kernels
-            handle = tstream.cuda_stream
-        stream_l = _S()
+        ids = [dv.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = dv.Comm(dev, g, rank, ids[0])
+        y_all = dv.DeviceMem(g * LAYERS * y_stride, dev)
 
         def gather():
-            dist.all_gather_into_tensor(y_all.view(-1), y_loc)
-    else:
-        y_dev_ptr = y_dev.ptr
-        stream_l = stream
+            comm.allgather(y_dev_ptr, y_all.ptr, LAYERS * y_stride, stream)
 
     def step(copy: bool):
         if copy:      # this step's activations: one pinned-host -> device copy

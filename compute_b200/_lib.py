@@ -90,6 +90,12 @@ SIGNATURES = {
                    C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_check_status": ([C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_destroy": ([C.c_void_p], C.c_int),
+    "cb_comm_unique_id": ([C.c_char_p], C.c_int),
+    "cb_comm_init_rank": ([C.c_int, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_comm_size": ([C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)], C.c_int),
+    "cb_comm_allgather": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p], C.c_int),
+    "cb_comm_allreduce": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_void_p], C.c_int),
+    "cb_comm_destroy": ([C.c_void_p], C.c_int),
 }
 
 _lib = None

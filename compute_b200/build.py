@@ -13,7 +13,7 @@ OUT = os.path.join(HERE, "libcudabackend.so")
 OBJ = os.path.join(HERE, "build")
 
 SOURCES = ["runtime.cu", "qdense.cu", "qdense_prefill.cu", "qdense_decode_tc.cu", "dot.cu", "dot_generic.cu", "gemm_tcgen05.cu",
-           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "helper_ops.cu", "graph.cu"]
+           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "helper_ops.cu", "graph.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-DCB_BUILDING"]
@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
         list(ex.map(run, jobs))
     if jobs or force or not os.path.exists(OUT):
-        run([cc, "-ccbin", host, "-shared", "-o", OUT] + objs + ["-cudart", "static", "-Xlinker", "--no-undefined"])
+        run([cc, "-ccbin", host, "-shared", "-o", OUT] + objs + ["-cudart", "static", "-ldl", "-Xlinker", "--no-undefined"])
     return OUT
 
 

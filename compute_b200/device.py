@@ -88,6 +88,39 @@ class Event:
             self.handle = None
 
 
+REDUCE_SUM, REDUCE_PRODUCT, REDUCE_MAX, REDUCE_MIN = range(4)
+COMM_ID_BYTES = 128
+
+
+class Comm:
+    """One rank of a communicator (one process per GPU).  `unique_id()` is called on one rank and its
+    128 bytes are handed to the others by the host program; then every rank constructs its Comm."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(COMM_ID_BYTES)
+        check(_lib.load().cb_comm_unique_id(buf))
+        return buf.raw
+
+    def __init__(self, dev: int, nranks: int, rank: int, uid: bytes):
+        assert len(uid) == COMM_ID_BYTES
+        self.dev, self.nranks, self.rank = dev, nranks, rank
+        h = C.c_void_p()
+        check(_lib.load().cb_comm_init_rank(dev, nranks, rank, uid, C.byref(h)))
+        self.handle = h
+
+    def allgather(self, send: int, recv: int, bytes_per_rank: int, stream=None) -> None:
+        check(_lib.load().cb_comm_allgather(self.handle, send, recv, bytes_per_rank, stream.handle if stream else None))
+
+    def allreduce(self, send: int, recv: int, count: int, dtype: int, op: int = REDUCE_SUM, stream=None) -> None:
+        check(_lib.load().cb_comm_allreduce(self.handle, send, recv, count, dtype, op, stream.handle if stream else None))
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.load().cb_comm_destroy(self.handle)
+            self.handle = None
+
+
 class DeviceMem:
     """A device allocation owned by this object."""
 

@@ -193,6 +193,23 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
 int cb_plan_check_status(const cb_plan* plan, const void* workspace);
 int cb_plan_destroy(cb_plan* plan);
 
+/* ---- collectives: one communicator rank per process and GPU (NCCL, loaded at run time)
+ * Replace CollectiveOps.AllReduce (collectiveops.go:10-39) and provide the all-gather at a
+ * column-shard boundary that the interface sketches (collectiveops.go:31-32; the reference has
+ * no implementation of either).  The 128-byte id is made on one rank and handed to the others by
+ * the host program (any channel); every rank then calls cb_comm_init_rank.  Without NCCL on the
+ * machine these return CB_ERR_NOT_IMPLEMENTED. */
+#define CB_COMM_ID_BYTES 128
+typedef struct cb_comm cb_comm;
+typedef enum { CB_REDUCE_SUM = 0, CB_REDUCE_PRODUCT = 1, CB_REDUCE_MAX = 2, CB_REDUCE_MIN = 3 } cb_reduce_op;
+int cb_comm_unique_id(unsigned char* id /* CB_COMM_ID_BYTES */);
+int cb_comm_init_rank(int dev, int nranks, int rank, const unsigned char* id, cb_comm** comm);
+int cb_comm_size(const cb_comm* comm, int* nranks, int* rank);
+/* recv[r * bytes_per_rank ...] = rank r's send, for every r; in place when send == recv + rank * bytes_per_rank */
+int cb_comm_allgather(cb_comm* comm, const void* send, void* recv, size_t bytes_per_rank, cb_stream stream);
+int cb_comm_allreduce(cb_comm* comm, const void* send, void* recv, size_t count, int32_t dtype, int32_t op, cb_stream stream);
+int cb_comm_destroy(cb_comm* comm);
+
 #ifdef __cplusplus
 }
 #endif
