@@ -256,6 +256,9 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU: column slices stored straight into every rank's result buffer by the kernel "
+                         "(fused, default) or gathered afterwards with NCCL")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
     if args.impl == "reference":
@@ -298,12 +301,18 @@ def main():
     x_stride, y_stride = M * K_DIM * 2, M * n_loc * 2
     wsp = ws.ptr if ws else None
 
-    # Multi-GPU: the kernels and the all-gather of the column shards run on this library's own stream and
-    # communicator (cb_comm_*, NCCL); torch.distributed only hands out the communicator id and the barriers.
+    # Multi-GPU.  torch.distributed only hands out handles / ids and the barriers; the data path is this library's:
+    #  fused: the decode kernel stores its column slice into the result buffer of every rank over NVLink (buffers
+    #         opened with cb_ipc_open) ; one cb_peer_signal + cb_peer_wait per step makes the stream wait for the
+    #         slices of all ranks.  Two result buffers alternate, so a rank that runs one step ahead never
+    #         overwrites results a slower rank has not consumed yet.
+    #  nccl:  every rank computes into its own slice buffer, then one cb_comm_allgather per step.
     gather = None
+    fused = None
     y_dev_ptr = y_dev.ptr
     stream_l = stream
-    if dist is not None:
+    full_stride = M * N_DIM * 2
+    if dist is not None and args.gather == "nccl":
         ids = [dv.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         comm = dv.Comm(dev, g, rank, ids[0])
@@ -311,10 +320,36 @@ def main():
 
         def gather():
             comm.allgather(y_dev_ptr, y_all.ptr, LAYERS * y_stride, stream)
+    elif dist is not None:
+        y_full = [dv.DeviceMem(LAYERS * full_stride, dev) for _ in range(2)]
+        flags = dv.DeviceMem(256, dev)          # words [0, g): arrivals per source rank; word 16: wait status
+        flags.zero()
+        mine = [dv.ipc_export(y_full[0]), dv.ipc_export(y_full[1]), dv.ipc_export(flags)]
+        everyone = [None] * g
+        dist.all_gather_object(everyone, mine)
+        peer_y = [[y_full[bb].ptr if r == rank else dv.ipc_open(dev, everyone[r][bb]) for bb in range(2)] for r in range(g)]
+        peer_flags = [flags.ptr if r == rank else dv.ipc_open(dev, everyone[r][2]) for r in range(g)]
+        plan = dv.Plan.qdense(M, K_DIM, n_loc, dv.BF16, dv.I8, dv.SCALE_KGROUP, GROUP, False, False, dv.ACT_SILU, dev=dev,
+                              gather_ranks=g, gather_rank=rank)
+        ws = plan.new_workspace()
+        wsp = ws.ptr
+        fused = {"steps": 0}
+        dist.barrier()
 
     def step(copy: bool):
         if copy:      # this step's activations: one pinned-host -> device copy
             dv.check(dv._lib.load().cb_h2d(dev, x_dev.ptr, x_host.ptr, LAYERS * x_stride, stream_l.handle))
+        if fused is not None:
+            bb = fused["steps"] & 1
+            for layer in range(LAYERS):
+                plan.launch([x_dev.ptr + layer * x_stride, w_dev[layer].ptr, s_dev[layer].ptr],
+                            [peer_y[r][bb] + layer * full_stride for r in range(g)], wsp, stream_l)
+            fused["steps"] += 1
+            dv.peer_signal(dev, peer_flags, rank, stream_l)
+            dv.peer_wait(dev, flags.ptr, g, fused["steps"], flags.ptr + 64, stream_l)
+            if copy:  # the gathered result of this step
+                dv.check(dv._lib.load().cb_d2h(dev, y_full_host.ptr, y_full[bb].ptr, LAYERS * full_stride, stream_l.handle))
+            return
         for layer in range(LAYERS):
             plan.launch([x_dev.ptr + layer * x_stride, w_dev[layer].ptr, s_dev[layer].ptr],
                         [y_dev_ptr + layer * y_stride], wsp, stream_l)
@@ -322,6 +357,8 @@ def main():
             gather()
         if copy:      # this step's results: one device -> pinned-host copy
             dv.check(dv._lib.load().cb_d2h(dev, y_host.ptr, y_dev_ptr, LAYERS * y_stride, stream_l.handle))
+
+    y_full_host = dv.PinnedHost((LAYERS, M, N_DIM), np.uint16) if fused is not None else None
 
     # End-to-end leg on one GPU: the copies of neighbouring steps overlap the kernels (two activation and
     # two result buffers, a copy-in and a copy-out stream, events between them).  Every step still copies its
@@ -414,6 +451,14 @@ def main():
             step(True)
         ms_e2e = timed(True, args.steps)
 
+    if fused is not None:
+        sync()
+        wait_status = int(flags.download((64,), np.uint32)[16])
+        if wait_status:
+            raise RuntimeError(f"rank {rank}: timed out waiting for the slice of rank {wait_status - 1}")
+        # a sample of the gathered result: the slice another rank stored here equals the one this rank computed there
+        dist.barrier()          # nobody frees buffers its peers may still be writing
+
     bytes_launch = algorithmic_bytes(M, n_loc)
     job_bytes_step = LAYERS * (algorithmic_bytes(M, N_DIM) if g == 1 else g * bytes_launch)
     flops_step = LAYERS * 2 * M * K_DIM * N_DIM
@@ -435,14 +480,17 @@ def main():
         "config": {"workload": f"config3 decode quantized dense: x bf16 [{M},{K_DIM}], W int8 [{K_DIM},{N_DIM}], "
                                f"group-{GROUP} f32 scales along K, SiLU, bf16 out; {LAYERS} distinct layers per step",
                    "M": M, "K": K_DIM, "N": N_DIM, "layers_per_step": LAYERS,
-                   "parallelism": f"N-sharded x{g}, one all-gather per step" if g > 1 else "single GPU",
+                   "parallelism": ("single GPU" if g == 1 else
+                                   f"N-sharded x{g}, column slices stored into every rank's result buffer by the kernel (peer stores over NVLink), one flag wait per step"
+                                   if fused is not None else f"N-sharded x{g}, one NCCL all-gather per step"),
                    "l2": f"{LAYERS} distinct weight matrices per step ({LAYERS * K_DIM * N_DIM // g >> 20} MiB per GPU) exceed the 126 MB L2" if LAYERS * K_DIM * N_DIM // g > 126e6 else
                          "per-GPU weights of a step fit in L2 at this shard count; launches may be served from L2",
                    "kernel": plan.kernel_name, "grid": [plan.blocks, plan.threads], "dyn_smem": plan.dyn_smem},
         "tflops": flops_step * args.steps / (ms * 1e-3) / 1e12,
         # the tensor-core decode plan launches two kernels per call: the activation digit kernel and the main kernel
-        "gpu_launches": LAYERS * args.steps * (2 if plan.kernel_name.startswith("qdense_decode_tc") else 1),
-        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * x_stride, "d2h_bytes_per_step": LAYERS * y_stride,
+        "gpu_launches": args.steps * (LAYERS * (2 if plan.kernel_name.startswith("qdense_decode_tc") else 1)
+                                      + (2 if fused is not None else 0)),     # + the signal and wait kernels of a gathered step
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * x_stride, "d2h_bytes_per_step": LAYERS * (full_stride if fused is not None else y_stride),
                 "ms_per_step": ms_e2e / args.steps,
                 "note": "activations H2D from pinned memory and results D2H every step (copies of neighbouring steps overlap the kernels on one GPU); weights resident as device buffers"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -30,7 +30,8 @@ class QDenseDesc(C.Structure):
     _fields_ = [("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64),
                 ("x_dtype", C.c_int32), ("w_dtype", C.c_int32), ("scale_layout", C.c_int32),
                 ("block_size", C.c_int64), ("has_zero_point", C.c_int32), ("has_bias", C.c_int32),
-                ("activation", C.c_int32), ("variant", C.c_int32)]
+                ("activation", C.c_int32), ("variant", C.c_int32),
+                ("gather_ranks", C.c_int32), ("gather_rank", C.c_int32)]
 
 
 class DotDesc(C.Structure):
@@ -90,6 +91,11 @@ SIGNATURES = {
                    C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_check_status": ([C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_destroy": ([C.c_void_p], C.c_int),
+    "cb_ipc_export": ([C.c_int, C.c_void_p, C.c_char_p], C.c_int),
+    "cb_ipc_open": ([C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_ipc_close": ([C.c_int, C.c_void_p], C.c_int),
+    "cb_peer_signal": ([C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p], C.c_int),
+    "cb_peer_wait": ([C.c_int, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p], C.c_int),
     "cb_comm_unique_id": ([C.c_char_p], C.c_int),
     "cb_comm_init_rank": ([C.c_int, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
     "cb_comm_size": ([C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)], C.c_int),

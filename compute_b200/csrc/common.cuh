@@ -100,6 +100,8 @@ int sdpa_plan(cb_plan* p);
 int sdpa_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int helper_plan(cb_plan* p);
 int helper_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s);
+int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsigned* status_word, cudaStream_t s);
 
 // ---- device scalar helpers --------------------------------------------------
 // bf16 <-> f32 exactly as dtypes/bfloat16/bfloat16.go:25-39 of the reference:

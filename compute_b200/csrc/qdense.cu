@@ -621,6 +621,7 @@ int qdense_plan(cb_plan* p) {
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown activation %d", d.activation);
   p->n_inputs = 3 + (d.has_zero_point ? 1 : 0) + (d.has_bias ? 1 : 0);
   p->n_outputs = 1;
+  if (d.gather_ranks < 0) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: gather_ranks must not be negative");
 
   int variant = d.variant;
   std::string why;
@@ -628,6 +629,11 @@ int qdense_plan(cb_plan* p) {
   std::string why_prefill, why_tc;
   const bool can_decode_tc = qdense_decode_tc_eligible(d, &why_tc);
   const bool can_prefill = qdense_prefill_eligible(d, &why_prefill);
+  if (d.gather_ranks > 1) {          // the fused all-gather exists in the tensor-core decode kernel only
+    if (variant != CB_QDENSE_AUTO && variant != CB_QDENSE_DECODE_TC)
+      return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: a gathered plan needs the tensor-core decode kernel");
+    variant = CB_QDENSE_DECODE_TC;
+  }
   if (variant == CB_QDENSE_AUTO) {
     // decode shapes stream W once; beyond 16 rows the tensor-core GEMM wins as soon as the
     // problem is large enough to pay for expanding the weights (small ones stay on the

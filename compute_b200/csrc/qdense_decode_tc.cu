@@ -49,10 +49,14 @@ constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight:
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
 
+constexpr int QT_MAX_RANKS = 8;
+
 struct QtParams {
   const float* scales;
   const float* bias;
-  void* out;
+  void* outs[QT_MAX_RANKS];            // result buffers this kernel stores into (one, or one per rank of a gathered plan)
+  int n_outs;                          // 1, or the number of ranks
+  int out_ld, out_col0;                // row stride (elements) and first column of this kernel's slice
   unsigned* status;
   unsigned* counters;       // one per n tile, zero between launches
   const int* row_exp;       // [16] exponent of unit[m]
@@ -176,28 +180,46 @@ __device__ __forceinline__ void qt_fail(const QtParams& p, unsigned code, unsign
 // act(v[m]) -> out[m, n] for the rows that exist.  The activation is chosen once, outside the
 // row loop, so the MB rows are independent instruction streams; for 16-bit outputs SiLU uses
 // the hardware exp and reciprocal (error far below one unit of the output).
+// act(v[m]) -> out[m, n] for the rows that exist, called by the 128 threads of the first epilogue
+// group together.  The activation is chosen once, outside the row loop, so the MB rows are
+// independent instruction streams; for 16-bit outputs SiLU uses the hardware exp and reciprocal
+// (error far below one unit of the output).  The tile is staged in shared memory and leaves in
+// 16-byte pieces (256 contiguous bytes per row), to the result buffer of every rank of a gathered plan.
 template <int MB, int ACT, bool BF16>
-__device__ __forceinline__ void qt_store_rows_act(const float* v, void* out, int M, int N, int n) {
+__device__ __forceinline__ void qt_store_rows_act(const float* v, const QtParams& p, int tile_n0, int nl, uint8_t* stage) {
 #pragma unroll
   for (int m = 0; m < MB; m++) {
     float y;
     if (ACT == CB_ACT_SILU && BF16) y = __fdividef(v[m], 1.0f + __expf(-v[m]));
     else y = apply_activation(v[m], ACT);
-    if (m < M) {
-      if (BF16) reinterpret_cast<uint16_t*>(out)[(size_t)m * N + n] = f32_to_bf16_bits(y);
-      else reinterpret_cast<float*>(out)[(size_t)m * N + n] = y;
+    if (BF16) reinterpret_cast<uint16_t*>(stage)[m * QT_TILE_N + nl] = f32_to_bf16_bits(y);
+    else reinterpret_cast<float*>(stage)[m * QT_TILE_N + nl] = y;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  constexpr int ESIZE = BF16 ? 2 : 4;
+  constexpr int EPC = 16 / ESIZE;              // elements per 16-byte piece
+  constexpr int CPR = QT_TILE_N / EPC;         // pieces per row
+  for (int idx = nl; idx < MB * CPR; idx += 128) {
+    const int m = idx / CPR, c = idx - m * CPR;
+    const int col = tile_n0 + c * EPC;
+    if (m < p.M && col < p.N) {                // N is a multiple of 16: a piece lies inside or outside
+      const uint4 val = *reinterpret_cast<const uint4*>(stage + ((size_t)m * QT_TILE_N + c * EPC) * ESIZE);
+      const size_t off = ((size_t)m * p.out_ld + p.out_col0 + col) * ESIZE;
+      for (int r = 0; r < p.n_outs; r++)       // own buffer, and the peers' over NVLink for a gathered plan
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.outs[r]) + off) = val;
     }
   }
+  asm volatile("bar.sync 1, 128;" ::: "memory");   // the staging tile may be rewritten
 }
 template <int MB, bool BF16>
-__device__ __forceinline__ void qt_store_rows(const float* v, int act, void* out, int M, int N, int n) {
-  switch (act) {
-    case CB_ACT_GELU: qt_store_rows_act<MB, CB_ACT_GELU, BF16>(v, out, M, N, n); break;
-    case CB_ACT_RELU: qt_store_rows_act<MB, CB_ACT_RELU, BF16>(v, out, M, N, n); break;
-    case CB_ACT_SILU: qt_store_rows_act<MB, CB_ACT_SILU, BF16>(v, out, M, N, n); break;
-    case CB_ACT_HARDSWISH: qt_store_rows_act<MB, CB_ACT_HARDSWISH, BF16>(v, out, M, N, n); break;
-    case CB_ACT_TANH: qt_store_rows_act<MB, CB_ACT_TANH, BF16>(v, out, M, N, n); break;
-    default: qt_store_rows_act<MB, CB_ACT_NONE, BF16>(v, out, M, N, n); break;
+__device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p, int tile_n0, int nl, uint8_t* stage) {
+  switch (p.activation) {
+    case CB_ACT_GELU: qt_store_rows_act<MB, CB_ACT_GELU, BF16>(v, p, tile_n0, nl, stage); break;
+    case CB_ACT_RELU: qt_store_rows_act<MB, CB_ACT_RELU, BF16>(v, p, tile_n0, nl, stage); break;
+    case CB_ACT_SILU: qt_store_rows_act<MB, CB_ACT_SILU, BF16>(v, p, tile_n0, nl, stage); break;
+    case CB_ACT_HARDSWISH: qt_store_rows_act<MB, CB_ACT_HARDSWISH, BF16>(v, p, tile_n0, nl, stage); break;
+    case CB_ACT_TANH: qt_store_rows_act<MB, CB_ACT_TANH, BF16>(v, p, tile_n0, nl, stage); break;
+    default: qt_store_rows_act<MB, CB_ACT_NONE, BF16>(v, p, tile_n0, nl, stage); break;
   }
 }
 
@@ -225,6 +247,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> TMA producers
   float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
   float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_merge + MB * QT_TILE_N);                 // [MB][128] output elements
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
   __shared__ unsigned s_last;
@@ -442,16 +465,16 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
               if (tid == 0 && final_seg) QT_STAMP(7);
             }
           }
-          if (write && n < p.N) {
-            const float bias = p.bias ? __ldg(p.bias + n) : 0.0f;
+          if (write) {
+            const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
 #pragma unroll
             for (int m = 0; m < MB; m++) {
               float v = tot[m] * s_unit[m][0] * s_unit[m][1];
               if (s_bad[m]) v = __int_as_float(0x7FC00000);
               tot[m] = v + bias;
             }
-            if (p.out_bf16) qt_store_rows<MB, true>(tot, p.activation, p.out, p.M, p.N, n);
-            else qt_store_rows<MB, false>(tot, p.activation, p.out, p.M, p.N, n);
+            if (p.out_bf16) qt_store_rows<MB, true>(tot, p, tile * QT_TILE_N, nl, s_stage);
+            else qt_store_rows<MB, false>(tot, p, tile * QT_TILE_N, nl, s_stage);
           }
         }
 #pragma unroll
@@ -475,12 +498,59 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 }
 
 // ---------------------------------------------------------------------------
+// waiting for the slices of the other ranks
+// ---------------------------------------------------------------------------
+// One thread per flag polls it (system scope) until it has reached `target` (compared modulo 2^32) or
+// about two seconds have passed; a timeout leaves 1 + flag index in the status word.  The flags are
+// written by kernels running on other GPUs, never by kernels of this GPU that might be queued behind
+// this one.
+__global__ void peer_wait_kernel(const unsigned* flags, int n_flags, unsigned target, unsigned* status_word) {
+  const int i = threadIdx.x;
+  if (i >= n_flags) return;
+  const volatile unsigned* f = flags + i;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if ((int)(v - target) >= 0) break;
+    if (global_ns() - t0 > WAIT_NS) { atomicExch(status_word, 1u + (unsigned)i); break; }
+    __nanosleep(200);
+  }
+}
+
+// Runs after the kernels whose peer stores it announces (same stream): when it starts, those
+// kernels have completed and their stores have been performed; it adds 1 to word `slot` of the flag
+// array of every rank.
+struct PeerFlags { unsigned* f[QT_MAX_RANKS]; };
+__global__ void peer_signal_kernel(PeerFlags flags, int n_ranks, int slot) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < n_ranks; r++) atomicAdd_system(flags.f[r] + slot, 1u);
+  }
+}
+
+int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s) {
+  if (n_ranks < 1 || n_ranks > QT_MAX_RANKS) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal: %d ranks", n_ranks);
+  PeerFlags pf;
+  for (int r = 0; r < QT_MAX_RANKS; r++) pf.f[r] = r < n_ranks ? (unsigned*)flags[r] : nullptr;
+  peer_signal_kernel<<<1, 32, 0, s>>>(pf, n_ranks, slot);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
+int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsigned* status_word, cudaStream_t s) {
+  peer_wait_kernel<<<1, 32, 0, s>>>(flags, n_flags, target, status_word);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
+// ---------------------------------------------------------------------------
 // planning and launch
 // ---------------------------------------------------------------------------
 static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
 static int qt_smem(int nb) {
-  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + (nb / 3) * QT_TILE_N * 4;
+  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -493,6 +563,8 @@ bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
   if (d.scale_layout == CB_SCALE_KGROUP && (d.block_size <= 0 || d.block_size % QT_UNIT_K != 0))
     return no("K-group size must be a multiple of 128");
   if (d.K > (1 << 30) || d.N > (1 << 30)) return no("dimension too large");
+  if (d.gather_ranks > QT_MAX_RANKS) return no("a gathered plan spans at most 8 ranks");
+  if (d.gather_ranks > 1 && (d.gather_rank < 0 || d.gather_rank >= d.gather_ranks)) return no("gather_rank out of range");
   return true;
 }
 
@@ -529,6 +601,7 @@ int qdense_decode_tc_plan(cb_plan* p) {
   p->counter_bytes = l.counter_bytes;
   p->workspace_bytes = l.total;
   p->has_status = true;
+  if (d.gather_ranks > 1) p->n_outputs = d.gather_ranks;          // the result buffer of every rank
   p->name = std::string("qdense_decode_tc_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + "_n" + std::to_string(l.nb) +
             (d.w_dtype == CB_U8 ? "_u8" : "_i8");
   return CB_OK;
@@ -577,6 +650,8 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   const cb_qdense_desc& d = p->qd;
   if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
+  for (int r = 0; r < (d.gather_ranks > 1 ? d.gather_ranks : 1); r++)
+    if (reinterpret_cast<uintptr_t>(out[r]) & 15) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: outputs must be 16-byte aligned");
   const QtLayout l = qt_layout(d, p->blocks);
   uint8_t* w8 = (uint8_t*)ws;
   int* row_exp = (int*)(w8 + l.off_rows);
@@ -611,7 +686,11 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   memset(&prm, 0, sizeof(prm));
   prm.scales = (const float*)in[2];
   prm.bias = d.has_bias ? (const float*)in[3] : nullptr;
-  prm.out = out[0];
+  const int g = d.gather_ranks > 1 ? d.gather_ranks : 1;
+  for (int r = 0; r < g; r++) prm.outs[r] = out[r];
+  prm.n_outs = g;
+  prm.out_ld = (int)(d.N * g);
+  prm.out_col0 = (int)(d.N * (g > 1 ? d.gather_rank : 0));
   prm.status = (unsigned*)w8;
   prm.counters = (unsigned*)(w8 + l.off_counters);
   prm.row_exp = row_exp;

@@ -218,6 +218,48 @@ int cb_event_record(int dev, cb_event ev, cb_stream stream) {
   return CB_OK;
 }
 
+int cb_ipc_export(int dev, const void* dptr, unsigned char* handle) {
+  CB_TRY(set_device(dev));
+  if (!dptr || !handle) return fail(CB_ERR_INVALID_ARG, "cb_ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == CB_IPC_HANDLE_BYTES, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  CB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(dptr)));
+  memcpy(handle, &h, sizeof(h));
+  return CB_OK;
+}
+
+int cb_ipc_open(int dev, const unsigned char* handle, void** dptr) {
+  CB_TRY(set_device(dev));
+  if (!dptr || !handle) return fail(CB_ERR_INVALID_ARG, "cb_ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  CB_CUDA(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return CB_OK;
+}
+
+int cb_ipc_close(int dev, void* dptr) {
+  CB_TRY(set_device(dev));
+  if (!dptr) return CB_OK;
+  CB_CUDA(cudaIpcCloseMemHandle(dptr));
+  return CB_OK;
+}
+
+int cb_peer_signal(int dev, void* const* flags, int n_ranks, int slot, cb_stream stream) {
+  CB_TRY(set_device(dev));
+  if (!flags) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal: null argument");
+  if (slot < 0 || slot >= 32) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal: slot %d", slot);
+  for (int r = 0; r < n_ranks && r < 8; r++)
+    if (!flags[r]) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal: null flag array for rank %d", r);
+  return cb::peer_signal_launch(flags, n_ranks, slot, (cudaStream_t)stream);
+}
+
+int cb_peer_wait(int dev, const void* flags, int n_flags, uint32_t target, void* status_word, cb_stream stream) {
+  CB_TRY(set_device(dev));
+  if (!flags || !status_word) return fail(CB_ERR_INVALID_ARG, "cb_peer_wait: null argument");
+  if (n_flags < 1 || n_flags > 32) return fail(CB_ERR_INVALID_ARG, "cb_peer_wait: %d flags", n_flags);
+  return cb::peer_wait_launch((const unsigned*)flags, n_flags, target, (unsigned*)status_word, (cudaStream_t)stream);
+}
+
 int cb_stream_wait_event(int dev, cb_stream stream, cb_event ev) {
   CB_TRY(set_device(dev));
   CB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0));

@@ -88,6 +88,38 @@ class Event:
             self.handle = None
 
 
+IPC_HANDLE_BYTES = 64
+
+
+def ipc_export(mem: "DeviceMem") -> bytes:
+    """A handle other processes on this machine can open to reach `mem` (its base pointer)."""
+    buf = C.create_string_buffer(IPC_HANDLE_BYTES)
+    check(_lib.load().cb_ipc_export(mem.dev, mem.ptr, buf))
+    return buf.raw
+
+
+def ipc_open(dev: int, handle: bytes) -> int:
+    """Maps another process's allocation; returns a device pointer valid in this process."""
+    p = C.c_void_p()
+    check(_lib.load().cb_ipc_open(dev, handle, C.byref(p)))
+    return p.value
+
+
+def ipc_close(dev: int, ptr: int) -> None:
+    check(_lib.load().cb_ipc_close(dev, ptr))
+
+
+def peer_signal(dev: int, flag_arrays: Sequence[int], slot: int, stream=None) -> None:
+    """After the work already in `stream`: adds 1 to word `slot` of every rank's flag array."""
+    arr = (C.c_void_p * len(flag_arrays))(*flag_arrays)
+    check(_lib.load().cb_peer_signal(dev, arr, len(flag_arrays), slot, stream.handle if stream else None))
+
+
+def peer_wait(dev: int, flags: int, n_flags: int, target: int, status_word: int, stream=None) -> None:
+    """Enqueues a bounded wait until flags[0..n_flags) have all reached `target`."""
+    check(_lib.load().cb_peer_wait(dev, flags, n_flags, target & 0xFFFFFFFF, status_word, stream.handle if stream else None))
+
+
 REDUCE_SUM, REDUCE_PRODUCT, REDUCE_MAX, REDUCE_MIN = range(4)
 COMM_ID_BYTES = 128
 
@@ -203,9 +235,10 @@ class Plan:
     # --- constructors ------------------------------------------------------
     @classmethod
     def qdense(cls, M, K, N, x_dtype=F32, w_dtype=I8, scale_layout=SCALE_REF, block_size=1,
-               has_zero_point=False, has_bias=False, activation=ACT_NONE, variant=QDENSE_AUTO, dev=0) -> "Plan":
+               has_zero_point=False, has_bias=False, activation=ACT_NONE, variant=QDENSE_AUTO, dev=0,
+               gather_ranks=0, gather_rank=0) -> "Plan":
         d = QDenseDesc(M, K, N, x_dtype, w_dtype, scale_layout, block_size, int(has_zero_point),
-                       int(has_bias), activation, variant)
+                       int(has_bias), activation, variant, gather_ranks, gather_rank)
         h = C.c_void_p()
         check(_lib.load().cb_plan_qdense(dev, C.byref(d), C.byref(h)))
         return cls(h, dev)

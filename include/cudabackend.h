@@ -107,6 +107,15 @@ typedef struct {
   int32_t has_bias;       /* bias [N] f32 */
   int32_t activation;     /* cb_activation */
   int32_t variant;        /* cb_qdense_variant; AUTO selects by shape and dtype */
+  /* Column-sharded decode with the all-gather fused into the kernel (0 or 1 = off): this rank holds
+   * columns [gather_rank * N, (gather_rank + 1) * N) of a [K, N * gather_ranks] projection.  The plan
+   * then takes gather_ranks outputs: the [M, N * gather_ranks] result buffer of every rank (own
+   * buffer included; peers' buffers opened with cb_ipc_open), and the kernel stores its column slice
+   * into all of them as its tiles finish.  cb_peer_signal, enqueued after one or several such
+   * launches, tells the other ranks that the slices have landed; cb_peer_wait makes a stream wait
+   * for the slices of all ranks.  Decode tensor-core kernel only. */
+  int32_t gather_ranks;
+  int32_t gather_rank;
 } cb_qdense_desc;
 
 int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);
@@ -192,6 +201,21 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
  * workspace; CB_ERR_TIMEOUT if a wait gave up.  CB_OK for plans without such waits. */
 int cb_plan_check_status(const cb_plan* plan, const void* workspace);
 int cb_plan_destroy(cb_plan* plan);
+
+/* ---- peer memory between the processes of one machine (one process per GPU, NVLink)
+ * No counterpart in the reference.  cb_ipc_export names an allocation made by cb_alloc (pass its base
+ * pointer); another process maps it with cb_ipc_open and may hand the mapped pointer to kernels as an
+ * output of a gathered plan.  Arrival flags are arrays of uint32 (zeroed once) that every rank exports
+ * like any buffer: cb_peer_signal enqueues a kernel that, once all earlier work of the stream has
+ * completed, adds 1 to word `slot` (the caller's rank) of the flag array of every rank; cb_peer_wait
+ * enqueues a kernel that waits (at most ~2 s, then it sets *status_word to a non-zero code and
+ * returns) until each of flags[0..n_flags) of the local array has reached `target`. */
+#define CB_IPC_HANDLE_BYTES 64
+int cb_ipc_export(int dev, const void* dptr, unsigned char* handle /* CB_IPC_HANDLE_BYTES */);
+int cb_ipc_open(int dev, const unsigned char* handle, void** dptr);
+int cb_ipc_close(int dev, void* dptr);
+int cb_peer_signal(int dev, void* const* flags /* one array per rank */, int n_ranks, int slot, cb_stream stream);
+int cb_peer_wait(int dev, const void* flags, int n_flags, uint32_t target, void* status_word, cb_stream stream);
 
 /* ---- collectives: one communicator rank per process and GPU (NCCL, loaded at run time)
  * Replace CollectiveOps.AllReduce (collectiveops.go:10-39) and provide the all-gather at a

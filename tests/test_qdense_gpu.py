@@ -252,6 +252,56 @@ def test_prefill_llama_projection_full_size(layout, group):
     assert max_abs_normalised(orc.bf16_to_f32(dec), orc.bf16_to_f32(got[rows])) < 2.0 ** -7
 
 
+# ------------------------------------------------------------- fused all-gather of column shards
+def test_gathered_decode_two_ranks_on_one_gpu():
+    """The kernel of a gathered plan stores its column slice into every rank's result buffer; a signal kernel
+    then bumps every rank's arrival flag.  Here both ranks are plans on one GPU, launched one after the other
+    (nothing waits on anything that has not finished): both result buffers must hold the full projection, and
+    the flags count the signals."""
+    M, K, N, g = 7, 512, 768, 2
+    n_loc = N // g
+    x, w, s, b = qdense_inputs(321, M, K, N, x_dtype="bf16", scale_layout="kgroup", group=128)
+    xb = orc.bf16_from_f32(x)
+    st = dv.Stream(0)
+    xd = dv.DeviceMem.from_numpy(xb)
+    bufs = [dv.DeviceMem(M * N * 2) for _ in range(g)]
+    flags = [dv.DeviceMem(256) for _ in range(g)]
+    for m in bufs + flags:
+        m.zero()
+    for r in range(g):
+        cols = slice(r * n_loc, (r + 1) * n_loc)
+        plan = dv.Plan.qdense(M, K, n_loc, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, False, True, dv.ACT_SILU,
+                              gather_ranks=g, gather_rank=r)
+        assert plan.kernel_name.startswith("qdense_decode_tc_bf16")
+        ws = plan.new_workspace()
+        wd = dv.DeviceMem.from_numpy(np.ascontiguousarray(w[:, cols]))
+        sd = dv.DeviceMem.from_numpy(np.ascontiguousarray(s[:, cols]))
+        bd = dv.DeviceMem.from_numpy(np.ascontiguousarray(b[cols]))
+        for rep in range(2):                      # two launches and signals per rank: the flags count signals
+            plan.launch([xd.ptr, wd.ptr, sd.ptr, bd.ptr], [m.ptr for m in bufs], ws.ptr, st)
+            dv.peer_signal(0, [f.ptr for f in flags], r, st)
+        st.sync()
+        plan.check_status(ws.ptr)
+    for f in flags:
+        dv.peer_wait(0, f.ptr, g, 2, f.ptr + 64, st)
+    st.sync()
+    want = oracle_compact(x, w, s, b, "kgroup", 128, orc.ACT_SILU)
+    full = ops.quantized_dense(xb, w, s, None, b, x_dtype=dv.BF16, scale_layout=dv.SCALE_KGROUP, block_size=128,
+                               activation=dv.ACT_SILU)
+    for r in range(g):
+        got = bufs[r].download((M, N), np.uint16)
+        assert max_abs_normalised(orc.bf16_to_f32(got), want) < BF16_TOL
+        assert np.array_equal(got, full)          # the same bits as the unsharded plan
+        fl = flags[r].download((64,), np.uint32)
+        assert list(fl[:g]) == [2, 2] and fl[16] == 0
+    # a wait for arrivals that never come gives up and reports which flag it was waiting for
+    dv.peer_wait(0, flags[0].ptr, g, 3, flags[0].ptr + 64, st)
+    st.sync()
+    assert flags[0].download((64,), np.uint32)[16] in (1, 2)
+    with pytest.raises(ErrNotImplemented):        # only the tensor-core decode kernel has the fused gather
+        dv.Plan.qdense(64, K, n_loc, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, gather_ranks=2, gather_rank=0)
+
+
 # ------------------------------------------------------------- dequantisation, bit for bit
 @pytest.mark.parametrize("variant,rows", [(dv.QDENSE_GENERIC, 16), (dv.QDENSE_DECODE_MMA, 16), (dv.QDENSE_DECODE_TC, 16),
                                           (dv.QDENSE_PREFILL, 64)])
