@@ -200,6 +200,8 @@ PREFILL_SHAPES = [
     (300, 512, 520, "ref", 16, True),
     (257, 1024, 1024, "kgroup", 128, False),
     (64, 320, 136, "ref", 1, False),
+    (40, 200, 272, "channel", 0, False),     # ragged K block and tiles
+    (129, 4096, 512, "channel", 0, False),
 ]
 
 
@@ -225,8 +227,9 @@ def test_prefill_matches_oracle(M, K, N, layout, block, with_zp, x_dtype):
         assert max_abs_normalised(got, want) < 1e-5
 
 
-def test_prefill_uint8_all_activations():
-    x, w, s, b = qdense_inputs(77, 40, 256, 264, scale_layout="channel", unsigned=True)
+@pytest.mark.parametrize("N", [264, 272])
+def test_prefill_uint8_all_activations(N):
+    x, w, s, b = qdense_inputs(77, 40, 256, N, scale_layout="channel", unsigned=True)
     for act in ACT.values():
         got = ops.quantized_dense(x, w, s, None, b, scale_layout=dv.SCALE_CHANNEL, activation=act, variant=dv.QDENSE_PREFILL)
         want = oracle_compact(x, w, s, b, "channel", 0, act)
