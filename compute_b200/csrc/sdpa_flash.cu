@@ -62,6 +62,16 @@ __device__ __forceinline__ uint32_t pack16x2(float lo, float hi, int ab_format) 
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// the same with the format known at compile time (the hot loop of the softmax)
+template <typename OT> __device__ __forceinline__ uint32_t pack16x2_t(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack16x2_t<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack16x2_t<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 // one [128 rows x 128 columns] tile = two TMA boxes of 64 columns
 __device__ __forceinline__ void fa_load_tile(uint8_t* dst, const CUtensorMap* map, int bshd, int row0, int head, int b, uint64_t* bar) {
@@ -245,11 +255,23 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (kv0 + c * 32 + i >= kv_limit) sr[c][i] = neg_biggest;   // -inf after scaling either way
       }
       // max of scale*s = scale*max(s) for a positive scale, scale*min(s) for a negative one
-      float ext = __uint_as_float(sr[0][0]);
+      // (the sign of the scale is decided once per block, not per element; two partial extremes
+      // keep the dependency chains short)
+      float ea = __uint_as_float(sr[0][0]), eb = __uint_as_float(sr[2][0]);
+      if (pos_scale) {
 #pragma unroll
-      for (int c = 0; c < 4; c++)
+        for (int i = 1; i < 64; i++) {
+          ea = fmaxf(ea, __uint_as_float(sr[i >> 5][i & 31]));
+          eb = fmaxf(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]));
+        }
+      } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) ext = pos_scale ? fmaxf(ext, __uint_as_float(sr[c][i])) : fminf(ext, __uint_as_float(sr[c][i]));
+        for (int i = 1; i < 64; i++) {
+          ea = fminf(ea, __uint_as_float(sr[i >> 5][i & 31]));
+          eb = fminf(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]));
+        }
+      }
+      const float ext = pos_scale ? fmaxf(ea, eb) : fminf(ea, eb);
       const float m_blk = ext * p.scale_log2;
       float m_new = fmaxf(m_used, m_blk);
       if (m_new == -INFINITY) m_new = 0.0f;          // nothing attendable so far
@@ -284,7 +306,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_used));
           l0 += p0;
           l1 += p1;
-          pk[i >> 1] = pack16x2(p0, p1, p.ab_format);
+          pk[i >> 1] = pack16x2_t<OT>(p0, p1);      // P has the dtype of the inputs, which is the output's
         }
         tmem_st16(s_addr + (uint32_t)(c * 16), pk);
       }
