@@ -726,7 +726,7 @@ static int launch_decode(const cb_plan* p, const void* const* in, void* const* o
   prm.sk_total = (long long)prm.sk_tiles * prm.cpt;
   prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
   prm.activation = d.activation;
-  { const char* e = getenv("CB_QDENSE_DEBUG_SKIP"); prm.debug_skip = (e && e[0] == '1') ? 1 : 0; }
+  prm.debug_skip = 0;
   { const char* e = getenv("CB_QDENSE_DEBUG_STAMPS");
     prm.dbg = (e && e[0] == '1') ? (unsigned long long*)(w8 + p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4) : nullptr; }
   if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))

@@ -90,12 +90,6 @@ qdense_planes_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sc
   }
 }
 
-// Timing diagnosis only: CB_QDENSE_DEBUG_SKIP=2 leaves out the weight expansion, =3 the GEMM.
-static int debug_skip() {
-  const char* e = getenv("CB_QDENSE_DEBUG_SKIP");
-  return (e && e[0] >= '0' && e[0] <= '9') ? e[0] - '0' : 0;
-}
-
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 static bool prefill_raw(const cb_qdense_desc& d) { return d.scale_layout == CB_SCALE_CHANNEL && !d.has_zero_point; }
@@ -144,10 +138,8 @@ int qdense_prefill_launch(const cb_plan* p, const void* const* in, void* const* 
   const dim3 grid(gx, (unsigned)((d.K + rows_per_cta - 1) / rows_per_cta));
   const uint8_t* wq = (const uint8_t*)in[1];
   const float* sc = (const float*)in[2];
-  const bool skip_expand = debug_skip() == 2, skip_gemm = debug_skip() == 3;
 #define QP_LAUNCH(WU, NP, RAW) qdense_planes_kernel<WU, NP, RAW><<<grid, 256, 0, s>>>(wq, sc, zp, wplanes, d.K, d.N, d.scale_layout, block, rows_per_cta)
-  if (skip_expand) {
-  } else if (d.w_dtype == CB_U8) {
+  if (d.w_dtype == CB_U8) {
     if (raw) QP_LAUNCH(true, 1, true); else if (wp == 2) QP_LAUNCH(true, 2, false); else QP_LAUNCH(true, 3, false);
   } else {
     if (raw) QP_LAUNCH(false, 1, true); else if (wp == 2) QP_LAUNCH(false, 2, false); else QP_LAUNCH(false, 3, false);
@@ -175,7 +167,6 @@ int qdense_prefill_launch(const cb_plan* p, const void* const* in, void* const* 
   g.col_scale = raw ? (const float*)in[2] : nullptr;
   g.bias = bias;
   g.activation = d.activation;
-  if (skip_gemm) return CB_OK;
   return gemm_tc_run(p->dev, p->blocks, g, s);
 }
 

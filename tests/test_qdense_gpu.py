@@ -137,6 +137,18 @@ def test_decode_uint8_no_bias_all_activations(variant, group):
         assert max_abs_normalised(got, want) < F32_TOL
 
 
+@pytest.mark.parametrize("M", list(range(1, 17)))
+def test_decode_tc_every_batch_size(M):
+    """M = 1..16 crosses the three digit-tile widths (5, 10 and 16 rows per digit plane)."""
+    K, N = 384, 400
+    x, w, s, b = qdense_inputs(500 + M, M, K, N, scale_layout="kgroup", group=128)
+    got, plan = ops.quantized_dense(x, w, s, None, b, scale_layout=dv.SCALE_KGROUP, block_size=128, activation=dv.ACT_GELU,
+                                    variant=dv.QDENSE_DECODE_TC, return_plan=True)
+    assert plan.kernel_name == f"qdense_decode_tc_f32_n{16 if M <= 5 else 32 if M <= 10 else 48}_i8"
+    want = oracle_compact(x, w, s, b, "kgroup", 128, orc.ACT_GELU)
+    assert max_abs_normalised(got, want) < 1e-5
+
+
 def test_decode_tc_fixed_point_digits_edge_cases():
     """Rows of zeros, rows spanning 30 binades, subnormals and a non-finite value: the int8 digit
     form of x keeps 20 bits below each row's maximum, so small entries beside a large one are
