@@ -497,7 +497,7 @@ def main():
     out = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": g, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16 activations x int8 weights, f32 accumulate", "data": "synthetic (seeded)",
+        "dtype": "int8 weights x int8 digits of the bf16 activations, s32 accumulate per 128-k unit, f32 across units", "data": "synthetic (seeded)",
         "config": {"workload": f"config3 decode quantized dense: x bf16 [{M},{K_DIM}], W int8 [{K_DIM},{N_DIM}], "
                                f"group-{GROUP} f32 scales along K, SiLU, bf16 out; {LAYERS} distinct layers per step",
                    "M": M, "K": K_DIM, "N": N_DIM, "layers_per_step": LAYERS,
