@@ -4,22 +4,23 @@
 //
 // The op is bound by reading W once from HBM, so the kernel spends no instruction on the
 // weights: TMA lands [128 k x 128 n] byte tiles of W in shared memory and tcgen05.mma kind::i8
-// consumes them in place as the MN-major operand.  The activations become the other operand by
-// writing each row in fixed point: x[m,k] = unit[m] * (d0 + 128 d1 + 16384 d2) with signed
-// base-128 digits (unit[m] a power of two chosen from the row maximum, 20 bits below it; exact
-// for bfloat16 values within 2^-13 of the row maximum, and 2^-21 of the row maximum otherwise
-// and for float32).  The digits of all rows form a [3*MB x K] int8 matrix (MB rows per digit),
-// so one MMA of shape (128 n) x (3*MB) x (32 k) yields the three digit sums of 128 output
+// consumes them in place as the MN-major operand.  The activations become the other operand in
+// block fixed point: for every row m and every 128-wide k unit u,
+//     x[m,k] = unit[m,u] * (d0 + 128 d1 + 16384 d2),   signed base-128 digits,
+// with unit[m,u] a power of two taken from the largest |x| of that row inside the unit, 20 bits
+// below it (exact for bfloat16 values within 2^-13 of that maximum; 2^-21 of the maximum
+// otherwise and for float32).  The digits of all rows form a [3*MB x K] int8 matrix (MB rows per
+// digit), so one MMA of shape (128 n) x (3*MB) x (32 k) yields the three digit sums of 128 output
 // columns, exactly, in s32 tensor memory.  Epilogue threads (one per output column) turn a
-// finished 128-k unit into f32, recombine the digits, multiply by the scale of that K group
-// and add it to their running totals.
+// finished 128-k unit into f32, recombine the digits, multiply by unit[m,u] and by the scale of
+// that K group, and add it to their running totals.
 //
-//   qdense_xdigits_kernel   x -> digits + per-row exponents (one CTA per row, a few microseconds)
+//   qdense_xdigits_kernel   x -> digits + unit[m,u] (one warp per row and k unit, all at once)
 //   qdense_decode_tc_kernel persistent, one CTA per SM over a balanced contiguous range of
 //                           (n tile, k unit) pairs:
 //       warp 8   TMA producer: weight tiles into an 8-stage ring (the first ones are requested
 //                before the digit kernel has finished)
-//       warp 10  TMA producer: the digit tile and the 128 scales of each unit
+//       warp 10  TMA producer: the digit tile, the 128 scales and the 16 unit[m,u] of each unit
 //       warps 9, 11  MMA issuers on alternate units: 4 MMAs (K = 32) per unit into one of 8 TMEM
 //                accumulators
 //       warps 0-7 epilogue as above, two groups of four warps on alternate units; a tile whose
@@ -47,6 +48,7 @@ constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP 
 constexpr int QT_TMEM_COLS = 512;
 constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
+constexpr int QT_UN_BYTES = 16 * 4;                     // unit[m,u] of the 16 rows of one k unit
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
 
 constexpr int QT_MAX_RANKS = 8;
@@ -59,8 +61,6 @@ struct QtParams {
   int out_ld, out_col0;                // row stride (elements) and first column of this kernel's slice
   unsigned* status;
   unsigned* counters;       // one per n tile, zero between launches
-  const int* row_exp;       // [16] exponent of unit[m]
-  const unsigned* row_bad;  // [16] non-zero when the row holds a non-finite value
   float* partials;          // [grid][2][MB][128]
   int M, K, N;
   int n_tiles, units_per_tile;
@@ -75,85 +75,77 @@ struct QtParams {
 // ---------------------------------------------------------------------------
 // x -> digits
 // ---------------------------------------------------------------------------
-constexpr int QX_THREADS = 512;
+constexpr int QX_THREADS = 256;       // 8 warps, one (row, k unit) task each
 
-// 8 consecutive elements of a row as floats (K is a multiple of 16, rows are 16-byte aligned)
-__device__ __forceinline__ void qx_load8(const __nv_bfloat16* row, int k, float (&v)[8]) {
-  const uint4 r = *reinterpret_cast<const uint4*>(row + k);
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+// Four consecutive elements x[m, k .. k+3] as floats; zeros beyond column K.
+__device__ __forceinline__ void qx_load4(const __nv_bfloat16* x, size_t m, int K, int k, float (&v)[4]) {
+  const uint2 r = k < K ? __ldg(reinterpret_cast<const uint2*>(x + m * K + k)) : make_uint2(0, 0);
+  v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+  v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
 }
-__device__ __forceinline__ void qx_load8(const float* row, int k, float (&v)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(row + k), b = *reinterpret_cast<const float4*>(row + k + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+__device__ __forceinline__ void qx_load4(const float* x, size_t m, int K, int k, float (&v)[4]) {
+  const float4 r = k < K ? __ldg(reinterpret_cast<const float4*>(x + m * K + k)) : make_float4(0, 0, 0, 0);
+  v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
 }
 
+// One warp per (row m, 128-wide k unit u): the unit's largest finite |x| fixes unit[m,u] = 2^-shift
+// (20 bits below it), every element becomes three signed base-128 digits, and unit[m,u] goes to
+// units[u][m] (NaN when the unit holds inf or NaN).  No pass over the whole row is needed, so all
+// M * ceil(K/128) tasks run at once.
 template <typename XT>
 __global__ void __launch_bounds__(QX_THREADS)
-qdense_xdigits_kernel(const XT* __restrict__ x, int K, int MB, int8_t* __restrict__ digits, int* __restrict__ row_exp,
-                      unsigned* __restrict__ row_bad) {
+qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int8_t* __restrict__ digits, float* __restrict__ units) {
   // The kernel that consumes the digits may start its own set-up now; it waits for this grid to
   // finish before it reads them.  This grid in turn may have been scheduled while the kernel
   // before it in the stream (which may produce x, and may still read the digit buffer) was
   // running: it waits for that kernel to finish before it touches either.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  __shared__ float s_max[QX_THREADS / 32];
-  __shared__ unsigned s_bad[QX_THREADS / 32];
-  const int m = blockIdx.x, tid = threadIdx.x;
-  const XT* row = x + (size_t)m * K;
-  float amax = 0.0f;
-  unsigned bad = 0;
-  for (int k = tid * 8; k < K; k += QX_THREADS * 8) {
-    float v[8];
-    qx_load8(row, k, v);
+  const int lane = threadIdx.x & 31;
+  const int task = blockIdx.x * (QX_THREADS / 32) + (threadIdx.x >> 5);
+  if (task >= M * G) return;
+  const int u = task / M, m = task - u * M;
+  const int k = u * QT_UNIT_K + 4 * lane;
+  float v[4];
+  qx_load4(x, (size_t)m, K, k, v);
+  uint32_t mx = 0;          // bits of the largest finite |x| (non-negative floats order like integers)
+  bool bad = false;
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-      const float a = fabsf(v[e]);
-      if (!(a <= 3.0e38f)) bad = 1;          // inf or NaN
-      else amax = fmaxf(amax, a);
-    }
+  for (int e = 0; e < 4; e++) {
+    const uint32_t a = __float_as_uint(v[e]) & 0x7FFFFFFFu;
+    if (a >= 0x7F800000u) { bad = true; v[e] = 0.0f; } else mx = max(mx, a);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
-  }
-  if ((tid & 31) == 0) { s_max[tid >> 5] = amax; s_bad[tid >> 5] = bad; }
-  __syncthreads();
-  amax = s_max[0]; bad = s_bad[0];
-#pragma unroll
-  for (int i = 1; i < QX_THREADS / 32; i++) { amax = fmaxf(amax, s_max[i]); bad |= s_bad[i]; }
-  int ex = 0;
-  (void)frexpf(amax, &ex);                 // amax < 2^ex
-  const int shift = 20 - ex;               // |x| * 2^shift <= 2^20
-  if (tid == 0) { row_exp[m] = -shift; row_bad[m] = bad; }
-  // 2^shift as two factors that are always normal floats (shift lies in [-108, 169])
-  const int sh1 = shift / 2, sh2 = shift - sh1;
+  mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+  bad = __any_sync(0xFFFFFFFFu, bad);
+  // amax < 2^ex: exponent field - 126 for a normal maximum, the position of the leading bit for a subnormal one
+  const int ef = (int)(mx >> 23);
+  const int ex = ef > 0 ? ef - 126 : (32 - __clz(mx)) - 149;
+  const int shift = min(20 - ex, 149);             // |x| * 2^shift <= 2^20; unit = 2^-shift stays a float
+  const int sh1 = shift / 2, sh2 = shift - sh1;    // two factors that are always normal floats
   const float p1 = __int_as_float((127 + sh1) << 23), p2 = __int_as_float((127 + sh2) << 23);
-  int8_t* d0 = digits + (size_t)(0 * MB + m) * K;
-  int8_t* d1 = digits + (size_t)(1 * MB + m) * K;
-  int8_t* d2 = digits + (size_t)(2 * MB + m) * K;
-  for (int k = tid * 8; k < K; k += QX_THREADS * 8) {
-    float v[8];
-    qx_load8(row, k, v);
-    uint32_t w0[2] = {0, 0}, w1[2] = {0, 0}, w2[2] = {0, 0};
+  uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-      const float f = (fabsf(v[e]) <= 3.0e38f) ? v[e] : 0.0f;
-      const int q = __float2int_rn(f * p1 * p2);
-      const int a = ((q + 64) & 127) - 64;
-      const int q1 = (q - a) >> 7;
-      const int b = ((q1 + 64) & 127) - 64;
-      const int c = (q1 - b) >> 7;
-      w0[e >> 2] |= (uint32_t)(a & 0xFF) << (8 * (e & 3));
-      w1[e >> 2] |= (uint32_t)(b & 0xFF) << (8 * (e & 3));
-      w2[e >> 2] |= (uint32_t)(c & 0xFF) << (8 * (e & 3));
-    }
-    *reinterpret_cast<uint2*>(d0 + k) = make_uint2(w0[0], w0[1]);
-    *reinterpret_cast<uint2*>(d1 + k) = make_uint2(w1[0], w1[1]);
-    *reinterpret_cast<uint2*>(d2 + k) = make_uint2(w2[0], w2[1]);
+  for (int e = 0; e < 4; e++) {
+    // round to nearest through the 1.5 * 2^23 offset (|q| <= 2^20)
+    const int q = (int)(__float_as_uint(fmaf(v[e] * p1, p2, 12582912.0f)) - 0x4B400000u);
+    const int a = ((q + 64) & 127) - 64;
+    const int q1 = (q - a) >> 7;
+    const int b = ((q1 + 64) & 127) - 64;
+    const int c = (q1 - b) >> 7;
+    w0 |= (uint32_t)(a & 0xFF) << (8 * e);
+    w1 |= (uint32_t)(b & 0xFF) << (8 * e);
+    w2 |= (uint32_t)(c & 0xFF) << (8 * e);
+  }
+  if (k < K) {               // K is a multiple of 16: a group of four lies inside or outside
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(0 * MB + m) * K + k) = w0;
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(1 * MB + m) * K + k) = w1;
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(2 * MB + m) * K + k) = w2;
+  }
+  if (lane == 0) {
+    // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN
+    float unit = shift <= 126 ? __int_as_float((127 - shift) << 23) : __int_as_float(1 << (149 - shift));
+    if (bad) unit = __int_as_float(0x7FC00000);
+    units[(size_t)u * 16 + m] = unit;
   }
 }
 
@@ -229,7 +221,7 @@ __device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p,
 template <int NB>      // MMA N extent: 3 digit planes of MB = NB / 3 rows (16 -> 5, 32 -> 10, 48 -> 16)
 __global__ void __launch_bounds__(QT_THREADS, 1)
 qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                        const __grid_constant__ CUtensorMap tmap_s, const QtParams p) {
+                        const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_u, const QtParams p) {
   constexpr int MB = NB / 3;
   constexpr int X_BYTES = NB * QT_UNIT_K;
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
@@ -248,11 +240,11 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
   float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_merge + MB * QT_TILE_N);                 // [MB][128] output elements
+  float* s_un = reinterpret_cast<float*>(s_stage + MB * QT_TILE_N * 4);                    // [QT_STAGES][32]: unit[m,u] of the unit
+                                                                                           // (16 used; TMA wants 128-byte aligned slots)
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
   __shared__ unsigned s_last;
-  __shared__ float s_unit[16][2];     // unit[m] as two normal factors
-  __shared__ unsigned s_bad[16];
 
   // Lets a following digit kernel of this library be scheduled early (it waits for this grid to
   // finish before it reads or writes anything); kernels launched the ordinary way are unaffected.
@@ -276,12 +268,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     early = n_units < QT_STAGES ? n_units : QT_STAGES;
     int tile = tile0, g = g0;
     for (int it = 0; it < early; it++) {
-      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES);
+      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES + QT_UN_BYTES);
       tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
       if (++g == G) { g = 0; tile++; }
     }
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_s);
+    prefetch_tensormap(&tmap_u);
   }
   if (tid == 0) {
     for (int b = 0; b < NBUF; b++) mbar_init(&acc_full[b], 1);
@@ -294,16 +287,10 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
   // Everything above (and the weight stream) overlaps the kernels before this one in the stream.
-  // The threads that read what those kernels produce (digits, row exponents) or write what they may
+  // The threads that read what those kernels produce (digits, unit exponents) or write what they may
   // still use (output, workspace) wait for them here; the weight producer and the MMA issuers,
   // which touch only weights, shared memory and tensor memory, do not.
   if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (tid < 16) {        // read long before the first tile is finished (shared-memory barriers lie in between)
-    const int e = p.row_exp[tid], e1 = e / 2, e2 = e - e1;       // e lies in [-169, 108]
-    s_unit[tid][0] = __int_as_float((127 + e1) << 23);
-    s_unit[tid][1] = __int_as_float((127 + e2) << 23);
-    s_bad[tid] = p.row_bad[tid];
-  }
   if (tid == 0) QT_STAMP(1);
 
   if (warp == QT_TMA_WARP) {
@@ -316,7 +303,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (it >= early) {
           const int s = it % QT_STAGES;
           if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
-          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
+          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES + QT_UN_BYTES);
           tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
         }
         if (++g == G) { g = 0; tile++; }
@@ -339,6 +326,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
         tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+        tma_load_2d(s_un + s * 32, &tmap_u, 0, g, &full[s]);                                            // unit[0..16, g]
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
       }
@@ -392,17 +380,20 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
         for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
         const float sc = sc_slots[(it % QT_SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
+        float un[MB];
+#pragma unroll
+        for (int m = 0; m < MB; m++) un[m] = s_un[buf * 32 + m];
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        // s32 -> f32 through the 1.5 * 2^23 offset (|sum| < 2^22), digits recombined, group scale applied
+        // s32 -> f32 through the 1.5 * 2^23 offset (|sum| < 2^22), digits recombined, unit and group scale applied
 #pragma unroll
         for (int m = 0; m < MB; m++) {
           const float f0 = __uint_as_float(acc[m] + 0x4B400000u) - 12582912.0f;
           const float f1 = __uint_as_float(acc[MB + m] + 0x4B400000u) - 12582912.0f;
           const float f2 = __uint_as_float(acc[2 * MB + m] + 0x4B400000u) - 12582912.0f;
-          tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)), sc, tot[m]);
+          tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)) * un[m], sc, tot[m]);
         }
       }
       const bool tile_ends = (g == G - 1);
@@ -468,11 +459,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           if (write) {
             const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
 #pragma unroll
-            for (int m = 0; m < MB; m++) {
-              float v = tot[m] * s_unit[m][0] * s_unit[m][1];
-              if (s_bad[m]) v = __int_as_float(0x7FC00000);
-              tot[m] = v + bias;
-            }
+            for (int m = 0; m < MB; m++) tot[m] += bias;
             if (p.out_bf16) qt_store_rows<MB, true>(tot, p, tile * QT_TILE_N, nl, s_stage);
             else qt_store_rows<MB, false>(tot, p, tile * QT_TILE_N, nl, s_stage);
           }
@@ -550,7 +537,7 @@ int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsign
 static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
 static int qt_smem(int nb) {
-  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
+  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4 + QT_STAGES * 128;
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -571,7 +558,7 @@ bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
 struct QtLayout {
   int nb, mb, n_tiles, units_per_tile;
   long long total_units;
-  size_t off_counters, off_rows, off_digits, counter_bytes, off_partials, off_stamps, total;
+  size_t off_counters, off_units, off_digits, counter_bytes, off_partials, off_stamps, total;
 };
 
 static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
@@ -582,8 +569,8 @@ static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
   l.units_per_tile = (int)((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
   l.total_units = (long long)l.n_tiles * l.units_per_tile;
   l.off_counters = QT_HEADER;
-  l.off_rows = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
-  l.off_digits = l.off_rows + 256;                             // 16 exponents + 16 flags
+  l.off_units = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
+  l.off_digits = l.off_units + qt_align((size_t)l.units_per_tile * 16 * 4);   // unit[u][16]
   l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
   l.off_partials = l.counter_bytes;
   l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
@@ -624,7 +611,7 @@ static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0,
 }
 
 template <int NB>
-static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const QtParams& prm, bool overlap, cudaStream_t s) {
+static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tu, const QtParams& prm, bool overlap, cudaStream_t s) {
   static std::atomic<bool> configured[64];
   if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
     CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB)));
@@ -642,7 +629,7 @@ static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMa
   attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, prm));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, tu, prm));
   return CB_OK;
 }
 
@@ -654,8 +641,7 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
     if (reinterpret_cast<uintptr_t>(out[r]) & 15) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: outputs must be 16-byte aligned");
   const QtLayout l = qt_layout(d, p->blocks);
   uint8_t* w8 = (uint8_t*)ws;
-  int* row_exp = (int*)(w8 + l.off_rows);
-  unsigned* row_bad = (unsigned*)(w8 + l.off_rows + 64);
+  float* units = (float*)(w8 + l.off_units);
   int8_t* digits = (int8_t*)(w8 + l.off_digits);
 
   // timing diagnosis only: CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
@@ -663,7 +649,8 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)d.M);
+    const int tasks = (int)d.M * l.units_per_tile;
+    cfg.gridDim = dim3((unsigned)((tasks + QX_THREADS / 32 - 1) / (QX_THREADS / 32)));
     cfg.blockDim = dim3(QX_THREADS);
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -672,12 +659,13 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (d.x_dtype == CB_BF16)
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units));
     else
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.K, l.mb, digits, row_exp, row_bad));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units));
   }
 
-  CUtensorMap tw, tx, ts;
+  CUtensorMap tw, tx, ts, tu;
+  CB_TRY(qt_encode_2d(&tu, units, 4, 16, (uint64_t)l.units_per_tile, 16, 1));
   const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
   CB_TRY(qt_encode_2d(&tw, in[1], 1, (uint64_t)d.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
   CB_TRY(qt_encode_2d(&tx, digits, 1, (uint64_t)d.K, (uint64_t)l.nb, QT_UNIT_K, (uint32_t)l.nb));
@@ -693,8 +681,6 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   prm.out_col0 = (int)(d.N * (g > 1 ? d.gather_rank : 0));
   prm.status = (unsigned*)w8;
   prm.counters = (unsigned*)(w8 + l.off_counters);
-  prm.row_exp = row_exp;
-  prm.row_bad = row_bad;
   prm.partials = (float*)(w8 + l.off_partials);
   prm.M = (int)d.M; prm.K = (int)d.K; prm.N = (int)d.N;
   prm.n_tiles = l.n_tiles;
@@ -706,9 +692,9 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
   prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
   switch (l.nb) {
-    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, true, s);
-    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, true, s);
-    default: return qt_launch_t<48>(p, tw, tx, ts, prm, true, s);
+    case 16: return qt_launch_t<16>(p, tw, tx, ts, tu, prm, true, s);
+    case 32: return qt_launch_t<32>(p, tw, tx, ts, tu, prm, true, s);
+    default: return qt_launch_t<48>(p, tw, tx, ts, tu, prm, true, s);
   }
 }
 
