@@ -94,13 +94,16 @@ __device__ __forceinline__ void qx_load4(const float* x, size_t m, int K, int k,
 // M * ceil(K/128) tasks run at once.
 template <typename XT>
 __global__ void __launch_bounds__(QX_THREADS)
-qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int8_t* __restrict__ digits, float* __restrict__ units) {
+qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int8_t* __restrict__ digits, float* __restrict__ units,
+                      unsigned long long* dbg) {
   // The kernel that consumes the digits may start its own set-up now; it waits for this grid to
   // finish before it reads them.  This grid in turn may have been scheduled while the kernel
   // before it in the stream (which may produce x, and may still read the digit buffer) was
   // running: it waits for that kernel to finish before it touches either.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[0] = global_ns();      // timing diagnosis only
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[1] = global_ns();
   const int lane = threadIdx.x & 31;
   const int task = blockIdx.x * (QX_THREADS / 32) + (threadIdx.x >> 5);
   if (task >= M * G) return;
@@ -147,6 +150,7 @@ qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int
     if (bad) unit = __int_as_float(0x7FC00000);
     units[(size_t)u * 16 + m] = unit;
   }
+  if (dbg && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) dbg[2] = global_ns();
 }
 
 // ---------------------------------------------------------------------------
@@ -574,7 +578,7 @@ static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
   l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
   l.off_partials = l.counter_bytes;
   l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
-  l.total = l.off_stamps + (size_t)blocks * 8 * 8;
+  l.total = l.off_stamps + (size_t)blocks * 8 * 8 + 64;
   return l;
 }
 
@@ -649,6 +653,7 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
+    unsigned long long* xdbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps + (size_t)p->blocks * 64) : nullptr;
     const int tasks = (int)d.M * l.units_per_tile;
     cfg.gridDim = dim3((unsigned)((tasks + QX_THREADS / 32 - 1) / (QX_THREADS / 32)));
     cfg.blockDim = dim3(QX_THREADS);
@@ -659,9 +664,9 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (d.x_dtype == CB_BF16)
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units, xdbg));
     else
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units, xdbg));
   }
 
   CUtensorMap tw, tx, ts, tu;
