@@ -53,6 +53,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Blackwell's packed-pair f32 arithmetic and three-input max/min: the softmax warps are bound by
+// instruction issue, so scaling, the running sum and the row extreme take half the instructions.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (d0, d1) = (a0, a1) * s + m
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float s, float m) {
+  asm("{\n\t.reg .b64 ra, rs, rm, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rs, {%4, %4};\n\tmov.b64 rm, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rs, rm;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(s), "f"(m));
+}
+// (d0, d1) += (a0, a1)
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
 // two f32 -> packed bf16x2 (format 1) or f16x2 (format 0), round to nearest even
 __device__ __forceinline__ uint32_t pack16x2(float lo, float hi, int ab_format) {
   if (ab_format == 1) {
@@ -260,15 +283,15 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       float ea = __uint_as_float(sr[0][0]), eb = __uint_as_float(sr[2][0]);
       if (pos_scale) {
 #pragma unroll
-        for (int i = 1; i < 64; i++) {
-          ea = fmaxf(ea, __uint_as_float(sr[i >> 5][i & 31]));
-          eb = fmaxf(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]));
+        for (int i = 0; i < 64; i += 2) {
+          ea = max3(ea, __uint_as_float(sr[i >> 5][i & 31]), __uint_as_float(sr[i >> 5][(i & 31) + 1]));
+          eb = max3(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]), __uint_as_float(sr[2 + (i >> 5)][(i & 31) + 1]));
         }
       } else {
 #pragma unroll
-        for (int i = 1; i < 64; i++) {
-          ea = fminf(ea, __uint_as_float(sr[i >> 5][i & 31]));
-          eb = fminf(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]));
+        for (int i = 0; i < 64; i += 2) {
+          ea = min3(ea, __uint_as_float(sr[i >> 5][i & 31]), __uint_as_float(sr[i >> 5][(i & 31) + 1]));
+          eb = min3(eb, __uint_as_float(sr[2 + (i >> 5)][i & 31]), __uint_as_float(sr[2 + (i >> 5)][(i & 31) + 1]));
         }
       }
       const float ext = pos_scale ? fmaxf(ea, eb) : fminf(ea, eb);
