@@ -20,7 +20,8 @@
 //                           (n tile, k unit) pairs:
 //       warp 8   TMA producer: weight tiles into an 8-stage ring (the first ones are requested
 //                before the digit kernel has finished)
-//       warp 10  TMA producer: the digit tile, the 128 scales and the 16 unit[m,u] of each unit
+//       warps 10, 12, 13  TMA producers: the digit tile, the 128 scales and the 16 unit[m,u] of each
+//                unit (one issuing thread per kind of load)
 //       warps 9, 11  MMA issuers on alternate units: 4 MMAs (K = 32) per unit into one of 8 TMEM
 //                accumulators
 //       warps 0-7 epilogue as above, two groups of four warps on alternate units; a tile whose
@@ -43,8 +44,8 @@ constexpr int QT_TILE_N = 128;
 constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
 constexpr int QT_STAGES = 8;
-constexpr int QT_THREADS = 384;                       // warps 0-7 epilogue, 8 weight TMA, 9 and 11 MMA, 10 side TMA
-constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;
+constexpr int QT_THREADS = 448;                       // warps 0-7 epilogue, 8 weight TMA, 9 and 11 MMA, 10/12/13 side TMA
+constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11, QT_SCALE_WARP = 12, QT_UNIT_WARP = 13;
 constexpr int QT_TMEM_COLS = 512;
 constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
@@ -294,7 +295,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   // The threads that read what those kernels produce (digits, unit exponents) or write what they may
   // still use (output, workspace) wait for them here; the weight producer and the MMA issuers,
   // which touch only weights, shared memory and tensor memory, do not.
-  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_UNIT_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid == 0) QT_STAMP(1);
 
   if (warp == QT_TMA_WARP) {
@@ -313,9 +314,11 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (++g == G) { g = 0; tile++; }
       }
     }
-  } else if (warp == QT_SIDE_WARP) {
-    // ------------------------------ TMA producer: digits and scales ------------
-    // Their bytes count towards the same stage barrier; the weight producer announces the total.
+  } else if (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP || warp == QT_UNIT_WARP) {
+    // ------------------------------ TMA producers: digits, scales, unit[m,u] ----
+    // Three small loads per unit, one issuing thread each (a thread that issued all three spent most
+    // of a unit's time on them, which set the pace of the whole pipeline).  Their bytes count towards
+    // the same stage barrier; the weight producer announces the total.
     // The 128 scales of a unit sit in a slot that is reused QT_SC_SLOTS units later, by which time
     // the epilogue of this unit has read them (it does so before it releases the accumulator,
     // which the MMA of unit it+8 waits for, which the stage reuse of unit it+16 waits for).
@@ -328,9 +331,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (it >= QT_STAGES) {
           if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
         }
-        tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
-        tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
-        tma_load_2d(s_un + s * 32, &tmap_u, 0, g, &full[s]);                                            // unit[0..16, g]
+        if (warp == QT_SIDE_WARP) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
+        else if (warp == QT_SCALE_WARP) tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+        else tma_load_2d(s_un + s * 32, &tmap_u, 0, g, &full[s]);                                                                 // unit[0..16, g]
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
       }
