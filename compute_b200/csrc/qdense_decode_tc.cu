@@ -44,12 +44,14 @@ constexpr int QT_TILE_N = 128;
 constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
 constexpr int QT_STAGES = 8;
-constexpr int QT_THREADS = 448;                       // warps 0-7 epilogue, 8 weight TMA, 9 and 11 MMA, 10/12/13 side TMA
-constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11, QT_SCALE_WARP = 12, QT_UNIT_WARP = 13;
+constexpr int QT_THREADS = 512;                       // warps 0-7 epilogue, 9 and 11 MMA, six TMA producers
+constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;   // weights (even units), MMA, digits (even), MMA
+constexpr int QT_TMA2_WARP = 12, QT_SIDE2_WARP = 13;                                      // weights, digits of the odd units
+constexpr int QT_SCALE_WARP = 14, QT_SCALE2_WARP = 15;                                    // scales of the even / odd units
+constexpr int QT_XROWS_EXTRA = 8;                      // rows below the digits in a digit tile; the first holds unit[m,u]
 constexpr int QT_TMEM_COLS = 512;
 constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
-constexpr int QT_UN_BYTES = 16 * 4;                     // unit[m,u] of the 16 rows of one k unit
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
 
 constexpr int QT_MAX_RANKS = 8;
@@ -91,12 +93,13 @@ __device__ __forceinline__ void qx_load4(const float* x, size_t m, int K, int k,
 
 // One warp per (row m, 128-wide k unit u): the unit's largest finite |x| fixes unit[m,u] = 2^-shift
 // (20 bits below it), every element becomes three signed base-128 digits, and unit[m,u] goes to
-// units[u][m] (NaN when the unit holds inf or NaN).  No pass over the whole row is needed, so all
+// row NB of the digit matrix (NaN when the unit holds inf or NaN).  No pass over the whole row is needed, so all
 // M * ceil(K/128) tasks run at once.
 template <typename XT>
 __global__ void __launch_bounds__(QX_THREADS)
-qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int8_t* __restrict__ digits, float* __restrict__ units,
+qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int NB, int G, int8_t* __restrict__ digits,
                       unsigned long long* dbg) {
+  const int MB = NB / 3;
   // The kernel that consumes the digits may start its own set-up now; it waits for this grid to
   // finish before it reads them.  This grid in turn may have been scheduled while the kernel
   // before it in the stream (which may produce x, and may still read the digit buffer) was
@@ -140,16 +143,18 @@ qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int MB, int G, int
     w1 |= (uint32_t)(b & 0xFF) << (8 * e);
     w2 |= (uint32_t)(c & 0xFF) << (8 * e);
   }
+  const size_t Kp = (size_t)G * QT_UNIT_K;     // row stride of the digit matrix (whole units)
   if (k < K) {               // K is a multiple of 16: a group of four lies inside or outside
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(0 * MB + m) * K + k) = w0;
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(1 * MB + m) * K + k) = w1;
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(2 * MB + m) * K + k) = w2;
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(0 * MB + m) * Kp + k) = w0;
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(1 * MB + m) * Kp + k) = w1;
+    *reinterpret_cast<uint32_t*>(digits + (size_t)(2 * MB + m) * Kp + k) = w2;
   }
   if (lane == 0) {
-    // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN
+    // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN.  It travels
+    // with the digits: row NB of the matrix (the first below the digit rows) holds, for every unit, its 16 floats.
     float unit = shift <= 126 ? __int_as_float((127 - shift) << 23) : __int_as_float(1 << (149 - shift));
     if (bad) unit = __int_as_float(0x7FC00000);
-    units[(size_t)u * 16 + m] = unit;
+    *reinterpret_cast<float*>(digits + (size_t)NB * Kp + (size_t)u * QT_UNIT_K + 4 * m) = unit;
   }
   if (dbg && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) dbg[2] = global_ns();
 }
@@ -226,9 +231,9 @@ __device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p,
 template <int NB>      // MMA N extent: 3 digit planes of MB = NB / 3 rows (16 -> 5, 32 -> 10, 48 -> 16)
 __global__ void __launch_bounds__(QT_THREADS, 1)
 qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                        const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_u, const QtParams p) {
+                        const __grid_constant__ CUtensorMap tmap_s, const QtParams p) {
   constexpr int MB = NB / 3;
-  constexpr int X_BYTES = NB * QT_UNIT_K;
+  constexpr int X_BYTES = (NB + QT_XROWS_EXTRA) * QT_UNIT_K;     // digit rows, then the row of unit[m,u]
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
   constexpr int NBUF = QT_STAGES;
   static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
@@ -245,8 +250,6 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
   float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_merge + MB * QT_TILE_N);                 // [MB][128] output elements
-  float* s_un = reinterpret_cast<float*>(s_stage + MB * QT_TILE_N * 4);                    // [QT_STAGES][32]: unit[m,u] of the unit
-                                                                                           // (16 used; TMA wants 128-byte aligned slots)
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
   __shared__ unsigned s_last;
@@ -262,24 +265,12 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
   const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
 
-  // The producer thread owns the stage barriers: it sets them up itself and starts the weight
-  // stream at once.  Weights do not depend on the digit kernel, so with a programmatic dependent
-  // launch the first QT_STAGES tiles are already in flight while that kernel still runs.
-  int early = 0;
   if (warp == QT_TMA_WARP && lane == 0) {
     for (int s = 0; s < QT_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
     fence_barrier_init();
     prefetch_tensormap(&tmap_w);
-    early = n_units < QT_STAGES ? n_units : QT_STAGES;
-    int tile = tile0, g = g0;
-    for (int it = 0; it < early; it++) {
-      mbar_expect_tx(&full[it], STAGE_BYTES + QT_SC_BYTES + QT_UN_BYTES);
-      tma_load_2d(base + it * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[it]);   // [128 k][128 n]
-      if (++g == G) { g = 0; tile++; }
-    }
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_s);
-    prefetch_tensormap(&tmap_u);
   }
   if (tid == 0) {
     for (int b = 0; b < NBUF; b++) mbar_init(&acc_full[b], 1);
@@ -291,49 +282,56 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
-  // Everything above (and the weight stream) overlaps the kernels before this one in the stream.
-  // The threads that read what those kernels produce (digits, unit exponents) or write what they may
-  // still use (output, workspace) wait for them here; the weight producer and the MMA issuers,
-  // which touch only weights, shared memory and tensor memory, do not.
-  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_UNIT_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Everything above overlaps the kernels before this one in the stream.  The threads that read what
+  // those kernels produce (digits, unit exponents) or write what they may still use (output,
+  // workspace) wait for them here; the weight and scale producers and the MMA issuers, which touch
+  // only weights, shared memory and tensor memory, do not: with a programmatic dependent launch the
+  // first QT_STAGES weight tiles and scale rows are requested while the digit kernel still runs.
+  // (Requesting them before the barrier above, by one thread, held the whole CTA back and was slower.)
+  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid == 0) QT_STAMP(1);
 
-  if (warp == QT_TMA_WARP) {
-    // ------------------------------ TMA producer: weights ----------------------
-    // One thread can issue a copy roughly every 50 ns and a unit needs three, so the weight
-    // tiles and the two small side loads have an issuing thread each (in different warps).
+  if (warp == QT_TMA_WARP || warp == QT_TMA2_WARP) {
+    // ------------------------------ TMA producers: weights ----------------------
+    // Issuing one tensor copy keeps a thread busy for several hundred cycles, more than half of what
+    // a unit's bytes take to arrive, so every kind of load (weights, digits, scales) has two issuing
+    // threads in different warps, on the even and the odd units.
     if (lane == 0) {
+      const int mine = warp == QT_TMA_WARP ? 0 : 1;
       int tile = tile0, g = g0;
       for (int it = 0; it < n_units; it++) {
-        if (it >= early) {
+        if ((it & 1) == mine) {
           const int s = it % QT_STAGES;
-          if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
-          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES + QT_UN_BYTES);
+          if (it >= QT_STAGES) {
+            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          }
+          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
           tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
         }
         if (++g == G) { g = 0; tile++; }
       }
     }
-  } else if (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP || warp == QT_UNIT_WARP) {
-    // ------------------------------ TMA producers: digits, scales, unit[m,u] ----
-    // Three small loads per unit, one issuing thread each (a thread that issued all three spent most
-    // of a unit's time on them, which set the pace of the whole pipeline).  Their bytes count towards
-    // the same stage barrier; the weight producer announces the total.
+  } else if (warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
+    // ------------------------------ TMA producers: digits (with unit[m,u]) and scales ----
+    // Their bytes count towards the same stage barrier; the weight producer announces the total.
     // The 128 scales of a unit sit in a slot that is reused QT_SC_SLOTS units later, by which time
     // the epilogue of this unit has read them (it does so before it releases the accumulator,
     // which the MMA of unit it+8 waits for, which the stage reuse of unit it+16 waits for).
     if (lane == 0) {
+      const int mine = (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP) ? 0 : 1;
+      const bool digits = warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP;
       const int gpr = p.scale_group ? p.scale_group / QT_UNIT_K : 0;    // units per scale row
       int tile = tile0, g = g0;
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
       for (int it = 0; it < n_units; it++) {
-        const int s = it % QT_STAGES;
-        if (it >= QT_STAGES) {
-          if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        if ((it & 1) == mine) {
+          const int s = it % QT_STAGES;
+          if (it >= QT_STAGES) {
+            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          }
+          if (digits) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB + 8 rows][128 k]
+          else tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
         }
-        if (warp == QT_SIDE_WARP) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB rows][128 k]
-        else if (warp == QT_SCALE_WARP) tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
-        else tma_load_2d(s_un + s * 32, &tmap_u, 0, g, &full[s]);                                                                 // unit[0..16, g]
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
       }
@@ -387,9 +385,10 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
         for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
         const float sc = sc_slots[(it % QT_SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
+        const float* s_xun = reinterpret_cast<const float*>(base + buf * STAGE_BYTES + QT_W_BYTES + NB * QT_UNIT_K);   // row NB of the digit tile
         float un[MB];
 #pragma unroll
-        for (int m = 0; m < MB; m++) un[m] = s_un[buf * 32 + m];
+        for (int m = 0; m < MB; m++) un[m] = s_xun[m];
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -544,7 +543,7 @@ int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsign
 static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
 static int qt_smem(int nb) {
-  return 1024 + QT_STAGES * (QT_W_BYTES + nb * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4 + QT_STAGES * 128;
+  return 1024 + QT_STAGES * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -565,7 +564,7 @@ bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
 struct QtLayout {
   int nb, mb, n_tiles, units_per_tile;
   long long total_units;
-  size_t off_counters, off_units, off_digits, counter_bytes, off_partials, off_stamps, total;
+  size_t off_counters, off_digits, counter_bytes, off_partials, off_stamps, total;
 };
 
 static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
@@ -576,9 +575,9 @@ static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
   l.units_per_tile = (int)((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
   l.total_units = (long long)l.n_tiles * l.units_per_tile;
   l.off_counters = QT_HEADER;
-  l.off_units = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
-  l.off_digits = l.off_units + qt_align((size_t)l.units_per_tile * 16 * 4);   // unit[u][16]
-  l.counter_bytes = qt_align(l.off_digits + (size_t)l.nb * d.K);   // all of this starts as zeros
+  l.off_digits = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
+  // [NB digit rows + 8][128 * units]: row NB holds unit[m,u], 16 floats at the start of every unit's 128 bytes
+  l.counter_bytes = qt_align(l.off_digits + (size_t)(l.nb + QT_XROWS_EXTRA) * l.units_per_tile * QT_UNIT_K);   // all of this starts as zeros
   l.off_partials = l.counter_bytes;
   l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
   l.total = l.off_stamps + (size_t)blocks * 8 * 8 + 64;
@@ -623,7 +622,7 @@ static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0,
 }
 
 template <int NB>
-static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tu, const QtParams& prm, bool overlap, cudaStream_t s) {
+static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const QtParams& prm, bool overlap, cudaStream_t s) {
   static std::atomic<bool> configured[64];
   if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
     CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB)));
@@ -641,7 +640,7 @@ static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMa
   attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, tu, prm));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, prm));
   return CB_OK;
 }
 
@@ -653,7 +652,6 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
     if (reinterpret_cast<uintptr_t>(out[r]) & 15) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: outputs must be 16-byte aligned");
   const QtLayout l = qt_layout(d, p->blocks);
   uint8_t* w8 = (uint8_t*)ws;
-  float* units = (float*)(w8 + l.off_units);
   int8_t* digits = (int8_t*)(w8 + l.off_digits);
 
   // timing diagnosis only: CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
@@ -672,16 +670,15 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (d.x_dtype == CB_BF16)
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units, xdbg));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.nb, l.units_per_tile, digits, xdbg));
     else
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.mb, l.units_per_tile, digits, units, xdbg));
+      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.nb, l.units_per_tile, digits, xdbg));
   }
 
-  CUtensorMap tw, tx, ts, tu;
-  CB_TRY(qt_encode_2d(&tu, units, 4, 16, (uint64_t)l.units_per_tile, 16, 1));
+  CUtensorMap tw, tx, ts;
   const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
   CB_TRY(qt_encode_2d(&tw, in[1], 1, (uint64_t)d.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
-  CB_TRY(qt_encode_2d(&tx, digits, 1, (uint64_t)d.K, (uint64_t)l.nb, QT_UNIT_K, (uint32_t)l.nb));
+  CB_TRY(qt_encode_2d(&tx, digits, 1, (uint64_t)l.units_per_tile * QT_UNIT_K, (uint64_t)(l.nb + QT_XROWS_EXTRA), QT_UNIT_K, (uint32_t)(l.nb + QT_XROWS_EXTRA)));
   CB_TRY(qt_encode_2d(&ts, in[2], 4, (uint64_t)d.N, scale_rows, QT_TILE_N, 1));
   QtParams prm;
   memset(&prm, 0, sizeof(prm));
@@ -705,9 +702,9 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
   prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
   switch (l.nb) {
-    case 16: return qt_launch_t<16>(p, tw, tx, ts, tu, prm, true, s);
-    case 32: return qt_launch_t<32>(p, tw, tx, ts, tu, prm, true, s);
-    default: return qt_launch_t<48>(p, tw, tx, ts, tu, prm, true, s);
+    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, true, s);
+    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, true, s);
+    default: return qt_launch_t<48>(p, tw, tx, ts, prm, true, s);
   }
 }
 
