@@ -40,17 +40,21 @@ namespace cb {
 
 using namespace tc;
 
+#ifndef QT_S16
+#define QT_S16 11
+#endif
 constexpr int QT_TILE_N = 128;
 constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
-constexpr int QT_STAGES = 8;
+// Stages of the weight ring (each with its digit tile and its TMEM accumulator), by digit-tile rows:
+// what shared memory holds.
+__host__ __device__ constexpr int qt_stages(int nb) { return nb == 16 ? QT_S16 : (nb == 32 ? 9 : 8); }
 constexpr int QT_THREADS = 512;                       // warps 0-7 epilogue, 9 and 11 MMA, six TMA producers
 constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;   // weights (even units), MMA, digits (even), MMA
 constexpr int QT_TMA2_WARP = 12, QT_SIDE2_WARP = 13;                                      // weights, digits of the odd units
 constexpr int QT_SCALE_WARP = 14, QT_SCALE2_WARP = 15;                                    // scales of the even / odd units
 constexpr int QT_XROWS_EXTRA = 8;                      // rows below the digits in a digit tile; the first holds unit[m,u]
 constexpr int QT_TMEM_COLS = 512;
-constexpr int QT_SC_SLOTS = 16;                         // scale rows in flight: stages + accumulators
 constexpr int QT_SC_BYTES = QT_TILE_N * 4;
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
 
@@ -235,20 +239,22 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int MB = NB / 3;
   constexpr int X_BYTES = (NB + QT_XROWS_EXTRA) * QT_UNIT_K;     // digit rows, then the row of unit[m,u]
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
-  constexpr int NBUF = QT_STAGES;
+  constexpr int STAGES = qt_stages(NB);
+  constexpr int NBUF = STAGES;
+  constexpr int SC_SLOTS = 2 * STAGES;             // scale rows in flight: stages + accumulators
   static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
-  static_assert(QT_SC_SLOTS >= QT_STAGES + NBUF, "a scale slot must outlive its stage and its accumulator");
+  static_assert(SC_SLOTS >= STAGES + NBUF, "a scale slot must outlive its stage and its accumulator");
   extern __shared__ uint8_t qt_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qt_smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base + QT_STAGES * STAGE_BYTES);
-  // Stage s and accumulator s travel together (QT_STAGES == NBUF): a unit's stage is refilled once
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + STAGES * STAGE_BYTES);
+  // Stage s and accumulator s travel together (STAGES == NBUF): a unit's stage is refilled once
   // the epilogue has read its accumulator, so the MMA thread waits on one barrier per unit and
   // commits once, which keeps its serial loop short.
-  uint64_t* full = bars;                       // [QT_STAGES] TMA -> MMA
-  uint64_t* acc_full = bars + QT_STAGES;       // [NBUF] MMA -> epilogue
+  uint64_t* full = bars;                       // [STAGES] TMA -> MMA
+  uint64_t* acc_full = bars + STAGES;       // [NBUF] MMA -> epilogue
   uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> TMA producers
-  float* sc_slots = reinterpret_cast<float*>(base + QT_STAGES * STAGE_BYTES + 512);        // [QT_SC_SLOTS][128]
-  float* s_merge = sc_slots + QT_SC_SLOTS * QT_TILE_N;                                     // [MB][128]
+  float* sc_slots = reinterpret_cast<float*>(base + STAGES * STAGE_BYTES + 512);        // [SC_SLOTS][128]
+  float* s_merge = sc_slots + SC_SLOTS * QT_TILE_N;                                     // [MB][128]
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_merge + MB * QT_TILE_N);                 // [MB][128] output elements
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
@@ -266,7 +272,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
 
   if (warp == QT_TMA_WARP && lane == 0) {
-    for (int s = 0; s < QT_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
     fence_barrier_init();
     prefetch_tensormap(&tmap_w);
     prefetch_tensormap(&tmap_x);
@@ -286,7 +292,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   // those kernels produce (digits, unit exponents) or write what they may still use (output,
   // workspace) wait for them here; the weight and scale producers and the MMA issuers, which touch
   // only weights, shared memory and tensor memory, do not: with a programmatic dependent launch the
-  // first QT_STAGES weight tiles and scale rows are requested while the digit kernel still runs.
+  // first STAGES weight tiles and scale rows are requested while the digit kernel still runs.
   // (Requesting them before the barrier above, by one thread, held the whole CTA back and was slower.)
   if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid == 0) QT_STAMP(1);
@@ -301,9 +307,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       int tile = tile0, g = g0;
       for (int it = 0; it < n_units; it++) {
         if ((it & 1) == mine) {
-          const int s = it % QT_STAGES;
-          if (it >= QT_STAGES) {
-            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          const int s = it % STAGES;
+          if (it >= STAGES) {
+            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
           mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
           tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
@@ -314,9 +320,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   } else if (warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
     // ------------------------------ TMA producers: digits (with unit[m,u]) and scales ----
     // Their bytes count towards the same stage barrier; the weight producer announces the total.
-    // The 128 scales of a unit sit in a slot that is reused QT_SC_SLOTS units later, by which time
+    // The 128 scales of a unit sit in a slot that is reused SC_SLOTS units later, by which time
     // the epilogue of this unit has read them (it does so before it releases the accumulator,
-    // which the MMA of unit it+8 waits for, which the stage reuse of unit it+16 waits for).
+    // which the MMA of unit it+STAGES waits for, which the stage reuse of unit it+2*STAGES waits for).
     if (lane == 0) {
       const int mine = (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP) ? 0 : 1;
       const bool digits = warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP;
@@ -325,12 +331,12 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
       for (int it = 0; it < n_units; it++) {
         if ((it & 1) == mine) {
-          const int s = it % QT_STAGES;
-          if (it >= QT_STAGES) {
-            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / QT_STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+          const int s = it % STAGES;
+          if (it >= STAGES) {
+            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
           if (digits) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB + 8 rows][128 k]
-          else tma_load_2d(sc_slots + (it % QT_SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+          else tma_load_2d(sc_slots + (it % SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
         }
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
@@ -349,8 +355,8 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const uint64_t db0 = smem_desc_sw128(smem_u32(base) + QT_W_BYTES, 16, 1024);
       const uint32_t idesc = p.idesc;
       for (int it = mine; it < n_units; it += 2) {
-        const int s = it % QT_STAGES;
-        if (!mbar_wait(&full[s], (uint32_t)((it / QT_STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        const int s = it % STAGES;
+        if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
         tc_fence_after();
         const uint64_t da = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
         const uint32_t d_tmem = tmem_base + (uint32_t)(s * NB);
@@ -384,7 +390,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         uint32_t acc[NB];
 #pragma unroll
         for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
-        const float sc = sc_slots[(it % QT_SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
+        const float sc = sc_slots[(it % SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
         const float* s_xun = reinterpret_cast<const float*>(base + buf * STAGE_BYTES + QT_W_BYTES + NB * QT_UNIT_K);   // row NB of the digit tile
         float un[MB];
 #pragma unroll
@@ -543,7 +549,8 @@ int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsign
 static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
 static int qt_smem(int nb) {
-  return 1024 + QT_STAGES * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + QT_SC_SLOTS * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
+  const int st = qt_stages(nb);
+  return 1024 + st * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + 2 * st * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
