@@ -37,7 +37,7 @@ METRIC = "int8 quantized-dense GB/s & TFLOP/s vs roofline (1/2/4/8 B200) vs goba
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
 # (profiles/); None until a capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = {1: 60_691_968 + 219_136, 4: None, 16: 60_830_208 + 194_304}   # profiles/qdense_decode_tc_config3_M16.md
+NCU_TRAFFIC_BYTES = {1: 60_721_664 + 210_432, 4: None, 16: 60_858_624 + 261_888}   # profiles/qdense_decode_tc_config3_M16.md
 
 
 def algorithmic_bytes(M: int, n_cols: int) -> int:
