@@ -648,8 +648,7 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
   const char* op = "FusedQuantizedDense";
   CB_TRY(check_fn(f, op));
   if (scheme == 2) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: GGML quantization scheme is not implemented by the cuda backend", op);
-  if (scheme == 1) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: NF4 quantization scheme is not implemented by the cuda backend", op);
-  if (scheme != 0) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: unknown quantization scheme %d", op, scheme);
+  if (scheme != 0 && scheme != 1) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: unknown quantization scheme %d", op, scheme);
   CB_TRY(check_values(f, op, {x, weights, scale}));
   if (zero_point) CB_TRY(check_values(f, op, {zero_point}));
   if (bias) CB_TRY(check_values(f, op, {bias}));
@@ -662,7 +661,9 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
     return fail(CB_ERR_INVALID_ARG, "%s: weights must be [%lld, N], got %s", op, (long long)K, weights->shape.str().c_str());
   const int64_t N = weights->shape.dims[1];
   if (weights->shape.dtype != CB_I8 && weights->shape.dtype != CB_U8)
-    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: Linear unsupported weight type %s", op, cb::dtype_name(weights->shape.dtype));
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: %s unsupported weight type %s", op, scheme == 1 ? "NF4" : "Linear", cb::dtype_name(weights->shape.dtype));
+  // NF4 uses a fixed lookup table and takes no zero points (quantizeddense.go:126-129)
+  if (scheme == 1 && zero_point) return fail(CB_ERR_INVALID_ARG, "%s: ZeroPoint must be nil for NF4 quantization scheme", op);
   if (block_size <= 0) return fail(CB_ERR_INVALID_ARG, "%s: BlockSize must be positive, got %lld", op, (long long)block_size);
   int layout;
   std::vector<int64_t> want;
@@ -697,6 +698,7 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
   n->qd.has_zero_point = zero_point ? 1 : 0;
   n->qd.has_bias = bias ? 1 : 0;
   n->qd.activation = activation;
+  n->qd.scheme = scheme;
   n->qd.variant = f->builder->be->fallback_only ? CB_QDENSE_GENERIC : CB_QDENSE_AUTO;
   *v = n;
   return CB_OK;

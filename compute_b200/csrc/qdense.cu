@@ -32,9 +32,36 @@ constexpr int QG_COLS = 128;
 constexpr int QG_ROWS = 8;
 constexpr int QG_KT = 256;
 
-template <typename XT, typename WT>
+// Weight element (k, n) as a float.  8-bit types are read as they are; Int4 / Uint4 are packed two
+// per byte over the flat element order, low nibble first, Int4 nibbles 8..15 meaning -8..-1
+// (internal/gobackend/ops/convertdtype.go:199-226).  Under the NF4 scheme the low four bits of the
+// element index the NormalFloat4 table of QLoRA (fused_ops.go:114-121; quantizeddense.go:586-609).
+struct PackedI4 {};
+struct PackedU4 {};
+__constant__ float kNf4Table[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+template <typename WT> struct WeightAt {
+  static __device__ __forceinline__ int get(const void* w, int64_t e) { return (int)reinterpret_cast<const WT*>(w)[e]; }
+};
+template <> struct WeightAt<PackedU4> {
+  static __device__ __forceinline__ int get(const void* w, int64_t e) {
+    const int b = reinterpret_cast<const uint8_t*>(w)[e >> 1];
+    return (e & 1) ? (b >> 4) : (b & 0x0F);
+  }
+};
+template <> struct WeightAt<PackedI4> {
+  static __device__ __forceinline__ int get(const void* w, int64_t e) {
+    const int v = WeightAt<PackedU4>::get(w, e);
+    return v >= 8 ? v - 16 : v;
+  }
+};
+
+template <typename XT, typename WT, bool NF4>
 __global__ void __launch_bounds__(QG_COLS)
-qdense_generic_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ scales,
+qdense_generic_kernel(const XT* __restrict__ x, const void* __restrict__ w, const float* __restrict__ scales,
                       const float* __restrict__ zps, const float* __restrict__ bias, XT* __restrict__ out,
                       int64_t M, int64_t K, int64_t N, int layout, int64_t block, int act) {
   __shared__ float xs[QG_ROWS][QG_KT];
@@ -56,7 +83,8 @@ qdense_generic_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const 
     if (n < N) {
       for (int kk = 0; kk < kt; kk++) {
         const int64_t k = kb + kk;
-        const float wf = (float)w[k * N + n];
+        const int wi = WeightAt<WT>::get(w, k * N + n);
+        const float wf = NF4 ? kNf4Table[wi & 0x0F] : (float)wi;
         int64_t si;
         if (layout == CB_SCALE_REF) si = k * nblk + n / block;
         else if (layout == CB_SCALE_CHANNEL) si = n;
@@ -611,8 +639,14 @@ int qdense_plan(cb_plan* p) {
   if (d.M < 0 || d.K < 0 || d.N < 0) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: negative dimension");
   if (d.x_dtype != CB_F32 && d.x_dtype != CB_BF16)
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x must be float32 (or bfloat16), got %s", dtype_name(d.x_dtype));
-  if (d.w_dtype != CB_I8 && d.w_dtype != CB_U8)
-    return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: Linear unsupported weight type %s", dtype_name(d.w_dtype));
+  if (d.scheme != CB_QUANT_LINEAR && d.scheme != CB_QUANT_NF4)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: unknown quantization scheme %d", d.scheme);
+  if (d.w_dtype != CB_I8 && d.w_dtype != CB_U8 && d.w_dtype != CB_I4 && d.w_dtype != CB_U4)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: %s unsupported weight type %s", d.scheme == CB_QUANT_NF4 ? "NF4" : "Linear", dtype_name(d.w_dtype));
+  if (d.scheme == CB_QUANT_NF4 && d.has_zero_point)
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: ZeroPoint must be nil for NF4 quantization scheme");
+  // the streaming and tensor-core kernels read int8 / uint8 Linear weights; everything else is the generic kernel's
+  const bool generic_only = d.scheme != CB_QUANT_LINEAR || d.w_dtype == CB_I4 || d.w_dtype == CB_U4;
   if (d.scale_layout < CB_SCALE_REF || d.scale_layout > CB_SCALE_KGROUP)
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown scale layout %d", d.scale_layout);
   if (d.scale_layout != CB_SCALE_CHANNEL && d.block_size <= 0)
@@ -625,10 +659,12 @@ int qdense_plan(cb_plan* p) {
 
   int variant = d.variant;
   std::string why;
-  const bool can_decode = decode_eligible(d, &why);
+  const bool can_decode = !generic_only && decode_eligible(d, &why);
+  if (generic_only) why = "packed 4-bit weights and the NF4 scheme run on the generic kernel";
   std::string why_prefill, why_tc;
-  const bool can_decode_tc = qdense_decode_tc_eligible(d, &why_tc);
-  const bool can_prefill = qdense_prefill_eligible(d, &why_prefill);
+  const bool can_decode_tc = !generic_only && qdense_decode_tc_eligible(d, &why_tc);
+  const bool can_prefill = !generic_only && qdense_prefill_eligible(d, &why_prefill);
+  if (generic_only) { why_tc = why; why_prefill = why; }
   if (d.gather_ranks > 1) {          // the fused all-gather exists in the tensor-core decode kernel only
     if (variant != CB_QDENSE_AUTO && variant != CB_QDENSE_DECODE_TC)
       return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: a gathered plan needs the tensor-core decode kernel");
@@ -660,7 +696,8 @@ int qdense_plan(cb_plan* p) {
     p->threads = QG_COLS;
     p->dyn_smem = 0;
     p->workspace_bytes = 0;
-    p->name = std::string("qdense_generic_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (d.w_dtype == CB_U8 ? "_u8" : "_i8");
+    const char* wn = d.w_dtype == CB_U8 ? "_u8" : (d.w_dtype == CB_I8 ? "_i8" : (d.w_dtype == CB_U4 ? "_u4" : "_i4"));
+    p->name = std::string("qdense_generic_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + wn + (d.scheme == CB_QUANT_NF4 ? "_nf4" : "");
     return CB_OK;
   }
   const int mt = d.M <= 8 ? 1 : 2;
@@ -677,7 +714,7 @@ int qdense_plan(cb_plan* p) {
   return CB_OK;
 }
 
-template <typename XT, typename WT>
+template <typename XT, typename WT, bool NF4>
 static int launch_generic(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   if (d.M == 0 || d.N == 0) return CB_OK;
@@ -685,7 +722,7 @@ static int launch_generic(const cb_plan* p, const void* const* in, void* const* 
   const float* zp = d.has_zero_point ? (const float*)in[idx++] : nullptr;
   const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
   dim3 grid((unsigned)((d.N + QG_COLS - 1) / QG_COLS), (unsigned)((d.M + QG_ROWS - 1) / QG_ROWS));
-  qdense_generic_kernel<XT, WT><<<grid, QG_COLS, 0, s>>>((const XT*)in[0], (const WT*)in[1], (const float*)in[2], zp,
+  qdense_generic_kernel<XT, WT, NF4><<<grid, QG_COLS, 0, s>>>((const XT*)in[0], in[1], (const float*)in[2], zp,
                                                          bias, (XT*)out[0], d.M, d.K, d.N, d.scale_layout,
                                                          d.block_size > 0 ? d.block_size : 1, d.activation);
   CB_CUDA(cudaGetLastError());
@@ -745,8 +782,16 @@ int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   if (p->variant == CB_QDENSE_PREFILL) return qdense_prefill_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_launch(p, in, out, ws, s);
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
-  if (bf) return wu ? launch_generic<__nv_bfloat16, uint8_t>(p, in, out, s) : launch_generic<__nv_bfloat16, int8_t>(p, in, out, s);
-  return wu ? launch_generic<float, uint8_t>(p, in, out, s) : launch_generic<float, int8_t>(p, in, out, s);
+  (void)wu;
+  const bool nf4 = d.scheme == CB_QUANT_NF4;
+#define QG_DISPATCH_W(XT, WT) (nf4 ? launch_generic<XT, WT, true>(p, in, out, s) : launch_generic<XT, WT, false>(p, in, out, s))
+#define QG_DISPATCH(XT)                                                     \
+  (d.w_dtype == CB_U8 ? QG_DISPATCH_W(XT, uint8_t)                          \
+   : d.w_dtype == CB_I8 ? QG_DISPATCH_W(XT, int8_t)                         \
+   : d.w_dtype == CB_U4 ? QG_DISPATCH_W(XT, PackedU4) : QG_DISPATCH_W(XT, PackedI4))
+  return bf ? QG_DISPATCH(__nv_bfloat16) : QG_DISPATCH(float);
+#undef QG_DISPATCH
+#undef QG_DISPATCH_W
 }
 
 
@@ -802,6 +847,7 @@ extern "C" int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, cons
   std::string why;
   if (d.x_dtype != CB_F32 && d.x_dtype != CB_BF16) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: x must be float32 or bfloat16");
   if (d.w_dtype != CB_I8 && d.w_dtype != CB_U8) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: weights must be int8 or uint8");
+  if (d.scheme != CB_QUANT_LINEAR) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: only the Linear scheme");
   if (!decode_eligible(d, &why)) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: %s", why.c_str());
   if (d.has_bias && !bias) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: bias is NULL");
   CB_TRY(set_device(dev));

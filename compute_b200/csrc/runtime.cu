@@ -72,6 +72,7 @@ const char* dtype_name(int d) {
     case CB_U16: return "Uint16"; case CB_U32: return "Uint32"; case CB_U64: return "Uint64";
     case CB_F16: return "Float16"; case CB_F32: return "Float32"; case CB_F64: return "Float64";
     case CB_BF16: return "BFloat16"; case CB_F8E5M2: return "F8E5M2"; case CB_F8E4M3FN: return "F8E4M3FN";
+    case CB_I4: return "Int4"; case CB_U4: return "Uint4";
     default: return "InvalidDType";
   }
 }

@@ -12,6 +12,7 @@ from ._lib import DotDesc, QDenseDesc, SdpaDesc, check
 # dtype codes of gomlx/compute dtypes/dtype_enum.go (also cb_dtype in cudabackend.h)
 INVALID, BOOL, I8, I16, I32, I64, U8, U16, U32, U64, F16, F32, F64, BF16 = range(14)
 F8E5M2, F8E4M3FN = 19, 20
+I4, U4 = 21, 22          # packed two per byte, low nibble first: quantized dense weights only
 DTYPE_SIZE = {BOOL: 1, I8: 1, U8: 1, I16: 2, U16: 2, F16: 2, BF16: 2, I32: 4, U32: 4, F32: 4,
               I64: 8, U64: 8, F64: 8, F8E5M2: 1, F8E4M3FN: 1}
 # numpy carrier of each dtype; half types travel as uint16 bit patterns
@@ -22,6 +23,7 @@ NP_CARRIER = {BOOL: np.bool_, I8: np.int8, U8: np.uint8, I16: np.int16, U16: np.
 ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
 SCALE_REF, SCALE_CHANNEL, SCALE_KGROUP = range(3)
 QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL, QDENSE_DECODE_TC = range(5)
+QUANT_LINEAR, QUANT_NF4 = 0, 1
 DOT_AUTO, DOT_GENERIC, DOT_TCGEN05 = range(3)
 SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH = range(3)
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
@@ -236,9 +238,9 @@ class Plan:
     @classmethod
     def qdense(cls, M, K, N, x_dtype=F32, w_dtype=I8, scale_layout=SCALE_REF, block_size=1,
                has_zero_point=False, has_bias=False, activation=ACT_NONE, variant=QDENSE_AUTO, dev=0,
-               gather_ranks=0, gather_rank=0) -> "Plan":
+               gather_ranks=0, gather_rank=0, scheme=QUANT_LINEAR) -> "Plan":
         d = QDenseDesc(M, K, N, x_dtype, w_dtype, scale_layout, block_size, int(has_zero_point),
-                       int(has_bias), activation, variant, gather_ranks, gather_rank)
+                       int(has_bias), activation, variant, gather_ranks, gather_rank, scheme)
         h = C.c_void_p()
         check(_lib.load().cb_plan_qdense(dev, C.byref(d), C.byref(h)))
         return cls(h, dev)

@@ -36,19 +36,28 @@ def _run(plan: dv.Plan, host_inputs, out_shape, out_np_dtype, dev: int = 0) -> n
 def quantized_dense(x: np.ndarray, w: np.ndarray, scales: np.ndarray, zero_points: Optional[np.ndarray] = None,
                     bias: Optional[np.ndarray] = None, *, x_dtype: int = dv.F32, scale_layout: int = dv.SCALE_REF,
                     block_size: int = 1, activation: int = dv.ACT_NONE, variant: int = dv.QDENSE_AUTO,
-                    dev: int = 0, return_plan: bool = False):
+                    dev: int = 0, return_plan: bool = False, scheme: int = dv.QUANT_LINEAR,
+                    packed: Optional[tuple] = None):
     """y = act(x @ dequant(w) + bias).  x: [..., K] f32 (or bf16 bits with x_dtype=BF16);
-    w: [K, N] int8/uint8; scales per `scale_layout`; bias [N] f32."""
+    w: [K, N] int8/uint8; scales per `scale_layout`; bias [N] f32.  Packed 4-bit weights:
+    `packed=(dv.I4 or dv.U4, N)` and `w` the uint8 bytes of the K*N elements, two per byte, low
+    nibble first.  `scheme=dv.QUANT_NF4`: the low nibble of every element indexes the NF4 table."""
     x = np.ascontiguousarray(x, dv.NP_CARRIER[x_dtype])
     w = np.ascontiguousarray(w)
-    if w.dtype not in (np.int8, np.uint8) or w.ndim != 2:
-        raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: weights must be [K, N] int8/uint8, got {w.dtype} {w.shape}")
     if x.ndim < 1:
         raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: x must have rank >= 1, got {x.ndim}")
     K = x.shape[-1]
-    if w.shape[0] != K:
-        raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: weights must be [{K}, N], got {list(w.shape)}")
-    N = w.shape[1]
+    if packed is not None:
+        w_code, N = packed
+        if w_code not in (dv.I4, dv.U4) or w.dtype != np.uint8 or w.size != (K * N + 1) // 2:
+            raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: packed weights must be {(K * N + 1) // 2} uint8 bytes, got {w.dtype} {w.shape}")
+    else:
+        if w.dtype not in (np.int8, np.uint8) or w.ndim != 2:
+            raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: weights must be [K, N] int8/uint8, got {w.dtype} {w.shape}")
+        if w.shape[0] != K:
+            raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: weights must be [{K}, N], got {list(w.shape)}")
+        N = w.shape[1]
+        w_code = dv.U8 if w.dtype == np.uint8 else dv.I8
     M = x.size // K if K else 0
     scales = np.ascontiguousarray(scales, np.float32)
     want = {dv.SCALE_REF: (K, -(-N // max(block_size, 1))), dv.SCALE_CHANNEL: (N,),
@@ -66,8 +75,8 @@ def quantized_dense(x: np.ndarray, w: np.ndarray, scales: np.ndarray, zero_point
         if b.shape != (N,):
             raise BackendError(ERR_INVALID_ARG, f"FusedQuantizedDense: bias must be [{N}], got {list(b.shape)}")
         ins.append(b)
-    plan = dv.Plan.qdense(M, K, N, x_dtype, dv.U8 if w.dtype == np.uint8 else dv.I8, scale_layout, block_size,
-                          zero_points is not None, bias is not None, activation, variant, dev)
+    plan = dv.Plan.qdense(M, K, N, x_dtype, w_code, scale_layout, block_size,
+                          zero_points is not None, bias is not None, activation, variant, dev, scheme=scheme)
     out = _run(plan, ins, x.shape[:-1] + (N,), dv.NP_CARRIER[x_dtype], dev)
     return (out, plan) if return_plan else out
 

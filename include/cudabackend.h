@@ -36,7 +36,8 @@ typedef enum {
 typedef enum {
   CB_INVALID = 0, CB_BOOL = 1, CB_I8 = 2, CB_I16 = 3, CB_I32 = 4, CB_I64 = 5,
   CB_U8 = 6, CB_U16 = 7, CB_U32 = 8, CB_U64 = 9, CB_F16 = 10, CB_F32 = 11,
-  CB_F64 = 12, CB_BF16 = 13, CB_F8E5M2 = 19, CB_F8E4M3FN = 20
+  CB_F64 = 12, CB_BF16 = 13, CB_F8E5M2 = 19, CB_F8E4M3FN = 20,
+  CB_I4 = 21, CB_U4 = 22     /* two elements per byte, low nibble first (quantized dense weights only) */
 } cb_dtype;
 
 /* compute.ActivationType (fused_ops.go:280-289). */
@@ -77,17 +78,23 @@ int cb_stream_wait_event(int dev, cb_stream stream, cb_event ev);  /* later work
 int cb_event_elapsed_ms(cb_event start, cb_event stop, float* ms);  /* syncs on stop */
 int cb_event_destroy(int dev, cb_event ev);
 
-/* ---- FusedQuantizedDense, Linear scheme, 8-bit weights
+/* ---- FusedQuantizedDense, Linear and NF4 schemes, 8-bit and packed 4-bit weights
  *      (FusedOps.FusedQuantizedDense fused_ops.go:413-435; builder/executor
  *       internal/gobackend/fusedops/quantizeddense.go:58-142, :330-418, :616-650;
  *       activation epilogue fusedops/dense.go:176-205).
- * y[M,N] = act( x[M,K] @ dequant(W[K,N]) + bias[N] ),  dequant = w*scale (+ zero_point).
+ * y[M,N] = act( x[M,K] @ dequant(W[K,N]) + bias[N] ),  dequant = w*scale (+ zero_point), or for
+ * NF4 table[w & 15]*scale (compute.NF4LookupTable, fused_ops.go:114-121; quantizeddense.go:586-609).
+ * Int4 / Uint4 weights are packed two per byte over the flat [K*N] element order, low nibble first,
+ * as the reference stores them (internal/gobackend/ops/convertdtype.go:199-226).
  * Launch inputs, in the reference's node-input order: x, weights, scales, zero_points?, bias?. */
 typedef enum {
   CB_SCALE_REF = 0,     /* the reference layout: scales [K, ceil(N/block_size)], block along N  */
   CB_SCALE_CHANNEL = 1, /* compact extension: scales [N], one per output channel               */
   CB_SCALE_KGROUP = 2   /* compact extension: scales [ceil(K/block_size), N], groups along K   */
 } cb_scale_layout;
+
+/* compute.QuantizationScheme (fused_ops.go:80-98); GGML is not built. */
+typedef enum { CB_QUANT_LINEAR = 0, CB_QUANT_NF4 = 1 } cb_quant_scheme;
 
 typedef enum {
   CB_QDENSE_AUTO = 0,
@@ -100,7 +107,7 @@ typedef enum {
 typedef struct {
   int64_t M, K, N;
   int32_t x_dtype;        /* CB_F32 (the reference's only type) or CB_BF16 (extension); out has the same type */
-  int32_t w_dtype;        /* CB_I8 or CB_U8 */
+  int32_t w_dtype;        /* CB_I8, CB_U8, or packed CB_I4 / CB_U4 (generic kernel) */
   int32_t scale_layout;   /* cb_scale_layout */
   int64_t block_size;     /* REF: columns per scale; KGROUP: rows per scale; CHANNEL: ignored */
   int32_t has_zero_point; /* zero points share the scale layout (f32) */
@@ -116,6 +123,7 @@ typedef struct {
    * for the slices of all ranks.  Decode tensor-core kernel only. */
   int32_t gather_ranks;
   int32_t gather_rank;
+  int32_t scheme;         /* cb_quant_scheme; NF4 takes no zero points and runs on the generic kernel */
 } cb_qdense_desc;
 
 int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);

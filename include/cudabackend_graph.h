@@ -79,7 +79,7 @@ int cbg_fn_convert_dtype(cbg_function* f, cbg_value* x, int32_t dtype, cbg_value
 int cbg_fn_transpose(cbg_function* f, cbg_value* x, const int* permutation, cbg_value** v);
 
 /* FusedOps.FusedQuantizedDense (fused_ops.go:413-435) with compute.Quantization (:204-234).
- * scheme: 0 Linear, 1 NF4, 2 GGML (only Linear is built).  block_axis 1 is the reference
+ * scheme: 0 Linear, 1 NF4 (weights as Int8 / Uint8 nibble indices), 2 GGML (not built).  block_axis 1 is the reference
  * layout scales [K, ceil(N/block_size)]; block_axis 0 is this backend's extension, scales
  * [ceil(K/block_size), N] (block_size = K gives one scale per output channel). */
 int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias /* or NULL */,

@@ -207,6 +207,72 @@ void orc_qdense_linear(const float* x, const void* w, int w_unsigned,
 }
 
 /* ------------------------------------------------------------------ */
+/* packed 4-bit weights and the NF4 scheme                            */
+/* ------------------------------------------------------------------ */
+
+/* Int4 / Uint4 storage: two elements per byte over the flat element order, the low nibble first;
+ * Int4 nibbles 8..15 mean -8..-1 (internal/gobackend/ops/convertdtype.go:199-226).  The reference
+ * unpacks such weights to one int8 / uint8 per element before the dense op
+ * (fusedops/quantizeddense.go:420-450), so the Linear scheme on packed weights is
+ * orc_unpack_* followed by orc_qdense_linear. */
+void orc_unpack_int4(const uint8_t* packed, int8_t* dst, size_t n_bytes) {
+  for (size_t i = 0; i < n_bytes; i++) {
+    int lo = packed[i] & 0x0F;
+    if (lo >= 8) lo -= 16;
+    const int hi = (int8_t)packed[i] >> 4; /* arithmetic shift keeps the sign */
+    dst[2 * i] = (int8_t)lo;
+    dst[2 * i + 1] = (int8_t)hi;
+  }
+}
+void orc_unpack_uint4(const uint8_t* packed, uint8_t* dst, size_t n_bytes) {
+  for (size_t i = 0; i < n_bytes; i++) {
+    dst[2 * i] = packed[i] & 0x0F;
+    dst[2 * i + 1] = packed[i] >> 4;
+  }
+}
+
+/* The 16 NormalFloat4 values of QLoRA (Dettmers et al. 2023, appendix E), as float32; the
+ * reference holds the same table (fused_ops.go:114-121). */
+static const float orc_nf4_table[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+const float* orc_nf4_values(void) { return orc_nf4_table; }
+
+/* NF4 scheme (quantizeddense.go:586-609): the low four bits of every (unpacked) weight index the
+ * table; per element, k ascending:  out += (x * table[w & 15]) * s, each operation rounded to f32;
+ * bias first; no zero points.  `w` holds one byte per element (int8 or uint8: only the low nibble
+ * is used). */
+static void qdense_nf4_unit(const float* x, const uint8_t* w, const float* scales, const float* bias,
+                            float* out, int64_t m, int64_t n0, int64_t n1,
+                            int64_t K, int64_t N, int64_t bs, int64_t nblk) {
+  float* o = out + m * N;
+  for (int64_t n = n0; n < n1; n++) o[n] = bias ? bias[n] : 0.0f;
+  for (int64_t k = 0; k < K; k++) {
+    const float xv = x[m * K + k];
+    const float* srow = scales + k * nblk;
+    int64_t blk = n0 / bs;
+    int64_t next = (blk + 1) * bs;
+    for (int64_t n = n0; n < n1; n++) {
+      if (n >= next) { blk++; next += bs; }
+      float p = xv * orc_nf4_table[w[k * N + n] & 0x0F];
+      p = p * srow[blk];
+      o[n] = o[n] + p;
+    }
+  }
+}
+
+void orc_qdense_nf4(const float* x, const void* w, const float* scales, const float* bias, float* out,
+                    int64_t M, int64_t K, int64_t N, int64_t block_size, int activation, int threads) {
+  const int64_t nblk = (N + block_size - 1) / block_size;
+  (void)threads; /* the work split does not change any element's arithmetic */
+  for (int64_t m = 0; m < M; m++)
+    qdense_nf4_unit(x, (const uint8_t*)w, scales, bias, out, m, 0, N, K, N, block_size, nblk);
+  orc_activation_f32(out, (size_t)(M * N), activation);
+}
+
+/* ------------------------------------------------------------------ */
 /* DotGeneral                                                         */
 /* ------------------------------------------------------------------ */
 

@@ -54,6 +54,12 @@ def lib(fast: bool = False):
                                         C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_int, C.c_int]
         L.orc_activation_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_int]
+        L.orc_unpack_int4.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_unpack_uint4.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_nf4_values.argtypes = []
+        L.orc_nf4_values.restype = C.POINTER(C.c_float)
+        L.orc_qdense_nf4.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int]
         L.orc_dot_general.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
@@ -163,6 +169,54 @@ def qdense_linear(x, w, scales, zero_points=None, bias=None, block_size: int = 1
     out = np.empty(x.shape[:-1] + (N,), np.float32)
     lib(fast).orc_qdense_linear(_p(x), _p(w), int(w.dtype == np.uint8), _p(scales), _p(zp), _p(b),
                                 _p(out), M, K, N, block_size, activation, threads)
+    return out
+
+
+def unpack_int4(packed, n: int) -> np.ndarray:
+    """Packed Int4 bytes -> the first `n` int8 values (convertdtype.go:199-214: low nibble first)."""
+    b = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+    out = np.empty(2 * b.size, np.int8)
+    lib().orc_unpack_int4(_p(b), _p(out), b.size)
+    return out[:n]
+
+
+def unpack_uint4(packed, n: int) -> np.ndarray:
+    """Packed Uint4 bytes -> the first `n` uint8 values (convertdtype.go:216-226)."""
+    b = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+    out = np.empty(2 * b.size, np.uint8)
+    lib().orc_unpack_uint4(_p(b), _p(out), b.size)
+    return out[:n]
+
+
+def pack_nibbles(values) -> np.ndarray:
+    """Flat 4-bit values (signed or unsigned) -> packed bytes, low nibble first (the inverse of unpack_*)."""
+    v = (np.asarray(values).astype(np.int16).reshape(-1) & 0x0F).astype(np.uint8)
+    if v.size % 2:
+        v = np.concatenate([v, np.zeros(1, np.uint8)])
+    return (v[0::2] | (v[1::2] << 4)).astype(np.uint8)
+
+
+def nf4_values() -> np.ndarray:
+    """The 16 NormalFloat4 table values (fused_ops.go:114-121)."""
+    ptr = lib().orc_nf4_values()
+    return np.array([ptr[i] for i in range(16)], np.float32)
+
+
+def qdense_nf4(x, w, scales, bias=None, block_size: int = 1, activation: int = ACT_NONE) -> np.ndarray:
+    """Reference FusedQuantizedDense, NF4 scheme (quantizeddense.go:586-609); `w` holds one int8 /
+    uint8 per element, of which the low nibble indexes the table."""
+    x = _c(x, np.float32)
+    K = x.shape[-1]
+    M = x.size // K if K else 0
+    w = np.ascontiguousarray(w)
+    assert w.dtype in (np.int8, np.uint8) and w.shape[0] == K
+    N = w.shape[1]
+    nblk = (N + block_size - 1) // block_size
+    scales = _c(scales, np.float32)
+    assert scales.shape == (K, nblk), (scales.shape, (K, nblk))
+    b = None if bias is None else _c(bias, np.float32)
+    out = np.empty(x.shape[:-1] + (N,), np.float32)
+    lib().orc_qdense_nf4(_p(x), _p(w), _p(scales), _p(b), _p(out), M, K, N, block_size, activation, 1)
     return out
 
 

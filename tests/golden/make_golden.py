@@ -201,3 +201,12 @@ with open(os.path.join(HERE, "backendtest_dense_epilogue.json"), "w") as f:
     json.dump(dict(source="gomlx/compute " + F, cases=dense_cases), f, indent=1)
 print("wrote", len(dot_cases), "dot,", len(sdpa_cases), "+", len(sdpa_error_cases), "sdpa,",
       len(dense_cases), "dense cases")
+
+# compute.NF4LookupTable (fused_ops.go:114-121), the 16 NormalFloat4 values of QLoRA as the
+# reference writes them (decimal expansions of float32 values).
+nf4 = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
+       -0.28444138169288635, -0.18477343022823334, -0.09105003625154495, 0.0,
+       0.07958029955625534, 0.16093020141124725, 0.24611230194568634, 0.33791524171829224,
+       0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0]
+with open(os.path.join(HERE, "nf4_table.json"), "w") as f:
+    json.dump(dict(source="gomlx/compute fused_ops.go:114-121", values=nf4), f, indent=1)

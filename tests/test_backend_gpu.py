@@ -195,9 +195,25 @@ def test_fused_quantized_dense_validation(backend):
         f.FusedQuantizedDense(x, w, None, q(BlockSize=8))
     with pytest.raises(BackendError):          # :123 only Axis=1 (and this backend's Axis=0)
         f.FusedQuantizedDense(x, w, None, q(BlockAxis=2))
-    for scheme in (be.QUANT_NF4, be.QUANT_GGML):
-        with pytest.raises(ErrNotImplemented):
-            f.FusedQuantizedDense(x, w, None, q(Scheme=scheme))
+    with pytest.raises(ErrNotImplemented):
+        f.FusedQuantizedDense(x, w, None, q(Scheme=be.QUANT_GGML))
+    with pytest.raises(BackendError) as e:     # :126 NF4 takes no zero points
+        f.FusedQuantizedDense(x, w, None, q(Scheme=be.QUANT_NF4, ZeroPoint=s))
+    assert "ZeroPoint must be nil for NF4" in str(e.value)
+
+
+def test_fused_quantized_dense_nf4_through_api(backend):
+    M, K, N, block = 3, 64, 48, 16
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    idx = rng.integers(0, 16, size=(K, N)).astype(np.uint8)
+    s = rng.uniform(0.01, 0.2, size=(K, N // block)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    def build(f, p):
+        return f.FusedQuantizedDense(p[0], p[1], p[3], be.Quantization(be.QUANT_NF4, p[2], None, 1, block), dv.ACT_NONE)
+    (got,), (shape,) = be.exec_graph(backend, [(x, dv.F32), (idx, dv.U8), (s, dv.F32), (b, dv.F32)], build)
+    assert shape == be.make_shape(dv.F32, M, N)
+    assert np.array_equal(got, orc.qdense_nf4(x, idx, s, b, block, orc.ACT_NONE))
 
 
 # ---------------------------------------------------------------- SDPA (fusedops.go, sdpa_direct_test.go)

@@ -197,6 +197,36 @@ def test_qdense_thread_split_is_bit_identical():
         assert np.array_equal(one, many) and np.array_equal(one, fast)
 
 
+def test_nibble_unpack_known_answers():
+    """The reference's own vectors (internal/gobackend/ops/convertdtype_test.go:13-80): byte 0xF0 is
+    (0, -1) as Int4 and (0, 15) as Uint4; byte 0x87 is (7, -8) and (7, 8)."""
+    packed = np.array([0xF0, 0x87], np.uint8)
+    assert orc.unpack_int4(packed, 4).tolist() == [0, -1, 7, -8]
+    assert orc.unpack_uint4(packed, 4).tolist() == [0, 15, 7, 8]
+    rng = np.random.default_rng(3)
+    v = rng.integers(-8, 8, size=101)
+    assert np.array_equal(orc.unpack_int4(orc.pack_nibbles(v), v.size), v)
+    u = rng.integers(0, 16, size=100)
+    assert np.array_equal(orc.unpack_uint4(orc.pack_nibbles(u), u.size), u)
+
+
+def test_nf4_table_and_dense():
+    """NormalFloat4: 16 increasing values in [-1, 1] with an exact zero at index 7 (fused_ops.go:114-121);
+    the dense op is sum_k (x * table[w & 15]) * scale in f32 (quantizeddense.go:586-609)."""
+    t = orc.nf4_values()
+    assert t.dtype == np.float32 and t[0] == -1.0 and t[7] == 0.0 and t[15] == 1.0 and np.all(np.diff(t) > 0)
+    golden = load_golden("nf4_table.json")["values"]
+    assert [float(v) for v in t] == golden
+    x = np.array([[1.0, 2.0], [0.5, -1.0]], np.float32)
+    w = np.array([[0, 15, 7], [15 | 0x30, 0, 8]], np.uint8)          # bits above the nibble are ignored
+    s = np.array([[2.0], [0.5]], np.float32)
+    got = orc.qdense_nf4(x, w, s, np.array([0.0, 1.0, 0.0], np.float32), 3, orc.ACT_NONE)
+    t8 = float(t[8])
+    want = np.array([[1 * -1 * 2 + 2 * 1 * 0.5, 1 + 1 * 1 * 2 + 2 * -1 * 0.5, 2 * t8 * 0.5],
+                     [0.5 * -1 * 2 - 1 * 0.5, 1 + 0.5 * 2 + 1 * 0.5, -1 * t8 * 0.5]], np.float32)
+    assert np.allclose(got, want, rtol=0, atol=1e-7)
+
+
 def test_expand_scales_layouts():
     s = np.arange(6, dtype=np.float32).reshape(2, 3)
     e = orc.expand_scales(s, "kgroup", 4, 3, group=2)

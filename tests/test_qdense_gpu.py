@@ -52,6 +52,69 @@ def test_generic_uint8_and_batch_dims():
     assert got.shape == (2, 3, 48) and np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("signed", [True, False])
+@pytest.mark.parametrize("N", [40, 37])
+def test_generic_packed_4bit_linear_bit_exact(signed, N):
+    """Int4 / Uint4 weights, two per byte over the flat element order (an odd N makes rows straddle
+    bytes): the reference unpacks them and runs the Linear scheme, so the bits are identical."""
+    M, K, block = 5, 33, 8
+    rng = np.random.default_rng(40 + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    vals = rng.integers(-8, 8, size=(K, N)) if signed else rng.integers(0, 16, size=(K, N))
+    packed = orc.pack_nibbles(vals)
+    w8 = (orc.unpack_int4(packed, K * N) if signed else orc.unpack_uint4(packed, K * N)).reshape(K, N)
+    assert np.array_equal(w8, vals)
+    nblk = -(-N // block)
+    s = rng.uniform(0.01, 0.2, size=(K, nblk)).astype(np.float32)
+    zp = rng.uniform(-0.05, 0.05, size=s.shape).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    for z in (None, zp):
+        got, plan = ops.quantized_dense(x, packed, s, z, b, block_size=block, activation=dv.ACT_RELU,
+                                        packed=(dv.I4 if signed else dv.U4, N), return_plan=True)
+        assert plan.kernel_name == ("qdense_generic_f32_i4" if signed else "qdense_generic_f32_u4")
+        assert np.array_equal(got, orc.qdense_linear(x, w8, s, z, b, block, orc.ACT_RELU))
+
+
+@pytest.mark.parametrize("w_kind", ["i8", "u8", "i4", "u4"])
+def test_generic_nf4_bit_exact(w_kind):
+    """NF4: the low nibble of each weight indexes the NormalFloat4 table (quantizeddense.go:586-609)."""
+    M, K, N, block = 4, 48, 36, 12
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    idx = rng.integers(0, 16, size=(K, N))
+    s = rng.uniform(0.01, 0.2, size=(K, N // block)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    want = orc.qdense_nf4(x, idx.astype(np.uint8), s, b, block, orc.ACT_SILU)
+    # an independent statement of the same arithmetic
+    table = orc.nf4_values()
+    acc = np.tile(b, (M, 1))
+    sx = np.repeat(s, block, axis=1)
+    for k in range(K):
+        acc = (acc + ((x[:, k:k + 1] * table[idx[k]][None, :]).astype(np.float32) * sx[k][None, :]).astype(np.float32)).astype(np.float32)
+    assert max_abs_normalised(want, orc.activation_f64(acc.astype(np.float64), orc.ACT_SILU)) < 1e-6
+    if w_kind == "u8":
+        got = ops.quantized_dense(x, idx.astype(np.uint8), s, None, b, block_size=block, activation=dv.ACT_SILU, scheme=dv.QUANT_NF4)
+    elif w_kind == "i8":      # Int4 values sign-extended to int8, as the reference's unpacking leaves them
+        got = ops.quantized_dense(x, np.where(idx >= 8, idx - 16, idx).astype(np.int8), s, None, b, block_size=block,
+                                  activation=dv.ACT_SILU, scheme=dv.QUANT_NF4)
+    else:
+        got = ops.quantized_dense(x, orc.pack_nibbles(idx), s, None, b, block_size=block, activation=dv.ACT_SILU,
+                                  scheme=dv.QUANT_NF4, packed=(dv.I4 if w_kind == "i4" else dv.U4, N))
+    assert max_abs_normalised(got, want) < 1e-6          # SiLU differs in the last bit between libm and the GPU
+    got0 = ops.quantized_dense(x, idx.astype(np.uint8), s, None, b, block_size=block, scheme=dv.QUANT_NF4)
+    assert np.array_equal(got0, orc.qdense_nf4(x, idx.astype(np.uint8), s, b, block, orc.ACT_NONE))
+
+
+def test_nf4_and_packed_validation():
+    with pytest.raises(BackendError) as e:
+        dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, has_zero_point=True, scheme=dv.QUANT_NF4)
+    assert "ZeroPoint must be nil for NF4" in str(e.value)
+    with pytest.raises(ErrNotImplemented):
+        dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, scheme=2)          # GGML
+    with pytest.raises(ErrNotImplemented):
+        dv.Plan.qdense(2, 4096, 4096, dv.BF16, dv.I4, dv.SCALE_KGROUP, 128, variant=dv.QDENSE_DECODE_TC)
+
+
 def test_dense_epilogue_golden_on_gpu():
     for case in load_golden("backendtest_dense_epilogue.json")["cases"]:
         x = tensor(case["x"], "f32")
