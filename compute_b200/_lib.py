@@ -37,7 +37,7 @@ class QDenseDesc(C.Structure):
 class DotDesc(C.Structure):
     _fields_ = [("B", C.c_int64), ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
                 ("rhs_transposed", C.c_int32), ("in_dtype", C.c_int32), ("out_dtype", C.c_int32),
-                ("variant", C.c_int32)]
+                ("variant", C.c_int32), ("has_bias", C.c_int32), ("activation", C.c_int32)]
 
 
 class SdpaDesc(C.Structure):

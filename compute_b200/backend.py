@@ -70,6 +70,7 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_iota": ([C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_convert_dtype": ([C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_transpose": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_sdpa": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(_SdpaOptions), C.POINTER(C.c_void_p)], C.c_int),
@@ -145,6 +146,17 @@ class DotGeneralConfig:
     """compute.DotGeneralConfig (standard_ops.go:91-111); 0 = InvalidDType = unset."""
     AccumulatorDType: int = 0
     OutputDType: int = 0
+
+
+# compute.DenseLayout (fused_ops.go:50-58)
+DENSE_LAYOUT_INPUT_OUTPUTS, DENSE_LAYOUT_OUTPUTS_INPUT = 0, 1
+
+
+@dataclass
+class DenseConfig:
+    """compute.DenseConfig (fused_ops.go:72-78)."""
+    Activation: int = dv.ACT_NONE
+    WeightLayout: int = DENSE_LAYOUT_INPUT_OUTPUTS
 
 
 @dataclass
@@ -315,6 +327,13 @@ class Function:
         return self._v(h)
 
     # ---- FusedOps on the path
+    def FusedDense(self, x: Value, weight: Value, bias: Optional[Value], options: Optional[DenseConfig] = None) -> Value:
+        o = options or DenseConfig()
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_dense(self.handle, x.handle, weight.handle, bias.handle if bias is not None else None,
+                                      o.Activation, o.WeightLayout, C.byref(h)))
+        return self._v(h)
+
     def FusedQuantizedDense(self, x: Value, weights: Value, bias: Optional[Value], weightsQuantization: Quantization,
                             activation: int = dv.ACT_NONE) -> Value:
         q = weightsQuantization

@@ -35,10 +35,39 @@ template <typename A> struct DotStore<A, __half> {
 constexpr int DG_TILE = 64;
 constexpr int DG_KT = 16;
 
+// FusedDense epilogue (internal/gobackend/fusedops/dense.go:111-205): bias[n] added to the matmul
+// result, then the activation, in the accumulator's type (f64 for f64, f32 otherwise).  Integer
+// dot products have no epilogue.
+__device__ inline double apply_activation_f64(double x, int act) {
+  switch (act) {
+    case CB_ACT_GELU: return x * 0.5 * (1.0 + erf(x * (1.0 / 1.4142135623730951)));     // gelu.go:113-118
+    case CB_ACT_RELU: return x < 0.0 ? 0.0 : x;
+    case CB_ACT_SILU: return x / (1.0 + exp(-x));
+    case CB_ACT_HARDSWISH: { const double g = fmin(fmax(x * (1.0 / 6.0) + 0.5, 0.0), 1.0); return x * g; }
+    case CB_ACT_TANH: return tanh(x);
+    default: return x;
+  }
+}
+template <typename T, typename A> struct DenseEpilogue {
+  static __device__ __forceinline__ A apply(A v, const T*, int64_t, int) { return v; }
+};
+template <typename T> struct DenseEpilogue<T, float> {
+  static __device__ __forceinline__ float apply(float v, const T* bias, int64_t n, int act) {
+    if (bias) v = __fadd_rn(v, DotIO<T, float>::load(bias, n));
+    return apply_activation(v, act);
+  }
+};
+template <> struct DenseEpilogue<double, double> {
+  static __device__ __forceinline__ double apply(double v, const double* bias, int64_t n, int act) {
+    if (bias) v = v + bias[n];
+    return apply_activation_f64(v, act);
+  }
+};
+
 template <typename T, typename O>
 __global__ void __launch_bounds__(256)
-dot_generic_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, O* __restrict__ out,
-                   int64_t M, int64_t N, int64_t K, int rhs_transposed) {
+dot_generic_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, const T* __restrict__ bias, O* __restrict__ out,
+                   int64_t M, int64_t N, int64_t K, int rhs_transposed, int act) {
   typedef typename DotAcc<T>::type A;
   __shared__ A As[DG_KT][DG_TILE + 1];
   __shared__ A Bs[DG_KT][DG_TILE + 1];
@@ -90,14 +119,15 @@ dot_generic_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, O* __re
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int64_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-      if (m < M && n < N) DotStore<A, O>::store(C, m * N + n, acc[i][j]);
+      if (m < M && n < N) DotStore<A, O>::store(C, m * N + n, DenseEpilogue<T, A>::apply(acc[i][j], bias, n, act));
     }
 }
 
 template <typename T, typename O>
 static int launch_t(const cb_dot_desc& d, const void* const* in, void* const* out, cudaStream_t s) {
   dim3 grid((unsigned)((d.N + DG_TILE - 1) / DG_TILE), (unsigned)((d.M + DG_TILE - 1) / DG_TILE), (unsigned)d.B);
-  dot_generic_kernel<T, O><<<grid, 256, 0, s>>>((const T*)in[0], (const T*)in[1], (O*)out[0], d.M, d.N, d.K, d.rhs_transposed);
+  dot_generic_kernel<T, O><<<grid, 256, 0, s>>>((const T*)in[0], (const T*)in[1], d.has_bias ? (const T*)in[2] : nullptr, (O*)out[0],
+                                                d.M, d.N, d.K, d.rhs_transposed, d.activation);
   CB_CUDA(cudaGetLastError());
   return CB_OK;
 }
@@ -109,6 +139,10 @@ static int launch_out(const cb_dot_desc& d, int od, const void* const* in, void*
   if (od == CB_F64) return launch_t<T, double>(d, in, out, s);
   return fail(CB_ERR_NOT_IMPLEMENTED, "no DotGeneral implementation found for layout and dtypes=%s,%s",
               dtype_name(d.in_dtype), dtype_name(od));
+}
+
+bool dot_generic_supports_epilogue(int in_dtype) {
+  return in_dtype == CB_F32 || in_dtype == CB_F64 || in_dtype == CB_BF16 || in_dtype == CB_F16;
 }
 
 bool dot_generic_supports(int in_dtype, int out_dtype) {

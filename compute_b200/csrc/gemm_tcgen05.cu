@@ -464,6 +464,18 @@ bool dot_tc_supports(const cb_dot_desc& d, std::string* why) {
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// FusedDense on half types: the epilogue reads an f32 bias, so a 16-bit bias is widened into the
+// workspace first (N elements).
+template <typename T>
+__global__ void bias_to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = Scalar<T>::load(src, i);
+}
+
+static size_t dot_tc_planes_bytes(const cb_dot_desc& d) {
+  return d.in_dtype == CB_F32 ? align256((size_t)3 * d.B * d.M * d.K * 2) + align256((size_t)3 * d.B * d.K * d.N * 2) : 0;
+}
+
 int dot_tc_plan(cb_plan* p) {
   const cb_dot_desc& d = p->dot;
   p->blocks = gemm_tc_blocks(p->n_sm, d.B, d.M, d.N);
@@ -471,11 +483,12 @@ int dot_tc_plan(cb_plan* p) {
   p->dyn_smem = GT_SMEM;
   p->counter_bytes = 256;
   p->workspace_bytes = 256;
-  if (d.in_dtype == CB_F32)      // three bf16 planes of each operand
-    p->workspace_bytes += align256((size_t)3 * d.B * d.M * d.K * 2) + align256((size_t)3 * d.B * d.K * d.N * 2);
+  p->workspace_bytes += dot_tc_planes_bytes(d);      // float32: three bf16 planes of each operand
+  if (d.has_bias && d.in_dtype != CB_F32) p->workspace_bytes += align256((size_t)d.N * 4);
   p->has_status = true;
   const int od = d.out_dtype ? d.out_dtype : d.in_dtype;
-  p->name = std::string("gemm_tcgen05_") + dtype_name(d.in_dtype) + "_" + dtype_name(od) + (d.rhs_transposed ? "_nt" : "_nn");
+  const bool dense = d.has_bias || d.activation != CB_ACT_NONE;
+  p->name = std::string("gemm_tcgen05_") + dtype_name(d.in_dtype) + "_" + dtype_name(od) + (d.rhs_transposed ? "_nt" : "_nn") + (dense ? "_dense" : "");
   return CB_OK;
 }
 
@@ -488,6 +501,19 @@ int dot_tc_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   g.rhs_transposed = d.rhs_transposed;
   g.ab_dtype = d.in_dtype;
   g.out_dtype = d.out_dtype ? d.out_dtype : d.in_dtype;
+  g.activation = d.activation;
+  if (d.has_bias) {
+    if (d.in_dtype == CB_F32) {
+      g.bias = (const float*)in[2];
+    } else {
+      float* b32 = (float*)((uint8_t*)ws + 256 + dot_tc_planes_bytes(d));
+      const unsigned blocks = (unsigned)((d.N + 255) / 256);
+      if (d.in_dtype == CB_BF16) bias_to_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)in[2], b32, d.N);
+      else bias_to_f32_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)in[2], b32, d.N);
+      CB_CUDA(cudaGetLastError());
+      g.bias = b32;
+    }
+  }
   if (d.in_dtype == CB_F32) {
     uint8_t* w8 = (uint8_t*)ws;
     uint16_t* pa = (uint16_t*)(w8 + 256);

@@ -642,6 +642,61 @@ int cbg_fn_dot_general(cbg_function* f, cbg_value* lhs, const int* lhs_contract,
   return CB_OK;
 }
 
+// FusedOps.FusedDense (fused_ops.go:336-347; builder internal/gobackend/fusedops/dense.go:34-108): the matmul is a
+// DotGeneral contracting x's last axis with the weight's first (InputOutputs) or last (OutputsInput) axis; bias and
+// activation become the epilogue of that same kernel instead of a second pass over the result.
+int cbg_fn_fused_dense(cbg_function* f, cbg_value* x, cbg_value* weight, cbg_value* bias, int activation, int weight_layout,
+                       cbg_value** v) {
+  const char* op = "FusedDense";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x, weight}));
+  if (bias) CB_TRY(check_values(f, op, {bias}));
+  const int xr = (int)x->shape.dims.size(), wr = (int)weight->shape.dims.size();
+  if (xr < 1 || wr < 2)
+    return fail(CB_ERR_INVALID_ARG, "%s: x must have rank >= 1 (got %d), weight must have rank >= 2 (got %d)", op, xr, wr);
+  if (weight->shape.dtype != x->shape.dtype)
+    return fail(CB_ERR_INVALID_ARG, "%s: x and weight must share one dtype, got %s and %s", op, cb::dtype_name(x->shape.dtype), cb::dtype_name(weight->shape.dtype));
+  if (activation < CB_ACT_NONE || activation > CB_ACT_TANH) return fail(CB_ERR_INVALID_ARG, "%s: unknown activation %d", op, activation);
+  const int64_t in_features = x->shape.dims.back();
+  int w_axis;
+  std::vector<int64_t> out_features;
+  if (weight_layout == 0) {            // DenseLayoutInputOutputs: [in_features, out_features...]
+    if (in_features != weight->shape.dims[0])
+      return fail(CB_ERR_INVALID_ARG, "%s: x's last dim (%lld) must match weight's first dim (%lld) for DenseLayoutInputOutputs", op,
+                  (long long)in_features, (long long)weight->shape.dims[0]);
+    w_axis = 0;
+    out_features.assign(weight->shape.dims.begin() + 1, weight->shape.dims.end());
+  } else if (weight_layout == 1) {     // DenseLayoutOutputsInput: [out_features..., in_features]
+    if (in_features != weight->shape.dims[wr - 1])
+      return fail(CB_ERR_INVALID_ARG, "%s: x's last dim (%lld) must match weight's last dim (%lld) for DenseLayoutOutputsInput", op,
+                  (long long)in_features, (long long)weight->shape.dims[wr - 1]);
+    w_axis = wr - 1;
+    out_features.assign(weight->shape.dims.begin(), weight->shape.dims.end() - 1);
+  } else {
+    return fail(CB_ERR_INVALID_ARG, "%s: unknown WeightLayout %d", op, weight_layout);
+  }
+  if (bias && (bias->shape.dtype != x->shape.dtype || bias->shape.dims != out_features))
+    return fail(CB_ERR_INVALID_ARG, "%s: bias must have the dtype of x and the out-features shape, got %s", op, bias->shape.str().c_str());
+  // the reference executes Float32 and Float64 (dense.go:149-163); the half types are this backend's extension
+  if (x->shape.dtype != CB_F32 && x->shape.dtype != CB_F64 && x->shape.dtype != CB_BF16 && x->shape.dtype != CB_F16)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: dtype %s", op, cb::dtype_name(x->shape.dtype));
+  const int lc = xr - 1;
+  cbg_value* res = nullptr;
+  CB_TRY(cbg_fn_dot_general(f, x, &lc, 1, nullptr, 0, weight, &w_axis, nullptr, 0, 0, &res));
+  if (bias || activation != CB_ACT_NONE) {
+    cbg_value* d = res;
+    while (d->kind == N_RESHAPE) d = d->inputs[0];
+    if (d->kind != N_DOT) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: the matmul did not lower to one kernel", op);
+    d->dot.activation = activation;
+    if (bias) {
+      d->dot.has_bias = 1;
+      d->inputs.push_back(bias);     // flat [N]: the out-feature axes in order, as the normalised rhs enumerates them
+    }
+  }
+  *v = res;
+  return CB_OK;
+}
+
 int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias, int scheme,
                                  cbg_value* scale, cbg_value* zero_point, int block_axis, int64_t block_size,
                                  int activation, cbg_value** v) {

@@ -246,8 +246,9 @@ class Plan:
         return cls(h, dev)
 
     @classmethod
-    def dot(cls, B, M, N, K, in_dtype=F32, out_dtype=INVALID, rhs_transposed=False, variant=DOT_AUTO, dev=0) -> "Plan":
-        d = DotDesc(B, M, N, K, int(rhs_transposed), in_dtype, out_dtype, variant)
+    def dot(cls, B, M, N, K, in_dtype=F32, out_dtype=INVALID, rhs_transposed=False, variant=DOT_AUTO, dev=0,
+            has_bias=False, activation=ACT_NONE) -> "Plan":
+        d = DotDesc(B, M, N, K, int(rhs_transposed), in_dtype, out_dtype, variant, int(has_bias), activation)
         h = C.c_void_p()
         check(_lib.load().cb_plan_dot(dev, C.byref(d), C.byref(h)))
         return cls(h, dev)

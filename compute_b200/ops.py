@@ -82,15 +82,20 @@ def quantized_dense(x: np.ndarray, w: np.ndarray, scales: np.ndarray, zero_point
 
 
 def dot_normalised(lhs: np.ndarray, rhs: np.ndarray, *, in_dtype: int, out_dtype: int = dv.INVALID,
-                   rhs_transposed: bool = False, variant: int = dv.DOT_AUTO, dev: int = 0, return_plan: bool = False):
-    """out[B,M,N] = lhs[B,M,K] x rhs[B,K,N] (or rhs[B,N,K] when rhs_transposed)."""
+                   rhs_transposed: bool = False, variant: int = dv.DOT_AUTO, dev: int = 0, return_plan: bool = False,
+                   bias: Optional[np.ndarray] = None, activation: int = dv.ACT_NONE):
+    """out[B,M,N] = lhs[B,M,K] x rhs[B,K,N] (or rhs[B,N,K] when rhs_transposed); with `bias` [N] (of the input
+    dtype) and / or `activation` the plan is FusedDense: act(dot + bias)."""
     lhs = np.ascontiguousarray(lhs, dv.NP_CARRIER[in_dtype])
     rhs = np.ascontiguousarray(rhs, dv.NP_CARRIER[in_dtype])
     B, M, K = lhs.shape
     N = rhs.shape[1] if rhs_transposed else rhs.shape[2]
     od = out_dtype or in_dtype
-    plan = dv.Plan.dot(B, M, N, K, in_dtype, out_dtype, rhs_transposed, variant, dev)
-    out = _run(plan, [lhs, rhs], (B, M, N), dv.NP_CARRIER[od], dev)
+    plan = dv.Plan.dot(B, M, N, K, in_dtype, out_dtype, rhs_transposed, variant, dev, has_bias=bias is not None, activation=activation)
+    ins = [lhs, rhs]
+    if bias is not None:
+        ins.append(np.ascontiguousarray(bias, dv.NP_CARRIER[in_dtype]).reshape(N))
+    out = _run(plan, ins, (B, M, N), dv.NP_CARRIER[od], dev)
     return (out, plan) if return_plan else out
 
 

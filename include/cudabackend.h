@@ -144,7 +144,11 @@ int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, const void* x, 
 /* ---- DotGeneral in normalised form (StandardOps.DotGeneral standard_ops.go:338-363;
  *      normalisation and dtype rules internal/gobackend/dot/dot.go:165-285; kernels dot/matmul/*).
  * out[B,M,N] = lhs[B,M,K] x rhs, rhs = [B,K,N] (rhs_transposed = 0) or [B,N,K] (= 1).
- * Half inputs accumulate in f32.  Launch inputs: lhs, rhs. */
+ * Half inputs accumulate in f32.  Launch inputs: lhs, rhs, bias?.
+ * With has_bias / activation the plan is FusedOps.FusedDense (fused_ops.go:336-347; builder and
+ * executor internal/gobackend/fusedops/dense.go:34-163): out = act(dot + bias[n]), bias [N] of the
+ * input dtype, float dtypes only (the reference executes f32 and f64; bf16 / f16 are this
+ * backend's extension, computed in f32 and rounded once). */
 typedef enum {
   CB_DOT_AUTO = 0,
   CB_DOT_GENERIC = 1,   /* CUDA-core tiled kernel, every supported dtype                       */
@@ -157,6 +161,8 @@ typedef struct {
   int32_t in_dtype;      /* f32, f64, bf16, f16, i32, i64 */
   int32_t out_dtype;     /* dtype stored; CB_INVALID = in_dtype */
   int32_t variant;       /* cb_dot_variant */
+  int32_t has_bias;      /* FusedDense: bias [N] follows rhs in the launch inputs */
+  int32_t activation;    /* FusedDense: cb_activation applied after the bias */
 } cb_dot_desc;
 
 int cb_plan_dot(int dev, const cb_dot_desc* desc, cb_plan** plan);

@@ -78,6 +78,12 @@ int cbg_fn_iota(cbg_function* f, int32_t dtype, int rank, const int64_t* dims, i
 int cbg_fn_convert_dtype(cbg_function* f, cbg_value* x, int32_t dtype, cbg_value** v);
 int cbg_fn_transpose(cbg_function* f, cbg_value* x, const int* permutation, cbg_value** v);
 
+/* FusedOps.FusedDense (fused_ops.go:336-347) with compute.DenseConfig (:72-78): y = act(x @ W + bias).
+ * weight_layout: 0 DenseLayoutInputOutputs (weight [in, out...]), 1 DenseLayoutOutputsInput ([out..., in]).
+ * Float32 and Float64 as in the reference, BFloat16 / Float16 as an extension. */
+int cbg_fn_fused_dense(cbg_function* f, cbg_value* x, cbg_value* weight, cbg_value* bias /* or NULL */,
+                       int activation, int weight_layout, cbg_value** v);
+
 /* FusedOps.FusedQuantizedDense (fused_ops.go:413-435) with compute.Quantization (:204-234).
  * scheme: 0 Linear, 1 NF4 (weights as Int8 / Uint8 nibble indices), 2 GGML (not built).  block_axis 1 is the reference
  * layout scales [K, ceil(N/block_size)]; block_axis 0 is this backend's extension, scales

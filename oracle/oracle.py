@@ -351,3 +351,27 @@ def sdpa_slice(q, k, v, b0, b1, h0, h1, layout="BHSD", scale=0.0, causal=False) 
     lib(True).orc_sdpa_f32_slice(_p(q), _p(k), _p(v), _p(out), B, Hq, Hkv, S, Skv, D, bshd,
                                  float(scale), int(causal), b0, b1, h0, h1)
     return out
+
+
+# ---------------------------------------------------------------- FusedDense
+def activation_f32(y: np.ndarray, activation: int) -> np.ndarray:
+    """fusedDenseApplyActivation on float32 data (dense.go:176-205), a copy is returned."""
+    out = np.array(y, np.float32, copy=True, order="C")
+    lib().orc_activation_f32(_p(out), out.size, activation)
+    return out
+
+
+def fused_dense(x, weight, bias=None, activation: int = ACT_NONE, outputs_input: bool = False, in_dtype: int = F32) -> np.ndarray:
+    """Reference FusedDense (fusedops/dense.go:34-163): DotGeneral contracting x's last axis with the weight's
+    first axis (or its last, `outputs_input`), bias added per flat out-feature index (`i % outFeatures`,
+    dense.go:166-174), then the activation; float32 and float64 as in the reference."""
+    assert in_dtype in (F32, F64)
+    x = _c(x, _NP_OF[in_dtype])
+    weight = _c(weight, _NP_OF[in_dtype])
+    y = dot_general(x, [x.ndim - 1], [], weight, [weight.ndim - 1 if outputs_input else 0], [], in_dtype)
+    if bias is not None:
+        b = _c(bias, _NP_OF[in_dtype]).reshape(-1)
+        y = (y.reshape(-1, b.size) + b[None, :]).astype(_NP_OF[in_dtype]).reshape(y.shape)
+    if in_dtype == F32:
+        return activation_f32(y, activation).reshape(y.shape)
+    return activation_f64(y, activation)

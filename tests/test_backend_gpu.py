@@ -160,6 +160,46 @@ def test_exec_protocol(backend):
         builder.Compile()
 
 
+# ---------------------------------------------------------------- FusedDense (fusedops.go:178-212)
+@pytest.mark.parametrize("case", load_golden("backendtest_dense_epilogue.json")["cases"], ids=lambda c: c["name"])
+@pytest.mark.parametrize("outputs_input", [False, True])
+def test_fused_dense_known_answers_through_api(backend, case, outputs_input):
+    x = tensor(case["x"], "f32")
+    w = tensor(case["w"], "i8").astype(np.float32)
+    bias = np.array(case["bias"], np.float32)
+    wv = np.ascontiguousarray(w.T) if outputs_input else w
+    cfg = be.DenseConfig(Activation=ACT[case["activation"]],
+                         WeightLayout=be.DENSE_LAYOUT_OUTPUTS_INPUT if outputs_input else be.DENSE_LAYOUT_INPUT_OUTPUTS)
+    (got,), _ = be.exec_graph(backend, [(x, dv.F32), (wv, dv.F32), (bias, dv.F32)], lambda f, p: f.FusedDense(p[0], p[1], p[2], cfg))
+    assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
+
+
+def test_fused_dense_shapes_and_validation(backend):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 3, 16)).astype(np.float32)
+    w = rng.standard_normal((16, 4, 5)).astype(np.float32)           # out features of rank 2
+    b = rng.standard_normal((4, 5)).astype(np.float32)
+    cfg = be.DenseConfig(Activation=dv.ACT_TANH)
+    (got,), (shape,) = be.exec_graph(backend, [(x, dv.F32), (w, dv.F32), (b, dv.F32)], lambda f, p: f.FusedDense(p[0], p[1], p[2], cfg))
+    assert shape == be.make_shape(dv.F32, 2, 3, 4, 5)
+    want = orc.fused_dense(x.reshape(6, 16), w.reshape(16, 20), b.reshape(20), orc.ACT_TANH).reshape(2, 3, 4, 5)
+    assert max_abs_normalised(got, want) < 1e-6
+    (plain,), _ = be.exec_graph(backend, [(x, dv.F32), (w, dv.F32)], lambda f, p: f.FusedDense(p[0], p[1], None))
+    assert max_abs_normalised(plain.reshape(6, 20), orc.fused_dense(x.reshape(6, 16), w.reshape(16, 20))) < 1e-6
+    f = backend.Builder("fd").Main()
+    xp = f.Parameter("x", be.make_shape(dv.F32, 2, 16))
+    wp = f.Parameter("w", be.make_shape(dv.F32, 8, 4))
+    with pytest.raises(BackendError) as e:        # dense.go:62-65
+        f.FusedDense(xp, wp, None)
+    assert "must match weight's first dim" in str(e.value)
+    with pytest.raises(BackendError):             # dense.go:81-82
+        f.FusedDense(xp, wp, None, be.DenseConfig(WeightLayout=7))
+    xi = f.Parameter("xi", be.make_shape(dv.I32, 2, 8))
+    wi = f.Parameter("wi", be.make_shape(dv.I32, 8, 4))
+    with pytest.raises(ErrNotImplemented):        # dense.go:160-162
+        f.FusedDense(xi, wi, None)
+
+
 # ---------------------------------------------------------------- FusedQuantizedDense
 @pytest.mark.parametrize("layout", ["ref", "channel", "kgroup"])
 def test_fused_quantized_dense_through_api(backend, layout):

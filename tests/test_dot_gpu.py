@@ -102,3 +102,52 @@ def test_config2_batched(dtype):
     got = ops.dot_normalised(lhs, rhs, in_dtype=code)
     want = as_f64(oracle_dot(lhs, rhs, code, False), code)
     assert max_abs_normalised(as_f64(got, code), want) < TOL[dtype]
+
+
+# ---------------------------------------------------------------- FusedDense (DotGeneral + bias + activation)
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "silu", "hard_swish", "tanh"])
+@pytest.mark.parametrize("dtype", ["f32", "f64"])
+def test_fused_dense_generic_matches_oracle(dtype, act):
+    """The reference's dtypes (fusedops/dense.go:149-163) on the CUDA-core kernel, both weight layouts."""
+    from tests.helpers import ACT
+    M, K, N = 7, 40, 37
+    code = DT[dtype]
+    x = make(3, (1, M, K), dtype)
+    w = make(4, (1, K, N), dtype, 0.3)
+    b = make(5, (N,), dtype)
+    want = orc.fused_dense(x[0], w[0], b, ACT[act], in_dtype=code)
+    got, plan = ops.dot_normalised(x, w, in_dtype=code, bias=b, activation=ACT[act], variant=dv.DOT_GENERIC, return_plan=True)
+    assert plan.kernel_name.endswith("_dense")
+    tol = 1e-6 if dtype == "f32" else 1e-13
+    assert max_abs_normalised(got[0].astype(np.float64), want.astype(np.float64)) < tol
+    got_t = ops.dot_normalised(x, np.ascontiguousarray(w.transpose(0, 2, 1)), in_dtype=code, rhs_transposed=True, bias=b,
+                               activation=ACT[act], variant=dv.DOT_GENERIC)
+    assert np.array_equal(got_t, got)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("act", ["none", "silu", "gelu"])
+def test_fused_dense_on_tensor_cores(dtype, act):
+    from tests.helpers import ACT
+    M, K, N = 200, 264, 136
+    code = DT[dtype]
+    x = make(6, (1, M, K), dtype)
+    w = make(7, (1, K, N), dtype, 0.1)
+    b = make(8, (N,), dtype)
+    f = lambda a: orc.to_f32(a, code) if dtype != "f32" else a
+    want = orc.fused_dense(f(x)[0].astype(np.float64), f(w)[0].astype(np.float64), f(b).astype(np.float64), ACT[act], in_dtype=orc.F64)
+    got, plan = ops.dot_normalised(x, w, in_dtype=code, bias=b, activation=ACT[act], variant=dv.DOT_TCGEN05, return_plan=True)
+    assert plan.kernel_name.startswith("gemm_tcgen05_") and plan.kernel_name.endswith("_dense")
+    assert max_abs_normalised(as_f64(got[0], code), want) < (1e-4 if dtype == "f32" else 2e-2)
+    # bias only, activation only
+    got_b = ops.dot_normalised(x, w, in_dtype=code, bias=b, variant=dv.DOT_TCGEN05)
+    want_b = orc.fused_dense(f(x)[0].astype(np.float64), f(w)[0].astype(np.float64), f(b).astype(np.float64), orc.ACT_NONE, in_dtype=orc.F64)
+    assert max_abs_normalised(as_f64(got_b[0], code), want_b) < (1e-4 if dtype == "f32" else 2e-2)
+
+
+def test_fused_dense_validation():
+    with pytest.raises(ErrNotImplemented):
+        dv.Plan.dot(1, 4, 4, 4, dv.I32, has_bias=True)
+    from compute_b200 import BackendError
+    with pytest.raises(BackendError):
+        dv.Plan.dot(1, 4, 4, 4, dv.F32, activation=17)

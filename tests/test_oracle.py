@@ -155,6 +155,17 @@ def test_dense_epilogue_golden(case):
     assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
 
 
+@pytest.mark.parametrize("case", DENSE, ids=[c["name"] for c in DENSE])
+def test_fused_dense_golden(case):
+    """The same reference cases (fusedops.go:178-212) through the oracle's FusedDense restatement."""
+    x = tensor(case["x"], "f32")
+    w = tensor(case["w"], "i8").astype(np.float32)
+    got = orc.fused_dense(x, w, np.array(case["bias"], np.float32), ACT[case["activation"]])
+    assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
+    got_t = orc.fused_dense(x, np.ascontiguousarray(w.T), np.array(case["bias"], np.float32), ACT[case["activation"]], outputs_input=True)
+    assert np.array_equal(got_t, got)
+
+
 def test_qdense_hand_computed():
     # K=2, N=4, BlockSize=2, power-of-two scales: every product is exact.
     x = np.float32([[1, 2], [-3, 0.5]])
