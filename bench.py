@@ -187,6 +187,24 @@ def other_kernels(dv, dev, stream):
                                                      "frac_of_measured_bf16_peak": tf / tpeak}
     for m in (q, k, v, o):
         m.free()
+    # the bandwidth-bound fused ops around the dense layers: 65536 rows of 4096 float32 (1 GiB in, 1 GiB out)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hpeak = float(json.load(f)["hbm_gbs"])
+    except Exception:
+        hpeak = FALLBACK_HBM_GBS
+    rows, L = 65536, 4096
+    xf = dv.DeviceMem.from_numpy(rng.standard_normal(rows * L, dtype=np.float32), dev)
+    gf = dv.DeviceMem.from_numpy(rng.standard_normal(L, dtype=np.float32), dev)
+    yf = dv.DeviceMem(rows * L * 4, dev)
+    for name, plan, ins in (("fused_softmax_65536x4096_f32", dv.Plan.softmax(dv.F32, rows, L, 1, dev=dev), [xf.ptr]),
+                            ("fused_layer_norm_65536x4096_f32", dv.Plan.layernorm(dv.F32, rows, L, 1e-5, True, True, dev=dev), [xf.ptr, gf.ptr, gf.ptr]),
+                            ("fused_gelu_268M_f32", dv.Plan.gelu(dv.F32, rows * L, True, dev=dev), [xf.ptr])):
+        us = time_plan(plan, ins, [yf.ptr], 10)
+        gbs = 2.0 * rows * L * 4 / us / 1e3
+        res[name] = {"kernel": plan.kernel_name, "us": us, "GB/s": gbs, "frac_of_measured_hbm": gbs / hpeak}
+    for m in (xf, gf, yf):
+        m.free()
     return res
 
 

@@ -21,9 +21,10 @@ from ._lib import BackendError, ErrNotImplemented, check
 
 # compute.OpType values used by Capabilities (optype.go)
 OP_PARAMETER, OP_CONSTANT, OP_DOT_GENERAL = 1, 2, 32
+OP_FUSED_SOFTMAX, OP_FUSED_LAYER_NORM, OP_FUSED_GELU, OP_FUSED_DENSE = 116, 117, 118, 119
 OP_FUSED_SDPA, OP_FUSED_QUANTIZED_DENSE = 120, 123
-OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 120: "FusedScaledDotProductAttention",
-            123: "FusedQuantizedDense"}
+OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 116: "FusedSoftmax", 117: "FusedLayerNorm", 118: "FusedGelu",
+            119: "FusedDense", 120: "FusedScaledDotProductAttention", 123: "FusedQuantizedDense"}
 
 # compute.QuantizationScheme (fused_ops.go:81-98)
 QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
@@ -70,6 +71,9 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_iota": ([C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_convert_dtype": ([C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_transpose": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_softmax": ([C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_gelu": ([C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_layer_norm": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
@@ -327,6 +331,24 @@ class Function:
         return self._v(h)
 
     # ---- FusedOps on the path
+    def FusedSoftmax(self, x: Value, axis: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_softmax(self.handle, x.handle, axis, C.byref(h)))
+        return self._v(h)
+
+    def FusedGelu(self, x: Value, exact: bool) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_gelu(self.handle, x.handle, int(exact), C.byref(h)))
+        return self._v(h)
+
+    def FusedLayerNorm(self, x: Value, axes: Sequence[int], epsilon: float, gamma: Optional[Value] = None,
+                       beta: Optional[Value] = None) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_fused_layer_norm(self.handle, x.handle, _ints(axes), len(axes), float(epsilon),
+                                           gamma.handle if gamma is not None else None,
+                                           beta.handle if beta is not None else None, C.byref(h)))
+        return self._v(h)
+
     def FusedDense(self, x: Value, weight: Value, bias: Optional[Value], options: Optional[DenseConfig] = None) -> Value:
         o = options or DenseConfig()
         h = C.c_void_p()

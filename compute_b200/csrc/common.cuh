@@ -61,13 +61,15 @@ const char* dtype_name(int d);
 
 // ---- plans ------------------------------------------------------------------
 enum PlanKind { PLAN_QDENSE = 1, PLAN_DOT, PLAN_SDPA, PLAN_COPY, PLAN_CONVERT, PLAN_IOTA,
-                PLAN_SLICE, PLAN_TRANSPOSE };
+                PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM };
 
 struct HelperDesc {
   int32_t dtype = 0, dtype_to = 0, rank = 0, axis = 0;
   int64_t n = 0;
   int64_t dims[8] = {0}, starts[8] = {0}, strides[8] = {0}, out_dims[8] = {0};
   int32_t perm[8] = {0};
+  double eps = 0.0;        // layer norm
+  int32_t flags = 0;       // layer norm: 1 = gamma, 2 = beta
 };
 
 }  // namespace cb
@@ -100,6 +102,8 @@ int sdpa_plan(cb_plan* p);
 int sdpa_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int helper_plan(cb_plan* p);
 int helper_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+int fused_small_plan(cb_plan* p);
+int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s);
 int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsigned* status_word, cudaStream_t s);
 

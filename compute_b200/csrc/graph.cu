@@ -41,7 +41,8 @@ struct Shape {
   }
 };
 
-enum NodeKind { N_PARAM, N_CONST, N_DOT, N_QDENSE, N_SDPA, N_RESHAPE, N_SLICE, N_IOTA, N_CONVERT, N_TRANSPOSE };
+enum NodeKind { N_PARAM, N_CONST, N_DOT, N_QDENSE, N_SDPA, N_RESHAPE, N_SLICE, N_IOTA, N_CONVERT, N_TRANSPOSE,
+                N_GELU, N_SOFTMAX, N_LAYERNORM };
 
 bool is_float(int d) { return d == CB_F16 || d == CB_F32 || d == CB_F64 || d == CB_BF16 || d == CB_F8E4M3FN || d == CB_F8E5M2; }
 bool is_half(int d) { return d == CB_F16 || d == CB_BF16; }
@@ -129,6 +130,9 @@ struct cbg_value {
   std::vector<int64_t> starts, limits, strides;
   std::vector<int32_t> perm;
   int axis = 0;
+  int64_t small_dims[3] = {0, 0, 0};   // softmax [outer, axis, inner]; layer norm [rows, norm size, 1]
+  double epsilon = 0.0;               // layer norm
+  int flags = 0;                      // gelu: exact; layer norm: 1 gamma, 2 beta
 };
 
 struct cbg_function {
@@ -275,11 +279,11 @@ int cbg_backend_num_devices(const cbg_backend* b) { return b ? b->n_devices : 0;
 int cbg_backend_device_description(const cbg_backend* b, int dev, char* buf, size_t n) { return cb_device_desc(dev, buf, n); }
 
 int cbg_backend_capabilities(const cbg_backend* b, int32_t* ops, int* n_ops, int32_t* dtypes, int* n_dtypes) {
-  // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32,
-  // FusedScaledDotProductAttention 120, FusedQuantizedDense 123.  The helper ops
+  // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32, FusedSoftmax 116, FusedLayerNorm 117,
+  // FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120, FusedQuantizedDense 123.  The helper ops
   // (Reshape, Slice, Iota, ConvertDType, Transpose) exist to serve DotGeneral and are
   // deliberately not advertised.
-  static const int32_t k_ops[] = {1, 2, 32, 120, 123};
+  static const int32_t k_ops[] = {1, 2, 32, 116, 117, 118, 119, 120, 123};
   static const int32_t k_dtypes[] = {CB_BOOL, CB_I8, CB_I32, CB_I64, CB_U8, CB_F16, CB_F32, CB_F64, CB_BF16};
   const int no = (int)(sizeof(k_ops) / sizeof(k_ops[0])), nd = (int)(sizeof(k_dtypes) / sizeof(k_dtypes[0]));
   if (ops && n_ops) for (int i = 0; i < std::min(*n_ops, no); i++) ops[i] = k_ops[i];
@@ -642,6 +646,86 @@ int cbg_fn_dot_general(cbg_function* f, cbg_value* lhs, const int* lhs_contract,
   return CB_OK;
 }
 
+static int check_small_dtype(const char* op, const cbg_value* x) {
+  const int d = x->shape.dtype;
+  if (d != CB_F32 && d != CB_F64 && d != CB_BF16 && d != CB_F16) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: dtype %s", op, cb::dtype_name(d));
+  return CB_OK;
+}
+
+// FusedOps.FusedSoftmax (fused_ops.go:318-323; internal/gobackend/fusedops/softmax.go:29-45): one non-negative axis.
+int cbg_fn_fused_softmax(cbg_function* f, cbg_value* x, int axis, cbg_value** v) {
+  const char* op = "FusedSoftmax";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  const int rank = (int)x->shape.dims.size();
+  if (axis < 0 || axis >= rank) return fail(CB_ERR_INVALID_ARG, "%s: axis %d out of range for rank %d", op, axis, rank);
+  CB_TRY(check_small_dtype(op, x));
+  cbg_value* n = add_node(f, N_SOFTMAX, x->shape, {x});
+  n->small_dims[0] = n->small_dims[2] = 1;
+  for (int i = 0; i < axis; i++) n->small_dims[0] *= x->shape.dims[i];
+  n->small_dims[1] = x->shape.dims[axis];
+  for (int i = axis + 1; i < rank; i++) n->small_dims[2] *= x->shape.dims[i];
+  *v = n;
+  return CB_OK;
+}
+
+// FusedOps.FusedGelu (fused_ops.go:325-328; fusedops/gelu.go:31-41).
+int cbg_fn_fused_gelu(cbg_function* f, cbg_value* x, int exact, cbg_value** v) {
+  const char* op = "FusedGelu";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  CB_TRY(check_small_dtype(op, x));
+  cbg_value* n = add_node(f, N_GELU, x->shape, {x});
+  n->flags = exact ? 1 : 0;
+  *v = n;
+  return CB_OK;
+}
+
+// FusedOps.FusedLayerNorm (fused_ops.go:330-333; fusedops/layernorm.go:40-68, :96-127): negative axes count from
+// the end; gamma and beta are indexed by the flat position inside the normalised axes, in the order given.  Axes
+// that are not the trailing ones are moved there by a transposition and moved back afterwards.
+int cbg_fn_fused_layer_norm(cbg_function* f, cbg_value* x, const int* axes, int n_axes, double epsilon, cbg_value* gamma,
+                            cbg_value* beta, cbg_value** v) {
+  const char* op = "FusedLayerNorm";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  if (gamma) CB_TRY(check_values(f, op, {gamma}));
+  if (beta) CB_TRY(check_values(f, op, {beta}));
+  const int rank = (int)x->shape.dims.size();
+  if (n_axes < 0 || (n_axes > 0 && !axes)) return fail(CB_ERR_INVALID_ARG, "%s: axes are NULL", op);
+  std::vector<int> norm;
+  std::vector<bool> is_norm(rank, false);
+  for (int i = 0; i < n_axes; i++) {
+    int a = axes[i] < 0 ? axes[i] + rank : axes[i];
+    if (a < 0 || a >= rank) return fail(CB_ERR_INVALID_ARG, "%s: axis %d out of range for rank %d", op, axes[i], rank);
+    if (is_norm[a]) return fail(CB_ERR_INVALID_ARG, "%s: axis %d given more than once", op, axes[i]);
+    is_norm[a] = true;
+    norm.push_back(a);
+  }
+  CB_TRY(check_small_dtype(op, x));
+  int64_t norm_size = 1;
+  for (int a : norm) norm_size *= x->shape.dims[a];
+  for (cbg_value* g : {gamma, beta})
+    if (g && (g->shape.dtype != x->shape.dtype || g->shape.size() != norm_size))
+      return fail(CB_ERR_INVALID_ARG, "%s: gamma and beta must have the dtype of x and %lld elements, got %s", op, (long long)norm_size, g->shape.str().c_str());
+  std::vector<int> perm, inverse(rank);
+  for (int a = 0; a < rank; a++) if (!is_norm[a]) perm.push_back(a);
+  for (int a : norm) perm.push_back(a);
+  for (int i = 0; i < rank; i++) inverse[perm[i]] = i;
+  cbg_value* xt = transpose_node(f, x, perm);
+  std::vector<cbg_value*> ins = {xt};
+  if (gamma) ins.push_back(gamma);
+  if (beta) ins.push_back(beta);
+  cbg_value* n = add_node(f, N_LAYERNORM, xt->shape, ins);
+  n->small_dims[0] = norm_size ? x->shape.size() / norm_size : 0;
+  n->small_dims[1] = norm_size;
+  n->small_dims[2] = 1;
+  n->epsilon = epsilon;
+  n->flags = (gamma ? 1 : 0) | (beta ? 2 : 0);
+  *v = transpose_node(f, n, inverse);
+  return CB_OK;
+}
+
 // FusedOps.FusedDense (fused_ops.go:336-347; builder internal/gobackend/fusedops/dense.go:34-108): the matmul is a
 // DotGeneral contracting x's last axis with the weight's first (InputOutputs) or last (OutputsInput) axis; bias and
 // activation become the epilogue of that same kernel instead of a second pass over the result.
@@ -867,6 +951,11 @@ int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec) {
         break;
       case N_IOTA: st = cb_plan_iota(dev, n->shape.dtype, (int)n->shape.dims.size(), n->shape.dims.data(), n->axis, &p); break;
       case N_CONVERT: st = cb_plan_convert(dev, n->inputs[0]->shape.dtype, n->shape.dtype, n->shape.size(), &p); break;
+      case N_GELU: st = cb_plan_gelu(dev, n->shape.dtype, n->shape.size(), n->flags, &p); break;
+      case N_SOFTMAX: st = cb_plan_softmax(dev, n->shape.dtype, n->small_dims[0], n->small_dims[1], n->small_dims[2], &p); break;
+      case N_LAYERNORM:
+        st = cb_plan_layernorm(dev, n->shape.dtype, n->small_dims[0], n->small_dims[1], n->epsilon, n->flags & 1, (n->flags & 2) ? 1 : 0, &p);
+        break;
       case N_TRANSPOSE:
         st = cb_plan_transpose(dev, n->shape.dtype, (int)n->inputs[0]->shape.dims.size(), n->inputs[0]->shape.dims.data(), n->perm.data(), &p);
         break;

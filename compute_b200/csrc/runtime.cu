@@ -396,6 +396,34 @@ int cb_plan_transpose(int dev, int32_t dtype, int32_t rank, const int64_t* dims,
   return finish_plan(helper_plan(p), p, plan);
 }
 
+int cb_plan_gelu(int dev, int32_t dtype, int64_t n, int32_t exact, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_GELU, plan, &p));
+  p->helper.dtype = dtype;
+  p->helper.n = n;
+  p->helper.axis = exact ? 1 : 0;
+  return finish_plan(fused_small_plan(p), p, plan);
+}
+
+int cb_plan_softmax(int dev, int32_t dtype, int64_t outer, int64_t axis_size, int64_t inner, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_SOFTMAX, plan, &p));
+  p->helper.dtype = dtype;
+  p->helper.dims[0] = outer; p->helper.dims[1] = axis_size; p->helper.dims[2] = inner;
+  return finish_plan(fused_small_plan(p), p, plan);
+}
+
+int cb_plan_layernorm(int dev, int32_t dtype, int64_t rows, int64_t norm_size, double epsilon, int32_t has_gamma,
+                      int32_t has_beta, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_LAYERNORM, plan, &p));
+  p->helper.dtype = dtype;
+  p->helper.dims[0] = rows; p->helper.dims[1] = norm_size; p->helper.dims[2] = 1;
+  p->helper.eps = epsilon;
+  p->helper.flags = (has_gamma ? 1 : 0) | (has_beta ? 2 : 0);
+  return finish_plan(fused_small_plan(p), p, plan);
+}
+
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes) {
   clear_error();
   if (!plan || !bytes) return fail(CB_ERR_INVALID_ARG, "NULL argument");
@@ -444,6 +472,7 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
     case PLAN_QDENSE: return qdense_launch(plan, inputs, outputs, workspace, s);
     case PLAN_DOT: return dot_launch(plan, inputs, outputs, workspace, s);
     case PLAN_SDPA: return sdpa_launch(plan, inputs, outputs, workspace, s);
+    case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: return fused_small_launch(plan, inputs, outputs, workspace, s);
     default: return helper_launch(plan, inputs, outputs, workspace, s);
   }
 }

@@ -254,6 +254,24 @@ class Plan:
         return cls(h, dev)
 
     @classmethod
+    def gelu(cls, dtype, n, exact=True, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_gelu(dev, dtype, n, int(exact), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def softmax(cls, dtype, outer, axis_size, inner=1, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_softmax(dev, dtype, outer, axis_size, inner, C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def layernorm(cls, dtype, rows, norm_size, epsilon=1e-5, has_gamma=False, has_beta=False, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_layernorm(dev, dtype, rows, norm_size, float(epsilon), int(has_gamma), int(has_beta), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
     def sdpa(cls, B, Hq, Hkv, S, Skv, D, dtype=F32, layout=LAYOUT_BHSD, scale=0.0, causal=False,
              mask_kind=MASK_NONE, mask_dims: Sequence[int] = (), has_seq_lens=False,
              bias_dims: Sequence[int] = (), variant=SDPA_AUTO, dev=0) -> "Plan":

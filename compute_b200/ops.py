@@ -142,3 +142,29 @@ def sdpa(q: np.ndarray, k: np.ndarray, v: np.ndarray, *, dtype: int = dv.F32, la
                         q_len is not None, bias_dims, variant, dev)
     out = _run(plan, ins, q.shape, carrier, dev)
     return (out, plan) if return_plan else out
+
+
+def softmax(x: np.ndarray, axis: int, *, dtype: int = dv.F32, dev: int = 0) -> np.ndarray:
+    """FusedSoftmax along one non-negative axis; x in the numpy carrier of `dtype`."""
+    x = np.ascontiguousarray(x, dv.NP_CARRIER[dtype])
+    if axis < 0 or axis >= x.ndim:
+        raise BackendError(ERR_INVALID_ARG, f"FusedSoftmax: axis {axis} out of range for rank {x.ndim}")
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    return _run(dv.Plan.softmax(dtype, outer, x.shape[axis], inner, dev), [x], x.shape, dv.NP_CARRIER[dtype], dev)
+
+
+def gelu(x: np.ndarray, exact: bool = True, *, dtype: int = dv.F32, dev: int = 0) -> np.ndarray:
+    """FusedGelu (erf form, or the tanh approximation)."""
+    x = np.ascontiguousarray(x, dv.NP_CARRIER[dtype])
+    return _run(dv.Plan.gelu(dtype, x.size, exact, dev), [x], x.shape, dv.NP_CARRIER[dtype], dev)
+
+
+def layer_norm_rows(x: np.ndarray, epsilon: float, gamma: Optional[np.ndarray] = None, beta: Optional[np.ndarray] = None, *,
+                    dtype: int = dv.F32, dev: int = 0) -> np.ndarray:
+    """FusedLayerNorm over the last axis of a 2-D x (other axis sets are transposed by the graph layer)."""
+    x = np.ascontiguousarray(x, dv.NP_CARRIER[dtype])
+    rows, L = x.shape
+    ins = [x] + [np.ascontiguousarray(a, dv.NP_CARRIER[dtype]).reshape(L) for a in (gamma, beta) if a is not None]
+    plan = dv.Plan.layernorm(dtype, rows, L, epsilon, gamma is not None, beta is not None, dev)
+    return _run(plan, ins, x.shape, dv.NP_CARRIER[dtype], dev)

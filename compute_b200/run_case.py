@@ -3,6 +3,7 @@
     python -m compute_b200.run_case gemm --dtype bf16 --b 1 --m 4096 --n 4096 --k 4096
     python -m compute_b200.run_case sdpa --b 8 --hq 32 --hkv 8 --s 2048 --d 128 --causal
     python -m compute_b200.run_case qdense --m 16            # decode (M <= 16) or prefill (M > 16)
+    python -m compute_b200.run_case softmax --m 65536 --n 4096   # also: gelu, layernorm (rows --m, row length --n)
 
 A small stand-alone driver for timing or profiling a single plan (inputs are seeded random
 data resident on the device; time is taken with CUDA events on the launching stream).  The
@@ -38,7 +39,7 @@ def _time(plan, ins, outs, dev, stream, reps, warmup):
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["gemm", "sdpa", "qdense"])
+    ap.add_argument("case", choices=["gemm", "sdpa", "qdense", "softmax", "gelu", "layernorm"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--b", type=int, default=1)
     ap.add_argument("--m", type=int, default=4096)
@@ -79,6 +80,23 @@ def main() -> None:
         us = _time(plan, [q.ptr, k.ptr, v.ptr], [o.ptr], dev, stream, a.reps, a.warmup)
         pairs = a.s * (a.s + 1) / 2 if a.causal else a.s * a.s
         out.update(kernel=plan.kernel_name, us=us, tflops=4.0 * a.b * a.hq * a.d * pairs / us / 1e6)
+    elif a.case in ("softmax", "gelu", "layernorm"):
+        code = dv.BF16 if a.dtype == "bf16" else dv.F32
+        size = 2 if a.dtype == "bf16" else 4
+        rows, L = a.m, a.n
+        x = dv.DeviceMem.from_numpy(_bf16(rng, rows * L, 1.0) if a.dtype == "bf16" else rng.standard_normal(rows * L, dtype=np.float32), dev)
+        y = dv.DeviceMem(rows * L * size, dev)
+        ins = [x.ptr]
+        if a.case == "softmax":
+            plan = dv.Plan.softmax(code, rows, L, 1, dev=dev)
+        elif a.case == "gelu":
+            plan = dv.Plan.gelu(code, rows * L, True, dev=dev)
+        else:
+            g = dv.DeviceMem.from_numpy(_bf16(rng, L, 1.0) if a.dtype == "bf16" else rng.standard_normal(L, dtype=np.float32), dev)
+            plan = dv.Plan.layernorm(code, rows, L, 1e-5, True, True, dev=dev)
+            ins += [g.ptr, g.ptr]
+        us = _time(plan, ins, [y.ptr], dev, stream, a.reps, a.warmup)
+        out.update(kernel=plan.kernel_name, us=us, GBps=2.0 * rows * L * size / us / 1e3)
     else:
         K, N = a.k, a.n if a.n != 4096 else 14336
         code = dv.BF16 if a.dtype == "bf16" else dv.F32

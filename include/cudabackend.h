@@ -201,6 +201,15 @@ int cb_plan_slice(int dev, int32_t dtype, int32_t rank, const int64_t* dims, con
 int cb_plan_transpose(int dev, int32_t dtype, int32_t rank, const int64_t* dims,
                       const int32_t* permutation, cb_plan** plan);
 
+/* ---- FusedGelu, FusedSoftmax, FusedLayerNorm (FusedOps, fused_ops.go:318-334; internal/gobackend/fusedops/gelu.go,
+ *      softmax.go, layernorm.go).  Float32 / Float64 as the reference, BFloat16 / Float16 computed in f32.
+ *      softmax: x viewed as [outer, axis_size, inner].  layer norm: rows of norm_size trailing elements;
+ *      launch inputs x, gamma?, beta? (gamma / beta [norm_size], dtype of x). */
+int cb_plan_gelu(int dev, int32_t dtype, int64_t n_elements, int32_t exact, cb_plan** plan);
+int cb_plan_softmax(int dev, int32_t dtype, int64_t outer, int64_t axis_size, int64_t inner, cb_plan** plan);
+int cb_plan_layernorm(int dev, int32_t dtype, int64_t rows, int64_t norm_size, double epsilon, int32_t has_gamma,
+                      int32_t has_beta, cb_plan** plan);
+
 /* ---- plans ("compile-time kernel selection by shape and dtype": created in Builder.Compile,
  *      builder.go:29-82; launched from Executable.Execute, executable.go:10-37) */
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes);

@@ -78,6 +78,13 @@ int cbg_fn_iota(cbg_function* f, int32_t dtype, int rank, const int64_t* dims, i
 int cbg_fn_convert_dtype(cbg_function* f, cbg_value* x, int32_t dtype, cbg_value** v);
 int cbg_fn_transpose(cbg_function* f, cbg_value* x, const int* permutation, cbg_value** v);
 
+/* FusedOps.FusedSoftmax / FusedGelu / FusedLayerNorm (fused_ops.go:318-334).  Softmax takes one non-negative axis;
+ * layer-norm axes may be negative (counted from the end) and need not be trailing; gamma / beta may be NULL. */
+int cbg_fn_fused_softmax(cbg_function* f, cbg_value* x, int axis, cbg_value** v);
+int cbg_fn_fused_gelu(cbg_function* f, cbg_value* x, int exact, cbg_value** v);
+int cbg_fn_fused_layer_norm(cbg_function* f, cbg_value* x, const int* axes, int n_axes, double epsilon,
+                            cbg_value* gamma /* or NULL */, cbg_value* beta /* or NULL */, cbg_value** v);
+
 /* FusedOps.FusedDense (fused_ops.go:336-347) with compute.DenseConfig (:72-78): y = act(x @ W + bias).
  * weight_layout: 0 DenseLayoutInputOutputs (weight [in, out...]), 1 DenseLayoutOutputsInput ([out..., in]).
  * Float32 and Float64 as in the reference, BFloat16 / Float16 as an extension. */

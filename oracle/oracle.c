@@ -273,6 +273,72 @@ void orc_qdense_nf4(const float* x, const void* w, const float* scales, const fl
 }
 
 /* ------------------------------------------------------------------ */
+/* FusedSoftmax, FusedGelu, FusedLayerNorm                            */
+/* ------------------------------------------------------------------ */
+
+/* softmax.go:83-118: x viewed as [outer, L, inner]; per line: max, exp(x - max) summed in index
+ * order, scaled by 1 / sum.  (The reference's float32 path uses its fastmath.Exp32 approximation;
+ * this restatement uses libm, and comparisons carry a tolerance.) */
+#define ORC_SOFTMAX(NAME, T, EXPF)                                                          \
+  void NAME(const T* x, T* y, int64_t outer, int64_t L, int64_t inner) {                    \
+    for (int64_t o = 0; o < outer; o++)                                                     \
+      for (int64_t in = 0; in < inner; in++) {                                              \
+        const int64_t base = o * L * inner + in;                                            \
+        T mx = (T)(-INFINITY);                                                              \
+        for (int64_t i = 0; i < L; i++) if (x[base + i * inner] > mx) mx = x[base + i * inner]; \
+        T sum = 0;                                                                          \
+        for (int64_t i = 0; i < L; i++) { y[base + i * inner] = (T)EXPF(x[base + i * inner] - mx); sum += y[base + i * inner]; } \
+        const T inv = (T)1 / sum;                                                           \
+        for (int64_t i = 0; i < L; i++) y[base + i * inner] *= inv;                         \
+      }                                                                                     \
+  }
+ORC_SOFTMAX(orc_softmax_f32, float, expf)
+ORC_SOFTMAX(orc_softmax_f64, double, exp)
+
+/* gelu.go:113-126: exact x/2 (1 + erf(x / sqrt 2)), or the tanh form; erf / tanh evaluated in double
+ * and rounded to T, the surrounding arithmetic in T. */
+void orc_gelu_f32(const float* x, float* y, size_t n, int exact) {
+  const float inv_sqrt2 = (float)(1.0 / sqrt(2.0)), c = (float)sqrt(2.0 / M_PI);
+  for (size_t i = 0; i < n; i++) {
+    const float v = x[i];
+    if (exact) y[i] = v * 0.5f * (1.0f + (float)erf((double)(v * inv_sqrt2)));
+    else { const float inner = c * (v + 0.044715f * v * v * v); y[i] = v * 0.5f * (1.0f + (float)tanh((double)inner)); }
+  }
+}
+void orc_gelu_f64(const double* x, double* y, size_t n, int exact) {
+  const double inv_sqrt2 = 1.0 / sqrt(2.0), c = sqrt(2.0 / M_PI);
+  for (size_t i = 0; i < n; i++) {
+    const double v = x[i];
+    if (exact) y[i] = v * 0.5 * (1.0 + erf(v * inv_sqrt2));
+    else { const double inner = c * (v + 0.044715 * v * v * v); y[i] = v * 0.5 * (1.0 + tanh(inner)); }
+  }
+}
+
+/* layernorm.go:129-168 (trailing axes): per row mean, variance of the differences (both summed in
+ * index order, divided by L), invStd = T(1 / sqrt(double(var) + eps)), then gamma and beta. */
+#define ORC_LAYERNORM(NAME, T)                                                              \
+  void NAME(const T* x, const T* gamma, const T* beta, T* y, int64_t rows, int64_t L, double eps) { \
+    for (int64_t r = 0; r < rows; r++) {                                                    \
+      const T* xr = x + r * L;                                                              \
+      T sum = 0;                                                                            \
+      for (int64_t i = 0; i < L; i++) sum += xr[i];                                         \
+      const T mean = sum / (T)L;                                                            \
+      T vs = 0;                                                                             \
+      for (int64_t i = 0; i < L; i++) { const T d = xr[i] - mean; vs += d * d; }            \
+      const T var = vs / (T)L;                                                              \
+      const T inv_std = (T)(1.0 / sqrt((double)var + eps));                                 \
+      for (int64_t i = 0; i < L; i++) {                                                     \
+        T v = (xr[i] - mean) * inv_std;                                                     \
+        if (gamma) v *= gamma[i];                                                           \
+        if (beta) v += beta[i];                                                             \
+        y[r * L + i] = v;                                                                   \
+      }                                                                                     \
+    }                                                                                       \
+  }
+ORC_LAYERNORM(orc_layernorm_f32, float)
+ORC_LAYERNORM(orc_layernorm_f64, double)
+
+/* ------------------------------------------------------------------ */
 /* DotGeneral                                                         */
 /* ------------------------------------------------------------------ */
 

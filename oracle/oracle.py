@@ -375,3 +375,53 @@ def fused_dense(x, weight, bias=None, activation: int = ACT_NONE, outputs_input:
     if in_dtype == F32:
         return activation_f32(y, activation).reshape(y.shape)
     return activation_f64(y, activation)
+
+
+# ---------------------------------------------------------------- FusedSoftmax / FusedGelu / FusedLayerNorm
+def _fp(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype not in (np.float32, np.float64):
+        a = a.astype(np.float32)
+    return a, ("f32" if a.dtype == np.float32 else "f64")
+
+
+def softmax(x, axis: int) -> np.ndarray:
+    """Reference FusedSoftmax (softmax.go:83-118) along one non-negative axis."""
+    x, suf = _fp(x)
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    y = np.empty_like(x)
+    fn = getattr(lib(), "orc_softmax_" + suf)
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
+    fn(_p(x), _p(y), outer, x.shape[axis], inner)
+    return y
+
+
+def gelu(x, exact: bool = True) -> np.ndarray:
+    """Reference FusedGelu (gelu.go:113-126)."""
+    x, suf = _fp(x)
+    y = np.empty_like(x)
+    fn = getattr(lib(), "orc_gelu_" + suf)
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    fn(_p(x), _p(y), x.size, int(exact))
+    return y
+
+
+def layer_norm(x, axes, epsilon: float, gamma=None, beta=None) -> np.ndarray:
+    """Reference FusedLayerNorm (layernorm.go:96-246): axes (negative = from the end) are moved to the end in
+    the order given, each row normalised, and the result moved back; gamma / beta are indexed by the flat
+    position inside the normalised axes."""
+    x, suf = _fp(x)
+    rank = x.ndim
+    norm = [a + rank if a < 0 else a for a in axes]
+    perm = [a for a in range(rank) if a not in norm] + norm
+    xt = np.ascontiguousarray(np.transpose(x, perm))
+    L = int(np.prod([x.shape[a] for a in norm], dtype=np.int64))
+    rows = xt.size // L if L else 0
+    y = np.empty_like(xt)
+    g = None if gamma is None else np.ascontiguousarray(gamma, x.dtype).reshape(-1)
+    b = None if beta is None else np.ascontiguousarray(beta, x.dtype).reshape(-1)
+    fn = getattr(lib(), "orc_layernorm_" + suf)
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_double]
+    fn(_p(xt), _p(g), _p(b), _p(y), rows, L, float(epsilon))
+    return np.ascontiguousarray(np.transpose(y, np.argsort(perm)))

@@ -210,3 +210,19 @@ nf4 = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
        0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0]
 with open(os.path.join(HERE, "nf4_table.json"), "w") as f:
     json.dump(dict(source="gomlx/compute fused_ops.go:114-121", values=nf4), f, indent=1)
+
+# FusedSoftmax / FusedGelu / FusedLayerNorm known answers (support/backendtest/fusedops.go:22-177).
+small_cases = dict(
+    softmax_1d=dict(cite=f"{F}:24-37", x=[1.0, 2.0, 3.0, 4.0], axis=0,
+                    want=[0.0320586, 0.0871443, 0.2368828, 0.6439143], tol=1e-3),
+    softmax_rows_sum_to_one=dict(cite=f"{F}:39-55", x=[[1, 2, 3], [4, 5, 6]], axis=1, tol=1e-3),
+    softmax_stability=dict(cite=f"{F}:67-87", x=[1000, 1001, 1002], axis=0, tol=1e-3),
+    gelu_exact=dict(cite=f"{F}:90-103", x=[-2.0, -1.0, -0.5, 0.0, 0.5, 1.0, 2.0],
+                    want=[-0.04550028, -0.15865526, -0.15426877, 0.0, 0.34573123, 0.84134474, 1.9544997], tol=1e-3),
+    layernorm_simple=dict(cite=f"{F}:128-157", x=[[1, 2, 3, 4], [5, 6, 7, 8]], axes=[1], epsilon=1e-5, mean_tol=1e-5, var_tol=1e-3),
+    layernorm_gamma_beta=dict(cite=f"{F}:159-176", x=[1, 2, 3], gamma=[2, 2, 2], beta=[1, 1, 1], axes=[0], epsilon=1e-5,
+                              want=[(1.0 - 2.0) / math.sqrt(2.0 / 3.0 + 1e-5) * 2.0 + 1.0, 1.0,
+                                    (3.0 - 2.0) / math.sqrt(2.0 / 3.0 + 1e-5) * 2.0 + 1.0], tol=1e-4),
+)
+with open(os.path.join(HERE, "backendtest_fused_small.json"), "w") as f:
+    json.dump(dict(source="gomlx/compute " + F, cases=small_cases), f, indent=1)

@@ -25,7 +25,8 @@ def test_backend_identity(backend):
     assert backend.Name() == "cuda" and backend.NumDevices() >= 1
     assert "B200" in backend.Description() or "cuda:0" in backend.Description()
     caps = backend.Capabilities()
-    for op in (be.OP_PARAMETER, be.OP_CONSTANT, be.OP_DOT_GENERAL, be.OP_FUSED_QUANTIZED_DENSE, be.OP_FUSED_SDPA):
+    for op in (be.OP_PARAMETER, be.OP_CONSTANT, be.OP_DOT_GENERAL, be.OP_FUSED_QUANTIZED_DENSE, be.OP_FUSED_SDPA,
+               be.OP_FUSED_DENSE, be.OP_FUSED_SOFTMAX, be.OP_FUSED_GELU, be.OP_FUSED_LAYER_NORM):
         assert caps.Operations.get(op)
     assert caps.DTypes.get(dv.BF16) and caps.DTypes.get(dv.F64) and not caps.Functions
     assert not backend.HasSharedBuffers()

@@ -238,6 +238,46 @@ def test_nf4_table_and_dense():
     assert np.allclose(got, want, rtol=0, atol=1e-7)
 
 
+SMALL = load_golden("backendtest_fused_small.json")["cases"]
+
+
+def check_fused_small(softmax, gelu, layer_norm):
+    """The reference's assertions for FusedSoftmax / FusedGelu / FusedLayerNorm (fusedops.go:22-177), against any
+    implementation of the three ops on float32 arrays."""
+    c = SMALL["softmax_1d"]
+    assert np.allclose(softmax(np.float32(c["x"]), c["axis"]), np.float32(c["want"]), rtol=0, atol=c["tol"])
+    c = SMALL["softmax_rows_sum_to_one"]
+    assert np.allclose(softmax(np.float32(c["x"]), c["axis"]).sum(axis=1), 1.0, rtol=0, atol=c["tol"])
+    c = SMALL["softmax_stability"]
+    y = softmax(np.float32(c["x"]), c["axis"])
+    assert np.isfinite(y).all() and abs(float(y.sum()) - 1.0) < c["tol"]
+    c = SMALL["gelu_exact"]
+    exact = gelu(np.float32(c["x"]), True)
+    assert np.allclose(exact, np.float32(c["want"]), rtol=0, atol=c["tol"])
+    assert np.abs(gelu(np.float32(c["x"]), False) - exact).max() > 1e-7          # the tanh form differs
+    c = SMALL["layernorm_simple"]
+    y = layer_norm(np.float32(c["x"]), c["axes"], c["epsilon"], None, None)
+    assert np.abs(y.mean(axis=1)).max() < c["mean_tol"] and np.abs(y.var(axis=1) - 1.0).max() < c["var_tol"]
+    c = SMALL["layernorm_gamma_beta"]
+    y = layer_norm(np.float32(c["x"]), c["axes"], c["epsilon"], np.float32(c["gamma"]), np.float32(c["beta"]))
+    assert np.allclose(y, np.float32(c["want"]), rtol=0, atol=c["tol"])
+
+
+def test_fused_small_ops_golden():
+    check_fused_small(orc.softmax, orc.gelu, orc.layer_norm)
+    # non-trailing and negative axes: the same numbers as normalising the transposed tensor
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    g = rng.standard_normal((3, 5)).astype(np.float32)
+    y = orc.layer_norm(x, [0, -1], 1e-5, g, None)
+    xt = np.transpose(x, (1, 0, 2)).reshape(4, 15)
+    want = ((xt - xt.mean(1, keepdims=True)) / np.sqrt(xt.var(1, keepdims=True) + 1e-5) * g.reshape(1, 15)).reshape(4, 3, 5).transpose(1, 0, 2)
+    assert np.allclose(y, want, rtol=0, atol=1e-5)
+    z = rng.standard_normal((2, 7, 3)).astype(np.float64)
+    e = np.exp(z - z.max(1, keepdims=True))
+    assert np.allclose(orc.softmax(z, 1), e / e.sum(1, keepdims=True), rtol=0, atol=1e-14)
+
+
 def test_expand_scales_layouts():
     s = np.arange(6, dtype=np.float32).reshape(2, 3)
     e = orc.expand_scales(s, "kgroup", 4, 3, group=2)
