@@ -86,6 +86,7 @@ SIGNATURES = {
     "cb_plan_gelu": ([C.c_int, C.c_int32, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_softmax": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_layernorm": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_double, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_cols_bias": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_workspace_bytes": ([C.c_void_p, C.POINTER(C.c_size_t)], C.c_int),
     "cb_plan_prepare_workspace": ([C.c_void_p, C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_kernel_name": ([C.c_void_p], C.c_char_p),

@@ -22,9 +22,9 @@ from ._lib import BackendError, ErrNotImplemented, check
 # compute.OpType values used by Capabilities (optype.go)
 OP_PARAMETER, OP_CONSTANT, OP_DOT_GENERAL = 1, 2, 32
 OP_FUSED_SOFTMAX, OP_FUSED_LAYER_NORM, OP_FUSED_GELU, OP_FUSED_DENSE = 116, 117, 118, 119
-OP_FUSED_SDPA, OP_FUSED_QUANTIZED_DENSE = 120, 123
+OP_FUSED_SDPA, OP_FUSED_ATTENTION_QKV_PROJECTION, OP_FUSED_QUANTIZED_DENSE = 120, 122, 123
 OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 116: "FusedSoftmax", 117: "FusedLayerNorm", 118: "FusedGelu",
-            119: "FusedDense", 120: "FusedScaledDotProductAttention", 123: "FusedQuantizedDense"}
+            119: "FusedDense", 120: "FusedScaledDotProductAttention", 122: "FusedAttentionQKVProjection", 123: "FusedQuantizedDense"}
 
 # compute.QuantizationScheme (fused_ops.go:81-98)
 QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
@@ -74,6 +74,8 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_fused_softmax": ([C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_gelu": ([C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_layer_norm": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_attention_qkv_projection": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                               C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
@@ -348,6 +350,15 @@ class Function:
                                            gamma.handle if gamma is not None else None,
                                            beta.handle if beta is not None else None, C.byref(h)))
         return self._v(h)
+
+    def FusedAttentionQKVProjection(self, x: Value, wQKV: Value, biasQ: Optional[Value], biasK: Optional[Value],
+                                    biasV: Optional[Value], queryDim: int, keyValueDim: int):
+        """Returns (query, key, value)."""
+        hv = lambda v: v.handle if v is not None else None
+        q, k, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        check(_g().cbg_fn_fused_attention_qkv_projection(self.handle, x.handle, wQKV.handle, hv(biasQ), hv(biasK), hv(biasV),
+                                                         queryDim, keyValueDim, C.byref(q), C.byref(k), C.byref(v)))
+        return self._v(q), self._v(k), self._v(v)
 
     def FusedDense(self, x: Value, weight: Value, bias: Optional[Value], options: Optional[DenseConfig] = None) -> Value:
         o = options or DenseConfig()

@@ -61,7 +61,7 @@ const char* dtype_name(int d);
 
 // ---- plans ------------------------------------------------------------------
 enum PlanKind { PLAN_QDENSE = 1, PLAN_DOT, PLAN_SDPA, PLAN_COPY, PLAN_CONVERT, PLAN_IOTA,
-                PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM };
+                PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM, PLAN_COLS_BIAS };
 
 struct HelperDesc {
   int32_t dtype = 0, dtype_to = 0, rank = 0, axis = 0;

@@ -308,13 +308,29 @@ layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, cons
   }
 }
 
+// Columns [first, first + width) of a [rows, total] matrix, plus an optional bias[width]: the scatter half of
+// FusedAttentionQKVProjection (internal/gobackend/fusedops/attentionqkv.go:140-199).
+template <typename T>
+__global__ void __launch_bounds__(FS_THREADS)
+cols_bias_kernel(const T* __restrict__ src, const T* __restrict__ bias, T* __restrict__ out, int64_t rows, int64_t total,
+                 int64_t first, int64_t width) {
+  typedef typename Scalar<T>::acc_t A;
+  const int64_t n = rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    A v = Scalar<T>::load(src, r * total + first + c);
+    if (bias) v += (A)Scalar<T>::load(bias, c);
+    Scalar<T>::store(out, i, v);
+  }
+}
+
 // ---- plans ------------------------------------------------------------------
 static bool fs_float(int d) { return d == CB_F32 || d == CB_F64 || d == CB_BF16 || d == CB_F16; }
 static size_t fs_acc_size(int d) { return d == CB_F64 ? 8 : 4; }
 
 int fused_small_plan(cb_plan* p) {
   HelperDesc& h = p->helper;
-  const char* op = p->kind == PLAN_GELU ? "FusedGelu" : (p->kind == PLAN_SOFTMAX ? "FusedSoftmax" : "FusedLayerNorm");
+  const char* op = p->kind == PLAN_GELU ? "FusedGelu" : (p->kind == PLAN_SOFTMAX ? "FusedSoftmax" : (p->kind == PLAN_COLS_BIAS ? "FusedAttentionQKVProjection" : "FusedLayerNorm"));
   if (!fs_float(h.dtype)) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: dtype %s", op, dtype_name(h.dtype));
   p->n_outputs = 1;
   p->threads = FS_THREADS;
@@ -324,6 +340,16 @@ int fused_small_plan(cb_plan* p) {
     p->n_inputs = 1;
     p->blocks = (int)std::max<int64_t>(1, std::min<int64_t>((h.n + FS_THREADS - 1) / FS_THREADS, (int64_t)p->n_sm * per_sm));
     p->name = std::string("gelu_") + (h.axis ? "exact_" : "tanh_") + dtype_name(h.dtype);
+    return CB_OK;
+  }
+  if (p->kind == PLAN_COLS_BIAS) {
+    const int64_t rows = h.dims[0], total = h.dims[1], first = h.dims[2], width = h.dims[3];
+    if (rows < 0 || total < 0 || first < 0 || width < 0 || first + width > total)
+      return fail(CB_ERR_INVALID_ARG, "%s: columns [%lld, %lld) do not lie inside %lld", op, (long long)first, (long long)(first + width), (long long)total);
+    h.n = rows * width;
+    p->n_inputs = 1 + ((h.flags & 1) ? 1 : 0);
+    p->blocks = (int)std::max<int64_t>(1, std::min<int64_t>((h.n + FS_THREADS - 1) / FS_THREADS, (int64_t)p->n_sm * per_sm));
+    p->name = std::string("cols_bias_") + dtype_name(h.dtype);
     return CB_OK;
   }
   const int64_t outer = h.dims[0], L = h.dims[1], inner = h.dims[2];
@@ -369,7 +395,10 @@ int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out
   int st = fs_by_dtype(h.dtype, [&](auto* t) {
     typedef typename std::remove_pointer<decltype(t)>::type T;
     constexpr int64_t VN = 16 / (int64_t)sizeof(T);
-    if (p->kind == PLAN_GELU) {
+    if (p->kind == PLAN_COLS_BIAS) {
+      cols_bias_kernel<T><<<p->blocks, FS_THREADS, 0, s>>>((const T*)in[0], (h.flags & 1) ? (const T*)in[1] : nullptr, (T*)out[0],
+                                                         h.dims[0], h.dims[1], h.dims[2], h.dims[3]);
+    } else if (p->kind == PLAN_GELU) {
       if (h.n % VN == 0 && aligned(in[0]) && aligned(out[0]))
         gelu_kernel<T, true><<<p->blocks, FS_THREADS, 0, s>>>((const T*)in[0], (T*)out[0], h.n, h.axis);
       else

@@ -42,7 +42,7 @@ struct Shape {
 };
 
 enum NodeKind { N_PARAM, N_CONST, N_DOT, N_QDENSE, N_SDPA, N_RESHAPE, N_SLICE, N_IOTA, N_CONVERT, N_TRANSPOSE,
-                N_GELU, N_SOFTMAX, N_LAYERNORM };
+                N_GELU, N_SOFTMAX, N_LAYERNORM, N_COLS_BIAS };
 
 bool is_float(int d) { return d == CB_F16 || d == CB_F32 || d == CB_F64 || d == CB_BF16 || d == CB_F8E4M3FN || d == CB_F8E5M2; }
 bool is_half(int d) { return d == CB_F16 || d == CB_BF16; }
@@ -130,7 +130,7 @@ struct cbg_value {
   std::vector<int64_t> starts, limits, strides;
   std::vector<int32_t> perm;
   int axis = 0;
-  int64_t small_dims[3] = {0, 0, 0};   // softmax [outer, axis, inner]; layer norm [rows, norm size, 1]
+  int64_t small_dims[4] = {0, 0, 0, 0};   // softmax [outer, axis, inner]; layer norm [rows, norm size, 1]; column slice [rows, total, first, width]
   double epsilon = 0.0;               // layer norm
   int flags = 0;                      // gelu: exact; layer norm: 1 gamma, 2 beta
 };
@@ -280,10 +280,11 @@ int cbg_backend_device_description(const cbg_backend* b, int dev, char* buf, siz
 
 int cbg_backend_capabilities(const cbg_backend* b, int32_t* ops, int* n_ops, int32_t* dtypes, int* n_dtypes) {
   // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32, FusedSoftmax 116, FusedLayerNorm 117,
-  // FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120, FusedQuantizedDense 123.  The helper ops
+  // FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120, FusedAttentionQKVProjection 122,
+  // FusedQuantizedDense 123.  The helper ops
   // (Reshape, Slice, Iota, ConvertDType, Transpose) exist to serve DotGeneral and are
   // deliberately not advertised.
-  static const int32_t k_ops[] = {1, 2, 32, 116, 117, 118, 119, 120, 123};
+  static const int32_t k_ops[] = {1, 2, 32, 116, 117, 118, 119, 120, 122, 123};
   static const int32_t k_dtypes[] = {CB_BOOL, CB_I8, CB_I32, CB_I64, CB_U8, CB_F16, CB_F32, CB_F64, CB_BF16};
   const int no = (int)(sizeof(k_ops) / sizeof(k_ops[0])), nd = (int)(sizeof(k_dtypes) / sizeof(k_dtypes[0]));
   if (ops && n_ops) for (int i = 0; i < std::min(*n_ops, no); i++) ops[i] = k_ops[i];
@@ -726,6 +727,49 @@ int cbg_fn_fused_layer_norm(cbg_function* f, cbg_value* x, const int* axes, int 
   return CB_OK;
 }
 
+// FusedOps.FusedAttentionQKVProjection (fused_ops.go:437-461; internal/gobackend/fusedops/attentionqkv.go:38-96): one
+// matmul x @ wQKV, then the three column ranges of the result, each with its optional bias.
+int cbg_fn_fused_attention_qkv_projection(cbg_function* f, cbg_value* x, cbg_value* w_qkv, cbg_value* bias_q, cbg_value* bias_k,
+                                          cbg_value* bias_v, int64_t query_dim, int64_t key_value_dim, cbg_value** query,
+                                          cbg_value** key, cbg_value** value) {
+  const char* op = "AttentionQKVProjection";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x, w_qkv}));
+  for (cbg_value* b : {bias_q, bias_k, bias_v}) if (b) CB_TRY(check_values(f, op, {b}));
+  const int xr = (int)x->shape.dims.size();
+  if (xr < 1) return fail(CB_ERR_INVALID_ARG, "%s: x must have rank >= 1, got %d", op, xr);
+  if (query_dim < 0 || key_value_dim < 0) return fail(CB_ERR_INVALID_ARG, "%s: negative projection dimension", op);
+  const int64_t total = query_dim + 2 * key_value_dim;
+  if (w_qkv->shape.dims.size() != 2 || w_qkv->shape.dims[0] != x->shape.dims.back() || w_qkv->shape.dims[1] != total)
+    return fail(CB_ERR_INVALID_ARG, "%s: wQKV must be [%lld, %lld], got %s", op, (long long)x->shape.dims.back(), (long long)total, w_qkv->shape.str().c_str());
+  if (w_qkv->shape.dtype != x->shape.dtype) return fail(CB_ERR_INVALID_ARG, "%s: x and wQKV must share one dtype", op);
+  const int64_t widths[3] = {query_dim, key_value_dim, key_value_dim};
+  cbg_value* biases[3] = {bias_q, bias_k, bias_v};
+  for (int i = 0; i < 3; i++)
+    if (biases[i] && (biases[i]->shape.dtype != x->shape.dtype || biases[i]->shape.dims != std::vector<int64_t>{widths[i]}))
+      return fail(CB_ERR_INVALID_ARG, "%s: bias %d must be [%lld] of the dtype of x, got %s", op, i, (long long)widths[i], biases[i]->shape.str().c_str());
+  // the reference executes Float32 and Float64 (attentionqkv.go:128-135); the half types are this backend's extension
+  CB_TRY(check_small_dtype("FusedAttentionQKVProjection", x));
+  const int lc = xr - 1, rc = 0;
+  cbg_value* combined = nullptr;
+  CB_TRY(cbg_fn_dot_general(f, x, &lc, 1, nullptr, 0, w_qkv, &rc, nullptr, 0, 0, &combined));
+  const int64_t rows = total ? combined->shape.size() / total : x->shape.size() / std::max<int64_t>(1, x->shape.dims.back());
+  cbg_value** outs[3] = {query, key, value};
+  int64_t first = 0;
+  for (int i = 0; i < 3; i++) {
+    Shape s = x->shape;
+    s.dims.back() = widths[i];
+    std::vector<cbg_value*> ins = {combined};
+    if (biases[i]) ins.push_back(biases[i]);
+    cbg_value* n = add_node(f, N_COLS_BIAS, s, ins);
+    n->small_dims[0] = rows; n->small_dims[1] = total; n->small_dims[2] = first; n->small_dims[3] = widths[i];
+    n->flags = biases[i] ? 1 : 0;
+    *outs[i] = n;
+    first += widths[i];
+  }
+  return CB_OK;
+}
+
 // FusedOps.FusedDense (fused_ops.go:336-347; builder internal/gobackend/fusedops/dense.go:34-108): the matmul is a
 // DotGeneral contracting x's last axis with the weight's first (InputOutputs) or last (OutputsInput) axis; bias and
 // activation become the epilogue of that same kernel instead of a second pass over the result.
@@ -953,6 +997,9 @@ int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec) {
       case N_CONVERT: st = cb_plan_convert(dev, n->inputs[0]->shape.dtype, n->shape.dtype, n->shape.size(), &p); break;
       case N_GELU: st = cb_plan_gelu(dev, n->shape.dtype, n->shape.size(), n->flags, &p); break;
       case N_SOFTMAX: st = cb_plan_softmax(dev, n->shape.dtype, n->small_dims[0], n->small_dims[1], n->small_dims[2], &p); break;
+      case N_COLS_BIAS:
+        st = cb_plan_cols_bias(dev, n->shape.dtype, n->small_dims[0], n->small_dims[1], n->small_dims[2], n->small_dims[3], n->flags & 1, &p);
+        break;
       case N_LAYERNORM:
         st = cb_plan_layernorm(dev, n->shape.dtype, n->small_dims[0], n->small_dims[1], n->epsilon, n->flags & 1, (n->flags & 2) ? 1 : 0, &p);
         break;

@@ -424,6 +424,16 @@ int cb_plan_layernorm(int dev, int32_t dtype, int64_t rows, int64_t norm_size, d
   return finish_plan(fused_small_plan(p), p, plan);
 }
 
+int cb_plan_cols_bias(int dev, int32_t dtype, int64_t rows, int64_t total_cols, int64_t first_col, int64_t n_cols,
+                      int32_t has_bias, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_COLS_BIAS, plan, &p));
+  p->helper.dtype = dtype;
+  p->helper.dims[0] = rows; p->helper.dims[1] = total_cols; p->helper.dims[2] = first_col; p->helper.dims[3] = n_cols;
+  p->helper.flags = has_bias ? 1 : 0;
+  return finish_plan(fused_small_plan(p), p, plan);
+}
+
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes) {
   clear_error();
   if (!plan || !bytes) return fail(CB_ERR_INVALID_ARG, "NULL argument");
@@ -472,7 +482,7 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
     case PLAN_QDENSE: return qdense_launch(plan, inputs, outputs, workspace, s);
     case PLAN_DOT: return dot_launch(plan, inputs, outputs, workspace, s);
     case PLAN_SDPA: return sdpa_launch(plan, inputs, outputs, workspace, s);
-    case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: return fused_small_launch(plan, inputs, outputs, workspace, s);
+    case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: case PLAN_COLS_BIAS: return fused_small_launch(plan, inputs, outputs, workspace, s);
     default: return helper_launch(plan, inputs, outputs, workspace, s);
   }
 }

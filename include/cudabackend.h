@@ -209,6 +209,10 @@ int cb_plan_gelu(int dev, int32_t dtype, int64_t n_elements, int32_t exact, cb_p
 int cb_plan_softmax(int dev, int32_t dtype, int64_t outer, int64_t axis_size, int64_t inner, cb_plan** plan);
 int cb_plan_layernorm(int dev, int32_t dtype, int64_t rows, int64_t norm_size, double epsilon, int32_t has_gamma,
                       int32_t has_beta, cb_plan** plan);
+/* out[rows, n_cols] = src[rows, total_cols][:, first_col : first_col + n_cols] + bias[n_cols]?  (launch inputs src, bias?):
+ * the scatter half of FusedAttentionQKVProjection (fused_ops.go:437-461; fusedops/attentionqkv.go:140-199). */
+int cb_plan_cols_bias(int dev, int32_t dtype, int64_t rows, int64_t total_cols, int64_t first_col, int64_t n_cols,
+                      int32_t has_bias, cb_plan** plan);
 
 /* ---- plans ("compile-time kernel selection by shape and dtype": created in Builder.Compile,
  *      builder.go:29-82; launched from Executable.Execute, executable.go:10-37) */

@@ -85,6 +85,13 @@ int cbg_fn_fused_gelu(cbg_function* f, cbg_value* x, int exact, cbg_value** v);
 int cbg_fn_fused_layer_norm(cbg_function* f, cbg_value* x, const int* axes, int n_axes, double epsilon,
                             cbg_value* gamma /* or NULL */, cbg_value* beta /* or NULL */, cbg_value** v);
 
+/* FusedOps.FusedAttentionQKVProjection (fused_ops.go:437-461): x [batch..., in] @ wQKV [in, q + 2 kv], split into
+ * query [.., q], key [.., kv], value [.., kv], each plus its optional bias. */
+int cbg_fn_fused_attention_qkv_projection(cbg_function* f, cbg_value* x, cbg_value* w_qkv, cbg_value* bias_q /* or NULL */,
+                                          cbg_value* bias_k /* or NULL */, cbg_value* bias_v /* or NULL */,
+                                          int64_t query_dim, int64_t key_value_dim, cbg_value** query, cbg_value** key,
+                                          cbg_value** value);
+
 /* FusedOps.FusedDense (fused_ops.go:336-347) with compute.DenseConfig (:72-78): y = act(x @ W + bias).
  * weight_layout: 0 DenseLayoutInputOutputs (weight [in, out...]), 1 DenseLayoutOutputsInput ([out..., in]).
  * Float32 and Float64 as in the reference, BFloat16 / Float16 as an extension. */

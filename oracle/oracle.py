@@ -425,3 +425,18 @@ def layer_norm(x, axes, epsilon: float, gamma=None, beta=None) -> np.ndarray:
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_double]
     fn(_p(xt), _p(g), _p(b), _p(y), rows, L, float(epsilon))
     return np.ascontiguousarray(np.transpose(y, np.argsort(perm)))
+
+
+def qkv_projection(x, w_qkv, bias_q, bias_k, bias_v, query_dim: int, key_value_dim: int, in_dtype: int = F32):
+    """Reference FusedAttentionQKVProjection (attentionqkv.go:38-199): DotGeneral of x's last axis with wQKV's first,
+    the three column ranges of the result, each plus its bias (in the dtype of x)."""
+    x = _c(x, _NP_OF[in_dtype])
+    y = dot_general(x, [x.ndim - 1], [], _c(w_qkv, _NP_OF[in_dtype]), [0], [], in_dtype)
+    outs, first = [], 0
+    for width, b in ((query_dim, bias_q), (key_value_dim, bias_k), (key_value_dim, bias_v)):
+        part = np.ascontiguousarray(y[..., first:first + width])
+        if b is not None:
+            part = (part + _c(b, _NP_OF[in_dtype]).reshape(width)).astype(_NP_OF[in_dtype])
+        outs.append(part)
+        first += width
+    return tuple(outs)

@@ -6,7 +6,7 @@ import pytest
 from compute_b200 import BackendError, ErrNotImplemented, backend as be, device as dv, ops
 from oracle import oracle as orc
 from tests.helpers import DT, as_f64, max_abs_normalised
-from tests.test_oracle import check_fused_small
+from tests.test_oracle import check_fused_small, check_qkv_projection
 
 pytestmark = pytest.mark.gpu
 TOL = {"f32": 2e-5, "f64": 1e-12, "bf16": 2e-2, "f16": 2e-2}     # f32: sums of 10^4 terms in another order
@@ -95,3 +95,33 @@ def test_through_the_backend_interface(backend):
     for build in (lambda: f.FusedSoftmax(xi, 1), lambda: f.FusedGelu(xi, True), lambda: f.FusedLayerNorm(xi, [1], 1e-5)):
         with pytest.raises(ErrNotImplemented):
             build()
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f64", "bf16"])
+def test_attention_qkv_projection(backend, dtype):
+    code = DT[dtype]
+    def run(x, w, bq, bk, bv, qd, kvd, c=dv.F32):
+        ins = [(x, c), (w, c)] + [(b, c) for b in (bq, bk, bv) if b is not None]
+        def build(f, p):
+            it = iter(p[2:])
+            return list(f.FusedAttentionQKVProjection(p[0], p[1], next(it) if bq is not None else None,
+                                                      next(it) if bk is not None else None, next(it) if bv is not None else None, qd, kvd))
+        outs, shapes = be.exec_graph(backend, ins, build)
+        return outs, shapes
+    if dtype == "f32":
+        check_qkv_projection(lambda *a: run(*a)[0])
+    x = make(1, (2, 5, 64), dtype)
+    w = make(2, (64, 48 + 2 * 16), dtype, 0.2)
+    bq, bv = make(3, (48,), dtype), make(4, (16,), dtype)
+    (q, k, v), shapes = run(x, w, bq, None, bv, 48, 16, code)
+    assert shapes == [be.make_shape(code, 2, 5, 48), be.make_shape(code, 2, 5, 16), be.make_shape(code, 2, 5, 16)]
+    wq, wk, wv = orc.qkv_projection(widen(x, dtype), widen(w, dtype), widen(bq, dtype), None, widen(bv, dtype), 48, 16,
+                                    in_dtype=orc.F64 if dtype != "f32" else orc.F32)
+    tol = {"f32": 1e-5, "f64": 1e-12, "bf16": 2e-2}[dtype]
+    for got, want in ((q, wq), (k, wk), (v, wv)):
+        assert max_abs_normalised(as_f64(got, code), want.astype(np.float64)) < tol
+    f = backend.Builder("qkv").Main()
+    xp = f.Parameter("x", be.make_shape(dv.F32, 2, 8))
+    wp = f.Parameter("w", be.make_shape(dv.F32, 8, 7))
+    with pytest.raises(BackendError):
+        f.FusedAttentionQKVProjection(xp, wp, None, None, None, 4, 2)      # 4 + 2 * 2 != 7

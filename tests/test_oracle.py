@@ -278,6 +278,18 @@ def test_fused_small_ops_golden():
     assert np.allclose(orc.softmax(z, 1), e / e.sum(1, keepdims=True), rtol=0, atol=1e-14)
 
 
+def check_qkv_projection(fn):
+    """support/backendtest/fusedops.go:497-524."""
+    x = np.float32([[1, 2, 3]])
+    w = np.float32([[1, 0, 0, 1], [0, 1, 0, 1], [0, 0, 1, 1]])
+    q, k, v = fn(x, w, np.float32([10, 20]), np.float32([100]), np.float32([1000]), 2, 1)
+    assert np.array_equal(q, np.float32([[11, 22]])) and np.array_equal(k, np.float32([[103]])) and np.array_equal(v, np.float32([[1006]]))
+
+
+def test_qkv_projection_golden():
+    check_qkv_projection(orc.qkv_projection)
+
+
 def test_expand_scales_layouts():
     s = np.arange(6, dtype=np.float32).reshape(2, 3)
     e = orc.expand_scales(s, "kgroup", 4, 3, group=2)
