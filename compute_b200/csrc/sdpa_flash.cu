@@ -127,10 +127,13 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __shared__ unsigned s_failed;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // heavy (late, causal) query tiles first
-  const int pair = p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs);
-  const int h = (int)((blockIdx.x / p.q_pairs) % p.Hq);
-  const int b = (int)(blockIdx.x / ((long long)p.q_pairs * p.Hq));
+  // Heaviest (late, causal) query tiles first over the whole grid: the last wave then holds only the
+  // lightest tiles.  Heads vary fastest, so the query heads of one KV group run side by side.
+  const int n_bh = p.B * p.Hq;
+  const int pair = p.q_pairs - 1 - (int)(blockIdx.x / n_bh);
+  const int bh = (int)(blockIdx.x % n_bh);
+  const int h = bh % p.Hq;
+  const int b = bh / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = pair * 2 * FA_BM;
   const int nb_all = (p.Skv + FA_BN - 1) / FA_BN;
