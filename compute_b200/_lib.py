@@ -31,7 +31,7 @@ class QDenseDesc(C.Structure):
                 ("x_dtype", C.c_int32), ("w_dtype", C.c_int32), ("scale_layout", C.c_int32),
                 ("block_size", C.c_int64), ("has_zero_point", C.c_int32), ("has_bias", C.c_int32),
                 ("activation", C.c_int32), ("variant", C.c_int32),
-                ("gather_ranks", C.c_int32), ("gather_rank", C.c_int32), ("scheme", C.c_int32)]
+                ("gather_ranks", C.c_int32), ("gather_rank", C.c_int32), ("scheme", C.c_int32), ("ggml_type", C.c_int32)]
 
 
 class DotDesc(C.Structure):

@@ -79,6 +79,7 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_fused_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_fused_quantized_dense_ggml": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_sdpa": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(_SdpaOptions), C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_not_implemented": ([C.c_void_p, C.c_char_p], C.c_int),
     "cbg_exec_num_inputs": ([C.c_void_p], C.c_int),
@@ -373,6 +374,12 @@ class Function:
         if q is None:
             raise BackendError(_lib.ERR_INVALID_ARG, "FusedQuantizedDense: weightsQuantization must not be nil")
         h = C.c_void_p()
+        if q.Scheme == QUANT_GGML:
+            if q.ZeroPoint is not None:
+                raise BackendError(_lib.ERR_INVALID_ARG, "FusedQuantizedDense(GGML): ZeroPoint must be nil for GGML scheme")
+            check(_g().cbg_fn_fused_quantized_dense_ggml(self.handle, x.handle, weights.handle,
+                                                         bias.handle if bias is not None else None, q.GGMLType, activation, C.byref(h)))
+            return self._v(h)
         check(_g().cbg_fn_fused_quantized_dense(
             self.handle, x.handle, weights.handle, bias.handle if bias is not None else None, q.Scheme,
             q.Scale.handle if q.Scale is not None else None, q.ZeroPoint.handle if q.ZeroPoint is not None else None,

@@ -825,12 +825,56 @@ int cbg_fn_fused_dense(cbg_function* f, cbg_value* x, cbg_value* weight, cbg_val
   return CB_OK;
 }
 
+// FusedQuantizedDense with compute.QuantGGML (internal/gobackend/fusedops/quantizeddense.go:181-248): weights
+// [N, bytesPerRow] Uint8 in the native block layout; K follows from the row bytes and must equal x's last dimension.
+int cbg_fn_fused_quantized_dense_ggml(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias, int ggml_type,
+                                      int activation, cbg_value** v) {
+  const char* op = "FusedQuantizedDense(GGML)";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x, weights}));
+  if (bias) CB_TRY(check_values(f, op, {bias}));
+  if (x->shape.dtype != CB_F32 && x->shape.dtype != CB_BF16)
+    return fail(CB_ERR_INVALID_ARG, "%s: x must be float32, got %s", op, cb::dtype_name(x->shape.dtype));
+  if (x->shape.dims.size() < 1) return fail(CB_ERR_INVALID_ARG, "%s: x must have rank >= 1, got %zu", op, x->shape.dims.size());
+  if (weights->shape.dims.size() != 2 || weights->shape.dtype != CB_U8)
+    return fail(CB_ERR_INVALID_ARG, "%s: weights must be [N, bytesPerRow] Uint8, got %s", op, weights->shape.str().c_str());
+  if (ggml_type != CB_GGML_Q4_0 && ggml_type != CB_GGML_Q8_0)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: GGML type %d not yet supported in fused path", op, ggml_type);
+  const int64_t N = weights->shape.dims[0], bytes_per_row = weights->shape.dims[1];
+  const int64_t block_bytes = ggml_type == CB_GGML_Q8_0 ? 34 : 18;
+  if (bytes_per_row % block_bytes != 0)
+    return fail(CB_ERR_INVALID_ARG, "%s: bytesPerRow=%lld is not a multiple of the %lld-byte block", op, (long long)bytes_per_row, (long long)block_bytes);
+  const int64_t K = bytes_per_row / block_bytes * 32;
+  if (x->shape.dims.back() != K)
+    return fail(CB_ERR_INVALID_ARG, "%s: x's last dim (%lld) must match K=%lld derived from weights", op, (long long)x->shape.dims.back(), (long long)K);
+  if (bias && (bias->shape.dtype != CB_F32 || bias->shape.dims != std::vector<int64_t>{N}))
+    return fail(CB_ERR_INVALID_ARG, "%s: bias must be (Float32)[%lld], got %s", op, (long long)N, bias->shape.str().c_str());
+  if (activation < CB_ACT_NONE || activation > CB_ACT_TANH) return fail(CB_ERR_INVALID_ARG, "%s: unknown activation %d", op, activation);
+  Shape s = x->shape;
+  s.dims.back() = N;
+  std::vector<cbg_value*> ins = {x, weights};
+  if (bias) ins.push_back(bias);
+  cbg_value* n = add_node(f, N_QDENSE, s, ins);
+  n->qd.M = K ? x->shape.size() / K : 0;
+  n->qd.K = K; n->qd.N = N;
+  n->qd.x_dtype = x->shape.dtype;
+  n->qd.w_dtype = CB_U8;
+  n->qd.scale_layout = CB_SCALE_CHANNEL;
+  n->qd.has_bias = bias ? 1 : 0;
+  n->qd.activation = activation;
+  n->qd.scheme = CB_QUANT_GGML;
+  n->qd.ggml_type = ggml_type;
+  n->qd.variant = CB_QDENSE_GENERIC;
+  *v = n;
+  return CB_OK;
+}
+
 int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias, int scheme,
                                  cbg_value* scale, cbg_value* zero_point, int block_axis, int64_t block_size,
                                  int activation, cbg_value** v) {
   const char* op = "FusedQuantizedDense";
   CB_TRY(check_fn(f, op));
-  if (scheme == 2) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: GGML quantization scheme is not implemented by the cuda backend", op);
+  if (scheme == 2) return fail(CB_ERR_INVALID_ARG, "%s: GGML weights go through cbg_fn_fused_quantized_dense_ggml", op);
   if (scheme != 0 && scheme != 1) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: unknown quantization scheme %d", op, scheme);
   CB_TRY(check_values(f, op, {x, weights, scale}));
   if (zero_point) CB_TRY(check_values(f, op, {zero_point}));

@@ -23,7 +23,8 @@ NP_CARRIER = {BOOL: np.bool_, I8: np.int8, U8: np.uint8, I16: np.int16, U16: np.
 ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
 SCALE_REF, SCALE_CHANNEL, SCALE_KGROUP = range(3)
 QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL, QDENSE_DECODE_TC = range(5)
-QUANT_LINEAR, QUANT_NF4 = 0, 1
+QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
+GGML_Q4_0, GGML_Q8_0 = 0, 1
 DOT_AUTO, DOT_GENERIC, DOT_TCGEN05 = range(3)
 SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH = range(3)
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
@@ -238,9 +239,9 @@ class Plan:
     @classmethod
     def qdense(cls, M, K, N, x_dtype=F32, w_dtype=I8, scale_layout=SCALE_REF, block_size=1,
                has_zero_point=False, has_bias=False, activation=ACT_NONE, variant=QDENSE_AUTO, dev=0,
-               gather_ranks=0, gather_rank=0, scheme=QUANT_LINEAR) -> "Plan":
+               gather_ranks=0, gather_rank=0, scheme=QUANT_LINEAR, ggml_type=0) -> "Plan":
         d = QDenseDesc(M, K, N, x_dtype, w_dtype, scale_layout, block_size, int(has_zero_point),
-                       int(has_bias), activation, variant, gather_ranks, gather_rank, scheme)
+                       int(has_bias), activation, variant, gather_ranks, gather_rank, scheme, ggml_type)
         h = C.c_void_p()
         check(_lib.load().cb_plan_qdense(dev, C.byref(d), C.byref(h)))
         return cls(h, dev)

@@ -93,8 +93,13 @@ typedef enum {
   CB_SCALE_KGROUP = 2   /* compact extension: scales [ceil(K/block_size), N], groups along K   */
 } cb_scale_layout;
 
-/* compute.QuantizationScheme (fused_ops.go:80-98); GGML is not built. */
-typedef enum { CB_QUANT_LINEAR = 0, CB_QUANT_NF4 = 1 } cb_quant_scheme;
+/* compute.QuantizationScheme (fused_ops.go:80-98) and compute.GGMLQuantType (:132-145).  GGML weights are
+ * [N, bytes_per_row] Uint8 in the native block layout with the scales inside the blocks: launch inputs x, weights,
+ * bias? (no scales, no zero points); scale_layout and block_size are ignored.  Built: Q4_0 (18-byte blocks of 32
+ * values: fp16 scale, 16 bytes of nibbles, value = (nibble - 8) * scale, low nibbles first half) and Q8_0 (34-byte
+ * blocks: fp16 scale, 32 int8); the other block formats return CB_ERR_NOT_IMPLEMENTED. */
+typedef enum { CB_QUANT_LINEAR = 0, CB_QUANT_NF4 = 1, CB_QUANT_GGML = 2 } cb_quant_scheme;
+typedef enum { CB_GGML_Q4_0 = 0, CB_GGML_Q8_0 = 1 } cb_ggml_type;
 
 typedef enum {
   CB_QDENSE_AUTO = 0,
@@ -124,6 +129,7 @@ typedef struct {
   int32_t gather_ranks;
   int32_t gather_rank;
   int32_t scheme;         /* cb_quant_scheme; NF4 takes no zero points and runs on the generic kernel */
+  int32_t ggml_type;      /* cb_ggml_type when scheme is CB_QUANT_GGML */
 } cb_qdense_desc;
 
 int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);

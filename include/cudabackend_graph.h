@@ -99,12 +99,17 @@ int cbg_fn_fused_dense(cbg_function* f, cbg_value* x, cbg_value* weight, cbg_val
                        int activation, int weight_layout, cbg_value** v);
 
 /* FusedOps.FusedQuantizedDense (fused_ops.go:413-435) with compute.Quantization (:204-234).
- * scheme: 0 Linear, 1 NF4 (weights as Int8 / Uint8 nibble indices), 2 GGML (not built).  block_axis 1 is the reference
+ * scheme: 0 Linear, 1 NF4 (weights as Int8 / Uint8 nibble indices); GGML has its own entry point below.  block_axis 1 is the reference
  * layout scales [K, ceil(N/block_size)]; block_axis 0 is this backend's extension, scales
  * [ceil(K/block_size), N] (block_size = K gives one scale per output channel). */
 int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias /* or NULL */,
                                  int scheme, cbg_value* scale, cbg_value* zero_point /* or NULL */,
                                  int block_axis, int64_t block_size, int activation, cbg_value** v);
+
+/* FusedQuantizedDense with compute.QuantGGML (fused_ops.go:92-97, :132-145): weights [N, bytesPerRow] Uint8 in the
+ * native GGML block layout (Q4_0 = 0 and Q8_0 = 1 are built), no scales or zero points. */
+int cbg_fn_fused_quantized_dense_ggml(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias /* or NULL */,
+                                      int ggml_type, int activation, cbg_value** v);
 
 /* FusedOps.FusedScaledDotProductAttention (fused_ops.go:349-378) with
  * ScaledDotProductAttentionConfig (:245-277); NULL values = unset. */

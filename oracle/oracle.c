@@ -273,6 +273,51 @@ void orc_qdense_nf4(const float* x, const void* w, const float* scales, const fl
 }
 
 /* ------------------------------------------------------------------ */
+/* GGML block formats Q4_0 and Q8_0                                   */
+/* ------------------------------------------------------------------ */
+
+/* quantizeddense_ggml.go:159-196.  A row is K / 32 blocks; a block starts with its scale d as a
+ * little-endian fp16.  Q8_0 (34 bytes): value i = d * int8(q[i]).  Q4_0 (18 bytes): value i = d * (low
+ * nibble of q[i] - 8), value 16 + i = d * (high nibble of q[i] - 8), i < 16. */
+void orc_ggml_dequant_row(const uint8_t* data, float* out, int64_t K, int ggml_type) {
+  const int64_t nblocks = K / 32;
+  const int bb = ggml_type == 1 ? 34 : 18;
+  for (int64_t b = 0; b < nblocks; b++) {
+    const uint8_t* blk = data + b * bb;
+    const float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    const uint8_t* qs = blk + 2;
+    float* o = out + b * 32;
+    if (ggml_type == 1) {
+      for (int i = 0; i < 32; i++) o[i] = d * (float)(int8_t)qs[i];
+    } else {
+      for (int i = 0; i < 16; i++) {
+        o[i] = d * (float)((int)(qs[i] & 0x0F) - 8);
+        o[16 + i] = d * (float)((int)(qs[i] >> 4) - 8);
+      }
+    }
+  }
+}
+
+/* quantizeddense_ggml.go:98-131: per output, the row is dequantised, dot = sum_k x[k] * w[k] in one
+ * float, k ascending; then + bias[n]; the activation over the whole output last (:89). */
+void orc_qdense_ggml(const float* x, const uint8_t* w, const float* bias, float* out,
+                     int64_t M, int64_t K, int64_t N, int ggml_type, int activation) {
+  const int64_t bytes_per_row = K / 32 * (ggml_type == 1 ? 34 : 18);
+  float* row = (float*)malloc((size_t)(K > 0 ? K : 1) * sizeof(float));
+  for (int64_t n = 0; n < N; n++) {
+    orc_ggml_dequant_row(w + n * bytes_per_row, row, K, ggml_type);
+    for (int64_t m = 0; m < M; m++) {
+      float dot = 0.0f;
+      for (int64_t k = 0; k < K; k++) { const float p = x[m * K + k] * row[k]; dot = dot + p; }
+      out[m * N + n] = dot;
+      if (bias) out[m * N + n] += bias[n];
+    }
+  }
+  free(row);
+  orc_activation_f32(out, (size_t)(M * N), activation);
+}
+
+/* ------------------------------------------------------------------ */
 /* FusedSoftmax, FusedGelu, FusedLayerNorm                            */
 /* ------------------------------------------------------------------ */
 

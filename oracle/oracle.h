@@ -121,6 +121,27 @@ void orc_gemm_f32_blocked(const float* A, const float* B, float* C,
 
 int orc_max_threads(void);
 
+/* Packed 4-bit weights and the NF4 scheme (convertdtype.go:199-226; quantizeddense.go:586-609). */
+void orc_unpack_int4(const uint8_t* packed, int8_t* dst, size_t n_bytes);
+void orc_unpack_uint4(const uint8_t* packed, uint8_t* dst, size_t n_bytes);
+const float* orc_nf4_values(void);
+void orc_qdense_nf4(const float* x, const void* w, const float* scales, const float* bias, float* out,
+                    int64_t M, int64_t K, int64_t N, int64_t block_size, int activation, int threads);
+
+/* GGML Q4_0 (type 0) and Q8_0 (type 1) blocks (quantizeddense_ggml.go:98-196). */
+void orc_ggml_dequant_row(const uint8_t* data, float* out, int64_t K, int ggml_type);
+void orc_qdense_ggml(const float* x, const uint8_t* w, const float* bias, float* out,
+                     int64_t M, int64_t K, int64_t N, int ggml_type, int activation);
+
+/* FusedSoftmax over [outer, L, inner], FusedGelu, FusedLayerNorm over trailing rows
+ * (softmax.go:83-118, gelu.go:113-126, layernorm.go:129-168). */
+void orc_softmax_f32(const float* x, float* y, int64_t outer, int64_t L, int64_t inner);
+void orc_softmax_f64(const double* x, double* y, int64_t outer, int64_t L, int64_t inner);
+void orc_gelu_f32(const float* x, float* y, size_t n, int exact);
+void orc_gelu_f64(const double* x, double* y, size_t n, int exact);
+void orc_layernorm_f32(const float* x, const float* gamma, const float* beta, float* y, int64_t rows, int64_t L, double eps);
+void orc_layernorm_f64(const double* x, const double* gamma, const double* beta, double* y, int64_t rows, int64_t L, double eps);
+
 #ifdef __cplusplus
 }
 #endif

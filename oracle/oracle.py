@@ -440,3 +440,57 @@ def qkv_projection(x, w_qkv, bias_q, bias_k, bias_v, query_dim: int, key_value_d
         outs.append(part)
         first += width
     return tuple(outs)
+
+
+# ---------------------------------------------------------------- GGML block formats
+GGML_Q4_0, GGML_Q8_0 = 0, 1
+GGML_BLOCK_BYTES = {GGML_Q4_0: 18, GGML_Q8_0: 34}
+
+
+def ggml_quantize_rows(w: np.ndarray, ggml_type: int) -> np.ndarray:
+    """Test data: float rows [N, K] -> native Q4_0 / Q8_0 blocks [N, bytesPerRow] (round-to-nearest block
+    quantisation; only the layout matters to the tests, which compare against orc.qdense_ggml on the same bytes)."""
+    w = np.asarray(w, np.float32)
+    N, K = w.shape
+    assert K % 32 == 0
+    blocks = w.reshape(N, K // 32, 32)
+    amax = np.abs(blocks).max(axis=2)
+    out = np.zeros((N, K // 32, GGML_BLOCK_BYTES[ggml_type]), np.uint8)
+    if ggml_type == GGML_Q8_0:
+        d = (amax / 127.0).astype(np.float16)
+        q = np.where(d[..., None] > 0, np.rint(blocks / np.maximum(d.astype(np.float32), 1e-30)[..., None]), 0).clip(-127, 127).astype(np.int8)
+        out[..., 2:] = q.view(np.uint8)
+    else:
+        d = (amax / 7.0).astype(np.float16)
+        q = (np.where(d[..., None] > 0, np.rint(blocks / np.maximum(d.astype(np.float32), 1e-30)[..., None]), 0).clip(-8, 7) + 8).astype(np.uint8)
+        out[..., 2:] = q[..., :16] | (q[..., 16:] << 4)
+    out[..., 0:2] = d.view(np.uint16)[..., None].view(np.uint8).reshape(N, K // 32, 2)
+    return np.ascontiguousarray(out.reshape(N, -1))
+
+
+def ggml_dequant_rows(data: np.ndarray, ggml_type: int) -> np.ndarray:
+    data = np.ascontiguousarray(data, np.uint8)
+    N, bpr = data.shape
+    K = bpr // GGML_BLOCK_BYTES[ggml_type] * 32
+    out = np.empty((N, K), np.float32)
+    fn = lib().orc_ggml_dequant_row
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int]
+    for n in range(N):
+        fn(data[n].ctypes.data, out[n].ctypes.data, K, ggml_type)
+    return out
+
+
+def qdense_ggml(x, w_blocks, bias=None, ggml_type: int = GGML_Q8_0, activation: int = ACT_NONE) -> np.ndarray:
+    """Reference FusedQuantizedDense, GGML scheme (quantizeddense_ggml.go:55-131)."""
+    x = _c(x, np.float32)
+    w_blocks = np.ascontiguousarray(w_blocks, np.uint8)
+    N, bpr = w_blocks.shape
+    K = bpr // GGML_BLOCK_BYTES[ggml_type] * 32
+    assert x.shape[-1] == K
+    M = x.size // K if K else 0
+    b = None if bias is None else _c(bias, np.float32)
+    out = np.empty(x.shape[:-1] + (N,), np.float32)
+    fn = lib().orc_qdense_ggml
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int]
+    fn(_p(x), _p(w_blocks), _p(b), _p(out), M, K, N, ggml_type, activation)
+    return out

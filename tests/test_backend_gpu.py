@@ -236,11 +236,34 @@ def test_fused_quantized_dense_validation(backend):
         f.FusedQuantizedDense(x, w, None, q(BlockSize=8))
     with pytest.raises(BackendError):          # :123 only Axis=1 (and this backend's Axis=0)
         f.FusedQuantizedDense(x, w, None, q(BlockAxis=2))
-    with pytest.raises(ErrNotImplemented):
+    with pytest.raises(BackendError):          # GGML: weights must be [N, bytesPerRow] Uint8 (quantizeddense.go:205-208)
         f.FusedQuantizedDense(x, w, None, q(Scheme=be.QUANT_GGML))
     with pytest.raises(BackendError) as e:     # :126 NF4 takes no zero points
         f.FusedQuantizedDense(x, w, None, q(Scheme=be.QUANT_NF4, ZeroPoint=s))
     assert "ZeroPoint must be nil for NF4" in str(e.value)
+
+
+def test_fused_quantized_dense_ggml_through_api(backend):
+    M, K, N = 3, 128, 24
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    for gt in (orc.GGML_Q8_0, orc.GGML_Q4_0):
+        wq = orc.ggml_quantize_rows(rng.standard_normal((N, K)).astype(np.float32), gt)
+        def build(f, p):
+            return f.FusedQuantizedDense(p[0], p[1], p[2], be.Quantization(be.QUANT_GGML, None, None, 0, 0, GGMLType=gt), dv.ACT_NONE)
+        (got,), (shape,) = be.exec_graph(backend, [(x, dv.F32), (wq, dv.U8), (b, dv.F32)], build)
+        assert shape == be.make_shape(dv.F32, M, N)
+        assert max_abs_normalised(got, orc.qdense_ggml(x, wq, b, gt)) < 1e-5
+    f = backend.Builder("ggml").Main()
+    xp = f.Parameter("x", be.make_shape(dv.F32, 2, 64))
+    wp = f.Parameter("w", be.make_shape(dv.U8, 8, 68))
+    with pytest.raises(BackendError) as e:     # quantizeddense.go:222-225: K derived from the row bytes is 64 for Q8_0, 96+ for Q4_0
+        f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_0))
+    assert not isinstance(e.value, ErrNotImplemented)
+    f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q8_0))
+    with pytest.raises(ErrNotImplemented):      # K-quants are not built
+        f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=5))
 
 
 def test_fused_quantized_dense_nf4_through_api(backend):

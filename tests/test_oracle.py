@@ -290,6 +290,30 @@ def test_qkv_projection_golden():
     check_qkv_projection(orc.qkv_projection)
 
 
+def test_ggml_blocks_hand_computed():
+    """Block layouts of quantizeddense_ggml.go:159-196 on hand-built bytes."""
+    q8 = np.zeros((1, 34), np.uint8)
+    q8[0, 0:2] = [0x00, 0x38]                                   # fp16 0.5, little endian
+    q8[0, 2:] = np.arange(32, dtype=np.int8).view(np.uint8)
+    q8[0, 2 + 5] = np.int8(-3).view(np.uint8)
+    want = 0.5 * np.arange(32, dtype=np.float32)
+    want[5] = -1.5
+    assert np.array_equal(orc.ggml_dequant_rows(q8, orc.GGML_Q8_0)[0], want)
+    q4 = np.zeros((1, 18), np.uint8)
+    q4[0, 0:2] = [0x00, 0x40]                                   # fp16 2.0
+    q4[0, 2:] = [i | ((15 - i) << 4) for i in range(16)]
+    d = orc.ggml_dequant_rows(q4, orc.GGML_Q4_0)[0]
+    assert np.array_equal(d[:16], 2.0 * (np.arange(16) - 8)) and np.array_equal(d[16:], 2.0 * (7 - np.arange(16)))
+    # dense: x @ dequant(w)^T + bias, then the activation
+    x = np.float32([[1.0] * 32, [0.5] * 32])
+    got = orc.qdense_ggml(x, q8, np.float32([1.0]), orc.GGML_Q8_0, orc.ACT_RELU)
+    assert np.array_equal(got, np.float32([[want.sum() + 1.0], [0.5 * want.sum() + 1.0]]))
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((4, 64)).astype(np.float32)
+    for t, tol in ((orc.GGML_Q8_0, 0.02), (orc.GGML_Q4_0, 0.3)):
+        assert np.abs(orc.ggml_dequant_rows(orc.ggml_quantize_rows(w, t), t) - w).max() < tol
+
+
 def test_expand_scales_layouts():
     s = np.arange(6, dtype=np.float32).reshape(2, 3)
     e = orc.expand_scales(s, "kgroup", 4, 3, group=2)

@@ -110,9 +110,41 @@ def test_nf4_and_packed_validation():
         dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, has_zero_point=True, scheme=dv.QUANT_NF4)
     assert "ZeroPoint must be nil for NF4" in str(e.value)
     with pytest.raises(ErrNotImplemented):
-        dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, scheme=2)          # GGML
+        dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, scheme=7)          # no such scheme
     with pytest.raises(ErrNotImplemented):
         dv.Plan.qdense(2, 4096, 4096, dv.BF16, dv.I4, dv.SCALE_KGROUP, 128, variant=dv.QDENSE_DECODE_TC)
+
+
+@pytest.mark.parametrize("ggml", ["q8_0", "q4_0"])
+@pytest.mark.parametrize("x_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 512), (5, 96, 40), (16, 2048, 264), (33, 64, 7)])
+def test_ggml_block_formats(M, K, N, x_dtype, ggml):
+    """GGML Q8_0 / Q4_0 weights [N, bytesPerRow] (quantizeddense_ggml.go:98-196) against the oracle on the same bytes."""
+    gt = orc.GGML_Q8_0 if ggml == "q8_0" else orc.GGML_Q4_0
+    rng = np.random.default_rng(M + N)
+    wq = orc.ggml_quantize_rows(rng.standard_normal((N, K)).astype(np.float32) * 0.05, gt)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.from_f32(x, orc.BF16) if x_dtype == "bf16" else x
+    xw = orc.to_f32(xin, orc.BF16) if x_dtype == "bf16" else x
+    want = orc.qdense_ggml(xw, wq, b, gt, orc.ACT_SILU)
+    plan = dv.Plan.qdense(M, K, N, code, dv.U8, has_bias=True, activation=dv.ACT_SILU, scheme=dv.QUANT_GGML,
+                          ggml_type=dv.GGML_Q8_0 if ggml == "q8_0" else dv.GGML_Q4_0)
+    assert plan.kernel_name == f"qdense_ggml_{x_dtype}_{ggml}"
+    got = ops._run(plan, [xin, wq, b], (M, N), dv.NP_CARRIER[code])
+    gotf = orc.to_f32(got, orc.BF16) if x_dtype == "bf16" else got
+    assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else F32_TOL)
+
+
+def test_ggml_validation():
+    with pytest.raises(ErrNotImplemented):
+        dv.Plan.qdense(1, 256, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=5)          # Q4_K: not built
+    with pytest.raises(BackendError):
+        dv.Plan.qdense(1, 48, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=dv.GGML_Q8_0)  # K not whole blocks
+    with pytest.raises(BackendError) as e:
+        dv.Plan.qdense(1, 64, 8, dv.F32, dv.U8, has_zero_point=True, scheme=dv.QUANT_GGML, ggml_type=dv.GGML_Q8_0)
+    assert "ZeroPoint must be nil for GGML" in str(e.value)
 
 
 def test_dense_epilogue_golden_on_gpu():
