@@ -4,7 +4,8 @@
 // reference's definition (internal/gobackend/fusedops/sdpa.go:373-519): row max, exp,
 // sum, normalise, P.V — evaluated blockwise, so the [S, Skv] scores never exist in memory.
 //
-// One CTA owns two 128-row query tiles of one (batch, query head) and walks the key/value
+// One CTA owns two 128-row query tiles — consecutive rows of one (batch, query head), or for causal
+// attention with an even GQA group the same rows of two heads of one KV group — and walks the key/value
 // blocks of 128 rows:
 //   warp 8      TMA producer: Q once, K and V blocks into two-stage rings (128B swizzle)
 //   warp 9      MMA issuer:  S_t = Q_t K^T (tcgen05.mma, smem x smem -> TMEM) and
@@ -40,6 +41,7 @@ struct FaParams {
   int bshd, causal, ab_format;
   float scale_log2;        // scale * log2(e)
   int q_pairs;             // ceil(S / 256)
+  int pair_heads;          // causal with an even GQA group: a CTA's two tiles are the same rows of two neighbouring heads
 };
 
 __device__ __forceinline__ void fa_fail(const FaParams& p, unsigned* s_failed, unsigned code, unsigned detail) {
@@ -129,18 +131,31 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Heaviest (late, causal) query tiles first over the whole grid: the last wave then holds only the
   // lightest tiles.  Heads vary fastest, so the query heads of one KV group run side by side.
-  const int n_bh = p.B * p.Hq;
-  const int pair = p.q_pairs - 1 - (int)(blockIdx.x / n_bh);
-  const int bh = (int)(blockIdx.x % n_bh);
-  const int h = bh % p.Hq;
-  const int b = bh / p.Hq;
-  const int hk = h / (p.Hq / p.Hkv);
-  const int q0 = pair * 2 * FA_BM;
+  // A CTA's two tiles are either two consecutive 128-row tiles of one head, or (causal, even GQA group) the same
+  // 128 rows of two neighbouring heads of one KV group: those walk exactly the same key/value blocks, so
+  // the two tiles alternate on the tensor core to the last block instead of one of them finishing early.
+  int th[2], tq0[2], b;
+  if (p.pair_heads) {
+    const int n_qt = (p.S + FA_BM - 1) / FA_BM, n_bhp = p.B * (p.Hq / 2);
+    const int qi = n_qt - 1 - (int)(blockIdx.x / n_bhp);
+    const int bhp = (int)(blockIdx.x % n_bhp);
+    b = bhp / (p.Hq / 2);
+    th[0] = 2 * (bhp % (p.Hq / 2)); th[1] = th[0] + 1;
+    tq0[0] = tq0[1] = qi * FA_BM;
+  } else {
+    const int n_bh = p.B * p.Hq;
+    const int pair = p.q_pairs - 1 - (int)(blockIdx.x / n_bh);
+    const int bh = (int)(blockIdx.x % n_bh);
+    b = bh / p.Hq;
+    th[0] = th[1] = bh % p.Hq;
+    tq0[0] = pair * 2 * FA_BM; tq0[1] = tq0[0] + FA_BM;
+  }
+  const int hk = th[0] / (p.Hq / p.Hkv);
   const int nb_all = (p.Skv + FA_BN - 1) / FA_BN;
   int nb[2];
 #pragma unroll
   for (int t = 0; t < 2; t++) {
-    const int qt = q0 + t * FA_BM;
+    const int qt = tq0[t];
     int n = nb_all;
     if (p.causal) n = min(n, (min(qt + FA_BM, p.S) + FA_BN - 1) / FA_BN);   // blocks with kv <= last row of the tile
     if (qt >= p.S) n = 0;
@@ -171,8 +186,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       mbar_expect_tx(q_full, 2 * FA_TILE_BYTES);
-      fa_load_tile(sQ, &tm_q, p.bshd, q0, h, b, q_full);
-      fa_load_tile(sQ + FA_TILE_BYTES, &tm_q, p.bshd, q0 + FA_BM, h, b, q_full);
+      fa_load_tile(sQ, &tm_q, p.bshd, tq0[0], th[0], b, q_full);
+      fa_load_tile(sQ + FA_TILE_BYTES, &tm_q, p.bshd, tq0[1], th[1], b, q_full);
       for (int j = 0; j < nb_max; j++) {
         const int s = j & 1;
         if (j >= 2 && !mbar_wait(&k_empty[s], (uint32_t)((j / 2 - 1) & 1))) { fa_fail(p, &s_failed, 1, (unsigned)j); break; }
@@ -251,7 +266,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // ------------------------------ softmax warpgroups ------------------------
     const int t = warp >> 2;                 // tile of this warpgroup
     const int wq = warp & 3;                 // TMEM lane quarter of this warp
-    const int row = q0 + t * FA_BM + wq * 32 + lane;
+    const int row = tq0[t] + wq * 32 + lane;
+    const int h = th[t];
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t s_addr = lane_base + (uint32_t)(t * 128);
     const uint32_t o_addr = lane_base + (uint32_t)(256 + t * 128);
@@ -397,7 +413,8 @@ bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why) {
 
 int sdpa_flash_plan(cb_plan* p) {
   const cb_sdpa_desc& d = p->sdpa;
-  p->blocks = (int)(d.B * d.Hq * ((d.S + 255) / 256));
+  const bool pair_heads = d.causal && d.Hkv > 0 && (d.Hq / d.Hkv) % 2 == 0;
+  p->blocks = pair_heads ? (int)(d.B * (d.Hq / 2) * ((d.S + FA_BM - 1) / FA_BM)) : (int)(d.B * d.Hq * ((d.S + 255) / 256));
   p->threads = FA_THREADS;
   p->dyn_smem = FA_SMEM;
   p->counter_bytes = 64;
@@ -460,6 +477,7 @@ int sdpa_flash_launch(const cb_plan* p, const void* const* in, void* const* out,
   const double scale = d.scale != 0.0 ? d.scale : 1.0 / sqrt((double)d.D);
   prm.scale_log2 = (float)(scale * 1.4426950408889634);
   prm.q_pairs = (int)((d.S + 255) / 256);
+  prm.pair_heads = (d.causal && d.Hkv > 0 && (d.Hq / d.Hkv) % 2 == 0) ? 1 : 0;
   return d.dtype == CB_BF16 ? launch_t<__nv_bfloat16>(p, tq, tk, tv, prm, s) : launch_t<__half>(p, tq, tk, tv, prm, s);
 }
 
