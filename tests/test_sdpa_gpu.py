@@ -114,3 +114,25 @@ def test_sdpa_config4_slice():
     ones = orc.bf16_from_f32(np.ones((B, Hkv, S, D), np.float32))
     got1 = orc.bf16_to_f32(ops.sdpa(q, k, ones, dtype=dv.BF16, causal=True))
     assert np.max(np.abs(got1 - 1.0)) < 2e-2
+
+
+# ------------------------------------------------------------- tensor-core kernel on ragged shapes
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,Hq,Hkv,S,Skv,layout,dtype", [
+    (2, 4, 2, 300, 300, "BHSD", "bf16"),      # even GQA group: causal CTAs pair two heads; rows and keys end inside a tile
+    (1, 6, 2, 257, 257, "BHSD", "bf16"),      # group of three: one head per CTA
+    (1, 2, 2, 128, 128, "BSHD", "f16"),       # no grouping, exactly one tile
+    (1, 4, 1, 129, 200, "BHSD", "bf16"),      # more keys than queries
+    (2, 8, 4, 384, 384, "BSHD", "bf16"),      # an odd number of 128-row tiles
+])
+def test_sdpa_flash_ragged_shapes(B, Hq, Hkv, S, Skv, layout, dtype, causal):
+    D = 128
+    code = DT[dtype]
+    rng = np.random.default_rng(S + Hq)
+    shp = (lambda h, s: (B, h, s, D)) if layout == "BHSD" else (lambda h, s: (B, s, h, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shp(h, s), dtype=np.float32), code) for h, s in ((Hq, S), (Hkv, Skv), (Hkv, Skv)))
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=dv.LAYOUT_BHSD if layout == "BHSD" else dv.LAYOUT_BSHD, causal=causal,
+                         variant=dv.SDPA_FLASH, return_plan=True)
+    assert plan.kernel_name.startswith("sdpa_flash_")
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), layout=layout, causal=causal)
+    assert max_abs_normalised(orc.to_f32(got, code), want) < 2e-2
