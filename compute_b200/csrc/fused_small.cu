@@ -15,9 +15,11 @@ namespace cb {
 constexpr int FS_THREADS = 256;
 constexpr int FS_SMEM_BYTES = 40 * 1024;      // row cache; longer rows are re-read from L2 / HBM
 
-template <typename A> __device__ __forceinline__ A fs_exp(A x);
-template <> __device__ __forceinline__ float fs_exp<float>(float x) { return expf(x); }
-template <> __device__ __forceinline__ double fs_exp<double>(double x) { return exp(x); }
+// FAST (16-bit element types): the hardware exponential, whose error is far below one unit of the output type.
+template <typename A, bool FAST = false> __device__ __forceinline__ A fs_exp(A x);
+template <> __device__ __forceinline__ float fs_exp<float, false>(float x) { return expf(x); }
+template <> __device__ __forceinline__ float fs_exp<float, true>(float x) { return __expf(x); }
+template <> __device__ __forceinline__ double fs_exp<double, false>(double x) { return exp(x); }
 
 template <typename A> __device__ __forceinline__ A fs_gelu(A x, bool exact);
 template <> __device__ __forceinline__ float fs_gelu<float>(float x, bool exact) {
@@ -29,6 +31,16 @@ template <> __device__ __forceinline__ double fs_gelu<double>(double x, bool exa
   if (exact) return (x * 0.5) * (1.0 + erf(x * 0.70710678118654752440));
   const double inner = 0.7978845608028654 * (x + 0.044715 * x * x * x);
   return (x * 0.5) * (1.0 + tanh(inner));
+}
+
+template <typename T> __device__ __forceinline__ uint32_t fs_pack2(float a, float b) { return 0; }
+template <> __device__ __forceinline__ uint32_t fs_pack2<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t fs_pack2<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 // Elements move in 16-byte pieces when the extent allows it (VEC), one at a time otherwise.
@@ -46,7 +58,13 @@ template <typename T, bool VEC> struct Chunk {
     }
   }
   static __device__ __forceinline__ void store(T* p, int64_t i, const A (&v)[N]) {
-    if (VEC) {
+    if (VEC && sizeof(T) == 2 && N == 8) {
+      // two elements per conversion instruction (round to nearest even; a NaN becomes the canonical NaN)
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) w[j] = fs_pack2<T>((float)v[2 * j], (float)v[2 * j + 1]);
+      *reinterpret_cast<uint4*>(p + i) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if (VEC) {
       union { uint4 raw; T e[16 / sizeof(T)]; } u;
 #pragma unroll
       for (int j = 0; j < N; j++) Scalar<T>::store(u.e, j, v[j]);
@@ -115,7 +133,7 @@ softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, in
       if (!cached) Ch::load(xr, i, v);
 #pragma unroll
       for (int j = 0; j < N; j++) {
-        const A e = fs_exp<A>((cached ? row[i + j] : v[j]) - mx);
+        const A e = fs_exp<A, sizeof(T) == 2>((cached ? row[i + j] : v[j]) - mx);
         if (cached) row[i + j] = e;
         sum += e;
       }
@@ -126,7 +144,7 @@ softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, in
       A v[N];
       if (!cached) Ch::load(xr, i, v);
 #pragma unroll
-      for (int j = 0; j < N; j++) v[j] = (cached ? row[i + j] : fs_exp<A>(v[j] - mx)) * inv;
+      for (int j = 0; j < N; j++) v[j] = (cached ? row[i + j] : fs_exp<A, sizeof(T) == 2>(v[j] - mx)) * inv;
       Ch::store(yr, i, v);
     }
     __syncthreads();                     // the row cache is rewritten by the next row
@@ -167,7 +185,7 @@ softmax_rows_reg_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows
 #pragma unroll
     for (int c = 0; c < R; c++)
 #pragma unroll
-      for (int j = 0; j < N; j++) { v[c][j] = fs_exp<A>(v[c][j] - mx); sum += v[c][j]; }     // exp(-inf) = 0 beyond the row
+      for (int j = 0; j < N; j++) { v[c][j] = fs_exp<A, sizeof(T) == 2>(v[c][j] - mx); sum += v[c][j]; }     // exp(-inf) = 0 beyond the row
     sum = fs_block_reduce<A, false>(sum, scratch);
     const A inv = (A)1 / sum;
 #pragma unroll
