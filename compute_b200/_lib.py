@@ -34,6 +34,10 @@ class QDenseDesc(C.Structure):
                 ("gather_ranks", C.c_int32), ("gather_rank", C.c_int32), ("scheme", C.c_int32), ("ggml_type", C.c_int32)]
 
 
+class QDenseMember(C.Structure):
+    _fields_ = [("N", C.c_int64), ("has_bias", C.c_int32), ("activation", C.c_int32)]
+
+
 class DotDesc(C.Structure):
     _fields_ = [("B", C.c_int64), ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
                 ("rhs_transposed", C.c_int32), ("in_dtype", C.c_int32), ("out_dtype", C.c_int32),
@@ -72,6 +76,7 @@ SIGNATURES = {
     "cb_event_elapsed_ms": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_float)], C.c_int),
     "cb_event_destroy": ([C.c_int, C.c_void_p], C.c_int),
     "cb_plan_qdense": ([C.c_int, C.POINTER(QDenseDesc), C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_qdense_group": ([C.c_int, C.POINTER(QDenseDesc), C.POINTER(QDenseMember), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cb_qdense_decode_static": ([C.c_int, C.POINTER(QDenseDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_dot": ([C.c_int, C.POINTER(DotDesc), C.POINTER(C.c_void_p)], C.c_int),
@@ -95,6 +100,11 @@ SIGNATURES = {
                    C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_check_status": ([C.c_void_p, C.c_void_p], C.c_int),
     "cb_plan_destroy": ([C.c_void_p], C.c_int),
+    "cb_plan_bind": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_void_p,
+                      C.POINTER(C.c_void_p)], C.c_int),
+    "cb_bound_launch": ([C.c_void_p, C.c_void_p], C.c_int),
+    "cb_bound_launch_many": ([C.POINTER(C.c_void_p), C.c_int, C.c_void_p], C.c_int),
+    "cb_bound_destroy": ([C.c_void_p], C.c_int),
     "cb_ipc_export": ([C.c_int, C.c_void_p, C.c_char_p], C.c_int),
     "cb_ipc_open": ([C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
     "cb_ipc_close": ([C.c_int, C.c_void_p], C.c_int),

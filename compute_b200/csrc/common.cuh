@@ -10,6 +10,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string>
+#include <vector>
 
 #include "../../include/cudabackend.h"
 
@@ -87,6 +88,7 @@ struct cb_plan {
   bool has_status = false;        // kernel keeps a status word at workspace offset 0
   std::string name;
   cb_qdense_desc qd{};
+  std::vector<cb_qdense_member> group;   // members of a grouped decode plan (one entry for an ordinary plan)
   cb_dot_desc dot{};
   cb_sdpa_desc sdpa{};
   cb::HelperDesc helper{};
@@ -96,6 +98,11 @@ namespace cb {
 
 int qdense_plan(cb_plan* p);
 int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+int qdense_group_plan(cb_plan* p);
+// Bound form of the tensor-core decode plan: everything a launch needs, prepared once.
+int qdense_decode_tc_bind(const cb_plan* p, const void* const* in, void* const* out, void* ws, void** impl);
+int qdense_decode_tc_launch_bound(const cb_plan* p, const void* impl, cudaStream_t s);
+void qdense_decode_tc_unbind(void* impl);
 int dot_plan(cb_plan* p);
 int dot_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int sdpa_plan(cb_plan* p);

@@ -251,8 +251,7 @@ struct QdParams {
   long long sk_total;   // sk_tiles * cpt
   int scale_group;      // rows per scale row; 0 = one scale per column
   int activation;
-  int debug_skip;       // diagnostics: 1 = stream the weights but skip the math
-  unsigned long long* dbg;   // diagnostics: per-CTA phase timestamps (16 per CTA) or NULL
+  unsigned long long* dbg;   // per-CTA phase time stamps (16 per CTA) in builds with -DCB_QD_STAMPS, else NULL
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -380,7 +379,11 @@ qdense_decode_kernel(const QdParams p) {
   const int gsteps = p.scale_group ? p.scale_group / 16 : 0;   // k-steps per scale group (0: one scale per column)
 
   int dbg_n = 0;
+#ifdef CB_QD_STAMPS
 #define QD_STAMP() do { if (p.dbg && tid == 0 && dbg_n < 16) p.dbg[cta * 16 + dbg_n++] = global_ns(); } while (0)
+#else
+#define QD_STAMP() do { (void)dbg_n; } while (0)
+#endif
   QD_STAMP();
 
   // ---- copy cursor: walks this warp's k-steps through all segments, QD_RING_STEPS ahead of the math.
@@ -532,7 +535,7 @@ qdense_decode_kernel(const QdParams p) {
           uint8_t* slot = my_ring + (n_done % QD_RING_STEPS) * QD_STEP_BYTES;
           asm volatile("cp.async.wait_group %0;" ::"n"(QD_RING_STEPS - 1) : "memory");
           __syncwarp();
-          if (!p.debug_skip) {
+          {
             // rows 2t, 2t+1, 2t+8, 2t+9: exactly the k indices the mma fragment assigns to lane t;
             // the 80-byte pitch makes the loads conflict-free.
             uint32_t L[4][2];
@@ -896,9 +899,11 @@ static int launch_decode(const cb_plan* p, const void* const* in, void* const* o
   prm.sk_total = (long long)prm.sk_tiles * prm.cpt;
   prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
   prm.activation = d.activation;
-  prm.debug_skip = 0;
-  { const char* e = getenv("CB_QDENSE_DEBUG_STAMPS");
-    prm.dbg = (e && e[0] == '1') ? (unsigned long long*)(w8 + p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4) : nullptr; }
+#ifdef CB_QD_STAMPS
+  prm.dbg = (unsigned long long*)(w8 + p->counter_bytes + (size_t)p->blocks * 2 * mt * 8 * QD_TILE_N * 4);
+#else
+  prm.dbg = nullptr;
+#endif
   if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
@@ -998,6 +1003,10 @@ extern "C" int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, cons
   if (d.scheme != CB_QUANT_LINEAR) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: only the Linear scheme");
   if (!decode_eligible(d, &why)) return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: %s", why.c_str());
   if (d.has_bias && !bias) return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: bias is NULL");
+  if (d.activation < CB_ACT_NONE || d.activation > CB_ACT_TANH)
+    return fail(CB_ERR_INVALID_ARG, "cb_qdense_decode_static: unknown activation %d", d.activation);
+  if (d.gather_ranks > 1)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "cb_qdense_decode_static: a gathered plan needs the tensor-core decode kernel (cb_plan_qdense)");
   CB_TRY(set_device(dev));
   const int mt = d.M <= 8 ? 1 : 2;
   const long long n_tiles = (d.N + QD_TILE_N - 1) / QD_TILE_N;

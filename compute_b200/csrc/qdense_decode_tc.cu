@@ -6,33 +6,43 @@
 // weights: TMA lands [128 k x 128 n] byte tiles of W in shared memory and tcgen05.mma kind::i8
 // consumes them in place as the MN-major operand.  The activations become the other operand in
 // block fixed point: for every row m and every 128-wide k unit u,
-//     x[m,k] = unit[m,u] * (d0 + 128 d1 + 16384 d2),   signed base-128 digits,
-// with unit[m,u] a power of two taken from the largest |x| of that row inside the unit, 20 bits
-// below it (exact for bfloat16 values within 2^-13 of that maximum; 2^-21 of the maximum
-// otherwise and for float32).  The digits of all rows form a [3*MB x K] int8 matrix (MB rows per
-// digit), so one MMA of shape (128 n) x (3*MB) x (32 k) yields the three digit sums of 128 output
-// columns, exactly, in s32 tensor memory.  Epilogue threads (one per output column) turn a
-// finished 128-k unit into f32, recombine the digits, multiply by unit[m,u] and by the scale of
-// that K group, and add it to their running totals.
+//     x[m,k] = unit[m,u] * (d0 + 128 d1 (+ 16384 d2)),   signed base-128 digits,
+// with unit[m,u] a power of two taken from the largest |x| of that row inside the unit.
+//   float32 x   three digit planes: 20 bits below the unit's maximum (error <= 2^-21 of it)
+//   bfloat16 x  two digit planes: 13 bits below the maximum.  A bfloat16 has 8 significant bits, so
+//               every element within 2^-6 of the unit's maximum is exact and smaller ones are
+//               rounded at 2^-14 of the maximum (1.2e-4 relative to the largest element of the
+//               unit; the output is rounded to bfloat16, 3.9e-3, and compared at 2e-2).
+// The digits of all rows form a [PLANES*MB x K] int8 matrix (MB rows per plane), so one MMA of
+// shape (128 n) x (PLANES*MB) x (32 k) yields the digit sums of 128 output columns, exactly, in
+// s32 tensor memory.  Epilogue threads (one per output column) turn a finished 128-k unit into
+// f32, recombine the digits, multiply by unit[m,u] and by the scale of that K group, and add it
+// to their running totals.
 //
-//   qdense_xdigits_kernel   x -> digits + unit[m,u] (one warp per row and k unit, all at once)
-//   qdense_decode_tc_kernel persistent, one CTA per SM over a balanced contiguous range of
-//                           (n tile, k unit) pairs:
-//       warp 8   TMA producer: weight tiles into an 8-stage ring (the first ones are requested
-//                before the digit kernel has finished)
-//       warps 10, 12, 13  TMA producers: the digit tile, the 128 scales and the 16 unit[m,u] of each
-//                unit (one issuing thread per kind of load)
-//       warps 9, 11  MMA issuers on alternate units: 4 MMAs (K = 32) per unit into one of 8 TMEM
-//                accumulators
-//       warps 0-7 epilogue as above, two groups of four warps on alternate units; a tile whose
-//                units are split between CTAs is finished by the CTA that arrives last, summing
-//                the parked partial tiles in CTA order (deterministic: the result does not
-//                depend on which CTA finishes)
+// One launch serves a GROUP of independent problems that share M and K (one problem is the
+// ordinary case): the work list is the column tiles of all problems in order, so the pipeline is
+// filled and drained once per group instead of once per projection.  Each problem has its own
+// weights, scales, bias, activation and result buffer(s) in a table of QtProblem records.
+//
+//   qdense_xdigits_kernel   x -> digits + unit[m,u] (one warp per x, row and k unit, all at once)
+//   qdense_decode_tc_kernel persistent over a contiguous range of (column tile, k unit) pairs:
+//       warps 8, 12   TMA producers of the weight tiles (even / odd units) into the stage ring; the
+//                     first ones are requested before the digit kernel has finished
+//       warps 10, 13  TMA producers of the digit tile, whose extra row carries the unit's 16 unit[m,u]
+//       warps 14, 15  TMA producers of the unit's 128 scales
+//       warps 9, 11   MMA issuers on alternate units: 4 MMAs (K = 32) per unit into the TMEM
+//                     accumulator that travels with the stage
+//       warps 0-7     epilogue as above, two groups of four warps on alternate units; a tile whose
+//                     units are split between CTAs is finished by the CTA that arrives last, summing
+//                     the parked partial tiles in CTA order (deterministic: the result does not
+//                     depend on which CTA finishes)
 // All mbarrier waits are bounded; a timeout sets the status word and TMEM is always freed.
+// Building with -DCB_QT_STAMPS adds per-CTA time stamps (timing diagnosis; off in the shipped build).
 #include "tc_common.cuh"
 
 #include <algorithm>
 #include <atomic>
+#include <memory>
 #include <stdlib.h>
 #include <string.h>
 
@@ -48,7 +58,7 @@ constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
 // Stages of the weight ring (each with its digit tile and its TMEM accumulator), by digit-tile rows:
 // what shared memory holds.
-__host__ __device__ constexpr int qt_stages(int nb) { return nb == 16 ? QT_S16 : (nb == 32 ? 9 : 8); }
+__host__ __device__ constexpr int qt_stages(int nb, int planes) { return nb == 16 ? (planes == 3 ? QT_S16 : QT_S16 - 1) : (nb == 32 ? 9 : 8); }
 constexpr int QT_THREADS = 512;                       // warps 0-7 epilogue, 9 and 11 MMA, six TMA producers
 constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;   // weights (even units), MMA, digits (even), MMA
 constexpr int QT_TMA2_WARP = 12, QT_SIDE2_WARP = 13;                                      // weights, digits of the odd units
@@ -59,30 +69,51 @@ constexpr int QT_SC_BYTES = QT_TILE_N * 4;
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
 
 constexpr int QT_MAX_RANKS = 8;
+constexpr int QT_MAX_PROBLEMS = CB_QDENSE_GROUP_MAX;
+
+// One problem of a launch.  The tensor maps are read by the TMA unit straight from this record
+// (kernel parameter space for a single unbound problem, global memory otherwise).
+struct alignas(64) QtProblem {
+  CUtensorMap tmap_w;                  // W [K rows][N bytes], 128 x 128 boxes, 128-byte swizzle
+  CUtensorMap tmap_s;                  // scales [rows][N] f32, 128 x 1 boxes
+  const float* bias;
+  void* outs[QT_MAX_RANKS];            // result buffers this problem is stored into (one, or one per rank of a gathered plan)
+  int N;
+  int out_ld, out_col0;                // row stride (elements) and first column of this kernel's slice
+  int activation;
+  int pad[10];
+};
+static_assert(sizeof(QtProblem) == 384, "QtProblem layout");
 
 struct QtParams {
-  const float* scales;
-  const float* bias;
-  void* outs[QT_MAX_RANKS];            // result buffers this kernel stores into (one, or one per rank of a gathered plan)
-  int n_outs;                          // 1, or the number of ranks
-  int out_ld, out_col0;                // row stride (elements) and first column of this kernel's slice
   unsigned* status;
-  unsigned* counters;       // one per n tile, zero between launches
+  unsigned* counters;       // one per column tile of the launch, zero between launches
   float* partials;          // [grid][2][MB][128]
-  int M, K, N;
-  int n_tiles, units_per_tile;
+  int M, K;
+  int n_problems;
+  int n_outs;               // 1, or the number of ranks
+  int tile_start[QT_MAX_PROBLEMS + 1];     // first column tile of every problem in the launch's list
+  int digit_row0[QT_MAX_PROBLEMS];         // first row of the problem's block in the digit matrix
+  int units_per_tile;
   long long total_units;
   int scale_group;          // 0: one scale per column; else rows of the K group
-  int activation;
   int out_bf16;
   uint32_t idesc;
-  unsigned long long* dbg;  // timing diagnosis only: 8 time stamps per CTA, or null
+#ifdef CB_QT_STAMPS
+  unsigned long long* dbg;  // 8 time stamps per CTA
+#endif
+};
+
+// The distinct activation matrices of a launch (problems given the same x share one digit block).
+struct QtXList {
+  const void* x[QT_MAX_PROBLEMS];
+  int n;
 };
 
 // ---------------------------------------------------------------------------
 // x -> digits
 // ---------------------------------------------------------------------------
-constexpr int QX_THREADS = 256;       // 8 warps, one (row, k unit) task each
+constexpr int QX_THREADS = 256;       // 8 warps, one (x, row, k unit) task each
 
 // Four consecutive elements x[m, k .. k+3] as floats; zeros beyond column K.
 __device__ __forceinline__ void qx_load4(const __nv_bfloat16* x, size_t m, int K, int k, float (&v)[4]) {
@@ -95,30 +126,40 @@ __device__ __forceinline__ void qx_load4(const float* x, size_t m, int K, int k,
   v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
 }
 
-// One warp per (row m, 128-wide k unit u): the unit's largest finite |x| fixes unit[m,u] = 2^-shift
-// (20 bits below it), every element becomes three signed base-128 digits, and unit[m,u] goes to
-// row NB of the digit matrix (NaN when the unit holds inf or NaN).  No pass over the whole row is needed, so all
-// M * ceil(K/128) tasks run at once.
-template <typename XT>
+// One warp per (activation matrix, row m, 128-wide k unit u): the unit's largest finite |x| fixes
+// unit[m,u] = 2^-shift (7*PLANES - 1 bits below it), every element becomes PLANES signed base-128
+// digits, and unit[m,u] goes to row NB of the block (NaN when the unit holds inf or NaN).  No pass
+// over the whole row is needed, so all tasks run at once.
+template <typename XT, int PLANES>
 __global__ void __launch_bounds__(QX_THREADS)
-qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int NB, int G, int8_t* __restrict__ digits,
-                      unsigned long long* dbg) {
-  const int MB = NB / 3;
+qdense_xdigits_kernel(const QtXList xl, int M, int K, int NB, int G, int8_t* __restrict__ digits
+#ifdef CB_QT_STAMPS
+                      , unsigned long long* dbg
+#endif
+                      ) {
+  constexpr int QBITS = 7 * PLANES - 1;
+  const int MB = NB / PLANES;                      // rows per digit plane (NB = 16 with three planes leaves one row unused)
   // The kernel that consumes the digits may start its own set-up now; it waits for this grid to
   // finish before it reads them.  This grid in turn may have been scheduled while the kernel
   // before it in the stream (which may produce x, and may still read the digit buffer) was
   // running: it waits for that kernel to finish before it touches either.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[0] = global_ns();      // timing diagnosis only
+#ifdef CB_QT_STAMPS
+  if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[0] = global_ns();
+#endif
   asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef CB_QT_STAMPS
   if (dbg && blockIdx.x == 0 && threadIdx.x == 0) dbg[1] = global_ns();
+#endif
   const int lane = threadIdx.x & 31;
   const int task = blockIdx.x * (QX_THREADS / 32) + (threadIdx.x >> 5);
-  if (task >= M * G) return;
-  const int u = task / M, m = task - u * M;
+  if (task >= xl.n * M * G) return;
+  const int xi = task / (M * G);
+  const int rem = task - xi * (M * G);
+  const int u = rem / M, m = rem - u * M;
   const int k = u * QT_UNIT_K + 4 * lane;
   float v[4];
-  qx_load4(x, (size_t)m, K, k, v);
+  qx_load4(reinterpret_cast<const XT*>(xl.x[xi]), (size_t)m, K, k, v);
   uint32_t mx = 0;          // bits of the largest finite |x| (non-negative floats order like integers)
   bool bad = false;
 #pragma unroll
@@ -131,7 +172,7 @@ qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int NB, int G, int
   // amax < 2^ex: exponent field - 126 for a normal maximum, the position of the leading bit for a subnormal one
   const int ef = (int)(mx >> 23);
   const int ex = ef > 0 ? ef - 126 : (32 - __clz(mx)) - 149;
-  const int shift = min(20 - ex, 149);             // |x| * 2^shift <= 2^20; unit = 2^-shift stays a float
+  const int shift = min(QBITS - ex, 149);          // |x| * 2^shift <= 2^QBITS; unit = 2^-shift stays a float
   const int sh1 = shift / 2, sh2 = shift - sh1;    // two factors that are always normal floats
   const float p1 = __int_as_float((127 + sh1) << 23), p2 = __int_as_float((127 + sh2) << 23);
   uint32_t w0 = 0, w1 = 0, w2 = 0;
@@ -141,26 +182,33 @@ qdense_xdigits_kernel(const XT* __restrict__ x, int M, int K, int NB, int G, int
     const int q = (int)(__float_as_uint(fmaf(v[e] * p1, p2, 12582912.0f)) - 0x4B400000u);
     const int a = ((q + 64) & 127) - 64;
     const int q1 = (q - a) >> 7;
-    const int b = ((q1 + 64) & 127) - 64;
-    const int c = (q1 - b) >> 7;
     w0 |= (uint32_t)(a & 0xFF) << (8 * e);
-    w1 |= (uint32_t)(b & 0xFF) << (8 * e);
-    w2 |= (uint32_t)(c & 0xFF) << (8 * e);
+    if (PLANES == 2) {
+      w1 |= (uint32_t)(q1 & 0xFF) << (8 * e);      // |q1| <= 64: the top digit needs no further split
+    } else {
+      const int b = ((q1 + 64) & 127) - 64;
+      const int c = (q1 - b) >> 7;
+      w1 |= (uint32_t)(b & 0xFF) << (8 * e);
+      w2 |= (uint32_t)(c & 0xFF) << (8 * e);
+    }
   }
   const size_t Kp = (size_t)G * QT_UNIT_K;     // row stride of the digit matrix (whole units)
+  int8_t* block = digits + (size_t)xi * (NB + QT_XROWS_EXTRA) * Kp;
   if (k < K) {               // K is a multiple of 16: a group of four lies inside or outside
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(0 * MB + m) * Kp + k) = w0;
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(1 * MB + m) * Kp + k) = w1;
-    *reinterpret_cast<uint32_t*>(digits + (size_t)(2 * MB + m) * Kp + k) = w2;
+    *reinterpret_cast<uint32_t*>(block + (size_t)(0 * MB + m) * Kp + k) = w0;
+    *reinterpret_cast<uint32_t*>(block + (size_t)(1 * MB + m) * Kp + k) = w1;
+    if (PLANES == 3) *reinterpret_cast<uint32_t*>(block + (size_t)(2 * MB + m) * Kp + k) = w2;
   }
   if (lane == 0) {
     // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN.  It travels
-    // with the digits: row NB of the matrix (the first below the digit rows) holds, for every unit, its 16 floats.
+    // with the digits: row NB of the block (the first below the digit rows) holds, for every unit, its 16 floats.
     float unit = shift <= 126 ? __int_as_float((127 - shift) << 23) : __int_as_float(1 << (149 - shift));
     if (bad) unit = __int_as_float(0x7FC00000);
-    *reinterpret_cast<float*>(digits + (size_t)NB * Kp + (size_t)u * QT_UNIT_K + 4 * m) = unit;
+    *reinterpret_cast<float*>(block + (size_t)NB * Kp + (size_t)u * QT_UNIT_K + 4 * m) = unit;
   }
+#ifdef CB_QT_STAMPS
   if (dbg && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) dbg[2] = global_ns();
+#endif
 }
 
 // ---------------------------------------------------------------------------
@@ -183,16 +231,37 @@ __device__ __forceinline__ void qt_fail(const QtParams& p, unsigned code, unsign
   atomicExch(&p.status[1], detail);
 }
 
-// act(v[m]) -> out[m, n] for the rows that exist.  The activation is chosen once, outside the
-// row loop, so the MB rows are independent instruction streams; for 16-bit outputs SiLU uses
-// the hardware exp and reciprocal (error far below one unit of the output).
+// Position of a role thread in its CTA's range of (column tile, k unit) pairs: the tile counts over
+// the whole launch, `pi` is the problem the tile belongs to.
+struct QtWalk {
+  int tile, g, pi, tile_end;
+};
+__device__ __forceinline__ void qt_walk_init(QtWalk& w, const QtParams& p, int tile0, int g0) {
+  w.tile = tile0; w.g = g0; w.pi = 0;
+  while (w.pi + 1 < p.n_problems && tile0 >= p.tile_start[w.pi + 1]) w.pi++;
+  w.tile_end = p.tile_start[w.pi + 1];
+}
+// one unit further; true when the walk entered the next problem
+__device__ __forceinline__ bool qt_walk_next(QtWalk& w, const QtParams& p, int G) {
+  if (++w.g < G) return false;
+  w.g = 0;
+  if (++w.tile < w.tile_end || w.pi + 1 >= p.n_problems) return false;
+  w.pi++;
+  w.tile_end = p.tile_start[w.pi + 1];
+  return true;
+}
+// Before the TMA unit reads a tensor map that the host wrote into global memory.
+__device__ __forceinline__ void qt_tensormap_acquire(const CUtensorMap* m) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(m) : "memory");
+}
+
 // act(v[m]) -> out[m, n] for the rows that exist, called by the 128 threads of the first epilogue
 // group together.  The activation is chosen once, outside the row loop, so the MB rows are
 // independent instruction streams; for 16-bit outputs SiLU uses the hardware exp and reciprocal
 // (error far below one unit of the output).  The tile is staged in shared memory and leaves in
 // 16-byte pieces (256 contiguous bytes per row), to the result buffer of every rank of a gathered plan.
 template <int MB, int ACT, bool BF16>
-__device__ __forceinline__ void qt_store_rows_act(const float* v, const QtParams& p, int tile_n0, int nl, uint8_t* stage) {
+__device__ __forceinline__ void qt_store_rows_act(const float* v, const QtParams& p, const QtProblem* pp, int tile_n0, int nl, uint8_t* stage) {
 #pragma unroll
   for (int m = 0; m < MB; m++) {
     float y;
@@ -205,41 +274,44 @@ __device__ __forceinline__ void qt_store_rows_act(const float* v, const QtParams
   constexpr int ESIZE = BF16 ? 2 : 4;
   constexpr int EPC = 16 / ESIZE;              // elements per 16-byte piece
   constexpr int CPR = QT_TILE_N / EPC;         // pieces per row
+  const int N = pp->N, out_ld = pp->out_ld, out_col0 = pp->out_col0;
   for (int idx = nl; idx < MB * CPR; idx += 128) {
     const int m = idx / CPR, c = idx - m * CPR;
     const int col = tile_n0 + c * EPC;
-    if (m < p.M && col < p.N) {                // N is a multiple of 16: a piece lies inside or outside
+    if (m < p.M && col < N) {                  // N is a multiple of 16: a piece lies inside or outside
       const uint4 val = *reinterpret_cast<const uint4*>(stage + ((size_t)m * QT_TILE_N + c * EPC) * ESIZE);
-      const size_t off = ((size_t)m * p.out_ld + p.out_col0 + col) * ESIZE;
+      const size_t off = ((size_t)m * out_ld + out_col0 + col) * ESIZE;
       for (int r = 0; r < p.n_outs; r++)       // own buffer, and the peers' over NVLink for a gathered plan
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.outs[r]) + off) = val;
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp->outs[r]) + off) = val;
     }
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");   // the staging tile may be rewritten
 }
 template <int MB, bool BF16>
-__device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p, int tile_n0, int nl, uint8_t* stage) {
-  switch (p.activation) {
-    case CB_ACT_GELU: qt_store_rows_act<MB, CB_ACT_GELU, BF16>(v, p, tile_n0, nl, stage); break;
-    case CB_ACT_RELU: qt_store_rows_act<MB, CB_ACT_RELU, BF16>(v, p, tile_n0, nl, stage); break;
-    case CB_ACT_SILU: qt_store_rows_act<MB, CB_ACT_SILU, BF16>(v, p, tile_n0, nl, stage); break;
-    case CB_ACT_HARDSWISH: qt_store_rows_act<MB, CB_ACT_HARDSWISH, BF16>(v, p, tile_n0, nl, stage); break;
-    case CB_ACT_TANH: qt_store_rows_act<MB, CB_ACT_TANH, BF16>(v, p, tile_n0, nl, stage); break;
-    default: qt_store_rows_act<MB, CB_ACT_NONE, BF16>(v, p, tile_n0, nl, stage); break;
+__device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p, const QtProblem* pp, int tile_n0, int nl, uint8_t* stage) {
+  switch (pp->activation) {
+    case CB_ACT_GELU: qt_store_rows_act<MB, CB_ACT_GELU, BF16>(v, p, pp, tile_n0, nl, stage); break;
+    case CB_ACT_RELU: qt_store_rows_act<MB, CB_ACT_RELU, BF16>(v, p, pp, tile_n0, nl, stage); break;
+    case CB_ACT_SILU: qt_store_rows_act<MB, CB_ACT_SILU, BF16>(v, p, pp, tile_n0, nl, stage); break;
+    case CB_ACT_HARDSWISH: qt_store_rows_act<MB, CB_ACT_HARDSWISH, BF16>(v, p, pp, tile_n0, nl, stage); break;
+    case CB_ACT_TANH: qt_store_rows_act<MB, CB_ACT_TANH, BF16>(v, p, pp, tile_n0, nl, stage); break;
+    default: qt_store_rows_act<MB, CB_ACT_NONE, BF16>(v, p, pp, tile_n0, nl, stage); break;
   }
 }
 
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
-template <int NB>      // MMA N extent: 3 digit planes of MB = NB / 3 rows (16 -> 5, 32 -> 10, 48 -> 16)
+// NB: MMA N extent = PLANES digit planes of MB = NB / PLANES rows
+//     (three planes: 16 -> 5 rows, 32 -> 10, 48 -> 16; two planes: 16 -> 8, 32 -> 16).
+template <int NB, int PLANES>
 __global__ void __launch_bounds__(QT_THREADS, 1)
-qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                        const __grid_constant__ CUtensorMap tmap_s, const QtParams p) {
-  constexpr int MB = NB / 3;
+qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ QtProblem single,
+                        const QtProblem* __restrict__ table, const QtParams p) {
+  constexpr int MB = NB / PLANES;
   constexpr int X_BYTES = (NB + QT_XROWS_EXTRA) * QT_UNIT_K;     // digit rows, then the row of unit[m,u]
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
-  constexpr int STAGES = qt_stages(NB);
+  constexpr int STAGES = qt_stages(NB, PLANES);
   constexpr int NBUF = STAGES;
   constexpr int SC_SLOTS = 2 * STAGES;             // scale rows in flight: stages + accumulators
   static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
@@ -264,19 +336,22 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   // finish before it reads or writes anything); kernels launched the ordinary way are unaffected.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef CB_QT_STAMPS
 #define QT_STAMP(i) do { if (p.dbg) p.dbg[(size_t)blockIdx.x * 8 + (i)] = global_ns(); } while (0)
+#else
+#define QT_STAMP(i) do { } while (0)
+#endif
   if (tid == 0) QT_STAMP(0);
   const int G = p.units_per_tile;
   const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
   const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
   const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
+  const QtProblem* const problems = table ? table : &single;
 
   if (warp == QT_TMA_WARP && lane == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
     fence_barrier_init();
-    prefetch_tensormap(&tmap_w);
     prefetch_tensormap(&tmap_x);
-    prefetch_tensormap(&tmap_s);
   }
   if (tid == 0) {
     for (int b = 0; b < NBUF; b++) mbar_init(&acc_full[b], 1);
@@ -304,7 +379,11 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     // threads in different warps, on the even and the odd units.
     if (lane == 0) {
       const int mine = warp == QT_TMA_WARP ? 0 : 1;
-      int tile = tile0, g = g0;
+      QtWalk w;
+      qt_walk_init(w, p, tile0, g0);
+      const CUtensorMap* map = &problems[w.pi].tmap_w;
+      if (table) qt_tensormap_acquire(map);
+      else prefetch_tensormap(map);
       for (int it = 0; it < n_units; it++) {
         if ((it & 1) == mine) {
           const int s = it % STAGES;
@@ -312,9 +391,12 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
           mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
-          tma_load_2d(base + s * STAGE_BYTES, &tmap_w, tile * QT_TILE_N, g * QT_UNIT_K, &full[s]);
+          tma_load_2d(base + s * STAGE_BYTES, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, w.g * QT_UNIT_K, &full[s]);
         }
-        if (++g == G) { g = 0; tile++; }
+        if (qt_walk_next(w, p, G)) {
+          map = &problems[w.pi].tmap_w;
+          qt_tensormap_acquire(map);
+        }
       }
     }
   } else if (warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
@@ -327,7 +409,11 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const int mine = (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP) ? 0 : 1;
       const bool digits = warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP;
       const int gpr = p.scale_group ? p.scale_group / QT_UNIT_K : 0;    // units per scale row
-      int tile = tile0, g = g0;
+      QtWalk w;
+      qt_walk_init(w, p, tile0, g0);
+      const CUtensorMap* map = &problems[w.pi].tmap_s;
+      if (table && !digits) qt_tensormap_acquire(map);
+      else if (!digits) prefetch_tensormap(map);
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
       for (int it = 0; it < n_units; it++) {
         if ((it & 1) == mine) {
@@ -335,11 +421,15 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           if (it >= STAGES) {
             if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
-          if (digits) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, g * QT_UNIT_K, 0, &full[s]);        // [NB + 8 rows][128 k]
-          else tma_load_2d(sc_slots + (it % SC_SLOTS) * QT_TILE_N, &tmap_s, tile * QT_TILE_N, srow, &full[s]);
+          if (digits) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, w.g * QT_UNIT_K, p.digit_row0[w.pi], &full[s]);        // [NB + 8 rows][128 k]
+          else tma_load_2d(sc_slots + (it % SC_SLOTS) * QT_TILE_N, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, srow, &full[s]);
         }
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
-        if (++g == G) { g = 0; tile++; srow = 0; sub = 0; }
+        if (w.g == G - 1) { srow = 0; sub = 0; }
+        if (qt_walk_next(w, p, G) && !digits) {
+          map = &problems[w.pi].tmap_s;
+          qt_tensormap_acquire(map);
+        }
       }
     }
   } else if (warp == QT_MMA_WARP || warp == QT_MMA2_WARP) {
@@ -379,7 +469,8 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
     for (int m = 0; m < MB; m++) tot[m] = 0.0f;
     bool failed = false;
-    int tile = tile0, g = g0;
+    QtWalk w;
+    qt_walk_init(w, p, tile0, g0);
     for (int it = 0; it < n_units; it++) {
       // After a timeout this group stops touching the pipeline but keeps walking the units, so that
       // the barriers below still see every thread (the status word reports the failure).
@@ -404,13 +495,18 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         for (int m = 0; m < MB; m++) {
           const float f0 = __uint_as_float(acc[m] + 0x4B400000u) - 12582912.0f;
           const float f1 = __uint_as_float(acc[MB + m] + 0x4B400000u) - 12582912.0f;
-          const float f2 = __uint_as_float(acc[2 * MB + m] + 0x4B400000u) - 12582912.0f;
-          tot[m] = fmaf(fmaf(f2, 16384.0f, fmaf(f1, 128.0f, f0)) * un[m], sc, tot[m]);
+          float q = fmaf(f1, 128.0f, f0);
+          if (PLANES == 3) {
+            const float f2 = __uint_as_float(acc[(PLANES - 1) * MB + m] + 0x4B400000u) - 12582912.0f;
+            q = fmaf(f2, 16384.0f, q);
+          }
+          tot[m] = fmaf(q * un[m], sc, tot[m]);
         }
       }
+      const int tile = w.tile, g = w.g;
       const bool tile_ends = (g == G - 1);
       const bool final_seg = it + 1 == n_units;
-      if (tile_ends || it + 1 == n_units) {
+      if (tile_ends || final_seg) {
         // ---- end of this CTA's share of the tile ----
         if (tid == 0 && final_seg) QT_STAMP(2);
         if (grp == 1) {
@@ -424,7 +520,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");      // s_merge may be rewritten
         if (grp == 0) {
-          const int n = tile * QT_TILE_N + nl;
+          const QtProblem* pp = &problems[w.pi];
+          const int tile_n0 = (tile - p.tile_start[w.pi]) * QT_TILE_N;
+          const int n = tile_n0 + nl;
           const bool whole = tile_ends && (it >= g);          // the tile's first unit is ours too
           bool write = true;
           if (!whole) {
@@ -469,17 +567,18 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             }
           }
           if (write) {
-            const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            const float* bias_p = pp->bias;
+            const float bias = (bias_p && n < pp->N) ? __ldg(bias_p + n) : 0.0f;
 #pragma unroll
             for (int m = 0; m < MB; m++) tot[m] += bias;
-            if (p.out_bf16) qt_store_rows<MB, true>(tot, p, tile * QT_TILE_N, nl, s_stage);
-            else qt_store_rows<MB, false>(tot, p, tile * QT_TILE_N, nl, s_stage);
+            if (p.out_bf16) qt_store_rows<MB, true>(tot, p, pp, tile_n0, nl, s_stage);
+            else qt_store_rows<MB, false>(tot, p, pp, tile_n0, nl, s_stage);
           }
         }
 #pragma unroll
         for (int m = 0; m < MB; m++) tot[m] = 0.0f;
       }
-      if (++g == G) { g = 0; tile++; }
+      qt_walk_next(w, p, G);
     }
     if (tid == 0) QT_STAMP(3);
     if (failed) { qt_fail(p, 4, 0); atomicExch(&s_failed, 1u); }
@@ -487,6 +586,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   // every role ends here; TMEM is released by the warp that allocated it
   tc_fence_before();
   __syncthreads();
+  if (s_failed) {
+    // A wait gave up: tensor copies this CTA requested may still be in flight towards its shared
+    // memory.  They complete within microseconds of their request; leave them a bounded 200 us.
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
   if (warp == QT_MMA_WARP) {
     __syncwarp();
     tc_fence_after();
@@ -546,11 +652,17 @@ int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsign
 // ---------------------------------------------------------------------------
 // planning and launch
 // ---------------------------------------------------------------------------
-static int qt_nb(int64_t M) { return M <= 5 ? 16 : (M <= 10 ? 32 : 48); }
+// Digit planes and MMA N extent by activation type and batch.  Up to five rows three planes fit the
+// narrowest MMA (16) for either type; beyond that bfloat16 needs only two planes (8 rows in 16, 16 in 32).
+static int qt_planes(const cb_qdense_desc& d) { return (d.x_dtype == CB_BF16 && d.M > 5) ? 2 : 3; }
+static int qt_nb(const cb_qdense_desc& d) {
+  if (qt_planes(d) == 2) return d.M <= 8 ? 16 : 32;
+  return d.M <= 5 ? 16 : (d.M <= 10 ? 32 : 48);
+}
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
-static int qt_smem(int nb) {
-  const int st = qt_stages(nb);
-  return 1024 + st * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + 2 * st * QT_SC_BYTES + 2 * (nb / 3) * QT_TILE_N * 4;
+static int qt_smem(int nb, int planes) {
+  const int st = qt_stages(nb, planes);
+  return 1024 + st * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + 2 * st * QT_SC_BYTES + 2 * (nb / planes) * QT_TILE_N * 4;
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -569,52 +681,123 @@ bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
 }
 
 struct QtLayout {
-  int nb, mb, n_tiles, units_per_tile;
+  int nb, mb, planes, n_problems, tiles_total, units_per_tile;
+  int tile_start[QT_MAX_PROBLEMS + 1];
   long long total_units;
-  size_t off_counters, off_digits, counter_bytes, off_partials, off_stamps, total;
+  size_t off_counters, off_digits, zero_bytes, off_partials, off_table, off_stamps, total;
 };
 
-static QtLayout qt_layout(const cb_qdense_desc& d, int blocks) {
+static QtLayout qt_layout(const cb_plan* p, int blocks) {
+  const cb_qdense_desc& d = p->qd;
   QtLayout l;
-  l.nb = qt_nb(d.M);
-  l.mb = l.nb / 3;
-  l.n_tiles = (int)((d.N + QT_TILE_N - 1) / QT_TILE_N);
+  l.planes = qt_planes(d);
+  l.nb = qt_nb(d);
+  l.mb = l.nb / l.planes;
+  l.n_problems = (int)p->group.size();
+  l.tiles_total = 0;
+  for (int i = 0; i < l.n_problems; i++) {
+    l.tile_start[i] = l.tiles_total;
+    l.tiles_total += (int)((p->group[i].N + QT_TILE_N - 1) / QT_TILE_N);
+  }
+  for (int i = l.n_problems; i <= QT_MAX_PROBLEMS; i++) l.tile_start[i] = l.tiles_total;
   l.units_per_tile = (int)((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
-  l.total_units = (long long)l.n_tiles * l.units_per_tile;
+  l.total_units = (long long)l.tiles_total * l.units_per_tile;
   l.off_counters = QT_HEADER;
-  l.off_digits = qt_align(l.off_counters + (size_t)l.n_tiles * 4);
-  // [NB digit rows + 8][128 * units]: row NB holds unit[m,u], 16 floats at the start of every unit's 128 bytes
-  l.counter_bytes = qt_align(l.off_digits + (size_t)(l.nb + QT_XROWS_EXTRA) * l.units_per_tile * QT_UNIT_K);   // all of this starts as zeros
-  l.off_partials = l.counter_bytes;
-  l.off_stamps = l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4;
-  l.total = l.off_stamps + (size_t)blocks * 8 * 8 + 64;
+  l.off_digits = qt_align(l.off_counters + (size_t)l.tiles_total * 4);
+  // one block of [NB digit rows + 8][128 * units] per problem: row NB of a block holds unit[m,u], 16 floats at the
+  // start of every unit's 128 bytes.  Counters and digits start as zeros.
+  l.zero_bytes = qt_align(l.off_digits + (size_t)l.n_problems * (l.nb + QT_XROWS_EXTRA) * l.units_per_tile * QT_UNIT_K);
+  l.off_partials = l.zero_bytes;
+  l.off_table = qt_align(l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4);
+  l.off_stamps = l.off_table + (size_t)l.n_problems * sizeof(QtProblem);
+  l.total = l.off_stamps;
+#ifdef CB_QT_STAMPS
+  l.total += (size_t)blocks * 8 * 8 + 64;
+#endif
   return l;
 }
 
-int qdense_decode_tc_plan(cb_plan* p) {
+static int qt_finish_plan(cb_plan* p) {
   const cb_qdense_desc& d = p->qd;
-  const long long tiles = (d.N + QT_TILE_N - 1) / QT_TILE_N;
+  long long tiles = 0;
+  for (const cb_qdense_member& m : p->group) tiles += (m.N + QT_TILE_N - 1) / QT_TILE_N;
+  if (tiles >= (1ll << 30)) return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: too many column tiles for one launch");
   const long long units = tiles * ((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
   p->blocks = (int)std::min<long long>(p->n_sm, units);
-  // When the column tiles fill three eighths of the machine or more (measured: 56 tiles on 148 SMs
-  // are still faster whole; 28 are not), every CTA takes one whole tile instead of an equal
-  // share of the units: the fewer, longer streams still saturate HBM (each SM gets a larger share of
-  // it), and no tile is split, so nothing is parked, counted or gathered at the end.
-  if (tiles <= p->n_sm && tiles * 8 >= (long long)p->n_sm * 3) p->blocks = (int)tiles;
-  const QtLayout l = qt_layout(d, p->blocks);
+  // Whole tiles per CTA when that keeps enough of the machine streaming: every CTA takes `waves`
+  // consecutive column tiles, so no tile is split and nothing is parked, counted or gathered at the
+  // end.  With one wave three eighths of the SMs are enough (measured: 56 tiles on 148 SMs are still
+  // faster whole, 28 are not — the fewer, longer streams still saturate HBM); with several waves
+  // the grid must cover three quarters of the SMs, else the units are split evenly over all SMs.
+  const long long waves = (tiles + p->n_sm - 1) / p->n_sm;
+  const long long whole_grid = (tiles + waves - 1) / waves;
+  if (whole_grid * waves == tiles &&
+      ((waves == 1 && tiles * 8 >= (long long)p->n_sm * 3) || (waves > 1 && whole_grid * 4 >= (long long)p->n_sm * 3)))
+    p->blocks = (int)whole_grid;
+  const QtLayout l = qt_layout(p, p->blocks);
   p->threads = QT_THREADS;
-  p->dyn_smem = qt_smem(l.nb);
-  p->counter_bytes = l.counter_bytes;
+  p->dyn_smem = qt_smem(l.nb, l.planes);
+  p->counter_bytes = l.zero_bytes;
   p->workspace_bytes = l.total;
   p->has_status = true;
-  if (d.gather_ranks > 1) p->n_outputs = d.gather_ranks;          // the result buffer of every rank
+  const int g = d.gather_ranks > 1 ? d.gather_ranks : 1;
+  p->n_outputs = (int)p->group.size() * g;
   p->name = std::string("qdense_decode_tc_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + "_n" + std::to_string(l.nb) +
-            (d.w_dtype == CB_U8 ? "_u8" : "_i8");
+            (l.planes == 2 ? "p2" : "") + (d.w_dtype == CB_U8 ? "_u8" : "_i8") +
+            (p->group.size() > 1 ? "_x" + std::to_string(p->group.size()) : "");
   return CB_OK;
 }
 
+int qdense_decode_tc_plan(cb_plan* p) {
+  cb_qdense_member m;
+  m.N = p->qd.N; m.has_bias = p->qd.has_bias; m.activation = p->qd.activation;
+  p->group.assign(1, m);
+  return qt_finish_plan(p);
+}
+
+int qdense_group_plan(cb_plan* p) {
+  cb_qdense_desc& d = p->qd;
+  const int n = (int)p->group.size();
+  if (n < 1 || n > QT_MAX_PROBLEMS)
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense group: %d members (1 to %d allowed)", n, QT_MAX_PROBLEMS);
+  if (d.x_dtype != CB_F32 && d.x_dtype != CB_BF16)
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x must be float32 (or bfloat16), got %s", dtype_name(d.x_dtype));
+  if (d.scheme != CB_QUANT_LINEAR || (d.w_dtype != CB_I8 && d.w_dtype != CB_U8))
+    return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense group: Linear int8 / uint8 weights only");
+  if (d.scale_layout < CB_SCALE_REF || d.scale_layout > CB_SCALE_KGROUP)
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown scale layout %d", d.scale_layout);
+  int inputs = 0;
+  for (int i = 0; i < n; i++) {
+    const cb_qdense_member& m = p->group[i];
+    if (m.activation < CB_ACT_NONE || m.activation > CB_ACT_TANH)
+      return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown activation %d", m.activation);
+    cb_qdense_desc one = d;
+    one.N = m.N; one.has_bias = m.has_bias; one.activation = m.activation;
+    std::string why;
+    if (!qdense_decode_tc_eligible(one, &why))
+      return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense group, member %d: %s", i, why.c_str());
+    inputs += 3 + (m.has_bias ? 1 : 0);
+  }
+  d.N = p->group[0].N; d.has_bias = p->group[0].has_bias; d.activation = p->group[0].activation;
+  d.variant = CB_QDENSE_DECODE_TC;
+  p->variant = CB_QDENSE_DECODE_TC;
+  p->n_inputs = inputs;
+  return qt_finish_plan(p);
+}
+
+// cuTensorMapEncodeTiled of a 2-D row-major matrix, remembered per thread: the encoding is a pure
+// function of its arguments, and a decode loop asks for the same few maps on every launch.
 // bytes == 1: a byte matrix in 128-byte swizzled tiles; bytes == 4: rows of floats, not swizzled
 static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0, uint64_t d1, uint32_t b0, uint32_t b1) {
+  struct Entry { const void* ptr; int bytes; uint64_t d0, d1; uint32_t b0, b1; bool valid; CUtensorMap map; };
+  constexpr int SLOTS = 64;
+  static thread_local Entry cache[SLOTS];
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
+  Entry& e = cache[(h >> 40) % SLOTS];
+  if (e.valid && e.ptr == ptr && e.bytes == bytes && e.d0 == d0 && e.d1 == d1 && e.b0 == b0 && e.b1 == b1) {
+    *m = e.map;
+    return CB_OK;
+  }
   encode_tiled_fn enc = tensor_map_encoder();
   if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {d0, d1};
@@ -626,94 +809,180 @@ static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0,
                    bytes == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  e.ptr = ptr; e.bytes = bytes; e.d0 = d0; e.d1 = d1; e.b0 = b0; e.b1 = b1; e.map = *m; e.valid = true;
   return CB_OK;
 }
 
-template <int NB>
-static int qt_launch_t(const cb_plan* p, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& ts, const QtParams& prm, bool overlap, cudaStream_t s) {
+// Everything the two launches of a decode call need.
+struct QtArgs {
+  CUtensorMap tmap_x;
+  QtProblem problems[QT_MAX_PROBLEMS];     // [0] doubles as the parameter-space record of a single problem
+  QtParams prm;
+  QtXList xl;
+  const QtProblem* table;                  // device copy of `problems` (null: single problem in parameter space)
+  int8_t* digits;
+  int nb, planes, mb, n_problems, units_per_tile;
+  bool bf16;
+  unsigned long long* xdbg;                // time stamps of the digit kernel (diagnostic builds only)
+};
+
+static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* out, void* ws, QtArgs* a) {
+  const cb_qdense_desc& d = p->qd;
+  const QtLayout l = qt_layout(p, p->blocks);
+  const int g = d.gather_ranks > 1 ? d.gather_ranks : 1;
+  uint8_t* w8 = (uint8_t*)ws;
+  memset(&a->prm, 0, sizeof(a->prm));
+  memset(&a->xl, 0, sizeof(a->xl));
+  a->nb = l.nb; a->planes = l.planes; a->mb = l.mb; a->n_problems = l.n_problems; a->units_per_tile = l.units_per_tile;
+  a->bf16 = d.x_dtype == CB_BF16;
+  a->digits = (int8_t*)(w8 + l.off_digits);
+  a->table = nullptr;
+  const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
+  const int block_rows = l.nb + QT_XROWS_EXTRA;
+  int ii = 0;
+  for (int i = 0; i < l.n_problems; i++) {
+    const cb_qdense_member& m = p->group[i];
+    const void* x = in[ii], *w = in[ii + 1], *sc = in[ii + 2];
+    const void* bias = m.has_bias ? in[ii + 3] : nullptr;
+    ii += 3 + (m.has_bias ? 1 : 0);
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(sc) & 15))
+      return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
+    QtProblem& q = a->problems[i];
+    memset(&q, 0, sizeof(q));
+    CB_TRY(qt_encode_2d(&q.tmap_w, w, 1, (uint64_t)m.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
+    CB_TRY(qt_encode_2d(&q.tmap_s, sc, 4, (uint64_t)m.N, scale_rows, QT_TILE_N, 1));
+    q.bias = (const float*)bias;
+    for (int r = 0; r < g; r++) {
+      void* o = out[i * g + r];
+      if (reinterpret_cast<uintptr_t>(o) & 15) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: outputs must be 16-byte aligned");
+      q.outs[r] = o;
+    }
+    q.N = (int)m.N;
+    q.out_ld = (int)(m.N * g);
+    q.out_col0 = (int)(m.N * (g > 1 ? d.gather_rank : 0));
+    q.activation = m.activation;
+    // problems given the same x share one block of digits
+    int xi = 0;
+    while (xi < a->xl.n && a->xl.x[xi] != x) xi++;
+    if (xi == a->xl.n) a->xl.x[a->xl.n++] = x;
+    a->prm.digit_row0[i] = xi * block_rows;
+  }
+  CB_TRY(qt_encode_2d(&a->tmap_x, a->digits, 1, (uint64_t)l.units_per_tile * QT_UNIT_K, (uint64_t)l.n_problems * block_rows,
+                      QT_UNIT_K, (uint32_t)block_rows));
+  QtParams& prm = a->prm;
+  prm.status = (unsigned*)w8;
+  prm.counters = (unsigned*)(w8 + l.off_counters);
+  prm.partials = (float*)(w8 + l.off_partials);
+  prm.M = (int)d.M; prm.K = (int)d.K;
+  prm.n_problems = l.n_problems;
+  prm.n_outs = g;
+  for (int i = 0; i <= QT_MAX_PROBLEMS; i++) prm.tile_start[i] = l.tile_start[i];
+  prm.units_per_tile = l.units_per_tile;
+  prm.total_units = l.total_units;
+  prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
+  prm.out_bf16 = a->bf16 ? 1 : 0;
+  prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
+  a->xdbg = nullptr;
+#ifdef CB_QT_STAMPS
+  prm.dbg = (unsigned long long*)(w8 + l.off_stamps);
+  a->xdbg = prm.dbg + (size_t)p->blocks * 8;
+#endif
+  return CB_OK;
+}
+
+template <int NB, int PLANES>
+static int qt_launch_main(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
   static std::atomic<bool> configured[64];
-  if (p->dev >= 64 || !configured[p->dev].load(std::memory_order_acquire)) {
-    CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB)));
-    if (p->dev < 64) configured[p->dev].store(true, std::memory_order_release);
+  int dev = 0;
+  CB_CUDA(cudaGetDevice(&dev));            // the current device: the one this launch goes to
+  if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB, PLANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB, PLANES)));
+    if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   // programmatic dependent launch: this grid may be scheduled while the digit kernel still runs
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)p->blocks);
   cfg.blockDim = dim3(QT_THREADS);
-  cfg.dynamicSmemBytes = (size_t)qt_smem(NB);
+  cfg.dynamicSmemBytes = (size_t)qt_smem(NB, PLANES);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB>, tw, tx, ts, prm));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB, PLANES>, a.tmap_x, a.problems[0], a.table, a.prm));
   return CB_OK;
 }
 
-int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  const cb_qdense_desc& d = p->qd;
-  if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
-    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
-  for (int r = 0; r < (d.gather_ranks > 1 ? d.gather_ranks : 1); r++)
-    if (reinterpret_cast<uintptr_t>(out[r]) & 15) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: outputs must be 16-byte aligned");
-  const QtLayout l = qt_layout(d, p->blocks);
-  uint8_t* w8 = (uint8_t*)ws;
-  int8_t* digits = (int8_t*)(w8 + l.off_digits);
+template <typename XT, int PLANES>
+static int qt_launch_digits(const QtArgs& a, int M, int K, cudaStream_t s) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  const int tasks = a.xl.n * M * a.units_per_tile;
+  cfg.gridDim = dim3((unsigned)((tasks + QX_THREADS / 32 - 1) / (QX_THREADS / 32)));
+  cfg.blockDim = dim3(QX_THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+#ifdef CB_QT_STAMPS
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits, a.xdbg));
+#else
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits));
+#endif
+  return CB_OK;
+}
 
-  // timing diagnosis only: CB_QDENSE_DEBUG_STAMPS=1 records per-CTA time stamps behind the parked partial tiles
-  const char* env_stamps = getenv("CB_QDENSE_DEBUG_STAMPS");
-  {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    unsigned long long* xdbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps + (size_t)p->blocks * 64) : nullptr;
-    const int tasks = (int)d.M * l.units_per_tile;
-    cfg.gridDim = dim3((unsigned)((tasks + QX_THREADS / 32 - 1) / (QX_THREADS / 32)));
-    cfg.blockDim = dim3(QX_THREADS);
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (d.x_dtype == CB_BF16)
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<__nv_bfloat16>, (const __nv_bfloat16*)in[0], (int)d.M, (int)d.K, l.nb, l.units_per_tile, digits, xdbg));
-    else
-      CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<float>, (const float*)in[0], (int)d.M, (int)d.K, l.nb, l.units_per_tile, digits, xdbg));
-  }
-
-  CUtensorMap tw, tx, ts;
-  const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
-  CB_TRY(qt_encode_2d(&tw, in[1], 1, (uint64_t)d.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
-  CB_TRY(qt_encode_2d(&tx, digits, 1, (uint64_t)l.units_per_tile * QT_UNIT_K, (uint64_t)(l.nb + QT_XROWS_EXTRA), QT_UNIT_K, (uint32_t)(l.nb + QT_XROWS_EXTRA)));
-  CB_TRY(qt_encode_2d(&ts, in[2], 4, (uint64_t)d.N, scale_rows, QT_TILE_N, 1));
-  QtParams prm;
-  memset(&prm, 0, sizeof(prm));
-  prm.scales = (const float*)in[2];
-  prm.bias = d.has_bias ? (const float*)in[3] : nullptr;
-  const int g = d.gather_ranks > 1 ? d.gather_ranks : 1;
-  for (int r = 0; r < g; r++) prm.outs[r] = out[r];
-  prm.n_outs = g;
-  prm.out_ld = (int)(d.N * g);
-  prm.out_col0 = (int)(d.N * (g > 1 ? d.gather_rank : 0));
-  prm.status = (unsigned*)w8;
-  prm.counters = (unsigned*)(w8 + l.off_counters);
-  prm.partials = (float*)(w8 + l.off_partials);
-  prm.M = (int)d.M; prm.K = (int)d.K; prm.N = (int)d.N;
-  prm.n_tiles = l.n_tiles;
-  prm.units_per_tile = l.units_per_tile;
-  prm.total_units = l.total_units;
-  prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
-  prm.activation = d.activation;
-  prm.out_bf16 = d.x_dtype == CB_BF16 ? 1 : 0;
-  prm.dbg = (env_stamps && env_stamps[0] == '1') ? (unsigned long long*)(w8 + l.off_stamps) : nullptr;
-  prm.idesc = idesc_i8(QT_TILE_N, l.nb, d.w_dtype == CB_U8 ? 0 : 1, 1, 1, 0);
-  switch (l.nb) {
-    case 16: return qt_launch_t<16>(p, tw, tx, ts, prm, true, s);
-    case 32: return qt_launch_t<32>(p, tw, tx, ts, prm, true, s);
-    default: return qt_launch_t<48>(p, tw, tx, ts, prm, true, s);
+static int qt_issue(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
+  const int M = (int)p->qd.M, K = (int)p->qd.K;
+  if (a.bf16 && a.planes == 2) CB_TRY((qt_launch_digits<__nv_bfloat16, 2>(a, M, K, s)));
+  else if (a.bf16) CB_TRY((qt_launch_digits<__nv_bfloat16, 3>(a, M, K, s)));
+  else CB_TRY((qt_launch_digits<float, 3>(a, M, K, s)));
+  if (a.planes == 2) return a.nb == 16 ? qt_launch_main<16, 2>(p, a, s) : qt_launch_main<32, 2>(p, a, s);
+  switch (a.nb) {
+    case 16: return qt_launch_main<16, 3>(p, a, s);
+    case 32: return qt_launch_main<32, 3>(p, a, s);
+    default: return qt_launch_main<48, 3>(p, a, s);
   }
 }
+
+int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  // A heap object: QtArgs carries 16 problem records and would be a large stack frame.
+  std::unique_ptr<QtArgs> a(new QtArgs);
+  CB_TRY(qt_fill_args(p, in, out, ws, a.get()));
+  if (a->n_problems > 1) {
+    // the table travels in stream order (a pageable source is staged before the call returns)
+    const QtLayout l = qt_layout(p, p->blocks);
+    QtProblem* table = reinterpret_cast<QtProblem*>((uint8_t*)ws + l.off_table);
+    CB_CUDA(cudaMemcpyAsync(table, a->problems, sizeof(QtProblem) * a->n_problems, cudaMemcpyHostToDevice, s));
+    a->table = table;
+  }
+  return qt_issue(p, *a, s);
+}
+
+int qdense_decode_tc_bind(const cb_plan* p, const void* const* in, void* const* out, void* ws, void** impl) {
+  std::unique_ptr<QtArgs> a(new QtArgs);
+  CB_TRY(qt_fill_args(p, in, out, ws, a.get()));
+  if (a->n_problems > 1) {
+    const QtLayout l = qt_layout(p, p->blocks);
+    QtProblem* table = reinterpret_cast<QtProblem*>((uint8_t*)ws + l.off_table);
+    // The copy must have landed before any stream may launch with this table (a copy from pageable
+    // memory can return once it is staged, and the launching streams do not wait for the default one).
+    CB_CUDA(cudaMemcpy(table, a->problems, sizeof(QtProblem) * a->n_problems, cudaMemcpyHostToDevice));
+    CB_CUDA(cudaStreamSynchronize(nullptr));
+    a->table = table;
+  }
+  *impl = a.release();
+  return CB_OK;
+}
+
+int qdense_decode_tc_launch_bound(const cb_plan* p, const void* impl, cudaStream_t s) {
+  return qt_issue(p, *static_cast<const QtArgs*>(impl), s);
+}
+
+void qdense_decode_tc_unbind(void* impl) { delete static_cast<QtArgs*>(impl); }
 
 }  // namespace cb

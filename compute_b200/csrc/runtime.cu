@@ -148,8 +148,15 @@ int cb_memset(int dev, void* dptr, int value, size_t bytes, cb_stream stream) {
 int cb_h2d(int dev, void* dst, const void* host_src, size_t bytes, cb_stream stream) {
   CB_TRY(set_device(dev));
   if (bytes == 0) return CB_OK;
-  if (stream) CB_CUDA(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
-  else CB_CUDA(cudaMemcpy(dst, host_src, bytes, cudaMemcpyHostToDevice));
+  if (stream) {
+    CB_CUDA(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  } else {
+    // A copy from pageable memory may return once the data are staged, before the transfer to the
+    // device has finished, and the streams of this library do not wait for the default stream:
+    // complete it here, so that "synchronous" holds for work on any stream.
+    CB_CUDA(cudaMemcpy(dst, host_src, bytes, cudaMemcpyHostToDevice));
+    CB_CUDA(cudaStreamSynchronize(nullptr));
+  }
   return CB_OK;
 }
 
@@ -311,6 +318,16 @@ int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan) {
   return finish_plan(qdense_plan(p), p, plan);
 }
 
+int cb_plan_qdense_group(int dev, const cb_qdense_desc* shared, const cb_qdense_member* members, int n_members,
+                         cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_QDENSE, plan, &p));
+  if (!shared || !members || n_members < 1) { delete p; return fail(CB_ERR_INVALID_ARG, "cb_plan_qdense_group: NULL or empty argument"); }
+  p->qd = *shared;
+  p->group.assign(members, members + n_members);
+  return finish_plan(qdense_group_plan(p), p, plan);
+}
+
 int cb_plan_dot(int dev, const cb_dot_desc* desc, cb_plan** plan) {
   cb_plan* p;
   CB_TRY(new_plan(dev, PLAN_DOT, plan, &p));
@@ -462,9 +479,20 @@ int cb_plan_grid(const cb_plan* plan, int* blocks, int* threads, int* dyn_smem_b
   return CB_OK;
 }
 
+static int check_launch_args(const cb_plan* plan, const void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                             const void* workspace);
+static int launch_checked(const cb_plan* plan, const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t s);
+
 int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
               void* const* outputs, int n_outputs, void* workspace, cb_stream stream) {
   clear_error();
+  CB_TRY(check_launch_args(plan, inputs, n_inputs, outputs, n_outputs, workspace));
+  CB_TRY(set_device(plan->dev));
+  return launch_checked(plan, inputs, outputs, workspace, (cudaStream_t)stream);
+}
+
+static int check_launch_args(const cb_plan* plan, const void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                             const void* workspace) {
   if (!plan) return fail(CB_ERR_INVALID_ARG, "plan is NULL");
   if (n_inputs != plan->n_inputs)
     return fail(CB_ERR_INVALID_ARG, "%s expects %d inputs, got %d", plan->name.c_str(), plan->n_inputs, n_inputs);
@@ -476,8 +504,10 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
     if (!outputs[i]) return fail(CB_ERR_INVALID_ARG, "%s: output %d is NULL", plan->name.c_str(), i);
   if (plan->workspace_bytes && !workspace)
     return fail(CB_ERR_INVALID_ARG, "%s needs %zu bytes of workspace", plan->name.c_str(), plan->workspace_bytes);
-  CB_TRY(set_device(plan->dev));
-  cudaStream_t s = (cudaStream_t)stream;
+  return CB_OK;
+}
+
+static int launch_checked(const cb_plan* plan, const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t s) {
   switch (plan->kind) {
     case PLAN_QDENSE: return qdense_launch(plan, inputs, outputs, workspace, s);
     case PLAN_DOT: return dot_launch(plan, inputs, outputs, workspace, s);
@@ -485,6 +515,72 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
     case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: case PLAN_COLS_BIAS: return fused_small_launch(plan, inputs, outputs, workspace, s);
     default: return helper_launch(plan, inputs, outputs, workspace, s);
   }
+}
+
+}  // extern "C"
+
+// A plan with its buffers fixed.  The tensor-core decode plan keeps its prepared launch arguments
+// (encoded tensor maps, problem table already in the workspace); every other plan keeps the
+// pointer lists and goes through its ordinary launch.
+struct cb_bound {
+  const cb_plan* plan = nullptr;
+  std::vector<const void*> in;
+  std::vector<void*> out;
+  void* ws = nullptr;
+  void* decode_tc = nullptr;
+};
+
+extern "C" {
+
+int cb_plan_bind(const cb_plan* plan, const void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                 void* workspace, cb_bound** bound) {
+  clear_error();
+  if (!bound) return fail(CB_ERR_INVALID_ARG, "cb_plan_bind: bound is NULL");
+  *bound = nullptr;
+  CB_TRY(check_launch_args(plan, inputs, n_inputs, outputs, n_outputs, workspace));
+  CB_TRY(set_device(plan->dev));
+  cb_bound* b = new cb_bound();
+  b->plan = plan;
+  b->in.assign(inputs, inputs + n_inputs);
+  b->out.assign(outputs, outputs + n_outputs);
+  b->ws = workspace;
+  if (plan->kind == PLAN_QDENSE && plan->variant == CB_QDENSE_DECODE_TC) {
+    const int st = qdense_decode_tc_bind(plan, b->in.data(), b->out.data(), workspace, &b->decode_tc);
+    if (st != CB_OK) { delete b; return st; }
+  }
+  *bound = b;
+  return CB_OK;
+}
+
+static int bound_launch(const cb_bound* b, cudaStream_t s) {
+  if (b->decode_tc) return qdense_decode_tc_launch_bound(b->plan, b->decode_tc, s);
+  return launch_checked(b->plan, b->in.data(), b->out.data(), b->ws, s);
+}
+
+int cb_bound_launch(const cb_bound* bound, cb_stream stream) {
+  clear_error();
+  if (!bound) return fail(CB_ERR_INVALID_ARG, "cb_bound_launch: bound is NULL");
+  CB_TRY(set_device(bound->plan->dev));
+  return bound_launch(bound, (cudaStream_t)stream);
+}
+
+int cb_bound_launch_many(const cb_bound* const* bounds, int n_bounds, cb_stream stream) {
+  clear_error();
+  if (n_bounds < 0 || (n_bounds > 0 && !bounds)) return fail(CB_ERR_INVALID_ARG, "cb_bound_launch_many: NULL argument");
+  int dev = -1;
+  for (int i = 0; i < n_bounds; i++) {
+    if (!bounds[i]) return fail(CB_ERR_INVALID_ARG, "cb_bound_launch_many: bound %d is NULL", i);
+    if (bounds[i]->plan->dev != dev) { dev = bounds[i]->plan->dev; CB_TRY(set_device(dev)); }
+    CB_TRY(bound_launch(bounds[i], (cudaStream_t)stream));
+  }
+  return CB_OK;
+}
+
+int cb_bound_destroy(cb_bound* bound) {
+  if (!bound) return CB_OK;
+  if (bound->decode_tc) qdense_decode_tc_unbind(bound->decode_tc);
+  delete bound;
+  return CB_OK;
 }
 
 int cb_plan_check_status(const cb_plan* plan, const void* workspace) {

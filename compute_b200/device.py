@@ -7,7 +7,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _lib
-from ._lib import DotDesc, QDenseDesc, SdpaDesc, check
+from ._lib import DotDesc, QDenseDesc, QDenseMember, SdpaDesc, check
 
 # dtype codes of gomlx/compute dtypes/dtype_enum.go (also cb_dtype in cudabackend.h)
 INVALID, BOOL, I8, I16, I32, I64, U8, U16, U32, U64, F16, F32, F64, BF16 = range(14)
@@ -247,6 +247,18 @@ class Plan:
         return cls(h, dev)
 
     @classmethod
+    def qdense_group(cls, M, K, members, x_dtype=F32, w_dtype=I8, scale_layout=SCALE_CHANNEL, block_size=0, dev=0,
+                     gather_ranks=0, gather_rank=0) -> "Plan":
+        """Several independent decode-shaped projections sharing M and K as one launch.  `members` is a
+        sequence of (N, has_bias, activation); launch inputs are x, w, scales, bias? per member in order."""
+        d = QDenseDesc(M, K, 0, x_dtype, w_dtype, scale_layout, block_size, 0, 0, ACT_NONE, QDENSE_DECODE_TC,
+                       gather_ranks, gather_rank, QUANT_LINEAR, 0)
+        arr = (QDenseMember * max(len(members), 1))(*[QDenseMember(int(n), int(b), int(a)) for n, b, a in members])
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_qdense_group(dev, C.byref(d), arr, len(members), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
     def dot(cls, B, M, N, K, in_dtype=F32, out_dtype=INVALID, rhs_transposed=False, variant=DOT_AUTO, dev=0,
             has_bias=False, activation=ACT_NONE) -> "Plan":
         d = DotDesc(B, M, N, K, int(rhs_transposed), in_dtype, out_dtype, variant, int(has_bias), activation)
@@ -349,6 +361,14 @@ class Plan:
     def check_status(self, workspace: Optional[int]) -> None:
         check(_lib.load().cb_plan_check_status(self.handle, workspace))
 
+    def bind(self, inputs: Sequence[int], outputs: Sequence[int], workspace: Optional[int] = None) -> "Bound":
+        """Fixes the buffers of this plan: later launches are only the kernel launches."""
+        ins = (C.c_void_p * max(len(inputs), 1))(*inputs)
+        outs = (C.c_void_p * max(len(outputs), 1))(*outputs)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_bind(self.handle, ins, len(inputs), outs, len(outputs), workspace, C.byref(h)))
+        return Bound(h, self)
+
     def destroy(self) -> None:
         if self.handle:
             _lib.load().cb_plan_destroy(self.handle)
@@ -359,3 +379,36 @@ class Plan:
             self.destroy()
         except Exception:
             pass
+
+
+class Bound:
+    """A plan bound to its buffers (cb_plan_bind); keeps the plan alive."""
+
+    def __init__(self, handle: C.c_void_p, plan: Plan):
+        self.handle = handle
+        self.plan = plan
+
+    def launch(self, stream: Optional[Stream] = None) -> None:
+        check(_lib.load().cb_bound_launch(self.handle, stream.handle if stream else None))
+
+    def destroy(self) -> None:
+        if self.handle:
+            _lib.load().cb_bound_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class BoundSequence:
+    """A step's launches, issued by one C call (cb_bound_launch_many)."""
+
+    def __init__(self, bounds: Sequence[Bound]):
+        self.bounds = list(bounds)
+        self._arr = (C.c_void_p * max(len(self.bounds), 1))(*[b.handle for b in self.bounds])
+
+    def launch(self, stream: Optional[Stream] = None) -> None:
+        check(_lib.load().cb_bound_launch_many(self._arr, len(self.bounds), stream.handle if stream else None))

@@ -134,6 +134,24 @@ typedef struct {
 
 int cb_plan_qdense(int dev, const cb_qdense_desc* desc, cb_plan** plan);
 
+/* Several independent decode-shaped projections as ONE launch of the tensor-core decode kernel: the members
+ * share M, K, the dtypes and the scale layout of `shared` (its N, has_bias and activation are ignored) and each
+ * has its own width, bias and activation — gate / up of a SwiGLU block, q / k / v of an attention block
+ * (fused_ops.go:413-461 describes them as separate FusedQuantizedDense calls on one x), or the same projection
+ * of several requests.  The fixed cost of a launch (pipeline fill and drain, 5-6 us against 9 us of streaming for a
+ * 4096 x 14336 layer) is paid once for the group, and members that are given the same x pointer share one
+ * conversion of x.  Launch inputs: x, weights, scales, bias? of member 0, then of member 1, ...; outputs: one per
+ * member (gather_ranks of them per member for a gathered plan, own buffer included).  At most 16 members; the
+ * decode tensor-core kernel's conditions apply (M <= 16, compact scales, K groups of a multiple of 128). */
+typedef struct {
+  int64_t N;
+  int32_t has_bias;
+  int32_t activation;     /* cb_activation */
+} cb_qdense_member;
+#define CB_QDENSE_GROUP_MAX 16
+int cb_plan_qdense_group(int dev, const cb_qdense_desc* shared, const cb_qdense_member* members, int n_members,
+                         cb_plan** plan);
+
 /* No counterpart in the reference: a decode-shaped (M <= 16, compact scales) quantized dense
  * for callers that cannot allocate device memory when they launch — a server that gave all of
  * HBM to its own arena, a plugin inside another framework's callback, a process whose allocator
@@ -234,6 +252,19 @@ int cb_launch(const cb_plan* plan, const void* const* inputs, int n_inputs,
  * workspace; CB_ERR_TIMEOUT if a wait gave up.  CB_OK for plans without such waits. */
 int cb_plan_check_status(const cb_plan* plan, const void* workspace);
 int cb_plan_destroy(cb_plan* plan);
+
+/* ---- bound launches: a plan with its buffers fixed (an Executable whose parameters stay resident between
+ *      Execute calls, executable.go:10-37: weights, activations and results of a decode loop live at fixed
+ *      addresses).  Binding does once what cb_launch does on every call — argument checks, tensor-map encoding,
+ *      the table of a grouped plan (copied into the workspace, synchronously) — so that a launch is only the
+ *      kernel launches, and cb_bound_launch_many issues a whole step's launches from one call.  The plan, the
+ *      buffers and the workspace must outlive the bound object; one workspace serves one bound object. */
+typedef struct cb_bound cb_bound;
+int cb_plan_bind(const cb_plan* plan, const void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                 void* workspace, cb_bound** bound);
+int cb_bound_launch(const cb_bound* bound, cb_stream stream);
+int cb_bound_launch_many(const cb_bound* const* bounds, int n_bounds, cb_stream stream);
+int cb_bound_destroy(cb_bound* bound);
 
 /* ---- peer memory between the processes of one machine (one process per GPU, NVLink)
  * No counterpart in the reference.  cb_ipc_export names an allocation made by cb_alloc (pass its base

@@ -36,7 +36,19 @@ def test_library_exports_every_declared_symbol():
 def test_plans_select_kernels_by_shape_and_dtype():
     p = dv.Plan.qdense(1, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, activation=dv.ACT_SILU)
     assert p.kernel_name == "qdense_decode_tc_bf16_n16_i8" and p.workspace_bytes > 0
-    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n48_i8")
+    # beyond five rows bfloat16 activations travel as two int8 digit planes (16 rows each at M = 16), float32 as three
+    assert dv.Plan.qdense(8, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n16p2_i8")
+    assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n32p2_i8")
+    assert dv.Plan.qdense(16, 4096, 14336, dv.F32, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n48_i8")
+    # a group of independent projections is one launch: 8 x 112 column tiles as 128 CTAs of 7 whole tiles
+    g = dv.Plan.qdense_group(16, 4096, [(14336, False, dv.ACT_SILU)] * 8, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128)
+    assert g.kernel_name == "qdense_decode_tc_bf16_n32p2_i8_x8" and g.blocks == 128
+    # an 8-way column shard of the same step: 8 x 14 tiles, one whole tile per CTA
+    assert dv.Plan.qdense_group(16, 4096, [(1792, False, dv.ACT_SILU)] * 8, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).blocks == 112
+    with pytest.raises(cb.ErrNotImplemented):      # members must suit the tensor-core decode kernel
+        dv.Plan.qdense_group(16, 4096, [(14336, False, 0)], dv.BF16, dv.I8, dv.SCALE_KGROUP, 64)
+    with pytest.raises(cb.BackendError):
+        dv.Plan.qdense_group(16, 4096, [(128, False, 0)] * 17, dv.BF16, dv.I8, dv.SCALE_CHANNEL)
     # K groups finer than the 128-row tensor-core unit stay on the mma.sync decode kernel; M > 16 is prefill
     assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 64).kernel_name == "qdense_decode_bf16_m16_i8"
     assert dv.Plan.qdense(2048, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_CHANNEL).kernel_name == "qdense_prefill_tcgen05_bf16_i8"

@@ -264,6 +264,156 @@ def test_decode_tc_fixed_point_digits_edge_cases():
     assert np.isnan(got[4]).all()
 
 
+@pytest.mark.parametrize("M", list(range(1, 17)))
+def test_decode_tc_bf16_two_digit_planes_every_batch_size(M):
+    """bfloat16 activations beyond five rows travel as two int8 digit planes (8 rows per plane up to M = 8, 16
+    beyond); up to five rows three planes fit the narrowest MMA, as for float32."""
+    K, N = 384, 400
+    x, w, s, b = qdense_inputs(700 + M, M, K, N, x_dtype="bf16", scale_layout="kgroup", group=128)
+    got, plan = ops.quantized_dense(orc.bf16_from_f32(x), w, s, None, b, x_dtype=dv.BF16, scale_layout=dv.SCALE_KGROUP,
+                                    block_size=128, activation=dv.ACT_GELU, variant=dv.QDENSE_DECODE_TC, return_plan=True)
+    assert plan.kernel_name == "qdense_decode_tc_bf16_" + ("n16" if M <= 5 else "n16p2" if M <= 8 else "n32p2") + "_i8"
+    want = oracle_compact(x, w, s, b, "kgroup", 128, orc.ACT_GELU)
+    assert max_abs_normalised(orc.bf16_to_f32(got), want) < BF16_TOL
+    assert max_abs_normalised(orc.bf16_to_f32(got), orc.bf16_to_f32(orc.bf16_from_f32(want))) < 2.0 ** -7
+
+
+def test_decode_tc_bf16_two_plane_error_bound():
+    """The two-plane fixed point keeps 13 bits below each 128-wide unit's maximum: elements within 2^-6 of it are
+    exact, smaller ones are rounded at 2^-14 of it, which is far below the bfloat16 rounding of the result itself
+    (2^-8 of its size).  Rows of zeros, a row spanning 30 binades, a huge row and a non-finite value behave as in
+    the three-plane form."""
+    M, K, N = 6, 512, 256
+    x, w, s, b = qdense_inputs(98, M, K, N, x_dtype="bf16", scale_layout="channel")
+    x[0] = 0.0
+    x[1] = orc.bf16_to_f32(orc.bf16_from_f32(x[1] * np.exp2(np.random.default_rng(1).integers(-30, 1, size=K)).astype(np.float32)))
+    x[3] = orc.bf16_to_f32(orc.bf16_from_f32(x[3] * np.float32(1e30)))
+    x[4, 17] = np.inf
+    got = orc.bf16_to_f32(ops.quantized_dense(orc.bf16_from_f32(x), w, s, None, b, x_dtype=dv.BF16, scale_layout=dv.SCALE_CHANNEL,
+                                              variant=dv.QDENSE_DECODE_TC))
+    ok = [0, 1, 2, 3, 5]
+    want = oracle_compact(np.ascontiguousarray(x[ok]), w, s, b, "channel", 0, orc.ACT_NONE)
+    for i, r in enumerate(ok):
+        scale = max(np.abs(want[i]).max(), 1e-30)
+        # one bfloat16 rounding of the result (2^-9 relative to its own size) plus the digit error
+        assert np.abs(got[r] - want[i]).max() / scale < 1.25 * 2.0 ** -8, r
+    assert np.isnan(got[4]).all()
+
+
+# ------------------------------------------------------------- grouped launch, bound launches
+def _group_case(x_dtype):
+    """Three projections of different widths on two activation matrices (members 0 and 2 share x)."""
+    M, K = 7, 512
+    widths = [(400, True, "silu"), (1792, False, "none"), (144, True, "gelu")]
+    rng = np.random.default_rng(11)
+    xs = [rng.standard_normal((M, K), dtype=np.float32) for _ in range(2)]
+    if x_dtype == "bf16":
+        xs = [orc.bf16_to_f32(orc.bf16_from_f32(x)) for x in xs]
+    members = []
+    for i, (N, has_b, act) in enumerate(widths):
+        _, w, s, b = qdense_inputs(40 + i, M, K, N, scale_layout="kgroup", group=128, bias=has_b)
+        members.append(dict(N=N, x=xs[0] if i != 1 else xs[1], xi=0 if i != 1 else 1, w=w, s=s, b=b, act=act))
+    return M, K, xs, members
+
+
+@pytest.mark.parametrize("x_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("bound", [False, True])
+def test_decode_group_matches_oracle_and_single_plans(x_dtype, bound):
+    """A group of independent projections runs as one launch; every member equals its own single-plan result
+    (same arithmetic per column; the order in which k units are summed may differ where tiles are split)."""
+    M, K, xs, members = _group_case(x_dtype)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    esize = 2 if x_dtype == "bf16" else 4
+    carrier = np.uint16 if x_dtype == "bf16" else np.float32
+    up = (lambda a: orc.bf16_from_f32(a)) if x_dtype == "bf16" else (lambda a: a)
+    plan = dv.Plan.qdense_group(M, K, [(m["N"], m["b"] is not None, ACT[m["act"]]) for m in members], code, dv.I8,
+                                dv.SCALE_KGROUP, 128)
+    assert plan.kernel_name.endswith("_x3")
+    st = dv.Stream(0)
+    xd = [dv.DeviceMem.from_numpy(up(x)) for x in xs]
+    ins, outs, keep = [], [], []
+    for m in members:
+        wd, sd = dv.DeviceMem.from_numpy(m["w"]), dv.DeviceMem.from_numpy(m["s"])
+        keep += [wd, sd]
+        ins += [xd[m["xi"]].ptr, wd.ptr, sd.ptr]
+        if m["b"] is not None:
+            bd = dv.DeviceMem.from_numpy(m["b"])
+            keep.append(bd)
+            ins.append(bd.ptr)
+        od = dv.DeviceMem(M * m["N"] * esize)
+        od.zero()
+        outs.append(od)
+    ws = plan.new_workspace()
+    if bound:
+        b = plan.bind(ins, [o.ptr for o in outs], ws.ptr)
+        for _ in range(3):                      # repeated launches leave the workspace ready
+            b.launch(st)
+        dv.BoundSequence([b, b]).launch(st)
+    else:
+        for _ in range(2):
+            plan.launch(ins, [o.ptr for o in outs], ws.ptr, st)
+    st.sync()
+    plan.check_status(ws.ptr)
+    for m, od in zip(members, outs):
+        got = od.download((M, m["N"]), carrier)
+        want = oracle_compact(m["x"], m["w"], m["s"], m["b"], "kgroup", 128, ACT[m["act"]])
+        single = ops.quantized_dense(up(m["x"]), m["w"], m["s"], None, m["b"], x_dtype=code, scale_layout=dv.SCALE_KGROUP,
+                                     block_size=128, activation=ACT[m["act"]], variant=dv.QDENSE_DECODE_TC)
+        if x_dtype == "bf16":
+            assert max_abs_normalised(orc.bf16_to_f32(got), want) < BF16_TOL
+            assert max_abs_normalised(orc.bf16_to_f32(got), orc.bf16_to_f32(single)) < 2.0 ** -7
+        else:
+            assert max_abs_normalised(got, want) < F32_TOL
+            assert max_abs_normalised(got, single) < 1e-6
+
+
+def test_decode_group_full_size_step():
+    """The benchmark's step as one launch: 4 distinct 4096 x 14336 layers at M = 16 (4 x 112 column tiles, 112 CTAs of
+    4 whole tiles); every layer carries the same bits as its own single launch."""
+    M, K, N, L = 16, 4096, 14336, 4
+    rng = np.random.default_rng(5)
+    plan = dv.Plan.qdense_group(M, K, [(N, False, dv.ACT_SILU)] * L, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128)
+    assert plan.blocks == 112
+    single = dv.Plan.qdense(M, K, N, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, False, False, dv.ACT_SILU)
+    st = dv.Stream(0)
+    ins, outs, ref_outs, keep = [], [], [], []
+    for layer in range(L):
+        x = orc.bf16_from_f32(rng.standard_normal((M, K), dtype=np.float32))
+        w = rng.integers(-127, 128, size=(K, N), dtype=np.int8)
+        s = rng.uniform(0.001, 0.02, size=(K // 128, N)).astype(np.float32)
+        d = [dv.DeviceMem.from_numpy(a) for a in (x, w, s)]
+        keep += d
+        ins += [m.ptr for m in d]
+        outs.append(dv.DeviceMem(M * N * 2))
+        ref_outs.append(dv.DeviceMem(M * N * 2))
+        if layer == L - 1:                      # one layer against the oracle; the rest against the single plan's bits
+            want = oracle_compact(orc.bf16_to_f32(x), w, s, None, "kgroup", 128, orc.ACT_SILU)
+    ws, ws1 = plan.new_workspace(), single.new_workspace()
+    plan.bind(ins, [o.ptr for o in outs], ws.ptr).launch(st)
+    for layer in range(L):
+        single.launch(ins[3 * layer:3 * layer + 3], [ref_outs[layer].ptr], ws1.ptr, st)
+    st.sync()
+    plan.check_status(ws.ptr)
+    for layer in range(L):
+        assert np.array_equal(outs[layer].download((M, N), np.uint16), ref_outs[layer].download((M, N), np.uint16))
+    assert max_abs_normalised(orc.bf16_to_f32(outs[L - 1].download((M, N), np.uint16)), want) < BF16_TOL
+
+
+def test_bound_launch_of_other_plans():
+    """cb_plan_bind works for every plan kind; plans without prepared state go through their ordinary launch."""
+    x, w, s, b = qdense_inputs(3, 40, 256, 272, scale_layout="channel")
+    plan = dv.Plan.qdense(40, 256, 272, dv.F32, dv.I8, dv.SCALE_CHANNEL, 0, False, True, dv.ACT_RELU, variant=dv.QDENSE_GENERIC)
+    d = [dv.DeviceMem.from_numpy(a) for a in (x, w, s, b)]
+    out = dv.DeviceMem(40 * 272 * 4)
+    bnd = plan.bind([m.ptr for m in d], [out.ptr], None)
+    bnd.launch(None)
+    dv.check(dv._lib.load().cb_stream_sync(0, None))
+    want = oracle_compact(x, w, s, b, "channel", 0, orc.ACT_RELU)
+    assert np.array_equal(out.download((40, 272), np.float32), want)
+    with pytest.raises(BackendError):
+        plan.bind([m.ptr for m in d[:3]], [out.ptr], None)
+
+
 @pytest.mark.parametrize("M", [1, 4, 16])
 def test_config3_full_size(M):
     """Decode-shaped projection 4096 x 14336, bf16 x, group-128 scales along K, SiLU."""
