@@ -62,7 +62,8 @@ const char* dtype_name(int d);
 
 // ---- plans ------------------------------------------------------------------
 enum PlanKind { PLAN_QDENSE = 1, PLAN_DOT, PLAN_SDPA, PLAN_COPY, PLAN_CONVERT, PLAN_IOTA,
-                PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM, PLAN_COLS_BIAS };
+                PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM, PLAN_COLS_BIAS,
+                PLAN_BINARY, PLAN_UNARY, PLAN_REDUCE, PLAN_BROADCAST, PLAN_RMSNORM };
 
 struct HelperDesc {
   int32_t dtype = 0, dtype_to = 0, rank = 0, axis = 0;
@@ -111,6 +112,10 @@ int helper_plan(cb_plan* p);
 int helper_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int fused_small_plan(cb_plan* p);
 int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+int elementwise_plan(cb_plan* p);
+int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+// out[i] = reduction over r of stacked[r][i], r in rank order (the local step of AllReduce)
+int stacked_reduce_launch(int dtype, int op, const void* stacked, int g, int64_t n, void* out, cudaStream_t s);
 int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s);
 int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsigned* status_word, cudaStream_t s);
 

@@ -22,17 +22,18 @@
 // One launch serves a GROUP of independent problems that share M and K (one problem is the
 // ordinary case): the work list is the column tiles of all problems in order, so the pipeline is
 // filled and drained once per group instead of once per projection.  Each problem has its own
-// weights, scales, bias, activation and result buffer(s) in a table of QtProblem records.
+// weights, scales, bias, activation and result buffer(s) in a table of QtProblem records that
+// travels in kernel parameter space (the TMA unit reads the tensor maps from there).
 //
 //   qdense_xdigits_kernel   x -> digits + unit[m,u] (one warp per x, row and k unit, all at once)
 //   qdense_decode_tc_kernel persistent over a contiguous range of (column tile, k unit) pairs:
-//       warps 8, 12   TMA producers of the weight tiles (even / odd units) into the stage ring; the
+//       warps 8, 12   TMA producers of the weight tiles (even / odd stages) into the stage ring; the
 //                     first ones are requested before the digit kernel has finished
 //       warps 10, 13  TMA producers of the digit tile, whose extra row carries the unit's 16 unit[m,u]
 //       warps 14, 15  TMA producers of the unit's 128 scales
-//       warps 9, 11   MMA issuers on alternate units: 4 MMAs (K = 32) per unit into the TMEM
+//       warps 9, 11   MMA issuers (even / odd stages): 4 MMAs (K = 32) per unit into the TMEM
 //                     accumulator that travels with the stage
-//       warps 0-7     epilogue as above, two groups of four warps on alternate units; a tile whose
+//       warps 0-7     epilogue as above, two groups of four warps (even / odd accumulators); a tile whose
 //                     units are split between CTAs is finished by the CTA that arrives last, summing
 //                     the parked partial tiles in CTA order (deterministic: the result does not
 //                     depend on which CTA finishes)
@@ -71,8 +72,8 @@ constexpr int QT_HEADER = 256;                          // status words, then ar
 constexpr int QT_MAX_RANKS = 8;
 constexpr int QT_MAX_PROBLEMS = CB_QDENSE_GROUP_MAX;
 
-// One problem of a launch.  The tensor maps are read by the TMA unit straight from this record
-// (kernel parameter space for a single unbound problem, global memory otherwise).
+// One problem of a launch.  The tensor maps are read by the TMA unit straight from this record,
+// which is part of the kernel parameters.
 struct alignas(64) QtProblem {
   CUtensorMap tmap_w;                  // W [K rows][N bytes], 128 x 128 boxes, 128-byte swizzle
   CUtensorMap tmap_s;                  // scales [rows][N] f32, 128 x 1 boxes
@@ -84,6 +85,8 @@ struct alignas(64) QtProblem {
   int pad[10];
 };
 static_assert(sizeof(QtProblem) == 384, "QtProblem layout");
+// The problems of a launch: kernels are instantiated for tables of 1, 4 and 16 records (0.4, 1.5 and 6 KB of parameters).
+template <int MAXP> struct QtTable { QtProblem p[MAXP]; };
 
 struct QtParams {
   unsigned* status;
@@ -226,9 +229,9 @@ __device__ __forceinline__ int qt_cta_of(long long total, int grid, long long u)
   return c;
 }
 
+// The first failure is the one reported (later ones are its consequences): code, then the unit it happened at.
 __device__ __forceinline__ void qt_fail(const QtParams& p, unsigned code, unsigned detail) {
-  atomicExch(&p.status[0], code);
-  atomicExch(&p.status[1], detail);
+  if (atomicCAS(&p.status[0], 0u, code) == 0u) atomicExch(&p.status[1], detail | (blockIdx.x << 16));
 }
 
 // Position of a role thread in its CTA's range of (column tile, k unit) pairs: the tile counts over
@@ -250,11 +253,6 @@ __device__ __forceinline__ bool qt_walk_next(QtWalk& w, const QtParams& p, int G
   w.tile_end = p.tile_start[w.pi + 1];
   return true;
 }
-// Before the TMA unit reads a tensor map that the host wrote into global memory.
-__device__ __forceinline__ void qt_tensormap_acquire(const CUtensorMap* m) {
-  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(m) : "memory");
-}
-
 // act(v[m]) -> out[m, n] for the rows that exist, called by the 128 threads of the first epilogue
 // group together.  The activation is chosen once, outside the row loop, so the MB rows are
 // independent instruction streams; for 16-bit outputs SiLU uses the hardware exp and reciprocal
@@ -304,10 +302,9 @@ __device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p,
 // ---------------------------------------------------------------------------
 // NB: MMA N extent = PLANES digit planes of MB = NB / PLANES rows
 //     (three planes: 16 -> 5 rows, 32 -> 10, 48 -> 16; two planes: 16 -> 8, 32 -> 16).
-template <int NB, int PLANES>
+template <int NB, int PLANES, int MAXP>
 __global__ void __launch_bounds__(QT_THREADS, 1)
-qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ QtProblem single,
-                        const QtProblem* __restrict__ table, const QtParams p) {
+qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ QtTable<MAXP> table, const QtParams p) {
   constexpr int MB = NB / PLANES;
   constexpr int X_BYTES = (NB + QT_XROWS_EXTRA) * QT_UNIT_K;     // digit rows, then the row of unit[m,u]
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
@@ -346,7 +343,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
   const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
   const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
   const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
-  const QtProblem* const problems = table ? table : &single;
+  const QtProblem* const problems = table.p;
 
   if (warp == QT_TMA_WARP && lane == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
@@ -376,27 +373,29 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     // ------------------------------ TMA producers: weights ----------------------
     // Issuing one tensor copy keeps a thread busy for several hundred cycles, more than half of what
     // a unit's bytes take to arrive, so every kind of load (weights, digits, scales) has two issuing
-    // threads in different warps, on the even and the odd units.
+    // threads in different warps.  Work is split by STAGE, not by unit: the even stages belong to one
+    // thread of each role (and to the first epilogue group), the odd stages to the other.  A parity
+    // wait tells two consecutive phases of a barrier apart, not three; a thread that owns a stage
+    // waits for every phase of that stage's barriers in turn and cannot run a phase ahead of them,
+    // whatever order the tiles arrive in.  (With the units split by their own parity and an odd
+    // number of stages, a stage alternated between the two threads, each saw every other phase,
+    // and a thread ahead of a late tile took the previous phase for the one it was waiting for.)
     if (lane == 0) {
       const int mine = warp == QT_TMA_WARP ? 0 : 1;
       QtWalk w;
       qt_walk_init(w, p, tile0, g0);
       const CUtensorMap* map = &problems[w.pi].tmap_w;
-      if (table) qt_tensormap_acquire(map);
-      else prefetch_tensormap(map);
+      prefetch_tensormap(map);
       for (int it = 0; it < n_units; it++) {
-        if ((it & 1) == mine) {
-          const int s = it % STAGES;
+        const int s = it % STAGES;
+        if ((s & 1) == mine) {
           if (it >= STAGES) {
             if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
           mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
           tma_load_2d(base + s * STAGE_BYTES, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, w.g * QT_UNIT_K, &full[s]);
         }
-        if (qt_walk_next(w, p, G)) {
-          map = &problems[w.pi].tmap_w;
-          qt_tensormap_acquire(map);
-        }
+        if (qt_walk_next(w, p, G)) map = &problems[w.pi].tmap_w;
       }
     }
   } else if (warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
@@ -412,12 +411,11 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
       QtWalk w;
       qt_walk_init(w, p, tile0, g0);
       const CUtensorMap* map = &problems[w.pi].tmap_s;
-      if (table && !digits) qt_tensormap_acquire(map);
-      else if (!digits) prefetch_tensormap(map);
+      if (!digits) prefetch_tensormap(map);
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
       for (int it = 0; it < n_units; it++) {
-        if ((it & 1) == mine) {
-          const int s = it % STAGES;
+        const int s = it % STAGES;
+        if ((s & 1) == mine) {
           if (it >= STAGES) {
             if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
@@ -426,16 +424,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
         }
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (w.g == G - 1) { srow = 0; sub = 0; }
-        if (qt_walk_next(w, p, G) && !digits) {
-          map = &problems[w.pi].tmap_s;
-          qt_tensormap_acquire(map);
-        }
+        if (qt_walk_next(w, p, G)) map = &problems[w.pi].tmap_s;
       }
     }
   } else if (warp == QT_MMA_WARP || warp == QT_MMA2_WARP) {
     // ------------------------------ MMA issuers -------------------------------
     // Issuing a unit (one wait, four MMAs, one commit) costs a single thread several hundred
-    // cycles, about what the unit's bytes take to arrive: two threads take alternate units.
+    // cycles, about what the unit's bytes take to arrive: two threads share the units by stage.
     if (lane == 0) {
       const int mine = warp == QT_MMA_WARP ? 0 : 1;
       // W: MN-major, 128 n bytes per k row, 8-row groups 1024 bytes apart, 32 k rows (4096 bytes) per MMA.
@@ -444,8 +439,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
       const uint64_t da0 = smem_desc_sw128(smem_u32(base), QT_W_BYTES, 1024);
       const uint64_t db0 = smem_desc_sw128(smem_u32(base) + QT_W_BYTES, 16, 1024);
       const uint32_t idesc = p.idesc;
-      for (int it = mine; it < n_units; it += 2) {
+      for (int it = 0; it < n_units; it++) {
         const int s = it % STAGES;
+        if ((s & 1) != mine) continue;
         if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
         tc_fence_after();
         const uint64_t da = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
@@ -458,8 +454,8 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     }
   } else {
     // ------------------------------ epilogue (warps 0-7) ----------------------
-    // Two groups of four warps take alternate units, so that one group's TMEM load and barrier
-    // round trips hide behind the other's arithmetic.  Each thread owns one output column of the
+    // Two groups of four warps share the units by accumulator (even / odd), so that one group's TMEM
+    // load and barrier round trips hide behind the other's arithmetic.  Each thread owns one output column of the
     // tile (TMEM lane) and keeps MB running totals; at the end of the CTA's share of a tile the
     // second group hands its totals to the first through shared memory.
     const int grp = warp >> 2, quarter = warp & 3;
@@ -474,8 +470,9 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     for (int it = 0; it < n_units; it++) {
       // After a timeout this group stops touching the pipeline but keeps walking the units, so that
       // the barriers below still see every thread (the status word reports the failure).
-      if ((it & 1) == grp && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
-      if ((it & 1) == grp && !failed) {
+      const bool own = ((it % NBUF) & 1) == grp;
+      if (own && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
+      if (own && !failed) {
         const int buf = it % NBUF;
         tc_fence_after();
         uint32_t acc[NB];
@@ -581,7 +578,7 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
       qt_walk_next(w, p, G);
     }
     if (tid == 0) QT_STAMP(3);
-    if (failed) { qt_fail(p, 4, 0); atomicExch(&s_failed, 1u); }
+    if (failed) { qt_fail(p, 4, (unsigned)(warp)); atomicExch(&s_failed, 1u); }
   }
   // every role ends here; TMEM is released by the warp that allocated it
   tc_fence_before();
@@ -684,7 +681,7 @@ struct QtLayout {
   int nb, mb, planes, n_problems, tiles_total, units_per_tile;
   int tile_start[QT_MAX_PROBLEMS + 1];
   long long total_units;
-  size_t off_counters, off_digits, zero_bytes, off_partials, off_table, off_stamps, total;
+  size_t off_counters, off_digits, zero_bytes, off_partials, off_stamps, total;
 };
 
 static QtLayout qt_layout(const cb_plan* p, int blocks) {
@@ -708,8 +705,7 @@ static QtLayout qt_layout(const cb_plan* p, int blocks) {
   // start of every unit's 128 bytes.  Counters and digits start as zeros.
   l.zero_bytes = qt_align(l.off_digits + (size_t)l.n_problems * (l.nb + QT_XROWS_EXTRA) * l.units_per_tile * QT_UNIT_K);
   l.off_partials = l.zero_bytes;
-  l.off_table = qt_align(l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4);
-  l.off_stamps = l.off_table + (size_t)l.n_problems * sizeof(QtProblem);
+  l.off_stamps = qt_align(l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4);
   l.total = l.off_stamps;
 #ifdef CB_QT_STAMPS
   l.total += (size_t)blocks * 8 * 8 + 64;
@@ -816,10 +812,9 @@ static int qt_encode_2d(CUtensorMap* m, const void* ptr, int bytes, uint64_t d0,
 // Everything the two launches of a decode call need.
 struct QtArgs {
   CUtensorMap tmap_x;
-  QtProblem problems[QT_MAX_PROBLEMS];     // [0] doubles as the parameter-space record of a single problem
+  QtTable<QT_MAX_PROBLEMS> table;          // the first 1, 4 or 16 records travel as kernel parameters
   QtParams prm;
   QtXList xl;
-  const QtProblem* table;                  // device copy of `problems` (null: single problem in parameter space)
   int8_t* digits;
   int nb, planes, mb, n_problems, units_per_tile;
   bool bf16;
@@ -836,7 +831,6 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
   a->nb = l.nb; a->planes = l.planes; a->mb = l.mb; a->n_problems = l.n_problems; a->units_per_tile = l.units_per_tile;
   a->bf16 = d.x_dtype == CB_BF16;
   a->digits = (int8_t*)(w8 + l.off_digits);
-  a->table = nullptr;
   const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
   const int block_rows = l.nb + QT_XROWS_EXTRA;
   int ii = 0;
@@ -847,7 +841,7 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
     ii += 3 + (m.has_bias ? 1 : 0);
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(sc) & 15))
       return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x, weights and scales must be 16-byte aligned");
-    QtProblem& q = a->problems[i];
+    QtProblem& q = a->table.p[i];
     memset(&q, 0, sizeof(q));
     CB_TRY(qt_encode_2d(&q.tmap_w, w, 1, (uint64_t)m.N, (uint64_t)d.K, QT_TILE_N, QT_UNIT_K));
     CB_TRY(qt_encode_2d(&q.tmap_s, sc, 4, (uint64_t)m.N, scale_rows, QT_TILE_N, 1));
@@ -890,13 +884,13 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
   return CB_OK;
 }
 
-template <int NB, int PLANES>
-static int qt_launch_main(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
+template <int NB, int PLANES, int MAXP>
+static int qt_launch_main_t(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
   static std::atomic<bool> configured[64];
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));            // the current device: the one this launch goes to
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB, PLANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB, PLANES)));
+    CB_CUDA(cudaFuncSetAttribute(qdense_decode_tc_kernel<NB, PLANES, MAXP>, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(NB, PLANES)));
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   // programmatic dependent launch: this grid may be scheduled while the digit kernel still runs
@@ -911,8 +905,15 @@ static int qt_launch_main(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB, PLANES>, a.tmap_x, a.problems[0], a.table, a.prm));
+  // the first MAXP records of the table (QtTable<MAXP> is a prefix of QtTable<QT_MAX_PROBLEMS>)
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB, PLANES, MAXP>, a.tmap_x, *reinterpret_cast<const QtTable<MAXP>*>(&a.table), a.prm));
   return CB_OK;
+}
+template <int NB, int PLANES>
+static int qt_launch_main(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
+  if (a.n_problems == 1) return qt_launch_main_t<NB, PLANES, 1>(p, a, s);
+  if (a.n_problems <= 4) return qt_launch_main_t<NB, PLANES, 4>(p, a, s);
+  return qt_launch_main_t<NB, PLANES, QT_MAX_PROBLEMS>(p, a, s);
 }
 
 template <typename XT, int PLANES>
@@ -953,28 +954,12 @@ int qdense_decode_tc_launch(const cb_plan* p, const void* const* in, void* const
   // A heap object: QtArgs carries 16 problem records and would be a large stack frame.
   std::unique_ptr<QtArgs> a(new QtArgs);
   CB_TRY(qt_fill_args(p, in, out, ws, a.get()));
-  if (a->n_problems > 1) {
-    // the table travels in stream order (a pageable source is staged before the call returns)
-    const QtLayout l = qt_layout(p, p->blocks);
-    QtProblem* table = reinterpret_cast<QtProblem*>((uint8_t*)ws + l.off_table);
-    CB_CUDA(cudaMemcpyAsync(table, a->problems, sizeof(QtProblem) * a->n_problems, cudaMemcpyHostToDevice, s));
-    a->table = table;
-  }
   return qt_issue(p, *a, s);
 }
 
 int qdense_decode_tc_bind(const cb_plan* p, const void* const* in, void* const* out, void* ws, void** impl) {
   std::unique_ptr<QtArgs> a(new QtArgs);
   CB_TRY(qt_fill_args(p, in, out, ws, a.get()));
-  if (a->n_problems > 1) {
-    const QtLayout l = qt_layout(p, p->blocks);
-    QtProblem* table = reinterpret_cast<QtProblem*>((uint8_t*)ws + l.off_table);
-    // The copy must have landed before any stream may launch with this table (a copy from pageable
-    // memory can return once it is staged, and the launching streams do not wait for the default one).
-    CB_CUDA(cudaMemcpy(table, a->problems, sizeof(QtProblem) * a->n_problems, cudaMemcpyHostToDevice));
-    CB_CUDA(cudaStreamSynchronize(nullptr));
-    a->table = table;
-  }
   *impl = a.release();
   return CB_OK;
 }

@@ -451,6 +451,62 @@ int cb_plan_cols_bias(int dev, int32_t dtype, int64_t rows, int64_t total_cols, 
   return finish_plan(fused_small_plan(p), p, plan);
 }
 
+int cb_plan_binary(int dev, int32_t op, int32_t dtype, int32_t rank, const int64_t* lhs_dims, const int64_t* rhs_dims, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_BINARY, plan, &p));
+  if (rank < 0 || rank > 8 || (rank > 0 && (!lhs_dims || !rhs_dims))) { delete p; return fail(CB_ERR_INVALID_ARG, "binary op: rank %d unsupported", rank); }
+  p->helper.dtype = dtype;
+  p->helper.rank = rank;
+  p->helper.axis = op;
+  for (int i = 0; i < rank; i++) { p->helper.dims[i] = lhs_dims[i]; p->helper.starts[i] = rhs_dims[i]; }
+  return finish_plan(elementwise_plan(p), p, plan);
+}
+
+int cb_plan_unary(int dev, int32_t op, int32_t dtype, int64_t n, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_UNARY, plan, &p));
+  p->helper.dtype = dtype;
+  p->helper.axis = op;
+  p->helper.n = n;
+  return finish_plan(elementwise_plan(p), p, plan);
+}
+
+int cb_plan_reduce(int dev, int32_t reduce_op, int32_t dtype, int32_t rank, const int64_t* dims, const int32_t* reduced_axis_flags,
+                   cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_REDUCE, plan, &p));
+  if (rank < 0 || rank > 8 || (rank > 0 && (!dims || !reduced_axis_flags))) { delete p; return fail(CB_ERR_INVALID_ARG, "reduce: rank %d unsupported", rank); }
+  p->helper.dtype = dtype;
+  p->helper.rank = rank;
+  p->helper.axis = reduce_op;
+  for (int i = 0; i < rank; i++) { p->helper.dims[i] = dims[i]; p->helper.perm[i] = reduced_axis_flags[i] ? 1 : 0; }
+  return finish_plan(elementwise_plan(p), p, plan);
+}
+
+int cb_plan_broadcast_in_dim(int dev, int32_t dtype, int32_t rank, const int64_t* dims, int32_t out_rank, const int64_t* out_dims,
+                             const int32_t* broadcast_axes, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_BROADCAST, plan, &p));
+  if (rank < 0 || rank > 8 || out_rank < 0 || out_rank > 8 || rank > out_rank) { delete p; return fail(CB_ERR_INVALID_ARG, "BroadcastInDim: ranks %d -> %d unsupported", rank, out_rank); }
+  p->helper.dtype = dtype;
+  p->helper.rank = rank;
+  p->helper.strides[0] = out_rank;
+  for (int i = 0; i < rank; i++) { p->helper.dims[i] = dims[i]; p->helper.perm[i] = broadcast_axes[i]; }
+  for (int i = 0; i < out_rank; i++) p->helper.out_dims[i] = out_dims[i];
+  return finish_plan(elementwise_plan(p), p, plan);
+}
+
+int cb_plan_rms_norm(int dev, int32_t dtype, int64_t rows, int64_t row_size, double epsilon, int32_t has_gamma, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_RMSNORM, plan, &p));
+  if (rows < 0 || row_size < 1) { delete p; return fail(CB_ERR_INVALID_ARG, "rms norm: rows %lld of %lld elements", (long long)rows, (long long)row_size); }
+  p->helper.dtype = dtype;
+  p->helper.dims[0] = rows; p->helper.dims[1] = row_size;
+  p->helper.eps = epsilon;
+  p->helper.flags = has_gamma ? 1 : 0;
+  return finish_plan(elementwise_plan(p), p, plan);
+}
+
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes) {
   clear_error();
   if (!plan || !bytes) return fail(CB_ERR_INVALID_ARG, "NULL argument");
@@ -513,6 +569,7 @@ static int launch_checked(const cb_plan* plan, const void* const* inputs, void* 
     case PLAN_DOT: return dot_launch(plan, inputs, outputs, workspace, s);
     case PLAN_SDPA: return sdpa_launch(plan, inputs, outputs, workspace, s);
     case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: case PLAN_COLS_BIAS: return fused_small_launch(plan, inputs, outputs, workspace, s);
+    case PLAN_BINARY: case PLAN_UNARY: case PLAN_REDUCE: case PLAN_BROADCAST: case PLAN_RMSNORM: return elementwise_launch(plan, inputs, outputs, workspace, s);
     default: return helper_launch(plan, inputs, outputs, workspace, s);
   }
 }

@@ -225,6 +225,27 @@ int cb_plan_slice(int dev, int32_t dtype, int32_t rank, const int64_t* dims, con
 int cb_plan_transpose(int dev, int32_t dtype, int32_t rank, const int64_t* dims,
                       const int32_t* permutation, cb_plan** plan);
 
+/* ---- element-wise and reduction ops around the projections of a decoder block (StandardOps, standard_ops.go:131-700;
+ *      executors internal/gobackend/ops).  Binary ops follow shapeinference.BinaryOp
+ *      (shapeinference/shapeinference.go:219-300): both operands are given with the same rank (a scalar as all
+ *      ones) and every dimension pair is equal or has a 1, which is broadcast.  Float dtypes (halves computed in
+ *      f32); binary ops also Int32 / Int64.  The reduce plan keeps the axes whose flag is 0 and reduces the others
+ *      (cb_reduce_op).  BroadcastInDim: standard_ops.go:232-254. */
+/* compute.ReduceOpType minus one (standard_ops.go:65-84) */
+typedef enum { CB_REDUCE_SUM = 0, CB_REDUCE_PRODUCT = 1, CB_REDUCE_MAX = 2, CB_REDUCE_MIN = 3 } cb_reduce_op;
+typedef enum { CB_BIN_ADD = 0, CB_BIN_SUB = 1, CB_BIN_MUL = 2, CB_BIN_DIV = 3, CB_BIN_MAX = 4, CB_BIN_MIN = 5 } cb_binary_op;
+typedef enum { CB_UN_NEG = 0, CB_UN_RSQRT = 1, CB_UN_SQRT = 2, CB_UN_EXP = 3, CB_UN_LOGISTIC = 4, CB_UN_TANH = 5 } cb_unary_op;
+int cb_plan_binary(int dev, int32_t op, int32_t dtype, int32_t rank, const int64_t* lhs_dims, const int64_t* rhs_dims, cb_plan** plan);
+int cb_plan_unary(int dev, int32_t op, int32_t dtype, int64_t n_elements, cb_plan** plan);
+int cb_plan_reduce(int dev, int32_t reduce_op, int32_t dtype, int32_t rank, const int64_t* dims, const int32_t* reduced_axis_flags,
+                   cb_plan** plan);
+int cb_plan_broadcast_in_dim(int dev, int32_t dtype, int32_t rank, const int64_t* dims, int32_t out_rank, const int64_t* out_dims,
+                             const int32_t* broadcast_axes, cb_plan** plan);
+/* y = x * rsqrt(mean(x^2 over the row) + epsilon) * gamma?  over rows of row_size trailing elements (launch inputs x,
+ * gamma?).  The interface has no fused RMS norm (FusedLayerNorm is mean-centred, internal/gobackend/fusedops/
+ * layernorm.go:102-137): Builder.Compile substitutes this plan for the decomposed Mul / ReduceSum / Rsqrt form. */
+int cb_plan_rms_norm(int dev, int32_t dtype, int64_t rows, int64_t row_size, double epsilon, int32_t has_gamma, cb_plan** plan);
+
 /* ---- FusedGelu, FusedSoftmax, FusedLayerNorm (FusedOps, fused_ops.go:318-334; internal/gobackend/fusedops/gelu.go,
  *      softmax.go, layernorm.go).  Float32 / Float64 as the reference, BFloat16 / Float16 computed in f32.
  *      softmax: x viewed as [outer, axis_size, inner].  layer norm: rows of norm_size trailing elements;
@@ -256,9 +277,9 @@ int cb_plan_destroy(cb_plan* plan);
 /* ---- bound launches: a plan with its buffers fixed (an Executable whose parameters stay resident between
  *      Execute calls, executable.go:10-37: weights, activations and results of a decode loop live at fixed
  *      addresses).  Binding does once what cb_launch does on every call — argument checks, tensor-map encoding,
- *      the table of a grouped plan (copied into the workspace, synchronously) — so that a launch is only the
- *      kernel launches, and cb_bound_launch_many issues a whole step's launches from one call.  The plan, the
- *      buffers and the workspace must outlive the bound object; one workspace serves one bound object. */
+ *      the problem table of a grouped plan — so that a launch is only the kernel launches, and
+ *      cb_bound_launch_many issues a whole step's launches from one call.  The plan, the buffers and the
+ *      workspace must outlive the bound object; one workspace serves one bound object at a time. */
 typedef struct cb_bound cb_bound;
 int cb_plan_bind(const cb_plan* plan, const void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
                  void* workspace, cb_bound** bound);
@@ -289,7 +310,6 @@ int cb_peer_wait(int dev, const void* flags, int n_flags, uint32_t target, void*
  * machine these return CB_ERR_NOT_IMPLEMENTED. */
 #define CB_COMM_ID_BYTES 128
 typedef struct cb_comm cb_comm;
-typedef enum { CB_REDUCE_SUM = 0, CB_REDUCE_PRODUCT = 1, CB_REDUCE_MAX = 2, CB_REDUCE_MIN = 3 } cb_reduce_op;
 int cb_comm_unique_id(unsigned char* id /* CB_COMM_ID_BYTES */);
 int cb_comm_init_rank(int dev, int nranks, int rank, const unsigned char* id, cb_comm** comm);
 int cb_comm_size(const cb_comm* comm, int* nranks, int* rank);
