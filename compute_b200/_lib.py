@@ -88,6 +88,12 @@ SIGNATURES = {
                        C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_transpose": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32),
                            C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_binary": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_unary": ([C.c_int, C.c_int32, C.c_int32, C.c_int64, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_reduce": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_broadcast_in_dim": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32),
+                                  C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_rms_norm": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_double, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_gelu": ([C.c_int, C.c_int32, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_softmax": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_layernorm": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_double, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),

@@ -87,6 +87,7 @@ struct cb_plan {
   size_t counter_bytes = 0;       // leading region of the workspace zeroed by prepare
   int blocks = 0, threads = 0, dyn_smem = 0;
   bool has_status = false;        // kernel keeps a status word at workspace offset 0
+  bool whole_tiles = false;       // decode tensor-core plan: every CTA takes whole column tiles (nothing is split or parked)
   std::string name;
   cb_qdense_desc qd{};
   std::vector<cb_qdense_member> group;   // members of a grouped decode plan (one entry for an ordinary plan)

@@ -26,17 +26,28 @@
 // travels in kernel parameter space (the TMA unit reads the tensor maps from there).
 //
 //   qdense_xdigits_kernel   x -> digits + unit[m,u] (one warp per x, row and k unit, all at once)
-//   qdense_decode_tc_kernel persistent over a contiguous range of (column tile, k unit) pairs:
-//       warps 8, 12   TMA producers of the weight tiles (even / odd stages) into the stage ring; the
-//                     first ones are requested before the digit kernel has finished
-//       warps 10, 13  TMA producers of the digit tile, whose extra row carries the unit's 16 unit[m,u]
-//       warps 14, 15  TMA producers of the unit's 128 scales
-//       warps 9, 11   MMA issuers (even / odd stages): 4 MMAs (K = 32) per unit into the TMEM
-//                     accumulator that travels with the stage
-//       warps 0-7     epilogue as above, two groups of four warps (even / odd accumulators); a tile whose
-//                     units are split between CTAs is finished by the CTA that arrives last, summing
-//                     the parked partial tiles in CTA order (deterministic: the result does not
-//                     depend on which CTA finishes)
+//   qdense_decode_tc_kernel persistent over a contiguous range of (column tile, k unit) pairs.
+//     Two rings decouple the memory stream from the arithmetic:
+//       stages        [weights 128 x 128 B | digit tile NB x 128 B] in shared memory, filled by TMA,
+//                     consumed by the MMA and handed back to the producers by the MMA's own
+//                     completion (tcgen05.commit), so the bytes in flight do not wait for the epilogue;
+//       accumulators  up to 16 TMEM accumulators of NB columns, each with a slot for the unit's 128
+//                     scales and 16 unit[m,u], released by the epilogue.
+//       warps 8, 12   TMA producers of the weight tiles into the stage ring; the first ones are
+//                     requested before the digit kernel has finished
+//       warps 10, 13  TMA producers of the digit tiles
+//       warps 14, 15  producers of the scale / unit slots
+//       warps 9, 11   MMA issuers: 4 MMAs (K = 32) per unit from a stage into an accumulator
+//       warps 0-7     epilogue as above, two groups of four warps; a tile whose units are split
+//                     between CTAs is finished by the CTA that arrives last, summing the parked
+//                     partial tiles in CTA order (deterministic: the result does not depend on
+//                     which CTA finishes)
+//     Every role comes in a pair, one thread (or group) for the even units and one for the odd ones,
+//     and both ring sizes are even: a stage, an accumulator and their barriers therefore always
+//     belong to the same member of each pair, which waits for every phase of those barriers in
+//     turn.  (A parity wait tells two consecutive phases apart, not three: with an odd ring a
+//     barrier alternated between the two members, each saw every other phase, and a thread ahead
+//     of a late tile took the previous phase for the one it was waiting for.)
 // All mbarrier waits are bounded; a timeout sets the status word and TMEM is always freed.
 // Building with -DCB_QT_STAMPS adds per-CTA time stamps (timing diagnosis; off in the shipped build).
 #include "tc_common.cuh"
@@ -51,23 +62,28 @@ namespace cb {
 
 using namespace tc;
 
-#ifndef QT_S16
-#define QT_S16 11
-#endif
 constexpr int QT_TILE_N = 128;
 constexpr int QT_UNIT_K = 128;
 constexpr int QT_W_BYTES = QT_TILE_N * QT_UNIT_K;     // 16 KB
-// Stages of the weight ring (each with its digit tile and its TMEM accumulator), by digit-tile rows:
-// what shared memory holds.
-__host__ __device__ constexpr int qt_stages(int nb, int planes) { return nb == 16 ? (planes == 3 ? QT_S16 : QT_S16 - 1) : (nb == 32 ? 9 : 8); }
-constexpr int QT_THREADS = 512;                       // warps 0-7 epilogue, 9 and 11 MMA, six TMA producers
+constexpr int QT_THREADS = 512;                       // warps 0-7 epilogue, 9 and 11 MMA, six producers
 constexpr int QT_TMA_WARP = 8, QT_MMA_WARP = 9, QT_SIDE_WARP = 10, QT_MMA2_WARP = 11;   // weights (even units), MMA, digits (even), MMA
 constexpr int QT_TMA2_WARP = 12, QT_SIDE2_WARP = 13;                                      // weights, digits of the odd units
-constexpr int QT_SCALE_WARP = 14, QT_SCALE2_WARP = 15;                                    // scales of the even / odd units
-constexpr int QT_XROWS_EXTRA = 8;                      // rows below the digits in a digit tile; the first holds unit[m,u]
+constexpr int QT_SCALE_WARP = 14, QT_SCALE2_WARP = 15;                                    // scale / unit slots of the even / odd units
 constexpr int QT_TMEM_COLS = 512;
-constexpr int QT_SC_BYTES = QT_TILE_N * 4;
+constexpr int QT_SC_BYTES = QT_TILE_N * 4;             // a unit's 128 scales
+constexpr int QT_UN_BYTES = 64;                         // a unit's 16 unit[m,u]
+constexpr int QT_SLOT_BYTES = 640;                      // scales, then unit[m,u]; slots stay 128-byte aligned
+constexpr int QT_BAR_BYTES = 1024;
 constexpr int QT_HEADER = 256;                          // status words, then arrival counters
+// Accumulators (even, at most 16) and stages (even: what shared memory holds) by MMA N extent and digit planes.
+__host__ __device__ constexpr int qt_accs(int nb) { return nb == 48 ? 10 : 16; }
+__host__ __device__ constexpr int qt_tail_bytes(int nb, int planes) {   // barriers, slots, merge tile, staging tile (16-bit results only with two planes)
+  return QT_BAR_BYTES + qt_accs(nb) * QT_SLOT_BYTES + (nb / planes) * QT_TILE_N * 4 + (nb / planes) * QT_TILE_N * (planes == 2 ? 2 : 4);
+}
+__host__ __device__ constexpr int qt_stages(int nb, int planes) {
+  return ((232448 - 1024 - qt_tail_bytes(nb, planes)) / (QT_W_BYTES + nb * QT_UNIT_K)) / 2 * 2 > 10 ? 10
+       : ((232448 - 1024 - qt_tail_bytes(nb, planes)) / (QT_W_BYTES + nb * QT_UNIT_K)) / 2 * 2;
+}
 
 constexpr int QT_MAX_RANKS = 8;
 constexpr int QT_MAX_PROBLEMS = CB_QDENSE_GROUP_MAX;
@@ -97,7 +113,10 @@ struct QtParams {
   int n_outs;               // 1, or the number of ranks
   int tile_start[QT_MAX_PROBLEMS + 1];     // first column tile of every problem in the launch's list
   int digit_row0[QT_MAX_PROBLEMS];         // first row of the problem's block in the digit matrix
+  const float* unit_rows[QT_MAX_PROBLEMS]; // the problem's unit[m,u]: 16 floats per k unit
   int units_per_tile;
+  int tiles_total;
+  int whole_tiles;          // 1: CTAs take whole tiles; 0: an equal share of the units, shared tiles fixed up
   long long total_units;
   int scale_group;          // 0: one scale per column; else rows of the K group
   int out_bf16;
@@ -131,11 +150,11 @@ __device__ __forceinline__ void qx_load4(const float* x, size_t m, int K, int k,
 
 // One warp per (activation matrix, row m, 128-wide k unit u): the unit's largest finite |x| fixes
 // unit[m,u] = 2^-shift (7*PLANES - 1 bits below it), every element becomes PLANES signed base-128
-// digits, and unit[m,u] goes to row NB of the block (NaN when the unit holds inf or NaN).  No pass
-// over the whole row is needed, so all tasks run at once.
+// digits in the matrix's block of NB rows, and unit[m,u] goes to the unit array, 16 floats per k unit
+// (NaN when the unit holds inf or NaN).  No pass over the whole row is needed, so all tasks run at once.
 template <typename XT, int PLANES>
 __global__ void __launch_bounds__(QX_THREADS)
-qdense_xdigits_kernel(const QtXList xl, int M, int K, int NB, int G, int8_t* __restrict__ digits
+qdense_xdigits_kernel(const QtXList xl, int M, int K, int NB, int G, int8_t* __restrict__ digits, float* __restrict__ unit_rows
 #ifdef CB_QT_STAMPS
                       , unsigned long long* dbg
 #endif
@@ -196,18 +215,17 @@ qdense_xdigits_kernel(const QtXList xl, int M, int K, int NB, int G, int8_t* __r
     }
   }
   const size_t Kp = (size_t)G * QT_UNIT_K;     // row stride of the digit matrix (whole units)
-  int8_t* block = digits + (size_t)xi * (NB + QT_XROWS_EXTRA) * Kp;
+  int8_t* block = digits + (size_t)xi * NB * Kp;
   if (k < K) {               // K is a multiple of 16: a group of four lies inside or outside
     *reinterpret_cast<uint32_t*>(block + (size_t)(0 * MB + m) * Kp + k) = w0;
     *reinterpret_cast<uint32_t*>(block + (size_t)(1 * MB + m) * Kp + k) = w1;
     if (PLANES == 3) *reinterpret_cast<uint32_t*>(block + (size_t)(2 * MB + m) * Kp + k) = w2;
   }
   if (lane == 0) {
-    // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN.  It travels
-    // with the digits: row NB of the block (the first below the digit rows) holds, for every unit, its 16 floats.
+    // 2^-shift, possibly a subnormal float (exact); NaN marks a unit holding inf or NaN
     float unit = shift <= 126 ? __int_as_float((127 - shift) << 23) : __int_as_float(1 << (149 - shift));
     if (bad) unit = __int_as_float(0x7FC00000);
-    *reinterpret_cast<float*>(block + (size_t)NB * Kp + (size_t)u * QT_UNIT_K + 4 * m) = unit;
+    unit_rows[((size_t)xi * G + u) * 16 + m] = unit;
   }
 #ifdef CB_QT_STAMPS
   if (dbg && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) dbg[2] = global_ns();
@@ -217,6 +235,7 @@ qdense_xdigits_kernel(const QtXList xl, int M, int K, int NB, int G, int8_t* __r
 // ---------------------------------------------------------------------------
 // schedule helpers (the same arithmetic on every CTA)
 // ---------------------------------------------------------------------------
+// split schedule: every CTA takes an equal share of the units; tiles shared between CTAs are fixed up at the end
 __device__ __forceinline__ long long qt_first_unit(long long total, int grid, int cta) {
   return (total * cta) / grid;
 }
@@ -228,28 +247,38 @@ __device__ __forceinline__ int qt_cta_of(long long total, int grid, long long u)
   while (c + 1 < grid && qt_first_unit(total, grid, c + 1) <= u) c++;
   return c;
 }
+// Whole-tile schedule: CTA c takes the column tiles c, c + grid, c + 2 grid, ...  At any moment neighbouring
+// CTAs therefore stream neighbouring column tiles of the same weight rows, as the CTAs of a single-wave
+// launch do: the 256-byte requests the tensor copies are promoted to in L2 are used by both neighbours
+// while they are still cached (with a run of consecutive tiles per CTA the second half was evicted before
+// its turn: 1.29 x the weight bytes came from DRAM), and the DRAM pages of a weight row are read together.
+__device__ __forceinline__ int qt_whole_tiles_of(const QtParams& p, int grid, int cta) {
+  return cta < p.tiles_total ? (p.tiles_total - cta + grid - 1) / grid : 0;
+}
 
 // The first failure is the one reported (later ones are its consequences): code, then the unit it happened at.
 __device__ __forceinline__ void qt_fail(const QtParams& p, unsigned code, unsigned detail) {
   if (atomicCAS(&p.status[0], 0u, code) == 0u) atomicExch(&p.status[1], detail | (blockIdx.x << 16));
 }
 
-// Position of a role thread in its CTA's range of (column tile, k unit) pairs: the tile counts over
-// the whole launch, `pi` is the problem the tile belongs to.
+// Position of a role thread in its CTA's sequence of (column tile, k unit) pairs: the tile counts over
+// the whole launch, `pi` is the problem the tile belongs to, `step` the distance to the CTA's next tile
+// (1 in the split schedule, the grid size in the whole-tile schedule).
 struct QtWalk {
-  int tile, g, pi, tile_end;
+  int tile, g, pi, tile_end, step;
 };
-__device__ __forceinline__ void qt_walk_init(QtWalk& w, const QtParams& p, int tile0, int g0) {
-  w.tile = tile0; w.g = g0; w.pi = 0;
+__device__ __forceinline__ void qt_walk_init(QtWalk& w, const QtParams& p, int tile0, int g0, int step) {
+  w.tile = tile0; w.g = g0; w.pi = 0; w.step = step;
   while (w.pi + 1 < p.n_problems && tile0 >= p.tile_start[w.pi + 1]) w.pi++;
   w.tile_end = p.tile_start[w.pi + 1];
 }
-// one unit further; true when the walk entered the next problem
+// one unit further; true when the walk entered another problem
 __device__ __forceinline__ bool qt_walk_next(QtWalk& w, const QtParams& p, int G) {
   if (++w.g < G) return false;
   w.g = 0;
-  if (++w.tile < w.tile_end || w.pi + 1 >= p.n_problems) return false;
-  w.pi++;
+  w.tile += w.step;
+  if (w.tile < w.tile_end || w.tile >= p.tiles_total) return false;
+  while (w.pi + 1 < p.n_problems && w.tile >= p.tile_start[w.pi + 1]) w.pi++;
   w.tile_end = p.tile_start[w.pi + 1];
   return true;
 }
@@ -300,30 +329,35 @@ __device__ __forceinline__ void qt_store_rows(const float* v, const QtParams& p,
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
+// global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), counted on an mbarrier
+__device__ __forceinline__ void qt_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // NB: MMA N extent = PLANES digit planes of MB = NB / PLANES rows
 //     (three planes: 16 -> 5 rows, 32 -> 10, 48 -> 16; two planes: 16 -> 8, 32 -> 16).
 template <int NB, int PLANES, int MAXP>
 __global__ void __launch_bounds__(QT_THREADS, 1)
 qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ QtTable<MAXP> table, const QtParams p) {
   constexpr int MB = NB / PLANES;
-  constexpr int X_BYTES = (NB + QT_XROWS_EXTRA) * QT_UNIT_K;     // digit rows, then the row of unit[m,u]
+  constexpr int X_BYTES = NB * QT_UNIT_K;
   constexpr int STAGE_BYTES = QT_W_BYTES + X_BYTES;
   constexpr int STAGES = qt_stages(NB, PLANES);
-  constexpr int NBUF = STAGES;
-  constexpr int SC_SLOTS = 2 * STAGES;             // scale rows in flight: stages + accumulators
-  static_assert(NBUF * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
-  static_assert(SC_SLOTS >= STAGES + NBUF, "a scale slot must outlive its stage and its accumulator");
+  constexpr int NACC = qt_accs(NB);
+  static_assert(NACC * NB <= QT_TMEM_COLS, "accumulators exceed tensor memory");
+  static_assert(STAGES % 2 == 0 && NACC % 2 == 0, "both rings must be even (see the note on parity waits)");
+  static_assert((2 * STAGES + 3 * NACC) * 8 <= QT_BAR_BYTES, "barrier area");
   extern __shared__ uint8_t qt_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qt_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + STAGES * STAGE_BYTES);
-  // Stage s and accumulator s travel together (STAGES == NBUF): a unit's stage is refilled once
-  // the epilogue has read its accumulator, so the MMA thread waits on one barrier per unit and
-  // commits once, which keeps its serial loop short.
-  uint64_t* full = bars;                       // [STAGES] TMA -> MMA
-  uint64_t* acc_full = bars + STAGES;       // [NBUF] MMA -> epilogue
-  uint64_t* acc_empty = acc_full + NBUF;       // [NBUF] epilogue -> TMA producers
-  float* sc_slots = reinterpret_cast<float*>(base + STAGES * STAGE_BYTES + 512);        // [SC_SLOTS][128]
-  float* s_merge = sc_slots + SC_SLOTS * QT_TILE_N;                                     // [MB][128]
+  uint64_t* full = bars;                         // [STAGES] TMA -> MMA: weights and digits of a unit have landed
+  uint64_t* stage_empty = full + STAGES;         // [STAGES] MMA done -> producers: the stage may be refilled
+  uint64_t* acc_full = stage_empty + STAGES;     // [NACC]  MMA done -> epilogue
+  uint64_t* acc_empty = acc_full + NACC;         // [NACC]  epilogue -> MMA issuers and slot producers
+  uint64_t* sc_full = acc_empty + NACC;          // [NACC]  scales and unit[m,u] of a unit have landed
+  uint8_t* slots = base + STAGES * STAGE_BYTES + QT_BAR_BYTES;                             // [NACC][640]
+  float* s_merge = reinterpret_cast<float*>(slots + NACC * QT_SLOT_BYTES);                 // [MB][128]
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_merge + MB * QT_TILE_N);                 // [MB][128] output elements
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
@@ -340,18 +374,24 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
 #endif
   if (tid == 0) QT_STAMP(0);
   const int G = p.units_per_tile;
-  const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
-  const int n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
-  const int tile0 = (int)(u0 / G), g0 = (int)(u0 - (long long)tile0 * G);
+  int n_units, tile0, g0, tile_step;
+  if (p.whole_tiles) {
+    n_units = qt_whole_tiles_of(p, gridDim.x, blockIdx.x) * G;
+    tile0 = blockIdx.x; g0 = 0; tile_step = gridDim.x;
+  } else {
+    const long long u0 = qt_first_unit(p.total_units, gridDim.x, blockIdx.x);
+    n_units = (int)(qt_first_unit(p.total_units, gridDim.x, blockIdx.x + 1) - u0);
+    tile0 = (int)(u0 / G); g0 = (int)(u0 - (long long)tile0 * G); tile_step = 1;
+  }
   const QtProblem* const problems = table.p;
 
   if (warp == QT_TMA_WARP && lane == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&stage_empty[s], 1); }
     fence_barrier_init();
     prefetch_tensormap(&tmap_x);
   }
   if (tid == 0) {
-    for (int b = 0; b < NBUF; b++) mbar_init(&acc_full[b], 1);
+    for (int a = 0; a < NACC; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); mbar_init(&sc_full[a], 1); }
     s_failed = 0;
     fence_barrier_init();
   }
@@ -361,66 +401,66 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
   // Everything above overlaps the kernels before this one in the stream.  The threads that read what
-  // those kernels produce (digits, unit exponents) or write what they may still use (output,
-  // workspace) wait for them here; the weight and scale producers and the MMA issuers, which touch
-  // only weights, shared memory and tensor memory, do not: with a programmatic dependent launch the
-  // first STAGES weight tiles and scale rows are requested while the digit kernel still runs.
+  // those kernels produce (digits, unit[m,u]) or write what they may still use (output, workspace)
+  // wait for them here; the weight producers and the MMA issuers, which touch only weights, shared
+  // memory and tensor memory, do not: with a programmatic dependent launch the first STAGES weight
+  // tiles are requested while the digit kernel still runs.
   // (Requesting them before the barrier above, by one thread, held the whole CTA back and was slower.)
-  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (warp < QT_TMA_WARP || warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid == 0) QT_STAMP(1);
 
-  if (warp == QT_TMA_WARP || warp == QT_TMA2_WARP) {
-    // ------------------------------ TMA producers: weights ----------------------
+  if (warp == QT_TMA_WARP || warp == QT_TMA2_WARP || warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP) {
+    // ------------------------------ TMA producers: weights, digits ----------------------
     // Issuing one tensor copy keeps a thread busy for several hundred cycles, more than half of what
-    // a unit's bytes take to arrive, so every kind of load (weights, digits, scales) has two issuing
-    // threads in different warps.  Work is split by STAGE, not by unit: the even stages belong to one
-    // thread of each role (and to the first epilogue group), the odd stages to the other.  A parity
-    // wait tells two consecutive phases of a barrier apart, not three; a thread that owns a stage
-    // waits for every phase of that stage's barriers in turn and cannot run a phase ahead of them,
-    // whatever order the tiles arrive in.  (With the units split by their own parity and an odd
-    // number of stages, a stage alternated between the two threads, each saw every other phase,
-    // and a thread ahead of a late tile took the previous phase for the one it was waiting for.)
+    // a unit's bytes take to arrive, so every kind of load has two issuing threads in different
+    // warps, one for the even units and one for the odd ones.  The weight producer announces the
+    // stage's bytes; the digit tile counts towards the same barrier.
     if (lane == 0) {
-      const int mine = warp == QT_TMA_WARP ? 0 : 1;
+      const int mine = (warp == QT_TMA_WARP || warp == QT_SIDE_WARP) ? 0 : 1;
+      const bool digits = warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP;
       QtWalk w;
-      qt_walk_init(w, p, tile0, g0);
+      qt_walk_init(w, p, tile0, g0, tile_step);
       const CUtensorMap* map = &problems[w.pi].tmap_w;
-      prefetch_tensormap(map);
+      if (!digits) prefetch_tensormap(map);
       for (int it = 0; it < n_units; it++) {
-        const int s = it % STAGES;
-        if ((s & 1) == mine) {
+        if ((it & 1) == mine) {
+          const int s = it % STAGES;
           if (it >= STAGES) {
-            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+            if (!mbar_wait(&stage_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, digits ? 5 : 1, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
-          mbar_expect_tx(&full[s], STAGE_BYTES + QT_SC_BYTES);
-          tma_load_2d(base + s * STAGE_BYTES, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, w.g * QT_UNIT_K, &full[s]);
+          if (digits) {
+            tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, w.g * QT_UNIT_K, p.digit_row0[w.pi], &full[s]);        // [NB rows][128 k]
+          } else {
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+            tma_load_2d(base + s * STAGE_BYTES, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, w.g * QT_UNIT_K, &full[s]);
+          }
         }
         if (qt_walk_next(w, p, G)) map = &problems[w.pi].tmap_w;
       }
     }
-  } else if (warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP || warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
-    // ------------------------------ TMA producers: digits (with unit[m,u]) and scales ----
-    // Their bytes count towards the same stage barrier; the weight producer announces the total.
-    // The 128 scales of a unit sit in a slot that is reused SC_SLOTS units later, by which time
-    // the epilogue of this unit has read them (it does so before it releases the accumulator,
-    // which the MMA of unit it+STAGES waits for, which the stage reuse of unit it+2*STAGES waits for).
+  } else if (warp == QT_SCALE_WARP || warp == QT_SCALE2_WARP) {
+    // ------------------------------ producers: scales and unit[m,u] ---------------------
+    // A unit's 128 scales and 16 unit[m,u] sit in the slot of the unit's accumulator, which the
+    // epilogue releases together with the accumulator.
     if (lane == 0) {
-      const int mine = (warp == QT_SIDE_WARP || warp == QT_SCALE_WARP) ? 0 : 1;
-      const bool digits = warp == QT_SIDE_WARP || warp == QT_SIDE2_WARP;
+      const int mine = warp == QT_SCALE_WARP ? 0 : 1;
       const int gpr = p.scale_group ? p.scale_group / QT_UNIT_K : 0;    // units per scale row
       QtWalk w;
-      qt_walk_init(w, p, tile0, g0);
+      qt_walk_init(w, p, tile0, g0, tile_step);
       const CUtensorMap* map = &problems[w.pi].tmap_s;
-      if (!digits) prefetch_tensormap(map);
+      prefetch_tensormap(map);
       int srow = gpr ? g0 / gpr : 0, sub = gpr ? g0 - srow * gpr : 0;
       for (int it = 0; it < n_units; it++) {
-        const int s = it % STAGES;
-        if ((s & 1) == mine) {
-          if (it >= STAGES) {
-            if (!mbar_wait(&acc_empty[s], (uint32_t)((it / STAGES - 1) & 1))) { qt_fail(p, 5, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        if ((it & 1) == mine) {
+          const int a = it % NACC;
+          if (it >= NACC) {
+            if (!mbar_wait(&acc_empty[a], (uint32_t)((it / NACC - 1) & 1))) { qt_fail(p, 6, (unsigned)it); atomicExch(&s_failed, 1u); break; }
           }
-          if (digits) tma_load_2d(base + s * STAGE_BYTES + QT_W_BYTES, &tmap_x, w.g * QT_UNIT_K, p.digit_row0[w.pi], &full[s]);        // [NB + 8 rows][128 k]
-          else tma_load_2d(sc_slots + (it % SC_SLOTS) * QT_TILE_N, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, srow, &full[s]);
+          uint8_t* slot = slots + a * QT_SLOT_BYTES;
+          mbar_expect_tx(&sc_full[a], QT_SC_BYTES + QT_UN_BYTES);
+          tma_load_2d(slot, map, (w.tile - p.tile_start[w.pi]) * QT_TILE_N, srow, &sc_full[a]);
+          qt_bulk_load(slot + QT_SC_BYTES, p.unit_rows[w.pi] + (size_t)w.g * 16, QT_UN_BYTES, &sc_full[a]);
         }
         if (gpr && ++sub == gpr) { sub = 0; srow++; }
         if (w.g == G - 1) { srow = 0; sub = 0; }
@@ -429,8 +469,8 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     }
   } else if (warp == QT_MMA_WARP || warp == QT_MMA2_WARP) {
     // ------------------------------ MMA issuers -------------------------------
-    // Issuing a unit (one wait, four MMAs, one commit) costs a single thread several hundred
-    // cycles, about what the unit's bytes take to arrive: two threads share the units by stage.
+    // Issuing a unit (two waits, four MMAs, two commits) costs a single thread several hundred
+    // cycles, about what the unit's bytes take to arrive: two threads take the even and the odd units.
     if (lane == 0) {
       const int mine = warp == QT_MMA_WARP ? 0 : 1;
       // W: MN-major, 128 n bytes per k row, 8-row groups 1024 bytes apart, 32 k rows (4096 bytes) per MMA.
@@ -439,24 +479,27 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
       const uint64_t da0 = smem_desc_sw128(smem_u32(base), QT_W_BYTES, 1024);
       const uint64_t db0 = smem_desc_sw128(smem_u32(base) + QT_W_BYTES, 16, 1024);
       const uint32_t idesc = p.idesc;
-      for (int it = 0; it < n_units; it++) {
-        const int s = it % STAGES;
-        if ((s & 1) != mine) continue;
+      for (int it = mine; it < n_units; it += 2) {
+        const int s = it % STAGES, a = it % NACC;
         if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1))) { qt_fail(p, 3, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        if (it >= NACC) {
+          if (!mbar_wait(&acc_empty[a], (uint32_t)((it / NACC - 1) & 1))) { qt_fail(p, 7, (unsigned)it); atomicExch(&s_failed, 1u); break; }
+        }
         tc_fence_after();
         const uint64_t da = da0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = db0 + (uint64_t)((s * STAGE_BYTES) >> 4);
-        const uint32_t d_tmem = tmem_base + (uint32_t)(s * NB);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * NB);
 #pragma unroll
         for (int j = 0; j < QT_UNIT_K / 32; j++)
           umma_i8(d_tmem, da + (uint64_t)((j * 32 * 128) >> 4), db + (uint64_t)((j * 32) >> 4), idesc, j > 0 ? 1u : 0u);
-        umma_commit(&acc_full[s]);
+        umma_commit(&stage_empty[s]);      // the stage goes back to the producers as soon as the MMAs have read it
+        umma_commit(&acc_full[a]);
       }
     }
   } else {
     // ------------------------------ epilogue (warps 0-7) ----------------------
-    // Two groups of four warps share the units by accumulator (even / odd), so that one group's TMEM
-    // load and barrier round trips hide behind the other's arithmetic.  Each thread owns one output column of the
-    // tile (TMEM lane) and keeps MB running totals; at the end of the CTA's share of a tile the
+    // Two groups of four warps take the even and the odd units, so that one group's TMEM load and
+    // barrier round trips hide behind the other's arithmetic.  Each thread owns one output column of
+    // the tile (TMEM lane) and keeps MB running totals; at the end of the CTA's share of a tile the
     // second group hands its totals to the first through shared memory.
     const int grp = warp >> 2, quarter = warp & 3;
     const int nl = quarter * 32 + lane;             // column within the tile = TMEM lane
@@ -466,27 +509,31 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     for (int m = 0; m < MB; m++) tot[m] = 0.0f;
     bool failed = false;
     QtWalk w;
-    qt_walk_init(w, p, tile0, g0);
+    qt_walk_init(w, p, tile0, g0, tile_step);
     for (int it = 0; it < n_units; it++) {
       // After a timeout this group stops touching the pipeline but keeps walking the units, so that
       // the barriers below still see every thread (the status word reports the failure).
-      const bool own = ((it % NBUF) & 1) == grp;
-      if (own && !failed && !mbar_wait(&acc_full[it % NBUF], (uint32_t)((it / NBUF) & 1))) failed = true;
+      const bool own = (it & 1) == grp;
       if (own && !failed) {
-        const int buf = it % NBUF;
+        const int a = it % NACC;
+        const uint32_t parity = (uint32_t)((it / NACC) & 1);
+        if (!mbar_wait(&sc_full[a], parity) || !mbar_wait(&acc_full[a], parity)) failed = true;
+      }
+      if (own && !failed) {
+        const int a = it % NACC;
         tc_fence_after();
         uint32_t acc[NB];
 #pragma unroll
-        for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(buf * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
-        const float sc = sc_slots[(it % SC_SLOTS) * QT_TILE_N + nl];      // zero beyond column N (TMA fill)
-        const float* s_xun = reinterpret_cast<const float*>(base + buf * STAGE_BYTES + QT_W_BYTES + NB * QT_UNIT_K);   // row NB of the digit tile
+        for (int c = 0; c < NB / 16; c++) tmem_ld16(tlane + (uint32_t)(a * NB + c * 16), *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
+        const float* slot = reinterpret_cast<const float*>(slots + a * QT_SLOT_BYTES);
+        const float sc = slot[nl];                                        // zero beyond column N (TMA fill)
         float un[MB];
 #pragma unroll
-        for (int m = 0; m < MB; m++) un[m] = s_xun[m];
+        for (int m = 0; m < MB; m++) un[m] = slot[QT_TILE_N + m];
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        if (lane == 0) mbar_arrive(&acc_empty[a]);
         // s32 -> f32 through the 1.5 * 2^23 offset (|sum| < 2^22), digits recombined, unit and group scale applied
 #pragma unroll
         for (int m = 0; m < MB; m++) {
@@ -658,8 +705,7 @@ static int qt_nb(const cb_qdense_desc& d) {
 }
 static size_t qt_align(size_t v) { return (v + 255) & ~(size_t)255; }
 static int qt_smem(int nb, int planes) {
-  const int st = qt_stages(nb, planes);
-  return 1024 + st * (QT_W_BYTES + (nb + QT_XROWS_EXTRA) * QT_UNIT_K) + 512 + 2 * st * QT_SC_BYTES + 2 * (nb / planes) * QT_TILE_N * 4;
+  return 1024 + qt_stages(nb, planes) * (QT_W_BYTES + nb * QT_UNIT_K) + qt_tail_bytes(nb, planes);
 }
 
 bool qdense_decode_tc_eligible(const cb_qdense_desc& d, std::string* why) {
@@ -681,7 +727,7 @@ struct QtLayout {
   int nb, mb, planes, n_problems, tiles_total, units_per_tile;
   int tile_start[QT_MAX_PROBLEMS + 1];
   long long total_units;
-  size_t off_counters, off_digits, zero_bytes, off_partials, off_stamps, total;
+  size_t off_counters, off_digits, off_units, zero_bytes, off_partials, off_stamps, total;
 };
 
 static QtLayout qt_layout(const cb_plan* p, int blocks) {
@@ -701,9 +747,10 @@ static QtLayout qt_layout(const cb_plan* p, int blocks) {
   l.total_units = (long long)l.tiles_total * l.units_per_tile;
   l.off_counters = QT_HEADER;
   l.off_digits = qt_align(l.off_counters + (size_t)l.tiles_total * 4);
-  // one block of [NB digit rows + 8][128 * units] per problem: row NB of a block holds unit[m,u], 16 floats at the
-  // start of every unit's 128 bytes.  Counters and digits start as zeros.
-  l.zero_bytes = qt_align(l.off_digits + (size_t)l.n_problems * (l.nb + QT_XROWS_EXTRA) * l.units_per_tile * QT_UNIT_K);
+  // one block of [NB digit rows][128 * units] per problem, then 16 unit[m,u] per problem and unit.
+  // Counters, digits and unit[m,u] start as zeros (rows beyond M are never written).
+  l.off_units = qt_align(l.off_digits + (size_t)l.n_problems * l.nb * l.units_per_tile * QT_UNIT_K);
+  l.zero_bytes = qt_align(l.off_units + (size_t)l.n_problems * l.units_per_tile * QT_UN_BYTES);
   l.off_partials = l.zero_bytes;
   l.off_stamps = qt_align(l.off_partials + (size_t)blocks * 2 * l.mb * QT_TILE_N * 4);
   l.total = l.off_stamps;
@@ -720,16 +767,19 @@ static int qt_finish_plan(cb_plan* p) {
   if (tiles >= (1ll << 30)) return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: too many column tiles for one launch");
   const long long units = tiles * ((d.K + QT_UNIT_K - 1) / QT_UNIT_K);
   p->blocks = (int)std::min<long long>(p->n_sm, units);
-  // Whole tiles per CTA when that keeps enough of the machine streaming: every CTA takes `waves`
-  // consecutive column tiles, so no tile is split and nothing is parked, counted or gathered at the
-  // end.  With one wave three eighths of the SMs are enough (measured: 56 tiles on 148 SMs are still
-  // faster whole, 28 are not — the fewer, longer streams still saturate HBM); with several waves
-  // the grid must cover three quarters of the SMs, else the units are split evenly over all SMs.
+  p->whole_tiles = false;
+  // Whole tiles per CTA when that keeps enough of the machine streaming: every CTA takes an equal
+  // share of the column tiles (give or take one), so no tile is split and nothing is parked, counted
+  // or gathered at the end.  With one wave three eighths of the SMs are enough (measured: 56 tiles on
+  // 148 SMs are still faster whole, 28 are not — the fewer, longer streams still saturate HBM); with
+  // several waves the grid must cover three quarters of the SMs, else the units are split evenly
+  // over all SMs.
   const long long waves = (tiles + p->n_sm - 1) / p->n_sm;
   const long long whole_grid = (tiles + waves - 1) / waves;
-  if (whole_grid * waves == tiles &&
-      ((waves == 1 && tiles * 8 >= (long long)p->n_sm * 3) || (waves > 1 && whole_grid * 4 >= (long long)p->n_sm * 3)))
+  if ((waves == 1 && tiles * 8 >= (long long)p->n_sm * 3) || (waves > 1 && whole_grid * 4 >= (long long)p->n_sm * 3)) {
     p->blocks = (int)whole_grid;
+    p->whole_tiles = true;
+  }
   const QtLayout l = qt_layout(p, p->blocks);
   p->threads = QT_THREADS;
   p->dyn_smem = qt_smem(l.nb, l.planes);
@@ -816,6 +866,7 @@ struct QtArgs {
   QtParams prm;
   QtXList xl;
   int8_t* digits;
+  float* unit_rows;
   int nb, planes, mb, n_problems, units_per_tile;
   bool bf16;
   unsigned long long* xdbg;                // time stamps of the digit kernel (diagnostic builds only)
@@ -831,8 +882,9 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
   a->nb = l.nb; a->planes = l.planes; a->mb = l.mb; a->n_problems = l.n_problems; a->units_per_tile = l.units_per_tile;
   a->bf16 = d.x_dtype == CB_BF16;
   a->digits = (int8_t*)(w8 + l.off_digits);
+  a->unit_rows = (float*)(w8 + l.off_units);
   const uint64_t scale_rows = d.scale_layout == CB_SCALE_KGROUP ? (uint64_t)((d.K + d.block_size - 1) / d.block_size) : 1;
-  const int block_rows = l.nb + QT_XROWS_EXTRA;
+  const int block_rows = l.nb;
   int ii = 0;
   for (int i = 0; i < l.n_problems; i++) {
     const cb_qdense_member& m = p->group[i];
@@ -860,6 +912,7 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
     while (xi < a->xl.n && a->xl.x[xi] != x) xi++;
     if (xi == a->xl.n) a->xl.x[a->xl.n++] = x;
     a->prm.digit_row0[i] = xi * block_rows;
+    a->prm.unit_rows[i] = reinterpret_cast<const float*>(w8 + l.off_units) + (size_t)xi * l.units_per_tile * 16;
   }
   CB_TRY(qt_encode_2d(&a->tmap_x, a->digits, 1, (uint64_t)l.units_per_tile * QT_UNIT_K, (uint64_t)l.n_problems * block_rows,
                       QT_UNIT_K, (uint32_t)block_rows));
@@ -872,6 +925,8 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
   prm.n_outs = g;
   for (int i = 0; i <= QT_MAX_PROBLEMS; i++) prm.tile_start[i] = l.tile_start[i];
   prm.units_per_tile = l.units_per_tile;
+  prm.tiles_total = l.tiles_total;
+  prm.whole_tiles = p->whole_tiles ? 1 : 0;
   prm.total_units = l.total_units;
   prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
   prm.out_bf16 = a->bf16 ? 1 : 0;
@@ -930,9 +985,9 @@ static int qt_launch_digits(const QtArgs& a, int M, int K, cudaStream_t s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
 #ifdef CB_QT_STAMPS
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits, a.xdbg));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits, a.unit_rows, a.xdbg));
 #else
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_xdigits_kernel<XT, PLANES>, a.xl, M, K, a.nb, a.units_per_tile, a.digits, a.unit_rows));
 #endif
   return CB_OK;
 }

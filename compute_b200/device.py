@@ -124,6 +124,8 @@ def peer_wait(dev: int, flags: int, n_flags: int, target: int, status_word: int,
 
 
 REDUCE_SUM, REDUCE_PRODUCT, REDUCE_MAX, REDUCE_MIN = range(4)
+BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_MAX, BIN_MIN = range(6)
+UN_NEG, UN_RSQRT, UN_SQRT, UN_EXP, UN_LOGISTIC, UN_TANH = range(6)
 COMM_ID_BYTES = 128
 
 
@@ -282,6 +284,42 @@ class Plan:
     def layernorm(cls, dtype, rows, norm_size, epsilon=1e-5, has_gamma=False, has_beta=False, dev=0) -> "Plan":
         h = C.c_void_p()
         check(_lib.load().cb_plan_layernorm(dev, dtype, rows, norm_size, float(epsilon), int(has_gamma), int(has_beta), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def binary(cls, op, dtype, lhs_dims, rhs_dims, dev=0) -> "Plan":
+        """Element-wise binary op; both shapes given with the same rank, dimensions equal or 1 (broadcast)."""
+        r = len(lhs_dims)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_binary(dev, op, dtype, r, (C.c_int64 * max(r, 1))(*lhs_dims), (C.c_int64 * max(r, 1))(*rhs_dims), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def unary(cls, op, dtype, n, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_unary(dev, op, dtype, n, C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def reduce(cls, op, dtype, dims, reduced_axes, dev=0) -> "Plan":
+        r = len(dims)
+        flags = [1 if a in set(reduced_axes) else 0 for a in range(r)]
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_reduce(dev, op, dtype, r, (C.c_int64 * max(r, 1))(*dims), (C.c_int32 * max(r, 1))(*flags), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def broadcast_in_dim(cls, dtype, dims, out_dims, broadcast_axes, dev=0) -> "Plan":
+        r, ro = len(dims), len(out_dims)
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_broadcast_in_dim(dev, dtype, r, (C.c_int64 * max(r, 1))(*dims), ro, (C.c_int64 * max(ro, 1))(*out_dims),
+                                                   (C.c_int32 * max(r, 1))(*broadcast_axes), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def rms_norm(cls, dtype, rows, row_size, epsilon=1e-5, has_gamma=True, dev=0) -> "Plan":
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_rms_norm(dev, dtype, rows, row_size, float(epsilon), int(has_gamma), C.byref(h)))
         return cls(h, dev)
 
     @classmethod

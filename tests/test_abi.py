@@ -40,7 +40,7 @@ def test_plans_select_kernels_by_shape_and_dtype():
     assert dv.Plan.qdense(8, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n16p2_i8")
     assert dv.Plan.qdense(16, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n32p2_i8")
     assert dv.Plan.qdense(16, 4096, 14336, dv.F32, dv.I8, dv.SCALE_KGROUP, 128).kernel_name.endswith("_n48_i8")
-    # a group of independent projections is one launch: 8 x 112 column tiles as 128 CTAs of 7 whole tiles
+    # a group of independent projections is one launch: 8 x 112 column tiles on 128 CTAs, 7 whole tiles each (c, c + 128, ...)
     g = dv.Plan.qdense_group(16, 4096, [(14336, False, dv.ACT_SILU)] * 8, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128)
     assert g.kernel_name == "qdense_decode_tc_bf16_n32p2_i8_x8" and g.blocks == 128
     # an 8-way column shard of the same step: 8 x 14 tiles, one whole tile per CTA

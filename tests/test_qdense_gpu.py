@@ -367,15 +367,17 @@ def test_decode_group_matches_oracle_and_single_plans(x_dtype, bound):
             assert max_abs_normalised(got, single) < 1e-6
 
 
-def test_decode_group_full_size_step():
-    """The benchmark's step as one launch: 4 distinct 4096 x 14336 layers at M = 16 (4 x 112 column tiles, 112 CTAs of
-    4 whole tiles).  Every layer agrees with its own single launch to one bfloat16 step of the largest value (the two
+@pytest.mark.parametrize("L,M,blocks", [(4, 16, 112), (6, 4, 135)])
+def test_decode_group_full_size_step(L, M, blocks):
+    """The benchmark's step as one launch: L distinct 4096 x 14336 layers (4 x 112 column tiles on 112 CTAs, four
+    tiles each; 6 x 112 tiles on 135 CTAs, five tiles each but for three CTAs with four).  CTA c takes the tiles
+    c, c + grid, ...  Every layer agrees with its own single launch to one bfloat16 step of the largest value (the two
     epilogue groups share a tile's k units by pipeline stage, so the order of the float32 additions depends on where
     the tile starts in a CTA's run) and the group launch is repeatable bit for bit."""
-    M, K, N, L = 16, 4096, 14336, 4
+    K, N = 4096, 14336
     rng = np.random.default_rng(5)
     plan = dv.Plan.qdense_group(M, K, [(N, False, dv.ACT_SILU)] * L, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128)
-    assert plan.blocks == 112
+    assert plan.blocks == blocks
     single = dv.Plan.qdense(M, K, N, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128, False, False, dv.ACT_SILU)
     st = dv.Stream(0)
     ins, outs, ref_outs, keep = [], [], [], []
