@@ -23,7 +23,9 @@ from ._lib import BackendError, ErrNotImplemented, check
 OP_PARAMETER, OP_CONSTANT, OP_DOT_GENERAL = 1, 2, 32
 OP_FUSED_SOFTMAX, OP_FUSED_LAYER_NORM, OP_FUSED_GELU, OP_FUSED_DENSE = 116, 117, 118, 119
 OP_FUSED_SDPA, OP_FUSED_ATTENTION_QKV_PROJECTION, OP_FUSED_QUANTIZED_DENSE = 120, 122, 123
-OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 116: "FusedSoftmax", 117: "FusedLayerNorm", 118: "FusedGelu",
+OP_ALL_REDUCE, OP_ALL_GATHER = 112, 114
+REDUCE_OP_SUM, REDUCE_OP_PRODUCT, REDUCE_OP_MAX, REDUCE_OP_MIN = 1, 2, 3, 4      # compute.ReduceOpType (standard_ops.go:65-84)
+OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 112: "AllReduce", 114: "AllGather", 116: "FusedSoftmax", 117: "FusedLayerNorm", 118: "FusedGelu",
             119: "FusedDense", 120: "FusedScaledDotProductAttention", 122: "FusedAttentionQKVProjection", 123: "FusedQuantizedDense"}
 
 # compute.QuantizationScheme (fused_ops.go:81-98)
@@ -82,6 +84,26 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_fused_quantized_dense_ggml": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_sdpa": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(_SdpaOptions), C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_not_implemented": ([C.c_void_p, C.c_char_p], C.c_int),
+    "cbg_fn_add": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_sub": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_mul": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_div": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_max": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_min": ([C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_neg": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_rsqrt": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_sqrt": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_exp": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_logistic": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_tanh": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_reduce_sum": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_reduce_max": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_broadcast_in_dim": ([C.c_void_p, C.c_void_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int), C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_all_reduce": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_all_gather": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_parameter_sharded": ([C.c_void_p, C.c_char_p, C.c_int32, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.c_int,
+                                 C.POINTER(C.c_char_p), C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_exec_input_sharding": ([C.c_void_p, C.c_int, C.c_char_p, C.c_size_t], C.c_int),
     "cbg_exec_num_inputs": ([C.c_void_p], C.c_int),
     "cbg_exec_num_outputs": ([C.c_void_p], C.c_int),
     "cbg_exec_input_info": ([C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
@@ -191,6 +213,38 @@ class ScaledDotProductAttentionConfig:
     Mask: Optional["Value"] = None
 
 
+@dataclass
+class DeviceMesh:
+    """distributed.DeviceMesh (distributed/devicemesh.go:23-110): named axes over the devices of a computation."""
+    AxesNames: Tuple[str, ...]
+    AxesSizes: Tuple[int, ...]
+
+    def NumDevices(self) -> int:
+        return int(np.prod(self.AxesSizes, dtype=np.int64)) if self.AxesSizes else 1
+
+    def ComputeReplicaGroups(self, axes: Sequence[str]) -> List[List[int]]:
+        """Groups of device indices that differ only along `axes` (distributed/devicemesh.go:224-293): the devices are
+        numbered row-major over the mesh; every group walks the listed axes (in mesh order) with the others fixed."""
+        for a in axes:
+            if a not in self.AxesNames:
+                raise BackendError(_lib.ERR_INVALID_ARG, f"mesh axis {a!r} not found in the mesh axes {list(self.AxesNames)}")
+        if len(set(axes)) != len(axes):
+            raise BackendError(_lib.ERR_INVALID_ARG, f"mesh axes {list(axes)} are repeated")
+        ids = np.arange(self.NumDevices()).reshape(self.AxesSizes)
+        red = [i for i, n in enumerate(self.AxesNames) if n in axes]
+        keep = [i for i in range(len(self.AxesNames)) if i not in red]
+        moved = np.transpose(ids, keep + red).reshape(-1, int(np.prod([self.AxesSizes[i] for i in red], dtype=np.int64)) if red else 1)
+        return [list(map(int, row)) for row in moved]
+
+
+@dataclass
+class ShardingSpec:
+    """distributed.ShardingSpec (distributed/shardingspec.go:43-110): per tensor axis the mesh axes it is sharded over
+    (an empty tuple = replicated; missing trailing axes are replicated)."""
+    Mesh: DeviceMesh
+    Axes: Tuple[Tuple[str, ...], ...] = ()
+
+
 class Value:
     """compute.Value: an opaque node of a function under construction."""
 
@@ -265,11 +319,16 @@ class Function:
     def _v(self, h) -> Value:
         return Value(h, self)
 
-    def Parameter(self, name: str, shape: Shape, sharding=None) -> Value:
-        if sharding is not None:
-            raise ErrNotImplemented(_lib.ERR_NOT_IMPLEMENTED, "Parameter: sharding specs are not implemented by the cuda backend")
+    def Parameter(self, name: str, shape: Shape, sharding: Optional[ShardingSpec] = None) -> Value:
         h = C.c_void_p()
-        check(_g().cbg_fn_parameter(self.handle, name.encode(), shape.dtype, shape.rank(), _i64(shape.dimensions), C.byref(h)))
+        if sharding is None:
+            check(_g().cbg_fn_parameter(self.handle, name.encode(), shape.dtype, shape.rank(), _i64(shape.dimensions), C.byref(h)))
+            return self._v(h)
+        mesh = sharding.Mesh
+        names = (C.c_char_p * max(len(mesh.AxesNames), 1))(*[n.encode() for n in mesh.AxesNames])
+        specs = (C.c_char_p * max(len(sharding.Axes), 1))(*[",".join(a).encode() for a in sharding.Axes])
+        check(_g().cbg_fn_parameter_sharded(self.handle, name.encode(), shape.dtype, shape.rank(), _i64(shape.dimensions), names,
+                                            _ints(mesh.AxesSizes), len(mesh.AxesNames), specs, len(sharding.Axes), C.byref(h)))
         return self._v(h)
 
     def Constant(self, flat, *dims: int, dtype: Optional[int] = None) -> Value:
@@ -280,6 +339,8 @@ class Function:
             dtype = rev[a.dtype]
         h = C.c_void_p()
         n = int(np.prod(dims, dtype=np.int64)) if dims else 1
+        if dtype in (dv.I4, dv.U4):
+            n = (n + 1) // 2
         if a.size != n:
             raise BackendError(_lib.ERR_INVALID_ARG, f"Constant: flat has {a.size} elements, dimensions {list(dims)} need {n}")
         check(_g().cbg_fn_constant(self.handle, a.ctypes.data, dtype, len(dims), _i64(dims), C.byref(h)))
@@ -332,6 +393,68 @@ class Function:
         h = C.c_void_p()
         check(_g().cbg_fn_transpose(self.handle, x.handle, _ints(permutation), C.byref(h)))
         return self._v(h)
+
+    # ---- element-wise / reduce ops a decoder block needs (float dtypes; not advertised in Capabilities)
+    def _binary(self, name: str, lhs: Value, rhs: Value) -> Value:
+        h = C.c_void_p()
+        check(getattr(_g(), "cbg_fn_" + name)(self.handle, lhs.handle, rhs.handle, C.byref(h)))
+        return self._v(h)
+
+    def _unary(self, name: str, x: Value) -> Value:
+        h = C.c_void_p()
+        check(getattr(_g(), "cbg_fn_" + name)(self.handle, x.handle, C.byref(h)))
+        return self._v(h)
+
+    def Add(self, lhs: Value, rhs: Value) -> Value: return self._binary("add", lhs, rhs)
+    def Sub(self, lhs: Value, rhs: Value) -> Value: return self._binary("sub", lhs, rhs)
+    def Mul(self, lhs: Value, rhs: Value) -> Value: return self._binary("mul", lhs, rhs)
+    def Div(self, lhs: Value, rhs: Value) -> Value: return self._binary("div", lhs, rhs)
+    def Max(self, lhs: Value, rhs: Value) -> Value: return self._binary("max", lhs, rhs)
+    def Min(self, lhs: Value, rhs: Value) -> Value: return self._binary("min", lhs, rhs)
+    def Neg(self, x: Value) -> Value: return self._unary("neg", x)
+    def Rsqrt(self, x: Value) -> Value: return self._unary("rsqrt", x)
+    def Sqrt(self, x: Value) -> Value: return self._unary("sqrt", x)
+    def Exp(self, x: Value) -> Value: return self._unary("exp", x)
+    def Logistic(self, x: Value) -> Value: return self._unary("logistic", x)
+    def Tanh(self, x: Value) -> Value: return self._unary("tanh", x)
+
+    def ReduceSum(self, x: Value, *axes: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_reduce_sum(self.handle, x.handle, _ints(axes), len(axes), C.byref(h)))
+        return self._v(h)
+
+    def ReduceMax(self, x: Value, *axes: int) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_reduce_max(self.handle, x.handle, _ints(axes), len(axes), C.byref(h)))
+        return self._v(h)
+
+    def BroadcastInDim(self, x: Value, outputShape: Shape, broadcastAxes: Sequence[int]) -> Value:
+        h = C.c_void_p()
+        check(_g().cbg_fn_broadcast_in_dim(self.handle, x.handle, outputShape.dtype, outputShape.rank(), _i64(outputShape.dimensions),
+                                           _ints(broadcastAxes), C.byref(h)))
+        return self._v(h)
+
+    # ---- CollectiveOps (collectiveops.go:10-39)
+    @staticmethod
+    def _groups(replicaGroups):
+        groups = [list(g) for g in (replicaGroups or [])]
+        flat = [r for g in groups for r in g]
+        return _ints(flat), _ints([len(g) for g in groups]), len(groups)
+
+    def AllReduce(self, operands: Sequence[Value], reductionType: int, replicaGroups=None) -> List[Value]:
+        ops = (C.c_void_p * max(len(operands), 1))(*[o.handle for o in operands])
+        outs = (C.c_void_p * max(len(operands), 1))()
+        flat, sizes, n = self._groups(replicaGroups)
+        check(_g().cbg_fn_all_reduce(self.handle, ops, len(operands), reductionType, flat, sizes, n, outs))
+        return [self._v(C.c_void_p(outs[i])) for i in range(len(operands))]
+
+    def AllGather(self, operands: Sequence[Value], gatherAxis: int, replicaGroups=None) -> List[Value]:
+        """The extension the interface sketches (collectiveops.go:31-32)."""
+        ops = (C.c_void_p * max(len(operands), 1))(*[o.handle for o in operands])
+        outs = (C.c_void_p * max(len(operands), 1))()
+        flat, sizes, n = self._groups(replicaGroups)
+        check(_g().cbg_fn_all_gather(self.handle, ops, len(operands), gatherAxis, flat, sizes, n, outs))
+        return [self._v(C.c_void_p(outs[i])) for i in range(len(operands))]
 
     # ---- FusedOps on the path
     def FusedSoftmax(self, x: Value, axis: int) -> Value:
@@ -439,6 +562,11 @@ class Executable:
             check(_g().cbg_exec_output_info(self.handle, i, C.byref(dt), C.byref(rk), dims))
             out.append(Shape(dt.value, tuple(dims[j] for j in range(rk.value))))
         return out
+
+    def InputSharding(self, i: int) -> str:
+        buf = C.create_string_buffer(512)
+        check(_g().cbg_exec_input_sharding(self.handle, i, buf, 512))
+        return buf.value.decode()
 
     def KernelNames(self) -> List[str]:
         buf = C.create_string_buffer(4096)
@@ -555,9 +683,14 @@ class Backend:
 
     # ---- DataInterface
     def BufferFromFlatData(self, deviceNum: int, flat: np.ndarray, shape: Shape) -> Buffer:
-        a = np.ascontiguousarray(flat, dv.NP_CARRIER.get(shape.dtype))
-        if a.size != shape.size():
-            raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} elements, shape needs {shape.size()}")
+        if shape.dtype in (dv.I4, dv.U4):        # packed sub-byte dtypes come as bytes, two elements each (buffer.go:47-49)
+            a = np.ascontiguousarray(flat, np.uint8)
+            if a.size != (shape.size() + 1) // 2:
+                raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} bytes, packed shape needs {(shape.size() + 1) // 2}")
+        else:
+            a = np.ascontiguousarray(flat, dv.NP_CARRIER.get(shape.dtype))
+            if a.size != shape.size():
+                raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} elements, shape needs {shape.size()}")
         h = C.c_void_p()
         check(_g().cbg_buffer_from_flat(self.handle, deviceNum, a.ctypes.data, shape.dtype, shape.rank(),
                                         _i64(shape.dimensions), C.byref(h)))

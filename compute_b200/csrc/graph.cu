@@ -15,6 +15,8 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
+#include <cmath>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -30,7 +32,8 @@ struct Shape {
   int32_t dtype = 0;
   std::vector<int64_t> dims;
   int64_t size() const { int64_t n = 1; for (auto d : dims) n *= d; return n; }
-  size_t bytes() const { return (size_t)size() * cb::dtype_size(dtype); }
+  // Int4 / Uint4 are packed two per byte over the flat element order (dtypes/dtype_enum.go:91-116)
+  size_t bytes() const { return (dtype == CB_I4 || dtype == CB_U4) ? ((size_t)size() + 1) / 2 : (size_t)size() * cb::dtype_size(dtype); }
   bool operator==(const Shape& o) const { return dtype == o.dtype && dims == o.dims; }
   std::string str() const {
     std::ostringstream s;
@@ -42,10 +45,13 @@ struct Shape {
 };
 
 enum NodeKind { N_PARAM, N_CONST, N_DOT, N_QDENSE, N_SDPA, N_RESHAPE, N_SLICE, N_IOTA, N_CONVERT, N_TRANSPOSE,
-                N_GELU, N_SOFTMAX, N_LAYERNORM, N_COLS_BIAS };
+                N_GELU, N_SOFTMAX, N_LAYERNORM, N_COLS_BIAS, N_BINARY, N_UNARY, N_REDUCE, N_BROADCAST, N_RMSNORM,
+                N_ALLREDUCE, N_ALLGATHER };
 
 bool is_float(int d) { return d == CB_F16 || d == CB_F32 || d == CB_F64 || d == CB_BF16 || d == CB_F8E4M3FN || d == CB_F8E5M2; }
 bool is_half(int d) { return d == CB_F16 || d == CB_BF16; }
+// dtypes a buffer, parameter or constant may have: the plain ones, and packed 4-bit weights
+bool storable(int d) { return (cb::dtype_size(d) != 0 && d <= CB_BF16) || d == CB_I4 || d == CB_U4; }
 
 // Size-bucketed pool of device allocations (the role of Backend.GetBuffer / PutBuffer,
 // internal/gobackend/buffers.go:117-180): cudaMalloc / cudaFree stay off the Execute path.
@@ -86,8 +92,35 @@ struct DevicePool {
 
 }  // namespace
 
+// Page-locked staging buffers for BufferFromFlatData / ToFlatData: the copy to or from the caller's
+// (pageable) slice is a plain memcpy, the transfer itself runs on a stream of this library and never
+// touches the default stream.
+struct PinnedPool {
+  std::mutex mu;
+  std::map<size_t, std::vector<void*>> free_lists;
+  int get(size_t bytes, void** p, size_t* cap) {
+    size_t b = 4096;
+    while (b < bytes) b <<= 1;
+    *cap = b;
+    {
+      std::lock_guard<std::mutex> l(mu);
+      auto it = free_lists.find(b);
+      if (it != free_lists.end() && !it->second.empty()) { *p = it->second.back(); it->second.pop_back(); return CB_OK; }
+    }
+    return cb_host_alloc(b, p);
+  }
+  void put(size_t cap, void* p) { std::lock_guard<std::mutex> l(mu); free_lists[cap].push_back(p); }
+  void release_all() {
+    std::lock_guard<std::mutex> l(mu);
+    for (auto& kv : free_lists) for (void* p : kv.second) cb_host_free(p);
+    free_lists.clear();
+  }
+};
+constexpr size_t PINNED_STAGING_MAX = (size_t)16 << 20;     // larger transfers go directly (one-off uploads of weights)
+
 struct cbg_backend {
   int n_devices = 0;
+  PinnedPool pinned;
   bool fallback_only = false;
   std::atomic<bool> finalized{false};
   std::string name = "cuda", description;
@@ -131,8 +164,12 @@ struct cbg_value {
   std::vector<int32_t> perm;
   int axis = 0;
   int64_t small_dims[4] = {0, 0, 0, 0};   // softmax [outer, axis, inner]; layer norm [rows, norm size, 1]; column slice [rows, total, first, width]
-  double epsilon = 0.0;               // layer norm
-  int flags = 0;                      // gelu: exact; layer norm: 1 gamma, 2 beta
+  double epsilon = 0.0;               // layer norm, rms norm
+  int flags = 0;                      // gelu: exact; layer norm: 1 gamma, 2 beta; rms norm: 1 gamma
+  int op = 0;                         // binary / unary / reduce op; AllReduce: cb_reduce_op; AllGather: the gather axis
+  std::vector<int32_t> axis_flags;    // reduce: 1 for every reduced axis; BroadcastInDim: the broadcast axes
+  std::vector<std::vector<int>> replica_groups;   // collectives: indices into the device assignment
+  std::string sharding;               // Parameter: the ShardingSpec it was declared with (text form), or empty
 };
 
 struct cbg_function {
@@ -151,15 +188,22 @@ struct cbg_builder {
   std::vector<int> assignment;
 };
 
+struct DevPlans {                             // the launch plan of one device
+  std::vector<cb_plan*> plans;                // per node (NULL for parameters, constants, reshapes, skipped nodes)
+  std::vector<size_t> ws_bytes;
+};
+
 struct cbg_exec {
   cbg_backend* be = nullptr;
   std::string name;
   std::unique_ptr<cbg_function> fn;          // owns the nodes
-  std::vector<cb_plan*> plans;               // per node (NULL for param/const/reshape)
-  std::vector<size_t> ws_bytes;
+  std::vector<char> live;                    // per node: its value is needed (outputs and their operands)
+  std::vector<int> group_of;                 // per node: -1, or the index of the grouped launch it belongs to
+  std::vector<std::vector<int>> groups;      // grouped FusedQuantizedDense launches: member nodes; the first member launches
   int replicas = 1;
   std::vector<int> assignment;
   std::mutex mu;
+  std::map<int, DevPlans> dev_plans;                                 // device -> plans (built at Compile for the assigned devices)
   std::map<int, std::vector<void*>> const_dev;                       // device -> per-node constant copy
   std::map<int, std::vector<std::vector<void*>>> idle_ws;            // device -> sets of prepared workspaces
   bool finalized = false;
@@ -242,6 +286,31 @@ cbg_value* reshape_node(cbg_function* f, cbg_value* x, const std::vector<int64_t
   return add_node(f, N_RESHAPE, s, {x});
 }
 
+// host <-> device through a pinned staging buffer and a pooled stream (to_device: host -> device)
+int staged_copy(cbg_backend* be, int dev, void* dptr, void* host, size_t bytes, bool to_device) {
+  if (bytes == 0) return CB_OK;
+  if (bytes > PINNED_STAGING_MAX) return to_device ? cb_h2d(dev, dptr, host, bytes, nullptr) : cb_d2h(dev, host, dptr, bytes, nullptr);
+  void* pin = nullptr;
+  size_t cap = 0;
+  CB_TRY(be->pinned.get(bytes, &pin, &cap));
+  cb_stream s = nullptr;
+  int st = be->get_stream(dev, &s);
+  if (st == CB_OK) {
+    if (to_device) {
+      memcpy(pin, host, bytes);
+      st = cb_h2d(dev, dptr, pin, bytes, s);
+      if (st == CB_OK) st = cb_stream_sync(dev, s);
+    } else {
+      st = cb_d2h(dev, pin, dptr, bytes, s);
+      if (st == CB_OK) st = cb_stream_sync(dev, s);
+      if (st == CB_OK) memcpy(host, pin, bytes);
+    }
+    be->put_stream(dev, s);
+  }
+  be->pinned.put(cap, pin);
+  return st;
+}
+
 }  // namespace
 
 extern "C" {
@@ -279,12 +348,13 @@ int cbg_backend_num_devices(const cbg_backend* b) { return b ? b->n_devices : 0;
 int cbg_backend_device_description(const cbg_backend* b, int dev, char* buf, size_t n) { return cb_device_desc(dev, buf, n); }
 
 int cbg_backend_capabilities(const cbg_backend* b, int32_t* ops, int* n_ops, int32_t* dtypes, int* n_dtypes) {
-  // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32, FusedSoftmax 116, FusedLayerNorm 117,
-  // FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120, FusedAttentionQKVProjection 122,
-  // FusedQuantizedDense 123.  The helper ops
-  // (Reshape, Slice, Iota, ConvertDType, Transpose) exist to serve DotGeneral and are
-  // deliberately not advertised.
-  static const int32_t k_ops[] = {1, 2, 32, 116, 117, 118, 119, 120, 122, 123};
+  // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32, AllReduce 112, AllGather 114, FusedSoftmax 116,
+  // FusedLayerNorm 117, FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120,
+  // FusedAttentionQKVProjection 122, FusedQuantizedDense 123.  The helper ops (Reshape, Slice, Iota, ConvertDType,
+  // Transpose) exist to serve DotGeneral, and the element-wise / reduce ops to serve a decoder block, for the float
+  // dtypes only: they are deliberately not advertised, so that the compliance suite's per-op sweeps over every dtype
+  // skip them.
+  static const int32_t k_ops[] = {1, 2, 32, 112, 114, 116, 117, 118, 119, 120, 122, 123};
   static const int32_t k_dtypes[] = {CB_BOOL, CB_I8, CB_I32, CB_I64, CB_U8, CB_F16, CB_F32, CB_F64, CB_BF16};
   const int no = (int)(sizeof(k_ops) / sizeof(k_ops[0])), nd = (int)(sizeof(k_dtypes) / sizeof(k_dtypes[0]));
   if (ops && n_ops) for (int i = 0; i < std::min(*n_ops, no); i++) ops[i] = k_ops[i];
@@ -304,6 +374,7 @@ int cbg_backend_finalize(cbg_backend* b) {
     for (cb_stream s : b->streams[d]) cb_stream_destroy(d, s);
     b->streams[d].clear();
   }
+  b->pinned.release_all();
   return CB_OK;
 }
 
@@ -322,7 +393,7 @@ int cbg_buffer_from_flat(cbg_backend* b, int dev, const void* host_flat, int32_t
   *buffer = nullptr;
   if (b->finalized.load()) return fail(CB_ERR_INVALID_ARG, "BufferFromFlatData: backend has been finalized");
   if (dev < 0 || dev >= b->n_devices) return fail(CB_ERR_INVALID_ARG, "BufferFromFlatData: device %d out of range [0,%d)", dev, b->n_devices);
-  if (cb::dtype_size(dtype) == 0 || dtype > CB_BF16) return fail(CB_ERR_NOT_IMPLEMENTED, "BufferFromFlatData: dtype %s is not supported", cb::dtype_name(dtype));
+  if (!storable(dtype)) return fail(CB_ERR_NOT_IMPLEMENTED, "BufferFromFlatData: dtype %s is not supported", cb::dtype_name(dtype));
   auto buf = std::make_unique<cbg_buffer>();
   buf->be = b;
   buf->dev = dev;
@@ -330,7 +401,7 @@ int cbg_buffer_from_flat(cbg_backend* b, int dev, const void* host_flat, int32_t
   CB_TRY(make_dims("BufferFromFlatData", rank, dims, &buf->shape.dims));
   if (buf->shape.bytes() > 0 && !host_flat) return fail(CB_ERR_INVALID_ARG, "BufferFromFlatData: flat data is NULL");
   CB_TRY(b->pools[dev]->get(dev, buf->shape.bytes(), &buf->ptr));
-  int st = cb_h2d(dev, buf->ptr, host_flat, buf->shape.bytes(), nullptr);
+  int st = staged_copy(b, dev, buf->ptr, const_cast<void*>(host_flat), buf->shape.bytes(), true);
   if (st != CB_OK) { b->pools[dev]->put(buf->shape.bytes(), buf->ptr); return st; }
   *buffer = buf.release();
   return CB_OK;
@@ -362,7 +433,7 @@ int cbg_buffer_to_flat(const cbg_buffer* buf, void* host_flat, size_t n_bytes) {
   CB_TRY(check_buffer(buf, "Buffer.ToFlatData"));
   if (n_bytes != buf->shape.bytes())
     return fail(CB_ERR_INVALID_ARG, "Buffer.ToFlatData: flat has %zu bytes, buffer %s needs %zu", n_bytes, buf->shape.str().c_str(), buf->shape.bytes());
-  return cb_d2h(buf->dev, host_flat, buf->ptr, n_bytes, nullptr);
+  return staged_copy(buf->be, buf->dev, buf->ptr, host_flat, n_bytes, false);
 }
 
 int cbg_buffer_copy_to_device(const cbg_buffer* buf, int dev, cbg_buffer** out) {
@@ -442,7 +513,7 @@ int cbg_builder_free(cbg_builder* bld) { delete bld; return CB_OK; }
 // ---------------------------------------------------------------- Function
 int cbg_fn_parameter(cbg_function* f, const char* name, int32_t dtype, int rank, const int64_t* dims, cbg_value** v) {
   CB_TRY(check_fn(f, "Parameter"));
-  if (cb::dtype_size(dtype) == 0 || dtype > CB_BF16) return fail(CB_ERR_NOT_IMPLEMENTED, "Parameter: dtype %s is not supported", cb::dtype_name(dtype));
+  if (!storable(dtype)) return fail(CB_ERR_NOT_IMPLEMENTED, "Parameter: dtype %s is not supported", cb::dtype_name(dtype));
   Shape s;
   s.dtype = dtype;
   CB_TRY(make_dims("Parameter", rank, dims, &s.dims));
@@ -456,7 +527,7 @@ int cbg_fn_parameter(cbg_function* f, const char* name, int32_t dtype, int rank,
 
 int cbg_fn_constant(cbg_function* f, const void* host_flat, int32_t dtype, int rank, const int64_t* dims, cbg_value** v) {
   CB_TRY(check_fn(f, "Constant"));
-  if (cb::dtype_size(dtype) == 0 || dtype > CB_BF16) return fail(CB_ERR_NOT_IMPLEMENTED, "Constant: dtype %s is not supported", cb::dtype_name(dtype));
+  if (!storable(dtype)) return fail(CB_ERR_NOT_IMPLEMENTED, "Constant: dtype %s is not supported", cb::dtype_name(dtype));
   Shape s;
   s.dtype = dtype;
   CB_TRY(make_dims("Constant", rank, dims, &s.dims));
@@ -887,8 +958,10 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
   if (weights->shape.dims.size() != 2 || weights->shape.dims[0] != K)
     return fail(CB_ERR_INVALID_ARG, "%s: weights must be [%lld, N], got %s", op, (long long)K, weights->shape.str().c_str());
   const int64_t N = weights->shape.dims[1];
-  if (weights->shape.dtype != CB_I8 && weights->shape.dtype != CB_U8)
-    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: %s unsupported weight type %s", op, scheme == 1 ? "NF4" : "Linear", cb::dtype_name(weights->shape.dtype));
+  // Int8 / Uint8, and for the Linear scheme the packed Int4 / Uint4 the reference unpacks first (quantizeddense.go:383-390)
+  const int wd = weights->shape.dtype;
+  if (wd != CB_I8 && wd != CB_U8 && !(scheme == 0 && (wd == CB_I4 || wd == CB_U4)))
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: %s unsupported weight type %s", op, scheme == 1 ? "NF4" : "Linear", cb::dtype_name(wd));
   // NF4 uses a fixed lookup table and takes no zero points (quantizeddense.go:126-129)
   if (scheme == 1 && zero_point) return fail(CB_ERR_INVALID_ARG, "%s: ZeroPoint must be nil for NF4 quantization scheme", op);
   if (block_size <= 0) return fail(CB_ERR_INVALID_ARG, "%s: BlockSize must be positive, got %lld", op, (long long)block_size);
@@ -910,6 +983,28 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
   if (bias && (bias->shape.dtype != CB_F32 || bias->shape.dims != std::vector<int64_t>{N}))
     return fail(CB_ERR_INVALID_ARG, "%s: bias must be (Float32)[%lld], got %s", op, (long long)N, bias->shape.str().c_str());
   if (activation < CB_ACT_NONE || activation > CB_ACT_TANH) return fail(CB_ERR_INVALID_ARG, "%s: unknown activation %d", op, activation);
+  // The reference expresses per-channel and K-group scales as [K, N] with BlockSize 1.  When such a scale is a
+  // Constant whose rows repeat within groups of g rows, it is folded to the compact layout ([N], or [K/g, N]):
+  // the same arithmetic element by element, and the layout the streaming kernels read.
+  if (layout == CB_SCALE_REF && block_size == 1 && !zero_point && scheme == 0 && scale->kind == N_CONST &&
+      (wd == CB_I8 || wd == CB_U8) && K > 1 && !f->builder->be->fallback_only) {
+    const float* sd = reinterpret_cast<const float*>(scale->const_data.data());
+    int64_t g = K;                                   // gcd of K and every row index where the row changes
+    for (int64_t r = 1; r < K && g > 1; r++)
+      if (memcmp(sd + r * N, sd + (r - 1) * N, (size_t)N * sizeof(float)) != 0) g = std::__gcd(g, r);
+    if (g > 1) {
+      Shape cs;
+      cs.dtype = CB_F32;
+      if (g == K) cs.dims = {N}; else cs.dims = {K / g, N};
+      cbg_value* folded = add_node(f, N_CONST, cs, {});
+      folded->const_data.resize(cs.bytes());
+      float* out = reinterpret_cast<float*>(folded->const_data.data());
+      for (int64_t r = 0; r < K / g; r++) memcpy(out + r * N, sd + r * g * N, (size_t)N * sizeof(float));
+      scale = folded;
+      layout = g == K ? CB_SCALE_CHANNEL : CB_SCALE_KGROUP;
+      block_size = g;
+    }
+  }
   Shape s = x->shape;
   s.dims.back() = N;
   std::vector<cbg_value*> ins = {x, weights, scale};
@@ -1000,38 +1095,373 @@ int cbg_fn_fused_sdpa(cbg_function* f, cbg_value* q, cbg_value* k, cbg_value* va
   return CB_OK;
 }
 
+
+// ---- element-wise and reduction ops of a decoder block (StandardOps, standard_ops.go:131-700)
+static int binary_op(cbg_function* f, const char* op, int code, cbg_value* lhs, cbg_value* rhs, cbg_value** v) {
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {lhs, rhs}));
+  const Shape &ls = lhs->shape, &rs = rhs->shape;
+  // shapeinference.BinaryOp (shapeinference/shapeinference.go:219-300)
+  if (ls.dtype != rs.dtype)
+    return fail(CB_ERR_INVALID_ARG, "data types (DType) for BinaryOp %s must match, got %s and %s", op, ls.str().c_str(), rs.str().c_str());
+  const bool is_flt = ls.dtype == CB_F32 || ls.dtype == CB_F64 || ls.dtype == CB_BF16 || ls.dtype == CB_F16;
+  if (!is_flt && ls.dtype != CB_I32 && ls.dtype != CB_I64)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: dtype %s is not implemented by the cuda backend", op, cb::dtype_name(ls.dtype));
+  Shape out;
+  out.dtype = ls.dtype;
+  if (ls.dims.empty()) out.dims = rs.dims;
+  else if (rs.dims.empty()) out.dims = ls.dims;
+  else {
+    if (ls.dims.size() != rs.dims.size())
+      return fail(CB_ERR_INVALID_ARG, "if operands are not scalars, their rank must match for BinaryOp (%s); got shapes %s and %s", op, ls.str().c_str(), rs.str().c_str());
+    for (size_t a = 0; a < ls.dims.size(); a++) {
+      const int64_t l = ls.dims[a], r = rs.dims[a];
+      if (l != r && l != 1 && r != 1)
+        return fail(CB_ERR_INVALID_ARG, "dimension of axis #%zu doesn't match and cannot be broadcast for BinaryOp (%s), got shapes %s and %s", a, op, ls.str().c_str(), rs.str().c_str());
+      out.dims.push_back(l == 1 ? r : l);
+    }
+  }
+  cbg_value* n = add_node(f, N_BINARY, out, {lhs, rhs});
+  n->op = code;
+  *v = n;
+  return CB_OK;
+}
+int cbg_fn_add(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Add", CB_BIN_ADD, lhs, rhs, v); }
+int cbg_fn_sub(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Sub", CB_BIN_SUB, lhs, rhs, v); }
+int cbg_fn_mul(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Mul", CB_BIN_MUL, lhs, rhs, v); }
+int cbg_fn_div(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Div", CB_BIN_DIV, lhs, rhs, v); }
+int cbg_fn_max(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Max", CB_BIN_MAX, lhs, rhs, v); }
+int cbg_fn_min(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v) { return binary_op(f, "Min", CB_BIN_MIN, lhs, rhs, v); }
+
+static int unary_op(cbg_function* f, const char* op, int code, cbg_value* x, cbg_value** v) {
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  CB_TRY(check_small_dtype(op, x));
+  cbg_value* n = add_node(f, N_UNARY, x->shape, {x});
+  n->op = code;
+  *v = n;
+  return CB_OK;
+}
+int cbg_fn_neg(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Neg", CB_UN_NEG, x, v); }
+int cbg_fn_rsqrt(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Rsqrt", CB_UN_RSQRT, x, v); }
+int cbg_fn_sqrt(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Sqrt", CB_UN_SQRT, x, v); }
+int cbg_fn_exp(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Exp", CB_UN_EXP, x, v); }
+int cbg_fn_logistic(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Logistic", CB_UN_LOGISTIC, x, v); }
+int cbg_fn_tanh(cbg_function* f, cbg_value* x, cbg_value** v) { return unary_op(f, "Tanh", CB_UN_TANH, x, v); }
+
+static int reduce_op(cbg_function* f, const char* op, int code, cbg_value* x, const int* axes, int n_axes, cbg_value** v) {
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  CB_TRY(check_small_dtype(op, x));
+  const int rank = (int)x->shape.dims.size();
+  std::vector<int32_t> flags(rank, 0);
+  if (n_axes == 0) std::fill(flags.begin(), flags.end(), 1);     // no axes: reduce everything (standard_ops.go:660-682)
+  for (int i = 0; i < n_axes; i++) {
+    const int a = axes[i] < 0 ? axes[i] + rank : axes[i];
+    if (a < 0 || a >= rank) return fail(CB_ERR_INVALID_ARG, "%s: axis %d out of range for rank %d", op, axes[i], rank);
+    if (flags[a]) return fail(CB_ERR_INVALID_ARG, "%s: axis %d given more than once", op, axes[i]);
+    flags[a] = 1;
+  }
+  Shape out;
+  out.dtype = x->shape.dtype;
+  for (int a = 0; a < rank; a++) if (!flags[a]) out.dims.push_back(x->shape.dims[a]);
+  cbg_value* n = add_node(f, N_REDUCE, out, {x});
+  n->op = code;
+  n->axis_flags = flags;
+  *v = n;
+  return CB_OK;
+}
+int cbg_fn_reduce_sum(cbg_function* f, cbg_value* x, const int* axes, int n_axes, cbg_value** v) { return reduce_op(f, "ReduceSum", CB_REDUCE_SUM, x, axes, n_axes, v); }
+int cbg_fn_reduce_max(cbg_function* f, cbg_value* x, const int* axes, int n_axes, cbg_value** v) { return reduce_op(f, "ReduceMax", CB_REDUCE_MAX, x, axes, n_axes, v); }
+
+// StandardOps.BroadcastInDim (standard_ops.go:232-254)
+int cbg_fn_broadcast_in_dim(cbg_function* f, cbg_value* x, int32_t dtype, int rank, const int64_t* dims, const int* broadcast_axes, cbg_value** v) {
+  const char* op = "BroadcastInDim";
+  CB_TRY(check_fn(f, op));
+  CB_TRY(check_values(f, op, {x}));
+  if (dtype != x->shape.dtype) return fail(CB_ERR_INVALID_ARG, "%s: output dtype %s differs from the operand's %s", op, cb::dtype_name(dtype), cb::dtype_name(x->shape.dtype));
+  Shape out;
+  out.dtype = dtype;
+  CB_TRY(make_dims(op, rank, dims, &out.dims));
+  const int xr = (int)x->shape.dims.size();
+  int prev = -1;
+  std::vector<int32_t> axes(xr);
+  for (int a = 0; a < xr; a++) {
+    const int t = broadcast_axes[a];
+    if (t <= prev || t >= rank) return fail(CB_ERR_INVALID_ARG, "%s: broadcastAxes must be increasing and inside the output rank %d", op, rank);
+    if (x->shape.dims[a] != 1 && x->shape.dims[a] != out.dims[t])
+      return fail(CB_ERR_INVALID_ARG, "%s: operand axis %d (%lld) cannot be broadcast into output axis %d (%lld)", op, a, (long long)x->shape.dims[a], t, (long long)out.dims[t]);
+    axes[a] = t;
+    prev = t;
+  }
+  cbg_value* n = add_node(f, N_BROADCAST, out, {x});
+  n->axis_flags = axes;
+  *v = n;
+  return CB_OK;
+}
+
+// ---- collectives (CollectiveOps.AllReduce collectiveops.go:10-20; the AllGather the interface sketches, :31-32)
+// Replica groups are indices into the device assignment, as DeviceMesh.ComputeReplicaGroups produces them
+// (distributed/devicemesh.go:224-293).  No groups = one group of all replicas; otherwise every replica belongs to
+// exactly one group.  Validated against the replica count at Compile.
+static int copy_groups(const char* op, const int* groups_flat, const int* group_sizes, int n_groups, std::vector<std::vector<int>>* out) {
+  out->clear();
+  if (n_groups < 0 || (n_groups > 0 && (!groups_flat || !group_sizes))) return fail(CB_ERR_INVALID_ARG, "%s: replica groups are NULL", op);
+  int k = 0;
+  for (int g = 0; g < n_groups; g++) {
+    if (group_sizes[g] < 1) return fail(CB_ERR_INVALID_ARG, "%s: replica group %d is empty", op, g);
+    out->emplace_back(groups_flat + k, groups_flat + k + group_sizes[g]);
+    k += group_sizes[g];
+  }
+  return CB_OK;
+}
+
+int cbg_fn_all_reduce(cbg_function* f, cbg_value* const* operands, int n_operands, int reduce_type, const int* groups_flat,
+                      const int* group_sizes, int n_groups, cbg_value** outputs) {
+  const char* op = "AllReduce";
+  CB_TRY(check_fn(f, op));
+  if (n_operands < 1 || !operands || !outputs) return fail(CB_ERR_INVALID_ARG, "%s: no operands", op);
+  // compute.ReduceOpType: Undefined 0, Sum 1, Product 2, Max 3, Min 4 (standard_ops.go:65-84)
+  if (reduce_type < 1 || reduce_type > 4) return fail(CB_ERR_INVALID_ARG, "%s: reduction type %d is undefined", op, reduce_type);
+  std::vector<std::vector<int>> groups;
+  CB_TRY(copy_groups(op, groups_flat, group_sizes, n_groups, &groups));
+  for (int i = 0; i < n_operands; i++) {
+    CB_TRY(check_values(f, op, {operands[i]}));
+    CB_TRY(check_small_dtype(op, operands[i]));
+  }
+  for (int i = 0; i < n_operands; i++) {
+    cbg_value* n = add_node(f, N_ALLREDUCE, operands[i]->shape, {operands[i]});
+    n->op = reduce_type - 1;      // cb_reduce_op
+    n->replica_groups = groups;
+    outputs[i] = n;
+  }
+  return CB_OK;
+}
+
+int cbg_fn_all_gather(cbg_function* f, cbg_value* const* operands, int n_operands, int gather_axis, const int* groups_flat,
+                      const int* group_sizes, int n_groups, cbg_value** outputs) {
+  const char* op = "AllGather";
+  CB_TRY(check_fn(f, op));
+  if (n_operands < 1 || !operands || !outputs) return fail(CB_ERR_INVALID_ARG, "%s: no operands", op);
+  std::vector<std::vector<int>> groups;
+  CB_TRY(copy_groups(op, groups_flat, group_sizes, n_groups, &groups));
+  for (size_t g = 1; g < groups.size(); g++)
+    if (groups[g].size() != groups[0].size()) return fail(CB_ERR_INVALID_ARG, "%s: all replica groups must have the same size", op);
+  for (int i = 0; i < n_operands; i++) {
+    CB_TRY(check_values(f, op, {operands[i]}));
+    const int rank = (int)operands[i]->shape.dims.size();
+    if (gather_axis < 0 || gather_axis >= rank) return fail(CB_ERR_INVALID_ARG, "%s: gather axis %d out of range for rank %d", op, gather_axis, rank);
+  }
+  const int spmd = f->builder->spmd > 0 ? f->builder->spmd : 1;
+  const int64_t gsize = groups.empty() ? spmd : (int64_t)groups[0].size();
+  for (int i = 0; i < n_operands; i++) {
+    Shape out = operands[i]->shape;
+    out.dims[gather_axis] *= gsize;
+    cbg_value* n = add_node(f, N_ALLGATHER, out, {operands[i]});
+    n->op = gather_axis;
+    n->replica_groups = groups;
+    outputs[i] = n;
+  }
+  return CB_OK;
+}
+
+// Function.Parameter with a ShardingSpec (function.go:57; distributed/shardingspec.go:43-110): one entry per tensor
+// axis, each a comma-separated list of mesh axis names ("" = replicated).  The spec is validated as
+// ShardingSpec.Validate does (known mesh axes, none used twice) and kept with the parameter; under SPMD every
+// replica is given its own shard, so the declared shape is the shard's.
+int cbg_fn_parameter_sharded(cbg_function* f, const char* name, int32_t dtype, int rank, const int64_t* dims,
+                             const char* const* mesh_axis_names, const int* mesh_axis_sizes, int n_mesh_axes,
+                             const char* const* axis_specs, int n_axis_specs, cbg_value** v) {
+  const char* op = "Parameter";
+  cb::clear_error();
+  if (n_mesh_axes < 0 || n_axis_specs < 0 || (n_mesh_axes > 0 && (!mesh_axis_names || !mesh_axis_sizes)) || (n_axis_specs > 0 && !axis_specs))
+    return fail(CB_ERR_INVALID_ARG, "%s: sharding spec is NULL", op);
+  if (n_axis_specs > rank) return fail(CB_ERR_INVALID_ARG, "%s: ShardingSpec has %d axes, the parameter has rank %d", op, n_axis_specs, rank);
+  std::vector<bool> used(n_mesh_axes, false);
+  std::string text;
+  for (int a = 0; a < n_axis_specs; a++) {
+    std::stringstream ss(axis_specs[a] ? axis_specs[a] : "");
+    std::string nm;
+    text += a ? ";" : "";
+    while (std::getline(ss, nm, ',')) {
+      if (nm.empty()) continue;
+      int idx = -1;
+      for (int m = 0; m < n_mesh_axes; m++) if (nm == mesh_axis_names[m]) idx = m;
+      if (idx < 0) return fail(CB_ERR_INVALID_ARG, "ShardingSpec axis #%d refers to unknown mesh axis \"%s\"", a, nm.c_str());
+      if (used[idx]) return fail(CB_ERR_INVALID_ARG, "mesh axis \"%s\" used more than once in ShardingSpec", nm.c_str());
+      used[idx] = true;
+      text += nm + ",";
+    }
+  }
+  CB_TRY(cbg_fn_parameter(f, name, dtype, rank, dims, v));
+  (*v)->sharding = text.empty() ? "replicated" : text;
+  return CB_OK;
+}
+
+int cbg_exec_input_sharding(const cbg_exec* e, int i, char* buf, size_t n) {
+  cb::clear_error();
+  if (!e || !buf || n == 0 || i < 0 || i >= (int)e->fn->params.size()) return fail(CB_ERR_INVALID_ARG, "Executable.Inputs: index %d out of range", i);
+  snprintf(buf, n, "%s", e->fn->params[i]->sharding.c_str());
+  return CB_OK;
+}
+
 int cbg_fn_not_implemented(cbg_function* f, const char* op_name) {
   cb::clear_error();
   return fail(CB_ERR_NOT_IMPLEMENTED, "%s: not implemented by the cuda backend", op_name ? op_name : "op");
 }
 
+}  // extern "C"
+
 // ---------------------------------------------------------------- Compile
-int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec) {
-  cb::clear_error();
-  if (!bld || !exec) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: NULL argument");
-  *exec = nullptr;
-  if (bld->compiled || !bld->main) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: builder %s was already compiled", bld->name.c_str());
-  if (bld->be->finalized.load()) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: backend has been finalized");
-  cbg_function* f = bld->main.get();
-  if (!f->returned) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: Main function of %s has no Return", bld->name.c_str());
-  auto e = std::make_unique<cbg_exec>();
-  e->be = bld->be;
-  e->name = bld->name;
-  e->replicas = bld->spmd > 0 ? bld->spmd : 1;
-  e->assignment = bld->assignment;
-  if (e->assignment.empty()) for (int i = 0; i < e->replicas; i++) e->assignment.push_back(i);
-  if ((int)e->assignment.size() != e->replicas)
-    return fail(CB_ERR_INVALID_ARG, "Builder.Compile: device assignment has %zu devices, %d replicas requested", e->assignment.size(), e->replicas);
-  e->plans.assign(f->nodes.size(), nullptr);
-  e->ws_bytes.assign(f->nodes.size(), 0);
+namespace {
+
+// the value of a one-element float constant, or false
+bool scalar_constant(const cbg_value* v, double* out) {
+  while (v->kind == N_RESHAPE || v->kind == N_BROADCAST) v = v->inputs[0];
+  if (v->kind != N_CONST || v->shape.size() != 1) return false;
+  const uint8_t* d = v->const_data.data();
+  switch (v->shape.dtype) {
+    case CB_F32: { float f; memcpy(&f, d, 4); *out = f; return true; }
+    case CB_F64: { double f; memcpy(&f, d, 8); *out = f; return true; }
+    case CB_BF16: { uint16_t h; memcpy(&h, d, 2); uint32_t b = (uint32_t)h << 16; float f; memcpy(&f, &b, 4); *out = f; return true; }
+    default: return false;
+  }
+}
+
+const cbg_value* through_reshape(const cbg_value* v) {
+  while (v->kind == N_RESHAPE) v = v->inputs[0];
+  return v;
+}
+
+// The decomposed RMS norm a caller of this interface writes (it has no fused one: FusedLayerNorm is mean-centred,
+// internal/gobackend/fusedops/layernorm.go:102-137):
+//     x * Reshape(Rsqrt(ReduceSum(x * x, last axis) * (1/H) + eps), [..., 1])  [ * gamma reshaped to [1..., H] ]
+// with either operand order in every product and sum, or Div by H instead of Mul by 1/H.  Matches at the last
+// product; returns x, gamma (or null) and eps.
+bool match_rms_core(const cbg_value* n, const cbg_value** x_out, double* eps_out) {
+  if (n->kind != N_BINARY || n->op != CB_BIN_MUL) return false;
+  for (int o = 0; o < 2; o++) {
+    const cbg_value* x = n->inputs[o];
+    const cbg_value* rr = n->inputs[1 - o];
+    if (x->shape.dims.empty()) continue;
+    const int64_t H = x->shape.dims.back();
+    std::vector<int64_t> want = x->shape.dims;
+    want.back() = 1;
+    if (rr->shape.dims != want) continue;
+    const cbg_value* r = through_reshape(rr);
+    if (r->kind != N_UNARY || r->op != CB_UN_RSQRT) continue;
+    const cbg_value* me = r->inputs[0];
+    if (me->kind != N_BINARY || me->op != CB_BIN_ADD) continue;
+    for (int a = 0; a < 2; a++) {
+      double eps = 0.0;
+      if (!scalar_constant(me->inputs[1 - a], &eps)) continue;
+      const cbg_value* ms = me->inputs[a];
+      if (ms->kind != N_BINARY) continue;
+      const cbg_value* ss = nullptr;
+      double c = 0.0;
+      if (ms->op == CB_BIN_MUL) {
+        for (int b = 0; b < 2 && !ss; b++)
+          if (scalar_constant(ms->inputs[1 - b], &c) && std::abs(c * (double)H - 1.0) < 1e-3) ss = ms->inputs[b];
+      } else if (ms->op == CB_BIN_DIV) {
+        if (scalar_constant(ms->inputs[1], &c) && std::abs(c - (double)H) < 1e-3 * (double)H) ss = ms->inputs[0];
+      }
+      if (!ss) continue;
+      ss = through_reshape(ss);
+      if (ss->kind != N_REDUCE || ss->op != CB_REDUCE_SUM) continue;
+      const cbg_value* sq = ss->inputs[0];
+      const int rank = (int)sq->shape.dims.size();
+      bool last_only = rank >= 1;
+      for (int d = 0; d < rank; d++) if ((ss->axis_flags[d] != 0) != (d == rank - 1)) last_only = false;
+      if (!last_only) continue;
+      if (sq->kind != N_BINARY || sq->op != CB_BIN_MUL || sq->inputs[0] != x || sq->inputs[1] != x) continue;
+      *x_out = x;
+      *eps_out = eps;
+      return true;
+    }
+  }
+  return false;
+}
+
+// Rewrites matching products into N_RMSNORM nodes (the nodes they replace become dead unless something else uses them).
+void fuse_rms_norms(cbg_function* f) {
+  // consumers first: the product with gamma is seen before the normalisation it scales
+  for (size_t ni = f->nodes.size(); ni-- > 0;) {
+    cbg_value* n = f->nodes[ni].get();
+    const cbg_value* x = nullptr;
+    double eps = 0.0;
+    if (n->kind != N_BINARY || n->op != CB_BIN_MUL) continue;
+    // with gamma: (x * rr) * g, g of H elements laid out along the last axis
+    bool done = false;
+    for (int o = 0; o < 2 && !done; o++) {
+      cbg_value* core = n->inputs[o];
+      cbg_value* g = n->inputs[1 - o];
+      if (!match_rms_core(core, &x, &eps)) continue;
+      const int64_t H = x->shape.dims.back();
+      bool g_ok = g->shape.dtype == x->shape.dtype && g->shape.size() == H && !g->shape.dims.empty() && g->shape.dims.back() == H;
+      if (!g_ok) continue;
+      n->kind = N_RMSNORM;
+      n->inputs = {const_cast<cbg_value*>(x), g};
+      n->epsilon = eps;
+      n->flags = 1;
+      done = true;
+    }
+    if (done) continue;
+    if (match_rms_core(n, &x, &eps)) {
+      n->kind = N_RMSNORM;
+      n->inputs = {const_cast<cbg_value*>(x)};
+      n->epsilon = eps;
+      n->flags = 0;
+    }
+  }
+}
+
+int check_replica_groups(const cbg_value* n, int replicas, const char* op) {
+  std::vector<bool> seen(replicas, false);
+  if (n->replica_groups.empty()) return CB_OK;
+  for (const auto& g : n->replica_groups)
+    for (int r : g) {
+      if (r < 0 || r >= replicas) return fail(CB_ERR_INVALID_ARG, "%s: replica %d out of range for %d devices", op, r, replicas);
+      if (seen[r]) return fail(CB_ERR_INVALID_ARG, "%s: replica %d appears in more than one replica group", op, r);
+      seen[r] = true;
+    }
+  for (int r = 0; r < replicas; r++)
+    if (!seen[r]) return fail(CB_ERR_INVALID_ARG, "%s: replica %d belongs to no replica group", op, r);
+  return CB_OK;
+}
+
+bool same_decode_group(const cb_qdense_desc& a, const cb_qdense_desc& b) {
+  return a.M == b.M && a.K == b.K && a.x_dtype == b.x_dtype && a.w_dtype == b.w_dtype && a.scale_layout == b.scale_layout &&
+         (a.scale_layout == CB_SCALE_CHANNEL || a.block_size == b.block_size);
+}
+
+int build_dev_plans(cbg_exec* e, int dev, DevPlans* dp) {
+  cbg_function* f = e->fn.get();
+  const size_t nn = f->nodes.size();
+  dp->plans.assign(nn, nullptr);
+  dp->ws_bytes.assign(nn, 0);
   int st = CB_OK;
-  for (size_t i = 0; i < f->nodes.size() && st == CB_OK; i++) {
+  for (size_t i = 0; i < nn && st == CB_OK; i++) {
     cbg_value* n = f->nodes[i].get();
+    if (!e->live[i]) continue;
     cb_plan* p = nullptr;
-    const int dev = e->assignment[0];   // plans hold no device state beyond the SM count
     switch (n->kind) {
       case N_DOT: st = cb_plan_dot(dev, &n->dot, &p); break;
-      case N_QDENSE: st = cb_plan_qdense(dev, &n->qd, &p); break;
+      case N_QDENSE:
+        if (e->group_of[i] >= 0) {
+          const std::vector<int>& members = e->groups[e->group_of[i]];
+          if (members[0] != (int)i) break;                 // launched with the first member
+          std::vector<cb_qdense_member> ms;
+          for (int m : members) {
+            const cb_qdense_desc& d = f->nodes[m]->qd;
+            cb_qdense_member mm;
+            mm.N = d.N; mm.has_bias = d.has_bias; mm.activation = d.activation;
+            ms.push_back(mm);
+          }
+          st = cb_plan_qdense_group(dev, &n->qd, ms.data(), (int)ms.size(), &p);
+        } else {
+          st = cb_plan_qdense(dev, &n->qd, &p);
+        }
+        break;
       case N_SDPA: st = cb_plan_sdpa(dev, &n->sdpa, &p); break;
       case N_SLICE:
         st = cb_plan_slice(dev, n->shape.dtype, (int)n->inputs[0]->shape.dims.size(), n->inputs[0]->shape.dims.data(),
@@ -1050,18 +1480,129 @@ int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec) {
       case N_TRANSPOSE:
         st = cb_plan_transpose(dev, n->shape.dtype, (int)n->inputs[0]->shape.dims.size(), n->inputs[0]->shape.dims.data(), n->perm.data(), &p);
         break;
-      default: break;
+      case N_BINARY: {
+        // both operands with the rank of the result (a scalar as all ones)
+        const int r = (int)n->shape.dims.size();
+        std::vector<int64_t> l(std::max(r, 1), 1), rr(std::max(r, 1), 1);
+        if (!n->inputs[0]->shape.dims.empty()) l = n->inputs[0]->shape.dims;
+        if (!n->inputs[1]->shape.dims.empty()) rr = n->inputs[1]->shape.dims;
+        st = cb_plan_binary(dev, n->op, n->shape.dtype, r, l.data(), rr.data(), &p);
+        break;
+      }
+      case N_UNARY: st = cb_plan_unary(dev, n->op, n->shape.dtype, n->shape.size(), &p); break;
+      case N_REDUCE:
+        st = cb_plan_reduce(dev, n->op, n->shape.dtype, (int)n->inputs[0]->shape.dims.size(), n->inputs[0]->shape.dims.data(), n->axis_flags.data(), &p);
+        break;
+      case N_BROADCAST:
+        st = cb_plan_broadcast_in_dim(dev, n->shape.dtype, (int)n->inputs[0]->shape.dims.size(), n->inputs[0]->shape.dims.data(),
+                                      (int)n->shape.dims.size(), n->shape.dims.data(), n->axis_flags.data(), &p);
+        break;
+      case N_RMSNORM: {
+        const int64_t H = n->shape.dims.back();
+        st = cb_plan_rms_norm(dev, n->shape.dtype, H ? n->shape.size() / H : 0, H, n->epsilon, n->flags & 1, &p);
+        break;
+      }
+      default: break;      // parameters, constants, reshapes, collectives
     }
     if (st == CB_OK && p) {
-      e->plans[i] = p;
-      cb_plan_workspace_bytes(p, &e->ws_bytes[i]);
+      dp->plans[i] = p;
+      cb_plan_workspace_bytes(p, &dp->ws_bytes[i]);
     }
   }
   if (st != CB_OK) {
-    for (cb_plan* p : e->plans) if (p) cb_plan_destroy(p);
-    return st;
+    for (cb_plan* p : dp->plans) if (p) cb_plan_destroy(p);
+    dp->plans.clear();
+  }
+  return st;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cbg_builder_compile(cbg_builder* bld, cbg_exec** exec) {
+  cb::clear_error();
+  if (!bld || !exec) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: NULL argument");
+  *exec = nullptr;
+  if (bld->compiled || !bld->main) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: builder %s was already compiled", bld->name.c_str());
+  if (bld->be->finalized.load()) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: backend has been finalized");
+  cbg_function* f = bld->main.get();
+  if (!f->returned) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: Main function of %s has no Return", bld->name.c_str());
+  auto e = std::make_unique<cbg_exec>();
+  e->be = bld->be;
+  e->name = bld->name;
+  e->replicas = bld->spmd > 0 ? bld->spmd : 1;
+  e->assignment = bld->assignment;
+  if (e->assignment.empty()) for (int i = 0; i < e->replicas; i++) e->assignment.push_back(i);
+  if ((int)e->assignment.size() != e->replicas)
+    return fail(CB_ERR_INVALID_ARG, "Builder.Compile: device assignment has %zu devices, %d replicas requested", e->assignment.size(), e->replicas);
+  for (size_t a = 0; a < e->assignment.size(); a++)
+    for (size_t b = a + 1; b < e->assignment.size(); b++)
+      if (e->assignment[a] == e->assignment[b]) return fail(CB_ERR_INVALID_ARG, "Builder.Compile: device %d assigned twice", e->assignment[a]);
+  const size_t nn = f->nodes.size();
+  for (size_t i = 0; i < nn; i++) {
+    const cbg_value* n = f->nodes[i].get();
+    if (n->kind == N_ALLREDUCE) CB_TRY(check_replica_groups(n, e->replicas, "AllReduce"));
+    if (n->kind == N_ALLGATHER) {
+      CB_TRY(check_replica_groups(n, e->replicas, "AllGather"));
+      const int64_t gsize = n->replica_groups.empty() ? e->replicas : (int64_t)n->replica_groups[0].size();
+      if (n->shape.dims[n->op] != n->inputs[0]->shape.dims[n->op] * gsize)
+        return fail(CB_ERR_INVALID_ARG, "AllGather: the result shape was inferred for %lld replicas per group; call DistributedSPMD before building the op",
+                    (long long)(n->inputs[0]->shape.dims[n->op] ? n->shape.dims[n->op] / n->inputs[0]->shape.dims[n->op] : 0));
+    }
+  }
+  // ---- graph passes: the decomposed RMS norm becomes one row kernel; values nobody needs are not computed
+  fuse_rms_norms(f);
+  e->live.assign(nn, 0);
+  for (cbg_value* o : f->outputs) e->live[o->index] = 1;
+  for (size_t i = nn; i-- > 0;)
+    if (e->live[i]) for (cbg_value* in : f->nodes[i]->inputs) e->live[in->index] = 1;
+  for (cbg_value* prm : f->params) e->live[prm->index] = 1;
+  // ---- independent decode-shaped FusedQuantizedDense nodes of one shape family become one grouped launch: a node
+  // joins the open group when all its operands were already available where the group's first member stands.
+  e->group_of.assign(nn, -1);
+  if (!e->be->fallback_only) {
+    std::vector<int> open;         // open groups (indices into e->groups)
+    for (size_t i = 0; i < nn; i++) {
+      cbg_value* n = f->nodes[i].get();
+      if (!e->live[i] || n->kind != N_QDENSE) continue;
+      cb_plan* probe = nullptr;
+      if (cb_plan_qdense(0, &n->qd, &probe) != CB_OK) { cb::clear_error(); continue; }
+      const bool decode_tc = std::string(cb_plan_kernel_name(probe)).rfind("qdense_decode_tc_", 0) == 0;
+      cb_plan_destroy(probe);
+      if (!decode_tc) continue;
+      int joined = -1;
+      for (int gi : open) {
+        std::vector<int>& members = e->groups[gi];
+        const cbg_value* first = f->nodes[members[0]].get();
+        if ((int)members.size() >= CB_QDENSE_GROUP_MAX || !same_decode_group(first->qd, n->qd)) continue;
+        bool ready = true;
+        for (const cbg_value* in : n->inputs) {
+          const cbg_value* root = through_reshape(in);       // parameters and constants exist from the start
+          if (root->kind != N_PARAM && root->kind != N_CONST && in->index >= first->index) ready = false;
+        }
+        if (!ready) continue;
+        joined = gi;
+        break;
+      }
+      if (joined >= 0) { e->groups[joined].push_back((int)i); e->group_of[i] = joined; }
+      else { e->groups.push_back({(int)i}); e->group_of[i] = (int)e->groups.size() - 1; open.push_back(e->group_of[i]); }
+    }
+    for (size_t gi = 0; gi < e->groups.size(); gi++)      // a group of one is an ordinary plan
+      if (e->groups[gi].size() == 1) e->group_of[e->groups[gi][0]] = -1;
   }
   e->fn = std::move(bld->main);
+  // plans for every assigned device (a plan carries its device: launches make that device current)
+  int st = CB_OK;
+  for (int dev : e->assignment) {
+    st = build_dev_plans(e.get(), dev, &e->dev_plans[dev]);
+    if (st != CB_OK) break;
+  }
+  if (st != CB_OK) {
+    for (auto& kv : e->dev_plans) for (cb_plan* p : kv.second.plans) if (p) cb_plan_destroy(p);
+    bld->main = std::move(e->fn);
+    return st;
+  }
   bld->compiled = true;
   *exec = e.release();
   return CB_OK;
@@ -1089,118 +1630,221 @@ int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n) {
   cb::clear_error();
   if (!e || !buf || n == 0) return fail(CB_ERR_INVALID_ARG, "NULL argument");
   std::string s;
-  for (cb_plan* p : e->plans) if (p) { s += cb_plan_kernel_name(p); s += "\n"; }
+  auto it = e->dev_plans.find(e->assignment[0]);
+  if (it != e->dev_plans.end())
+    for (size_t i = 0; i < it->second.plans.size(); i++) {
+      const cbg_value* nd = e->fn->nodes[i].get();
+      if (it->second.plans[i]) { s += cb_plan_kernel_name(it->second.plans[i]); s += "\n"; }
+      else if (e->live[i] && nd->kind == N_ALLREDUCE) s += "all_reduce\n";
+      else if (e->live[i] && nd->kind == N_ALLGATHER) s += "all_gather\n";
+    }
   snprintf(buf, n, "%s", s.c_str());
   return CB_OK;
 }
 
-static int run_replica(cbg_exec* e, int dev, cbg_buffer* const* inputs, const uint8_t* donate, cbg_buffer** outputs) {
+}  // extern "C"
+
+namespace {
+
+// One replica of an Execute call.
+struct Replica {
+  int dev = 0;
+  DevicePool* pool = nullptr;
+  const DevPlans* dp = nullptr;
+  cb_stream stream = nullptr;
+  std::vector<void*> consts, ws, mem;
+  std::vector<char> owned, taken;
+  std::vector<std::pair<size_t, void*>> scratch;      // pool memory to give back after the final sync
+  std::vector<cb_event> events;
+  cbg_buffer* const* inputs = nullptr;
+  const uint8_t* donate = nullptr;
+  std::vector<cbg_buffer*> outs;
+};
+
+int setup_replica(cbg_exec* e, Replica& r) {
   cbg_function* f = e->fn.get();
-  cbg_backend* be = e->be;
-  DevicePool& pool = *be->pools[dev];
   const size_t nn = f->nodes.size();
-  // constants of this device and a set of prepared workspaces
-  std::vector<void*> consts, ws;
+  r.pool = e->be->pools[r.dev].get();
   {
     std::lock_guard<std::mutex> l(e->mu);
-    auto it = e->const_dev.find(dev);
+    auto pit = e->dev_plans.find(r.dev);
+    if (pit == e->dev_plans.end()) {                    // a device chosen at Execute (defaultDevice) rather than at Compile
+      DevPlans dp;
+      CB_TRY(build_dev_plans(e, r.dev, &dp));
+      pit = e->dev_plans.emplace(r.dev, std::move(dp)).first;
+    }
+    r.dp = &pit->second;
+    auto it = e->const_dev.find(r.dev);
     if (it == e->const_dev.end()) {
       std::vector<void*> c(nn, nullptr);
-      for (size_t i = 0; i < nn; i++) {
+      int st = CB_OK;
+      for (size_t i = 0; i < nn && st == CB_OK; i++) {
         cbg_value* n = f->nodes[i].get();
-        if (n->kind != N_CONST) continue;
-        CB_TRY(cb_alloc(dev, n->const_data.size(), &c[i]));
-        CB_TRY(cb_h2d(dev, c[i], n->const_data.data(), n->const_data.size(), nullptr));
+        if (n->kind != N_CONST || !e->live[i]) continue;
+        st = cb_alloc(r.dev, n->const_data.size(), &c[i]);
+        if (st == CB_OK) st = cb_h2d(r.dev, c[i], n->const_data.data(), n->const_data.size(), nullptr);
       }
-      it = e->const_dev.emplace(dev, std::move(c)).first;
+      if (st != CB_OK) { for (void* p : c) if (p) cb_free(r.dev, p); return st; }
+      it = e->const_dev.emplace(r.dev, std::move(c)).first;
     }
-    consts = it->second;
-    auto& idle = e->idle_ws[dev];
-    if (!idle.empty()) { ws = std::move(idle.back()); idle.pop_back(); }
+    r.consts = it->second;
+    auto& idle = e->idle_ws[r.dev];
+    if (!idle.empty()) { r.ws = std::move(idle.back()); idle.pop_back(); }
   }
-  if (ws.empty()) {
-    ws.assign(nn, nullptr);
-    for (size_t i = 0; i < nn; i++) {
-      if (!e->plans[i] || e->ws_bytes[i] == 0) continue;
-      CB_TRY(cb_alloc(dev, e->ws_bytes[i], &ws[i]));
-      CB_TRY(cb_plan_prepare_workspace(e->plans[i], ws[i], nullptr));
+  if (r.ws.empty()) {
+    r.ws.assign(nn, nullptr);
+    int st = CB_OK;
+    for (size_t i = 0; i < nn && st == CB_OK; i++) {
+      if (!r.dp->plans[i] || r.dp->ws_bytes[i] == 0) continue;
+      st = cb_alloc(r.dev, r.dp->ws_bytes[i], &r.ws[i]);
+      if (st == CB_OK) st = cb_plan_prepare_workspace(r.dp->plans[i], r.ws[i], nullptr);
     }
-    CB_TRY(cb_stream_sync(dev, nullptr));
+    if (st == CB_OK) st = cb_stream_sync(r.dev, nullptr);
+    if (st != CB_OK) { for (void* p : r.ws) if (p) cb_free(r.dev, p); r.ws.clear(); return st; }
   }
-  cb_stream stream = nullptr;
-  CB_TRY(be->get_stream(dev, &stream));
+  CB_TRY(e->be->get_stream(r.dev, &r.stream));
+  r.mem.assign(nn, nullptr);
+  r.owned.assign(nn, 0);
+  r.taken.assign(nn, 0);
+  // parameters and constants exist from the start (a grouped launch may read operands declared after its first member)
+  for (size_t i = 0; i < nn; i++) {
+    const cbg_value* n = f->nodes[i].get();
+    if (n->kind == N_PARAM) r.mem[i] = r.inputs[n->param_index]->ptr;
+    else if (n->kind == N_CONST) r.mem[i] = r.consts[i];
+  }
+  return CB_OK;
+}
 
-  std::vector<void*> mem(nn, nullptr);      // device pointer of every node's value
-  std::vector<bool> owned(nn, false);       // allocated from the pool by this call
-  int st = CB_OK;
-  for (size_t i = 0; i < nn && st == CB_OK; i++) {
-    cbg_value* n = f->nodes[i].get();
-    switch (n->kind) {
-      case N_PARAM: mem[i] = inputs[n->param_index]->ptr; break;
-      case N_CONST: mem[i] = consts[i]; break;
-      case N_RESHAPE: mem[i] = mem[n->inputs[0]->index]; break;     // same bytes, new shape
-      default: {
-        st = pool.get(dev, n->shape.bytes(), &mem[i]);
-        if (st != CB_OK) break;
-        owned[i] = true;
-        const void* in[8];
-        for (size_t k = 0; k < n->inputs.size(); k++) in[k] = mem[n->inputs[k]->index];
-        void* out[1] = {mem[i]};
-        // a kernel launch with zero elements is skipped inside cb_launch
-        st = cb_launch(e->plans[i], in, (int)n->inputs.size(), out, 1, ws[i], stream);
+// the memory of an operand; a Reshape shares its operand's
+void* operand_ptr(const Replica& r, const cbg_value* v) {
+  while (v->kind == N_RESHAPE) v = v->inputs[0];
+  return r.mem[v->index];
+}
+
+int new_event(Replica& r, cb_event* ev) {
+  CB_TRY(cb_event_create(r.dev, ev));
+  r.events.push_back(*ev);
+  return CB_OK;
+}
+
+// AllReduce / AllGather over the replicas of one Execute call (one process drives all devices): every member of a
+// group pulls the operands of its peers with peer copies on its own stream, after an event that says the operand
+// is ready, and reduces them in group order (so all members end with the same bits).  Operand buffers stay alive
+// until the final sync of the call.
+int run_collective(cbg_exec* e, cbg_value* n, std::vector<Replica>& reps) {
+  const size_t idx = (size_t)n->index;
+  const int in_idx = n->inputs[0]->index;
+  const size_t bytes = n->inputs[0]->shape.bytes();
+  std::vector<std::vector<int>> groups = n->replica_groups;
+  if (groups.empty()) { groups.emplace_back(); for (int r = 0; r < (int)reps.size(); r++) groups[0].push_back(r); }
+  std::vector<cb_event> ready(reps.size(), nullptr);
+  for (size_t r = 0; r < reps.size(); r++) {
+    CB_TRY(new_event(reps[r], &ready[r]));
+    CB_TRY(cb_event_record(reps[r].dev, ready[r], reps[r].stream));
+    CB_TRY(reps[r].pool->get(reps[r].dev, n->shape.bytes(), &reps[r].mem[idx]));
+    reps[r].owned[idx] = 1;
+  }
+  for (const auto& g : groups) {
+    const int gs = (int)g.size();
+    for (int d : g) {
+      Replica& me = reps[d];
+      for (int src : g) if (src != d) CB_TRY(cb_stream_wait_event(me.dev, me.stream, ready[src]));
+      if (n->kind == N_ALLREDUCE) {
+        void* stack = nullptr;
+        CB_TRY(me.pool->get(me.dev, bytes * gs, &stack));
+        me.scratch.emplace_back(bytes * gs, stack);
+        for (int k = 0; k < gs; k++)
+          CB_TRY(cb_d2d(me.dev, (uint8_t*)stack + (size_t)k * bytes, reps[g[k]].dev, reps[g[k]].mem[in_idx], bytes, me.stream));
+        CB_TRY(cb::set_device(me.dev));
+        CB_TRY(cb::stacked_reduce_launch(n->shape.dtype, n->op, stack, gs, n->shape.size(), me.mem[idx], (cudaStream_t)me.stream));
+      } else {
+        // out viewed as [outer, group, chunk]: member k's operand fills [:, k, :]
+        const Shape& is = n->inputs[0]->shape;
+        int64_t outer = 1, chunk = cb::dtype_size(is.dtype);
+        for (int a = 0; a < n->op; a++) outer *= is.dims[a];
+        for (size_t a = (size_t)n->op; a < is.dims.size(); a++) chunk *= is.dims[a];
+        for (int k = 0; k < gs; k++) {
+          const Replica& src = reps[g[k]];
+          if (outer == 1 || chunk == 0) {
+            CB_TRY(cb_d2d(me.dev, (uint8_t*)me.mem[idx] + (size_t)k * chunk, src.dev, src.mem[in_idx], (size_t)chunk, me.stream));
+          } else {
+            CB_TRY(cb::set_device(me.dev));
+            cudaMemcpy3DPeerParms pr;
+            memset(&pr, 0, sizeof(pr));
+            pr.srcDevice = src.dev;
+            pr.dstDevice = me.dev;
+            pr.srcPtr = make_cudaPitchedPtr(src.mem[in_idx], (size_t)chunk, (size_t)chunk, (size_t)outer);
+            pr.dstPtr = make_cudaPitchedPtr((uint8_t*)me.mem[idx] + (size_t)k * chunk, (size_t)chunk * gs, (size_t)chunk * gs, (size_t)outer);
+            pr.extent = make_cudaExtent((size_t)chunk, (size_t)outer, 1);
+            CB_CUDA(cudaMemcpy3DPeerAsync(&pr, (cudaStream_t)me.stream));
+          }
+        }
       }
     }
   }
-  // outputs: every output is a distinct buffer owned by the caller
-  std::vector<bool> taken(nn, false);
-  std::vector<cbg_buffer*> outs;
-  for (size_t o = 0; o < f->outputs.size() && st == CB_OK; o++) {
+  return CB_OK;
+}
+
+int launch_node(cbg_exec* e, Replica& r, size_t i) {
+  cbg_function* f = e->fn.get();
+  cbg_value* n = f->nodes[i].get();
+  switch (n->kind) {
+    case N_PARAM: r.mem[i] = r.inputs[n->param_index]->ptr; return CB_OK;
+    case N_CONST: r.mem[i] = r.consts[i]; return CB_OK;
+    case N_RESHAPE: r.mem[i] = r.mem[n->inputs[0]->index]; return CB_OK;     // same bytes, new shape
+    default: break;
+  }
+  if (n->kind == N_QDENSE && e->group_of[i] >= 0) {
+    const std::vector<int>& members = e->groups[e->group_of[i]];
+    if (members[0] != (int)i) return CB_OK;       // computed by the first member's launch
+    std::vector<const void*> in;
+    std::vector<void*> out;
+    for (int m : members) {
+      CB_TRY(r.pool->get(r.dev, f->nodes[m]->shape.bytes(), &r.mem[m]));
+      r.owned[m] = 1;
+      for (const cbg_value* v : f->nodes[m]->inputs) in.push_back(operand_ptr(r, v));
+      out.push_back(r.mem[m]);
+    }
+    return cb_launch(r.dp->plans[i], in.data(), (int)in.size(), out.data(), (int)out.size(), r.ws[i], r.stream);
+  }
+  CB_TRY(r.pool->get(r.dev, n->shape.bytes(), &r.mem[i]));
+  r.owned[i] = 1;
+  const void* in[8];
+  for (size_t k = 0; k < n->inputs.size(); k++) in[k] = operand_ptr(r, n->inputs[k]);
+  void* out[1] = {r.mem[i]};
+  // a kernel launch with zero elements is skipped inside cb_launch
+  return cb_launch(r.dp->plans[i], in, (int)n->inputs.size(), out, 1, r.ws[i], r.stream);
+}
+
+int collect_outputs(cbg_exec* e, Replica& r) {
+  cbg_function* f = e->fn.get();
+  for (size_t o = 0; o < f->outputs.size(); o++) {
     cbg_value* n = f->outputs[o];
     // root of the aliasing chain (Reshape shares memory with its operand)
     cbg_value* root = n;
     while (root->kind == N_RESHAPE) root = root->inputs[0];
     auto buf = std::make_unique<cbg_buffer>();
-    buf->be = be;
-    buf->dev = dev;
+    buf->be = e->be;
+    buf->dev = r.dev;
     buf->shape = n->shape;
     const int ri = root->index;
-    const bool donated_param = root->kind == N_PARAM && donate && donate[root->param_index];
-    if ((owned[ri] || donated_param) && !taken[ri]) {
-      buf->ptr = mem[ri];              // hand the memory over
-      taken[ri] = true;
+    const bool donated_param = root->kind == N_PARAM && r.donate && r.donate[root->param_index];
+    if ((r.owned[ri] || donated_param) && !r.taken[ri]) {
+      buf->ptr = r.mem[ri];              // hand the memory over
+      r.taken[ri] = 1;
     } else {
-      st = pool.get(dev, n->shape.bytes(), &buf->ptr);
-      if (st == CB_OK) st = cb_d2d(dev, buf->ptr, dev, mem[ri], n->shape.bytes(), stream);
+      CB_TRY(r.pool->get(r.dev, n->shape.bytes(), &buf->ptr));
+      int st = cb_d2d(r.dev, buf->ptr, r.dev, r.mem[ri], n->shape.bytes(), r.stream);
+      if (st != CB_OK) { r.pool->put(n->shape.bytes(), buf->ptr); return st; }
     }
-    if (st == CB_OK) outs.push_back(buf.release());
+    r.outs.push_back(buf.release());
   }
-  int sync_st = cb_stream_sync(dev, stream);
-  if (st == CB_OK) st = sync_st;
-  for (size_t i = 0; i < nn && st == CB_OK; i++)
-    if (e->plans[i] && ws[i]) st = cb_plan_check_status(e->plans[i], ws[i]);
-  be->put_stream(dev, stream);
-  for (size_t i = 0; i < nn; i++)
-    if (owned[i] && !taken[i]) pool.put(f->nodes[i]->shape.bytes(), mem[i]);
-  {
-    std::lock_guard<std::mutex> l(e->mu);
-    e->idle_ws[dev].push_back(std::move(ws));
-  }
-  // donated inputs are consumed: their memory returns to the pool unless an output took it
-  if (donate)
-    for (size_t p = 0; p < f->params.size(); p++)
-      if (donate[p]) {
-        cbg_buffer* b = inputs[p];
-        if (!taken[f->params[p]->index]) pool.put(b->shape.bytes(), b->ptr);
-        b->ptr = nullptr;
-        b->valid = false;
-      }
-  if (st != CB_OK) {
-    for (cbg_buffer* b : outs) { pool.put(b->shape.bytes(), b->ptr); delete b; }
-    return st;
-  }
-  for (size_t o = 0; o < outs.size(); o++) outputs[o] = outs[o];
   return CB_OK;
 }
+
+}  // namespace
+
+extern "C" {
 
 int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const uint8_t* donate,
                      int default_device, cbg_buffer** outputs, int n_outputs) {
@@ -1213,6 +1857,7 @@ int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const
   if (n_inputs != np * e->replicas)
     return fail(CB_ERR_INVALID_ARG, "Execute: %s expects %d inputs (%d parameters x %d devices), got %d", e->name.c_str(), np * e->replicas, np, e->replicas, n_inputs);
   if (n_outputs < no * e->replicas) return fail(CB_ERR_INVALID_ARG, "Execute: room for %d outputs, %d needed", n_outputs, no * e->replicas);
+  std::vector<Replica> reps(e->replicas);
   for (int r = 0; r < e->replicas; r++) {
     const int dev = e->replicas == 1 ? (e->assignment.size() == 1 && e->assignment[0] != 0 ? e->assignment[0] : default_device) : e->assignment[r];
     if (dev < 0 || dev >= e->be->n_devices) return fail(CB_ERR_INVALID_ARG, "Execute: device %d out of range [0,%d)", dev, e->be->n_devices);
@@ -1226,18 +1871,81 @@ int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const
         return fail(CB_ERR_INVALID_ARG, "Execute: input #%d (%s) has shape %s, parameter wants %s", i, p->name.c_str(), b->shape.str().c_str(), p->shape.str().c_str());
       if (b->dev != dev) return fail(CB_ERR_INVALID_ARG, "Execute: input #%d (%s) is on device %d, execution is on device %d", i, p->name.c_str(), b->dev, dev);
     }
+    reps[r].dev = dev;
+    reps[r].inputs = inputs + r * np;
+    reps[r].donate = donate ? donate + r * np : nullptr;
   }
-  for (int r = 0; r < e->replicas; r++) {
-    const int dev = e->replicas == 1 ? (e->assignment.size() == 1 && e->assignment[0] != 0 ? e->assignment[0] : default_device) : e->assignment[r];
-    CB_TRY(run_replica(e, dev, inputs + r * np, donate ? donate + r * np : nullptr, outputs + r * no));
+  if (donate)       // a buffer donated twice would be handed to the pool twice
+    for (int a = 0; a < n_inputs; a++)
+      for (int b = a + 1; b < n_inputs; b++)
+        if (donate[a] && donate[b] && inputs[a] == inputs[b])
+          return fail(CB_ERR_INVALID_ARG, "Execute: the same buffer is donated as input #%d and input #%d", a, b);
+
+  // ---- launch: every replica is set up, then the nodes are walked once, each node launched on every replica
+  // before the next (all launches are asynchronous, so the devices run side by side; collectives see the operands
+  // of all replicas at their node); one sync per device at the end.
+  const auto t_start = std::chrono::steady_clock::now();
+  int st = CB_OK;
+  int n_setup = 0;
+  for (; n_setup < e->replicas && st == CB_OK; n_setup++) st = setup_replica(e, reps[n_setup]);
+  if (st != CB_OK) n_setup--;                 // the one that failed set nothing up that needs returning
+  const size_t nn = f->nodes.size();
+  for (size_t i = 0; i < nn && st == CB_OK; i++) {
+    if (!e->live[i]) continue;
+    cbg_value* n = f->nodes[i].get();
+    if (n->kind == N_ALLREDUCE || n->kind == N_ALLGATHER) { st = run_collective(e, n, reps); continue; }
+    for (int r = 0; r < e->replicas && st == CB_OK; r++) st = launch_node(e, reps[r], i);
   }
+  for (int r = 0; r < e->replicas && st == CB_OK; r++) st = collect_outputs(e, reps[r]);
+  for (int r = 0; r < n_setup; r++) {
+    if (!reps[r].stream) continue;
+    const int sync_st = cb_stream_sync(reps[r].dev, reps[r].stream);
+    if (st == CB_OK) st = sync_st;
+  }
+  // Kernels with bounded waits report through a status word in their workspace; a wait gives up only after two
+  // seconds, so the words are read (one small blocking copy per plan) only when the call took that long.
+  const double elapsed = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count();
+  if (st == CB_OK && elapsed > 1.5)
+    for (int r = 0; r < n_setup && st == CB_OK; r++)
+      for (size_t i = 0; i < nn && st == CB_OK; i++)
+        if (reps[r].dp->plans[i] && reps[r].ws[i]) st = cb_plan_check_status(reps[r].dp->plans[i], reps[r].ws[i]);
+
+  // ---- give everything back
+  for (int r = 0; r < n_setup; r++) {
+    Replica& rp = reps[r];
+    for (cb_event ev : rp.events) cb_event_destroy(rp.dev, ev);
+    if (rp.stream) e->be->put_stream(rp.dev, rp.stream);
+    for (size_t i = 0; i < rp.mem.size(); i++)
+      if (rp.owned[i] && !rp.taken[i]) rp.pool->put(f->nodes[i]->shape.bytes(), rp.mem[i]);
+    for (auto& sc : rp.scratch) rp.pool->put(sc.first, sc.second);
+    if (!rp.ws.empty()) {
+      std::lock_guard<std::mutex> l(e->mu);
+      e->idle_ws[rp.dev].push_back(std::move(rp.ws));
+    }
+    // donated inputs are consumed: their memory returns to the pool unless an output took it
+    if (rp.donate)
+      for (size_t p = 0; p < f->params.size(); p++)
+        if (rp.donate[p]) {
+          cbg_buffer* b = rp.inputs[p];
+          if (!b->valid) continue;
+          if (rp.taken.empty() || !rp.taken[f->params[p]->index]) rp.pool->put(b->shape.bytes(), b->ptr);
+          b->ptr = nullptr;
+          b->valid = false;
+        }
+  }
+  if (st != CB_OK) {
+    for (Replica& rp : reps) for (cbg_buffer* b : rp.outs) { rp.pool->put(b->shape.bytes(), b->ptr); delete b; }
+    return st;
+  }
+  for (int r = 0; r < e->replicas; r++)
+    for (int o = 0; o < no; o++) outputs[r * no + o] = reps[r].outs[o];
   return CB_OK;
 }
 
 int cbg_exec_finalize(cbg_exec* e) {
   cb::clear_error();
   if (!e) return CB_OK;
-  for (cb_plan* p : e->plans) if (p) cb_plan_destroy(p);
+  for (auto& kv : e->dev_plans) for (cb_plan* p : kv.second.plans) if (p) cb_plan_destroy(p);
   for (auto& kv : e->const_dev) for (void* p : kv.second) if (p) cb_free(kv.first, p);
   for (auto& kv : e->idle_ws) for (auto& set : kv.second) for (void* p : set) if (p) cb_free(kv.first, p);
   delete e;

@@ -125,17 +125,62 @@ typedef struct {
 int cbg_fn_fused_sdpa(cbg_function* f, cbg_value* query, cbg_value* key, cbg_value* value, int axes_layout,
                       const cbg_sdpa_options* options /* or NULL */, cbg_value** output);
 
+/* ---- StandardOps a decoder block needs around its projections (standard_ops.go:131-700): element-wise binary ops
+ * with the broadcasting rule of shapeinference.BinaryOp (equal ranks, every dimension pair equal or with a 1; a scalar
+ * takes the other side's shape), unary ops, reductions over the listed axes (none = all; negative = from the end;
+ * the reduced axes are dropped), BroadcastInDim (:232-254).  Float dtypes; the binary ops also Int32 / Int64.
+ * Builder.Compile recognises the decomposed RMS norm  x * Reshape(Rsqrt(ReduceSum(x * x, last) * (1/H) + eps)) [* gamma]
+ * and runs it as one row kernel. */
+int cbg_fn_add(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_sub(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_mul(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_div(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_max(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_min(cbg_function* f, cbg_value* lhs, cbg_value* rhs, cbg_value** v);
+int cbg_fn_neg(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_rsqrt(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_sqrt(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_exp(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_logistic(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_tanh(cbg_function* f, cbg_value* x, cbg_value** v);
+int cbg_fn_reduce_sum(cbg_function* f, cbg_value* x, const int* axes, int n_axes, cbg_value** v);
+int cbg_fn_reduce_max(cbg_function* f, cbg_value* x, const int* axes, int n_axes, cbg_value** v);
+int cbg_fn_broadcast_in_dim(cbg_function* f, cbg_value* x, int32_t dtype, int rank, const int64_t* dims, const int* broadcast_axes,
+                            cbg_value** v);
+
+/* ---- CollectiveOps (collectiveops.go:10-39) under Builder.DistributedSPMD: AllReduce as the interface declares it
+ * (reduce_type: compute.ReduceOpType, 1 Sum, 2 Product, 3 Max, 4 Min) and the AllGather it sketches (:31-32; the
+ * result's gather axis is the operand's times the group size — call DistributedSPMD first).  replica groups: indices
+ * into the device assignment, groups_flat holding group_sizes[0] + group_sizes[1] + ... entries; n_groups = 0 means
+ * one group of all replicas; otherwise every replica belongs to exactly one group
+ * (distributed/devicemesh.go:224-293 computes them).  One output per operand. */
+int cbg_fn_all_reduce(cbg_function* f, cbg_value* const* operands, int n_operands, int reduce_type, const int* groups_flat,
+                      const int* group_sizes, int n_groups, cbg_value** outputs);
+int cbg_fn_all_gather(cbg_function* f, cbg_value* const* operands, int n_operands, int gather_axis, const int* groups_flat,
+                      const int* group_sizes, int n_groups, cbg_value** outputs);
+
+/* Function.Parameter with its ShardingSpec (function.go:57; distributed/shardingspec.go:43-110): the mesh (axis names
+ * and sizes) and, per tensor axis, a comma-separated list of mesh axes ("" = replicated; missing axes = replicated).
+ * Validated as ShardingSpec.Validate does; under SPMD the declared shape is the shard every replica is given.
+ * cbg_exec_input_sharding reads the spec back ("" = declared without one). */
+int cbg_fn_parameter_sharded(cbg_function* f, const char* name, int32_t dtype, int rank, const int64_t* dims,
+                             const char* const* mesh_axis_names, const int* mesh_axis_sizes, int n_mesh_axes,
+                             const char* const* axis_specs, int n_axis_specs, cbg_value** v);
+
 /* Any other op of the interface, by OpType name (e.g. "Neg", "FusedSoftmax", "AllReduce"):
  * returns CB_ERR_NOT_IMPLEMENTED with the reference's wording. */
 int cbg_fn_not_implemented(cbg_function* f, const char* op_name);
 
 /* ---- Executable.  inputs: one buffer per parameter (device-major under SPMD,
- * executable.go:33-35); donate may be NULL.  outputs must hold cbg_exec_num_outputs handles. */
+ * executable.go:33-35); donate may be NULL.  outputs must hold cbg_exec_num_outputs handles per replica and come back
+ * device-major too (outputs[replica * num_outputs + i]).  Under SPMD all replicas are launched before any is waited
+ * for, so the devices run side by side. */
 int cbg_exec_num_inputs(const cbg_exec* e);
 int cbg_exec_num_outputs(const cbg_exec* e);
 int cbg_exec_input_info(const cbg_exec* e, int i, char* name, size_t name_len, int32_t* dtype, int* rank, int64_t* dims);
 int cbg_exec_output_info(const cbg_exec* e, int i, int32_t* dtype, int* rank, int64_t* dims);
 int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n);      /* launch plan, one kernel per line */
+int cbg_exec_input_sharding(const cbg_exec* e, int i, char* buf, size_t n);
 int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const uint8_t* donate,
                      int default_device, cbg_buffer** outputs, int n_outputs);
 int cbg_exec_finalize(cbg_exec* e);                                        /* Executable.Finalize; frees the handle */

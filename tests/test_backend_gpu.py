@@ -26,8 +26,10 @@ def test_backend_identity(backend):
     assert "B200" in backend.Description() or "cuda:0" in backend.Description()
     caps = backend.Capabilities()
     for op in (be.OP_PARAMETER, be.OP_CONSTANT, be.OP_DOT_GENERAL, be.OP_FUSED_QUANTIZED_DENSE, be.OP_FUSED_SDPA,
-               be.OP_FUSED_DENSE, be.OP_FUSED_SOFTMAX, be.OP_FUSED_GELU, be.OP_FUSED_LAYER_NORM):
+               be.OP_FUSED_DENSE, be.OP_FUSED_SOFTMAX, be.OP_FUSED_GELU, be.OP_FUSED_LAYER_NORM,
+               be.OP_FUSED_ATTENTION_QKV_PROJECTION, be.OP_ALL_REDUCE, be.OP_ALL_GATHER):
         assert caps.Operations.get(op)
+    assert len(caps.Operations) == 12        # element-wise and data-movement helpers exist but are not advertised
     assert caps.DTypes.get(dv.BF16) and caps.DTypes.get(dv.F64) and not caps.Functions
     assert not backend.HasSharedBuffers()
 
@@ -114,8 +116,10 @@ def test_dot_general_validation(backend):
     with pytest.raises(BackendError):   # axis used twice
         f.DotGeneral(a, [1], [1], b, [0], [0])
     with pytest.raises(ErrNotImplemented):
-        f.Neg(a)
+        f.Abs(a)
     with pytest.raises(ErrNotImplemented):
+        f.While(a)
+    with pytest.raises(BackendError):   # ReduceOpUndefined
         f.AllReduce([a], 0, [[0]])
 
 
