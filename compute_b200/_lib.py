@@ -116,6 +116,7 @@ SIGNATURES = {
     "cb_ipc_close": ([C.c_int, C.c_void_p], C.c_int),
     "cb_peer_signal": ([C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p], C.c_int),
     "cb_peer_wait": ([C.c_int, C.c_void_p, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p], C.c_int),
+    "cb_peer_signal_wait": ([C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p], C.c_int),
     "cb_comm_unique_id": ([C.c_char_p], C.c_int),
     "cb_comm_init_rank": ([C.c_int, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
     "cb_comm_size": ([C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)], C.c_int),

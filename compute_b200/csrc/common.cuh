@@ -118,6 +118,7 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
 // out[i] = reduction over r of stacked[r][i], r in rank order (the local step of AllReduce)
 int stacked_reduce_launch(int dtype, int op, const void* stacked, int g, int64_t n, void* out, cudaStream_t s);
 int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s);
+int peer_signal_wait_launch(void* const* flags, int n_ranks, int slot, const unsigned* local, uint32_t target, unsigned* status_word, cudaStream_t s);
 int peer_wait_launch(const unsigned* flags, int n_flags, uint32_t target, unsigned* status_word, cudaStream_t s);
 
 // ---- device scalar helpers --------------------------------------------------

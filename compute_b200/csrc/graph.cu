@@ -1278,11 +1278,13 @@ int cbg_fn_parameter_sharded(cbg_function* f, const char* name, int32_t dtype, i
     return fail(CB_ERR_INVALID_ARG, "%s: sharding spec is NULL", op);
   if (n_axis_specs > rank) return fail(CB_ERR_INVALID_ARG, "%s: ShardingSpec has %d axes, the parameter has rank %d", op, n_axis_specs, rank);
   std::vector<bool> used(n_mesh_axes, false);
-  std::string text;
+  std::string text;                 // per tensor axis its mesh axes joined by ',', tensor axes joined by ';'
+  bool sharded = false;
   for (int a = 0; a < n_axis_specs; a++) {
     std::stringstream ss(axis_specs[a] ? axis_specs[a] : "");
     std::string nm;
-    text += a ? ";" : "";
+    if (a) text += ";";
+    bool first = true;
     while (std::getline(ss, nm, ',')) {
       if (nm.empty()) continue;
       int idx = -1;
@@ -1290,11 +1292,13 @@ int cbg_fn_parameter_sharded(cbg_function* f, const char* name, int32_t dtype, i
       if (idx < 0) return fail(CB_ERR_INVALID_ARG, "ShardingSpec axis #%d refers to unknown mesh axis \"%s\"", a, nm.c_str());
       if (used[idx]) return fail(CB_ERR_INVALID_ARG, "mesh axis \"%s\" used more than once in ShardingSpec", nm.c_str());
       used[idx] = true;
-      text += nm + ",";
+      text += (first ? "" : ",") + nm;
+      first = false;
+      sharded = true;
     }
   }
   CB_TRY(cbg_fn_parameter(f, name, dtype, rank, dims, v));
-  (*v)->sharding = text.empty() ? "replicated" : text;
+  (*v)->sharding = sharded ? text : "replicated";
   return CB_OK;
 }
 

@@ -678,6 +678,46 @@ __global__ void peer_signal_kernel(PeerFlags flags, int n_ranks, int slot) {
   }
 }
 
+// Both steps in one launch, chained to the kernels before and after it by programmatic dependent launch (its
+// launch latency overlaps the tail of the kernel whose stores it announces, and the next kernel of the stream is
+// scheduled while it polls): signals once the preceding kernels have completed, then waits for every rank.
+__global__ void peer_signal_wait_kernel(PeerFlags flags, int n_ranks, int slot, const unsigned* local, unsigned target, unsigned* status_word) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < n_ranks; r++) atomicAdd_system(flags.f[r] + slot, 1u);
+  }
+  const int i = threadIdx.x;
+  if (i >= n_ranks) return;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local + i) : "memory");
+    if ((int)(v - target) >= 0) break;
+    if (global_ns() - t0 > WAIT_NS) { atomicExch(status_word, 1u + (unsigned)i); break; }
+    __nanosleep(100);
+  }
+}
+
+int peer_signal_wait_launch(void* const* flags, int n_ranks, int slot, const unsigned* local, uint32_t target, unsigned* status_word, cudaStream_t s) {
+  if (n_ranks < 1 || n_ranks > QT_MAX_RANKS) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal_wait: %d ranks", n_ranks);
+  PeerFlags pf;
+  for (int r = 0; r < QT_MAX_RANKS; r++) pf.f[r] = r < n_ranks ? (unsigned*)flags[r] : nullptr;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB_CUDA(cudaLaunchKernelEx(&cfg, peer_signal_wait_kernel, pf, n_ranks, slot, local, (unsigned)target, status_word));
+  return CB_OK;
+}
+
 int peer_signal_launch(void* const* flags, int n_ranks, int slot, cudaStream_t s) {
   if (n_ranks < 1 || n_ranks > QT_MAX_RANKS) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal: %d ranks", n_ranks);
   PeerFlags pf;

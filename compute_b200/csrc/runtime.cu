@@ -268,6 +268,16 @@ int cb_peer_wait(int dev, const void* flags, int n_flags, uint32_t target, void*
   return cb::peer_wait_launch((const unsigned*)flags, n_flags, target, (unsigned*)status_word, (cudaStream_t)stream);
 }
 
+int cb_peer_signal_wait(int dev, void* const* flags, int n_ranks, int slot, const void* local_flags, uint32_t target,
+                        void* status_word, cb_stream stream) {
+  CB_TRY(set_device(dev));
+  if (!flags || !local_flags || !status_word) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal_wait: null argument");
+  if (slot < 0 || slot >= 32) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal_wait: slot %d", slot);
+  for (int r = 0; r < n_ranks && r < 8; r++)
+    if (!flags[r]) return fail(CB_ERR_INVALID_ARG, "cb_peer_signal_wait: null flag array for rank %d", r);
+  return cb::peer_signal_wait_launch(flags, n_ranks, slot, (const unsigned*)local_flags, target, (unsigned*)status_word, (cudaStream_t)stream);
+}
+
 int cb_stream_wait_event(int dev, cb_stream stream, cb_event ev) {
   CB_TRY(set_device(dev));
   CB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0));

@@ -123,6 +123,20 @@ def peer_wait(dev: int, flags: int, n_flags: int, target: int, status_word: int,
     check(_lib.load().cb_peer_wait(dev, flags, n_flags, target & 0xFFFFFFFF, status_word, stream.handle if stream else None))
 
 
+class PeerBarrier:
+    """cb_peer_signal_wait with its argument array built once: one call per step signals this rank's slices and waits
+    for everyone's."""
+
+    def __init__(self, dev: int, flag_arrays: Sequence[int], rank: int, local_flags: int, status_word: int):
+        self.dev, self.rank, self.n = dev, rank, len(flag_arrays)
+        self._arr = (C.c_void_p * self.n)(*flag_arrays)
+        self.local, self.status = local_flags, status_word
+
+    def signal_wait(self, target: int, stream=None) -> None:
+        check(_lib.load().cb_peer_signal_wait(self.dev, self._arr, self.n, self.rank, self.local, target & 0xFFFFFFFF, self.status,
+                                              stream.handle if stream else None))
+
+
 REDUCE_SUM, REDUCE_PRODUCT, REDUCE_MAX, REDUCE_MIN = range(4)
 BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_MAX, BIN_MIN = range(6)
 UN_NEG, UN_RSQRT, UN_SQRT, UN_EXP, UN_LOGISTIC, UN_TANH = range(6)

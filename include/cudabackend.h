@@ -301,6 +301,11 @@ int cb_ipc_open(int dev, const unsigned char* handle, void** dptr);
 int cb_ipc_close(int dev, void* dptr);
 int cb_peer_signal(int dev, void* const* flags /* one array per rank */, int n_ranks, int slot, cb_stream stream);
 int cb_peer_wait(int dev, const void* flags, int n_flags, uint32_t target, void* status_word, cb_stream stream);
+/* Both in one kernel (one launch fewer per step, chained to its neighbours in the stream by programmatic dependent
+ * launch): adds 1 to word `slot` of every rank's flag array once the earlier work of the stream has completed, then
+ * waits (bounded, as cb_peer_wait) until local_flags[0..n_ranks) have all reached `target`. */
+int cb_peer_signal_wait(int dev, void* const* flags /* one array per rank */, int n_ranks, int slot, const void* local_flags,
+                        uint32_t target, void* status_word, cb_stream stream);
 
 /* ---- collectives: one communicator rank per process and GPU (NCCL, loaded at run time)
  * Replace CollectiveOps.AllReduce (collectiveops.go:10-39) and provide the all-gather at a

@@ -40,6 +40,10 @@ def _worker(rank, g, conn):
             plan.launch([xd.ptr, wd.ptr, sd.ptr], outs, ws.ptr, st)
             dv.peer_signal(dev, fls, rank, st)
             dv.peer_wait(dev, flags.ptr, g, rep + 1, flags.ptr + 64, st)
+        # the same step with the signal and the wait as one kernel
+        barrier = dv.PeerBarrier(dev, fls, rank, flags.ptr, flags.ptr + 64)
+        plan.launch([xd.ptr, wd.ptr, sd.ptr], outs, ws.ptr, st)
+        barrier.signal_wait(4, st)
         st.sync()
         plan.check_status(ws.ptr)
         got = y.download((M, N), np.uint16)
@@ -85,6 +89,6 @@ def test_two_processes_two_gpus():
     for r, res in enumerate(results):
         assert res[0] == "ok", res
         _, got, arrivals, status = res
-        assert arrivals == [3, 3] and status == 0
+        assert arrivals == [4, 4] and status == 0
         assert max_abs_normalised(orc.bf16_to_f32(got), want) < 2e-2
     assert np.array_equal(results[0][1], results[1][1])

@@ -295,7 +295,7 @@ def test_column_sharded_projection_as_one_spmd_executable(backend, g):
     (total,) = f.AllReduce([f.ConvertDType(y_loc, dv.F32)], be.REDUCE_OP_SUM, groups)
     f.Return([y_all, total])
     exe = builder.Compile()
-    assert exe.InputSharding(1) == "tp," and exe.InputSharding(0) == "replicated"
+    assert exe.InputSharding(1) == ";tp" and exe.InputSharding(0) == "replicated"
     assert "all_gather" in exe.KernelNames() and "all_reduce" in exe.KernelNames()
     inputs = []
     for r in range(g):
