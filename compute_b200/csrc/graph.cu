@@ -289,6 +289,17 @@ cbg_value* reshape_node(cbg_function* f, cbg_value* x, const std::vector<int64_t
 // host <-> device through a pinned staging buffer and a pooled stream (to_device: host -> device)
 int staged_copy(cbg_backend* be, int dev, void* dptr, void* host, size_t bytes, bool to_device) {
   if (bytes == 0) return CB_OK;
+  // The caller's memory is itself page-locked (from cb_host_alloc, or registered): no staging copy is needed.
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost) {
+    cb_stream s = nullptr;
+    CB_TRY(be->get_stream(dev, &s));
+    int st = to_device ? cb_h2d(dev, dptr, host, bytes, s) : cb_d2h(dev, host, dptr, bytes, s);
+    if (st == CB_OK) st = cb_stream_sync(dev, s);
+    be->put_stream(dev, s);
+    return st;
+  }
+  (void)cudaGetLastError();
   if (bytes > PINNED_STAGING_MAX) return to_device ? cb_h2d(dev, dptr, host, bytes, nullptr) : cb_d2h(dev, host, dptr, bytes, nullptr);
   void* pin = nullptr;
   size_t cap = 0;

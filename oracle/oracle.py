@@ -494,3 +494,58 @@ def qdense_ggml(x, w_blocks, bias=None, ggml_type: int = GGML_Q8_0, activation: 
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int]
     fn(_p(x), _p(w_blocks), _p(b), _p(out), M, K, N, ggml_type, activation)
     return out
+
+
+# ---------------------------------------------------------------- decoder block (composition of the ops above)
+def _bf(a: np.ndarray) -> np.ndarray:
+    """Round float32 values to bfloat16 and back (what a bfloat16 graph stores between ops)."""
+    return bf16_to_f32(bf16_from_f32(np.ascontiguousarray(a, np.float32)))
+
+
+def rms_norm(x: np.ndarray, gamma: np.ndarray, eps: float) -> np.ndarray:
+    x64 = np.asarray(x, np.float64)
+    return (x64 / np.sqrt((x64 ** 2).mean(-1, keepdims=True) + eps) * np.asarray(gamma, np.float64)).astype(np.float32)
+
+
+def decoder_block(x, weights, heads: int, kv_heads: int, head_dim: int, eps: float, cache_k=None, cache_v=None,
+                  rows=None, threads: int = 1):
+    """The Llama-style block of the fifth benchmark configuration from the reference's ops: RMS norm, int8 per-channel
+    quantized dense (quantizeddense.go:616-650) for q / k / v / o / gate / up / down, fused SDPA (sdpa.go:373-636, BSHD,
+    grouped KV heads), SwiGLU, residuals; every op's result is rounded to bfloat16, as a bfloat16 graph stores it.
+    x: [B, S, H] float32 values.  Prefill (no cache): causal attention over the S tokens; with `rows` = list of (b, s)
+    only those tokens' outputs are computed beyond the key / value projections (which all tokens need).  Decode:
+    attention over cache_k / cache_v [B, Skv, kv_heads, head_dim].  Returns y (for `rows` when given), k, v."""
+    B, S, H = x.shape
+    qd = lambda a, name, act=ACT_NONE: _bf(qdense_linear(np.ascontiguousarray(a, np.float32).reshape(-1, a.shape[-1]), weights[name],
+                                                         np.repeat(weights[name + "_scale"], weights[name].shape[0], axis=0), None, None, 1, act,
+                                                         threads=threads, fast=True))
+    g1, g2 = bf16_to_f32(weights["g1"]), bf16_to_f32(weights["g2"])
+    h = _bf(rms_norm(x, g1, eps))
+    k = qd(h, "wk").reshape(B, S, kv_heads, head_dim)
+    v = qd(h, "wv").reshape(B, S, kv_heads, head_dim)
+    if cache_k is not None:
+        q = qd(h, "wq").reshape(B, S, heads, head_dim)
+        att = _bf(sdpa(q, cache_k, cache_v, layout="BSHD", causal=False, fast=True))
+        sel_x, sel_att = x.reshape(B * S, H), att.reshape(B * S, heads * head_dim)
+    elif rows is None:
+        q = qd(h, "wq").reshape(B, S, heads, head_dim)
+        att = _bf(sdpa(q, k, v, layout="BSHD", causal=True, fast=True))
+        sel_x, sel_att = x.reshape(B * S, H), att.reshape(B * S, heads * head_dim)
+    else:
+        sel_x = np.stack([x[b, s] for b, s in rows])
+        hq = np.stack([h[b, s] for b, s in rows])
+        q = qd(hq, "wq").reshape(len(rows), heads, head_dim)
+        att = np.empty((len(rows), heads, head_dim), np.float32)
+        for i, (b, s) in enumerate(rows):       # a token attends to the tokens up to itself: one query row per call
+            att[i] = sdpa(q[i][None, None], k[b:b + 1, :s + 1], v[b:b + 1, :s + 1], layout="BSHD", causal=False, fast=True)[0, 0]
+        sel_att = _bf(att).reshape(len(rows), heads * head_dim)
+    o = qd(sel_att, "wo")
+    x1 = _bf(sel_x + o)
+    h2 = _bf(rms_norm(x1, g2, eps))
+    gate = qd(h2, "wg", ACT_SILU)
+    up = qd(h2, "wu")
+    d = qd(_bf(gate * up), "wd")
+    y = _bf(x1 + d)
+    if rows is None:
+        y = y.reshape(B, S, H)
+    return y, k, v
