@@ -241,6 +241,48 @@ def sdpa_leg(dv, dev, stream, hq, hkv, tpeak, check=False):
     return out
 
 
+def decoder_block_legs():
+    """The fifth configuration: one Llama-style decoder block (hidden 4096, 32 / 8 heads of 128, MLP 14336, int8
+    per-channel projections, bf16 activations) as one Executable, prefill 4 x 512 tokens and decode 16 x 1 token over a
+    key / value cache of 2048 positions.  Inputs are resident buffers; the time is wall clock per Executable.Execute
+    (launches plus the final sync), results finalised every step."""
+    from compute_b200 import backend as be, decoder_block as blk
+    cfg = blk.BlockConfig()
+    backend = be.New("")
+    weights = blk.make_block_weights(cfg, 5)
+    rng = np.random.default_rng(9)
+    out = {}
+    for mode, (B, S, kv) in (("config5_decode_16x1_kv2048", (16, 1, 2048)), ("config5_prefill_4x512", (4, 512, 0))):
+        exe, names = blk.compile_block(backend, cfg, B, S, kv)
+        host = dict(weights)
+        host["x"] = bf16_bits(rng.standard_normal((B, S, cfg.hidden), dtype=np.float32))
+        if kv:
+            host["cache_k"] = bf16_bits(rng.standard_normal((B, kv, cfg.kv_heads, cfg.head_dim), dtype=np.float32))
+            host["cache_v"] = bf16_bits(rng.standard_normal((B, kv, cfg.kv_heads, cfg.head_dim), dtype=np.float32))
+        bufs = [backend.BufferFromFlatData(0, host[n], blk.parameter_shape(n, cfg, B, S, kv)) for n in names]
+
+        def step():
+            for o in exe.Execute(bufs, None, 0):
+                o.Finalize()
+        for _ in range(3):
+            step()
+        reps = 30 if kv else 10
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            step()
+        ms_block = (time.perf_counter() - t0) / reps * 1e3
+        tokens = B * S
+        weight_bytes = sum(int(np.prod(v.shape)) for k_, v in weights.items() if k_ in blk.PROJECTIONS)
+        flops = 2.0 * tokens * weight_bytes + (4.0 * B * cfg.heads * cfg.head_dim * (S * (S + 1) / 2 if not kv else kv))
+        out[mode] = {"ms_per_block": ms_block, "tokens": tokens, "kernels": exe.KernelNames(),
+                     "weight_GB/s": weight_bytes / ms_block / 1e6, "TFLOP/s": flops / ms_block / 1e9}
+        for b in bufs:
+            b.Finalize()
+        exe.Finalize()
+    backend.Finalize()
+    return out
+
+
 # --------------------------------------------------------------------------- CPU baselines
 def cpu_baseline(M: int, seconds: float = 12.0):
     """The oracle port (the reference's scalar loop nest with its row / N-tile parallel split) timed on the host
@@ -761,6 +803,7 @@ def main():
                 p2.check_status(ws2.ptr)
             out["other_decode_batches"] = extra
             out["other_path_kernels"] = other_kernels(dv, dev, stream)
+            out["decoder_block"] = decoder_block_legs()
         if not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(M)
             if not args.no_extra:

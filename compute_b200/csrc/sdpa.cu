@@ -11,6 +11,9 @@ int sdpa_generic_launch(const cb_plan* p, const void* const* in, void* const* ou
 bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why);
 int sdpa_flash_plan(cb_plan* p);
 int sdpa_flash_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+bool sdpa_decode_supports(const cb_sdpa_desc& d, std::string* why);
+int sdpa_decode_plan(cb_plan* p);
+int sdpa_decode_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int sdpa_validate_operands(const cb_sdpa_desc& d);
 
 int sdpa_plan(cb_plan* p) {
@@ -32,7 +35,15 @@ int sdpa_plan(cb_plan* p) {
   int variant = d.variant;
   std::string why;
   const bool flash_ok = sdpa_flash_supports(d, &why);
-  if (variant == CB_SDPA_AUTO) variant = flash_ok ? CB_SDPA_FLASH : CB_SDPA_GENERIC;
+  std::string why_decode;
+  const bool decode_ok = sdpa_decode_supports(d, &why_decode);
+  // long query tiles go to the tensor-core kernel, a few query tokens over a long cache to the streaming kernel
+  if (variant == CB_SDPA_AUTO) variant = flash_ok ? CB_SDPA_FLASH : (decode_ok ? CB_SDPA_DECODE : CB_SDPA_GENERIC);
+  if (variant == CB_SDPA_DECODE) {
+    if (!decode_ok) return fail(CB_ERR_NOT_IMPLEMENTED, "%s decode kernel: %s", op, why_decode.c_str());
+    p->variant = variant;
+    return sdpa_decode_plan(p);
+  }
   if (variant == CB_SDPA_FLASH) {
     if (!flash_ok) return fail(CB_ERR_NOT_IMPLEMENTED, "%s flash kernel: %s", op, why.c_str());
     p->variant = variant;
@@ -44,6 +55,7 @@ int sdpa_plan(cb_plan* p) {
 
 int sdpa_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   if (p->variant == CB_SDPA_FLASH) return sdpa_flash_launch(p, in, out, ws, s);
+  if (p->variant == CB_SDPA_DECODE) return sdpa_decode_launch(p, in, out, ws, s);
   return sdpa_generic_launch(p, in, out, s);
 }
 

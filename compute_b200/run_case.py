@@ -2,7 +2,9 @@
 
     python -m compute_b200.run_case gemm --dtype bf16 --b 1 --m 4096 --n 4096 --k 4096
     python -m compute_b200.run_case sdpa --b 8 --hq 32 --hkv 8 --s 2048 --d 128 --causal
+    python -m compute_b200.run_case sdpa --b 16 --sq 1 --s 2048 --bshd      # one new token against a 2048-key cache
     python -m compute_b200.run_case qdense --m 16            # decode (M <= 16) or prefill (M > 16)
+    python -m compute_b200.run_case qdense --m 16 --layers 8 # eight independent projections as one grouped launch
     python -m compute_b200.run_case softmax --m 65536 --n 4096   # also: gelu, layernorm (rows --m, row length --n)
 
 A small stand-alone driver for timing or profiling a single plan (inputs are seeded random
@@ -49,6 +51,9 @@ def main() -> None:
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--s", type=int, default=2048)
     ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--sq", type=int, default=0, help="query length when it differs from the key length --s")
+    ap.add_argument("--bshd", action="store_true", help="[batch, seq, heads, dim] operands instead of [batch, heads, seq, dim]")
+    ap.add_argument("--layers", type=int, default=1, help="qdense: this many independent projections as one grouped launch")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--layout", default="kgroup", choices=["channel", "kgroup"])
     ap.add_argument("--group", type=int, default=128)
@@ -72,14 +77,17 @@ def main() -> None:
         us = _time(plan, [lhs.ptr, rhs.ptr], [res.ptr], dev, stream, a.reps, a.warmup)
         out.update(kernel=plan.kernel_name, us=us, tflops=2.0 * a.b * a.m * a.n * a.k / us / 1e6)
     elif a.case == "sdpa":
-        q = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hq * a.s * a.d, 1.0), dev)
+        sq = a.sq or a.s
+        q = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hq * sq * a.d, 1.0), dev)
         k = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
         v = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
-        o = dv.DeviceMem(a.b * a.hq * a.s * a.d * 2, dev)
-        plan = dv.Plan.sdpa(a.b, a.hq, a.hkv, a.s, a.s, a.d, dv.BF16, causal=a.causal, dev=dev)
+        o = dv.DeviceMem(a.b * a.hq * sq * a.d * 2, dev)
+        plan = dv.Plan.sdpa(a.b, a.hq, a.hkv, sq, a.s, a.d, dv.BF16, causal=a.causal,
+                            layout=dv.LAYOUT_BSHD if a.bshd else dv.LAYOUT_BHSD, dev=dev)
         us = _time(plan, [q.ptr, k.ptr, v.ptr], [o.ptr], dev, stream, a.reps, a.warmup)
-        pairs = a.s * (a.s + 1) / 2 if a.causal else a.s * a.s
-        out.update(kernel=plan.kernel_name, us=us, tflops=4.0 * a.b * a.hq * a.d * pairs / us / 1e6)
+        pairs = (a.s * (a.s + 1) / 2 if a.causal else a.s * a.s) if sq == a.s else sq * a.s
+        out.update(kernel=plan.kernel_name, us=us, tflops=4.0 * a.b * a.hq * a.d * pairs / us / 1e6,
+                   kv_GBps=2.0 * a.b * a.hkv * a.s * a.d * 2 / us / 1e3)
     elif a.case in ("softmax", "gelu", "layernorm"):
         code = dv.BF16 if a.dtype == "bf16" else dv.F32
         size = 2 if a.dtype == "bf16" else 4
@@ -105,10 +113,21 @@ def main() -> None:
         rows = 1 if a.layout == "channel" else -(-K // a.group)
         sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=rows * N).astype(np.float32), dev)
         y = dv.DeviceMem(a.m * N * (2 if a.dtype == "bf16" else 4), dev)
-        plan = dv.Plan.qdense(a.m, K, N, code, dv.I8, dv.SCALE_CHANNEL if a.layout == "channel" else dv.SCALE_KGROUP,
-                              a.group, False, False, dv.ACT_SILU, dev=dev)
-        us = _time(plan, [x.ptr, w.ptr, sc.ptr], [y.ptr], dev, stream, a.reps, a.warmup)
-        out.update(kernel=plan.kernel_name, us=us, weight_GBps=K * N / us / 1e3, tflops=2.0 * a.m * K * N / us / 1e6)
+        layout = dv.SCALE_CHANNEL if a.layout == "channel" else dv.SCALE_KGROUP
+        if a.layers > 1:
+            # independent projections (own weights, scales, outputs; one shared activation) as one launch
+            ws_ = [w] + [dv.DeviceMem.from_numpy(rng.integers(-127, 128, size=K * N, dtype=np.int8), dev) for _ in range(a.layers - 1)]
+            ys = [y] + [dv.DeviceMem(a.m * N * (2 if a.dtype == "bf16" else 4), dev) for _ in range(a.layers - 1)]
+            plan = dv.Plan.qdense_group(a.m, K, [(N, False, dv.ACT_SILU)] * a.layers, code, dv.I8, layout, a.group, dev=dev)
+            ins = []
+            for wl in ws_:
+                ins += [x.ptr, wl.ptr, sc.ptr]
+            us = _time(plan, ins, [t.ptr for t in ys], dev, stream, a.reps, a.warmup)
+        else:
+            plan = dv.Plan.qdense(a.m, K, N, code, dv.I8, layout, a.group, False, False, dv.ACT_SILU, dev=dev)
+            us = _time(plan, [x.ptr, w.ptr, sc.ptr], [y.ptr], dev, stream, a.reps, a.warmup)
+        out.update(kernel=plan.kernel_name, blocks=plan.blocks, us=us, weight_GBps=a.layers * K * N / us / 1e3,
+                   tflops=2.0 * a.layers * a.m * K * N / us / 1e6)
     print(json.dumps(out))
 
 

@@ -136,3 +136,39 @@ def test_sdpa_flash_ragged_shapes(B, Hq, Hkv, S, Skv, layout, dtype, causal):
     assert plan.kernel_name.startswith("sdpa_flash_")
     want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), layout=layout, causal=causal)
     assert max_abs_normalised(orc.to_f32(got, code), want) < 2e-2
+
+
+# ------------------------------------------------------------- decode shapes: a few query tokens over a long cache
+DECODE_CASES = [
+    # B, Hq, Hkv, S, Skv, D, layout, dtype, causal
+    (16, 32, 8, 1, 2048, 128, "BSHD", "bf16", False),      # the decode step of the fifth benchmark configuration
+    (2, 8, 8, 1, 300, 64, "BHSD", "f16", False),           # no grouping, head_dim 64, a cache that is no multiple of anything
+    (3, 8, 2, 2, 1000, 128, "BHSD", "bf16", False),        # two query tokens, group of 4: 8 rows per KV head
+    (2, 4, 2, 2, 257, 128, "BSHD", "bf16", True),          # causal as the reference defines it: row s sees the keys 0..s
+    (1, 16, 4, 1, 8192, 128, "BHSD", "bf16", False),       # one sequence: the cache is split many ways
+    (2, 32, 2, 1, 1024, 128, "BSHD", "bf16", False),       # a group of 16 query heads: both halves of the 16-row tile
+    (2, 8, 2, 3, 515, 64, "BHSD", "f16", True),            # 12 rows (3 tokens x group of 4), causal, head_dim 64
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,Skv,D,layout,dtype,causal", DECODE_CASES)
+def test_sdpa_decode_kernel(B, Hq, Hkv, S, Skv, D, layout, dtype, causal):
+    rng = np.random.default_rng(B * 1000 + Skv)
+    code = DT[dtype]
+    shape = (lambda h, s: (B, s, h, D)) if layout == "BSHD" else (lambda h, s: (B, h, s, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shape(h, s), dtype=np.float32), code) for h, s in ((Hq, S), (Hkv, Skv), (Hkv, Skv)))
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, return_plan=True)
+    assert plan.kernel_name.startswith("sdpa_decode_"), plan.kernel_name
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), layout=layout, causal=causal)
+    assert max_abs_normalised(orc.to_f32(got, code), want) < 2e-2
+    # the generic kernel (the reference's per-row algorithm) agrees more tightly than the tolerance
+    gen = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, variant=dv.SDPA_GENERIC)
+    assert max_abs_normalised(orc.to_f32(got, code), orc.to_f32(gen, code)) < 2.0 ** -7
+
+
+def test_sdpa_decode_kernel_is_refused_where_it_does_not_apply():
+    with pytest.raises(ErrNotImplemented):      # float32 stays on the generic kernel
+        dv.Plan.sdpa(2, 8, 2, 1, 1024, 128, dv.F32, variant=dv.SDPA_DECODE)
+    with pytest.raises(ErrNotImplemented):      # more query rows per KV head than a CTA carries
+        dv.Plan.sdpa(2, 64, 2, 1, 1024, 128, dv.BF16, variant=dv.SDPA_DECODE)
+    assert dv.Plan.sdpa(2, 8, 2, 1, 64, 128, dv.BF16).kernel_name.startswith("sdpa_generic")      # a short cache
