@@ -119,6 +119,9 @@ SIGNATURES = {
     "cb_peer_signal_wait": ([C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p], C.c_int),
     "cb_comm_unique_id": ([C.c_char_p], C.c_int),
     "cb_comm_init_rank": ([C.c_int, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_comm_init_rank_timeout": ([C.c_int, C.c_int, C.c_int, C.c_char_p, C.c_double, C.POINTER(C.c_void_p)], C.c_int),
+    "cb_comm_check": ([C.c_void_p], C.c_int),
+    "cb_comm_sync": ([C.c_void_p, C.c_void_p, C.c_double], C.c_int),
     "cb_comm_size": ([C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)], C.c_int),
     "cb_comm_allgather": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p], C.c_int),
     "cb_comm_allreduce": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_void_p], C.c_int),

@@ -11,6 +11,7 @@ with an explicit dtype (compute_b200.device.BF16 / F16).
 from __future__ import annotations
 
 import ctypes as C
+import re
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -109,6 +110,7 @@ _GRAPH_SIGNATURES = {
     "cbg_exec_input_info": ([C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
     "cbg_exec_output_info": ([C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
     "cbg_exec_kernel_names": ([C.c_void_p, C.c_char_p, C.c_size_t], C.c_int),
+    "cbg_exec_last_trace": ([C.c_void_p, C.c_char_p, C.c_size_t], C.c_int),
     "cbg_exec_execute": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_uint8), C.c_int, C.POINTER(C.c_void_p), C.c_int], C.c_int),
     "cbg_exec_finalize": ([C.c_void_p], C.c_int),
 }
@@ -572,6 +574,20 @@ class Executable:
         buf = C.create_string_buffer(4096)
         check(_g().cbg_exec_kernel_names(self.handle, buf, 4096))
         return [s for s in buf.value.decode().split("\n") if s]
+
+    def LastTrace(self) -> List[dict]:
+        """The per-launch device times of the latest Execute when the backend was created with the
+        "trace" option (or CUDABACKEND_TRACE=1): one dict per launch (device, node, kernel, out, us)."""
+        buf = C.create_string_buffer(1 << 16)
+        check(_g().cbg_exec_last_trace(self.handle, buf, 1 << 16))
+        rows = []
+        pat = re.compile(r"cudabackend trace: exec=(\S+) device=(\d+) node=(\d+) kernel=(\S+) out=(.*) us=([0-9.]+)$")
+        for line in buf.value.decode().split("\n"):
+            m = pat.match(line)
+            if m:
+                rows.append({"exec": m.group(1), "device": int(m.group(2)), "node": int(m.group(3)), "kernel": m.group(4),
+                             "out": m.group(5), "us": float(m.group(6))})
+        return rows
 
     def Execute(self, inputs: Sequence[Buffer], donate: Optional[Sequence[bool]] = None, defaultDevice: int = 0) -> List[Buffer]:
         n_in = len(inputs)

@@ -201,6 +201,53 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restri
     __syncthreads();      // s_part / s_inv are rewritten for the next row
   }
 }
+// The streaming form for rows whose bytes are a multiple of 16 and that fit 16 vectors per lane: one warp per row,
+// the row read once with 16-byte loads into registers, reduced by shuffles (no shared memory, no block barrier),
+// written with 16-byte stores.  NV = vectors per lane.
+template <typename T, int NV>
+__global__ void __launch_bounds__(RMS_THREADS)
+rmsnorm_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, int64_t rows, int64_t L, float eps) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (RMS_THREADS / 32) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (RMS_THREADS / 32);
+  const int64_t n_vec = L / VEC;
+  for (int64_t row = warp; row < rows; row += n_warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * L);
+    uint4 raw[NV];
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      const int64_t c = lane + (int64_t)j * 32;
+      raw[j] = c < n_vec ? __ldg(xr + c) : make_uint4(0, 0, 0, 0);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      const T* e = reinterpret_cast<const T*>(&raw[j]);
+#pragma unroll
+      for (int i = 0; i < VEC; i++) { const float t = (float)e[i]; ss = fmaf(t, t, ss); }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+    const float inv = rsqrtf(ss / (float)L + eps);
+    uint4* orow = reinterpret_cast<uint4*>(out + row * L);
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      const int64_t c = lane + (int64_t)j * 32;
+      if (c < n_vec) {
+        uint4 gv = make_uint4(0, 0, 0, 0);
+        if (gamma) gv = __ldg(reinterpret_cast<const uint4*>(gamma) + c);
+        const T* e = reinterpret_cast<const T*>(&raw[j]);
+        const T* ge = reinterpret_cast<const T*>(&gv);
+        uint4 ov;
+        T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+        for (int i = 0; i < VEC; i++) oe[i] = (T)((float)e[i] * inv * (gamma ? (float)ge[i] : 1.0f));
+        orow[c] = ov;
+      }
+    }
+  }
+}
 template <>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel<double>(const double* __restrict__ x, const double* __restrict__ gamma, double* __restrict__ out, int64_t rows, int64_t L, float eps) {
@@ -398,7 +445,24 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
     case PLAN_RMSNORM:
       CB_TRY(by_float(h.dtype, "rms norm", [&](auto* t) {
         typedef typename std::remove_pointer<decltype(t)>::type T;
-        rmsnorm_kernel<T><<<p->blocks, RMS_THREADS, 0, s>>>((const T*)in[0], (h.flags & 1) ? (const T*)in[1] : nullptr, (T*)out[0], h.dims[0], h.dims[1], (float)h.eps);
+        const T* g = (h.flags & 1) ? (const T*)in[1] : nullptr;
+        if constexpr (sizeof(T) <= 4) {
+          constexpr int VEC = 16 / (int)sizeof(T);
+          const int64_t L = h.dims[1], per_lane = (L / VEC + 31) / 32;
+          const bool aligned = !((reinterpret_cast<uintptr_t>(in[0]) | reinterpret_cast<uintptr_t>(out[0]) | reinterpret_cast<uintptr_t>(g)) & 15);
+          if (L % VEC == 0 && per_lane <= 16 && aligned) {
+            const int64_t want = (h.dims[0] + RMS_THREADS / 32 - 1) / (RMS_THREADS / 32);
+            const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)p->n_sm * 8));
+            auto go = [&](auto nv) {
+              rmsnorm_warp_kernel<T, decltype(nv)::value><<<grid, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], L, (float)h.eps);
+            };
+            if (per_lane <= 1) go(std::integral_constant<int, 1>()); else if (per_lane <= 2) go(std::integral_constant<int, 2>());
+            else if (per_lane <= 4) go(std::integral_constant<int, 4>()); else if (per_lane <= 8) go(std::integral_constant<int, 8>());
+            else go(std::integral_constant<int, 16>());
+            return (int)CB_OK;
+          }
+        }
+        rmsnorm_kernel<T><<<p->blocks, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], h.dims[1], (float)h.eps);
         return (int)CB_OK;
       }));
       break;

@@ -122,6 +122,7 @@ struct cbg_backend {
   int n_devices = 0;
   PinnedPool pinned;
   bool fallback_only = false;
+  bool trace = false;                 // option "trace" or CUDABACKEND_TRACE=1: per-launch device times of every Execute
   std::atomic<bool> finalized{false};
   std::string name = "cuda", description;
   std::vector<std::unique_ptr<DevicePool>> pools;
@@ -206,6 +207,7 @@ struct cbg_exec {
   std::map<int, DevPlans> dev_plans;                                 // device -> plans (built at Compile for the assigned devices)
   std::map<int, std::vector<void*>> const_dev;                       // device -> per-node constant copy
   std::map<int, std::vector<std::vector<void*>>> idle_ws;            // device -> sets of prepared workspaces
+  std::string last_trace;                                            // the trace of the latest traced Execute (under mu)
   bool finalized = false;
 };
 
@@ -338,9 +340,11 @@ int cbg_backend_new(const char* config, cbg_backend** backend) {
   while (std::getline(ss, item, ',')) {
     if (item.empty()) continue;
     if (item == "fallback_only") b->fallback_only = true;
+    else if (item == "trace") b->trace = true;
     else if (item.rfind("devices=", 0) == 0) { /* accepted; device visibility is the process's */ }
     else return fail(CB_ERR_INVALID_ARG, "unknown configuration option \"%s\" for the cuda backend", item.c_str());
   }
+  if (const char* t = getenv("CUDABACKEND_TRACE")) b->trace = b->trace || (t[0] && strcmp(t, "0") != 0);   // read once, here
   int n = 0;
   CB_TRY(cb_init(&n));
   b->n_devices = n;
@@ -1657,6 +1661,14 @@ int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n) {
   return CB_OK;
 }
 
+int cbg_exec_last_trace(cbg_exec* e, char* buf, size_t n) {
+  cb::clear_error();
+  if (!e || !buf || n == 0) return fail(CB_ERR_INVALID_ARG, "NULL argument");
+  std::lock_guard<std::mutex> l(e->mu);
+  snprintf(buf, n, "%s", e->last_trace.c_str());
+  return CB_OK;
+}
+
 }  // extern "C"
 
 namespace {
@@ -1671,6 +1683,7 @@ struct Replica {
   std::vector<char> owned, taken;
   std::vector<std::pair<size_t, void*>> scratch;      // pool memory to give back after the final sync
   std::vector<cb_event> events;
+  std::vector<std::pair<int, cb_event>> marks;        // tracing: (node, event recorded after its launch); node -1 = start
   cbg_buffer* const* inputs = nullptr;
   const uint8_t* donate = nullptr;
   std::vector<cbg_buffer*> outs;
@@ -1905,17 +1918,49 @@ int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const
   for (; n_setup < e->replicas && st == CB_OK; n_setup++) st = setup_replica(e, reps[n_setup]);
   if (st != CB_OK) n_setup--;                 // the one that failed set nothing up that needs returning
   const size_t nn = f->nodes.size();
+  const bool trace = e->be->trace;
+  auto mark = [&](Replica& rp, int node) {       // an event on the replica's stream after the launch of `node`
+    cb_event ev = nullptr;
+    int ms = cb_event_create(rp.dev, &ev);
+    if (ms == CB_OK) ms = cb_event_record(rp.dev, ev, rp.stream);
+    if (ms == CB_OK) { rp.marks.emplace_back(node, ev); rp.events.push_back(ev); }
+    return ms;
+  };
+  if (trace) for (int r = 0; r < n_setup && st == CB_OK; r++) st = mark(reps[r], -1);
   for (size_t i = 0; i < nn && st == CB_OK; i++) {
     if (!e->live[i]) continue;
     cbg_value* n = f->nodes[i].get();
-    if (n->kind == N_ALLREDUCE || n->kind == N_ALLGATHER) { st = run_collective(e, n, reps); continue; }
-    for (int r = 0; r < e->replicas && st == CB_OK; r++) st = launch_node(e, reps[r], i);
+    if (n->kind == N_ALLREDUCE || n->kind == N_ALLGATHER) st = run_collective(e, n, reps);
+    else for (int r = 0; r < e->replicas && st == CB_OK; r++) st = launch_node(e, reps[r], i);
+    const bool launches = n->kind == N_ALLREDUCE || n->kind == N_ALLGATHER || (reps[0].dp->plans[i] && (e->group_of[i] < 0 || e->groups[e->group_of[i]][0] == (int)i));
+    if (trace && launches) for (int r = 0; r < e->replicas && st == CB_OK; r++) st = mark(reps[r], (int)i);
   }
   for (int r = 0; r < e->replicas && st == CB_OK; r++) st = collect_outputs(e, reps[r]);
   for (int r = 0; r < n_setup; r++) {
     if (!reps[r].stream) continue;
     const int sync_st = cb_stream_sync(reps[r].dev, reps[r].stream);
     if (st == CB_OK) st = sync_st;
+  }
+  if (trace && st == CB_OK) {
+    // one line per launch: device time between the events after the previous launch and after this one
+    std::string text;
+    char line[512];
+    for (int r = 0; r < n_setup; r++) {
+      const Replica& rp = reps[r];
+      for (size_t k = 1; k < rp.marks.size(); k++) {
+        float ms = 0.0f;
+        if (cb_event_elapsed_ms(rp.marks[k - 1].second, rp.marks[k].second, &ms) != CB_OK) continue;
+        const int i = rp.marks[k].first;
+        const cbg_value* nd = f->nodes[i].get();
+        const char* kn = rp.dp->plans[i] ? cb_plan_kernel_name(rp.dp->plans[i]) : (nd->kind == N_ALLREDUCE ? "all_reduce" : "all_gather");
+        snprintf(line, sizeof(line), "cudabackend trace: exec=%s device=%d node=%d kernel=%s out=%s us=%.2f\n",
+                 e->name.c_str(), rp.dev, i, kn, nd->shape.str().c_str(), ms * 1e3);
+        text += line;
+      }
+    }
+    fputs(text.c_str(), stderr);
+    std::lock_guard<std::mutex> l(e->mu);
+    e->last_trace = std::move(text);
   }
   // Kernels with bounded waits report through a status word in their workspace; a wait gives up only after two
   // seconds, so the words are read (one small blocking copy per plan) only when the call took that long.

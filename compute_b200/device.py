@@ -153,12 +153,23 @@ class Comm:
         check(_lib.load().cb_comm_unique_id(buf))
         return buf.raw
 
-    def __init__(self, dev: int, nranks: int, rank: int, uid: bytes):
+    def __init__(self, dev: int, nranks: int, rank: int, uid: bytes, timeout_s: float = 0.0):
+        """`timeout_s` bounds the initialisation and every later wait on the communicator (0: the
+        CUDABACKEND_COMM_TIMEOUT_S environment variable, else 600 s); when it passes the communicator
+        is aborted and BackendError(ERR_TIMEOUT) raised.  dev < 0: the current device."""
         assert len(uid) == COMM_ID_BYTES
         self.dev, self.nranks, self.rank = dev, nranks, rank
         h = C.c_void_p()
-        check(_lib.load().cb_comm_init_rank(dev, nranks, rank, uid, C.byref(h)))
+        check(_lib.load().cb_comm_init_rank_timeout(dev, nranks, rank, uid, float(timeout_s), C.byref(h)))
         self.handle = h
+
+    def check(self) -> None:
+        """One poll of the communicator's asynchronous state; raises once NCCL has reported an error."""
+        check(_lib.load().cb_comm_check(self.handle))
+
+    def sync(self, stream=None, timeout_s: float = 0.0) -> None:
+        """Waits for `stream` while watching the communicator; aborts it and raises ERR_TIMEOUT when the limit passes."""
+        check(_lib.load().cb_comm_sync(self.handle, stream.handle if stream else None, float(timeout_s)))
 
     def allgather(self, send: int, recv: int, bytes_per_rank: int, stream=None) -> None:
         check(_lib.load().cb_comm_allgather(self.handle, send, recv, bytes_per_rank, stream.handle if stream else None))

@@ -181,6 +181,12 @@ int cbg_exec_input_info(const cbg_exec* e, int i, char* name, size_t name_len, i
 int cbg_exec_output_info(const cbg_exec* e, int i, int32_t* dtype, int* rank, int64_t* dims);
 int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n);      /* launch plan, one kernel per line */
 int cbg_exec_input_sharding(const cbg_exec* e, int i, char* buf, size_t n);
+/* Tracing (the reference only logs the chosen implementation at klog -v=1, internal/gobackend/dot/dot.go:176-181; there are
+   no timers).  With the backend option "trace" or CUDABACKEND_TRACE=1 in the environment at cbg_backend_new, every Execute
+   records an event after each launch and, after its final sync, writes one line per launch to stderr:
+     cudabackend trace: exec=<name> device=<d> node=<i> kernel=<plan name> out=<shape> us=<device time>
+   The lines of the latest traced Execute can be read back here (empty when tracing is off). */
+int cbg_exec_last_trace(cbg_exec* e, char* buf, size_t n);
 int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const uint8_t* donate,
                      int default_device, cbg_buffer** outputs, int n_outputs);
 int cbg_exec_finalize(cbg_exec* e);                                        /* Executable.Finalize; frees the handle */

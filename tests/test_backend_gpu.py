@@ -354,3 +354,37 @@ def test_decoder_style_graph(backend):
     att = orc.sdpa(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], layout="BSHD", causal=True)
     want = att.reshape(B * S, H * D).astype(np.float64) @ wo.astype(np.float64)
     assert max_abs_normalised(got, want) < 1e-4
+
+
+def test_trace_option_reports_every_launch(capfd):
+    """The "trace" option: one line per launch with its device time, on stderr and through LastTrace."""
+    b = be.New("trace")
+    try:
+        rng = np.random.default_rng(12)
+        x = rng.standard_normal((4, 256), dtype=np.float32)
+        w = rng.integers(-127, 128, size=(256, 384), dtype=np.int8)
+        sc = rng.uniform(0.001, 0.02, size=(1, 384)).astype(np.float32)
+        builder = b.Builder("traced")
+        fn = builder.Main()
+        px = fn.Parameter("x", be.make_shape(dv.F32, 4, 256))
+        pw = fn.Parameter("w", be.make_shape(dv.I8, 256, 384))
+        ps = fn.Parameter("s", be.make_shape(dv.F32, 1, 384))
+        y = fn.FusedQuantizedDense(px, pw, None, be.Quantization(be.QUANT_LINEAR, ps, None, 0, 256))
+        fn.Return([fn.FusedSoftmax(y, 1)])
+        exe = builder.Compile()
+        bufs = [b.BufferFromFlatData(0, a, be.make_shape(d, *a.shape)) for a, d in ((x, dv.F32), (w, dv.I8), (sc, dv.F32))]
+        assert exe.LastTrace() == []
+        (out,) = exe.Execute(bufs, None, 0)
+        rows = exe.LastTrace()
+        assert [r["kernel"] for r in rows] == exe.KernelNames() and len(rows) == 2
+        assert all(r["device"] == 0 and 0.0 < r["us"] < 1e5 for r in rows)
+        err = capfd.readouterr().err
+        assert err.count("cudabackend trace: exec=traced") == 2
+        out.Finalize()
+        for t in bufs:
+            t.Finalize()
+        exe.Finalize()
+    finally:
+        b.Finalize()
+    with pytest.raises(BackendError):
+        be.New("traces")          # unknown options are still rejected

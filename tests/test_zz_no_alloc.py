@@ -12,7 +12,7 @@ import pytest
 
 from compute_b200 import BackendError, _lib, device as dv, ops
 from oracle import oracle as orc
-from tests.helpers import qdense_inputs
+from tests.helpers import max_abs_normalised, qdense_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +44,30 @@ def test_static_scratch_matches_planned_kernel_twice(M, K, N, x_dtype):
     for _ in range(2):          # the second call reuses whatever the first left in the scratch
         got = run_static(xin, w, s, b, desc, (M, N))
         assert np.array_equal(got, want)
+
+
+def test_static_scratch_uint8_weights_per_channel_scales_no_bias():
+    """The other template arm of the entry point: unsigned weights, one scale per column, no bias, no activation."""
+    M, K, N = 8, 768, 1024
+    x, wu, s, _ = qdense_inputs(91, M, K, N, x_dtype="f32", scale_layout="channel", bias=False, unsigned=True)
+    want = ops.quantized_dense(x, wu, s, None, None, x_dtype=dv.F32, scale_layout=dv.SCALE_CHANNEL, variant=dv.QDENSE_DECODE_MMA)
+    ref = orc.qdense_linear(x, wu, orc.expand_scales(s, "channel", K, N, 0), None, None, 1, orc.ACT_NONE, threads=orc.max_threads())
+    assert max_abs_normalised(want, ref) < 1e-4
+    desc = _lib.QDenseDesc(M, K, N, dv.F32, dv.U8, dv.SCALE_CHANNEL, 0, 0, 0, dv.ACT_NONE, dv.QDENSE_AUTO)
+    for _ in range(2):
+        got = run_static(x, wu, s, None, desc, (M, N))
+        assert np.array_equal(got, want)
+
+
+def test_static_scratch_rejects_bad_descriptors():
+    lib = _lib.load()
+    d = dv.DeviceMem(4096)
+    bad_act = _lib.QDenseDesc(4, 512, 512, dv.F32, dv.I8, dv.SCALE_CHANNEL, 0, 0, 0, 99, 0)
+    assert lib.cb_qdense_decode_static(0, C.byref(bad_act), d.ptr, d.ptr, d.ptr, None, d.ptr, None) == _lib.ERR_INVALID_ARG
+    assert b"activation" in lib.cb_last_error()
+    gathered = _lib.QDenseDesc(4, 512, 512, dv.F32, dv.I8, dv.SCALE_CHANNEL, 0, 0, 0, 0, 0, 2, 0)
+    assert lib.cb_qdense_decode_static(0, C.byref(gathered), d.ptr, d.ptr, d.ptr, None, d.ptr, None) == _lib.ERR_NOT_IMPLEMENTED
+    d.free()
 
 
 def test_static_scratch_rejects_what_it_cannot_hold():
