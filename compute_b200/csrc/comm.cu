@@ -7,13 +7,16 @@
 // link-time dependency on it: without NCCL these entry points return CB_ERR_NOT_IMPLEMENTED and
 // everything else works.
 //
-// Failure handling (the reference has none: it is one process on one device).  Communicators are
-// created non-blocking, so no NCCL call can park the host thread for ever: initialisation and every
-// enqueue are followed by polling ncclCommGetAsyncError under a time limit; when the limit passes
-// or NCCL reports an asynchronous error the communicator is aborted (ncclCommAbort, which also ends
-// its kernels on the device), the call returns CB_ERR_TIMEOUT / CB_ERR_CUDA, and every later call on
-// the handle fails at once.  cb_comm_sync is the host-side watchdog for work already enqueued: it
-// waits for the stream with the same limit and the same abort.
+// Failure handling (the reference has none: it is one process on one device).  A communicator made
+// with a time limit (cb_comm_init_rank_timeout, limit > 0) is non-blocking, so no NCCL call can park
+// the host thread for ever: initialisation and every enqueue are followed by polling
+// ncclCommGetAsyncError under the limit; when it passes or NCCL reports an asynchronous error the
+// communicator is aborted (ncclCommAbort, which also ends its kernels on the device), the call
+// returns CB_ERR_TIMEOUT / CB_ERR_CUDA, and every later call on the handle fails at once.  A
+// non-blocking enqueue is handed to a helper thread inside NCCL, which costs tens of microseconds
+// per call, so cb_comm_init_rank (no limit) keeps the blocking kind for the per-step path.  For
+// both kinds cb_comm_sync is the host-side watchdog for work already enqueued: it waits for the
+// stream under a limit and aborts the communicator when a peer has left.
 #include "common.cuh"
 
 #include <chrono>
@@ -141,7 +144,7 @@ int settle(cb_comm* c, int r, const char* what) {
       return fail(CB_ERR_TIMEOUT, "%s: rank %d of %d still in progress after %.1f s (a peer that never joined or has left?); communicator aborted",
                   what, c->rank, c->nranks, waited);
     }
-    if (spin > 100) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    if (waited > 2e-3) std::this_thread::sleep_for(std::chrono::microseconds(100));     // spin for the first two milliseconds
     else std::this_thread::yield();
   }
 }
@@ -193,7 +196,7 @@ int cb_comm_init_rank_timeout(int dev, int nranks, int rank, const unsigned char
   c->dev = dev; c->nranks = nranks; c->rank = rank;
   c->timeout_s = timeout_s > 0.0 ? timeout_s : default_timeout_s();
   int st;
-  if (nccl().can_abort) {
+  if (nccl().can_abort && timeout_s > 0.0) {
     NcclConfig cfg;
     cfg.size = sizeof(cfg); cfg.magic = 0xcafebeefu; cfg.version = 21800;
     cfg.blocking = 0;
@@ -224,7 +227,7 @@ int cb_comm_check(cb_comm* comm) {
   clear_error();
   if (!comm) return fail(CB_ERR_INVALID_ARG, "cb_comm_check: null communicator");
   CB_TRY(check_alive(comm, "cb_comm_check"));
-  if (!comm->nonblocking) return CB_OK;
+  if (!nccl().get_async_error) return CB_OK;
   int state = 0;
   const int q = nccl().get_async_error(comm->nccl, &state);
   if (q != 0) { const int st = nccl_check(q, "ncclCommGetAsyncError"); abort_comm(comm); return st; }

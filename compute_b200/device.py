@@ -154,9 +154,10 @@ class Comm:
         return buf.raw
 
     def __init__(self, dev: int, nranks: int, rank: int, uid: bytes, timeout_s: float = 0.0):
-        """`timeout_s` bounds the initialisation and every later wait on the communicator (0: the
-        CUDABACKEND_COMM_TIMEOUT_S environment variable, else 600 s); when it passes the communicator
-        is aborted and BackendError(ERR_TIMEOUT) raised.  dev < 0: the current device."""
+        """`timeout_s` > 0 makes a non-blocking communicator: the initialisation and every enqueue
+        are bounded by it, and when it passes the communicator is aborted and BackendError(ERR_TIMEOUT)
+        raised.  0 keeps the blocking kind (cheaper per call), watched through `sync`.
+        dev < 0: the current device."""
         assert len(uid) == COMM_ID_BYTES
         self.dev, self.nranks, self.rank = dev, nranks, rank
         h = C.c_void_p()

@@ -319,13 +319,16 @@ typedef struct cb_comm cb_comm;
 int cb_comm_unique_id(unsigned char* id /* CB_COMM_ID_BYTES */);
 int cb_comm_init_rank(int dev, int nranks, int rank, const unsigned char* id, cb_comm** comm);
 /* Failure handling; no counterpart in the reference, which is one process on one device (errors there are returned
- * values, compute.go:39-48).  Communicators are non-blocking: initialisation and every enqueue poll the asynchronous
- * state under a time limit (timeout_s; 0 = CUDABACKEND_COMM_TIMEOUT_S or 600 s).  When the limit passes — a rank that
- * never joined, a peer that left — or NCCL reports an error, the communicator is aborted, the call returns
- * CB_ERR_TIMEOUT / CB_ERR_CUDA, and every later call on the handle fails at once (cb_comm_destroy still frees it).
+ * values, compute.go:39-48).  With timeout_s > 0 the communicator is non-blocking: initialisation and every enqueue poll
+ * the asynchronous state under that limit.  When it passes — a rank that never joined, a peer that left — or NCCL
+ * reports an error, the communicator is aborted, the call returns CB_ERR_TIMEOUT / CB_ERR_CUDA, and every later call on
+ * the handle fails at once (cb_comm_destroy still frees it).  Non-blocking enqueues cost tens of microseconds each, so
+ * timeout_s = 0 (and cb_comm_init_rank) makes the blocking kind, whose watchdog is cb_comm_sync alone.
  * dev < 0 = the calling thread's current device.
  *   cb_comm_check  one poll: CB_OK while healthy, the error (and an abort) once NCCL has reported one
- *   cb_comm_sync   waits for `stream` like cb_stream_sync, polling the communicator, with the same limit and abort */
+ *   cb_comm_sync   waits for `stream` like cb_stream_sync while polling the communicator; past timeout_s (0 = the
+ *                  communicator's own limit, else CUDABACKEND_COMM_TIMEOUT_S, else 600 s) it aborts the communicator,
+ *                  which ends the collective's kernel, and returns CB_ERR_TIMEOUT */
 int cb_comm_init_rank_timeout(int dev, int nranks, int rank, const unsigned char* id, double timeout_s, cb_comm** comm);
 int cb_comm_check(cb_comm* comm);
 int cb_comm_sync(cb_comm* comm, cb_stream stream, double timeout_s);

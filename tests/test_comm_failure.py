@@ -97,9 +97,20 @@ def test_enqueue_that_stays_in_progress_times_out(fake_lib):
     assert "timeout True True" in out and "aborts 1" in out
 
 
-def test_library_without_the_config_entry_points_falls_back_to_blocking(fake_lib):
+def test_no_time_limit_keeps_the_blocking_kind(fake_lib):
     out = run_case(fake_lib, """
         c = dv.Comm(-1, 2, 0, uid)
+        c.allreduce(1, 1, 4, dv.F32)
+        c.check()
+        c.close()
+        print("inits", fake.fake_nccl_inits(), "destroys", fake.fake_nccl_destroys())
+    """, FAKE_NCCL_REFUSE_CONFIG=1, FAKE_NCCL_ENQUEUE_RESULT=0, FAKE_NCCL_POLLS=0)
+    assert "inits 1 destroys 1" in out         # the configuration record was never offered
+
+
+def test_library_that_refuses_the_config_record_falls_back_to_blocking(fake_lib):
+    out = run_case(fake_lib, """
+        c = dv.Comm(-1, 2, 0, uid, timeout_s=1.0)
         c.allreduce(1, 1, 4, dv.F32)
         c.close()
         print("inits", fake.fake_nccl_inits(), "destroys", fake.fake_nccl_destroys())
