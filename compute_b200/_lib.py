@@ -93,6 +93,7 @@ SIGNATURES = {
     "cb_plan_reduce": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_broadcast_in_dim": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32),
                                   C.POINTER(C.c_void_p)], C.c_int),
+    "cb_plan_embedding_lookup": ([C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_rms_norm": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_double, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_gelu": ([C.c_int, C.c_int32, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)], C.c_int),
     "cb_plan_softmax": ([C.c_int, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p)], C.c_int),

@@ -24,6 +24,7 @@ from ._lib import BackendError, ErrNotImplemented, check
 OP_PARAMETER, OP_CONSTANT, OP_DOT_GENERAL = 1, 2, 32
 OP_FUSED_SOFTMAX, OP_FUSED_LAYER_NORM, OP_FUSED_GELU, OP_FUSED_DENSE = 116, 117, 118, 119
 OP_FUSED_SDPA, OP_FUSED_ATTENTION_QKV_PROJECTION, OP_FUSED_QUANTIZED_DENSE = 120, 122, 123
+OP_QUANTIZED_EMBEDDING_LOOKUP = 124
 OP_ALL_REDUCE, OP_ALL_GATHER = 112, 114
 REDUCE_OP_SUM, REDUCE_OP_PRODUCT, REDUCE_OP_MAX, REDUCE_OP_MIN = 1, 2, 3, 4      # compute.ReduceOpType (standard_ops.go:65-84)
 OP_NAMES = {1: "Parameter", 2: "Constant", 32: "DotGeneral", 112: "AllReduce", 114: "AllGather", 116: "FusedSoftmax", 117: "FusedLayerNorm", 118: "FusedGelu",
@@ -82,6 +83,7 @@ _GRAPH_SIGNATURES = {
     "cbg_fn_fused_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
+    "cbg_fn_quantized_embedding_lookup": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_quantized_dense_ggml": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_fused_sdpa": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(_SdpaOptions), C.POINTER(C.c_void_p)], C.c_int),
     "cbg_fn_not_implemented": ([C.c_void_p, C.c_char_p], C.c_int),
@@ -509,6 +511,16 @@ class Function:
             self.handle, x.handle, weights.handle, bias.handle if bias is not None else None, q.Scheme,
             q.Scale.handle if q.Scale is not None else None, q.ZeroPoint.handle if q.ZeroPoint is not None else None,
             q.BlockAxis, q.BlockSize, activation, C.byref(h)))
+        return self._v(h)
+
+    def QuantizedEmbeddingLookup(self, data: Value, indices: Value, dataQuantization: Quantization) -> Value:
+        """FusedOps.QuantizedEmbeddingLookup (fused_ops.go:394-411): data [vocabSize, bytesPerRow] Uint8 GGML blocks,
+        indices integer [batch..., 1] -> Float32 [batch..., K]."""
+        q = dataQuantization
+        if q is None:
+            raise BackendError(_lib.ERR_INVALID_ARG, "QuantizedEmbeddingLookup: dataQuantization must not be nil")
+        h = C.c_void_p()
+        check(_g().cbg_fn_quantized_embedding_lookup(self.handle, data.handle, indices.handle, q.Scheme, q.GGMLType, C.byref(h)))
         return self._v(h)
 
     def FusedScaledDotProductAttention(self, query: Value, key: Value, value: Value, axesLayout: int = LAYOUT_BHSD,

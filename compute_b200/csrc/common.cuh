@@ -63,7 +63,7 @@ const char* dtype_name(int d);
 // ---- plans ------------------------------------------------------------------
 enum PlanKind { PLAN_QDENSE = 1, PLAN_DOT, PLAN_SDPA, PLAN_COPY, PLAN_CONVERT, PLAN_IOTA,
                 PLAN_SLICE, PLAN_TRANSPOSE, PLAN_GELU, PLAN_SOFTMAX, PLAN_LAYERNORM, PLAN_COLS_BIAS,
-                PLAN_BINARY, PLAN_UNARY, PLAN_REDUCE, PLAN_BROADCAST, PLAN_RMSNORM };
+                PLAN_BINARY, PLAN_UNARY, PLAN_REDUCE, PLAN_BROADCAST, PLAN_RMSNORM, PLAN_EMBEDDING };
 
 struct HelperDesc {
   int32_t dtype = 0, dtype_to = 0, rank = 0, axis = 0;
@@ -114,6 +114,11 @@ int helper_launch(const cb_plan* p, const void* const* in, void* const* out, voi
 int fused_small_plan(cb_plan* p);
 int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int elementwise_plan(cb_plan* p);
+int qdense_ggml_plan(cb_plan* p);
+int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s);
+int embedding_lookup_plan(cb_plan* p);
+int embedding_lookup_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+int embedding_lookup_check(const cb_plan* p, const void* ws);
 int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 // out[i] = reduction over r of stacked[r][i], r in rank order (the local step of AllReduce)
 int stacked_reduce_launch(int dtype, int op, const void* stacked, int g, int64_t n, void* out, cudaStream_t s);

@@ -46,7 +46,7 @@ struct Shape {
 
 enum NodeKind { N_PARAM, N_CONST, N_DOT, N_QDENSE, N_SDPA, N_RESHAPE, N_SLICE, N_IOTA, N_CONVERT, N_TRANSPOSE,
                 N_GELU, N_SOFTMAX, N_LAYERNORM, N_COLS_BIAS, N_BINARY, N_UNARY, N_REDUCE, N_BROADCAST, N_RMSNORM,
-                N_ALLREDUCE, N_ALLGATHER };
+                N_ALLREDUCE, N_ALLGATHER, N_EMBEDDING };
 
 bool is_float(int d) { return d == CB_F16 || d == CB_F32 || d == CB_F64 || d == CB_BF16 || d == CB_F8E4M3FN || d == CB_F8E5M2; }
 bool is_half(int d) { return d == CB_F16 || d == CB_BF16; }
@@ -365,11 +365,11 @@ int cbg_backend_device_description(const cbg_backend* b, int dev, char* buf, siz
 int cbg_backend_capabilities(const cbg_backend* b, int32_t* ops, int* n_ops, int32_t* dtypes, int* n_dtypes) {
   // OpType codes of optype.go: Parameter 1, Constant 2, DotGeneral 32, AllReduce 112, AllGather 114, FusedSoftmax 116,
   // FusedLayerNorm 117, FusedGelu 118, FusedDense 119, FusedScaledDotProductAttention 120,
-  // FusedAttentionQKVProjection 122, FusedQuantizedDense 123.  The helper ops (Reshape, Slice, Iota, ConvertDType,
+  // FusedAttentionQKVProjection 122, FusedQuantizedDense 123, QuantizedEmbeddingLookup 124.  The helper ops (Reshape, Slice, Iota, ConvertDType,
   // Transpose) exist to serve DotGeneral, and the element-wise / reduce ops to serve a decoder block, for the float
   // dtypes only: they are deliberately not advertised, so that the compliance suite's per-op sweeps over every dtype
   // skip them.
-  static const int32_t k_ops[] = {1, 2, 32, 112, 114, 116, 117, 118, 119, 120, 122, 123};
+  static const int32_t k_ops[] = {1, 2, 32, 112, 114, 116, 117, 118, 119, 120, 122, 123, 124};
   static const int32_t k_dtypes[] = {CB_BOOL, CB_I8, CB_I32, CB_I64, CB_U8, CB_F16, CB_F32, CB_F64, CB_BF16};
   const int no = (int)(sizeof(k_ops) / sizeof(k_ops[0])), nd = (int)(sizeof(k_dtypes) / sizeof(k_dtypes[0]));
   if (ops && n_ops) for (int i = 0; i < std::min(*n_ops, no); i++) ops[i] = k_ops[i];
@@ -911,6 +911,49 @@ int cbg_fn_fused_dense(cbg_function* f, cbg_value* x, cbg_value* weight, cbg_val
   return CB_OK;
 }
 
+// validateGGMLTypeSupported and deriveGGMLK (internal/gobackend/fusedops/quantizeddense.go:145-176)
+static int ggml_derive_k(const char* op, int64_t bytes_per_row, int ggml_type, int64_t* K) {
+  int vpb = 0, bpb = 0;
+  switch (ggml_type) {
+    case CB_GGML_Q4_0: case CB_GGML_IQ4_NL: vpb = 32; bpb = 18; break;
+    case CB_GGML_Q8_0: vpb = 32; bpb = 34; break;
+    case CB_GGML_Q4_K: vpb = 256; bpb = 144; break;
+    case CB_GGML_Q6_K: vpb = 256; bpb = 210; break;
+    default: return fail(CB_ERR_NOT_IMPLEMENTED, "%s: GGML type %d not supported in fused path", op, ggml_type);
+  }
+  if (bytes_per_row % bpb != 0)
+    return fail(CB_ERR_INVALID_ARG, "%s: bytesPerRow %lld not divisible by bytesPerBlock %d", op, (long long)bytes_per_row, bpb);
+  *K = bytes_per_row / bpb * vpb;
+  return CB_OK;
+}
+
+// QuantizedEmbeddingLookup (internal/gobackend/fusedops/quantizeddense.go:250-321): data [vocab, bytesPerRow] Uint8 in a
+// GGML block layout, indices integer with last dimension 1; the result replaces that dimension by K, Float32.
+int cbg_fn_quantized_embedding_lookup(cbg_function* f, cbg_value* data, cbg_value* indices, int scheme, int ggml_type, cbg_value** v) {
+  const char* op = "QuantizedEmbeddingLookup";
+  CB_TRY(check_fn(f, op));
+  if (scheme != CB_QUANT_GGML) return fail(CB_ERR_NOT_IMPLEMENTED, "%s: only QuantGGML scheme is supported, got scheme %d", op, scheme);
+  CB_TRY(check_values(f, op, {data, indices}));
+  if (data->shape.dims.size() != 2 || data->shape.dtype != CB_U8)
+    return fail(CB_ERR_INVALID_ARG, "%s: data must be [vocabSize, bytesPerRow] Uint8, got %s", op, data->shape.str().c_str());
+  const int idt = indices->shape.dtype;
+  const bool is_int = idt == CB_I8 || idt == CB_U8 || idt == CB_I32 || idt == CB_I64 || idt == CB_U32 || idt == CB_U64 || idt == CB_I16 || idt == CB_U16;
+  if (!is_int) return fail(CB_ERR_INVALID_ARG, "%s: indices must be integer, got %s", op, cb::dtype_name(idt));
+  if (indices->shape.dims.empty() || indices->shape.dims.back() != 1)
+    return fail(CB_ERR_INVALID_ARG, "%s: indices last dim must be 1, got shape %s", op, indices->shape.str().c_str());
+  int64_t K = 0;
+  CB_TRY(ggml_derive_k(op, data->shape.dims[1], ggml_type, &K));
+  if (idt != CB_I8 && idt != CB_U8 && idt != CB_I32 && idt != CB_I64)
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: indices of dtype %s are not implemented", op, cb::dtype_name(idt));
+  Shape s = indices->shape;
+  s.dtype = CB_F32;
+  s.dims.back() = K;
+  cbg_value* n = add_node(f, N_EMBEDDING, s, {data, indices});
+  n->axis = ggml_type;
+  *v = n;
+  return CB_OK;
+}
+
 // FusedQuantizedDense with compute.QuantGGML (internal/gobackend/fusedops/quantizeddense.go:181-248): weights
 // [N, bytesPerRow] Uint8 in the native block layout; K follows from the row bytes and must equal x's last dimension.
 int cbg_fn_fused_quantized_dense_ggml(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias, int ggml_type,
@@ -924,13 +967,9 @@ int cbg_fn_fused_quantized_dense_ggml(cbg_function* f, cbg_value* x, cbg_value* 
   if (x->shape.dims.size() < 1) return fail(CB_ERR_INVALID_ARG, "%s: x must have rank >= 1, got %zu", op, x->shape.dims.size());
   if (weights->shape.dims.size() != 2 || weights->shape.dtype != CB_U8)
     return fail(CB_ERR_INVALID_ARG, "%s: weights must be [N, bytesPerRow] Uint8, got %s", op, weights->shape.str().c_str());
-  if (ggml_type != CB_GGML_Q4_0 && ggml_type != CB_GGML_Q8_0)
-    return fail(CB_ERR_NOT_IMPLEMENTED, "%s: GGML type %d not yet supported in fused path", op, ggml_type);
-  const int64_t N = weights->shape.dims[0], bytes_per_row = weights->shape.dims[1];
-  const int64_t block_bytes = ggml_type == CB_GGML_Q8_0 ? 34 : 18;
-  if (bytes_per_row % block_bytes != 0)
-    return fail(CB_ERR_INVALID_ARG, "%s: bytesPerRow=%lld is not a multiple of the %lld-byte block", op, (long long)bytes_per_row, (long long)block_bytes);
-  const int64_t K = bytes_per_row / block_bytes * 32;
+  int64_t K = 0;
+  CB_TRY(ggml_derive_k(op, weights->shape.dims[1], ggml_type, &K));
+  const int64_t N = weights->shape.dims[0];
   if (x->shape.dims.back() != K)
     return fail(CB_ERR_INVALID_ARG, "%s: x's last dim (%lld) must match K=%lld derived from weights", op, (long long)x->shape.dims.back(), (long long)K);
   if (bias && (bias->shape.dtype != CB_F32 || bias->shape.dims != std::vector<int64_t>{N}))
@@ -1521,6 +1560,10 @@ int build_dev_plans(cbg_exec* e, int dev, DevPlans* dp) {
         st = cb_plan_rms_norm(dev, n->shape.dtype, H ? n->shape.size() / H : 0, H, n->epsilon, n->flags & 1, &p);
         break;
       }
+      case N_EMBEDDING:
+        st = cb_plan_embedding_lookup(dev, n->inputs[0]->shape.dims[0], n->inputs[0]->shape.dims[1], n->inputs[1]->shape.size(),
+                                      n->inputs[1]->shape.dtype, n->axis, &p);
+        break;
       default: break;      // parameters, constants, reshapes, collectives
     }
     if (st == CB_OK && p) {
@@ -1941,6 +1984,12 @@ int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const
     const int sync_st = cb_stream_sync(reps[r].dev, reps[r].stream);
     if (st == CB_OK) st = sync_st;
   }
+  // an index outside the table is an error of the call (quantizeddense.go:487-489): the lookup's status words are read
+  if (st == CB_OK)
+    for (int r = 0; r < n_setup && st == CB_OK; r++)
+      for (size_t i = 0; i < nn && st == CB_OK; i++)
+        if (e->live[i] && f->nodes[i]->kind == N_EMBEDDING && reps[r].dp->plans[i] && reps[r].ws[i])
+          st = cb_plan_check_status(reps[r].dp->plans[i], reps[r].ws[i]);
   if (trace && st == CB_OK) {
     // one line per launch: device time between the events after the previous launch and after this one
     std::string text;

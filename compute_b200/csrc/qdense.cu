@@ -110,120 +110,6 @@ qdense_generic_kernel(const XT* __restrict__ x, const void* __restrict__ w, cons
 }
 
 // ---------------------------------------------------------------------------
-// GGML block formats (internal/gobackend/fusedops/quantizeddense_ggml.go:98-196)
-// ---------------------------------------------------------------------------
-// Weights [N, bytes_per_row]: row n holds K / 32 blocks.  One warp per weight row: lanes take blocks
-// round-robin, dequantise a block's 32 values (value = scale * q, the scale a little-endian fp16 at the
-// block's start) and multiply them with up to QGG_ROWS rows of x (fused multiply-adds); a butterfly adds
-// the lanes.  The reference adds the products k-ascending in one float; here the sum is split across lanes, so
-// the result agrees to rounding, not bit for bit.
-constexpr int QGG_ROWS = 16;
-constexpr int QGG_WARPS = 8;
-
-// 32 consecutive elements x[row, k0 .. k0 + 31] as floats.
-__device__ __forceinline__ void qgg_load32(const float* xr, float (&v)[32]) {
-#pragma unroll
-  for (int q = 0; q < 8; q++) {
-    const float4 t = __ldg(reinterpret_cast<const float4*>(xr) + q);
-    v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
-  }
-}
-__device__ __forceinline__ void qgg_load32(const __nv_bfloat16* xr, float (&v)[32]) {
-#pragma unroll
-  for (int q = 0; q < 4; q++) {
-    const uint4 t = __ldg(reinterpret_cast<const uint4*>(xr) + q);
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-      v[8 * q + 2 * e] = __uint_as_float(w[e] << 16);
-      v[8 * q + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-    }
-  }
-}
-
-// STAGED (K a multiple of 256, 16-byte aligned weights): a warp copies the 32 blocks it is about to use
-// (1088 or 576 contiguous bytes) into shared memory in 16-byte pieces and every lane reads its block from
-// there; otherwise every lane reads its block from global memory two bytes at a time.
-template <typename XT, int GGML, bool STAGED>
-__global__ void __launch_bounds__(QGG_WARPS * 32)
-qdense_ggml_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ bias, XT* __restrict__ out,
-                   int64_t M, int64_t K, int64_t N, int act) {
-  constexpr int BLOCK_BYTES = GGML == CB_GGML_Q8_0 ? 34 : 18;
-  constexpr int SUPER = STAGED ? 4 : 1;                 // 32-block chunks requested together: bytes in flight per warp
-  constexpr int CHUNK_VECS = 32 * BLOCK_BYTES / 16;
-  __shared__ uint4 stage[STAGED ? QGG_WARPS : 1][STAGED ? SUPER * CHUNK_VECS : 1];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t n = (int64_t)blockIdx.x * QGG_WARPS + warp;
-  const int64_t m0 = (int64_t)blockIdx.y * QGG_ROWS;
-  if (n >= N) return;                                   // whole warps leave together
-  const int rows = (int)min((int64_t)QGG_ROWS, M - m0);
-  const int64_t nblocks = K / 32;
-  const uint8_t* row = w + n * nblocks * BLOCK_BYTES;
-  float acc[QGG_ROWS];
-#pragma unroll
-  for (int i = 0; i < QGG_ROWS; i++) acc[i] = 0.0f;
-  for (int64_t s0 = 0; s0 < nblocks; s0 += 32 * SUPER) {
-    if (STAGED) {
-      const int nvec = (int)(min((int64_t)32 * SUPER, nblocks - s0) * BLOCK_BYTES / 16);
-      const uint4* src = reinterpret_cast<const uint4*>(row + s0 * BLOCK_BYTES);
-      __syncwarp();                                      // the previous chunks have been read
-      for (int v = lane; v < nvec; v += 32) stage[warp][v] = __ldg(src + v);
-      __syncwarp();
-    }
-#pragma unroll 1
-    for (int c = 0; c < SUPER; c++) {
-    const int64_t b = s0 + c * 32 + lane;
-    const uint16_t* blk16 = STAGED
-        ? reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(stage[warp]) + (c * 32 + lane) * BLOCK_BYTES)
-        : reinterpret_cast<const uint16_t*>(row + b * BLOCK_BYTES);     // rows and blocks start on even bytes
-    if (b < nblocks) {
-      const float d = __half2float(__ushort_as_half(blk16[0]));
-      float wv[32];
-      if (GGML == CB_GGML_Q8_0) {
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-          const uint32_t q = blk16[1 + i];
-          wv[2 * i] = __fmul_rn(d, (float)(int8_t)(q & 0xFF));
-          wv[2 * i + 1] = __fmul_rn(d, (float)(int8_t)(q >> 8));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const uint32_t q = blk16[1 + i];
-          wv[2 * i] = __fmul_rn(d, (float)((int)(q & 0x0F) - 8));
-          wv[16 + 2 * i] = __fmul_rn(d, (float)((int)((q >> 4) & 0x0F) - 8));
-          wv[2 * i + 1] = __fmul_rn(d, (float)((int)((q >> 8) & 0x0F) - 8));
-          wv[16 + 2 * i + 1] = __fmul_rn(d, (float)((int)(q >> 12) - 8));
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < QGG_ROWS; i++) {
-        if (i < rows) {
-          float xv[32];
-          qgg_load32(x + (m0 + i) * K + b * 32, xv);
-          float s = acc[i];
-#pragma unroll
-          for (int k = 0; k < 32; k++) s = fmaf(xv[k], wv[k], s);
-          acc[i] = s;
-        }
-      }
-    }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < QGG_ROWS; i++) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
-  }
-  if (lane == 0) {
-    const float bv = bias ? bias[n] : 0.0f;
-#pragma unroll
-    for (int i = 0; i < QGG_ROWS; i++)
-      if (i < rows) Scalar<XT>::store(out, (m0 + i) * N + n, apply_activation(bias ? __fadd_rn(acc[i], bv) : acc[i], act));
-  }
-}
-
-// ---------------------------------------------------------------------------
 // decode kernel
 // ---------------------------------------------------------------------------
 constexpr int QD_TILE_N = 64;                  // columns per tile
@@ -756,25 +642,7 @@ int qdense_plan(cb_plan* p) {
   if (d.M < 0 || d.K < 0 || d.N < 0) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: negative dimension");
   if (d.x_dtype != CB_F32 && d.x_dtype != CB_BF16)
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: x must be float32 (or bfloat16), got %s", dtype_name(d.x_dtype));
-  if (d.scheme == CB_QUANT_GGML) {
-    // quantizeddense.go:181-248: weights [N, bytesPerRow] Uint8, K derived from the row bytes, no zero points
-    if (d.ggml_type != CB_GGML_Q4_0 && d.ggml_type != CB_GGML_Q8_0)
-      return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense(GGML): GGML type %d not yet supported in fused path", d.ggml_type);
-    if (d.w_dtype != CB_U8) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): weights must be [N, bytesPerRow] Uint8, got %s", dtype_name(d.w_dtype));
-    if (d.K % 32 != 0) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): K=%lld is not a whole number of 32-value blocks", (long long)d.K);
-    if (d.has_zero_point) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): ZeroPoint must be nil for GGML scheme");
-    if (d.activation < CB_ACT_NONE || d.activation > CB_ACT_TANH) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense: unknown activation %d", d.activation);
-    if (d.gather_ranks > 1) return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense(GGML): a gathered plan needs the tensor-core decode kernel");
-    if ((d.N + QGG_WARPS - 1) / QGG_WARPS > 0x7FFFFFFFLL || (d.M + QGG_ROWS - 1) / QGG_ROWS > 65535)
-      return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense(GGML): shape too large for one launch");
-    p->n_inputs = 2 + (d.has_bias ? 1 : 0);
-    p->n_outputs = 1;
-    p->variant = CB_QDENSE_GENERIC;
-    p->blocks = (int)(((d.N + QGG_WARPS - 1) / QGG_WARPS) * ((d.M + QGG_ROWS - 1) / QGG_ROWS));
-    p->threads = QGG_WARPS * 32;
-    p->name = std::string("qdense_ggml_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (d.ggml_type == CB_GGML_Q8_0 ? "_q8_0" : "_q4_0");
-    return CB_OK;
-  }
+  if (d.scheme == CB_QUANT_GGML) return qdense_ggml_plan(p);
   if (d.scheme != CB_QUANT_LINEAR && d.scheme != CB_QUANT_NF4)
     return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: unknown quantization scheme %d", d.scheme);
   if (d.w_dtype != CB_I8 && d.w_dtype != CB_U8 && d.w_dtype != CB_I4 && d.w_dtype != CB_U4)
@@ -919,21 +787,7 @@ int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   if (p->variant == CB_QDENSE_DECODE_MMA) return launch_decode(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_PREFILL) return qdense_prefill_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_launch(p, in, out, ws, s);
-  if (d.scheme == CB_QUANT_GGML) {
-    if (d.M == 0 || d.N == 0) return CB_OK;
-    const float* bias = d.has_bias ? (const float*)in[2] : nullptr;
-    dim3 grid((unsigned)((d.N + QGG_WARPS - 1) / QGG_WARPS), (unsigned)((d.M + QGG_ROWS - 1) / QGG_ROWS));
-    const bool staged = d.K % 256 == 0 && (reinterpret_cast<uintptr_t>(in[1]) & 15) == 0;
-    if ((reinterpret_cast<uintptr_t>(in[0]) & 15) != 0) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): x must be 16-byte aligned");
-#define QGG_LAUNCH_S(XT, G, S) qdense_ggml_kernel<XT, G, S><<<grid, QGG_WARPS * 32, 0, s>>>((const XT*)in[0], (const uint8_t*)in[1], bias, (XT*)out[0], d.M, d.K, d.N, d.activation)
-#define QGG_LAUNCH(XT, G) do { if (staged) QGG_LAUNCH_S(XT, G, true); else QGG_LAUNCH_S(XT, G, false); } while (0)
-    if (d.x_dtype == CB_BF16) { if (d.ggml_type == CB_GGML_Q8_0) QGG_LAUNCH(__nv_bfloat16, CB_GGML_Q8_0); else QGG_LAUNCH(__nv_bfloat16, CB_GGML_Q4_0); }
-    else { if (d.ggml_type == CB_GGML_Q8_0) QGG_LAUNCH(float, CB_GGML_Q8_0); else QGG_LAUNCH(float, CB_GGML_Q4_0); }
-#undef QGG_LAUNCH_S
-#undef QGG_LAUNCH
-    CB_CUDA(cudaGetLastError());
-    return CB_OK;
-  }
+  if (d.scheme == CB_QUANT_GGML) return qdense_ggml_launch(p, in, out, s);
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
   (void)wu;
   const bool nf4 = d.scheme == CB_QUANT_NF4;

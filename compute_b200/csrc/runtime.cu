@@ -517,6 +517,16 @@ int cb_plan_rms_norm(int dev, int32_t dtype, int64_t rows, int64_t row_size, dou
   return finish_plan(elementwise_plan(p), p, plan);
 }
 
+int cb_plan_embedding_lookup(int dev, int64_t vocab, int64_t bytes_per_row, int64_t n_indices, int32_t index_dtype, int32_t ggml_type, cb_plan** plan) {
+  cb_plan* p;
+  CB_TRY(new_plan(dev, PLAN_EMBEDDING, plan, &p));
+  p->helper.dtype = index_dtype;
+  p->helper.dims[0] = vocab; p->helper.dims[1] = bytes_per_row;
+  p->helper.n = n_indices;
+  p->helper.axis = ggml_type;
+  return finish_plan(embedding_lookup_plan(p), p, plan);
+}
+
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes) {
   clear_error();
   if (!plan || !bytes) return fail(CB_ERR_INVALID_ARG, "NULL argument");
@@ -580,6 +590,7 @@ static int launch_checked(const cb_plan* plan, const void* const* inputs, void* 
     case PLAN_SDPA: return sdpa_launch(plan, inputs, outputs, workspace, s);
     case PLAN_GELU: case PLAN_SOFTMAX: case PLAN_LAYERNORM: case PLAN_COLS_BIAS: return fused_small_launch(plan, inputs, outputs, workspace, s);
     case PLAN_BINARY: case PLAN_UNARY: case PLAN_REDUCE: case PLAN_BROADCAST: case PLAN_RMSNORM: return elementwise_launch(plan, inputs, outputs, workspace, s);
+    case PLAN_EMBEDDING: return embedding_lookup_launch(plan, inputs, outputs, workspace, s);
     default: return helper_launch(plan, inputs, outputs, workspace, s);
   }
 }
@@ -653,6 +664,7 @@ int cb_bound_destroy(cb_bound* bound) {
 int cb_plan_check_status(const cb_plan* plan, const void* workspace) {
   clear_error();
   if (!plan) return fail(CB_ERR_INVALID_ARG, "plan is NULL");
+  if (plan->kind == PLAN_EMBEDDING && workspace) { CB_TRY(set_device(plan->dev)); return embedding_lookup_check(plan, workspace); }
   if (!plan->has_status || !workspace) return CB_OK;
   CB_TRY(set_device(plan->dev));
   unsigned int word[2] = {0, 0};

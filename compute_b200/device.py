@@ -24,7 +24,7 @@ ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
 SCALE_REF, SCALE_CHANNEL, SCALE_KGROUP = range(3)
 QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL, QDENSE_DECODE_TC = range(5)
 QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
-GGML_Q4_0, GGML_Q8_0 = 0, 1
+GGML_Q4_0, GGML_Q8_0, GGML_IQ4_NL, GGML_Q4_K, GGML_Q6_K = 0, 1, 2, 5, 7       # compute.GGMLQuantType (fused_ops.go:132-145)
 DOT_AUTO, DOT_GENERIC, DOT_TCGEN05 = range(3)
 SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH, SDPA_DECODE = range(4)
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
@@ -292,6 +292,13 @@ class Plan:
         d = DotDesc(B, M, N, K, int(rhs_transposed), in_dtype, out_dtype, variant, int(has_bias), activation)
         h = C.c_void_p()
         check(_lib.load().cb_plan_dot(dev, C.byref(d), C.byref(h)))
+        return cls(h, dev)
+
+    @classmethod
+    def embedding_lookup(cls, vocab, bytes_per_row, n_indices, index_dtype, ggml_type, dev=0) -> "Plan":
+        """QuantizedEmbeddingLookup: launch inputs table, indices; output float32 [n_indices, K]."""
+        h = C.c_void_p()
+        check(_lib.load().cb_plan_embedding_lookup(dev, vocab, bytes_per_row, n_indices, index_dtype, ggml_type, C.byref(h)))
         return cls(h, dev)
 
     @classmethod

@@ -99,7 +99,7 @@ typedef enum {
  * values: fp16 scale, 16 bytes of nibbles, value = (nibble - 8) * scale, low nibbles first half) and Q8_0 (34-byte
  * blocks: fp16 scale, 32 int8); the other block formats return CB_ERR_NOT_IMPLEMENTED. */
 typedef enum { CB_QUANT_LINEAR = 0, CB_QUANT_NF4 = 1, CB_QUANT_GGML = 2 } cb_quant_scheme;
-typedef enum { CB_GGML_Q4_0 = 0, CB_GGML_Q8_0 = 1 } cb_ggml_type;
+typedef enum { CB_GGML_Q4_0 = 0, CB_GGML_Q8_0 = 1, CB_GGML_IQ4_NL = 2, CB_GGML_Q4_K = 5, CB_GGML_Q6_K = 7 } cb_ggml_type;
 
 typedef enum {
   CB_QDENSE_AUTO = 0,
@@ -246,6 +246,15 @@ int cb_plan_broadcast_in_dim(int dev, int32_t dtype, int32_t rank, const int64_t
  * gamma?).  The interface has no fused RMS norm (FusedLayerNorm is mean-centred, internal/gobackend/fusedops/
  * layernorm.go:102-137): Builder.Compile substitutes this plan for the decomposed Mul / ReduceSum / Rsqrt form. */
 int cb_plan_rms_norm(int dev, int32_t dtype, int64_t rows, int64_t row_size, double epsilon, int32_t has_gamma, cb_plan** plan);
+
+/* ---- QuantizedEmbeddingLookup (fused_ops.go:394-411; internal/gobackend/fusedops/quantizeddense.go:250-321, 455-499):
+ * out[i, 0..K) float32 = the dequantised row indices[i] of a GGML block table [vocab, bytes_per_row] bytes; K follows from
+ * bytes_per_row and the block format (deriveGGMLK, quantizeddense.go:165-176; bytes_per_row must be whole blocks).
+ * Launch inputs: table, indices (n_indices integers of index_dtype: int8 / uint8 / int32 / int64); output: [n_indices, K].
+ * The plan needs its workspace.  An index outside [0, vocab) is an error in the reference; here its row is written as
+ * zeros and cb_plan_check_status(plan, workspace) — after the stream has been synchronised — returns CB_ERR_INVALID_ARG
+ * naming the first such position. */
+int cb_plan_embedding_lookup(int dev, int64_t vocab, int64_t bytes_per_row, int64_t n_indices, int32_t index_dtype, int32_t ggml_type, cb_plan** plan);
 
 /* ---- FusedGelu, FusedSoftmax, FusedLayerNorm (FusedOps, fused_ops.go:318-334; internal/gobackend/fusedops/gelu.go,
  *      softmax.go, layernorm.go).  Float32 / Float64 as the reference, BFloat16 / Float16 computed in f32.

@@ -107,9 +107,16 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
                                  int block_axis, int64_t block_size, int activation, cbg_value** v);
 
 /* FusedQuantizedDense with compute.QuantGGML (fused_ops.go:92-97, :132-145): weights [N, bytesPerRow] Uint8 in the
- * native GGML block layout (Q4_0 = 0 and Q8_0 = 1 are built), no scales or zero points. */
+ * native GGML block layout, no scales or zero points.  ggml_type is compute.GGMLQuantType: Q4_0 = 0, Q8_0 = 1,
+ * IQ4_NL = 2, Q4_K = 5, Q6_K = 7 — the five the reference supports (quantizeddense.go:145-152); the others return
+ * CB_ERR_NOT_IMPLEMENTED as there. */
 int cbg_fn_fused_quantized_dense_ggml(cbg_function* f, cbg_value* x, cbg_value* weights, cbg_value* bias /* or NULL */,
                                       int ggml_type, int activation, cbg_value** v);
+/* FusedOps.QuantizedEmbeddingLookup (fused_ops.go:394-411; internal/gobackend/fusedops/quantizeddense.go:250-321):
+ * data [vocabSize, bytesPerRow] Uint8 GGML blocks, indices integer [batch..., 1] -> Float32 [batch..., K].  scheme must be
+ * 2 (GGML), else CB_ERR_NOT_IMPLEMENTED.  An index outside the table makes Execute return an error, as the reference's
+ * executor does (:487-489). */
+int cbg_fn_quantized_embedding_lookup(cbg_function* f, cbg_value* data, cbg_value* indices, int scheme, int ggml_type, cbg_value** v);
 
 /* FusedOps.FusedScaledDotProductAttention (fused_ops.go:349-378) with
  * ScaledDotProductAttentionConfig (:245-277); NULL values = unset. */

@@ -273,26 +273,88 @@ void orc_qdense_nf4(const float* x, const void* w, const float* scales, const fl
 }
 
 /* ------------------------------------------------------------------ */
-/* GGML block formats Q4_0 and Q8_0                                   */
+/* GGML block formats Q4_0, Q8_0, IQ4_NL, Q4_K, Q6_K                  */
 /* ------------------------------------------------------------------ */
 
-/* quantizeddense_ggml.go:159-196.  A row is K / 32 blocks; a block starts with its scale d as a
- * little-endian fp16.  Q8_0 (34 bytes): value i = d * int8(q[i]).  Q4_0 (18 bytes): value i = d * (low
- * nibble of q[i] - 8), value 16 + i = d * (high nibble of q[i] - 8), i < 16. */
+/* Type codes of compute.GGMLQuantType (fused_ops.go:132-145); values and bytes per block (:148-176). */
+enum { ORC_GGML_Q4_0 = 0, ORC_GGML_Q8_0 = 1, ORC_GGML_IQ4_NL = 2, ORC_GGML_Q4_K = 5, ORC_GGML_Q6_K = 7 };
+int orc_ggml_values_per_block(int t) { return (t == ORC_GGML_Q4_0 || t == ORC_GGML_Q8_0 || t == ORC_GGML_IQ4_NL) ? 32 : (t == ORC_GGML_Q4_K || t == ORC_GGML_Q6_K) ? 256 : 0; }
+int orc_ggml_bytes_per_block(int t) {
+  switch (t) { case ORC_GGML_Q4_0: case ORC_GGML_IQ4_NL: return 18; case ORC_GGML_Q8_0: return 34; case ORC_GGML_Q4_K: return 144; case ORC_GGML_Q6_K: return 210; default: return 0; }
+}
+/* compute.IQ4NLLookupTable (fused_ops.go:127-130) */
+static const float orc_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* getScaleMinK4 (quantizeddense_ggml.go:219-228): the 6-bit scale and min of sub-block j from the 12 packed bytes */
+static void orc_scale_min_k4(int j, const uint8_t* sc, uint8_t* scale, uint8_t* min) {
+  if (j < 4) { *scale = sc[j] & 63; *min = sc[j + 4] & 63; }
+  else { *scale = (uint8_t)((sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4)); *min = (uint8_t)((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4)); }
+}
+
+/* quantizeddense_ggml.go:157-302.  A row is K / values_per_block blocks; fp16 fields are little-endian.
+ *   Q8_0 (34 bytes): d, 32 int8: value i = d * q[i].
+ *   Q4_0 (18 bytes): d, 16 bytes: value i = d * (low nibble of q[i] - 8), value 16 + i = d * (high nibble - 8).
+ *   IQ4_NL: as Q4_0 with table[nibble] in place of nibble - 8.
+ *   Q4_K (144 bytes): d, dmin, 12 bytes of 6-bit scales / mins, 128 nibble bytes; 4 chunks of 64 values: the low nibbles
+ *     of 32 bytes with (scale, min) 2c, then their high nibbles with 2c + 1; value = (d * scale) * nibble - dmin * min.
+ *   Q6_K (210 bytes): ql[128], qh[64], int8 scales[16], d; two halves of 128 values; value = (d * scale) * (q - 32)
+ *     with q = 4 low bits from ql, 2 high bits from qh. */
 void orc_ggml_dequant_row(const uint8_t* data, float* out, int64_t K, int ggml_type) {
-  const int64_t nblocks = K / 32;
-  const int bb = ggml_type == 1 ? 34 : 18;
+  const int vpb = orc_ggml_values_per_block(ggml_type), bb = orc_ggml_bytes_per_block(ggml_type);
+  if (!vpb) return;
+  const int64_t nblocks = K / vpb;
   for (int64_t b = 0; b < nblocks; b++) {
     const uint8_t* blk = data + b * bb;
-    const float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
-    const uint8_t* qs = blk + 2;
-    float* o = out + b * 32;
-    if (ggml_type == 1) {
-      for (int i = 0; i < 32; i++) o[i] = d * (float)(int8_t)qs[i];
-    } else {
+    float* o = out + b * vpb;
+    if (ggml_type == ORC_GGML_Q8_0) {
+      const float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+      for (int i = 0; i < 32; i++) o[i] = d * (float)(int8_t)blk[2 + i];
+    } else if (ggml_type == ORC_GGML_Q4_0 || ggml_type == ORC_GGML_IQ4_NL) {
+      const float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+      const uint8_t* qs = blk + 2;
       for (int i = 0; i < 16; i++) {
-        o[i] = d * (float)((int)(qs[i] & 0x0F) - 8);
-        o[16 + i] = d * (float)((int)(qs[i] >> 4) - 8);
+        if (ggml_type == ORC_GGML_Q4_0) {
+          o[i] = d * (float)((int)(qs[i] & 0x0F) - 8);
+          o[16 + i] = d * (float)((int)(qs[i] >> 4) - 8);
+        } else {
+          o[i] = d * orc_iq4nl[qs[i] & 0x0F];
+          o[16 + i] = d * orc_iq4nl[qs[i] >> 4];
+        }
+      }
+    } else if (ggml_type == ORC_GGML_Q4_K) {
+      const float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+      const float dmin = orc_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+      const uint8_t* scales = blk + 4;
+      const uint8_t* qs = blk + 16;
+      int idx = 0;
+      for (int chunk = 0; chunk < 4; chunk++) {
+        uint8_t sc1, m1, sc2, m2;
+        orc_scale_min_k4(2 * chunk, scales, &sc1, &m1);
+        orc_scale_min_k4(2 * chunk + 1, scales, &sc2, &m2);
+        const float d1 = d * (float)sc1, min1 = dmin * (float)m1;
+        const float d2 = d * (float)sc2, min2 = dmin * (float)m2;
+        for (int l = 0; l < 32; l++) { const float t = d1 * (float)(qs[chunk * 32 + l] & 0xF); o[idx++] = t - min1; }
+        for (int l = 0; l < 32; l++) { const float t = d2 * (float)(qs[chunk * 32 + l] >> 4); o[idx++] = t - min2; }
+      }
+    } else {  /* Q6_K */
+      const uint8_t* ql = blk;
+      const uint8_t* qh = blk + 128;
+      const int8_t* sc = (const int8_t*)(blk + 192);
+      const float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8)));
+      for (int half = 0; half < 2; half++) {
+        for (int l = 0; l < 32; l++) {
+          const int is = l / 16;
+          const int q1 = (int)(int8_t)((ql[l] & 0xF) | ((qh[l] & 3) << 4)) - 32;
+          const int q2 = (int)(int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+          const int q3 = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+          const int q4 = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+          float t;
+          t = d * (float)sc[is];     o[l]      = t * (float)q1;
+          t = d * (float)sc[is + 2]; o[l + 32] = t * (float)q2;
+          t = d * (float)sc[is + 4]; o[l + 64] = t * (float)q3;
+          t = d * (float)sc[is + 6]; o[l + 96] = t * (float)q4;
+        }
+        o += 128; ql += 64; qh += 32; sc += 8;
       }
     }
   }
@@ -302,7 +364,8 @@ void orc_ggml_dequant_row(const uint8_t* data, float* out, int64_t K, int ggml_t
  * float, k ascending; then + bias[n]; the activation over the whole output last (:89). */
 void orc_qdense_ggml(const float* x, const uint8_t* w, const float* bias, float* out,
                      int64_t M, int64_t K, int64_t N, int ggml_type, int activation) {
-  const int64_t bytes_per_row = K / 32 * (ggml_type == 1 ? 34 : 18);
+  const int vpb = orc_ggml_values_per_block(ggml_type);
+  const int64_t bytes_per_row = vpb ? K / vpb * orc_ggml_bytes_per_block(ggml_type) : 0;
   float* row = (float*)malloc((size_t)(K > 0 ? K : 1) * sizeof(float));
   for (int64_t n = 0; n < N; n++) {
     orc_ggml_dequant_row(w + n * bytes_per_row, row, K, ggml_type);
@@ -315,6 +378,19 @@ void orc_qdense_ggml(const float* x, const uint8_t* w, const float* bias, float*
   }
   free(row);
   orc_activation_f32(out, (size_t)(M * N), activation);
+}
+
+/* execQuantizedEmbeddingLookup (quantizeddense.go:455-499): out[i, :] = the dequantised row indices[i] of the table;
+ * returns the position of the first index outside [0, vocab) (the reference returns an error there), or -1. */
+int64_t orc_embedding_lookup(const uint8_t* table, const int64_t* indices, float* out, int64_t vocab, int64_t n_indices,
+                             int64_t K, int ggml_type) {
+  const int vpb = orc_ggml_values_per_block(ggml_type);
+  const int64_t bytes_per_row = vpb ? K / vpb * orc_ggml_bytes_per_block(ggml_type) : 0;
+  for (int64_t i = 0; i < n_indices; i++) {
+    if (indices[i] < 0 || indices[i] >= vocab) return i;
+    orc_ggml_dequant_row(table + indices[i] * bytes_per_row, out + i * K, K, ggml_type);
+  }
+  return -1;
 }
 
 /* ------------------------------------------------------------------ */

@@ -443,8 +443,76 @@ def qkv_projection(x, w_qkv, bias_q, bias_k, bias_v, query_dim: int, key_value_d
 
 
 # ---------------------------------------------------------------- GGML block formats
-GGML_Q4_0, GGML_Q8_0 = 0, 1
-GGML_BLOCK_BYTES = {GGML_Q4_0: 18, GGML_Q8_0: 34}
+# compute.GGMLQuantType (fused_ops.go:132-145): codes, bytes per block and values per block (:148-176)
+GGML_Q4_0, GGML_Q8_0, GGML_IQ4_NL, GGML_Q4_K, GGML_Q6_K = 0, 1, 2, 5, 7
+GGML_BLOCK_BYTES = {GGML_Q4_0: 18, GGML_Q8_0: 34, GGML_IQ4_NL: 18, GGML_Q4_K: 144, GGML_Q6_K: 210}
+GGML_BLOCK_VALUES = {GGML_Q4_0: 32, GGML_Q8_0: 32, GGML_IQ4_NL: 32, GGML_Q4_K: 256, GGML_Q6_K: 256}
+GGML_NAMES = {GGML_Q4_0: "q4_0", GGML_Q8_0: "q8_0", GGML_IQ4_NL: "iq4_nl", GGML_Q4_K: "q4_k", GGML_Q6_K: "q6_k"}
+IQ4NL_TABLE = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)   # fused_ops.go:127-130
+
+
+def ggml_random_rows(rng, N: int, K: int, ggml_type: int) -> np.ndarray:
+    """Test data: [N, bytesPerRow] native blocks with every quant / packed-scale byte random (all bit patterns are
+    legal there) and the fp16 block scales drawn from U(0.001, 0.02)."""
+    vpb, bb = GGML_BLOCK_VALUES[ggml_type], GGML_BLOCK_BYTES[ggml_type]
+    assert K % vpb == 0
+    nb = K // vpb
+    out = rng.integers(0, 256, size=(N, nb, bb), dtype=np.int64).astype(np.uint8)
+    def put_f16(offset):
+        d = rng.uniform(0.001, 0.02, size=(N, nb)).astype(np.float16)
+        out[..., offset:offset + 2] = d.view(np.uint16)[..., None].view(np.uint8).reshape(N, nb, 2)
+    if ggml_type == GGML_Q6_K:
+        put_f16(208)
+    else:
+        put_f16(0)
+        if ggml_type == GGML_Q4_K:
+            put_f16(2)
+    return np.ascontiguousarray(out.reshape(N, nb * bb))
+
+
+def ggml_dequant_rows_numpy(data: np.ndarray, ggml_type: int) -> np.ndarray:
+    """A second, vectorised restatement of quantizeddense_ggml.go:157-302 (float32 arithmetic in the reference's
+    order); tests hold it against the C one bit for bit."""
+    data = np.ascontiguousarray(data, np.uint8)
+    N, bpr = data.shape
+    bb, vpb = GGML_BLOCK_BYTES[ggml_type], GGML_BLOCK_VALUES[ggml_type]
+    blk = data.reshape(N, bpr // bb, bb)
+    f16 = lambda o: np.ascontiguousarray(blk[..., o:o + 2]).view(np.float16)[..., 0].astype(np.float32)
+    f32 = np.float32
+    if ggml_type == GGML_Q8_0:
+        vals = f16(0)[..., None] * blk[..., 2:].view(np.int8).astype(f32)
+    elif ggml_type in (GGML_Q4_0, GGML_IQ4_NL):
+        qs = blk[..., 2:]
+        nib = np.concatenate([qs & 0xF, qs >> 4], axis=-1)
+        q = nib.astype(f32) - f32(8) if ggml_type == GGML_Q4_0 else IQ4NL_TABLE[nib]
+        vals = f16(0)[..., None] * q
+    elif ggml_type == GGML_Q4_K:
+        d, dmin, sc, qs = f16(0), f16(2), blk[..., 4:16].astype(np.int32), blk[..., 16:]
+        scale = np.empty(blk.shape[:2] + (8,), np.int32)
+        mn = np.empty_like(scale)
+        for j in range(8):
+            if j < 4:
+                scale[..., j], mn[..., j] = sc[..., j] & 63, sc[..., j + 4] & 63
+            else:
+                scale[..., j] = (sc[..., j + 4] & 0xF) | ((sc[..., j - 4] >> 6) << 4)
+                mn[..., j] = (sc[..., j + 4] >> 4) | ((sc[..., j] >> 6) << 4)
+        dd = d[..., None] * scale.astype(f32)
+        mm = dmin[..., None] * mn.astype(f32)
+        q = qs.reshape(blk.shape[:2] + (4, 32))
+        nib = np.stack([q & 0xF, q >> 4], axis=3).reshape(blk.shape[:2] + (8, 32)).astype(f32)     # sub-block j = 2 * chunk + half
+        vals = (dd[..., None] * nib - mm[..., None]).reshape(blk.shape[:2] + (256,))
+    else:
+        ql = blk[..., 0:128].reshape(blk.shape[:2] + (2, 64)).astype(np.int32)
+        qh = blk[..., 128:192].reshape(blk.shape[:2] + (2, 32)).astype(np.int32)
+        sc = blk[..., 192:208].view(np.int8).reshape(blk.shape[:2] + (2, 8)).astype(f32)
+        d = f16(208)
+        lo, hi = ql[..., :32], ql[..., 32:]
+        q = np.stack([(lo & 0xF) | ((qh & 3) << 4), (hi & 0xF) | (((qh >> 2) & 3) << 4),
+                      (lo >> 4) | (((qh >> 4) & 3) << 4), (hi >> 4) | (((qh >> 6) & 3) << 4)], axis=3) - 32     # [N, nb, 2, 4, 32]
+        ds = d[..., None, None] * sc                                                                           # [N, nb, 2, 8]
+        scale = np.repeat(ds.reshape(blk.shape[:2] + (2, 4, 2)), 16, axis=-1)                                    # index 2 * quarter + l // 16
+        vals = (scale * q.astype(f32)).reshape(blk.shape[:2] + (256,))
+    return np.ascontiguousarray(vals.reshape(N, -1).astype(f32))
 
 
 def ggml_quantize_rows(w: np.ndarray, ggml_type: int) -> np.ndarray:
@@ -471,7 +539,7 @@ def ggml_quantize_rows(w: np.ndarray, ggml_type: int) -> np.ndarray:
 def ggml_dequant_rows(data: np.ndarray, ggml_type: int) -> np.ndarray:
     data = np.ascontiguousarray(data, np.uint8)
     N, bpr = data.shape
-    K = bpr // GGML_BLOCK_BYTES[ggml_type] * 32
+    K = bpr // GGML_BLOCK_BYTES[ggml_type] * GGML_BLOCK_VALUES[ggml_type]
     out = np.empty((N, K), np.float32)
     fn = lib().orc_ggml_dequant_row
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int]
@@ -485,7 +553,7 @@ def qdense_ggml(x, w_blocks, bias=None, ggml_type: int = GGML_Q8_0, activation: 
     x = _c(x, np.float32)
     w_blocks = np.ascontiguousarray(w_blocks, np.uint8)
     N, bpr = w_blocks.shape
-    K = bpr // GGML_BLOCK_BYTES[ggml_type] * 32
+    K = bpr // GGML_BLOCK_BYTES[ggml_type] * GGML_BLOCK_VALUES[ggml_type]
     assert x.shape[-1] == K
     M = x.size // K if K else 0
     b = None if bias is None else _c(bias, np.float32)
@@ -493,6 +561,24 @@ def qdense_ggml(x, w_blocks, bias=None, ggml_type: int = GGML_Q8_0, activation: 
     fn = lib().orc_qdense_ggml
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int]
     fn(_p(x), _p(w_blocks), _p(b), _p(out), M, K, N, ggml_type, activation)
+    return out
+
+
+def embedding_lookup(table, indices, ggml_type: int) -> np.ndarray:
+    """Reference QuantizedEmbeddingLookup (quantizeddense.go:250-321, 455-499): indices [..., 1] of any integer
+    dtype -> float32 [..., K]; an index outside the table raises, as the reference returns an error."""
+    table = np.ascontiguousarray(table, np.uint8)
+    idx = np.ascontiguousarray(indices).astype(np.int64)
+    assert idx.ndim >= 1 and idx.shape[-1] == 1
+    vocab, bpr = table.shape
+    K = bpr // GGML_BLOCK_BYTES[ggml_type] * GGML_BLOCK_VALUES[ggml_type]
+    out = np.empty(idx.shape[:-1] + (K,), np.float32)
+    fn = lib().orc_embedding_lookup
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int]
+    fn.restype = C.c_int64
+    bad = fn(_p(table), _p(idx), _p(out), vocab, idx.size, K, ggml_type)
+    if bad >= 0:
+        raise IndexError(f"QuantizedEmbeddingLookup: index {int(idx.reshape(-1)[bad])} out of range [0, {vocab})")
     return out
 
 

@@ -27,9 +27,9 @@ def test_backend_identity(backend):
     caps = backend.Capabilities()
     for op in (be.OP_PARAMETER, be.OP_CONSTANT, be.OP_DOT_GENERAL, be.OP_FUSED_QUANTIZED_DENSE, be.OP_FUSED_SDPA,
                be.OP_FUSED_DENSE, be.OP_FUSED_SOFTMAX, be.OP_FUSED_GELU, be.OP_FUSED_LAYER_NORM,
-               be.OP_FUSED_ATTENTION_QKV_PROJECTION, be.OP_ALL_REDUCE, be.OP_ALL_GATHER):
+               be.OP_FUSED_ATTENTION_QKV_PROJECTION, be.OP_ALL_REDUCE, be.OP_ALL_GATHER, be.OP_QUANTIZED_EMBEDDING_LOOKUP):
         assert caps.Operations.get(op)
-    assert len(caps.Operations) == 12        # element-wise and data-movement helpers exist but are not advertised
+    assert len(caps.Operations) == 13        # element-wise and data-movement helpers exist but are not advertised
     assert caps.DTypes.get(dv.BF16) and caps.DTypes.get(dv.F64) and not caps.Functions
     assert not backend.HasSharedBuffers()
 
@@ -266,8 +266,45 @@ def test_fused_quantized_dense_ggml_through_api(backend):
         f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_0))
     assert not isinstance(e.value, ErrNotImplemented)
     f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q8_0))
-    with pytest.raises(ErrNotImplemented):      # K-quants are not built
-        f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=5))
+    with pytest.raises(ErrNotImplemented):      # Q2_K: not supported in the fused path, as in the reference (quantizeddense.go:145-152)
+        f.FusedQuantizedDense(xp, wp, None, be.Quantization(be.QUANT_GGML, GGMLType=3))
+
+
+def test_quantized_embedding_lookup_through_api(backend):
+    """A token-embedding table in Q4_K blocks feeding a Q6_K projection: lookup -> FusedQuantizedDense in one Executable."""
+    vocab, K, N = 64, 512, 24
+    rng = np.random.default_rng(17)
+    table = orc.ggml_random_rows(rng, vocab, K, orc.GGML_Q4_K)
+    wq = orc.ggml_random_rows(rng, N, K, orc.GGML_Q6_K)
+    idx = rng.integers(0, vocab, size=(2, 3, 1)).astype(np.int32)
+    def build(f, p):
+        emb = f.QuantizedEmbeddingLookup(p[0], p[1], be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_K))
+        return [emb, f.FusedQuantizedDense(emb, p[2], None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q6_K))]
+    (emb, y), (s_emb, s_y) = be.exec_graph(backend, [(table, dv.U8), (idx, dv.I32), (wq, dv.U8)], build)
+    assert s_emb == be.make_shape(dv.F32, 2, 3, K) and s_y == be.make_shape(dv.F32, 2, 3, N)
+    want = orc.embedding_lookup(table, idx, orc.GGML_Q4_K)
+    assert np.array_equal(emb.view(np.uint32), want.view(np.uint32))
+    assert max_abs_normalised(y, orc.qdense_ggml(want, wq, None, orc.GGML_Q6_K)) < 1e-4
+    # an index outside the table is an error of Execute (quantizeddense.go:487-489)
+    bad = idx.copy()
+    bad[1, 1, 0] = vocab + 3
+    with pytest.raises(BackendError) as e:
+        be.exec_graph(backend, [(table, dv.U8), (bad, dv.I32), (wq, dv.U8)], build)
+    assert "out of range [0, 64)" in str(e.value)
+    # builder validation (quantizeddense.go:262-302)
+    f = backend.Builder("lookup").Main()
+    tp = f.Parameter("t", be.make_shape(dv.U8, vocab, 144 * 2))
+    ip = f.Parameter("i", be.make_shape(dv.I32, 4, 1))
+    with pytest.raises(ErrNotImplemented):
+        f.QuantizedEmbeddingLookup(tp, ip, be.Quantization(be.QUANT_LINEAR))
+    with pytest.raises(BackendError) as e:
+        f.QuantizedEmbeddingLookup(tp, f.Parameter("i2", be.make_shape(dv.I32, 4)), be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_K))
+    assert "indices last dim must be 1" in str(e.value)
+    with pytest.raises(BackendError) as e:
+        f.QuantizedEmbeddingLookup(tp, f.Parameter("i3", be.make_shape(dv.F32, 4, 1)), be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_K))
+    assert "indices must be integer" in str(e.value)
+    with pytest.raises(BackendError):           # 288 bytes are not whole Q6_K blocks
+        f.QuantizedEmbeddingLookup(tp, ip, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q6_K))
 
 
 def test_fused_quantized_dense_nf4_through_api(backend):

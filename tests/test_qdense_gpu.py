@@ -137,9 +137,99 @@ def test_ggml_block_formats(M, K, N, x_dtype, ggml):
     assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else F32_TOL)
 
 
-def test_ggml_validation():
+GGML_TYPES = {"q4_0": dv.GGML_Q4_0, "q8_0": dv.GGML_Q8_0, "iq4_nl": dv.GGML_IQ4_NL, "q4_k": dv.GGML_Q4_K, "q6_k": dv.GGML_Q6_K}
+
+
+@pytest.mark.parametrize("ggml", list(GGML_TYPES))
+@pytest.mark.parametrize("M,K,N,bias,act", [
+    (1, 4096, 520, False, "none"),        # one token; N leaves a partly filled CTA and warp
+    (3, 256, 33, True, "gelu"),           # one K-quant block per row
+    (4, 1280, 64, True, "silu"),          # K is not a multiple of the 1024-value chunk
+    (16, 2304, 40, False, "relu"),
+    (21, 512, 9, True, "tanh"),           # two passes over the rows of x
+])
+def test_ggml_every_format_random_blocks(ggml, M, K, N, bias, act):
+    """All five block formats of quantizeddense_ggml.go:133-302 on blocks whose quant and packed-scale bytes are random
+    (every bit pattern of the 6-bit scale packing and of the high / low quant bits occurs)."""
+    gt = GGML_TYPES[ggml]
+    rng = np.random.default_rng(1000 * gt + M + N)
+    wq = orc.ggml_random_rows(rng, N, K, gt)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32) if bias else None
+    want = orc.qdense_ggml(x, wq, b, gt, ACT[act])
+    plan = dv.Plan.qdense(M, K, N, dv.F32, dv.U8, has_bias=bias, activation=ACT[act], scheme=dv.QUANT_GGML, ggml_type=gt)
+    assert plan.kernel_name == f"qdense_ggml_f32_{ggml}"
+    got = ops._run(plan, [x, wq] + ([b] if bias else []), (M, N), np.float32)
+    assert max_abs_normalised(got, want) < F32_TOL
+
+
+@pytest.mark.parametrize("ggml", list(GGML_TYPES))
+def test_ggml_dequantised_values_are_bit_exact(ggml):
+    """x = identity rows picks single weights: every dequantised value must carry the reference's bits."""
+    gt = GGML_TYPES[ggml]
+    K, N = 512, 37
+    rng = np.random.default_rng(7 + gt)
+    wq = orc.ggml_random_rows(rng, N, K, gt)
+    want = orc.ggml_dequant_rows(wq, gt)                  # [N, K]
+    for k0 in (0, 256):
+        x = np.zeros((16, K), np.float32)
+        cols = k0 + rng.choice(256, size=16, replace=False)
+        x[np.arange(16), cols] = 1.0
+        plan = dv.Plan.qdense(16, K, N, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=gt)
+        got = ops._run(plan, [x, wq], (16, N), np.float32)
+        # every selected weight with the reference's bits (the sum adds +0 to it, so a -0 weight reads back as +0)
+        assert np.array_equal(got, want[:, cols].T) and not np.isnan(got).any()
+
+
+@pytest.mark.parametrize("ggml", list(GGML_TYPES))
+@pytest.mark.parametrize("index_dtype", ["i32", "i64", "u8"])
+def test_quantized_embedding_lookup(ggml, index_dtype):
+    """QuantizedEmbeddingLookup (quantizeddense.go:455-499): rows of a block table, bit for bit."""
+    gt = GGML_TYPES[ggml]
+    vocab, K = 200, 1280
+    rng = np.random.default_rng(31 + gt)
+    table = orc.ggml_random_rows(rng, vocab, K, gt)
+    npdt, code = {"i32": (np.int32, dv.I32), "i64": (np.int64, dv.I64), "u8": (np.uint8, dv.U8)}[index_dtype]
+    idx = rng.integers(0, vocab, size=(3, 5, 1)).astype(npdt)
+    idx[0, 0, 0], idx[2, 4, 0] = 0, vocab - 1
+    want = orc.embedding_lookup(table, idx, gt)
+    plan = dv.Plan.embedding_lookup(vocab, table.shape[1], idx.size, code, gt)
+    assert plan.kernel_name == f"embedding_lookup_{ggml}"
+    got = ops._run(plan, [table, idx], (3, 5, K), np.float32)         # checks the plan's status words too
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # an index outside the table: zeros for that row and the reference's error from the status check
+    bad = idx.copy().astype(np.int64)
+    bad[1, 2, 0] = vocab
+    plan64 = dv.Plan.embedding_lookup(vocab, table.shape[1], idx.size, dv.I64, gt)
+    bufs = [dv.DeviceMem.from_numpy(a) for a in (table, bad)]
+    out, ws64 = dv.DeviceMem(15 * K * 4), plan64.new_workspace()
+    plan64.launch([b.ptr for b in bufs], [out.ptr], ws64.ptr)
+    dv.check(dv._lib.load().cb_stream_sync(0, None))
+    got = out.download((3, 5, K), np.float32)
+    assert not got[1, 2].any() and np.array_equal(got[0], want[0])
+    with pytest.raises(BackendError) as e:
+        plan64.check_status(ws64.ptr)
+    assert "position 7 out of range [0, 200)" in str(e.value)
+    for m in bufs + [out, ws64]:
+        m.free()
+
+
+def test_embedding_lookup_validation():
+    with pytest.raises(BackendError):            # bytesPerRow must be whole blocks (quantizeddense.go:171-174)
+        dv.Plan.embedding_lookup(10, 100, 4, dv.I32, dv.GGML_Q4_0)
     with pytest.raises(ErrNotImplemented):
-        dv.Plan.qdense(1, 256, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=5)          # Q4_K: not built
+        dv.Plan.embedding_lookup(10, 84, 4, dv.I32, 3)              # Q2_K
+    with pytest.raises(BackendError) as e:
+        dv.Plan.embedding_lookup(10, 36, 4, dv.F32, dv.GGML_Q4_0)
+    assert "indices must be integer" in str(e.value)
+
+
+def test_ggml_validation():
+    for unsupported in (3, 4, 6):          # Q2_K, Q3_K, Q5_K: ErrNotImplemented in the reference too (quantizeddense.go:145-152)
+        with pytest.raises(ErrNotImplemented):
+            dv.Plan.qdense(1, 256, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=unsupported)
+    with pytest.raises(BackendError):
+        dv.Plan.qdense(1, 128, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=dv.GGML_Q4_K)  # K-quants: K in whole 256-value blocks
     with pytest.raises(BackendError):
         dv.Plan.qdense(1, 48, 8, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=dv.GGML_Q8_0)  # K not whole blocks
     with pytest.raises(BackendError) as e:
