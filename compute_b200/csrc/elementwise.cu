@@ -201,24 +201,28 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restri
     __syncthreads();      // s_part / s_inv are rewritten for the next row
   }
 }
-// The streaming form for rows whose bytes are a multiple of 16 and that fit 16 vectors per lane: one warp per row,
-// the row read once with 16-byte loads into registers, reduced by shuffles (no shared memory, no block barrier),
-// written with 16-byte stores.  NV = vectors per lane.
-template <typename T, int NV>
+// The streaming form for rows whose bytes are a multiple of 16: WPR warps per row (1 for short rows, 4 from 128 vectors
+// up, so that a few thousand rows still fill the SMs with loads in flight), the row read once with 16-byte loads into
+// registers (NV vectors per lane), reduced by shuffles and, for WPR > 1, one exchange through shared memory, written
+// with 16-byte stores.  Rows are taken block-wide in a grid-stride loop, so every thread reaches every barrier.
+template <typename T, int NV, int WPR>
 __global__ void __launch_bounds__(RMS_THREADS)
-rmsnorm_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, int64_t rows, int64_t L, float eps) {
+rmsnorm_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, int64_t rows, int64_t L, float eps) {
   constexpr int VEC = 16 / (int)sizeof(T);
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = (int64_t)blockIdx.x * (RMS_THREADS / 32) + (threadIdx.x >> 5);
-  const int64_t n_warps = (int64_t)gridDim.x * (RMS_THREADS / 32);
+  constexpr int RPB = RMS_THREADS / 32 / WPR;             // rows per block and pass
+  __shared__ float s_part[RPB][WPR];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r_in = warp / WPR, w_in = warp % WPR;
   const int64_t n_vec = L / VEC;
-  for (int64_t row = warp; row < rows; row += n_warps) {
+  for (int64_t row0 = (int64_t)blockIdx.x * RPB; row0 < rows; row0 += (int64_t)gridDim.x * RPB) {
+    const int64_t row = row0 + r_in;
+    const bool live = row < rows;
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * L);
     uint4 raw[NV];
 #pragma unroll
     for (int j = 0; j < NV; j++) {
-      const int64_t c = lane + (int64_t)j * 32;
-      raw[j] = c < n_vec ? __ldg(xr + c) : make_uint4(0, 0, 0, 0);
+      const int64_t c = (int64_t)(j * WPR + w_in) * 32 + lane;
+      raw[j] = (live && c < n_vec) ? __ldg(xr + c) : make_uint4(0, 0, 0, 0);
     }
     float ss = 0.0f;
 #pragma unroll
@@ -229,12 +233,20 @@ rmsnorm_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __r
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+    if (WPR > 1) {
+      if (lane == 0) s_part[r_in][w_in] = ss;
+      __syncthreads();
+      ss = 0.0f;
+#pragma unroll
+      for (int k = 0; k < WPR; k++) ss += s_part[r_in][k];
+      __syncthreads();                      // the partials are rewritten in the next pass
+    }
     const float inv = rsqrtf(ss / (float)L + eps);
     uint4* orow = reinterpret_cast<uint4*>(out + row * L);
 #pragma unroll
     for (int j = 0; j < NV; j++) {
-      const int64_t c = lane + (int64_t)j * 32;
-      if (c < n_vec) {
+      const int64_t c = (int64_t)(j * WPR + w_in) * 32 + lane;
+      if (live && c < n_vec) {
         uint4 gv = make_uint4(0, 0, 0, 0);
         if (gamma) gv = __ldg(reinterpret_cast<const uint4*>(gamma) + c);
         const T* e = reinterpret_cast<const T*>(&raw[j]);
@@ -448,17 +460,22 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
         const T* g = (h.flags & 1) ? (const T*)in[1] : nullptr;
         if constexpr (sizeof(T) <= 4) {
           constexpr int VEC = 16 / (int)sizeof(T);
-          const int64_t L = h.dims[1], per_lane = (L / VEC + 31) / 32;
+          const int64_t L = h.dims[1], n_vec = L / VEC;
           const bool aligned = !((reinterpret_cast<uintptr_t>(in[0]) | reinterpret_cast<uintptr_t>(out[0]) | reinterpret_cast<uintptr_t>(g)) & 15);
-          if (L % VEC == 0 && per_lane <= 16 && aligned) {
-            const int64_t want = (h.dims[0] + RMS_THREADS / 32 - 1) / (RMS_THREADS / 32);
+          const int wpr = n_vec >= 128 ? 4 : 1;
+          const int64_t per_lane = (n_vec + 32 * wpr - 1) / (32 * wpr);
+          if (L % VEC == 0 && per_lane <= 8 && aligned) {
+            const int rpb = RMS_THREADS / 32 / wpr;
+            const int64_t want = (h.dims[0] + rpb - 1) / rpb;
             const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)p->n_sm * 8));
-            auto go = [&](auto nv) {
-              rmsnorm_warp_kernel<T, decltype(nv)::value><<<grid, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], L, (float)h.eps);
+            auto go = [&](auto nv, auto w) {
+              rmsnorm_vec_kernel<T, decltype(nv)::value, decltype(w)::value><<<grid, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], L, (float)h.eps);
             };
-            if (per_lane <= 1) go(std::integral_constant<int, 1>()); else if (per_lane <= 2) go(std::integral_constant<int, 2>());
-            else if (per_lane <= 4) go(std::integral_constant<int, 4>()); else if (per_lane <= 8) go(std::integral_constant<int, 8>());
-            else go(std::integral_constant<int, 16>());
+            auto by_nv = [&](auto w) {
+              if (per_lane <= 1) go(std::integral_constant<int, 1>(), w); else if (per_lane <= 2) go(std::integral_constant<int, 2>(), w);
+              else if (per_lane <= 4) go(std::integral_constant<int, 4>(), w); else go(std::integral_constant<int, 8>(), w);
+            };
+            if (wpr == 4) by_nv(std::integral_constant<int, 4>()); else by_nv(std::integral_constant<int, 1>());
             return (int)CB_OK;
           }
         }

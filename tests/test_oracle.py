@@ -155,6 +155,36 @@ def test_dense_epilogue_golden(case):
     assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
 
 
+def requantise(w_ref, scale, zero_point, unsigned):
+    """Integer weights q with q * scale + zero_point == w_ref exactly (power-of-two scale, dyadic zero point)."""
+    q = (w_ref.astype(np.float64) - zero_point) / scale
+    assert np.array_equal(q, np.rint(q))
+    q = q.astype(np.int64)
+    assert q.min() >= (0 if unsigned else -128) and q.max() <= (255 if unsigned else 127)
+    return q.astype(np.uint8 if unsigned else np.int8)
+
+
+SCALED = [(0.25, None, False), (0.5, None, False), (0.25, 0.5, False), (0.125, -16.0, True), (1.0, 3.0, False)]
+
+
+@pytest.mark.parametrize("scale,zp,unsigned", SCALED)
+@pytest.mark.parametrize("case", DENSE, ids=[c["name"] for c in DENSE])
+def test_dense_epilogue_golden_with_scales_and_zero_points(case, scale, zp, unsigned):
+    """The reference's FusedDense numbers (fusedops.go:178-212) replayed through the quantized op with weights
+    stored as q = (w - zero_point) / scale: non-unit power-of-two scales and dyadic zero points dequantise to the
+    reference's weights exactly (quantizeddense.go:637-647: w * s + zp), so its expected values bind the scale and
+    zero-point path too."""
+    x = tensor(case["x"], "f32")
+    w_ref = tensor(case["w"], "i8")
+    K, N = w_ref.shape
+    q = requantise(w_ref, scale, zp or 0.0, unsigned)
+    for block in (1, 2, N):
+        nblk = (N + block - 1) // block
+        got = orc.qdense_linear(x, q, np.full((K, nblk), scale, np.float32), None if zp is None else np.full((K, nblk), zp, np.float32),
+                                np.array(case["bias"], np.float32), block, ACT[case["activation"]])
+        assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
+
+
 @pytest.mark.parametrize("case", DENSE, ids=[c["name"] for c in DENSE])
 def test_fused_dense_golden(case):
     """The same reference cases (fusedops.go:178-212) through the oracle's FusedDense restatement."""

@@ -247,6 +247,50 @@ def test_dense_epilogue_golden_on_gpu():
         assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
 
 
+@pytest.mark.parametrize("scale,zp,unsigned", [(0.25, None, False), (0.25, 0.5, False), (0.125, -16.0, True), (1.0, 3.0, False)])
+def test_dense_epilogue_golden_with_scales_and_zero_points_on_gpu(scale, zp, unsigned):
+    """fusedops.go:178-212 through the generic kernel with q = (w - zero_point) / scale: the reference's expected
+    numbers, exactly, with non-unit scales and zero points in the reference's own layout."""
+    from tests.test_oracle import requantise
+    for case in load_golden("backendtest_dense_epilogue.json")["cases"]:
+        x = tensor(case["x"], "f32")
+        w_ref = tensor(case["w"], "i8")
+        K, N = w_ref.shape
+        q = requantise(w_ref, scale, zp or 0.0, unsigned)
+        for block in (1, N):
+            nblk = (N + block - 1) // block
+            got = ops.quantized_dense(x, q, np.full((K, nblk), scale, np.float32), None if zp is None else np.full((K, nblk), zp, np.float32),
+                                      np.array(case["bias"], np.float32), block_size=block, activation=ACT[case["activation"]])
+            assert np.array_equal(got.ravel(), np.array(case["want"]["data"], np.float32))
+
+
+@pytest.mark.parametrize("variant,M_pad,x_dtype", [(dv.QDENSE_DECODE_TC, 0, "f32"), (dv.QDENSE_DECODE_TC, 0, "bf16"), (dv.QDENSE_DECODE_TC, 16, "bf16"),
+                                                   (dv.QDENSE_DECODE_MMA, 0, "f32"), (dv.QDENSE_PREFILL, 128, "f32")])
+def test_dense_epilogue_golden_through_the_tensor_core_kernels(variant, M_pad, x_dtype):
+    """The same reference cases embedded in a shape the streaming kernels accept: x padded with zero columns to K = 256
+    (the weights under them random), N padded to 256 with random columns, rows padded with zeros; weights q = 4 w with
+    scale 1/4 per 128-row group.  Every product and sum is a small dyadic number, so whatever the summation order the
+    reference's expected values must come back exactly in the original rows and columns."""
+    rng = np.random.default_rng(3)
+    for case in load_golden("backendtest_dense_epilogue.json")["cases"]:
+        x0 = tensor(case["x"], "f32")
+        w0 = tensor(case["w"], "i8")
+        (M0, K0), N0 = x0.shape, w0.shape[1]
+        K, N, M = 256, 256, max(M0, M_pad)
+        x = np.zeros((M, K), np.float32); x[:M0, :K0] = x0
+        q = rng.integers(-127, 128, size=(K, N), dtype=np.int64).astype(np.int8)
+        q[:K0, :N0] = 4 * w0
+        s = np.full((K // 128, N), 0.25, np.float32)
+        b = rng.standard_normal(N).astype(np.float32); b[:N0] = np.array(case["bias"], np.float32)
+        code = dv.BF16 if x_dtype == "bf16" else dv.F32
+        xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x          # the cases' values are exact in bfloat16
+        got, plan = ops.quantized_dense(xin, q, s, None, b, x_dtype=code, scale_layout=dv.SCALE_KGROUP, block_size=128,
+                                        activation=ACT[case["activation"]], variant=variant, return_plan=True)
+        gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+        want = np.array(case["want"]["data"], np.float32).reshape(M0, N0)
+        assert np.array_equal(gotf[:M0, :N0], want), (plan.kernel_name, case["name"])
+
+
 def test_config1_reference_cpu_case():
     """x f32 [64,1024], W int8 [1024,1024], per-output-channel scales, bias, no activation."""
     x, w, s, b = qdense_inputs(0x5EED0001, 64, 1024, 1024, scale_layout="channel")

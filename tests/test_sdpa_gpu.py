@@ -98,19 +98,22 @@ def test_sdpa_other_dtypes(dtype):
 
 
 def test_sdpa_config4_slice():
-    """B=8, 32 query / 8 kv heads, head_dim 128, seq 2048, bf16, causal: one (batch, kv head)
-    group of the full configuration against the oracle, the rest through a checksum identity
-    (with V = ones every output element is exactly 1)."""
+    """B=8, 32 query / 8 kv heads, head_dim 128, seq 2048, bf16, causal: two (batch, kv head) groups of the
+    full configuration against the oracle, the rest through a checksum identity (with V = ones every output
+    element is exactly 1).  A sampled group is all four query heads of its KV head over all 2048 query
+    positions: both head pairs that the causal kernel gives to one CTA (heads 4h, 4h+1 and 4h+2, 4h+3), and
+    every 128-row query tile from the first (one key tile) to the last (sixteen).  The second group is the
+    last batch entry and last KV head: the work items the persistent grid reaches last."""
     B, Hq, Hkv, S, D = 8, 32, 8, 2048, 128
     rng = np.random.default_rng(0x5EED0004)
     q = orc.bf16_from_f32(rng.standard_normal((B, Hq, S, D), dtype=np.float32))
     k = orc.bf16_from_f32(rng.standard_normal((B, Hkv, S, D), dtype=np.float32))
     v = orc.bf16_from_f32(rng.standard_normal((B, Hkv, S, D), dtype=np.float32))
     got = ops.sdpa(q, k, v, dtype=dv.BF16, causal=True)
-    b, h = 3, 5
-    qs = orc.bf16_to_f32(q[b:b + 1, 4 * h:4 * h + 4])
-    want = orc.sdpa(qs, orc.bf16_to_f32(k[b:b + 1, h:h + 1]), orc.bf16_to_f32(v[b:b + 1, h:h + 1]), causal=True, fast=True)
-    assert max_abs_normalised(orc.bf16_to_f32(got[b:b + 1, 4 * h:4 * h + 4]), want) < 2e-2
+    for b, h in ((3, 5), (B - 1, Hkv - 1)):
+        qs = orc.bf16_to_f32(q[b:b + 1, 4 * h:4 * h + 4])
+        want = orc.sdpa(qs, orc.bf16_to_f32(k[b:b + 1, h:h + 1]), orc.bf16_to_f32(v[b:b + 1, h:h + 1]), causal=True, fast=True)
+        assert max_abs_normalised(orc.bf16_to_f32(got[b:b + 1, 4 * h:4 * h + 4]), want) < 2e-2
     ones = orc.bf16_from_f32(np.ones((B, Hkv, S, D), np.float32))
     got1 = orc.bf16_to_f32(ops.sdpa(q, k, ones, dtype=dv.BF16, causal=True))
     assert np.max(np.abs(got1 - 1.0)) < 2e-2
