@@ -26,7 +26,7 @@ int dot_plan(cb_plan* p) {
   std::string why;
   const bool tc_ok = dot_tc_supports(d, &why);
   if (variant == CB_DOT_AUTO) variant = tc_ok ? CB_DOT_TCGEN05 : CB_DOT_GENERIC;
-  if (variant == CB_DOT_TCGEN05) {
+  if (variant == CB_DOT_TCGEN05 || variant == CB_DOT_TCGEN05_EXACT) {
     if (!tc_ok) return fail(CB_ERR_NOT_IMPLEMENTED, "DotGeneral tcgen05 kernel: %s", why.c_str());
     p->variant = variant;
     return dot_tc_plan(p);
@@ -42,7 +42,7 @@ int dot_plan(cb_plan* p) {
 }
 
 int dot_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  if (p->variant == CB_DOT_TCGEN05) return dot_tc_launch(p, in, out, ws, s);
+  if (p->variant == CB_DOT_TCGEN05 || p->variant == CB_DOT_TCGEN05_EXACT) return dot_tc_launch(p, in, out, ws, s);
   return dot_generic_launch(p->dot, in, out, s);
 }
 

@@ -41,12 +41,14 @@ int gemm_tc_threads();
 int gemm_tc_smem();
 int gemm_tc_run(int dev, int blocks, const GemmTcProblem& g, cudaStream_t s);
 
-// The passes of a full-precision product of an operand with `pa` planes and one with `pb`,
-// smallest terms first; returns their number (plane index sums above 2 are left out).
-int gemm_tc_split_passes(int pa, int pb, int* pass_a, int* pass_b);
+// The passes of a product of an operand with `pa` planes and one with `pb`, smallest terms first; returns their
+// number.  Plane index sums above max_sum are left out (2 for three-plane operands, 1 for two-plane ones: what is
+// dropped is no larger than what the planes themselves leave out).
+int gemm_tc_split_passes(int pa, int pb, int max_sum, int* pass_a, int* pass_b);
 
-// planes[i][e] for i < n_planes (2 or 3), e < n: the bf16 split of src.  Non-finite values
-// go to plane 0 alone.
-int split_f32_planes(const float* src, uint16_t* planes, size_t n, int n_planes, cudaStream_t s);
+// planes_x[i][e] for i < n_planes (2 or 3), e < n_x: the bf16 split of src_x, for two operands in one launch (n_b may
+// be 0).  Non-finite values go to plane 0 alone.
+int split_f32_planes(const float* src_a, uint16_t* planes_a, size_t n_a, const float* src_b, uint16_t* planes_b, size_t n_b,
+                     int n_planes, cudaStream_t s);
 
 }  // namespace cb

@@ -299,12 +299,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // ---------------------------------------------------------------------------
 // float32 -> bf16 planes
 // ---------------------------------------------------------------------------
+// One launch splits both operands: elements [0, n_a) come from src_a, the rest from src_b (both counts are rounded up
+// to the 4-element vectors a thread handles, so a vector never straddles the two).
 __global__ void __launch_bounds__(256)
-split_f32_planes_kernel(const float* __restrict__ src, uint16_t* __restrict__ planes, size_t n, int n_planes) {
+split_f32_planes_kernel(const float* __restrict__ src_a, uint16_t* __restrict__ planes_a, size_t n_a,
+                        const float* __restrict__ src_b, uint16_t* __restrict__ planes_b, size_t n_b, int n_planes) {
   // the GEMM that consumes the planes may set itself up meanwhile; it waits for this grid before it loads
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
-  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+  const size_t va = (n_a + 3) / 4, vb = (n_b + 3) / 4;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < va + vb; vi += stride) {
+    const bool second = vi >= va;
+    const float* src = second ? src_b : src_a;
+    uint16_t* planes = second ? planes_b : planes_a;
+    const size_t n = second ? n_b : n_a;
+    const size_t i = (second ? vi - va : vi) * 4;
     float v[4];
     if (i + 4 <= n && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
       const float4 f = *reinterpret_cast<const float4*>(src + i);
@@ -336,19 +345,21 @@ split_f32_planes_kernel(const float* __restrict__ src, uint16_t* __restrict__ pl
   }
 }
 
-int split_f32_planes(const float* src, uint16_t* planes, size_t n, int n_planes, cudaStream_t s) {
-  if (n == 0) return CB_OK;
+int split_f32_planes(const float* src_a, uint16_t* planes_a, size_t n_a, const float* src_b, uint16_t* planes_b, size_t n_b,
+                     int n_planes, cudaStream_t s) {
+  if (n_a + n_b == 0) return CB_OK;
   if (n_planes < 1 || n_planes > 3) return fail(CB_ERR_INVALID_ARG, "split_f32_planes: %d planes", n_planes);
-  const size_t want = (n / 4 + 255) / 256;
+  const size_t want = ((n_a + n_b) / 4 + 255) / 256;
   const int blocks = (int)std::min<size_t>(std::max<size_t>(want, 1), 148 * 16);
-  split_f32_planes_kernel<<<blocks, 256, 0, s>>>(src, planes, n, n_planes);
+  split_f32_planes_kernel<<<blocks, 256, 0, s>>>(src_a, planes_a, n_a, src_b, planes_b, n_b, n_planes);
   CB_CUDA(cudaGetLastError());
   return CB_OK;
 }
 
-int gemm_tc_split_passes(int pa, int pb, int* pass_a, int* pass_b) {
+// Plane products a_i * b_j with i + j <= max_sum (what lies beyond is below the planes' own residual).
+int gemm_tc_split_passes(int pa, int pb, int max_sum, int* pass_a, int* pass_b) {
   int n = 0;
-  for (int sum = 2; sum >= 0; sum--)            // smallest products first
+  for (int sum = max_sum; sum >= 0; sum--)      // smallest products first
     for (int i = pa - 1; i >= 0; i--) {
       const int j = sum - i;
       if (j < 0 || j >= pb) continue;
@@ -455,9 +466,9 @@ bool dot_tc_supports(const cb_dot_desc& d, std::string* why) {
   if (d.N % 8 != 0) return no("N must be a multiple of 8");
   if (d.M > (1 << 30) || d.N > (1 << 30) || d.K > (1 << 30) || d.B > (1 << 18)) return no("dimension too large");
   // small problems are launch bound: unless asked for explicitly, the generic kernel serves them
-  // (float32 pays two split launches on top, so its threshold is higher)
+  // (float32 pays a split launch on top, so its threshold is higher)
   const double macs = (double)d.B * d.M * d.N * d.K;
-  if (d.variant != CB_DOT_TCGEN05 && macs < (d.in_dtype == CB_F32 ? 256.0 * 256 * 256 : 128.0 * 256 * 256))
+  if (d.variant != CB_DOT_TCGEN05 && d.variant != CB_DOT_TCGEN05_EXACT && macs < (d.in_dtype == CB_F32 ? 256.0 * 256 * 256 : 128.0 * 256 * 256))
     return no("problem too small for the tensor-core tile");
   return true;
 }
@@ -472,8 +483,10 @@ __global__ void bias_to_f32_kernel(const T* __restrict__ src, float* __restrict_
   if (i < n) dst[i] = Scalar<T>::load(src, i);
 }
 
+static int dot_tc_planes(const cb_dot_desc& d) { return d.variant == CB_DOT_TCGEN05_EXACT ? 3 : 2; }
 static size_t dot_tc_planes_bytes(const cb_dot_desc& d) {
-  return d.in_dtype == CB_F32 ? align256((size_t)3 * d.B * d.M * d.K * 2) + align256((size_t)3 * d.B * d.K * d.N * 2) : 0;
+  const size_t np = (size_t)dot_tc_planes(d);
+  return d.in_dtype == CB_F32 ? align256(np * d.B * d.M * d.K * 2) + align256(np * d.B * d.K * d.N * 2) : 0;
 }
 
 int dot_tc_plan(cb_plan* p) {
@@ -483,12 +496,13 @@ int dot_tc_plan(cb_plan* p) {
   p->dyn_smem = GT_SMEM;
   p->counter_bytes = 256;
   p->workspace_bytes = 256;
-  p->workspace_bytes += dot_tc_planes_bytes(d);      // float32: three bf16 planes of each operand
+  p->workspace_bytes += dot_tc_planes_bytes(d);      // float32: two (or, exact, three) bf16 planes of each operand
   if (d.has_bias && d.in_dtype != CB_F32) p->workspace_bytes += align256((size_t)d.N * 4);
   p->has_status = true;
   const int od = d.out_dtype ? d.out_dtype : d.in_dtype;
   const bool dense = d.has_bias || d.activation != CB_ACT_NONE;
-  p->name = std::string("gemm_tcgen05_") + dtype_name(d.in_dtype) + "_" + dtype_name(od) + (d.rhs_transposed ? "_nt" : "_nn") + (dense ? "_dense" : "");
+  p->name = std::string("gemm_tcgen05_") + dtype_name(d.in_dtype) + "_" + dtype_name(od) + (d.rhs_transposed ? "_nt" : "_nn") + (dense ? "_dense" : "") +
+            (d.in_dtype == CB_F32 && d.variant == CB_DOT_TCGEN05_EXACT ? "_6pass" : "");
   return CB_OK;
 }
 
@@ -517,13 +531,13 @@ int dot_tc_launch(const cb_plan* p, const void* const* in, void* const* out, voi
   if (d.in_dtype == CB_F32) {
     uint8_t* w8 = (uint8_t*)ws;
     uint16_t* pa = (uint16_t*)(w8 + 256);
-    uint16_t* pb = (uint16_t*)(w8 + 256 + align256((size_t)3 * d.B * d.M * d.K * 2));
-    CB_TRY(split_f32_planes((const float*)in[0], pa, (size_t)d.B * d.M * d.K, 3, s));
-    CB_TRY(split_f32_planes((const float*)in[1], pb, (size_t)d.B * d.K * d.N, 3, s));
+    const int np = dot_tc_planes(d);
+    uint16_t* pb = (uint16_t*)(w8 + 256 + align256((size_t)np * d.B * d.M * d.K * 2));
+    CB_TRY(split_f32_planes((const float*)in[0], pa, (size_t)d.B * d.M * d.K, (const float*)in[1], pb, (size_t)d.B * d.K * d.N, np, s));
     g.a = pa; g.b = pb;
-    g.planes_a = g.planes_b = 3;
+    g.planes_a = g.planes_b = np;
     g.ab_dtype = CB_BF16;
-    g.n_pass = gemm_tc_split_passes(3, 3, g.pass_a, g.pass_b);
+    g.n_pass = gemm_tc_split_passes(np, np, np == 3 ? 2 : 1, g.pass_a, g.pass_b);
   }
   return gemm_tc_run(p->dev, p->blocks, g, s);
 }

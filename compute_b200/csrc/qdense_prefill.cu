@@ -151,7 +151,7 @@ int qdense_prefill_launch(const cb_plan* p, const void* const* in, void* const* 
   g.a = in[0];
   g.planes_a = 1;
   if (d.x_dtype == CB_F32) {
-    CB_TRY(split_f32_planes((const float*)in[0], xplanes, (size_t)d.M * d.K, 3, s));
+    CB_TRY(split_f32_planes((const float*)in[0], xplanes, (size_t)d.M * d.K, nullptr, nullptr, 0, 3, s));
     g.a = xplanes;
     g.planes_a = 3;
   }
@@ -163,7 +163,7 @@ int qdense_prefill_launch(const cb_plan* p, const void* const* in, void* const* 
   g.rhs_transposed = 0;
   g.ab_dtype = CB_BF16;
   g.out_dtype = d.x_dtype;
-  g.n_pass = gemm_tc_split_passes(g.planes_a, g.planes_b, g.pass_a, g.pass_b);
+  g.n_pass = gemm_tc_split_passes(g.planes_a, g.planes_b, 2, g.pass_a, g.pass_b);
   g.col_scale = raw ? (const float*)in[2] : nullptr;
   g.bias = bias;
   g.activation = d.activation;

@@ -176,7 +176,9 @@ int cb_qdense_decode_static(int dev, const cb_qdense_desc* desc, const void* x, 
 typedef enum {
   CB_DOT_AUTO = 0,
   CB_DOT_GENERIC = 1,   /* CUDA-core tiled kernel, every supported dtype                       */
-  CB_DOT_TCGEN05 = 2    /* tcgen05 / TMEM / TMA kernel (bf16, f16; f32 via 3-way bf16 split)   */
+  CB_DOT_TCGEN05 = 2,   /* tcgen05 / TMEM / TMA kernel: bf16, f16; f32 as two bf16 planes per operand and three
+                           plane products (a0b0 + a0b1 + a1b0: about 2^-17 relative per term, inside the 1e-4 bar) */
+  CB_DOT_TCGEN05_EXACT = 3  /* the same kernel with three planes per operand and six products (about 2e-6)         */
 } cb_dot_variant;
 
 typedef struct {

@@ -41,14 +41,19 @@ def test_dot_matches_oracle(B, M, N, K, transposed, dtype, variant):
 @pytest.mark.parametrize("transposed", [False, True])
 @pytest.mark.parametrize("B,M,N,K", [(1, 128, 256, 192), (4, 200, 72, 264), (2, 65, 136, 40), (1, 300, 520, 1024)])
 def test_dot_f32_on_tensor_cores(B, M, N, K, transposed):
-    """float32 operands as three bf16 planes each, six plane products in one f32 accumulator."""
+    """float32 operands as bf16 planes in one f32 accumulator: two planes each and three plane products by default
+    (inside the 1e-4 bar with a margin), three planes and six products as the exact variant."""
     lhs = make(11, (B, M, K), "f32")
     rhs = make(12, (B, N, K) if transposed else (B, K, N), "f32")
     want = oracle_dot(lhs, rhs, orc.F32, transposed).astype(np.float64)
     got, plan = ops.dot_normalised(lhs, rhs, in_dtype=dv.F32, rhs_transposed=transposed, variant=dv.DOT_TCGEN05,
                                    return_plan=True)
-    assert plan.kernel_name.startswith("gemm_tcgen05_Float32_Float32")
-    assert max_abs_normalised(got.astype(np.float64), want) < 2e-6
+    assert plan.kernel_name.startswith("gemm_tcgen05_Float32_Float32") and not plan.kernel_name.endswith("_6pass")
+    assert max_abs_normalised(got.astype(np.float64), want) < 2e-5
+    got6, plan6 = ops.dot_normalised(lhs, rhs, in_dtype=dv.F32, rhs_transposed=transposed, variant=dv.DOT_TCGEN05_EXACT,
+                                     return_plan=True)
+    assert plan6.kernel_name.endswith("_6pass")
+    assert max_abs_normalised(got6.astype(np.float64), want) < 2e-6
     # non-finite inputs propagate as in IEEE arithmetic
     lhs[0, 3, 5] = np.inf
     got = ops.dot_normalised(lhs, rhs, in_dtype=dv.F32, rhs_transposed=transposed, variant=dv.DOT_TCGEN05)
@@ -102,6 +107,26 @@ def test_config2_batched(dtype):
     got = ops.dot_normalised(lhs, rhs, in_dtype=code)
     want = as_f64(oracle_dot(lhs, rhs, code, False), code)
     assert max_abs_normalised(as_f64(got, code), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("B,M,N,K,dtype", [
+    (10, 512, 1024, 192, "bf16"),     # 160 tiles on 148 persistent CTAs: a second, short round
+    (10, 512, 1000, 192, "f16"),      # the same with a ragged last column tile
+    (5, 512, 2048, 64, "f32"),        # float32 planes: three passes through the ring per tile
+    (40, 512, 512, 64, "bf16"),       # one k-block per tile: the ring never fills
+    (3, 200, 520, 128, "bf16"),       # ragged tiles, fewer tiles than CTAs
+])
+def test_dot_tile_schedules(B, M, N, K, dtype, transposed):
+    """Shapes that stress the persistent schedule of the tensor-core kernel: more tiles than CTAs by a few, ragged
+    edges, very short K, several passes per tile."""
+    code = DT[dtype]
+    lhs = make(21, (B, M, K), dtype, K ** -0.5)
+    rhs = make(22, (B, N, K) if transposed else (B, K, N), dtype, 1.0)
+    got, plan = ops.dot_normalised(lhs, rhs, in_dtype=code, rhs_transposed=transposed, variant=dv.DOT_TCGEN05, return_plan=True)
+    assert plan.kernel_name.startswith("gemm_tcgen05_")
+    want = as_f64(oracle_dot(lhs, rhs, code, transposed), code)
+    assert max_abs_normalised(as_f64(got, code), want) < (2e-5 if dtype == "f32" else TOL[dtype])
 
 
 # ---------------------------------------------------------------- FusedDense (DotGeneral + bias + activation)
