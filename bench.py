@@ -37,9 +37,9 @@ K_DIM, N_DIM, GROUP = 4096, 14336, 128
 LAYERS = 8
 METRIC = "int8 quantized-dense GB/s & TFLOP/s vs roofline (1/2/4/8 B200) vs gobackend AVX"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch (8 layers) from the committed ncu capture
-# profiles/qdense_decode_tc_group_config3_M16.md; None where no capture of that batch size exists.
-NCU_TRAFFIC_BYTES = {16: 491_900_000}
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch (8 layers) from the ncu capture summarised under
+# profiles/ (qdense_decode_tc_group_config3_M16); None where no capture of that batch size exists.
+NCU_TRAFFIC_BYTES = {16: 480_726_016}
 
 
 def algorithmic_bytes(M: int, n_cols: int) -> int:
