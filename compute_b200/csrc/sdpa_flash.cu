@@ -11,7 +11,8 @@
 //   warp 9      MMA issuer:  S_t = Q_t K^T (tcgen05.mma, smem x smem -> TMEM) and
 //               O_t += P_t V (P_t read from TMEM, V from smem as the MN-major operand)
 //   warps 0-3 / 4-7  softmax of tile 0 / tile 1: tcgen05.ld of S, scale, causal mask,
-//               running max and sum, exp2, P written back over S as packed 16-bit
+//               running max and sum, exp2, P written back over S as packed 16-bit, announced to the MMA
+//               warp in chunks of 32 keys so that P.V starts while the later chunks are still computed
 // The two tiles alternate on the tensor core, so one tile's softmax overlaps the other's
 // matrix products.  O stays in TMEM and is rescaled only when a row maximum grows by more
 // than 2^8 (the stale maximum is used consistently for P and the row sum, so the result is
@@ -53,6 +54,13 @@ __device__ __forceinline__ void fa_fail(const FaParams& p, unsigned* s_failed, u
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// The same, kept in program order against the tensor-memory stores and barrier arrivals around it (the compiler may
+// otherwise hoist all of a block's exponentials above the first store, which would announce every chunk at the end).
+__device__ __forceinline__ float fast_exp2_ordered(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 // Blackwell's packed-pair f32 arithmetic and three-input max/min: the softmax warps are bound by
@@ -123,8 +131,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
   uint64_t* s_full = bars + 9;        // [2] per tile: scores ready
-  uint64_t* p_full = bars + 11;       // [2] per tile: probabilities written
-  uint64_t* o_done = bars + 13;       // [2] per tile: P.V of a block finished
+  uint64_t* o_done = bars + 11;       // [2] per tile: P.V of a block finished
+  uint64_t* p_chunk = bars + 13;      // [2][4] per tile and 32-key chunk of a block: probabilities written
   __shared__ uint32_t s_tmem;
   __shared__ unsigned s_failed;
 
@@ -168,7 +176,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int s = 0; s < 2; s++) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4); mbar_init(&o_done[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&o_done[s], 1);
+      for (int c = 0; c < 4; c++) mbar_init(&p_chunk[s * 4 + c], 4);
     }
     s_failed = 0;
     fence_barrier_init();
@@ -217,14 +226,16 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         umma_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int t, int s, bool accumulate) {   // O_t (+)= P_t V_s
+      // O_t (+)= P_t V_s, the 32 keys of chunk c: issued as soon as the softmax warps have written that chunk, so the
+      // tensor core works on the first chunks while the last ones are still being exponentiated
+      auto issue_pv_chunk = [&](int t, int s, int c, bool accumulate) {
         const uint32_t d = tmem_base + (uint32_t)(256 + t * 128);
         const uint32_t a = tmem_base + (uint32_t)(t * 128);
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; kk++)
+        for (int kk = 2 * c; kk < 2 * c + 2; kk++)
           umma_f16_ts(d, a + (uint32_t)(kk * 8), smem_desc_sw128(v_addr + s * FA_TILE_BYTES + kk * 16 * 128, FA_HALF_BYTES, 1024),
                       idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
-        umma_commit(&o_done[t]);
+        if (c == 3) umma_commit(&o_done[t]);
       };
       if (ok) {
         // block 0 scores
@@ -241,12 +252,15 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; t++) {
           if (j < nb[t]) {
-            if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { fa_fail(p, &s_failed, 5, (unsigned)(j * 2 + t)); ok = false; break; }
-            if (t == 0 || j >= nb[0]) {
-              if (!mbar_wait(&v_full[s], (uint32_t)((j / 2) & 1))) { fa_fail(p, &s_failed, 6, (unsigned)j); ok = false; break; }
+            for (int c = 0; c < 4 && ok; c++) {
+              if (!mbar_wait(&p_chunk[t * 4 + c], (uint32_t)(j & 1))) { fa_fail(p, &s_failed, 5, (unsigned)(j * 2 + t)); ok = false; break; }
+              if (c == 0 && (t == 0 || j >= nb[0])) {
+                if (!mbar_wait(&v_full[s], (uint32_t)((j / 2) & 1))) { fa_fail(p, &s_failed, 6, (unsigned)j); ok = false; break; }
+              }
+              tc_fence_after();
+              issue_pv_chunk(t, s, c, j > 0);
             }
-            tc_fence_after();
-            issue_pv(t, s, j > 0);
+            if (!ok) break;
           }
           if (j + 1 < nb[t]) {
             if (!k_next_ready) {
@@ -338,17 +352,25 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_st_wait();
       }
       // probabilities, row sum, P over S as packed 16-bit pairs
+      // A chunk of 32 keys is announced one chunk late: its store has had the arithmetic of the next chunk to complete,
+      // so the wait for it costs nothing, and the P.V products of the early chunks overlap the rest of this loop.
       float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; c++) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), p.scale_log2, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, -m_used));
-          l0 += p0;
-          l1 += p1;
+          float a0, a1;
+          fma2(a0, a1, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]), p.scale_log2, -m_used);
+          const float p0 = fast_exp2_ordered(a0), p1 = fast_exp2_ordered(a1);
+          add2(l0, l1, p0, p1);
           pk[i >> 1] = pack16x2_t<OT>(p0, p1);      // P has the dtype of the inputs, which is the output's
+        }
+        if (c > 0) {
+          tmem_st_wait();                            // the store of chunk c - 1
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_chunk[t * 4 + c - 1]);
         }
         tmem_st16(s_addr + (uint32_t)(c * 16), pk);
       }
@@ -356,7 +378,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
+      if (lane == 0) mbar_arrive(&p_chunk[t * 4 + 3]);
     }
     // epilogue: O / l
     if (!failed && nb[t] > 0) {
