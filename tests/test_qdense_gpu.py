@@ -547,6 +547,70 @@ def test_decode_group_full_size_step(L, M, blocks):
         assert np.array_equal(outs[layer].download((M, N), np.uint16), first[layer])
 
 
+@pytest.mark.parametrize("seed", list(range(24)))
+def test_decode_group_random_shapes(seed):
+    """A seeded sweep over what the grouped launch has to get right together: 1..16 members of unequal, ragged widths (so the
+    tile count lands on either side of the whole-tile / split-schedule thresholds), K from one to 24 units (stage and
+    accumulator rings wrap many times or never), every batch size (16-, 32- and 48-column MMAs; two or three digit
+    planes), shared and private activations, bias and activation per member; each member against the oracle, and the
+    launch repeated back to back bit for bit."""
+    rng = np.random.default_rng(9000 + seed)
+    x_dtype = "bf16" if seed % 3 else "f32"
+    M = int(rng.integers(1, 17))
+    K = 128 * int(rng.choice([1, 2, 3, 5, 8, 24]))
+    n_members = int(rng.choice([1, 2, 3, 5, 8, 16]))
+    widths = [int(rng.choice([16, 48, 128, 144, 528, 1792, 3008])) for _ in range(n_members)]
+    n_x = int(rng.integers(1, min(3, n_members) + 1))
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    esize, carrier = (2, np.uint16) if x_dtype == "bf16" else (4, np.float32)
+    xs = [rng.standard_normal((M, K), dtype=np.float32) * np.float32(10.0 ** rng.integers(-3, 1)) for _ in range(n_x)]
+    if x_dtype == "bf16":
+        xs = [orc.bf16_to_f32(orc.bf16_from_f32(x)) for x in xs]
+    up = (lambda a: orc.bf16_from_f32(a)) if x_dtype == "bf16" else (lambda a: a)
+    # Tanh is left to the other tests: here pre-activations reach tens, where its output saturates at 1 while the float32
+    # rounding noise of the reference's own k-ascending sum (about 1e-4 absolute at that size) stays, so a bar normalised
+    # by the largest output would measure the oracle, not the kernel.
+    acts = [v for k_, v in ACT.items() if k_ != "tanh"]
+    members = []
+    for N in widths:
+        members.append({"N": N, "xi": int(rng.integers(0, n_x)), "act": acts[int(rng.integers(0, len(acts)))],
+                        "w": rng.integers(-127, 128, size=(K, N), dtype=np.int8),
+                        "s": rng.uniform(0.001, 0.02, size=(K // 128, N)).astype(np.float32),
+                        "b": (rng.standard_normal(N) * 0.1).astype(np.float32) if rng.integers(0, 2) else None})
+    plan = dv.Plan.qdense_group(M, K, [(m["N"], m["b"] is not None, m["act"]) for m in members], code, dv.I8, dv.SCALE_KGROUP, 128)
+    st = dv.Stream(0)
+    xd = [dv.DeviceMem.from_numpy(up(x)) for x in xs]
+    ins, outs, keep = [], [], []
+    for m in members:
+        wd, sd = dv.DeviceMem.from_numpy(m["w"]), dv.DeviceMem.from_numpy(m["s"])
+        keep += [wd, sd]
+        ins += [xd[m["xi"]].ptr, wd.ptr, sd.ptr]
+        if m["b"] is not None:
+            keep.append(dv.DeviceMem.from_numpy(m["b"]))
+            ins.append(keep[-1].ptr)
+        outs.append(dv.DeviceMem(M * m["N"] * esize))
+        outs[-1].zero()
+    ws = plan.new_workspace()
+    bound = plan.bind(ins, [o.ptr for o in outs], ws.ptr)
+    bound.launch(st)
+    st.sync()
+    plan.check_status(ws.ptr)
+    first = [o.download((M, m["N"]), carrier) for o, m in zip(outs, members)]
+    for m, got in zip(members, first):
+        want = oracle_compact(xs[m["xi"]], m["w"], m["s"], m["b"], "kgroup", 128, m["act"])
+        gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+        assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else F32_TOL), (plan.kernel_name, plan.blocks, m["N"])
+    for o in outs:
+        o.zero()
+    dv.BoundSequence([bound, bound, bound]).launch(st)
+    st.sync()
+    plan.check_status(ws.ptr)
+    for o, m, f in zip(outs, members, first):
+        assert np.array_equal(o.download((M, m["N"]), carrier), f), (plan.kernel_name, plan.blocks, m["N"])
+    for d in xd + keep + outs + [ws]:
+        d.free()
+
+
 def test_bound_launch_of_other_plans():
     """cb_plan_bind works for every plan kind; plans without prepared state go through their ordinary launch."""
     x, w, s, b = qdense_inputs(3, 40, 256, 272, scale_layout="channel")
