@@ -113,6 +113,7 @@ _GRAPH_SIGNATURES = {
     "cbg_exec_output_info": ([C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int64)], C.c_int),
     "cbg_exec_kernel_names": ([C.c_void_p, C.c_char_p, C.c_size_t], C.c_int),
     "cbg_exec_last_trace": ([C.c_void_p, C.c_char_p, C.c_size_t], C.c_int),
+    "cbg_exec_graph_replays": ([C.c_void_p], C.c_int),
     "cbg_exec_execute": ([C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_uint8), C.c_int, C.POINTER(C.c_void_p), C.c_int], C.c_int),
     "cbg_exec_finalize": ([C.c_void_p], C.c_int),
 }
@@ -586,6 +587,10 @@ class Executable:
         buf = C.create_string_buffer(4096)
         check(_g().cbg_exec_kernel_names(self.handle, buf, 4096))
         return [s for s in buf.value.decode().split("\n") if s]
+
+    def GraphReplays(self) -> int:
+        """How many Execute calls so far were replays of a captured CUDA graph."""
+        return int(_g().cbg_exec_graph_replays(self.handle))
 
     def LastTrace(self) -> List[dict]:
         """The per-launch device times of the latest Execute when the backend was created with the

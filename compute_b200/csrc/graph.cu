@@ -123,6 +123,7 @@ struct cbg_backend {
   PinnedPool pinned;
   bool fallback_only = false;
   bool trace = false;                 // option "trace" or CUDABACKEND_TRACE=1: per-launch device times of every Execute
+  bool no_graphs = false;             // option "no_graphs": never replay an Execute as a CUDA graph
   std::atomic<bool> finalized{false};
   std::string name = "cuda", description;
   std::vector<std::unique_ptr<DevicePool>> pools;
@@ -208,6 +209,22 @@ struct cbg_exec {
   std::map<int, std::vector<void*>> const_dev;                       // device -> per-node constant copy
   std::map<int, std::vector<std::vector<void*>>> idle_ws;            // device -> sets of prepared workspaces
   std::string last_trace;                                            // the trace of the latest traced Execute (under mu)
+  // Replay as CUDA graphs (one device, no collectives): an Execute whose input buffers are the ones of an earlier call is
+  // launched as one instantiated graph instead of node by node.  An instance owns the memory of every intermediate value
+  // and its workspaces, so its kernel parameters never change; results are copied out into fresh buffers.
+  struct GraphInstance {
+    int dev = 0;
+    std::vector<void*> key;                    // the input pointers it was captured with
+    int seen = 0;                              // calls with this key so far; captured at the second
+    cudaGraphExec_t exec = nullptr;
+    std::vector<void*> mem, ws;                // per node: the memory the graph reads and writes, and its workspaces
+    std::vector<void*> owned_mem;              // the allocations behind mem (parameters and constants are not the instance's)
+    bool busy = false;                         // one replay at a time (the instance's memory is shared state)
+    int launches = 0;
+  };
+  std::vector<std::unique_ptr<GraphInstance>> graphs;                // under mu
+  bool graphs_off = false;                                           // set when a capture failed: stay on the plain path
+  int graph_replays = 0;
   bool finalized = false;
 };
 
@@ -341,6 +358,7 @@ int cbg_backend_new(const char* config, cbg_backend** backend) {
     if (item.empty()) continue;
     if (item == "fallback_only") b->fallback_only = true;
     else if (item == "trace") b->trace = true;
+    else if (item == "no_graphs") b->no_graphs = true;
     else if (item.rfind("devices=", 0) == 0) { /* accepted; device visibility is the process's */ }
     else return fail(CB_ERR_INVALID_ARG, "unknown configuration option \"%s\" for the cuda backend", item.c_str());
   }
@@ -1704,6 +1722,12 @@ int cbg_exec_kernel_names(const cbg_exec* e, char* buf, size_t n) {
   return CB_OK;
 }
 
+int cbg_exec_graph_replays(cbg_exec* e) {
+  if (!e) return 0;
+  std::lock_guard<std::mutex> l(e->mu);
+  return e->graph_replays;
+}
+
 int cbg_exec_last_trace(cbg_exec* e, char* buf, size_t n) {
   cb::clear_error();
   if (!e || !buf || n == 0) return fail(CB_ERR_INVALID_ARG, "NULL argument");
@@ -1871,15 +1895,19 @@ int launch_node(cbg_exec* e, Replica& r, size_t i) {
     std::vector<const void*> in;
     std::vector<void*> out;
     for (int m : members) {
-      CB_TRY(r.pool->get(r.dev, f->nodes[m]->shape.bytes(), &r.mem[m]));
-      r.owned[m] = 1;
+      if (!r.mem[m]) {                            // (a graph instance brings its own memory)
+        CB_TRY(r.pool->get(r.dev, f->nodes[m]->shape.bytes(), &r.mem[m]));
+        r.owned[m] = 1;
+      }
       for (const cbg_value* v : f->nodes[m]->inputs) in.push_back(operand_ptr(r, v));
       out.push_back(r.mem[m]);
     }
     return cb_launch(r.dp->plans[i], in.data(), (int)in.size(), out.data(), (int)out.size(), r.ws[i], r.stream);
   }
-  CB_TRY(r.pool->get(r.dev, n->shape.bytes(), &r.mem[i]));
-  r.owned[i] = 1;
+  if (!r.mem[i]) {
+    CB_TRY(r.pool->get(r.dev, n->shape.bytes(), &r.mem[i]));
+    r.owned[i] = 1;
+  }
   const void* in[8];
   for (size_t k = 0; k < n->inputs.size(); k++) in[k] = operand_ptr(r, n->inputs[k]);
   void* out[1] = {r.mem[i]};
@@ -1910,6 +1938,101 @@ int collect_outputs(cbg_exec* e, Replica& r) {
     }
     r.outs.push_back(buf.release());
   }
+  return CB_OK;
+}
+
+
+// ---------------------------------------------------------------- replay as a CUDA graph
+bool graph_eligible(cbg_exec* e, const uint8_t* donate, int n_inputs) {
+  if (e->replicas != 1 || e->be->trace || e->be->no_graphs || e->graphs_off) return false;
+  if (donate) for (int i = 0; i < n_inputs; i++) if (donate[i]) return false;      // donation changes who owns the buffers
+  cbg_function* f = e->fn.get();
+  for (size_t i = 0; i < f->nodes.size(); i++) {
+    if (!e->live[i]) continue;
+    const NodeKind k = f->nodes[i]->kind;
+    if (k == N_ALLREDUCE || k == N_ALLGATHER || k == N_EMBEDDING) return false;     // (the lookup reports through status words)
+  }
+  return true;
+}
+
+void graph_instance_free(cbg_exec::GraphInstance* g) {
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  for (void* p : g->owned_mem) if (p) cb_free(g->dev, p);
+  for (void* p : g->ws) if (p) cb_free(g->dev, p);
+  g->exec = nullptr; g->owned_mem.clear(); g->ws.clear(); g->mem.clear();
+}
+
+// Captures one pass over the nodes into a graph whose every buffer belongs to the instance.  On any failure the
+// executable stays on the plain path for good (graphs_off) and the caller carries on there.
+int graph_build(cbg_exec* e, cbg_exec::GraphInstance* g, cbg_buffer* const* inputs) {
+  cbg_function* f = e->fn.get();
+  const size_t nn = f->nodes.size();
+  Replica r;
+  r.dev = g->dev;
+  r.inputs = inputs;
+  CB_TRY(setup_replica(e, r));
+  g->ws = std::move(r.ws);                      // stay with the instance: the kernels' parameters point into them
+  r.ws = g->ws;
+  int st = CB_OK;
+  for (size_t i = 0; i < nn && st == CB_OK; i++) {
+    const cbg_value* n = f->nodes[i].get();
+    if (!e->live[i] || n->kind == N_PARAM || n->kind == N_CONST || n->kind == N_RESHAPE) continue;
+    void* p = nullptr;
+    st = cb_alloc(r.dev, std::max<size_t>(n->shape.bytes(), 16), &p);
+    if (st == CB_OK) { r.mem[i] = p; g->owned_mem.push_back(p); }
+  }
+  cudaGraph_t graph = nullptr;
+  bool capturing = false;
+  if (st == CB_OK) {
+    if (cudaStreamBeginCapture((cudaStream_t)r.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) capturing = true;
+    else st = fail(CB_ERR_CUDA, "graph capture could not begin");
+  }
+  for (size_t i = 0; i < nn && st == CB_OK; i++)
+    if (e->live[i]) st = launch_node(e, r, i);
+  if (capturing) {
+    const cudaError_t ce = cudaStreamEndCapture((cudaStream_t)r.stream, &graph);
+    if (ce != cudaSuccess || !graph) { if (st == CB_OK) st = fail(CB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce)); }
+  }
+  if (st == CB_OK && cudaGraphInstantiate(&g->exec, graph, 0) != cudaSuccess) st = fail(CB_ERR_CUDA, "graph instantiation failed");
+  if (graph) cudaGraphDestroy(graph);
+  cudaGetLastError();                           // a failed capture leaves a sticky-looking error behind; it is not one
+  e->be->put_stream(r.dev, r.stream);
+  if (st != CB_OK) { graph_instance_free(g); return st; }
+  g->mem = r.mem;
+  return CB_OK;
+}
+
+// One Execute through an instance: launch, copy the results into fresh buffers, sync.
+int graph_replay(cbg_exec* e, cbg_exec::GraphInstance* g, cbg_buffer* const* inputs, cbg_buffer** outputs) {
+  cbg_function* f = e->fn.get();
+  const size_t nn = f->nodes.size();
+  Replica r;
+  r.dev = g->dev;
+  r.pool = e->be->pools[r.dev].get();
+  r.inputs = inputs;
+  r.mem = g->mem;
+  r.owned.assign(nn, 0);
+  r.taken.assign(nn, 0);
+  {
+    std::lock_guard<std::mutex> l(e->mu);
+    r.dp = &e->dev_plans.find(r.dev)->second;
+  }
+  CB_TRY(e->be->get_stream(r.dev, &r.stream));
+  const auto t_start = std::chrono::steady_clock::now();
+  int st = cudaGraphLaunch(g->exec, (cudaStream_t)r.stream) == cudaSuccess ? CB_OK : fail(CB_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  if (st == CB_OK) st = collect_outputs(e, r);
+  const int sync_st = cb_stream_sync(r.dev, r.stream);
+  if (st == CB_OK) st = sync_st;
+  const double elapsed = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count();
+  if (st == CB_OK && elapsed > 1.5)
+    for (size_t i = 0; i < nn && st == CB_OK; i++)
+      if (r.dp->plans[i] && g->ws[i]) st = cb_plan_check_status(r.dp->plans[i], g->ws[i]);
+  e->be->put_stream(r.dev, r.stream);
+  if (st != CB_OK) {
+    for (cbg_buffer* b : r.outs) { r.pool->put(b->shape.bytes(), b->ptr); delete b; }
+    return st;
+  }
+  for (size_t o = 0; o < f->outputs.size(); o++) outputs[o] = r.outs[o];
   return CB_OK;
 }
 
@@ -1951,6 +2074,52 @@ int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const
       for (int b = a + 1; b < n_inputs; b++)
         if (donate[a] && donate[b] && inputs[a] == inputs[b])
           return fail(CB_ERR_INVALID_ARG, "Execute: the same buffer is donated as input #%d and input #%d", a, b);
+
+  // ---- a call whose input buffers are those of an earlier call replays that call's CUDA graph
+  if (graph_eligible(e, donate, n_inputs)) {
+    const int dev = reps[0].dev;
+    cbg_exec::GraphInstance* g = nullptr;
+    bool build = false;
+    {
+      std::lock_guard<std::mutex> l(e->mu);
+      for (auto& gi : e->graphs) {
+        if (gi->dev != dev || (int)gi->key.size() != n_inputs) continue;
+        bool same = true;
+        for (int i = 0; i < n_inputs && same; i++) same = gi->key[i] == inputs[i]->ptr;
+        if (same) { g = gi.get(); break; }
+      }
+      if (!g && e->graphs.size() < 8) {
+        e->graphs.push_back(std::make_unique<cbg_exec::GraphInstance>());
+        g = e->graphs.back().get();
+        g->dev = dev;
+        for (int i = 0; i < n_inputs; i++) g->key.push_back(inputs[i]->ptr);
+      }
+      if (g) {
+        g->seen++;
+        if (g->busy) g = nullptr;                         // another thread is inside this instance: plain path
+        else if (g->exec) g->busy = true;
+        else if (g->seen >= 2) { g->busy = true; build = true; }      // the first call ran plainly and configured every kernel
+        else g = nullptr;
+      }
+    }
+    if (g) {
+      int gst = CB_OK;
+      if (build) {
+        gst = graph_build(e, g, inputs);
+        if (gst != CB_OK) { cb::clear_error(); e->graphs_off = true; }
+      }
+      if (gst == CB_OK) {
+        gst = graph_replay(e, g, inputs, outputs);
+        std::lock_guard<std::mutex> l(e->mu);
+        g->busy = false;
+        g->launches++;
+        e->graph_replays++;
+        return gst;
+      }
+      std::lock_guard<std::mutex> l(e->mu);
+      g->busy = false;
+    }
+  }
 
   // ---- launch: every replica is set up, then the nodes are walked once, each node launched on every replica
   // before the next (all launches are asynchronous, so the devices run side by side; collectives see the operands
@@ -2057,6 +2226,7 @@ int cbg_exec_finalize(cbg_exec* e) {
   for (auto& kv : e->dev_plans) for (cb_plan* p : kv.second.plans) if (p) cb_plan_destroy(p);
   for (auto& kv : e->const_dev) for (void* p : kv.second) if (p) cb_free(kv.first, p);
   for (auto& kv : e->idle_ws) for (auto& set : kv.second) for (void* p : set) if (p) cb_free(kv.first, p);
+  for (auto& g : e->graphs) graph_instance_free(g.get());
   delete e;
   return CB_OK;
 }

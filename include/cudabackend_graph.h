@@ -194,6 +194,13 @@ int cbg_exec_input_sharding(const cbg_exec* e, int i, char* buf, size_t n);
      cudabackend trace: exec=<name> device=<d> node=<i> kernel=<plan name> out=<shape> us=<device time>
    The lines of the latest traced Execute can be read back here (empty when tracing is off). */
 int cbg_exec_last_trace(cbg_exec* e, char* buf, size_t n);
+/* Replay as CUDA graphs (no counterpart in the reference, whose executor walks its nodes on the host every time,
+   internal/gobackend/exec.go:176-233).  On one device and without collectives, the second Execute with the same input
+   buffers captures one pass over the nodes into a CUDA graph whose intermediate memory and workspaces belong to the
+   executable, and that and every later call with those buffers is one graph launch plus the copy of the results into
+   fresh buffers.  Calls with other buffers, donated inputs, a traced backend or the backend option "no_graphs" take the
+   node-by-node path; up to eight buffer sets are remembered.  Returns how many calls were replays so far. */
+int cbg_exec_graph_replays(cbg_exec* e);
 int cbg_exec_execute(cbg_exec* e, cbg_buffer* const* inputs, int n_inputs, const uint8_t* donate,
                      int default_device, cbg_buffer** outputs, int n_outputs);
 int cbg_exec_finalize(cbg_exec* e);                                        /* Executable.Finalize; frees the handle */

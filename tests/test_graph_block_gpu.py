@@ -346,3 +346,55 @@ def test_replica_groups_are_validated(backend):
     with pytest.raises(BackendError):
         f2b = backend.Builder("bad-spec").Main()
         f2b.Parameter("p", be.make_shape(dv.F32, 4, 4), be.ShardingSpec(mesh, (("nope",),)))
+
+
+def test_repeated_execute_replays_a_cuda_graph():
+    """The second and later calls with the same input buffers are one graph launch: same bits as the node-by-node call,
+    for a graph with a grouped decode launch, an RMS norm pattern, element-wise ops and attention in it."""
+    rng = np.random.default_rng(41)
+    H, N = 512, 768
+    x = orc.bf16_from_f32(rng.standard_normal((8, H), dtype=np.float32))
+    g = orc.bf16_from_f32(rng.uniform(0.5, 1.5, size=(H,)).astype(np.float32))
+    w1 = rng.integers(-127, 128, size=(H, N), dtype=np.int8)
+    w2 = rng.integers(-127, 128, size=(H, N), dtype=np.int8)
+    s1 = rng.uniform(0.001, 0.02, size=(1, N)).astype(np.float32)
+    s2 = rng.uniform(0.001, 0.02, size=(1, N)).astype(np.float32)
+    results = {}
+    for cfg in ("", "no_graphs"):
+        b = be.New(cfg)
+        builder = b.Builder("replay")
+        f = builder.Main()
+        px = f.Parameter("x", be.make_shape(dv.BF16, 8, H))
+        pg = f.Parameter("g", be.make_shape(dv.BF16, H))
+        pw1, pw2 = f.Parameter("w1", be.make_shape(dv.I8, H, N)), f.Parameter("w2", be.make_shape(dv.I8, H, N))
+        ps1, ps2 = f.Parameter("s1", be.make_shape(dv.F32, 1, N)), f.Parameter("s2", be.make_shape(dv.F32, 1, N))
+        xn = _rms_graph(f, px, pg, H, 1e-5, dv.BF16, True, False)
+        a = f.FusedQuantizedDense(xn, pw1, None, be.Quantization(be.QUANT_LINEAR, ps1, None, 0, H), dv.ACT_SILU)
+        c = f.FusedQuantizedDense(xn, pw2, None, be.Quantization(be.QUANT_LINEAR, ps2, None, 0, H), dv.ACT_NONE)
+        f.Return([f.Mul(a, c), xn])
+        exe = builder.Compile()
+        bufs = [b.BufferFromFlatData(0, arr, be.make_shape(d, *arr.shape)) for arr, d in
+                ((x, dv.BF16), (g, dv.BF16), (w1, dv.I8), (w2, dv.I8), (s1, dv.F32), (s2, dv.F32))]
+        outs = []
+        for _ in range(5):
+            res = exe.Execute(bufs, None, 0)
+            outs.append([r.ToNumpy() for r in res])
+            for r in res:
+                r.Finalize()
+        assert exe.GraphReplays() == (4 if cfg == "" else 0)
+        for o in outs[1:]:
+            assert all(np.array_equal(p, q) for p, q in zip(o, outs[0]))
+        results[cfg] = outs[0]
+        # other input buffers: the plain path again, then a second instance
+        x2 = orc.bf16_from_f32(rng.standard_normal((8, H), dtype=np.float32))
+        bx2 = b.BufferFromFlatData(0, x2, be.make_shape(dv.BF16, 8, H))
+        r1 = [r.ToNumpy() for r in exe.Execute([bx2] + bufs[1:], None, 0)]
+        r2 = [r.ToNumpy() for r in exe.Execute([bx2] + bufs[1:], None, 0)]
+        assert all(np.array_equal(p, q) for p, q in zip(r1, r2)) and not np.array_equal(r1[1], outs[0][1])
+        assert exe.GraphReplays() == (5 if cfg == "" else 0)
+        bx2.Finalize()
+        for t in bufs:
+            t.Finalize()
+        exe.Finalize()
+        b.Finalize()
+    assert all(np.array_equal(p, q) for p, q in zip(results[""], results["no_graphs"]))
