@@ -308,38 +308,51 @@ split_f32_planes_kernel(const float* __restrict__ src_a, uint16_t* __restrict__ 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t va = (n_a + 3) / 4, vb = (n_b + 3) / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < va + vb; vi += stride) {
-    const bool second = vi >= va;
-    const float* src = second ? src_b : src_a;
-    uint16_t* planes = second ? planes_b : planes_a;
-    const size_t n = second ? n_b : n_a;
-    const size_t i = (second ? vi - va : vi) * 4;
-    float v[4];
-    if (i + 4 <= n && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-      const float4 f = *reinterpret_cast<const float4*>(src + i);
-      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    } else {
+  constexpr int UNROLL = 4;            // vectors whose loads are in flight together
+  for (size_t v0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < va + vb; v0 += stride * UNROLL) {
+    float v[UNROLL][4];
+    const float* srcs[UNROLL];
+    uint16_t* dsts[UNROLL];
+    size_t ns[UNROLL], is[UNROLL];
 #pragma unroll
-      for (int e = 0; e < 4; e++) v[e] = (i + e < n) ? src[i + e] : 0.0f;
-    }
-    uint16_t pl[3][4];
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-      const uint16_t h = f32_to_bf16_bits(v[e]);
-      float rest = v[e] - bf16_bits_to_f32(h);
-      if (!isfinite(v[e])) rest = 0.0f;
-      const uint16_t m = f32_to_bf16_bits(rest);
-      rest -= bf16_bits_to_f32(m);
-      pl[0][e] = h; pl[1][e] = m; pl[2][e] = f32_to_bf16_bits(rest);
-    }
-#pragma unroll
-    for (int q = 0; q < 3; q++) {
-      if (q >= n_planes) break;
-      uint16_t* dst = planes + (size_t)q * n + i;
-      if (i + 4 <= n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)pl[q][0] | ((uint32_t)pl[q][1] << 16), (uint32_t)pl[q][2] | ((uint32_t)pl[q][3] << 16));
+    for (int u = 0; u < UNROLL; u++) {
+      const size_t vi = v0 + (size_t)u * stride;
+      const bool live = vi < va + vb, second = vi >= va;
+      srcs[u] = second ? src_b : src_a;
+      dsts[u] = second ? planes_b : planes_a;
+      ns[u] = live ? (second ? n_b : n_a) : 0;
+      is[u] = (second ? vi - va : vi) * 4;
+      if (is[u] + 4 <= ns[u] && (reinterpret_cast<uintptr_t>(srcs[u]) & 15) == 0) {
+        const float4 f = *reinterpret_cast<const float4*>(srcs[u] + is[u]);
+        v[u][0] = f.x; v[u][1] = f.y; v[u][2] = f.z; v[u][3] = f.w;
       } else {
-        for (int e = 0; e < 4; e++) if (i + e < n) dst[e] = pl[q][e];
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[u][e] = (is[u] + e < ns[u]) ? srcs[u][is[u] + e] : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+      const size_t n = ns[u], i = is[u];
+      if (i >= n) continue;
+      uint16_t pl[3][4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint16_t h = f32_to_bf16_bits(v[u][e]);
+        float rest = v[u][e] - bf16_bits_to_f32(h);
+        if (!isfinite(v[u][e])) rest = 0.0f;
+        const uint16_t m = f32_to_bf16_bits(rest);
+        rest -= bf16_bits_to_f32(m);
+        pl[0][e] = h; pl[1][e] = m; pl[2][e] = f32_to_bf16_bits(rest);
+      }
+#pragma unroll
+      for (int q = 0; q < 3; q++) {
+        if (q >= n_planes) break;
+        uint16_t* dst = dsts[u] + (size_t)q * n + i;
+        if (i + 4 <= n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)pl[q][0] | ((uint32_t)pl[q][1] << 16), (uint32_t)pl[q][2] | ((uint32_t)pl[q][3] << 16));
+        } else {
+          for (int e = 0; e < 4; e++) if (i + e < n) dst[e] = pl[q][e];
+        }
       }
     }
   }
@@ -349,7 +362,7 @@ int split_f32_planes(const float* src_a, uint16_t* planes_a, size_t n_a, const f
                      int n_planes, cudaStream_t s) {
   if (n_a + n_b == 0) return CB_OK;
   if (n_planes < 1 || n_planes > 3) return fail(CB_ERR_INVALID_ARG, "split_f32_planes: %d planes", n_planes);
-  const size_t want = ((n_a + n_b) / 4 + 255) / 256;
+  const size_t want = ((n_a + n_b) / 16 + 255) / 256;         // four vectors of four elements per thread and pass
   const int blocks = (int)std::min<size_t>(std::max<size_t>(want, 1), 148 * 16);
   split_f32_planes_kernel<<<blocks, 256, 0, s>>>(src_a, planes_a, n_a, src_b, planes_b, n_b, n_planes);
   CB_CUDA(cudaGetLastError());

@@ -116,19 +116,40 @@ __device__ __forceinline__ void gg_decode32(const uint8_t* chunk, int u, float (
 // Copies `len` bytes starting at g (anywhere) into the warp's stage with 16-byte loads from the boundary below g and
 // returns the staged address of g's first byte.  Vectors that would cross `end` (the end of the whole buffer) are read
 // byte by byte.  The caller's __syncwarp separates the copy from the reads.
+__device__ __forceinline__ uint4 gg_load16(const uint8_t* s, const uint8_t* end) {
+  if (s + 16 <= end) return __ldg(reinterpret_cast<const uint4*>(s));
+  uint32_t w[4] = {0, 0, 0, 0};
+  for (int b = 0; b < 16; b++) if (s + b < end) w[b >> 2] |= (uint32_t)s[b] << (8 * (b & 3));
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
 __device__ __forceinline__ const uint8_t* gg_stage(uint8_t* stage, const uint8_t* g, int len, const uint8_t* end, int lane) {
   const int lead = (int)(reinterpret_cast<uintptr_t>(g) & 15);
   const uint8_t* src = g - lead;
   const int nvec = (lead + len + 15) >> 4;
-  for (int v = lane; v < nvec; v += 32) {
-    const uint8_t* s = src + 16 * v;
-    if (s + 16 <= end) {
-      reinterpret_cast<uint4*>(stage)[v] = __ldg(reinterpret_cast<const uint4*>(s));
-    } else {
-      for (int b = 0; b < 16; b++) stage[16 * v + b] = s + b < end ? s[b] : (uint8_t)0;
-    }
-  }
+  for (int v = lane; v < nvec; v += 32) reinterpret_cast<uint4*>(stage)[v] = gg_load16(src + 16 * v, end);
   return stage + lead;
+}
+// The same in two halves, so that a row's bytes travel while the previous row is decoded: the loads into registers
+// (at most GG_PRE vectors per lane: 1103 bytes are 69 vectors), and later the stores into the stage.
+constexpr int GG_PRE = 3;
+struct GgPrefetch { uint4 v[GG_PRE]; int lead, nvec; };
+__device__ __forceinline__ void gg_prefetch(GgPrefetch& pf, const uint8_t* g, int len, const uint8_t* end, int lane) {
+  pf.lead = (int)(reinterpret_cast<uintptr_t>(g) & 15);
+  pf.nvec = g ? (pf.lead + len + 15) >> 4 : 0;
+  const uint8_t* src = g - pf.lead;
+#pragma unroll
+  for (int j = 0; j < GG_PRE; j++) {
+    const int v = lane + 32 * j;
+    if (v < pf.nvec) pf.v[j] = gg_load16(src + 16 * v, end);
+  }
+}
+__device__ __forceinline__ const uint8_t* gg_commit(uint8_t* stage, const GgPrefetch& pf, int lane) {
+#pragma unroll
+  for (int j = 0; j < GG_PRE; j++) {
+    const int v = lane + 32 * j;
+    if (v < pf.nvec) reinterpret_cast<uint4*>(stage)[v] = pf.v[j];
+  }
+  return stage + pf.lead;
 }
 
 template <typename XT> __device__ __forceinline__ float gg_x(const XT* p, int64_t i);
@@ -137,9 +158,9 @@ template <> __device__ __forceinline__ float gg_x<__nv_bfloat16>(const __nv_bflo
 
 // Dense kernel.  A CTA of 8 warps stages a [rows, 1024] slice of x in shared memory once (float32, every lane's
 // 32-value segment padded to 36 floats so that the lanes' 16-byte reads fall in different banks) and reuses it for 32
-// weight rows, four per warp; a warp stages the bytes of its row's 1024-value chunk with coalesced 16-byte loads and
-// every lane decodes one 32-value unit from there and multiplies it with the rows of x; a butterfly adds the lanes at
-// the end.  MR = rows of x per CTA pass (1, 4 or 16).  (Giving every lane an output column instead — x read as
+// weight rows, four per warp; a warp stages the bytes of its row's 1024-value chunk with coalesced 16-byte loads (requested
+// one row ahead, so that they travel while the previous row is decoded) and every lane decodes one 32-value unit from
+// there and multiplies it with the rows of x; a butterfly adds the lanes at the end.  MR = rows of x per CTA pass (1, 4 or 16).  (Giving every lane an output column instead — x read as
 // broadcasts, no final reduction — measured 1.3-1.7x slower: the decode, not the reduction, is what costs.)
 constexpr int GG_RPW = 4;                    // weight rows per warp
 constexpr int GG_XPITCH = 36;
@@ -152,7 +173,7 @@ qdense_ggml_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, cons
   __shared__ float s_lut[16];
   if (threadIdx.x < 16) s_lut[threadIdx.x] = c_iq4nl[threadIdx.x];
   float* xs = reinterpret_cast<float*>(gg_smem);                                   // [MR][32][GG_XPITCH]
-  uint8_t* wstage = gg_smem + (size_t)MR * 32 * GG_XPITCH * sizeof(float) + (threadIdx.x >> 5) * GG_WSTAGE;
+  uint8_t* wstage = gg_smem + (size_t)MR * 32 * GG_XPITCH * sizeof(float) + (threadIdx.x >> 5) * (2 * GG_WSTAGE);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t n0 = ((int64_t)blockIdx.x * GG_WARPS + warp) * GG_RPW;
   const int64_t m0 = (int64_t)blockIdx.y * MR;
@@ -165,7 +186,19 @@ qdense_ggml_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, cons
   for (int r = 0; r < GG_RPW; r++)
 #pragma unroll
     for (int i = 0; i < MR; i++) acc[r][i] = 0.0f;
+  // the bytes of (row r, chunk at kc), or nothing for a row past N or a chunk past K
+  auto chunk_ptr = [&](int r, int64_t kc) -> const uint8_t* {
+    return (n0 + r < N && kc < K) ? w + (n0 + r) * bytes_per_row + kc / VPB * BB : nullptr;
+  };
+  auto chunk_len = [&](int64_t kc) { return (int)min((int64_t)gg_chunk_bytes(GGML), bytes_per_row - kc / VPB * BB); };
 
+  // With few rows of x the accumulators leave room for the next row's bytes in registers; with 16 rows (64 accumulators)
+  // holding them costs more than the latency they hide (measured 266 against 210 us on 4096 x 14336), so there a row is
+  // staged when its turn comes.
+  constexpr bool PIPE = MR <= 4;
+  GgPrefetch pf;
+  pf.nvec = 0; pf.lead = 0;
+  if (PIPE) gg_prefetch(pf, chunk_ptr(0, 0), chunk_len(0), w_end, lane);
   for (int64_t kc = 0; kc < K; kc += GG_CHUNK) {
     __syncthreads();                       // the previous slice of x has been used by every warp (and the table is written)
     for (int idx = threadIdx.x; idx < MR * GG_CHUNK; idx += GG_WARPS * 32) {
@@ -174,15 +207,27 @@ qdense_ggml_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, cons
     }
     __syncthreads();
     const bool active = kc + 32 * lane < K;
-    const int len = (int)min((int64_t)gg_chunk_bytes(GGML), bytes_per_row - kc / VPB * BB);
 #pragma unroll
     for (int r = 0; r < GG_RPW; r++) {     // unrolled: the accumulators stay in registers
-      const int64_t n = n0 + r;
-      if (n >= N) continue;                // uniform across the warp
-      __syncwarp();                        // the previous row's bytes have been decoded
-      const uint8_t* chunk = gg_stage(wstage, w + n * bytes_per_row + kc / VPB * BB, len, w_end, lane);
-      __syncwarp();
-      if (active) {
+      // Two stage buffers alternate: the bytes of this row were requested one row ago and are written now, and the next
+      // row's (or the next chunk's first row's) are requested before this one is decoded.  A buffer is rewritten two rows
+      // later, after a __syncwarp that every lane reaches only when it has decoded this row.
+      bool have;                           // uniform across the warp
+      const uint8_t* chunk;
+      if (PIPE) {
+        have = pf.nvec > 0;
+        chunk = gg_commit(wstage + (r & 1) * GG_WSTAGE, pf, lane);
+        __syncwarp();
+        if (r + 1 < GG_RPW) gg_prefetch(pf, chunk_ptr(r + 1, kc), chunk_len(kc), w_end, lane);
+        else gg_prefetch(pf, chunk_ptr(0, kc + GG_CHUNK), kc + GG_CHUNK < K ? chunk_len(kc + GG_CHUNK) : 0, w_end, lane);
+      } else {
+        const uint8_t* g = chunk_ptr(r, kc);
+        have = g != nullptr;
+        __syncwarp();                      // the previous row's bytes have been decoded
+        chunk = have ? gg_stage(wstage, g, chunk_len(kc), w_end, lane) : wstage;
+        __syncwarp();
+      }
+      if (have && active) {
         float wv[32];
         gg_decode32<GGML>(chunk, lane, wv, s_lut);
 #pragma unroll
@@ -271,7 +316,7 @@ bool gg_supported(int t) {
 }
 
 int gg_mr(int64_t M) { return M <= 1 ? 1 : M <= 4 ? 4 : 16; }
-size_t gg_smem_bytes(int mr) { return (size_t)mr * 32 * GG_XPITCH * sizeof(float) + (size_t)GG_WARPS * GG_WSTAGE; }
+size_t gg_smem_bytes(int mr) { return (size_t)mr * 32 * GG_XPITCH * sizeof(float) + (size_t)GG_WARPS * 2 * GG_WSTAGE; }
 
 template <typename XT, int GGML, int MR>
 int gg_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out, cudaStream_t s) {
