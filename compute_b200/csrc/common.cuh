@@ -115,7 +115,10 @@ int fused_small_plan(cb_plan* p);
 int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int elementwise_plan(cb_plan* p);
 int qdense_ggml_plan(cb_plan* p);
-int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s);
+int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+bool qdense_ggml_mma_supports(const cb_qdense_desc& d);
+void qdense_ggml_mma_plan(cb_plan* p, const char* type_name);
+int qdense_ggml_mma_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int embedding_lookup_plan(cb_plan* p);
 int embedding_lookup_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 int embedding_lookup_check(const cb_plan* p, const void* ws);

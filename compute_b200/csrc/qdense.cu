@@ -784,10 +784,10 @@ static int launch_decode(const cb_plan* p, const void* const* in, void* const* o
 
 int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
+  if (d.scheme == CB_QUANT_GGML) return qdense_ggml_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_MMA) return launch_decode(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_PREFILL) return qdense_prefill_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_launch(p, in, out, ws, s);
-  if (d.scheme == CB_QUANT_GGML) return qdense_ggml_launch(p, in, out, s);
   const bool bf = d.x_dtype == CB_BF16, wu = d.w_dtype == CB_U8;
   (void)wu;
   const bool nf4 = d.scheme == CB_QUANT_NF4;

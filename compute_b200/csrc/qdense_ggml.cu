@@ -394,14 +394,20 @@ int qdense_ggml_plan(cb_plan* p) {
   p->threads = GG_WARPS * 32;
   p->dyn_smem = (int)gg_smem_bytes(mr);
   p->name = std::string("qdense_ggml_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + gg_name(d.ggml_type);
+  // decode shapes of the formats whose blocks feed the integer tensor cores directly (CB_QDENSE_GENERIC keeps this kernel)
+  if (qdense_ggml_mma_supports(d)) qdense_ggml_mma_plan(p, gg_name(d.ggml_type));
   return CB_OK;
 }
 
-int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s) {
+int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   if (d.M == 0 || d.N == 0) return CB_OK;
   if ((reinterpret_cast<uintptr_t>(in[0]) & 15) != 0 || (reinterpret_cast<uintptr_t>(in[1]) & 15) != 0)
     return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): x and weights must be 16-byte aligned");
+  if (qdense_ggml_mma_supports(d)) {
+    if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): the plan needs its workspace (digit planes of x)");
+    return qdense_ggml_mma_launch(p, in, out, ws, s);
+  }
   return d.x_dtype == CB_BF16 ? gg_launch_t<__nv_bfloat16>(d, in, out, s) : gg_launch_t<float>(d, in, out, s);
 }
 

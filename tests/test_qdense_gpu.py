@@ -131,7 +131,8 @@ def test_ggml_block_formats(M, K, N, x_dtype, ggml):
     want = orc.qdense_ggml(xw, wq, b, gt, orc.ACT_SILU)
     plan = dv.Plan.qdense(M, K, N, code, dv.U8, has_bias=True, activation=dv.ACT_SILU, scheme=dv.QUANT_GGML,
                           ggml_type=dv.GGML_Q8_0 if ggml == "q8_0" else dv.GGML_Q4_0)
-    assert plan.kernel_name == f"qdense_ggml_{x_dtype}_{ggml}"
+    # decode shapes with K in whole 256-value steps run on the integer tensor cores, the rest on the CUDA-core kernel
+    assert plan.kernel_name == f"qdense_ggml_{'mma_' if M <= 16 and K % 256 == 0 else ''}{x_dtype}_{ggml}"
     got = ops._run(plan, [xin, wq, b], (M, N), dv.NP_CARRIER[code])
     gotf = orc.to_f32(got, orc.BF16) if x_dtype == "bf16" else got
     assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else F32_TOL)
@@ -158,9 +159,50 @@ def test_ggml_every_format_random_blocks(ggml, M, K, N, bias, act):
     b = rng.standard_normal(N).astype(np.float32) if bias else None
     want = orc.qdense_ggml(x, wq, b, gt, ACT[act])
     plan = dv.Plan.qdense(M, K, N, dv.F32, dv.U8, has_bias=bias, activation=ACT[act], scheme=dv.QUANT_GGML, ggml_type=gt)
-    assert plan.kernel_name == f"qdense_ggml_f32_{ggml}"
+    on_tensor_cores = M <= 16 and K % 256 == 0 and ggml != "q6_k"
+    assert plan.kernel_name == f"qdense_ggml_{'mma_' if on_tensor_cores else ''}f32_{ggml}"
     got = ops._run(plan, [x, wq] + ([b] if bias else []), (M, N), np.float32)
     assert max_abs_normalised(got, want) < F32_TOL
+    # the CUDA-core kernel on the same case
+    plan_cc = dv.Plan.qdense(M, K, N, dv.F32, dv.U8, has_bias=bias, activation=ACT[act], scheme=dv.QUANT_GGML, ggml_type=gt,
+                             variant=dv.QDENSE_GENERIC)
+    assert plan_cc.kernel_name == f"qdense_ggml_f32_{ggml}"
+    got_cc = ops._run(plan_cc, [x, wq] + ([b] if bias else []), (M, N), np.float32)
+    assert max_abs_normalised(got_cc, want) < F32_TOL
+
+
+@pytest.mark.parametrize("ggml", ["q4_0", "q8_0", "iq4_nl", "q4_k"])
+@pytest.mark.parametrize("M,K,N,x_dtype", [(1, 4096, 14336, "f32"), (2, 256, 64, "f32"), (5, 768, 130, "bf16"), (16, 2048, 1000, "f32"),
+                                           (7, 512, 63, "f32")])
+def test_ggml_on_tensor_cores(ggml, M, K, N, x_dtype):
+    """The integer-tensor-core kernel: one, two and six 8-column tiles of (digit plane, row) columns, both halves of K
+    with one step or many, ragged N (rows past the end are computed and dropped), a row of x that is all zeros and one
+    that is a thousand times larger than the others (its own unit), inf in x -> that row comes back NaN."""
+    gt = GGML_TYPES[ggml]
+    rng = np.random.default_rng(77 + gt + M)
+    wq = orc.ggml_random_rows(rng, N, K, gt)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if M >= 5:
+        x[1] = 0.0
+        x[2] *= 1000.0
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    xw = orc.bf16_to_f32(xin) if x_dtype == "bf16" else x
+    want = orc.qdense_ggml(xw, wq, b, gt, orc.ACT_GELU)
+    plan = dv.Plan.qdense(M, K, N, code, dv.U8, has_bias=True, activation=dv.ACT_GELU, scheme=dv.QUANT_GGML, ggml_type=gt)
+    assert plan.kernel_name == f"qdense_ggml_mma_{x_dtype}_{ggml}" and plan.workspace_bytes > 0
+    got = ops._run(plan, [xin, wq, b], (M, N), dv.NP_CARRIER[code])
+    gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+    # every row against its own largest value: the huge row must not hide the others
+    for m in range(M):
+        assert max_abs_normalised(gotf[m], want[m]) < (BF16_TOL if x_dtype == "bf16" else F32_TOL), m
+    if M >= 5 and x_dtype == "f32":
+        x[3, 17] = np.inf
+        got = ops._run(plan, [x, wq, b], (M, N), np.float32)
+        assert np.isnan(got[3]).all() and np.isfinite(got[0]).all()
+    with pytest.raises(BackendError):            # the digit planes live in the plan's workspace
+        plan.launch([0x1000, 0x2000, 0x3000], [0x4000], None)
 
 
 @pytest.mark.parametrize("ggml", list(GGML_TYPES))
@@ -175,7 +217,7 @@ def test_ggml_dequantised_values_are_bit_exact(ggml):
         x = np.zeros((16, K), np.float32)
         cols = k0 + rng.choice(256, size=16, replace=False)
         x[np.arange(16), cols] = 1.0
-        plan = dv.Plan.qdense(16, K, N, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=gt)
+        plan = dv.Plan.qdense(16, K, N, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=gt, variant=dv.QDENSE_GENERIC)
         got = ops._run(plan, [x, wq], (16, N), np.float32)
         # every selected weight with the reference's bits (the sum adds +0 to it, so a -0 weight reads back as +0)
         assert np.array_equal(got, want[:, cols].T) and not np.isnan(got).any()
