@@ -9,8 +9,8 @@
 //   the row (20 bits below it: an error of at most 2^-21 of the row's maximum per element);
 // one MMA forms, for 16 weight rows and one 32-value block, the exact integer dot products with eight (digit plane, x
 // row) columns, and the block's own scale is applied to that integer in float32:
-//   Q8_0    d * sum(q x)                      Q4_0    d * (sum(n x) - 8 sum(x))       n = nibble
-//   IQ4_NL  d * sum(table[n] x)               Q4_K    (d sc) * sum(n x) - (dmin m) * sum(x)
+//   Q8_0    d * sum(q x)                      Q4_0    (d / 16) * sum(16 (n - 8) x)    n = nibble
+//   IQ4_NL  d * sum(table[n] x)               Q4_K    d * sum over the super-block of sc * sum(n x)  -  (dmin m) * sum(x)
 // sum(x) per block comes from the digit kernel.  The k index of the product is permuted (lane t of a quad owns the
 // values 8t..8t+7 of the block, for the weights and for the digits alike), so every operand fragment is eight
 // contiguous bytes.
@@ -24,6 +24,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstring>
 #include <string>
 
 namespace cb {
@@ -37,35 +38,37 @@ constexpr int GM_MAX_COLS = 48;             // 3 digit planes x 16 rows of x
 
 __host__ __device__ constexpr int gm_block_bytes(int t) { return t == CB_GGML_Q8_0 ? 34 : t == CB_GGML_Q4_K ? 144 : 18; }
 __host__ __device__ constexpr int gm_seg(int t) { return t == CB_GGML_Q4_K ? 144 : 8 * gm_block_bytes(t); }   // bytes of 256 values
-__host__ __device__ constexpr int gm_pitch(int t) { return gm_seg(t) + 16; }
+// Row pitch in the ring.  18-byte blocks: 176 bytes = 44 words, so the eight rows of a fragment read start in banks 0, 12,
+// 24, 4, 16, 28, 8, 20.  Q4_K: 160 bytes = 40 words, the four rows of a half-warp's 64-bit reads start 8 banks apart.  Q8_0:
+// 288 bytes (rows g and g + 4 share banks; 304 would not, but two CTAs of three stages would no longer fit one SM).
+__host__ __device__ constexpr int gm_pitch(int t) { return t == CB_GGML_Q4_K ? 160 : t == CB_GGML_Q8_0 ? 288 : 176; }
 __host__ __device__ constexpr int gm_stage_bytes(int t) { return 16 * gm_pitch(t); }
+__host__ __device__ constexpr int gm_tiles(int M) { return (3 * M + 7) / 8; }             // 8-column tiles of (plane, row) columns
 
 __device__ __forceinline__ void gm_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-// Eight bytes starting at shared address `a` (a multiple of 2): three aligned words and two funnel shifts.
-__device__ __forceinline__ void gm_lds8(uint32_t a, uint32_t& w0, uint32_t& w1) {
-  const uint32_t base = a & ~3u, sh = (a & 2u) * 8u;
-  uint32_t x0, x1, x2;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x0) : "r"(base));
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x1) : "r"(base + 4));
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x2) : "r"(base + 8));
-  w0 = __funnelshift_r(x0, x1, sh);
-  w1 = __funnelshift_r(x1, x2, sh);
+// Eight bytes at p + off.  p is 8-byte aligned and off is a constant once the caller's loop is unrolled, so the choice
+// below is made by the compiler: one 64-bit read, two 32-bit reads, or (off = 2 mod 4) three words and two funnel shifts.
+__device__ __forceinline__ void gm_ld8(const unsigned char* p, int off, uint32_t& w0, uint32_t& w1) {
+  if (off % 8 == 0) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p + off);
+    w0 = v.x; w1 = v.y;
+  } else if (off % 4 == 0) {
+    w0 = *reinterpret_cast<const uint32_t*>(p + off); w1 = *reinterpret_cast<const uint32_t*>(p + off + 4);
+  } else {
+    const uint32_t x0 = *reinterpret_cast<const uint32_t*>(p + off - 2), x1 = *reinterpret_cast<const uint32_t*>(p + off + 2),
+                   x2 = *reinterpret_cast<const uint32_t*>(p + off + 6);
+    w0 = __funnelshift_r(x0, x1, 16); w1 = __funnelshift_r(x1, x2, 16);
+  }
 }
-__device__ __forceinline__ float gm_lds_f16(uint32_t a) {
-  unsigned short h;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(a));
-  return __half2float(__ushort_as_half(h));
-}
-__device__ __forceinline__ uint32_t gm_lds_u8(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
+// int -> float for |c| < 2^22 with an integer add and a float add (the conversion instruction shares its issue queue
+// with the shared-memory reads, which is what this kernel waits on)
+__device__ __forceinline__ float gm_i2f(int c) { return __int_as_float(0x4B400000 + c) - 12582912.0f; }
+__device__ __forceinline__ float gm_f16(const unsigned char* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
 
 // compute.IQ4NLLookupTable (fused_ops.go:127-130) as int8, four entries per word
 __device__ __forceinline__ uint32_t gm_iq4nl(uint32_t nibbles) {      // four bytes holding 0..15 -> their table values
@@ -79,14 +82,24 @@ __device__ __forceinline__ uint32_t gm_iq4nl(uint32_t nibbles) {      // four by
 
 // ---- x -> digits, one block per row of x
 constexpr int GD_THREADS = 256;
-template <typename XT> __device__ __forceinline__ float gd_x(const XT* p, int64_t i);
-template <> __device__ __forceinline__ float gd_x<float>(const float* p, int64_t i) { return __ldg(p + i); }
-template <> __device__ __forceinline__ float gd_x<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+constexpr int GD_CACHE = 4;                 // a thread keeps its first 16 values in registers between the two passes
+template <typename XT> __device__ __forceinline__ float4 gd_x4(const XT* p, int64_t i);
+template <> __device__ __forceinline__ float4 gd_x4<float>(const float* p, int64_t i) { return __ldg(reinterpret_cast<const float4*>(p + i)); }
+template <> __device__ __forceinline__ float4 gd_x4<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p + i));
+  return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+}
 
-// digits [3][M][K] int8, dsum [3][M][K / 32] int32 (sum of a block's digits), units [M] float
+// digits [cols][K] int8 with column = plane * M + m; dsum [K / 32][cols] float = the sum of a block's digits (written
+// when the format has a per-block minimum); units [M] float.  `cols` is 3 M rounded up to whole 8-column tiles: the
+// columns past 3 M are never written and whatever they hold only reaches results that are dropped.
 template <typename XT>
 __global__ void __launch_bounds__(GD_THREADS)
-ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int8_t* __restrict__ digits, int* __restrict__ dsum, float* __restrict__ units) {
+ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int8_t* __restrict__ digits, float* __restrict__ dsum, float* __restrict__ units) {
+  // The product kernel may be scheduled now (it requests weights, then waits for this grid); this grid may itself
+  // have been scheduled while the kernel before it, which may produce x or still read the digits, was running.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ uint32_t s_mx[GD_THREADS / 32];
   __shared__ int s_bad;
   const int m = blockIdx.x;
@@ -95,10 +108,21 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int8_t* __res
   __syncthreads();
   uint32_t mx = 0;
   bool bad = false;
-  for (int64_t k = threadIdx.x; k < K; k += GD_THREADS) {
-    const uint32_t a = __float_as_uint(gd_x<XT>(xr, k)) & 0x7FFFFFFFu;
-    if (a >= 0x7F800000u) bad = true; else mx = max(mx, a);
+  float4 cache[GD_CACHE];
+  auto look = [&](const float4& v) {
+    const uint32_t a[4] = {__float_as_uint(v.x) & 0x7FFFFFFFu, __float_as_uint(v.y) & 0x7FFFFFFFu, __float_as_uint(v.z) & 0x7FFFFFFFu,
+                           __float_as_uint(v.w) & 0x7FFFFFFFu};
+#pragma unroll
+    for (int e = 0; e < 4; e++) { if (a[e] >= 0x7F800000u) bad = true; else mx = max(mx, a[e]); }
+  };
+#pragma unroll
+  for (int i = 0; i < GD_CACHE; i++) {
+    const int64_t k = ((int64_t)i * GD_THREADS + threadIdx.x) * 4;
+    cache[i] = k < K ? gd_x4<XT>(xr, k) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+#pragma unroll
+  for (int i = 0; i < GD_CACHE; i++) look(cache[i]);
+  for (int64_t k = ((int64_t)GD_CACHE * GD_THREADS + threadIdx.x) * 4; k < K; k += GD_THREADS * 4) look(gd_x4<XT>(xr, k));
   mx = __reduce_max_sync(0xFFFFFFFFu, mx);
   if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(&s_bad, 1);
   if ((threadIdx.x & 31) == 0) s_mx[threadIdx.x >> 5] = mx;
@@ -116,14 +140,14 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int8_t* __res
     if (s_bad) unit = __int_as_float(0x7FC00000);      // a row holding inf or NaN comes back NaN
     units[m] = unit;
   }
-  const int64_t U = K / 32;
   // a thread converts 4 consecutive values; the 8 threads of a 32-value block add their digit sums by shuffles
-  for (int64_t k = (int64_t)threadIdx.x * 4; k < K; k += GD_THREADS * 4) {
+  auto convert = [&](const float4& v4, int64_t k) {
+    const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
     uint32_t w0 = 0, w1 = 0, w2 = 0;
     int s0 = 0, s1 = 0, s2 = 0;
 #pragma unroll
     for (int e = 0; e < 4; e++) {
-      float v = gd_x<XT>(xr, k + e);
+      float v = vv[e];
       if ((__float_as_uint(v) & 0x7FFFFFFFu) >= 0x7F800000u) v = 0.0f;
       const int q = (int)(__float_as_uint(fmaf(v * p1, p2, 12582912.0f)) - 0x4B400000u);     // round to nearest, |q| <= 2^20
       const int a = ((q + 64) & 127) - 64;
@@ -136,135 +160,192 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int8_t* __res
     *reinterpret_cast<uint32_t*>(digits + ((int64_t)0 * M + m) * K + k) = w0;
     *reinterpret_cast<uint32_t*>(digits + ((int64_t)1 * M + m) * K + k) = w1;
     *reinterpret_cast<uint32_t*>(digits + ((int64_t)2 * M + m) * K + k) = w2;
+    if (dsum) {
 #pragma unroll
-    for (int d = 1; d < 8; d <<= 1) {
-      s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, d); s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, d); s2 += __shfl_xor_sync(0xFFFFFFFFu, s2, d);
+      for (int d = 1; d < 8; d <<= 1) {
+        s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, d); s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, d); s2 += __shfl_xor_sync(0xFFFFFFFFu, s2, d);
+      }
+      if ((threadIdx.x & 7) == 0) {
+        float* o = dsum + (k / 32) * cols;
+        o[0 * M + m] = (float)s0; o[1 * M + m] = (float)s1; o[2 * M + m] = (float)s2;
+      }
     }
-    if ((threadIdx.x & 7) == 0) {
-      const int64_t u = k / 32;
-      dsum[((int64_t)0 * M + m) * U + u] = s0; dsum[((int64_t)1 * M + m) * U + u] = s1; dsum[((int64_t)2 * M + m) * U + u] = s2;
-    }
+  };
+#pragma unroll
+  for (int i = 0; i < GD_CACHE; i++) {
+    const int64_t k = ((int64_t)i * GD_THREADS + threadIdx.x) * 4;
+    if (k < K) convert(cache[i], k);                      // K is a multiple of 256: whole warps take this branch together
   }
+  for (int64_t k = ((int64_t)GD_CACHE * GD_THREADS + threadIdx.x) * 4; k < K; k += GD_THREADS * 4) convert(gd_x4<XT>(xr, k), k);
 }
 
 // ---- the products.  NT = 8-column tiles of (plane, row) columns: column c = plane * M + m, 3 M columns in all.
 template <typename XT, int GGML, int NT>
 __global__ void __launch_bounds__(GM_WARPS * 32, 2)
-ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits, const int* __restrict__ dsum, const float* __restrict__ units,
+ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits, const float* __restrict__ dsum, const float* __restrict__ units,
                 const float* __restrict__ bias, XT* __restrict__ out, int M, int64_t K, int64_t N, int act) {
   constexpr int BB = gm_block_bytes(GGML), SEG = gm_seg(GGML), PITCH = gm_pitch(GGML), STAGE = gm_stage_bytes(GGML);
+  constexpr int COLS = 8 * NT;
   extern __shared__ __align__(16) unsigned char gm_smem[];
+  // a following digit kernel of this library may be scheduled early: it waits for this grid before it touches anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int half = warp >> 2;                                  // which half of K
   const int64_t row0 = (int64_t)blockIdx.x * GM_ROWS + (warp & 3) * 16;
-  const int64_t U = K / 32, steps_all = K / GM_STEP;
+  const int64_t steps_all = K / GM_STEP;
   const int64_t step0 = half == 0 ? 0 : (steps_all + 1) / 2, step1 = half == 0 ? (steps_all + 1) / 2 : steps_all;
   const int n_steps = (int)(step1 - step0);
   const int64_t bytes_per_row = K / (GGML == CB_GGML_Q4_K ? 256 : 32) * BB;
-  const int ncols = 3 * M;
-  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(gm_smem) + warp * GM_STAGES * STAGE;
+  unsigned char* ring = gm_smem + warp * GM_STAGES * STAGE;
 
-  // this warp's 16 rows, 16 bytes per copy: SEG / 16 copies per row and stage
-  auto fill = [&](int s) {
+  // The ring: one copy instruction moves 128 contiguous bytes of each of four rows (lane l: row l / 8, piece l % 8), so
+  // a step takes the 16 rows in four such instructions per 128 bytes of the segment, and one more for the 16-byte
+  // piece that remains (lanes 0-15, one row each).  Rows past N repeat the last one; their results are not stored.
+  constexpr int VPR = SEG / 16;
+  static_assert(VPR % 8 == 1, "a step's segment is whole 128-byte runs plus one 16-byte piece");
+  const uint8_t* fbase = w + row0 * bytes_per_row + step0 * SEG;
+  // Byte offsets of rows 4 i + l / 8 from the warp's first row: negative when that row itself lies past N (the last CTA
+  // of a ragged N), at least -63 rows of at most 2^24 / 32 * 34 bytes, so 32 signed bits hold them.
+  int frow[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) frow[i] = (int)(min(row0 + 4 * i + (lane >> 3), N - 1) - row0) * (int)bytes_per_row + (lane & 7) * 16;
+  const int frem = (int)(min(row0 + (lane & 15), N - 1) - row0) * (int)bytes_per_row + (VPR - 1) * 16;
+  const uint32_t fdst = (uint32_t)__cvta_generic_to_shared(ring) + (lane >> 3) * PITCH + (lane & 7) * 16;
+  const uint32_t fdst_rem = (uint32_t)__cvta_generic_to_shared(ring) + (lane & 15) * PITCH + (VPR - 1) * 16;
+  auto fill = [&](int s, int slot) {
     if (s < n_steps) {
-      const uint32_t st = ring + (s % GM_STAGES) * STAGE;
-      constexpr int VPR = SEG / 16;
-      for (int id = lane; id < 16 * VPR; id += 32) {
-        const int r = id / VPR, v = id % VPR;
-        const int64_t row = min(row0 + r, N - 1);             // rows past N repeat the last one; their results are not stored
-        const uint8_t* src = w + row * bytes_per_row + (step0 + s) * SEG + v * 16;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(st + r * PITCH + v * 16), "l"(src) : "memory");
-      }
+      const uint8_t* src = fbase + (int64_t)s * SEG;
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int h = 0; h < VPR / 8; h++)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(fdst + slot * STAGE + i * 4 * PITCH + h * 128), "l"(src + (int64_t)frow[i] + h * 128) : "memory");
+      if (lane < 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(fdst_rem + slot * STAGE), "l"(src + (int64_t)frem) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 #pragma unroll
-  for (int s = 0; s < GM_STAGES - 1; s++) fill(s);
+  for (int s = 0; s < GM_STAGES - 1; s++) fill(s, s);
 
   float acc[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; j++) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f; }
-  // the digit rows and block sums this lane reads: B fragment column 8j + g, C columns 8j + 2t and 8j + 2t + 1
-  const int8_t* dcol[NT];
-  const int* scol0[NT];
-  const int* scol1[NT];
-#pragma unroll
-  for (int j = 0; j < NT; j++) {
-    const int cb = 8 * j + g, c0 = 8 * j + 2 * t, c1 = c0 + 1;
-    dcol[j] = cb < ncols ? digits + (int64_t)cb * K : nullptr;
-    scol0[j] = c0 < ncols ? dsum + (int64_t)c0 * U : nullptr;
-    scol1[j] = c1 < ncols ? dsum + (int64_t)c1 * U : nullptr;
-  }
 
+  // weights do not come from the digit kernel; everything below reads what it wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // B fragment of tile j: column 8 j + g, the block's values 8 t .. 8 t + 7; C columns 8 j + 2 t and 8 j + 2 t + 1
+  const int8_t* bp = digits + (int64_t)g * K + step0 * GM_STEP + 8 * t;
+  const float* sp = dsum + step0 * 8 * COLS + 2 * t;
+  const int64_t tile_stride = 8 * K;
+  uint2 bnext[NT];
+#pragma unroll
+  for (int j = 0; j < NT; j++) bnext[j] = n_steps > 0 ? __ldg(reinterpret_cast<const uint2*>(bp + j * tile_stride)) : make_uint2(0u, 0u);
+
+  int slot = 0;
   for (int s = 0; s < n_steps; s++) {
     asm volatile("cp.async.wait_group %0;" :: "n"(GM_STAGES - 2) : "memory");
     __syncwarp();
-    fill(s + GM_STAGES - 1);
-    const uint32_t st = ring + (s % GM_STAGES) * STAGE;
-    const uint32_t rlo = st + g * PITCH, rhi = st + (g + 8) * PITCH;
-    const int64_t u0 = (step0 + s) * 8;                       // first 32-value block of this step
+    fill(s + GM_STAGES - 1, slot == 0 ? GM_STAGES - 1 : slot - 1);
+    const unsigned char* rlo = ring + slot * STAGE + g * PITCH;
+    const unsigned char* rhi = rlo + 8 * PITCH;
+    slot = slot + 1 == GM_STAGES ? 0 : slot + 1;
+    const bool last_step = s + 1 == n_steps;
+
+    // Q4_K: the super-block's header, once per step and row
+    float dl = 0.f, dh = 0.f, ml = 0.f, mh = 0.f;
+    uint32_t ql0 = 0, ql1 = 0, ql2 = 0, qh0 = 0, qh1 = 0, qh2 = 0;
+    int isum[NT][4];
+    if (GGML == CB_GGML_Q4_K) {
+      dl = gm_f16(rlo); ml = gm_f16(rlo + 2); dh = gm_f16(rhi); mh = gm_f16(rhi + 2);
+      ql0 = *reinterpret_cast<const uint32_t*>(rlo + 4); ql1 = *reinterpret_cast<const uint32_t*>(rlo + 8); ql2 = *reinterpret_cast<const uint32_t*>(rlo + 12);
+      qh0 = *reinterpret_cast<const uint32_t*>(rhi + 4); qh1 = *reinterpret_cast<const uint32_t*>(rhi + 8); qh2 = *reinterpret_cast<const uint32_t*>(rhi + 12);
+#pragma unroll
+      for (int j = 0; j < NT; j++) { isum[j][0] = isum[j][1] = isum[j][2] = isum[j][3] = 0; }
+    }
 #pragma unroll
     for (int u = 0; u < 8; u++) {
+      // ---- B fragments: this block's were requested one block ago; request the next block's now
+      uint2 b[NT];
+#pragma unroll
+      for (int j = 0; j < NT; j++) b[j] = bnext[j];
+      if (!(last_step && u == 7)) {
+        const int8_t* nb = bp + ((int64_t)s * 8 + u + 1) * 32;
+#pragma unroll
+        for (int j = 0; j < NT; j++) bnext[j] = __ldg(reinterpret_cast<const uint2*>(nb + j * tile_stride));
+      }
       // ---- A fragments: rows g and g + 8, the block's values 8t .. 8t + 7
       uint32_t a0, a1, a2, a3;
-      float dl, dh, ml = 0.0f, mh = 0.0f;                       // scale (and, Q4_K, min term) of the two rows
       if (GGML == CB_GGML_Q8_0) {
-        gm_lds8(rlo + u * 34 + 2 + 8 * t, a0, a2);
-        gm_lds8(rhi + u * 34 + 2 + 8 * t, a1, a3);
-        dl = gm_lds_f16(rlo + u * 34); dh = gm_lds_f16(rhi + u * 34);
+        gm_ld8(rlo + 8 * t, u * 34 + 2, a0, a2);
+        gm_ld8(rhi + 8 * t, u * 34 + 2, a1, a3);
+        dl = gm_f16(rlo + u * 34); dh = gm_f16(rhi + u * 34);
       } else if (GGML == CB_GGML_Q4_0 || GGML == CB_GGML_IQ4_NL) {
         uint32_t l0, l1, h0, h1;
-        gm_lds8(rlo + u * 18 + 2 + 8 * (t & 1), l0, l1);
-        gm_lds8(rhi + u * 18 + 2 + 8 * (t & 1), h0, h1);
-        const int sh = 4 * (t >> 1);                            // values 0-15 are the low nibbles, 16-31 the high ones
-        a0 = (l0 >> sh) & 0x0F0F0F0Fu; a2 = (l1 >> sh) & 0x0F0F0F0Fu;
-        a1 = (h0 >> sh) & 0x0F0F0F0Fu; a3 = (h1 >> sh) & 0x0F0F0F0Fu;
-        if (GGML == CB_GGML_IQ4_NL) { a0 = gm_iq4nl(a0); a1 = gm_iq4nl(a1); a2 = gm_iq4nl(a2); a3 = gm_iq4nl(a3); }
-        dl = gm_lds_f16(rlo + u * 18); dh = gm_lds_f16(rhi + u * 18);
-      } else {  // Q4_K: sub-block u of the row's block: bytes 16 + 32 (u / 2) + 8t .., low nibbles for even u, high for odd
-        uint2 l, h;
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(l.x), "=r"(l.y) : "r"(rlo + 16 + 32 * (u >> 1) + 8 * t));
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(h.x), "=r"(h.y) : "r"(rhi + 16 + 32 * (u >> 1) + 8 * t));
+        gm_ld8(rlo + 8 * (t & 1), u * 18 + 2, l0, l1);
+        gm_ld8(rhi + 8 * (t & 1), u * 18 + 2, h0, h1);
+        dl = gm_f16(rlo + u * 18); dh = gm_f16(rhi + u * 18);
+        if (GGML == CB_GGML_IQ4_NL) {
+          const int sh = 4 * (t >> 1);                          // values 0-15 are the low nibbles, 16-31 the high ones
+          a0 = gm_iq4nl((l0 >> sh) & 0x0F0F0F0Fu); a2 = gm_iq4nl((l1 >> sh) & 0x0F0F0F0Fu);
+          a1 = gm_iq4nl((h0 >> sh) & 0x0F0F0F0Fu); a3 = gm_iq4nl((h1 >> sh) & 0x0F0F0F0Fu);
+        } else {
+          // the nibble goes to the top of its byte with its top bit flipped: as int8 that is 16 (n - 8), and the 1/16 goes
+          // into the block's scale (exact: a power of two)
+          const int sh = 4 - 4 * (t >> 1);
+          a0 = ((l0 << sh) & 0xF0F0F0F0u) ^ 0x80808080u; a2 = ((l1 << sh) & 0xF0F0F0F0u) ^ 0x80808080u;
+          a1 = ((h0 << sh) & 0xF0F0F0F0u) ^ 0x80808080u; a3 = ((h1 << sh) & 0xF0F0F0F0u) ^ 0x80808080u;
+          dl *= 0.0625f; dh *= 0.0625f;
+        }
+      } else {  // Q4_K: sub-block u of the super-block: bytes 16 + 32 (u / 2) + 8t .., low nibbles for even u, high for odd
+        const uint2 l = *reinterpret_cast<const uint2*>(rlo + 16 + 32 * (u >> 1) + 8 * t);
+        const uint2 h = *reinterpret_cast<const uint2*>(rhi + 16 + 32 * (u >> 1) + 8 * t);
         const int sh = 4 * (u & 1);
         a0 = (l.x >> sh) & 0x0F0F0F0Fu; a2 = (l.y >> sh) & 0x0F0F0F0Fu;
         a1 = (h.x >> sh) & 0x0F0F0F0Fu; a3 = (h.y >> sh) & 0x0F0F0F0Fu;
-        // getScaleMinK4 (quantizeddense_ggml.go:219-228) on the 12 packed bytes at offset 4
-        auto scale_min = [&](uint32_t rowa, float& dsc, float& dmn) {
-          uint32_t sc, mn;
-          if (u < 4) { sc = gm_lds_u8(rowa + 4 + u) & 63u; mn = gm_lds_u8(rowa + 8 + u) & 63u; }
-          else {
-            const uint32_t x4 = gm_lds_u8(rowa + 8 + u), xa = gm_lds_u8(rowa + u), xb = gm_lds_u8(rowa + 4 + u);
-            sc = (x4 & 0xFu) | ((xa >> 6) << 4);
-            mn = (x4 >> 4) | ((xb >> 6) << 4);
-          }
-          dsc = __fmul_rn(gm_lds_f16(rowa), (float)sc);
-          dmn = __fmul_rn(gm_lds_f16(rowa + 2), (float)mn);
-        };
-        scale_min(rlo, dl, ml);
-        scale_min(rhi, dh, mh);
       }
-      const int64_t ub = u0 + u;
+      // getScaleMinK4 (quantizeddense_ggml.go:219-228) on the 12 packed bytes q[0..11] = words q0, q1, q2
+      int scl = 0, sch = 0;
+      float mnl = 0.f, mnh = 0.f;
+      if (GGML == CB_GGML_Q4_K) {
+        auto scale_min = [&](uint32_t q0, uint32_t q1, uint32_t q2, int& sc, int& mn) {
+          if (u < 4) { sc = (q0 >> (8 * u)) & 63; mn = (q1 >> (8 * u)) & 63; }
+          else {
+            const int v = u - 4;
+            const uint32_t x4 = (q2 >> (8 * v)) & 0xFFu, xa = (q0 >> (8 * v)) & 0xFFu, xb = (q1 >> (8 * v)) & 0xFFu;
+            sc = (int)((x4 & 0xFu) | ((xa >> 6) << 4));
+            mn = (int)((x4 >> 4) | ((xb >> 6) << 4));
+          }
+        };
+        int mn_l, mn_h;
+        scale_min(ql0, ql1, ql2, scl, mn_l);
+        scale_min(qh0, qh1, qh2, sch, mn_h);
+        mnl = ml * (float)mn_l; mnh = mh * (float)mn_h;       // dmin * m, exact: 11 x 6 bits
+      }
 #pragma unroll
       for (int j = 0; j < NT; j++) {
-        uint2 b = make_uint2(0u, 0u);
-        if (dcol[j]) b = __ldg(reinterpret_cast<const uint2*>(dcol[j] + ub * 32 + 8 * t));
         int c[4];
-        gm_mma(c, a0, a1, a2, a3, b.x, b.y);
-        if (GGML == CB_GGML_Q8_0 || GGML == CB_GGML_IQ4_NL) {
-          acc[j][0] = fmaf(dl, (float)c[0], acc[j][0]); acc[j][1] = fmaf(dl, (float)c[1], acc[j][1]);
-          acc[j][2] = fmaf(dh, (float)c[2], acc[j][2]); acc[j][3] = fmaf(dh, (float)c[3], acc[j][3]);
+        gm_mma(c, a0, a1, a2, a3, b[j].x, b[j].y);
+        if (GGML == CB_GGML_Q4_K) {
+          // the 6-bit scales multiply the integer sums; the super-block's d comes once per step.  The minimum takes
+          // the block's digit sums of the two columns.
+          isum[j][0] += scl * c[0]; isum[j][1] += scl * c[1]; isum[j][2] += sch * c[2]; isum[j][3] += sch * c[3];
+          const float2 x = __ldg(reinterpret_cast<const float2*>(sp + ((int64_t)s * 8 + u) * COLS + 8 * j));
+          acc[j][0] = fmaf(-mnl, x.x, acc[j][0]); acc[j][1] = fmaf(-mnl, x.y, acc[j][1]);
+          acc[j][2] = fmaf(-mnh, x.x, acc[j][2]); acc[j][3] = fmaf(-mnh, x.y, acc[j][3]);
         } else {
-          const int x0 = scol0[j] ? __ldg(scol0[j] + ub) : 0, x1 = scol1[j] ? __ldg(scol1[j] + ub) : 0;   // sum of the block's digits
-          if (GGML == CB_GGML_Q4_0) {
-            acc[j][0] = fmaf(dl, (float)(c[0] - 8 * x0), acc[j][0]); acc[j][1] = fmaf(dl, (float)(c[1] - 8 * x1), acc[j][1]);
-            acc[j][2] = fmaf(dh, (float)(c[2] - 8 * x0), acc[j][2]); acc[j][3] = fmaf(dh, (float)(c[3] - 8 * x1), acc[j][3]);
-          } else {
-            const float f0 = (float)x0, f1 = (float)x1;
-            acc[j][0] += fmaf(dl, (float)c[0], -ml * f0); acc[j][1] += fmaf(dl, (float)c[1], -ml * f1);
-            acc[j][2] += fmaf(dh, (float)c[2], -mh * f0); acc[j][3] += fmaf(dh, (float)c[3], -mh * f1);
-          }
+          // |c| <= 32 * 127 * 64 < 2^22
+          acc[j][0] = fmaf(dl, gm_i2f(c[0]), acc[j][0]); acc[j][1] = fmaf(dl, gm_i2f(c[1]), acc[j][1]);
+          acc[j][2] = fmaf(dh, gm_i2f(c[2]), acc[j][2]); acc[j][3] = fmaf(dh, gm_i2f(c[3]), acc[j][3]);
         }
+      }
+    }
+    if (GGML == CB_GGML_Q4_K) {
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+        acc[j][0] = fmaf(dl, (float)isum[j][0], acc[j][0]); acc[j][1] = fmaf(dl, (float)isum[j][1], acc[j][1]);
+        acc[j][2] = fmaf(dh, (float)isum[j][2], acc[j][2]); acc[j][3] = fmaf(dh, (float)isum[j][3], acc[j][3]);
       }
     }
   }
@@ -277,8 +358,8 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
   for (int j = 0; j < NT; j++) {
     const int c0 = 8 * j + 2 * t;
     float* p0 = part + ((half * GM_ROWS + rl) * GM_MAX_COLS), *p1 = part + ((half * GM_ROWS + rl + 8) * GM_MAX_COLS);
-    if (c0 < ncols) { p0[c0] = acc[j][0]; p1[c0] = acc[j][2]; }
-    if (c0 + 1 < ncols) { p0[c0 + 1] = acc[j][1]; p1[c0 + 1] = acc[j][3]; }
+    *reinterpret_cast<float2*>(p0 + c0) = make_float2(acc[j][0], acc[j][1]);
+    *reinterpret_cast<float2*>(p1 + c0) = make_float2(acc[j][2], acc[j][3]);
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < GM_ROWS * M; idx += GM_WARPS * 32) {
@@ -303,14 +384,34 @@ size_t gm_smem_bytes(int ggml) {
 }
 
 static size_t gm_align(size_t b) { return (b + 255) & ~(size_t)255; }
+// The digit kernel's outputs in the plan's workspace.  Each array is followed by at least 256 spare bytes: the product
+// kernel requests the digits of the block after the one it works on.
 struct GmLayout { size_t off_digits, off_dsum, off_units, total; };
 GmLayout gm_layout(int64_t M, int64_t K) {
+  const size_t cols = 8 * (size_t)gm_tiles((int)M);
   GmLayout l;
   l.off_digits = 0;
-  l.off_dsum = gm_align((size_t)(3 * M * K));
-  l.off_units = l.off_dsum + gm_align((size_t)(3 * M * (K / 32)) * 4);
+  l.off_dsum = gm_align(cols * (size_t)K) + 256;
+  l.off_units = l.off_dsum + gm_align(cols * (size_t)(K / 32) * 4) + 256;
   l.total = l.off_units + 256;
   return l;
+}
+
+template <typename K_, typename... Args>
+int gm_launch_pdl(K_ kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
+  return CB_OK;
 }
 
 template <typename XT, int GGML, int NT>
@@ -326,23 +427,27 @@ int gm_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out
   const GmLayout l = gm_layout(d.M, d.K);
   uint8_t* w8 = (uint8_t*)ws;
   int8_t* digits = (int8_t*)(w8 + l.off_digits);
-  int* dsum = (int*)(w8 + l.off_dsum);
+  float* dsum = (float*)(w8 + l.off_dsum);
   float* units = (float*)(w8 + l.off_units);
-  ggml_row_digits_kernel<XT><<<(unsigned)d.M, GD_THREADS, 0, s>>>((const XT*)in[0], (int)d.M, d.K, digits, dsum, units);
-  CB_CUDA(cudaGetLastError());
+  int rc = gm_launch_pdl(ggml_row_digits_kernel<XT>, dim3((unsigned)d.M), dim3(GD_THREADS), 0, s, (const XT*)in[0], (int)d.M, (int64_t)d.K, 8 * NT,
+                         digits, GGML == CB_GGML_Q4_K ? dsum : (float*)nullptr, units);
+  if (rc != CB_OK) return rc;
   const float* bias = d.has_bias ? (const float*)in[2] : nullptr;
-  ggml_mma_kernel<XT, GGML, NT><<<(unsigned)((d.N + GM_ROWS - 1) / GM_ROWS), GM_WARPS * 32, smem, s>>>(
-      (const uint8_t*)in[1], digits, dsum, units, bias, (XT*)out[0], (int)d.M, d.K, d.N, d.activation);
-  CB_CUDA(cudaGetLastError());
-  return CB_OK;
+  return gm_launch_pdl(ggml_mma_kernel<XT, GGML, NT>, dim3((unsigned)((d.N + GM_ROWS - 1) / GM_ROWS)), dim3(GM_WARPS * 32), smem, s,
+                       (const uint8_t*)in[1], (const int8_t*)digits, (const float*)dsum, (const float*)units, bias, (XT*)out[0], (int)d.M,
+                       (int64_t)d.K, (int64_t)d.N, (int)d.activation);
 }
 
 template <typename XT, int GGML>
 int gm_launch_n(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  const int ncols = 3 * (int)d.M;
-  if (ncols <= 8) return gm_launch_k<XT, GGML, 1>(d, in, out, ws, s);
-  if (ncols <= 16) return gm_launch_k<XT, GGML, 2>(d, in, out, ws, s);
-  return gm_launch_k<XT, GGML, 6>(d, in, out, ws, s);
+  switch (gm_tiles((int)d.M)) {
+    case 1: return gm_launch_k<XT, GGML, 1>(d, in, out, ws, s);
+    case 2: return gm_launch_k<XT, GGML, 2>(d, in, out, ws, s);
+    case 3: return gm_launch_k<XT, GGML, 3>(d, in, out, ws, s);
+    case 4: return gm_launch_k<XT, GGML, 4>(d, in, out, ws, s);
+    case 5: return gm_launch_k<XT, GGML, 5>(d, in, out, ws, s);
+    default: return gm_launch_k<XT, GGML, 6>(d, in, out, ws, s);
+  }
 }
 
 template <typename XT>
@@ -360,7 +465,7 @@ int gm_launch_t(const cb_qdense_desc& d, const void* const* in, void* const* out
 bool qdense_ggml_mma_supports(const cb_qdense_desc& d) {
   if (d.scheme != CB_QUANT_GGML || d.variant == CB_QDENSE_GENERIC) return false;
   if (d.ggml_type != CB_GGML_Q4_0 && d.ggml_type != CB_GGML_Q8_0 && d.ggml_type != CB_GGML_IQ4_NL && d.ggml_type != CB_GGML_Q4_K) return false;
-  return d.M >= 1 && d.M <= 16 && d.K >= 256 && d.K % 256 == 0 && d.N >= 1 && (d.N + GM_ROWS - 1) / GM_ROWS <= 0x7FFFFFFFLL;
+  return d.M >= 1 && d.M <= 16 && d.K >= 256 && d.K % 256 == 0 && d.K <= (1 << 24) && d.N >= 1 && (d.N + GM_ROWS - 1) / GM_ROWS <= 0x7FFFFFFFLL;
 }
 
 void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {

@@ -54,6 +54,8 @@ def main() -> None:
     ap.add_argument("--sq", type=int, default=0, help="query length when it differs from the key length --s")
     ap.add_argument("--bshd", action="store_true", help="[batch, seq, heads, dim] operands instead of [batch, heads, seq, dim]")
     ap.add_argument("--layers", type=int, default=1, help="qdense: this many independent projections as one grouped launch")
+    ap.add_argument("--ggml", default="", choices=["", "q4_0", "q8_0", "iq4_nl", "q4_k", "q6_k"],
+                    help="qdense: weights in this GGML block format instead of int8 with separate scales")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--layout", default="kgroup", choices=["channel", "kgroup"])
     ap.add_argument("--group", type=int, default=128)
@@ -114,6 +116,31 @@ def main() -> None:
         sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=rows * N).astype(np.float32), dev)
         y = dv.DeviceMem(a.m * N * (2 if a.dtype == "bf16" else 4), dev)
         layout = dv.SCALE_CHANNEL if a.layout == "channel" else dv.SCALE_KGROUP
+        if a.ggml:
+            # random block bytes with a finite half-precision scale in every block
+            gt, values, bb, scale_at = {"q4_0": (dv.GGML_Q4_0, 32, 18, (0,)), "q8_0": (dv.GGML_Q8_0, 32, 34, (0,)),
+                                        "iq4_nl": (dv.GGML_IQ4_NL, 32, 18, (0,)), "q4_k": (dv.GGML_Q4_K, 256, 144, (0, 2)),
+                                        "q6_k": (dv.GGML_Q6_K, 256, 210, (208,))}[a.ggml]
+            blocks = rng.integers(0, 256, size=(N, K // values, bb), dtype=np.uint8)
+            for o in scale_at:
+                blocks[:, :, o:o + 2] = np.frombuffer(np.float16(0.03125).tobytes(), np.uint8)
+            # --layers copies of the weights, one launch each in turn: more bytes than the L2 holds between two uses of a copy
+            wgs = [dv.DeviceMem.from_numpy(blocks.reshape(N, -1), dev) for _ in range(a.layers)]
+            plan = dv.Plan.qdense(a.m, K, N, code, dv.U8, has_bias=False, activation=dv.ACT_SILU, scheme=dv.QUANT_GGML, ggml_type=gt, dev=dev)
+            ws = plan.new_workspace()
+            e0, e1 = dv.Event(dev), dv.Event(dev)
+            for it in range(a.reps + a.warmup):
+                if it == a.warmup:
+                    e0.record(stream)
+                for wg in wgs:
+                    plan.launch([x.ptr, wg.ptr], [y.ptr], ws.ptr if ws else None, stream)
+            e1.record(stream)
+            stream.sync()
+            us = e0.elapsed_ms(e1) * 1e3 / (a.reps * a.layers)
+            out.update(kernel=plan.kernel_name, blocks=plan.blocks, us=us, weight_GBps=blocks.nbytes / us / 1e3,
+                       tflops=2.0 * a.m * K * N / us / 1e6)
+            print(json.dumps(out))
+            return
         if a.layers > 1:
             # independent projections (own weights, scales, outputs; one shared activation) as one launch
             ws_ = [w] + [dv.DeviceMem.from_numpy(rng.integers(-127, 128, size=K * N, dtype=np.int8), dev) for _ in range(a.layers - 1)]
