@@ -16,9 +16,11 @@
 // contiguous bytes.
 //
 // A CTA owns 64 weight rows: warps 0-3 take 16 rows each over the first half of K, warps 4-7 the same rows over the second
-// half; every warp streams its rows through a private three-stage ring of 256-value steps filled by cp.async.  At the
-// end the halves and the digit planes are combined through shared memory, bias and activation applied, results stored.
-#include "common.cuh"
+// half; every warp streams its rows through a private three-stage ring of 256-value steps, each stage one TMA tile
+// (16 rows x the step's bytes) announced on the warp's own mbarrier.  At the end the halves and the digit planes are
+// combined through shared memory, bias and activation applied, results stored.  Every wait is bounded: a stage that does
+// not arrive within two seconds ends the kernel with a status word set, which cb_plan_check_status reports.
+#include "tc_common.cuh"
 
 #include <cuda_fp16.h>
 
@@ -35,13 +37,21 @@ constexpr int GM_ROWS = 64;                 // weight rows per CTA
 constexpr int GM_STEP = 256;                // values per ring stage and row
 constexpr int GM_STAGES = 3;
 constexpr int GM_MAX_COLS = 48;             // 3 digit planes x 16 rows of x
+constexpr int GM_BAR_BYTES = 256;           // the stages' barriers (8 warps x 3) and the digits' one
+constexpr int GM_DPAD = 32;                 // bytes between two columns of digits in shared memory, past K
+// A CTA asks for at least this much shared memory, so that no more than two fit an SM.  With three, the CTAs of the
+// next launch of a decode loop (scheduled early, as dependents) settle beside the running ones and both slow down:
+// IQ4_NL at M = 4 took 28 us with the floor and 49 us without.
+constexpr size_t GM_SMEM_FLOOR = 78 * 1024;
+constexpr size_t GM_SMEM_CTA = 112 * 1024;  // what a CTA may use while two still fit an SM (227 KB, 1 KB reserved per CTA)
 
 __host__ __device__ constexpr int gm_block_bytes(int t) { return t == CB_GGML_Q8_0 ? 34 : t == CB_GGML_Q4_K ? 144 : 18; }
 __host__ __device__ constexpr int gm_seg(int t) { return t == CB_GGML_Q4_K ? 144 : 8 * gm_block_bytes(t); }   // bytes of 256 values
-// Row pitch in the ring.  18-byte blocks: 176 bytes = 44 words, so the eight rows of a fragment read start in banks 0, 12,
-// 24, 4, 16, 28, 8, 20.  Q4_K: 160 bytes = 40 words, the four rows of a half-warp's 64-bit reads start 8 banks apart.  Q8_0:
-// 288 bytes (rows g and g + 4 share banks; 304 would not, but two CTAs of three stages would no longer fit one SM).
-__host__ __device__ constexpr int gm_pitch(int t) { return t == CB_GGML_Q4_K ? 160 : t == CB_GGML_Q8_0 ? 288 : 176; }
+// Row pitch in the ring = the inner extent of the TMA box.  18-byte blocks: the step's 144 bytes = 36 words, so the eight
+// rows of a fragment read start in banks 0, 4, .., 28 and the two 8-byte halves a row is read in fill the gaps.  Q4_K:
+// 160 bytes (the box takes 16 bytes of the next step along): the four rows of a half-warp's 64-bit reads start 8 banks
+// apart.  Q8_0: the step's 272 bytes.
+__host__ __device__ constexpr int gm_pitch(int t) { return t == CB_GGML_Q4_K ? 160 : gm_seg(t); }
 __host__ __device__ constexpr int gm_stage_bytes(int t) { return 16 * gm_pitch(t); }
 __host__ __device__ constexpr int gm_tiles(int M) { return (3 * M + 7) / 8; }             // 8-column tiles of (plane, row) columns
 
@@ -180,13 +190,16 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int
 }
 
 // ---- the products.  NT = 8-column tiles of (plane, row) columns: column c = plane * M + m, 3 M columns in all.
-template <typename XT, int GGML, int NT>
+// BSMEM: the digits of all columns are brought into shared memory once per CTA (small M); otherwise every block's B
+// fragments come through L1, requested one block ahead.
+template <typename XT, int GGML, int NT, bool BSMEM>
 __global__ void __launch_bounds__(GM_WARPS * 32, 2)
-ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits, const float* __restrict__ dsum, const float* __restrict__ units,
-                const float* __restrict__ bias, XT* __restrict__ out, int M, int64_t K, int64_t N, int act) {
-  constexpr int BB = gm_block_bytes(GGML), SEG = gm_seg(GGML), PITCH = gm_pitch(GGML), STAGE = gm_stage_bytes(GGML);
+ggml_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __restrict__ digits, const float* __restrict__ dsum,
+                const float* __restrict__ units, const float* __restrict__ bias, XT* __restrict__ out, int M, int64_t K, int64_t N, int act,
+                unsigned* __restrict__ status) {
+  constexpr int SEG = gm_seg(GGML), PITCH = gm_pitch(GGML), STAGE = gm_stage_bytes(GGML);
   constexpr int COLS = 8 * NT;
-  extern __shared__ __align__(16) unsigned char gm_smem[];
+  extern __shared__ __align__(1024) unsigned char gm_smem[];
   // a following digit kernel of this library may be scheduled early: it waits for this grid before it touches anything
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -196,34 +209,27 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
   const int64_t steps_all = K / GM_STEP;
   const int64_t step0 = half == 0 ? 0 : (steps_all + 1) / 2, step1 = half == 0 ? (steps_all + 1) / 2 : steps_all;
   const int n_steps = (int)(step1 - step0);
-  const int64_t bytes_per_row = K / (GGML == CB_GGML_Q4_K ? 256 : 32) * BB;
   unsigned char* ring = gm_smem + warp * GM_STAGES * STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + warp * GM_STAGES;
+  uint64_t* bar_digits = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + GM_WARPS * GM_STAGES;
+  unsigned char* dsm = gm_smem + GM_WARPS * GM_STAGES * STAGE + GM_BAR_BYTES;     // [3 M columns][K + 32] when BSMEM
+  const int ncols = 3 * M;
+  const int64_t dpitch = K + GM_DPAD;
 
-  // The ring: one copy instruction moves 128 contiguous bytes of each of four rows (lane l: row l / 8, piece l % 8), so
-  // a step takes the 16 rows in four such instructions per 128 bytes of the segment, and one more for the 16-byte
-  // piece that remains (lanes 0-15, one row each).  Rows past N repeat the last one; their results are not stored.
-  constexpr int VPR = SEG / 16;
-  static_assert(VPR % 8 == 1, "a step's segment is whole 128-byte runs plus one 16-byte piece");
-  const uint8_t* fbase = w + row0 * bytes_per_row + step0 * SEG;
-  // Byte offsets of rows 4 i + l / 8 from the warp's first row: negative when that row itself lies past N (the last CTA
-  // of a ragged N), at least -63 rows of at most 2^24 / 32 * 34 bytes, so 32 signed bits hold them.
-  int frow[4];
+  // The ring: lane 0 asks for one tile per step - the warp's 16 rows by the step's bytes of each - and the stage's
+  // barrier completes when all of it has landed.  Rows past N come back as zeros (scale 0); their results are not stored.
+  if (lane == 0) {
 #pragma unroll
-  for (int i = 0; i < 4; i++) frow[i] = (int)(min(row0 + 4 * i + (lane >> 3), N - 1) - row0) * (int)bytes_per_row + (lane & 7) * 16;
-  const int frem = (int)(min(row0 + (lane & 15), N - 1) - row0) * (int)bytes_per_row + (VPR - 1) * 16;
-  const uint32_t fdst = (uint32_t)__cvta_generic_to_shared(ring) + (lane >> 3) * PITCH + (lane & 7) * 16;
-  const uint32_t fdst_rem = (uint32_t)__cvta_generic_to_shared(ring) + (lane & 15) * PITCH + (VPR - 1) * 16;
+    for (int k = 0; k < GM_STAGES; k++) tc::mbar_init(&bars[k], 1);
+    if (BSMEM && warp == 0) tc::mbar_init(bar_digits, 1);
+    tc::fence_barrier_init();
+  }
+  if (BSMEM) __syncthreads(); else __syncwarp();
   auto fill = [&](int s, int slot) {
-    if (s < n_steps) {
-      const uint8_t* src = fbase + (int64_t)s * SEG;
-#pragma unroll
-      for (int i = 0; i < 4; i++)
-#pragma unroll
-        for (int h = 0; h < VPR / 8; h++)
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(fdst + slot * STAGE + i * 4 * PITCH + h * 128), "l"(src + (int64_t)frow[i] + h * 128) : "memory");
-      if (lane < 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(fdst_rem + slot * STAGE), "l"(src + (int64_t)frem) : "memory");
+    if (s < n_steps && lane == 0) {
+      tc::mbar_expect_tx(&bars[slot], STAGE);
+      tc::tma_load_2d(ring + slot * STAGE, &tmap_w, (int)((step0 + s) * (SEG / 4)), (int)row0, &bars[slot]);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
   };
 #pragma unroll
   for (int s = 0; s < GM_STAGES - 1; s++) fill(s, s);
@@ -235,22 +241,47 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
   // weights do not come from the digit kernel; everything below reads what it wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // B fragment of tile j: column 8 j + g, the block's values 8 t .. 8 t + 7; C columns 8 j + 2 t and 8 j + 2 t + 1
+  // B fragment of tile j: column 8 j + g, the block's values 8 t .. 8 t + 7; C columns 8 j + 2 t and 8 j + 2 t + 1.
+  // Columns from 3 M on do not exist: in shared memory their fragments are zero, in global memory they are whatever
+  // the padded digit buffer holds (their products are dropped).
   const int8_t* bp = digits + (int64_t)g * K + step0 * GM_STEP + 8 * t;
+  const unsigned char* bs = dsm + (int64_t)g * dpitch + step0 * GM_STEP + 8 * t;
   const float* sp = dsum + step0 * 8 * COLS + 2 * t;
-  const int64_t tile_stride = 8 * K;
-  uint2 bnext[NT];
+  const int64_t tile_stride = 8 * (BSMEM ? dpitch : K);
+  bool colv[NT];
 #pragma unroll
-  for (int j = 0; j < NT; j++) bnext[j] = n_steps > 0 ? __ldg(reinterpret_cast<const uint2*>(bp + j * tile_stride)) : make_uint2(0u, 0u);
+  for (int j = 0; j < NT; j++) colv[j] = 8 * j + g < ncols;
+  uint2 bnext[NT];
+  bool failed = false;
+  if (BSMEM) {
+    // one bulk copy per column, K bytes each, rows K + 32 bytes apart: the four columns a half-warp reads 64 bits of
+    // start 8 banks apart
+    if (threadIdx.x == 0) {
+      tc::mbar_expect_tx(bar_digits, (uint32_t)(ncols * K));
+      for (int c = 0; c < ncols; c++)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(tc::smem_u32(dsm + c * dpitch)), "l"(digits + (int64_t)c * K), "r"((uint32_t)K), "r"(tc::smem_u32(bar_digits)) : "memory");
+    }
+    const bool ok = tc::mbar_wait(bar_digits, 0);
+    if (!__all_sync(0xFFFFFFFFu, ok)) failed = true;
+  } else {
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+      bnext[j] = n_steps > 0 ? __ldg(reinterpret_cast<const uint2*>(bp + j * tile_stride)) : make_uint2(0u, 0u);
+  }
 
   int slot = 0;
-  for (int s = 0; s < n_steps; s++) {
-    asm volatile("cp.async.wait_group %0;" :: "n"(GM_STAGES - 2) : "memory");
-    __syncwarp();
+  uint32_t phase = 0;
+  int consumed = 0;                                            // steps whose stage has been waited for
+  for (int s = 0; s < n_steps && !failed; s++) {
+    const bool ok = tc::mbar_wait(&bars[slot], phase);
+    if (!__all_sync(0xFFFFFFFFu, ok)) { failed = true; break; }
+    consumed = s + 1;
+    // every lane has passed the vote, so the stage read in the previous step is free
     fill(s + GM_STAGES - 1, slot == 0 ? GM_STAGES - 1 : slot - 1);
     const unsigned char* rlo = ring + slot * STAGE + g * PITCH;
     const unsigned char* rhi = rlo + 8 * PITCH;
-    slot = slot + 1 == GM_STAGES ? 0 : slot + 1;
+    if (++slot == GM_STAGES) { slot = 0; phase ^= 1u; }
     const bool last_step = s + 1 == n_steps;
 
     // Q4_K: the super-block's header, once per step and row
@@ -266,14 +297,20 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
     }
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-      // ---- B fragments: this block's were requested one block ago; request the next block's now
+      // ---- B fragments: from shared memory, or requested one block ago (and the next block's requested now)
       uint2 b[NT];
+      if (BSMEM) {
 #pragma unroll
-      for (int j = 0; j < NT; j++) b[j] = bnext[j];
-      if (!(last_step && u == 7)) {
-        const int8_t* nb = bp + ((int64_t)s * 8 + u + 1) * 32;
+        for (int j = 0; j < NT; j++)
+          b[j] = colv[j] ? *reinterpret_cast<const uint2*>(bs + j * tile_stride + (s * 8 + u) * 32) : make_uint2(0u, 0u);
+      } else {
 #pragma unroll
-        for (int j = 0; j < NT; j++) bnext[j] = __ldg(reinterpret_cast<const uint2*>(nb + j * tile_stride));
+        for (int j = 0; j < NT; j++) b[j] = bnext[j];
+        if (!(last_step && u == 7)) {
+          const int8_t* nb = bp + ((int64_t)s * 8 + u + 1) * 32;
+#pragma unroll
+          for (int j = 0; j < NT; j++) bnext[j] = __ldg(reinterpret_cast<const uint2*>(nb + j * tile_stride));
+        }
       }
       // ---- A fragments: rows g and g + 8, the block's values 8t .. 8t + 7
       uint32_t a0, a1, a2, a3;
@@ -349,8 +386,18 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
       }
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();                                             // the rings are free: they become the exchange buffer
+  if (failed) {
+    // A stage did not arrive.  Tiles that were asked for may still land: give each one more bounded wait before the
+    // shared memory is given up, record the failure, and leave the outputs alone.
+    if (lane == 0) {
+      const int issued = min(n_steps, consumed + GM_STAGES - 1);
+      for (int s = consumed; s < issued; s++) tc::mbar_wait(&bars[s % GM_STAGES], (uint32_t)((s / GM_STAGES) & 1));
+      if (BSMEM && threadIdx.x == 0) tc::mbar_wait(bar_digits, 0);
+      if (atomicCAS(&status[0], 0u, 1u) == 0u) atomicExch(&status[1], (unsigned)blockIdx.x << 8 | (unsigned)warp);
+    }
+  }
+  const int any_failed = __syncthreads_or(failed ? 1 : 0);     // the rings are free: they become the exchange buffer
+  if (any_failed) return;
   // ---- halves of K and digit planes meet in shared memory: part[half][row][column]
   float* part = reinterpret_cast<float*>(gm_smem);
   const int rl = (warp & 3) * 16 + g;
@@ -379,19 +426,47 @@ ggml_mma_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ digits
   }
 }
 
-size_t gm_smem_bytes(int ggml) {
-  return std::max((size_t)GM_WARPS * GM_STAGES * gm_stage_bytes(ggml), (size_t)2 * GM_ROWS * GM_MAX_COLS * sizeof(float));
+size_t gm_smem_bytes(int ggml) {      // the rings and their barriers; the exchange buffer lies over the rings
+  static_assert((size_t)GM_WARPS * GM_STAGES * gm_stage_bytes(CB_GGML_Q4_0) >= (size_t)2 * GM_ROWS * GM_MAX_COLS * sizeof(float), "exchange buffer");
+  return (size_t)GM_WARPS * GM_STAGES * gm_stage_bytes(ggml) + GM_BAR_BYTES;
+}
+size_t gm_digit_smem(int64_t M, int64_t K) { return (size_t)(3 * M) * (size_t)(K + GM_DPAD); }
+bool gm_digits_resident(int ggml, int64_t M, int64_t K) { return gm_smem_bytes(ggml) + gm_digit_smem(M, K) <= GM_SMEM_CTA; }
+
+// The weights as a matrix of 32-bit words [N rows][bytes per row / 4], in boxes of 16 rows by one step (plus, for Q4_K,
+// four words of the next).  Encoding is a pure function of its arguments and a decode loop asks for the same few maps
+// on every launch, so the last ones are remembered per thread.
+int gm_encode(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes) {
+  struct Entry { const void* ptr; uint64_t row_bytes, rows; uint32_t box_bytes; bool valid; CUtensorMap map; };
+  constexpr int SLOTS = 64;
+  static thread_local Entry cache[SLOTS];
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
+  Entry& e = cache[(h >> 40) % SLOTS];
+  if (e.valid && e.ptr == ptr && e.row_bytes == row_bytes && e.rows == rows && e.box_bytes == box_bytes) { *m = e.map; return CB_OK; }
+  encode_tiled_fn enc = tensor_map_encoder();
+  if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {row_bytes / 4, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes / 4, 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  e.ptr = ptr; e.row_bytes = row_bytes; e.rows = rows; e.box_bytes = box_bytes; e.map = *m; e.valid = true;
+  return CB_OK;
 }
 
 static size_t gm_align(size_t b) { return (b + 255) & ~(size_t)255; }
 // The digit kernel's outputs in the plan's workspace.  Each array is followed by at least 256 spare bytes: the product
 // kernel requests the digits of the block after the one it works on.
+// The first 256 bytes hold the status words (zeroed when the workspace is prepared).
+constexpr size_t GM_HEADER = 256;
 struct GmLayout { size_t off_digits, off_dsum, off_units, total; };
 GmLayout gm_layout(int64_t M, int64_t K) {
   const size_t cols = 8 * (size_t)gm_tiles((int)M);
   GmLayout l;
-  l.off_digits = 0;
-  l.off_dsum = gm_align(cols * (size_t)K) + 256;
+  l.off_digits = GM_HEADER;
+  l.off_dsum = l.off_digits + gm_align(cols * (size_t)K) + 256;
   l.off_units = l.off_dsum + gm_align(cols * (size_t)(K / 32) * 4) + 256;
   l.total = l.off_units + 256;
   return l;
@@ -414,17 +489,19 @@ int gm_launch_pdl(K_ kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s,
   return CB_OK;
 }
 
-template <typename XT, int GGML, int NT>
+template <typename XT, int GGML, int NT, bool BSMEM>
 int gm_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   static std::atomic<bool> configured[64];
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));
-  const size_t smem = gm_smem_bytes(GGML);
+  const size_t smem = std::max(gm_smem_bytes(GGML) + (BSMEM ? gm_digit_smem(d.M, d.K) : 0), GM_SMEM_FLOOR);
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    CB_CUDA(cudaFuncSetAttribute(ggml_mma_kernel<XT, GGML, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CB_CUDA(cudaFuncSetAttribute(ggml_mma_kernel<XT, GGML, NT, BSMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM_CTA));
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   const GmLayout l = gm_layout(d.M, d.K);
+  CUtensorMap tmap;
+  CB_TRY(gm_encode(&tmap, in[1], (uint64_t)(d.K / (GGML == CB_GGML_Q4_K ? 256 : 32) * gm_block_bytes(GGML)), (uint64_t)d.N, (uint32_t)gm_pitch(GGML)));
   uint8_t* w8 = (uint8_t*)ws;
   int8_t* digits = (int8_t*)(w8 + l.off_digits);
   float* dsum = (float*)(w8 + l.off_dsum);
@@ -433,20 +510,21 @@ int gm_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out
                          digits, GGML == CB_GGML_Q4_K ? dsum : (float*)nullptr, units);
   if (rc != CB_OK) return rc;
   const float* bias = d.has_bias ? (const float*)in[2] : nullptr;
-  return gm_launch_pdl(ggml_mma_kernel<XT, GGML, NT>, dim3((unsigned)((d.N + GM_ROWS - 1) / GM_ROWS)), dim3(GM_WARPS * 32), smem, s,
-                       (const uint8_t*)in[1], (const int8_t*)digits, (const float*)dsum, (const float*)units, bias, (XT*)out[0], (int)d.M,
-                       (int64_t)d.K, (int64_t)d.N, (int)d.activation);
+  return gm_launch_pdl(ggml_mma_kernel<XT, GGML, NT, BSMEM>, dim3((unsigned)((d.N + GM_ROWS - 1) / GM_ROWS)), dim3(GM_WARPS * 32), smem, s,
+                       tmap, (const int8_t*)digits, (const float*)dsum, (const float*)units, bias, (XT*)out[0], (int)d.M,
+                       (int64_t)d.K, (int64_t)d.N, (int)d.activation, (unsigned*)w8);
 }
 
 template <typename XT, int GGML>
 int gm_launch_n(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const bool resident = gm_digits_resident(GGML, d.M, d.K);
   switch (gm_tiles((int)d.M)) {
-    case 1: return gm_launch_k<XT, GGML, 1>(d, in, out, ws, s);
-    case 2: return gm_launch_k<XT, GGML, 2>(d, in, out, ws, s);
-    case 3: return gm_launch_k<XT, GGML, 3>(d, in, out, ws, s);
-    case 4: return gm_launch_k<XT, GGML, 4>(d, in, out, ws, s);
-    case 5: return gm_launch_k<XT, GGML, 5>(d, in, out, ws, s);
-    default: return gm_launch_k<XT, GGML, 6>(d, in, out, ws, s);
+    case 1: return resident ? gm_launch_k<XT, GGML, 1, true>(d, in, out, ws, s) : gm_launch_k<XT, GGML, 1, false>(d, in, out, ws, s);
+    case 2: return resident ? gm_launch_k<XT, GGML, 2, true>(d, in, out, ws, s) : gm_launch_k<XT, GGML, 2, false>(d, in, out, ws, s);
+    case 3: return gm_launch_k<XT, GGML, 3, false>(d, in, out, ws, s);
+    case 4: return gm_launch_k<XT, GGML, 4, false>(d, in, out, ws, s);
+    case 5: return gm_launch_k<XT, GGML, 5, false>(d, in, out, ws, s);
+    default: return gm_launch_k<XT, GGML, 6, false>(d, in, out, ws, s);
   }
 }
 
@@ -472,9 +550,11 @@ void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {
   const cb_qdense_desc& d = p->qd;
   p->blocks = (int)((d.N + GM_ROWS - 1) / GM_ROWS);
   p->threads = GM_WARPS * 32;
-  p->dyn_smem = (int)gm_smem_bytes(d.ggml_type);
+  p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)d.M) <= 2 && gm_digits_resident(d.ggml_type, d.M, d.K) ? gm_digit_smem(d.M, d.K) : 0),
+                              GM_SMEM_FLOOR);
   p->workspace_bytes = gm_layout(d.M, d.K).total;
-  p->counter_bytes = 0;
+  p->counter_bytes = GM_HEADER;
+  p->has_status = true;
   p->name = std::string("qdense_ggml_mma_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + type_name;
 }
 
