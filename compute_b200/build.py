@@ -13,7 +13,7 @@ OUT = os.path.join(HERE, "libcudabackend.so")
 OBJ = os.path.join(HERE, "build")
 
 SOURCES = ["runtime.cu", "qdense.cu", "qdense_prefill.cu", "qdense_decode_tc.cu", "dot.cu", "dot_generic.cu", "gemm_tcgen05.cu",
-           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "sdpa_decode.cu", "qdense_ggml.cu", "qdense_ggml_mma.cu", "helper_ops.cu", "fused_small.cu", "elementwise.cu", "graph.cu", "comm.cu"]
+           "sdpa.cu", "sdpa_generic.cu", "sdpa_flash.cu", "sdpa_decode.cu", "qdense_ggml.cu", "qdense_ggml_mma.cu", "qdense_w4.cu", "helper_ops.cu", "fused_small.cu", "elementwise.cu", "graph.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-DCB_BUILDING"]

@@ -87,6 +87,7 @@ struct cb_plan {
   size_t counter_bytes = 0;       // leading region of the workspace zeroed by prepare
   int blocks = 0, threads = 0, dyn_smem = 0;
   bool has_status = false;        // kernel keeps a status word at workspace offset 0
+  bool w4_stream = false;         // quantized dense on packed 4-bit weights: the streaming decode kernel, not the generic one
   bool whole_tiles = false;       // decode tensor-core plan: every CTA takes whole column tiles (nothing is split or parked)
   std::string name;
   cb_qdense_desc qd{};
@@ -116,6 +117,9 @@ int fused_small_launch(const cb_plan* p, const void* const* in, void* const* out
 int elementwise_plan(cb_plan* p);
 int qdense_ggml_plan(cb_plan* p);
 int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
+bool qdense_w4_supports(const cb_qdense_desc& d);
+void qdense_w4_plan(cb_plan* p);
+int qdense_w4_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);
 bool qdense_ggml_mma_supports(const cb_qdense_desc& d);
 void qdense_ggml_mma_plan(cb_plan* p, const char* type_name);
 int qdense_ggml_mma_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s);

@@ -695,6 +695,11 @@ int qdense_plan(cb_plan* p) {
   if (variant == CB_QDENSE_PREFILL) return qdense_prefill_plan(p);
   if (variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_plan(p);
 
+  if (variant == CB_QDENSE_GENERIC && qdense_w4_supports(d)) {   // decode shapes of the packed 4-bit formats
+    p->w4_stream = true;
+    qdense_w4_plan(p);
+    return CB_OK;
+  }
   if (variant == CB_QDENSE_GENERIC) {
     p->blocks = (int)(((d.N + QG_COLS - 1) / QG_COLS) * ((d.M + QG_ROWS - 1) / QG_ROWS));
     p->threads = QG_COLS;
@@ -785,6 +790,7 @@ static int launch_decode(const cb_plan* p, const void* const* in, void* const* o
 int qdense_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   if (d.scheme == CB_QUANT_GGML) return qdense_ggml_launch(p, in, out, ws, s);
+  if (p->w4_stream) return qdense_w4_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_MMA) return launch_decode(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_PREFILL) return qdense_prefill_launch(p, in, out, ws, s);
   if (p->variant == CB_QDENSE_DECODE_TC) return qdense_decode_tc_launch(p, in, out, ws, s);

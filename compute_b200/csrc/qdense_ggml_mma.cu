@@ -38,6 +38,7 @@ constexpr int GM_STEP = 256;                // values per ring stage and row
 constexpr int GM_STAGES = 3;
 constexpr int GM_MAX_COLS = 48;             // 3 digit planes x 16 rows of x
 constexpr int GM_BAR_BYTES = 256;           // the stages' barriers (8 warps x 3) and the digits' one
+static_assert((GM_WARPS * GM_STAGES + 1) * 8 <= GM_BAR_BYTES, "barrier area");
 constexpr int GM_DPAD = 32;                 // bytes between two columns of digits in shared memory, past K
 // A CTA asks for at least this much shared memory, so that no more than two fit an SM.  With three, the CTAs of the
 // next launch of a decode loop (scheduled early, as dependents) settle beside the running ones and both slow down:

@@ -1,0 +1,248 @@
+// Packed 4-bit weights (Int4 / Uint4 Linear, NF4) for decode shapes: M <= 16, reference scales [K, N / block].
+// Reference arithmetic: internal/gobackend/fusedops/quantizeddense.go:586-650 (per output column, k ascending:
+// x * w * scale, or x * (w * scale + zero point)); nibble order internal/gobackend/ops/convertdtype.go:199-226.
+//
+// The weights are read once, as they lie: element (k, n) is nibble n & 1 of byte (k N + n) / 2, so a row of W is N / 2
+// contiguous bytes and a lane that reads one 32-bit word holds eight neighbouring columns of one k.  The scale of a
+// row belongs to (k, n / block): with block a multiple of 8 it is one float for the lane's word, multiplied into x
+// instead of into eight weights.  Every lane keeps the sums of its eight columns for up to eight rows of x in
+// registers; the rows of W go round the eight warps of a CTA, and the K range is cut over gridDim.z CTAs, so that
+// three to four CTAs fill every SM.  Partial sums meet in shared memory (fixed order), then in a workspace
+// [cut][M][N]; a second small kernel adds the cuts in order, the bias and the activation.
+//
+// A nibble becomes a float without a conversion: its four bits go to the top of the mantissa of 1.0, which is
+// 1 + n / 16 (for Int4 the nibble's top bit is flipped first: n ^ 8 = n + 8).  The sums run over those floats and the
+// sum of the scaled x is kept beside them: sum x s n = 16 (sum x s f - sum x s), and - 8 sum x s for Int4.
+#include "common.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <string>
+
+namespace cb {
+namespace {
+
+constexpr int W4_WARPS = 8;
+constexpr int W4_COLS = 256;               // columns per CTA: 32 lanes x 8
+__host__ __device__ constexpr int w4_unroll(int mr) { return mr >= 8 ? 4 : 8; }   // rows of W a lane has in flight
+enum { W4_U4 = 0, W4_I4 = 1, W4_NF4 = 2 };
+
+// NormalFloat4 (fused_ops.go:114-121)
+__constant__ float kW4Nf4[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+template <int MODE>
+__device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut) {
+  if (MODE == W4_NF4) return lut[(word >> (4 * i)) & 0xFu];
+  const uint32_t at19 = 4 * i <= 19 ? word << (19 - 4 * i) : word >> (4 * i - 19);
+  return __uint_as_float((at19 & 0x00780000u) ^ (MODE == W4_I4 ? 0x3FC00000u : 0x3F800000u));
+}
+
+// grid (row tiles of x, column tiles, cuts of K); partial [gridDim.z][M][N]
+template <typename XT, int MODE, int MR, bool ZP>
+__global__ void __launch_bounds__(W4_WARPS * 32, MR >= 4 ? 2 : 3)
+qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const float* __restrict__ scales, const float* __restrict__ zps,
+                 float* __restrict__ partial, int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_per_cta) {
+  constexpr int W4_UNROLL = w4_unroll(MR);
+  extern __shared__ __align__(16) unsigned char w4_smem[];
+  float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_per_cta]
+  float* red = xs + (size_t)MR * rows_per_cta;                                 // [W4_WARPS][MR][W4_COLS]
+  __shared__ float lut[16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int m0 = blockIdx.x * MR;
+  const int64_t k0 = (int64_t)blockIdx.z * rows_per_cta;
+  const int kc = (int)min((int64_t)rows_per_cta, K - k0);                      // rows of this cut
+  const int64_t n0 = (int64_t)blockIdx.y * W4_COLS + lane * 8;
+  const bool active = n0 < N;
+  if (MODE == W4_NF4 && threadIdx.x < 16) lut[threadIdx.x] = kW4Nf4[threadIdx.x];
+  for (int idx = threadIdx.x; idx < MR * rows_per_cta; idx += W4_WARPS * 32) {
+    const int m = idx / rows_per_cta, kk = idx % rows_per_cta;
+    xs[idx] = (m0 + m < M && kk < kc) ? (float)Scalar<XT>::load(x, (int64_t)(m0 + m) * K + k0 + kk) : 0.0f;
+  }
+  __syncthreads();
+
+  float acc[MR][8], sx[MR], zacc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; m++) {
+    sx[m] = 0.0f; zacc[m] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[m][i] = 0.0f;
+  }
+  if (active) {
+    const int64_t wrow = N / 8;                                                // words per row of W
+    const uint32_t* wp = w + k0 * wrow + n0 / 8;
+    const float* sp = scales + k0 * nblk + n0 / block;
+    const float* zp = ZP ? zps + k0 * nblk + n0 / block : nullptr;
+    // rows kk = warp, warp + 8, ...: W4_UNROLL of them requested together
+    for (int kb = warp; kb < kc; kb += W4_WARPS * W4_UNROLL) {
+      uint32_t wv[W4_UNROLL];
+      float sv[W4_UNROLL], zv[W4_UNROLL];
+#pragma unroll
+      for (int u = 0; u < W4_UNROLL; u++) {
+        const int kk = kb + u * W4_WARPS;
+        const bool in = kk < kc;
+        wv[u] = in ? __ldg(wp + (int64_t)kk * wrow) : 0u;
+        sv[u] = in ? __ldg(sp + (int64_t)kk * nblk) : 0.0f;
+        zv[u] = (ZP && in) ? __ldg(zp + (int64_t)kk * nblk) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < W4_UNROLL; u++) {
+        const int kk = kb + u * W4_WARPS;
+        const bool in = kk < kc;                                               // rows past the cut add nothing
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = w4_value<MODE>(wv[u], i, lut);
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+          const float xv = in ? xs[m * rows_per_cta + kk] : 0.0f;
+          const float xsv = xv * sv[u];
+          if (MODE != W4_NF4) sx[m] += xsv;
+          if (ZP) zacc[m] = fmaf(xv, zv[u], zacc[m]);
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[m][i] = fmaf(xsv, f[i], acc[m][i]);
+        }
+      }
+    }
+  }
+  // ---- the eight warps' sums, added in warp order
+#pragma unroll
+  for (int m = 0; m < MR; m++) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      // Uint4: n = 16 (f - 1); Int4: n = 16 (f - 1) - 8, f built from the nibble with its top bit flipped
+      v[i] = MODE == W4_NF4 ? acc[m][i] : MODE == W4_U4 ? 16.0f * (acc[m][i] - sx[m]) : fmaf(16.0f, acc[m][i], -24.0f * sx[m]);
+      v[i] += zacc[m];
+    }
+    float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * MR + m) * W4_COLS + lane * 8);
+    dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+    dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  __syncthreads();
+  const int64_t n = (int64_t)blockIdx.y * W4_COLS + threadIdx.x;
+  if (n < N) {
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      if (m0 + m >= M) break;
+      float v = 0.0f;
+#pragma unroll
+      for (int wq = 0; wq < W4_WARPS; wq++) v += red[((size_t)wq * MR + m) * W4_COLS + threadIdx.x];
+      partial[((int64_t)blockIdx.z * M + m0 + m) * N + n] = v;
+    }
+  }
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(256)
+qdense_w4_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, XT* __restrict__ out, int64_t MN, int64_t N, int cuts, int act) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= MN) return;
+  float v = 0.0f;
+  for (int c = 0; c < cuts; c++) v += __ldcg(partial + (int64_t)c * MN + i);
+  if (bias) v = __fadd_rn(v, bias[i % N]);
+  Scalar<XT>::store(out, i, apply_activation(v, act));
+}
+
+int w4_rows(const cb_qdense_desc& d) { return d.M <= 1 ? 1 : d.M <= 2 ? 2 : d.M <= 4 ? 4 : 8; }
+
+// how K is cut: enough CTAs for four per SM, at least 64 rows each, whole groups of eight rows
+void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_per_cta) {
+  const int mr = w4_rows(d);
+  const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS);
+  long long want = (4LL * std::max(n_sm, 1) + tiles - 1) / tiles;
+  want = std::max(1LL, std::min(want, (long long)((d.K + 63) / 64)));
+  long long rows = (d.K + want - 1) / want;
+  rows = (rows + W4_WARPS - 1) / W4_WARPS * W4_WARPS;
+  *rows_per_cta = (int)rows;
+  *cuts = (int)((d.K + rows - 1) / rows);
+}
+
+size_t w4_smem_bytes(int mr, int rows_per_cta) { return ((size_t)mr * rows_per_cta + (size_t)W4_WARPS * mr * W4_COLS) * sizeof(float); }
+
+template <typename XT, int MODE, int MR, bool ZP>
+int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const cb_qdense_desc& d = p->qd;
+  int cuts = 0, rows = 0;
+  w4_cuts(d, p->n_sm, &cuts, &rows);
+  const size_t smem = w4_smem_bytes(MR, rows);
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  CB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    CB_CUDA(cudaFuncSetAttribute(qdense_w4_kernel<XT, MODE, MR, ZP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    if (dev < 64) configured[dev].store(true, std::memory_order_release);
+  }
+  int idx = 3;
+  const float* zp = d.has_zero_point ? (const float*)in[idx++] : nullptr;
+  const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
+  const int64_t nblk = (d.N + d.block_size - 1) / d.block_size;
+  dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + W4_COLS - 1) / W4_COLS), (unsigned)cuts);
+  qdense_w4_kernel<XT, MODE, MR, ZP><<<grid, W4_WARPS * 32, smem, s>>>((const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, (float*)ws,
+                                                                    (int)d.M, d.K, d.N, d.block_size, nblk, rows);
+  CB_CUDA(cudaGetLastError());
+  const int64_t mn = d.M * d.N;
+  qdense_w4_finish_kernel<XT><<<(unsigned)((mn + 255) / 256), 256, 0, s>>>((const float*)ws, bias, (XT*)out[0], mn, d.N, cuts, d.activation);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
+template <typename XT, int MODE, bool ZP>
+int w4_launch_m(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  switch (w4_rows(p->qd)) {
+    case 1: return w4_launch_k<XT, MODE, 1, ZP>(p, in, out, ws, s);
+    case 2: return w4_launch_k<XT, MODE, 2, ZP>(p, in, out, ws, s);
+    case 4: return w4_launch_k<XT, MODE, 4, ZP>(p, in, out, ws, s);
+    default: return w4_launch_k<XT, MODE, 8, ZP>(p, in, out, ws, s);
+  }
+}
+
+template <typename XT>
+int w4_launch_t(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const cb_qdense_desc& d = p->qd;
+  if (d.scheme == CB_QUANT_NF4) return w4_launch_m<XT, W4_NF4, false>(p, in, out, ws, s);
+  if (d.w_dtype == CB_I4) return d.has_zero_point ? w4_launch_m<XT, W4_I4, true>(p, in, out, ws, s) : w4_launch_m<XT, W4_I4, false>(p, in, out, ws, s);
+  return d.has_zero_point ? w4_launch_m<XT, W4_U4, true>(p, in, out, ws, s) : w4_launch_m<XT, W4_U4, false>(p, in, out, ws, s);
+}
+
+}  // namespace
+
+// Decode shapes of the packed 4-bit formats with the reference's scale layout.  The generic kernel keeps everything
+// else, and these too when the plan asks for it by name (it sums in the reference's order).
+bool qdense_w4_supports(const cb_qdense_desc& d) {
+  if (d.variant != CB_QDENSE_AUTO) return false;
+  if (d.w_dtype != CB_I4 && d.w_dtype != CB_U4) return false;
+  if (d.scheme != CB_QUANT_LINEAR && d.scheme != CB_QUANT_NF4) return false;
+  if (d.scale_layout != CB_SCALE_REF || d.block_size < 8 || d.block_size % 8 != 0) return false;
+  if (d.gather_ranks > 1) return false;
+  // below a few hundred thousand weights the launch of a second kernel costs more than the generic kernel's loop
+  return d.M >= 1 && d.M <= 16 && d.N >= 8 && d.N % 8 == 0 && d.K >= 64 && d.K * d.N >= (1 << 18) && d.K < (1LL << 31) && d.N < (1LL << 31);
+}
+
+void qdense_w4_plan(cb_plan* p) {
+  const cb_qdense_desc& d = p->qd;
+  int cuts = 0, rows = 0;
+  w4_cuts(d, p->n_sm, &cuts, &rows);
+  const int mr = w4_rows(d);
+  p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS) * cuts);
+  p->threads = W4_WARPS * 32;
+  p->dyn_smem = (int)w4_smem_bytes(mr, rows);
+  p->workspace_bytes = (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
+  p->counter_bytes = 0;
+  p->has_status = false;
+  p->name = std::string("qdense_w4_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (d.w_dtype == CB_U4 ? "_u4" : "_i4") +
+            (d.scheme == CB_QUANT_NF4 ? "_nf4" : "");
+}
+
+int qdense_w4_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const cb_qdense_desc& d = p->qd;
+  if (d.M == 0 || d.N == 0) return CB_OK;
+  if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (packed 4-bit): the plan needs its workspace (partial sums of the cuts of K)");
+  if ((reinterpret_cast<uintptr_t>(in[1]) & 3) || (reinterpret_cast<uintptr_t>(in[2]) & 3))
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (packed 4-bit): weights and scales must be 4-byte aligned");
+  return d.x_dtype == CB_BF16 ? w4_launch_t<__nv_bfloat16>(p, in, out, ws, s) : w4_launch_t<float>(p, in, out, ws, s);
+}
+
+}  // namespace cb

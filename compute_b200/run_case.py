@@ -136,6 +136,7 @@ def main() -> None:
                     plan.launch([x.ptr, wg.ptr], [y.ptr], ws.ptr if ws else None, stream)
             e1.record(stream)
             stream.sync()
+            plan.check_status(ws.ptr if ws else None)
             us = e0.elapsed_ms(e1) * 1e3 / (a.reps * a.layers)
             out.update(kernel=plan.kernel_name, blocks=plan.blocks, us=us, weight_GBps=blocks.nbytes / us / 1e3,
                        tflops=2.0 * a.m * K * N / us / 1e6)

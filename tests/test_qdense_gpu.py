@@ -105,6 +105,52 @@ def test_generic_nf4_bit_exact(w_kind):
     assert np.array_equal(got0, orc.qdense_nf4(x, idx.astype(np.uint8), s, b, block, orc.ACT_NONE))
 
 
+@pytest.mark.parametrize("kind", ["i4", "u4", "nf4_u4", "nf4_i4"])
+@pytest.mark.parametrize("M,K,N,block,x_dtype", [(1, 4096, 14336, 64, "f32"), (5, 520, 520, 8, "f32"), (16, 1024, 264, 24, "bf16"),
+                                                 (2, 300, 1000, 40, "f32"), (9, 2048, 136, 136, "f32")])
+def test_packed_4bit_decode_shapes(kind, M, K, N, block, x_dtype):
+    """Decode shapes of the packed 4-bit formats run on the streaming kernel: one, two, four and eight rows of x per
+    thread (and two row tiles), K cut over CTAs with a ragged last cut, ragged column tiles, every block size that is
+    a multiple of 8, zero points, bias and activation, float32 and bfloat16 x."""
+    rng = np.random.default_rng(M * 1000 + N)
+    nf4 = kind.startswith("nf4")
+    signed = kind.endswith("i4")
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if M >= 5:
+        x[1] = 0.0
+        x[2] *= 100.0
+    vals = rng.integers(0, 16, size=(K, N))
+    packed = orc.pack_nibbles(vals)
+    nblk = -(-N // block)
+    s = rng.uniform(0.01, 0.2, size=(K, nblk)).astype(np.float32)
+    zp = None if nf4 else rng.uniform(-0.05, 0.05, size=s.shape).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    xw = orc.bf16_to_f32(xin) if x_dtype == "bf16" else x
+    tol = BF16_TOL if x_dtype == "bf16" else F32_TOL
+    for z in ((None,) if nf4 else (None, zp)):
+        if nf4:
+            want = orc.qdense_nf4(xw, vals.astype(np.uint8), s, b, block, orc.ACT_GELU)
+        else:
+            w8 = np.where(vals >= 8, vals - 16, vals) if signed else vals
+            want = orc.qdense_linear(xw, w8.astype(np.int8 if signed else np.uint8), s, z, b, block, orc.ACT_GELU)
+        got, plan = ops.quantized_dense(xin, packed, s, z, b, x_dtype=code, block_size=block, activation=dv.ACT_GELU,
+                                        scheme=dv.QUANT_NF4 if nf4 else dv.QUANT_LINEAR, packed=(dv.I4 if signed else dv.U4, N),
+                                        return_plan=True)
+        assert plan.kernel_name == f"qdense_w4_{x_dtype}_{'i4' if signed else 'u4'}{'_nf4' if nf4 else ''}" and plan.workspace_bytes > 0
+        gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+        for m in range(M):
+            assert max_abs_normalised(gotf[m], want[m]) < tol, (m, z is not None)
+        # the generic kernel, by name, on the same case
+        got_g, plan_g = ops.quantized_dense(xin, packed, s, z, b, x_dtype=code, block_size=block, activation=dv.ACT_GELU,
+                                            scheme=dv.QUANT_NF4 if nf4 else dv.QUANT_LINEAR, packed=(dv.I4 if signed else dv.U4, N),
+                                            variant=dv.QDENSE_GENERIC, return_plan=True)
+        assert plan_g.kernel_name.startswith("qdense_generic_")
+        if M * K * N > 2 ** 24:
+            break                                  # the generic kernel needs milliseconds per call on the full projection
+
+
 def test_nf4_and_packed_validation():
     with pytest.raises(BackendError) as e:
         dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, has_zero_point=True, scheme=dv.QUANT_NF4)
