@@ -17,6 +17,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstring>
 #include <string>
 
 namespace cb {
@@ -41,25 +42,32 @@ __device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut
   return __uint_as_float((at19 & 0x00780000u) ^ (MODE == W4_I4 ? 0x3FC00000u : 0x3F800000u));
 }
 
-// grid (row tiles of x, column tiles, cuts of K); partial [gridDim.z][M][N]
-template <typename XT, int MODE, int MR, bool ZP>
-__global__ void __launch_bounds__(W4_WARPS * 32, MR >= 4 ? 2 : 3)
+// grid (row tiles of x, column tiles, cuts of K); partial [gridDim.z][M][N].  K is counted in groups of 8 warps x
+// W4_UNROLL rows; cut z takes groups [z G / cuts, (z + 1) G / cuts).  TAIL: K is not a whole number of groups, so the
+// rows of the last group are checked one by one.
+template <typename XT, int MODE, int MR, bool ZP, bool TAIL>
+__global__ void __launch_bounds__(W4_WARPS * 32, MR >= 2 ? 2 : 3)
 qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const float* __restrict__ scales, const float* __restrict__ zps,
-                 float* __restrict__ partial, int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_per_cta) {
-  constexpr int W4_UNROLL = w4_unroll(MR);
+                 float* __restrict__ partial, int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
+  constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL;
+  // the kernel that adds the cuts may be scheduled now; it waits for this grid before it reads the partial sums
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(16) unsigned char w4_smem[];
-  float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_per_cta]
-  float* red = xs + (size_t)MR * rows_per_cta;                                 // [W4_WARPS][MR][W4_COLS]
+  float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_max]
+  float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][W4_COLS]
   __shared__ float lut[16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int m0 = blockIdx.x * MR;
-  const int64_t k0 = (int64_t)blockIdx.z * rows_per_cta;
-  const int kc = (int)min((int64_t)rows_per_cta, K - k0);                      // rows of this cut
+  const int64_t G = (K + GROUP - 1) / GROUP;
+  const int64_t g0 = (int64_t)blockIdx.z * G / gridDim.z, g1 = ((int64_t)blockIdx.z + 1) * G / gridDim.z;
+  const int64_t k0 = g0 * GROUP;
+  const int kc = (int)(min(K, g1 * GROUP) - k0);                               // rows of this cut
+  const int n_groups = (int)(g1 - g0);
   const int64_t n0 = (int64_t)blockIdx.y * W4_COLS + lane * 8;
   const bool active = n0 < N;
   if (MODE == W4_NF4 && threadIdx.x < 16) lut[threadIdx.x] = kW4Nf4[threadIdx.x];
-  for (int idx = threadIdx.x; idx < MR * rows_per_cta; idx += W4_WARPS * 32) {
-    const int m = idx / rows_per_cta, kk = idx % rows_per_cta;
+  for (int idx = threadIdx.x; idx < MR * rows_max; idx += W4_WARPS * 32) {
+    const int m = idx / rows_max, kk = idx % rows_max;
     xs[idx] = (m0 + m < M && kk < kc) ? (float)Scalar<XT>::load(x, (int64_t)(m0 + m) * K + k0 + kk) : 0.0f;
   }
   __syncthreads();
@@ -71,33 +79,42 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[m][i] = 0.0f;
   }
-  if (active) {
+  if (active && n_groups > 0) {
     const int64_t wrow = N / 8;                                                // words per row of W
-    const uint32_t* wp = w + k0 * wrow + n0 / 8;
-    const float* sp = scales + k0 * nblk + n0 / block;
-    const float* zp = ZP ? zps + k0 * nblk + n0 / block : nullptr;
-    // rows kk = warp, warp + 8, ...: W4_UNROLL of them requested together
-    for (int kb = warp; kb < kc; kb += W4_WARPS * W4_UNROLL) {
+    // this warp's rows of a group: warp, warp + 8, ...; the next group is requested before this one is consumed
+    const uint32_t* wq = w + (k0 + warp) * wrow + n0 / 8;
+    const float* sq = scales + (k0 + warp) * nblk + n0 / block;
+    const float* zq = ZP ? zps + (k0 + warp) * nblk + n0 / block : nullptr;
+    const int64_t w8 = W4_WARPS * wrow, s8 = W4_WARPS * nblk;
+    uint32_t wn[W4_UNROLL];
+    float sn[W4_UNROLL], zn[W4_UNROLL];
+    auto request = [&](int g) {
+#pragma unroll
+      for (int u = 0; u < W4_UNROLL; u++) {
+        const bool in = !TAIL || g * GROUP + warp + u * W4_WARPS < kc;
+        wn[u] = in ? __ldg(wq + u * w8) : 0u;
+        sn[u] = in ? __ldg(sq + u * s8) : 0.0f;
+        zn[u] = (ZP && in) ? __ldg(zq + u * s8) : 0.0f;
+      }
+      wq += GROUP * wrow; sq += GROUP * nblk;
+      if (ZP) zq += GROUP * nblk;
+    };
+    request(0);
+    const float* xr = xs + warp;
+    for (int g = 0; g < n_groups; g++) {
       uint32_t wv[W4_UNROLL];
       float sv[W4_UNROLL], zv[W4_UNROLL];
 #pragma unroll
-      for (int u = 0; u < W4_UNROLL; u++) {
-        const int kk = kb + u * W4_WARPS;
-        const bool in = kk < kc;
-        wv[u] = in ? __ldg(wp + (int64_t)kk * wrow) : 0u;
-        sv[u] = in ? __ldg(sp + (int64_t)kk * nblk) : 0.0f;
-        zv[u] = (ZP && in) ? __ldg(zp + (int64_t)kk * nblk) : 0.0f;
-      }
+      for (int u = 0; u < W4_UNROLL; u++) { wv[u] = wn[u]; sv[u] = sn[u]; zv[u] = zn[u]; }
+      if (g + 1 < n_groups) request(g + 1);
 #pragma unroll
       for (int u = 0; u < W4_UNROLL; u++) {
-        const int kk = kb + u * W4_WARPS;
-        const bool in = kk < kc;                                               // rows past the cut add nothing
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) f[i] = w4_value<MODE>(wv[u], i, lut);
 #pragma unroll
         for (int m = 0; m < MR; m++) {
-          const float xv = in ? xs[m * rows_per_cta + kk] : 0.0f;
+          const float xv = xr[m * rows_max + u * W4_WARPS];                    // rows past K hold 0 here and scale 0
           const float xsv = xv * sv[u];
           if (MODE != W4_NF4) sx[m] += xsv;
           if (ZP) zacc[m] = fmaf(xv, zv[u], zacc[m]);
@@ -105,6 +122,7 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
           for (int i = 0; i < 8; i++) acc[m][i] = fmaf(xsv, f[i], acc[m][i]);
         }
       }
+      xr += GROUP;
     }
   }
   // ---- the eight warps' sums, added in warp order
@@ -138,6 +156,7 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
 template <typename XT>
 __global__ void __launch_bounds__(256)
 qdense_w4_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, XT* __restrict__ out, int64_t MN, int64_t N, int cuts, int act) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= MN) return;
   float v = 0.0f;
@@ -148,21 +167,31 @@ qdense_w4_finish_kernel(const float* __restrict__ partial, const float* __restri
 
 int w4_rows(const cb_qdense_desc& d) { return d.M <= 1 ? 1 : d.M <= 2 ? 2 : d.M <= 4 ? 4 : 8; }
 
-// how K is cut: enough CTAs for four per SM, at least 64 rows each, whole groups of eight rows
-void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_per_cta) {
+// How K is cut.  A CTA costs a fixed set-up and a reduction, so few long CTAs beat many short ones, but the CTAs must
+// fill whole waves: with `slots` CTAs resident on the GPU at once, the cut count that fills one wave best is taken when
+// it reaches 0.8 of the wave, otherwise the best of two waves.  Cuts are whole groups of rows, at least two per cut.
+void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   const int mr = w4_rows(d);
+  const int group = W4_WARPS * w4_unroll(mr);
+  const long long G = (d.K + group - 1) / group;
   const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS);
-  long long want = (4LL * std::max(n_sm, 1) + tiles - 1) / tiles;
-  want = std::max(1LL, std::min(want, (long long)((d.K + 63) / 64)));
-  long long rows = (d.K + want - 1) / want;
-  rows = (rows + W4_WARPS - 1) / W4_WARPS * W4_WARPS;
-  *rows_per_cta = (int)rows;
-  *cuts = (int)((d.K + rows - 1) / rows);
+  const long long slots = (long long)std::max(n_sm, 1) * (mr >= 2 ? 2 : 3);
+  const long long max_cuts = std::max(1LL, G / 2);
+  long long best = 1;
+  double best_fill = 0.0;
+  for (int waves = 1; waves <= 2 && best_fill < 0.8; waves++) {
+    for (long long c = 1; c <= max_cuts && tiles * c <= waves * slots; c++) {
+      const double fill = (double)(tiles * c) / (double)(waves * slots);
+      if (fill > best_fill) { best_fill = fill; best = c; }
+    }
+  }
+  *cuts = (int)best;
+  *rows_max = (int)(((G + best - 1) / best) * group);
 }
 
 size_t w4_smem_bytes(int mr, int rows_per_cta) { return ((size_t)mr * rows_per_cta + (size_t)W4_WARPS * mr * W4_COLS) * sizeof(float); }
 
-template <typename XT, int MODE, int MR, bool ZP>
+template <typename XT, int MODE, int MR, bool ZP, bool TAIL>
 int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   int cuts = 0, rows = 0;
@@ -172,7 +201,7 @@ int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void*
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    CB_CUDA(cudaFuncSetAttribute(qdense_w4_kernel<XT, MODE, MR, ZP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    CB_CUDA(cudaFuncSetAttribute(qdense_w4_kernel<XT, MODE, MR, ZP, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   int idx = 3;
@@ -180,23 +209,36 @@ int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void*
   const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
   const int64_t nblk = (d.N + d.block_size - 1) / d.block_size;
   dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + W4_COLS - 1) / W4_COLS), (unsigned)cuts);
-  qdense_w4_kernel<XT, MODE, MR, ZP><<<grid, W4_WARPS * 32, smem, s>>>((const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, (float*)ws,
+  qdense_w4_kernel<XT, MODE, MR, ZP, TAIL><<<grid, W4_WARPS * 32, smem, s>>>((const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, (float*)ws,
                                                                     (int)d.M, d.K, d.N, d.block_size, nblk, rows);
   CB_CUDA(cudaGetLastError());
   const int64_t mn = d.M * d.N;
-  qdense_w4_finish_kernel<XT><<<(unsigned)((mn + 255) / 256), 256, 0, s>>>((const float*)ws, bias, (XT*)out[0], mn, d.N, cuts, d.activation);
-  CB_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)((mn + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_w4_finish_kernel<XT>, (const float*)ws, bias, (XT*)out[0], mn, (int64_t)d.N, cuts, (int)d.activation));
   return CB_OK;
 }
 
 template <typename XT, int MODE, bool ZP>
 int w4_launch_m(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  switch (w4_rows(p->qd)) {
-    case 1: return w4_launch_k<XT, MODE, 1, ZP>(p, in, out, ws, s);
-    case 2: return w4_launch_k<XT, MODE, 2, ZP>(p, in, out, ws, s);
-    case 4: return w4_launch_k<XT, MODE, 4, ZP>(p, in, out, ws, s);
-    default: return w4_launch_k<XT, MODE, 8, ZP>(p, in, out, ws, s);
+  const int mr = w4_rows(p->qd);
+  const bool tail = p->qd.K % (W4_WARPS * w4_unroll(mr)) != 0;
+#define W4_GO(MR_) (tail ? w4_launch_k<XT, MODE, MR_, ZP, true>(p, in, out, ws, s) : w4_launch_k<XT, MODE, MR_, ZP, false>(p, in, out, ws, s))
+  switch (mr) {
+    case 1: return W4_GO(1);
+    case 2: return W4_GO(2);
+    case 4: return W4_GO(4);
+    default: return W4_GO(8);
   }
+#undef W4_GO
 }
 
 template <typename XT>

@@ -56,6 +56,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=1, help="qdense: this many independent projections as one grouped launch")
     ap.add_argument("--ggml", default="", choices=["", "q4_0", "q8_0", "iq4_nl", "q4_k", "q6_k"],
                     help="qdense: weights in this GGML block format instead of int8 with separate scales")
+    ap.add_argument("--packed4", default="", choices=["", "i4", "u4", "nf4"],
+                    help="qdense: packed 4-bit weights (Int4 / Uint4 Linear, or NF4 on Uint4) with the reference's [K, N / group] scales")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--layout", default="kgroup", choices=["channel", "kgroup"])
     ap.add_argument("--group", type=int, default=128)
@@ -116,6 +118,27 @@ def main() -> None:
         sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=rows * N).astype(np.float32), dev)
         y = dv.DeviceMem(a.m * N * (2 if a.dtype == "bf16" else 4), dev)
         layout = dv.SCALE_CHANNEL if a.layout == "channel" else dv.SCALE_KGROUP
+        if a.packed4:
+            nblk = -(-N // a.group)
+            scr = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=K * nblk).astype(np.float32), dev)
+            # --layers copies of the weights, one launch each in turn
+            wps = [dv.DeviceMem.from_numpy(rng.integers(0, 256, size=K * N // 2, dtype=np.uint8), dev) for _ in range(a.layers)]
+            plan = dv.Plan.qdense(a.m, K, N, code, dv.I4 if a.packed4 == "i4" else dv.U4, dv.SCALE_REF, a.group, activation=dv.ACT_SILU,
+                                  scheme=dv.QUANT_NF4 if a.packed4 == "nf4" else dv.QUANT_LINEAR, dev=dev)
+            ws = plan.new_workspace()
+            e0, e1 = dv.Event(dev), dv.Event(dev)
+            for it in range(a.reps + a.warmup):
+                if it == a.warmup:
+                    e0.record(stream)
+                for wp in wps:
+                    plan.launch([x.ptr, wp.ptr, scr.ptr], [y.ptr], ws.ptr if ws else None, stream)
+            e1.record(stream)
+            stream.sync()
+            us = e0.elapsed_ms(e1) * 1e3 / (a.reps * a.layers)
+            out.update(kernel=plan.kernel_name, blocks=plan.blocks, us=us, weight_GBps=(K * N / 2 + K * nblk * 4) / us / 1e3,
+                       tflops=2.0 * a.m * K * N / us / 1e6)
+            print(json.dumps(out))
+            return
         if a.ggml:
             # random block bytes with a finite half-precision scale in every block
             gt, values, bb, scale_at = {"q4_0": (dv.GGML_Q4_0, 32, 18, (0,)), "q8_0": (dv.GGML_Q8_0, 32, 34, (0,)),
