@@ -1030,9 +1030,10 @@ int cbg_fn_fused_quantized_dense(cbg_function* f, cbg_value* x, cbg_value* weigh
   if (weights->shape.dims.size() != 2 || weights->shape.dims[0] != K)
     return fail(CB_ERR_INVALID_ARG, "%s: weights must be [%lld, N], got %s", op, (long long)K, weights->shape.str().c_str());
   const int64_t N = weights->shape.dims[1];
-  // Int8 / Uint8, and for the Linear scheme the packed Int4 / Uint4 the reference unpacks first (quantizeddense.go:383-390)
+  // Int8 / Uint8, and the packed Int4 / Uint4 the reference unpacks first (quantizeddense.go:380-390; under NF4 the
+  // nibbles are table indices, :392-409)
   const int wd = weights->shape.dtype;
-  if (wd != CB_I8 && wd != CB_U8 && !(scheme == 0 && (wd == CB_I4 || wd == CB_U4)))
+  if (wd != CB_I8 && wd != CB_U8 && wd != CB_I4 && wd != CB_U4)
     return fail(CB_ERR_NOT_IMPLEMENTED, "%s: %s unsupported weight type %s", op, scheme == 1 ? "NF4" : "Linear", cb::dtype_name(wd));
   // NF4 uses a fixed lookup table and takes no zero points (quantizeddense.go:126-129)
   if (scheme == 1 && zero_point) return fail(CB_ERR_INVALID_ARG, "%s: ZeroPoint must be nil for NF4 quantization scheme", op);

@@ -275,7 +275,9 @@ int cb_plan_cols_bias(int dev, int32_t dtype, int64_t rows, int64_t total_cols, 
  *      builder.go:29-82; launched from Executable.Execute, executable.go:10-37) */
 int cb_plan_workspace_bytes(const cb_plan* plan, size_t* bytes);
 /* Scratch memory is caller-owned.  A freshly allocated workspace must be prepared once
- * (this zeroes the arrival counters some kernels keep in it); launches leave it prepared. */
+ * (this zeroes the arrival counters and status words some kernels keep in it); launches leave it prepared.
+ * Which plans need one is the plan's business (cb_plan_workspace_bytes): the decode kernels of the quantized dense
+ * op do - int8 on the tensor cores, GGML blocks on the integer tensor cores, packed 4-bit weights. */
 int cb_plan_prepare_workspace(const cb_plan* plan, void* workspace, cb_stream stream);
 const char* cb_plan_kernel_name(const cb_plan* plan);
 int cb_plan_grid(const cb_plan* plan, int* blocks, int* threads, int* dyn_smem_bytes);

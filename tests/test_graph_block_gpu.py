@@ -398,3 +398,54 @@ def test_repeated_execute_replays_a_cuda_graph():
         exe.Finalize()
         b.Finalize()
     assert all(np.array_equal(p, q) for p, q in zip(results[""], results["no_graphs"]))
+
+
+def test_packed_4bit_and_ggml_decode_kernels_in_a_replayed_graph():
+    """FusedQuantizedDense at decode shapes through the Backend API: packed Uint4 under NF4 runs on the streaming kernel,
+    Q4_K and Q8_0 on the integer tensor cores.  All need workspaces, are dependent launches, and two of them take a tensor
+    map in their parameters; from the second Execute on they are replayed from a captured CUDA graph.  Every call gives the
+    bits of the first, and the first agrees with the oracle."""
+    rng = np.random.default_rng(43)
+    M, K, N, block = 3, 512, 640, 64
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    idx = rng.integers(0, 16, size=(K, N))
+    packed = orc.pack_nibbles(idx)
+    s = rng.uniform(0.01, 0.2, size=(K, N // block)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    wq4k = orc.ggml_random_rows(rng, N, K, orc.GGML_Q4_K)
+    wq80 = orc.ggml_random_rows(rng, N, K, orc.GGML_Q8_0)
+    want = [orc.qdense_nf4(x, idx.astype(np.uint8), s, bias, block, orc.ACT_NONE),
+            orc.qdense_ggml(x, wq4k, bias, orc.GGML_Q4_K, orc.ACT_NONE),
+            orc.qdense_ggml(x, wq80, None, orc.GGML_Q8_0, orc.ACT_NONE)]
+    b = be.New("")
+    builder = b.Builder("w4_ggml")
+    f = builder.Main()
+    px = f.Parameter("x", be.make_shape(dv.F32, M, K))
+    pw = f.Parameter("w", be.make_shape(dv.U4, K, N))
+    ps = f.Parameter("s", be.make_shape(dv.F32, K, N // block))
+    pb = f.Parameter("b", be.make_shape(dv.F32, N))
+    pk = f.Parameter("wk", be.make_shape(dv.U8, *wq4k.shape))
+    p8 = f.Parameter("w8", be.make_shape(dv.U8, *wq80.shape))
+    y0 = f.FusedQuantizedDense(px, pw, pb, be.Quantization(be.QUANT_NF4, ps, None, 1, block), dv.ACT_NONE)
+    y1 = f.FusedQuantizedDense(px, pk, pb, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q4_K), dv.ACT_NONE)
+    y2 = f.FusedQuantizedDense(px, p8, None, be.Quantization(be.QUANT_GGML, GGMLType=orc.GGML_Q8_0), dv.ACT_NONE)
+    f.Return([y0, y1, y2])
+    exe = builder.Compile()
+    bufs = [b.BufferFromFlatData(0, x, be.make_shape(dv.F32, M, K)), b.BufferFromFlatData(0, packed, be.make_shape(dv.U4, K, N)),
+            b.BufferFromFlatData(0, s, be.make_shape(dv.F32, *s.shape)), b.BufferFromFlatData(0, bias, be.make_shape(dv.F32, N)),
+            b.BufferFromFlatData(0, wq4k, be.make_shape(dv.U8, *wq4k.shape)), b.BufferFromFlatData(0, wq80, be.make_shape(dv.U8, *wq80.shape))]
+    outs = []
+    for _ in range(4):
+        res = exe.Execute(bufs, None, 0)
+        outs.append([r.ToNumpy() for r in res])
+        for r in res:
+            r.Finalize()
+    assert exe.GraphReplays() == 3
+    for got, w in zip(outs[0], want):
+        assert max_abs_normalised(got, w) < 1e-4
+    for o in outs[1:]:
+        assert all(np.array_equal(p, q) for p, q in zip(o, outs[0]))
+    for t in bufs:
+        t.Finalize()
+    exe.Finalize()
+    b.Finalize()
