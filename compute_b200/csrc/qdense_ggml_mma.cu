@@ -15,7 +15,7 @@
 // values 8t..8t+7 of the block, for the weights and for the digits alike), so every operand fragment is eight
 // contiguous bytes.
 //
-// A CTA owns 64 weight rows: warps 0-3 take 16 rows each over the first half of K, warps 4-7 the same rows over the second
+// A CTA owns up to 64 weight rows: warps 0-3 take 16 rows each over the first half of K, warps 4-7 the same rows over the second
 // half; every warp streams its rows through a private three-stage ring of 256-value steps, each stage one TMA tile
 // (16 rows x the step's bytes) announced on the warp's own mbarrier.  At the end the halves and the digit planes are
 // combined through shared memory, bias and activation applied, results stored.  Every wait is bounded: a stage that does
@@ -44,6 +44,12 @@ constexpr int GM_DPAD = 32;                 // bytes between two columns of digi
 // next launch of a decode loop (scheduled early, as dependents) settle beside the running ones and both slow down:
 // IQ4_NL at M = 4 took 28 us with the floor and 49 us without.
 constexpr size_t GM_SMEM_FLOOR = 78 * 1024;
+// CTAs of a launch: two per SM when W has the row groups for it, never more than four groups per CTA.  With the fixed
+// 64 rows per CTA that this replaces, 14336 rows gave 224 CTAs: 76 SMs with two and 72 with one.
+__host__ inline int gm_grid(int64_t N, int n_sm) {
+  const int64_t G = (N + 15) / 16;
+  return (int)std::max((G + 3) / 4, std::min<int64_t>(2 * (int64_t)std::max(n_sm, 1), G));
+}
 constexpr size_t GM_SMEM_CTA = 112 * 1024;  // what a CTA may use while two still fit an SM (227 KB, 1 KB reserved per CTA)
 
 __host__ __device__ constexpr int gm_block_bytes(int t) { return t == CB_GGML_Q8_0 ? 34 : t == CB_GGML_Q4_K ? 144 : 18; }
@@ -206,10 +212,16 @@ ggml_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __rest
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int half = warp >> 2;                                  // which half of K
-  const int64_t row0 = (int64_t)blockIdx.x * GM_ROWS + (warp & 3) * 16;
+  // The 16-row groups of W are dealt out evenly: CTA b takes groups [b G / grid, (b + 1) G / grid), at most four (the
+  // host sizes the grid so); warp pairs without a group only take part in the barriers.
+  const int64_t G = (N + 15) / 16;
+  const int64_t g_begin = (int64_t)blockIdx.x * G / gridDim.x;
+  const int n_groups = (int)(((int64_t)blockIdx.x + 1) * G / gridDim.x - g_begin);
+  const int64_t row_base = g_begin * 16;
+  const int64_t row0 = row_base + (warp & 3) * 16;
   const int64_t steps_all = K / GM_STEP;
   const int64_t step0 = half == 0 ? 0 : (steps_all + 1) / 2, step1 = half == 0 ? (steps_all + 1) / 2 : steps_all;
-  const int n_steps = (int)(step1 - step0);
+  const int n_steps = (warp & 3) < n_groups ? (int)(step1 - step0) : 0;
   unsigned char* ring = gm_smem + warp * GM_STAGES * STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + warp * GM_STAGES;
   uint64_t* bar_digits = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + GM_WARPS * GM_STAGES;
@@ -412,8 +424,8 @@ ggml_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __rest
   __syncthreads();
   for (int idx = threadIdx.x; idx < GM_ROWS * M; idx += GM_WARPS * 32) {
     const int m = idx / GM_ROWS, r = idx % GM_ROWS;            // consecutive threads write consecutive columns of out
-    const int64_t n = (int64_t)blockIdx.x * GM_ROWS + r;
-    if (n >= N) continue;
+    const int64_t n = row_base + r;
+    if (r >= 16 * n_groups || n >= N) continue;
     float v = 0.0f;
 #pragma unroll
     for (int pl = 2; pl >= 0; pl--) {                          // smallest plane last: unit * (A0 + 128 A1 + 16384 A2)
@@ -491,7 +503,7 @@ int gm_launch_pdl(K_ kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s,
 }
 
 template <typename XT, int GGML, int NT, bool BSMEM>
-int gm_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+int gm_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   static std::atomic<bool> configured[64];
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));
@@ -511,31 +523,31 @@ int gm_launch_k(const cb_qdense_desc& d, const void* const* in, void* const* out
                          digits, GGML == CB_GGML_Q4_K ? dsum : (float*)nullptr, units);
   if (rc != CB_OK) return rc;
   const float* bias = d.has_bias ? (const float*)in[2] : nullptr;
-  return gm_launch_pdl(ggml_mma_kernel<XT, GGML, NT, BSMEM>, dim3((unsigned)((d.N + GM_ROWS - 1) / GM_ROWS)), dim3(GM_WARPS * 32), smem, s,
+  return gm_launch_pdl(ggml_mma_kernel<XT, GGML, NT, BSMEM>, dim3((unsigned)gm_grid(d.N, n_sm)), dim3(GM_WARPS * 32), smem, s,
                        tmap, (const int8_t*)digits, (const float*)dsum, (const float*)units, bias, (XT*)out[0], (int)d.M,
                        (int64_t)d.K, (int64_t)d.N, (int)d.activation, (unsigned*)w8);
 }
 
 template <typename XT, int GGML>
-int gm_launch_n(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+int gm_launch_n(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const bool resident = gm_digits_resident(GGML, d.M, d.K);
   switch (gm_tiles((int)d.M)) {
-    case 1: return resident ? gm_launch_k<XT, GGML, 1, true>(d, in, out, ws, s) : gm_launch_k<XT, GGML, 1, false>(d, in, out, ws, s);
-    case 2: return resident ? gm_launch_k<XT, GGML, 2, true>(d, in, out, ws, s) : gm_launch_k<XT, GGML, 2, false>(d, in, out, ws, s);
-    case 3: return gm_launch_k<XT, GGML, 3, false>(d, in, out, ws, s);
-    case 4: return gm_launch_k<XT, GGML, 4, false>(d, in, out, ws, s);
-    case 5: return gm_launch_k<XT, GGML, 5, false>(d, in, out, ws, s);
-    default: return gm_launch_k<XT, GGML, 6, false>(d, in, out, ws, s);
+    case 1: return resident ? gm_launch_k<XT, GGML, 1, true>(d, n_sm, in, out, ws, s) : gm_launch_k<XT, GGML, 1, false>(d, n_sm, in, out, ws, s);
+    case 2: return resident ? gm_launch_k<XT, GGML, 2, true>(d, n_sm, in, out, ws, s) : gm_launch_k<XT, GGML, 2, false>(d, n_sm, in, out, ws, s);
+    case 3: return gm_launch_k<XT, GGML, 3, false>(d, n_sm, in, out, ws, s);
+    case 4: return gm_launch_k<XT, GGML, 4, false>(d, n_sm, in, out, ws, s);
+    case 5: return gm_launch_k<XT, GGML, 5, false>(d, n_sm, in, out, ws, s);
+    default: return gm_launch_k<XT, GGML, 6, false>(d, n_sm, in, out, ws, s);
   }
 }
 
 template <typename XT>
-int gm_launch_t(const cb_qdense_desc& d, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+int gm_launch_t(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   switch (d.ggml_type) {
-    case CB_GGML_Q4_0: return gm_launch_n<XT, CB_GGML_Q4_0>(d, in, out, ws, s);
-    case CB_GGML_Q8_0: return gm_launch_n<XT, CB_GGML_Q8_0>(d, in, out, ws, s);
-    case CB_GGML_IQ4_NL: return gm_launch_n<XT, CB_GGML_IQ4_NL>(d, in, out, ws, s);
-    default: return gm_launch_n<XT, CB_GGML_Q4_K>(d, in, out, ws, s);
+    case CB_GGML_Q4_0: return gm_launch_n<XT, CB_GGML_Q4_0>(d, n_sm, in, out, ws, s);
+    case CB_GGML_Q8_0: return gm_launch_n<XT, CB_GGML_Q8_0>(d, n_sm, in, out, ws, s);
+    case CB_GGML_IQ4_NL: return gm_launch_n<XT, CB_GGML_IQ4_NL>(d, n_sm, in, out, ws, s);
+    default: return gm_launch_n<XT, CB_GGML_Q4_K>(d, n_sm, in, out, ws, s);
   }
 }
 
@@ -549,7 +561,7 @@ bool qdense_ggml_mma_supports(const cb_qdense_desc& d) {
 
 void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {
   const cb_qdense_desc& d = p->qd;
-  p->blocks = (int)((d.N + GM_ROWS - 1) / GM_ROWS);
+  p->blocks = gm_grid(d.N, p->n_sm);
   p->threads = GM_WARPS * 32;
   p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)d.M) <= 2 && gm_digits_resident(d.ggml_type, d.M, d.K) ? gm_digit_smem(d.M, d.K) : 0),
                               GM_SMEM_FLOOR);
@@ -561,7 +573,7 @@ void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {
 
 int qdense_ggml_mma_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
-  return d.x_dtype == CB_BF16 ? gm_launch_t<__nv_bfloat16>(d, in, out, ws, s) : gm_launch_t<float>(d, in, out, ws, s);
+  return d.x_dtype == CB_BF16 ? gm_launch_t<__nv_bfloat16>(d, p->n_sm, in, out, ws, s) : gm_launch_t<float>(d, p->n_sm, in, out, ws, s);
 }
 
 }  // namespace cb
