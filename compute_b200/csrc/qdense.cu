@@ -667,8 +667,9 @@ int qdense_plan(cb_plan* p) {
   if (generic_only) why = "packed 4-bit weights and the NF4 scheme run on the generic kernel";
   std::string why_prefill, why_tc;
   const bool can_decode_tc = !generic_only && qdense_decode_tc_eligible(d, &why_tc);
-  const bool can_prefill = !generic_only && qdense_prefill_eligible(d, &why_prefill);
-  if (generic_only) { why_tc = why; why_prefill = why; }
+  // the prefill path expands every weight format of the Linear and NF4 schemes to bf16 planes
+  const bool can_prefill = qdense_prefill_eligible(d, &why_prefill);
+  if (generic_only) why_tc = why;
   if (d.gather_ranks > 1) {          // the fused all-gather exists in the tensor-core decode kernel only
     if (variant != CB_QDENSE_AUTO && variant != CB_QDENSE_DECODE_TC)
       return fail(CB_ERR_NOT_IMPLEMENTED, "FusedQuantizedDense: a gathered plan needs the tensor-core decode kernel");

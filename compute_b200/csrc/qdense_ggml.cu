@@ -13,6 +13,7 @@
 //
 // Both kernels give every lane one 32-value unit of a staged 1024-value chunk of a row.
 #include "common.cuh"
+#include "gemm_tc.h"
 
 #include <cuda_fp16.h>
 
@@ -300,6 +301,69 @@ embedding_lookup_kernel(const uint8_t* __restrict__ table, const IT* __restrict_
   }
 }
 
+// ---- prefill: every weight row dequantised once into bf16 planes [plane][N][K] for the tensor-core GEMM
+// (w = p0 + p1 (+ p2), p0 = bf16(w), p1 = bf16(w - p0), ...).  One CTA per weight row, a warp per 1024-value chunk.
+template <int GGML, int NPLANES>
+__global__ void __launch_bounds__(GG_WARPS * 32)
+ggml_planes_kernel(const uint8_t* __restrict__ w, uint16_t* __restrict__ planes, int64_t N, int64_t K) {
+  // the GEMM that consumes the planes may set itself up meanwhile; it waits for this grid before it loads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ __align__(16) uint8_t stage[GG_WARPS][GG_WSTAGE];
+  __shared__ float s_lut[16];
+  if (threadIdx.x < 16) s_lut[threadIdx.x] = c_iq4nl[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = blockIdx.x;
+  constexpr int VPB = gg_values(GGML), BB = gg_bytes(GGML);
+  const int64_t bytes_per_row = K / VPB * BB;
+  const uint8_t* src = w + row * bytes_per_row;
+  const uint8_t* end = w + N * bytes_per_row;
+  const size_t plane_elems = (size_t)N * K;
+  for (int64_t kc = (int64_t)warp * GG_CHUNK; kc < K; kc += (int64_t)GG_WARPS * GG_CHUNK) {
+    const int len = (int)min((int64_t)gg_chunk_bytes(GGML), bytes_per_row - kc / VPB * BB);
+    __syncwarp();
+    const uint8_t* chunk = gg_stage(stage[warp], src + kc / VPB * BB, len, end, lane);
+    __syncwarp();
+    if (kc + 32 * lane < K) {
+      float wv[32];
+      gg_decode32<GGML>(chunk, lane, wv, s_lut);
+#pragma unroll
+      for (int q = 0; q < NPLANES; q++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+          pk[e] = (uint32_t)f32_to_bf16_bits(wv[2 * e]) | ((uint32_t)f32_to_bf16_bits(wv[2 * e + 1]) << 16);
+          // what the planes so far leave over (nothing for non-finite values)
+          const float h0 = __uint_as_float(pk[e] << 16), h1 = __uint_as_float(pk[e] & 0xFFFF0000u);
+          wv[2 * e] = isfinite(wv[2 * e]) ? wv[2 * e] - h0 : 0.0f;
+          wv[2 * e + 1] = isfinite(wv[2 * e + 1]) ? wv[2 * e + 1] - h1 : 0.0f;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(planes + (size_t)q * plane_elems + (size_t)row * K + kc + 32 * lane);
+#pragma unroll
+        for (int v = 0; v < 4; v++) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+      }
+    }
+  }
+}
+
+size_t gg_align256(size_t v) { return (v + 255) & ~(size_t)255; }
+// More than 16 rows of x and enough work to pay for expanding the weights (the same rule as for 8-bit weights).
+bool gg_prefill_supports(const cb_qdense_desc& d) {
+  if (d.variant != CB_QDENSE_AUTO && d.variant != CB_QDENSE_PREFILL) return false;
+  if (d.K % 32 != 0 || d.N % 8 != 0 || d.K < 32 || d.N < 8 || d.M < 1) return false;
+  if (d.M > (1 << 30) || d.K > (1 << 30) || d.N > (1 << 30)) return false;
+  return d.variant == CB_QDENSE_PREFILL || (d.M > 16 && (double)d.M * d.K * d.N >= 64.0 * 1024 * 1024);
+}
+int gg_prefill_w_planes(const cb_qdense_desc& d) { return 2; }    // 16 mantissa bits of d * q
+int gg_prefill_x_planes(const cb_qdense_desc& d) { return d.x_dtype == CB_F32 ? 2 : 1; }
+
+template <int GGML>
+int gg_planes_launch(const cb_qdense_desc& d, const uint8_t* w, uint16_t* planes, cudaStream_t s) {
+  ggml_planes_kernel<GGML, 2><<<(unsigned)d.N, GG_WARPS * 32, 0, s>>>(w, planes, d.N, d.K);
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
 const char* gg_name(int t) {
   switch (t) {
     case CB_GGML_Q4_0: return "q4_0";
@@ -396,7 +460,59 @@ int qdense_ggml_plan(cb_plan* p) {
   p->name = std::string("qdense_ggml_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + gg_name(d.ggml_type);
   // decode shapes of the formats whose blocks feed the integer tensor cores directly (CB_QDENSE_GENERIC keeps this kernel)
   if (qdense_ggml_mma_supports(d)) qdense_ggml_mma_plan(p, gg_name(d.ggml_type));
+  else if (gg_prefill_supports(d)) {
+    // prefill shapes: the rows of W dequantised to bf16 planes once, then the tensor-core GEMM (W as the transposed operand)
+    p->variant = CB_QDENSE_PREFILL;
+    p->blocks = gemm_tc_blocks(p->n_sm, 1, d.M, d.N);
+    p->threads = gemm_tc_threads();
+    p->dyn_smem = gemm_tc_smem();
+    p->counter_bytes = 256;
+    p->workspace_bytes = 256 + gg_align256((size_t)gg_prefill_w_planes(d) * d.N * d.K * 2) +
+                         (d.x_dtype == CB_F32 ? gg_align256((size_t)gg_prefill_x_planes(d) * d.M * d.K * 2) : 0);
+    p->has_status = true;
+    p->name = std::string("qdense_ggml_prefill_tcgen05_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + gg_name(d.ggml_type);
+  } else if (d.variant == CB_QDENSE_PREFILL) {
+    return fail(CB_ERR_NOT_IMPLEMENTED, "%s prefill kernel: K must be a multiple of 32 and N of 8", op);
+  }
   return CB_OK;
+}
+
+static int qdense_ggml_prefill_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  const cb_qdense_desc& d = p->qd;
+  if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): the plan needs its workspace (bf16 planes of the weights)");
+  uint8_t* w8 = (uint8_t*)ws;
+  const int wp = gg_prefill_w_planes(d), xp = gg_prefill_x_planes(d);
+  uint16_t* wplanes = (uint16_t*)(w8 + 256);
+  uint16_t* xplanes = (uint16_t*)(w8 + 256 + gg_align256((size_t)wp * d.N * d.K * 2));
+  const uint8_t* wq = (const uint8_t*)in[1];
+  switch (d.ggml_type) {
+    case CB_GGML_Q4_0: CB_TRY(gg_planes_launch<CB_GGML_Q4_0>(d, wq, wplanes, s)); break;
+    case CB_GGML_Q8_0: CB_TRY(gg_planes_launch<CB_GGML_Q8_0>(d, wq, wplanes, s)); break;
+    case CB_GGML_IQ4_NL: CB_TRY(gg_planes_launch<CB_GGML_IQ4_NL>(d, wq, wplanes, s)); break;
+    case CB_GGML_Q4_K: CB_TRY(gg_planes_launch<CB_GGML_Q4_K>(d, wq, wplanes, s)); break;
+    default: CB_TRY(gg_planes_launch<CB_GGML_Q6_K>(d, wq, wplanes, s)); break;
+  }
+  GemmTcProblem g;
+  g.a = in[0];
+  g.planes_a = 1;
+  if (d.x_dtype == CB_F32) {
+    CB_TRY(split_f32_planes((const float*)in[0], xplanes, (size_t)d.M * d.K, nullptr, nullptr, 0, xp, s));
+    g.a = xplanes;
+    g.planes_a = xp;
+  }
+  g.b = wplanes;
+  g.planes_b = wp;
+  g.out = out[0];
+  g.status = (unsigned*)ws;
+  g.B = 1; g.M = d.M; g.N = d.N; g.K = d.K;
+  g.rhs_transposed = 1;
+  g.ab_dtype = CB_BF16;
+  g.out_dtype = d.x_dtype;
+  g.n_pass = gemm_tc_split_passes(g.planes_a, g.planes_b, 1, g.pass_a, g.pass_b);
+  g.col_scale = nullptr;
+  g.bias = d.has_bias ? (const float*)in[2] : nullptr;
+  g.activation = d.activation;
+  return gemm_tc_run(p->dev, p->blocks, g, s);
 }
 
 int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
@@ -408,6 +524,7 @@ int qdense_ggml_launch(const cb_plan* p, const void* const* in, void* const* out
     if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense(GGML): the plan needs its workspace (digit planes of x)");
     return qdense_ggml_mma_launch(p, in, out, ws, s);
   }
+  if (p->variant == CB_QDENSE_PREFILL) return qdense_ggml_prefill_launch(p, in, out, ws, s);
   return d.x_dtype == CB_BF16 ? gg_launch_t<__nv_bfloat16>(d, in, out, s) : gg_launch_t<float>(d, in, out, s);
 }
 

@@ -252,6 +252,29 @@ def test_ggml_on_tensor_cores(ggml, M, K, N, x_dtype):
 
 
 @pytest.mark.parametrize("ggml", list(GGML_TYPES))
+@pytest.mark.parametrize("M,K,N,x_dtype,auto", [(17, 256, 72, "f32", False), (300, 512, 520, "f32", True), (130, 1024, 264, "bf16", False),
+                                                (2048, 768, 1000, "bf16", True)])
+def test_ggml_prefill_on_the_gemm(ggml, M, K, N, x_dtype, auto):
+    """More than 16 rows of x: the weight rows are dequantised once into two bf16 planes and the product runs on the
+    tensor-core GEMM with W as the transposed operand; a plan picks this by itself from 2^26 multiply-adds on."""
+    gt = GGML_TYPES[ggml]
+    rng = np.random.default_rng(5 * M + gt)
+    wq = orc.ggml_random_rows(rng, N, K, gt)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    xw = orc.bf16_to_f32(xin) if x_dtype == "bf16" else x
+    want = orc.qdense_ggml(xw, wq, b, gt, orc.ACT_SILU)
+    plan = dv.Plan.qdense(M, K, N, code, dv.U8, has_bias=True, activation=dv.ACT_SILU, scheme=dv.QUANT_GGML, ggml_type=gt,
+                          variant=dv.QDENSE_AUTO if auto else dv.QDENSE_PREFILL)
+    assert plan.kernel_name == f"qdense_ggml_prefill_tcgen05_{x_dtype}_{ggml}" and plan.workspace_bytes > 0
+    got = ops._run(plan, [xin, wq, b], (M, N), dv.NP_CARRIER[code])
+    gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+    assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else 3e-5)
+
+
+@pytest.mark.parametrize("ggml", list(GGML_TYPES))
 def test_ggml_dequantised_values_are_bit_exact(ggml):
     """x = identity rows picks single weights: every dequantised value must carry the reference's bits."""
     gt = GGML_TYPES[ggml]
@@ -782,6 +805,43 @@ def test_prefill_matches_oracle(M, K, N, layout, block, with_zp, x_dtype):
         assert max_abs_normalised(orc.bf16_to_f32(got), orc.bf16_to_f32(orc.bf16_from_f32(want))) < 2.0 ** -7
     else:
         assert max_abs_normalised(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("kind", ["i4", "u4", "nf4_u4", "nf4_i4", "nf4_u8"])
+@pytest.mark.parametrize("M,K,N,block,with_zp,x_dtype", [(17, 64, 72, 8, False, "f32"), (300, 512, 520, 16, True, "f32"),
+                                                        (130, 1024, 264, 24, True, "bf16"), (2048, 520, 1000, 40, False, "f32")])
+def test_prefill_packed_4bit_and_nf4(kind, M, K, N, block, with_zp, x_dtype):
+    """More than 16 rows of x on packed Int4 / Uint4 weights and NF4 indices (packed or one per byte): the weights are
+    expanded to bf16 planes and multiplied on the tensor cores; above 2^26 multiply-adds that is what a plan picks by
+    itself."""
+    rng = np.random.default_rng(M + N)
+    nf4, signed = kind.startswith("nf4"), kind.endswith("i4")
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    vals = rng.integers(0, 16, size=(K, N))
+    nblk = -(-N // block)
+    s = rng.uniform(0.01, 0.2, size=(K, nblk)).astype(np.float32)
+    zp = rng.uniform(-0.05, 0.05, size=s.shape).astype(np.float32) if with_zp and not nf4 else None
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    xw = orc.bf16_to_f32(xin) if x_dtype == "bf16" else x
+    if nf4:
+        want = orc.qdense_nf4(xw, vals.astype(np.uint8), s, b, block, orc.ACT_GELU)
+    else:
+        w8 = np.where(vals >= 8, vals - 16, vals).astype(np.int8) if signed else vals.astype(np.uint8)
+        want = orc.qdense_linear(xw, w8, s, zp, b, block, orc.ACT_GELU, threads=orc.max_threads())
+    big = M * K * N >= 2 ** 26
+    if kind == "nf4_u8":
+        got, plan = ops.quantized_dense(xin, vals.astype(np.uint8), s, None, b, x_dtype=code, block_size=block, activation=dv.ACT_GELU,
+                                        scheme=dv.QUANT_NF4, variant=dv.QDENSE_AUTO if big else dv.QDENSE_PREFILL, return_plan=True)
+    else:
+        got, plan = ops.quantized_dense(xin, orc.pack_nibbles(vals), s, zp, b, x_dtype=code, block_size=block, activation=dv.ACT_GELU,
+                                        scheme=dv.QUANT_NF4 if nf4 else dv.QUANT_LINEAR, packed=(dv.I4 if signed else dv.U4, N),
+                                        variant=dv.QDENSE_AUTO if big else dv.QDENSE_PREFILL, return_plan=True)
+    wname = "u8" if kind == "nf4_u8" else ("i4" if signed else "u4")
+    assert plan.kernel_name == f"qdense_prefill_tcgen05_{x_dtype}_{wname}{'_nf4' if nf4 else ''}"
+    gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+    assert max_abs_normalised(gotf, want) < (BF16_TOL if x_dtype == "bf16" else 2e-5)
 
 
 @pytest.mark.parametrize("N", [264, 272])
