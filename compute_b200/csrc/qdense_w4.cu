@@ -13,7 +13,7 @@
 // A nibble becomes a float without a conversion: its four bits go to the top of the mantissa of 1.0, which is
 // 1 + n / 16 (for Int4 the nibble's top bit is flipped first: n ^ 8 = n + 8).  The sums run over those floats and the
 // sum of the scaled x is kept beside them: sum x s n = 16 (sum x s f - sum x s), and - 8 sum x s for Int4.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 #include <algorithm>
 #include <atomic>
@@ -23,7 +23,9 @@
 namespace cb {
 namespace {
 
-constexpr int W4_WARPS = 8;
+constexpr int W4_WARPS = 8;                // warps that multiply; the TMA form adds one that asks for the tiles
+constexpr int W4_STAGES = 6;               // TMA form: groups of rows in flight or in use per CTA
+constexpr size_t W4_HEADER = 256;          // status words at the start of the workspace
 constexpr int W4_COLS = 256;               // columns per CTA: 32 lanes x 8
 __host__ __device__ constexpr int w4_unroll(int mr) { return mr >= 8 ? 4 : 8; }   // rows of W a lane has in flight
 enum { W4_U4 = 0, W4_I4 = 1, W4_NF4 = 2 };
@@ -35,6 +37,12 @@ __constant__ float kW4Nf4[16] = {
     0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
     0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
 
+// shared memory before the barriers: x of the cut, then the reduction buffer with, in the TMA form, the ring under it
+__host__ __device__ constexpr size_t w4_data_bytes(int mr, int rows_max, bool tma) {
+  const size_t xs = (size_t)mr * rows_max * 4, red = (size_t)W4_WARPS * mr * W4_COLS * 4, ring = (size_t)W4_STAGES * W4_WARPS * w4_unroll(mr) * 128;
+  return xs + (tma && ring > red ? ring : red);
+}
+
 template <int MODE>
 __device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut) {
   if (MODE == W4_NF4) return lut[(word >> (4 * i)) & 0xFu];
@@ -44,19 +52,31 @@ __device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut
 
 // grid (row tiles of x, column tiles, cuts of K); partial [gridDim.z][M][N].  K is counted in groups of 8 warps x
 // W4_UNROLL rows; cut z takes groups [z G / cuts, (z + 1) G / cuts).  TAIL: K is not a whole number of groups, so the
-// rows of the last group are checked one by one.
-template <typename XT, int MODE, int MR, bool ZP, bool TAIL>
-__global__ void __launch_bounds__(W4_WARPS * 32, MR >= 2 ? 2 : 3)
-qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const float* __restrict__ scales, const float* __restrict__ zps,
-                 float* __restrict__ partial, int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
-  constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL;
+// rows of the last group are checked one by one.  TMA: a ninth warp asks for every group of rows as one tile (GROUP rows
+// x 128 bytes of the CTA's 256 columns) into a ring of W4_STAGES stages; the eight others read their rows' words from
+// it.  Every wait is bounded; one that gives up ends the kernel with the status word set.  Without TMA (N / 2 not a
+// multiple of 16 bytes) every lane loads its words itself, the next group requested before the current one is consumed.
+template <typename XT, int MODE, int MR, bool ZP, bool TAIL, bool TMA>
+__global__ void __launch_bounds__((W4_WARPS + (TMA ? 1 : 0)) * 32, MR >= 2 ? 2 : 3)
+qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restrict__ x, const uint32_t* __restrict__ w,
+                 const float* __restrict__ scales, const float* __restrict__ zps, float* __restrict__ partial, unsigned* __restrict__ status,
+                 int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
+  constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL, STAGE = GROUP * 128;
   // the kernel that adds the cuts may be scheduled now; it waits for this grid before it reads the partial sums
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  extern __shared__ __align__(16) unsigned char w4_smem[];
+  extern __shared__ __align__(1024) unsigned char w4_smem[];
   float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_max]
-  float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][W4_COLS]
+  float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][W4_COLS]; the ring lies under it
+  const uint32_t* ring = reinterpret_cast<const uint32_t*>(red);               // [W4_STAGES][GROUP][32 words]
+  uint64_t* full = reinterpret_cast<uint64_t*>(w4_smem + w4_data_bytes(MR, rows_max, TMA));
+  uint64_t* empty = full + W4_STAGES;
   __shared__ float lut[16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (TMA && threadIdx.x == 0) {
+#pragma unroll
+    for (int k = 0; k < W4_STAGES; k++) { tc::mbar_init(&full[k], 1); tc::mbar_init(&empty[k], W4_WARPS); }
+    tc::fence_barrier_init();
+  }
   const int m0 = blockIdx.x * MR;
   const int64_t G = (K + GROUP - 1) / GROUP;
   const int64_t g0 = (int64_t)blockIdx.z * G / gridDim.z, g1 = ((int64_t)blockIdx.z + 1) * G / gridDim.z;
@@ -66,7 +86,7 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
   const int64_t n0 = (int64_t)blockIdx.y * W4_COLS + lane * 8;
   const bool active = n0 < N;
   if (MODE == W4_NF4 && threadIdx.x < 16) lut[threadIdx.x] = kW4Nf4[threadIdx.x];
-  for (int idx = threadIdx.x; idx < MR * rows_max; idx += W4_WARPS * 32) {
+  for (int idx = threadIdx.x; idx < MR * rows_max; idx += blockDim.x) {
     const int m = idx / rows_max, kk = idx % rows_max;
     xs[idx] = (m0 + m < M && kk < kc) ? (float)Scalar<XT>::load(x, (int64_t)(m0 + m) * K + k0 + kk) : 0.0f;
   }
@@ -79,12 +99,27 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[m][i] = 0.0f;
   }
-  if (active && n_groups > 0) {
+  bool failed = false;
+  int issued = 0;                                                              // tiles asked for (the asking lane only)
+  if (TMA && warp == W4_WARPS) {
+    // ---- the ninth warp: one tile per group, as soon as the stage it goes to has been read by all eight warps
+    if (lane == 0) {
+      for (int g = 0; g < n_groups; g++) {
+        const int slot = g % W4_STAGES, round = g / W4_STAGES;
+        if (round > 0 && !tc::mbar_wait(&empty[slot], (uint32_t)((round - 1) & 1))) { failed = true; break; }
+        tc::mbar_expect_tx(&full[slot], STAGE);
+        tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * (W4_COLS / 8)), (int)(k0 + (int64_t)g * GROUP),
+                        &full[slot]);
+        issued = g + 1;
+      }
+    }
+  } else if ((TMA || active) && n_groups > 0) {
     const int64_t wrow = N / 8;                                                // words per row of W
+    const int64_t n0s = active ? n0 : 0;                                       // lanes past N (TMA form) work on zeros of column 0's scales
     // this warp's rows of a group: warp, warp + 8, ...; the next group is requested before this one is consumed
-    const uint32_t* wq = w + (k0 + warp) * wrow + n0 / 8;
-    const float* sq = scales + (k0 + warp) * nblk + n0 / block;
-    const float* zq = ZP ? zps + (k0 + warp) * nblk + n0 / block : nullptr;
+    const uint32_t* wq = w + (k0 + warp) * wrow + n0s / 8;
+    const float* sq = scales + (k0 + warp) * nblk + n0s / block;
+    const float* zq = ZP ? zps + (k0 + warp) * nblk + n0s / block : nullptr;
     const int64_t w8 = W4_WARPS * wrow, s8 = W4_WARPS * nblk;
     uint32_t wn[W4_UNROLL];
     float sn[W4_UNROLL], zn[W4_UNROLL];
@@ -92,20 +127,33 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
 #pragma unroll
       for (int u = 0; u < W4_UNROLL; u++) {
         const bool in = !TAIL || g * GROUP + warp + u * W4_WARPS < kc;
-        wn[u] = in ? __ldg(wq + u * w8) : 0u;
+        if (!TMA) wn[u] = in ? __ldg(wq + u * w8) : 0u;
         sn[u] = in ? __ldg(sq + u * s8) : 0.0f;
         zn[u] = (ZP && in) ? __ldg(zq + u * s8) : 0.0f;
       }
-      wq += GROUP * wrow; sq += GROUP * nblk;
+      if (!TMA) wq += GROUP * wrow;
+      sq += GROUP * nblk;
       if (ZP) zq += GROUP * nblk;
     };
     request(0);
     const float* xr = xs + warp;
+    int slot = 0;
+    uint32_t phase = 0;
     for (int g = 0; g < n_groups; g++) {
       uint32_t wv[W4_UNROLL];
       float sv[W4_UNROLL], zv[W4_UNROLL];
+      if (TMA) {
+        const bool ok = tc::mbar_wait(&full[slot], phase);
+        if (!__all_sync(0xFFFFFFFFu, ok)) { failed = true; break; }
+        const uint32_t* st = ring + (size_t)slot * (STAGE / 4) + warp * 32 + lane;
 #pragma unroll
-      for (int u = 0; u < W4_UNROLL; u++) { wv[u] = wn[u]; sv[u] = sn[u]; zv[u] = zn[u]; }
+        for (int u = 0; u < W4_UNROLL; u++) wv[u] = st[u * W4_WARPS * 32];
+        __syncwarp();                                                          // every lane holds its words: the stage may be refilled
+        if (lane == 0) tc::mbar_arrive(&empty[slot]);
+        if (++slot == W4_STAGES) { slot = 0; phase ^= 1u; }
+      }
+#pragma unroll
+      for (int u = 0; u < W4_UNROLL; u++) { if (!TMA) wv[u] = wn[u]; sv[u] = sn[u]; zv[u] = zn[u]; }
       if (g + 1 < n_groups) request(g + 1);
 #pragma unroll
       for (int u = 0; u < W4_UNROLL; u++) {
@@ -125,6 +173,16 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
       xr += GROUP;
     }
   }
+  if (TMA) {
+    // the ring becomes the reduction buffer once every warp has read its last stage; a wait that gave up ends the CTA
+    if (__syncthreads_or(failed ? 1 : 0)) {
+      // tiles that were asked for may still land: one more bounded wait for each before the shared memory is given up
+      for (int g = max(0, issued - W4_STAGES); g < issued; g++) tc::mbar_wait(&full[g % W4_STAGES], (uint32_t)((g / W4_STAGES) & 1));
+      if (threadIdx.x == 0 && atomicCAS(&status[0], 0u, 1u) == 0u) atomicExch(&status[1], blockIdx.y | (blockIdx.z << 16));
+      return;
+    }
+    if (warp == W4_WARPS) return;
+  }
   // ---- the eight warps' sums, added in warp order
 #pragma unroll
   for (int m = 0; m < MR; m++) {
@@ -141,7 +199,7 @@ qdense_w4_kernel(const XT* __restrict__ x, const uint32_t* __restrict__ w, const
   }
   __syncthreads();
   const int64_t n = (int64_t)blockIdx.y * W4_COLS + threadIdx.x;
-  if (n < N) {
+  if (n < N && threadIdx.x < W4_COLS) {
 #pragma unroll
     for (int m = 0; m < MR; m++) {
       if (m0 + m >= M) break;
@@ -189,19 +247,44 @@ void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   *rows_max = (int)(((G + best - 1) / best) * group);
 }
 
-size_t w4_smem_bytes(int mr, int rows_per_cta) { return ((size_t)mr * rows_per_cta + (size_t)W4_WARPS * mr * W4_COLS) * sizeof(float); }
+size_t w4_smem_bytes(int mr, int rows_max, bool tma) { return w4_data_bytes(mr, rows_max, tma) + (tma ? 2 * W4_STAGES * sizeof(uint64_t) : 0); }
+// the packed rows as 32-bit words [K][N / 8], in boxes of one group of rows by the 32 words of a column tile
+bool w4_tma(const cb_qdense_desc& d) { return d.N % 32 == 0; }
+int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t group) {
+  struct Entry { const void* ptr; uint64_t K, N; uint32_t group; bool valid; CUtensorMap map; };
+  constexpr int SLOTS = 64;
+  static thread_local Entry cache[SLOTS];
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
+  Entry& e = cache[(h >> 40) % SLOTS];
+  if (e.valid && e.ptr == ptr && e.K == K && e.N == N && e.group == group) { *m = e.map; return CB_OK; }
+  encode_tiled_fn enc = tensor_map_encoder();
+  if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {N / 8, K};
+  cuuint64_t strides[1] = {N / 2};
+  cuuint32_t box[2] = {W4_COLS / 8, group};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  e.ptr = ptr; e.K = K; e.N = N; e.group = group; e.map = *m; e.valid = true;
+  return CB_OK;
+}
 
-template <typename XT, int MODE, int MR, bool ZP, bool TAIL>
+template <typename XT, int MODE, int MR, bool ZP, bool TAIL, bool TMA>
 int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   int cuts = 0, rows = 0;
   w4_cuts(d, p->n_sm, &cuts, &rows);
-  const size_t smem = w4_smem_bytes(MR, rows);
+  const size_t smem = w4_smem_bytes(MR, rows, TMA);
+  CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  if (TMA) CB_TRY(w4_encode(&tmap, in[1], (uint64_t)d.K, (uint64_t)d.N, (uint32_t)(W4_WARPS * w4_unroll(MR))));
+  float* partial = (float*)((uint8_t*)ws + W4_HEADER);
   static std::atomic<bool> configured[64];
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    CB_CUDA(cudaFuncSetAttribute(qdense_w4_kernel<XT, MODE, MR, ZP, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    CB_CUDA(cudaFuncSetAttribute(qdense_w4_kernel<XT, MODE, MR, ZP, TAIL, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   int idx = 3;
@@ -209,8 +292,8 @@ int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void*
   const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
   const int64_t nblk = (d.N + d.block_size - 1) / d.block_size;
   dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + W4_COLS - 1) / W4_COLS), (unsigned)cuts);
-  qdense_w4_kernel<XT, MODE, MR, ZP, TAIL><<<grid, W4_WARPS * 32, smem, s>>>((const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, (float*)ws,
-                                                                    (int)d.M, d.K, d.N, d.block_size, nblk, rows);
+  qdense_w4_kernel<XT, MODE, MR, ZP, TAIL, TMA><<<grid, (W4_WARPS + (TMA ? 1 : 0)) * 32, smem, s>>>(
+      tmap, (const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, partial, (unsigned*)ws, (int)d.M, d.K, d.N, d.block_size, nblk, rows);
   CB_CUDA(cudaGetLastError());
   const int64_t mn = d.M * d.N;
   cudaLaunchConfig_t cfg;
@@ -223,7 +306,7 @@ int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void*
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_w4_finish_kernel<XT>, (const float*)ws, bias, (XT*)out[0], mn, (int64_t)d.N, cuts, (int)d.activation));
+  CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_w4_finish_kernel<XT>, (const float*)partial, bias, (XT*)out[0], mn, (int64_t)d.N, cuts, (int)d.activation));
   return CB_OK;
 }
 
@@ -231,7 +314,9 @@ template <typename XT, int MODE, bool ZP>
 int w4_launch_m(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const int mr = w4_rows(p->qd);
   const bool tail = p->qd.K % (W4_WARPS * w4_unroll(mr)) != 0;
-#define W4_GO(MR_) (tail ? w4_launch_k<XT, MODE, MR_, ZP, true>(p, in, out, ws, s) : w4_launch_k<XT, MODE, MR_, ZP, false>(p, in, out, ws, s))
+  const bool tma = w4_tma(p->qd) && (reinterpret_cast<uintptr_t>(in[1]) & 15) == 0;
+#define W4_GO(MR_) (tma ? (tail ? w4_launch_k<XT, MODE, MR_, ZP, true, true>(p, in, out, ws, s) : w4_launch_k<XT, MODE, MR_, ZP, false, true>(p, in, out, ws, s)) \
+                        : (tail ? w4_launch_k<XT, MODE, MR_, ZP, true, false>(p, in, out, ws, s) : w4_launch_k<XT, MODE, MR_, ZP, false, false>(p, in, out, ws, s)))
   switch (mr) {
     case 1: return W4_GO(1);
     case 2: return W4_GO(2);
@@ -269,11 +354,11 @@ void qdense_w4_plan(cb_plan* p) {
   w4_cuts(d, p->n_sm, &cuts, &rows);
   const int mr = w4_rows(d);
   p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS) * cuts);
-  p->threads = W4_WARPS * 32;
-  p->dyn_smem = (int)w4_smem_bytes(mr, rows);
-  p->workspace_bytes = (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
-  p->counter_bytes = 0;
-  p->has_status = false;
+  p->threads = (W4_WARPS + (w4_tma(d) ? 1 : 0)) * 32;
+  p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d));
+  p->workspace_bytes = W4_HEADER + (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
+  p->counter_bytes = W4_HEADER;
+  p->has_status = true;
   p->name = std::string("qdense_w4_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (d.w_dtype == CB_U4 ? "_u4" : "_i4") +
             (d.scheme == CB_QUANT_NF4 ? "_nf4" : "");
 }
