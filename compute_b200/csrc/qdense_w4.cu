@@ -23,7 +23,7 @@
 namespace cb {
 namespace {
 
-constexpr int W4_WARPS = 8;                // warps that multiply; the TMA form adds one that asks for the tiles
+constexpr int W4_WARPS = 8;
 constexpr int W4_STAGES = 6;               // TMA form: groups of rows in flight or in use per CTA
 constexpr size_t W4_HEADER = 256;          // status words at the start of the workspace
 constexpr int W4_COLS = 256;               // columns per CTA: 32 lanes x 8
@@ -52,12 +52,12 @@ __device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut
 
 // grid (row tiles of x, column tiles, cuts of K); partial [gridDim.z][M][N].  K is counted in groups of 8 warps x
 // W4_UNROLL rows; cut z takes groups [z G / cuts, (z + 1) G / cuts).  TAIL: K is not a whole number of groups, so the
-// rows of the last group are checked one by one.  TMA: a ninth warp asks for every group of rows as one tile (GROUP rows
-// x 128 bytes of the CTA's 256 columns) into a ring of W4_STAGES stages; the eight others read their rows' words from
-// it.  Every wait is bounded; one that gives up ends the kernel with the status word set.  Without TMA (N / 2 not a
+// rows of the last group are checked one by one.  TMA: every group of rows arrives as one tile (GROUP rows x 128
+// bytes of the CTA's 256 columns) in a ring of W4_STAGES stages, asked for by thread 0; the warps read their rows'
+// words from it.  Every wait is bounded; one that gives up ends the kernel with the status word set.  Without TMA (N / 2 not a
 // multiple of 16 bytes) every lane loads its words itself, the next group requested before the current one is consumed.
 template <typename XT, int MODE, int MR, bool ZP, bool TAIL, bool TMA>
-__global__ void __launch_bounds__((W4_WARPS + (TMA ? 1 : 0)) * 32, MR >= 2 ? 2 : 3)
+__global__ void __launch_bounds__(W4_WARPS * 32, MR >= 2 ? 2 : 3)
 qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restrict__ x, const uint32_t* __restrict__ w,
                  const float* __restrict__ scales, const float* __restrict__ zps, float* __restrict__ partial, unsigned* __restrict__ status,
                  int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
@@ -100,20 +100,21 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
     for (int i = 0; i < 8; i++) acc[m][i] = 0.0f;
   }
   bool failed = false;
-  int issued = 0;                                                              // tiles asked for (the asking lane only)
-  if (TMA && warp == W4_WARPS) {
-    // ---- the ninth warp: one tile per group, as soon as the stage it goes to has been read by all eight warps
-    if (lane == 0) {
-      for (int g = 0; g < n_groups; g++) {
-        const int slot = g % W4_STAGES, round = g / W4_STAGES;
-        if (round > 0 && !tc::mbar_wait(&empty[slot], (uint32_t)((round - 1) & 1))) { failed = true; break; }
-        tc::mbar_expect_tx(&full[slot], STAGE);
-        tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * (W4_COLS / 8)), (int)(k0 + (int64_t)g * GROUP),
-                        &full[slot]);
-        issued = g + 1;
-      }
-    }
-  } else if ((TMA || active) && n_groups > 0) {
+  int issued = 0;                                                              // tiles asked for (thread 0 only)
+  // TMA form: thread 0 asks for group g + W4_STAGES - 1 when it starts on group g; the stage that tile goes to held
+  // group g - 1, which every warp has copied to registers (and said so on the stage's `empty` barrier) by then or soon.
+  auto ask = [&](int g) {                                                      // thread 0 only; false if the stage never came free
+    const int slot = g % W4_STAGES, round = g / W4_STAGES;
+    if (round > 0 && !tc::mbar_wait(&empty[slot], (uint32_t)((round - 1) & 1))) return false;
+    tc::mbar_expect_tx(&full[slot], STAGE);
+    tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * (W4_COLS / 8)), (int)(k0 + (int64_t)g * GROUP),
+                    &full[slot]);
+    issued = g + 1;
+    return true;
+  };
+  if (TMA && threadIdx.x == 0)
+    for (int g = 0; g < min(n_groups, W4_STAGES - 1); g++) ask(g);
+  if ((TMA || active) && n_groups > 0) {
     const int64_t wrow = N / 8;                                                // words per row of W
     const int64_t n0s = active ? n0 : 0;                                       // lanes past N (TMA form) work on zeros of column 0's scales
     // this warp's rows of a group: warp, warp + 8, ...; the next group is requested before this one is consumed
@@ -143,7 +144,9 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
       uint32_t wv[W4_UNROLL];
       float sv[W4_UNROLL], zv[W4_UNROLL];
       if (TMA) {
-        const bool ok = tc::mbar_wait(&full[slot], phase);
+        bool ok = true;
+        if (threadIdx.x == 0 && g + W4_STAGES - 1 < n_groups) ok = ask(g + W4_STAGES - 1);
+        ok = ok && tc::mbar_wait(&full[slot], phase);
         if (!__all_sync(0xFFFFFFFFu, ok)) { failed = true; break; }
         const uint32_t* st = ring + (size_t)slot * (STAGE / 4) + warp * 32 + lane;
 #pragma unroll
@@ -181,7 +184,6 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
       if (threadIdx.x == 0 && atomicCAS(&status[0], 0u, 1u) == 0u) atomicExch(&status[1], blockIdx.y | (blockIdx.z << 16));
       return;
     }
-    if (warp == W4_WARPS) return;
   }
   // ---- the eight warps' sums, added in warp order
 #pragma unroll
@@ -199,7 +201,7 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
   }
   __syncthreads();
   const int64_t n = (int64_t)blockIdx.y * W4_COLS + threadIdx.x;
-  if (n < N && threadIdx.x < W4_COLS) {
+  if (n < N) {
 #pragma unroll
     for (int m = 0; m < MR; m++) {
       if (m0 + m >= M) break;
@@ -292,7 +294,7 @@ int w4_launch_k(const cb_plan* p, const void* const* in, void* const* out, void*
   const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
   const int64_t nblk = (d.N + d.block_size - 1) / d.block_size;
   dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + W4_COLS - 1) / W4_COLS), (unsigned)cuts);
-  qdense_w4_kernel<XT, MODE, MR, ZP, TAIL, TMA><<<grid, (W4_WARPS + (TMA ? 1 : 0)) * 32, smem, s>>>(
+  qdense_w4_kernel<XT, MODE, MR, ZP, TAIL, TMA><<<grid, W4_WARPS * 32, smem, s>>>(
       tmap, (const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, partial, (unsigned*)ws, (int)d.M, d.K, d.N, d.block_size, nblk, rows);
   CB_CUDA(cudaGetLastError());
   const int64_t mn = d.M * d.N;
@@ -354,7 +356,7 @@ void qdense_w4_plan(cb_plan* p) {
   w4_cuts(d, p->n_sm, &cuts, &rows);
   const int mr = w4_rows(d);
   p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS) * cuts);
-  p->threads = (W4_WARPS + (w4_tma(d) ? 1 : 0)) * 32;
+  p->threads = W4_WARPS * 32;
   p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d));
   p->workspace_bytes = W4_HEADER + (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
   p->counter_bytes = W4_HEADER;
