@@ -681,7 +681,7 @@ int qdense_plan(cb_plan* p) {
     // CUDA-core kernel, which also keeps the reference's summation order)
     if (can_decode_tc) variant = CB_QDENSE_DECODE_TC;
     else if (can_decode) variant = CB_QDENSE_DECODE_MMA;
-    else if (can_prefill && d.M > 16 && (double)d.M * d.K * d.N >= 64.0 * 1024 * 1024) variant = CB_QDENSE_PREFILL;
+    else if (can_prefill && d.M > 16 && (double)d.M * d.K * d.N >= 64.0 * 1024 * 1024 && !qdense_w4_supports(d)) variant = CB_QDENSE_PREFILL;
     else variant = CB_QDENSE_GENERIC;
   }
   if (variant == CB_QDENSE_DECODE_MMA && !can_decode)

@@ -37,6 +37,9 @@ constexpr int GM_ROWS = 64;                 // weight rows per CTA
 constexpr int GM_STEP = 256;                // values per ring stage and row
 constexpr int GM_STAGES = 3;
 constexpr int GM_MAX_COLS = 48;             // 3 digit planes x 16 rows of x
+// Up to this many rows of x the kernel runs once per 16 rows: four runs of 37 us beat expanding the weights to bf16 planes
+// for the GEMM (176 us whatever M on the 4096 x 14336 projection).
+constexpr int GM_MAX_M = 64;
 constexpr int GM_BAR_BYTES = 256;           // the stages' barriers (8 warps x 3) and the digits' one
 static_assert((GM_WARPS * GM_STAGES + 1) * 8 <= GM_BAR_BYTES, "barrier area");
 constexpr int GM_DPAD = 32;                 // bytes between two columns of digits in shared memory, past K
@@ -554,26 +557,35 @@ int gm_launch_t(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
 }  // namespace
 
 bool qdense_ggml_mma_supports(const cb_qdense_desc& d) {
-  if (d.scheme != CB_QUANT_GGML || d.variant == CB_QDENSE_GENERIC) return false;
+  if (d.scheme != CB_QUANT_GGML || d.variant != CB_QDENSE_AUTO) return false;    // by name: the CUDA-core kernel or the prefill path
   if (d.ggml_type != CB_GGML_Q4_0 && d.ggml_type != CB_GGML_Q8_0 && d.ggml_type != CB_GGML_IQ4_NL && d.ggml_type != CB_GGML_Q4_K) return false;
-  return d.M >= 1 && d.M <= 16 && d.K >= 256 && d.K % 256 == 0 && d.K <= (1 << 24) && d.N >= 1 && (d.N + GM_ROWS - 1) / GM_ROWS <= 0x7FFFFFFFLL;
+  return d.M >= 1 && d.M <= GM_MAX_M && d.K >= 256 && d.K % 256 == 0 && d.K <= (1 << 24) && d.N >= 1 && (d.N + GM_ROWS - 1) / GM_ROWS <= 0x7FFFFFFFLL;
 }
 
 void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {
   const cb_qdense_desc& d = p->qd;
   p->blocks = gm_grid(d.N, p->n_sm);
   p->threads = GM_WARPS * 32;
-  p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)d.M) <= 2 && gm_digits_resident(d.ggml_type, d.M, d.K) ? gm_digit_smem(d.M, d.K) : 0),
+  const int64_t m16 = std::min<int64_t>(d.M, 16);
+  p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)m16) <= 2 && gm_digits_resident(d.ggml_type, m16, d.K) ? gm_digit_smem(m16, d.K) : 0),
                               GM_SMEM_FLOOR);
-  p->workspace_bytes = gm_layout(d.M, d.K).total;
+  p->workspace_bytes = gm_layout(std::min<int64_t>(d.M, 16), d.K).total;
   p->counter_bytes = GM_HEADER;
   p->has_status = true;
   p->name = std::string("qdense_ggml_mma_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + type_name;
 }
 
 int qdense_ggml_mma_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  const cb_qdense_desc& d = p->qd;
-  return d.x_dtype == CB_BF16 ? gm_launch_t<__nv_bfloat16>(d, p->n_sm, in, out, ws, s) : gm_launch_t<float>(d, p->n_sm, in, out, ws, s);
+  // 16 rows of x per run; the runs follow each other on the stream and share the workspace
+  const size_t esz = p->qd.x_dtype == CB_BF16 ? 2 : 4;
+  for (int64_t m0 = 0; m0 < p->qd.M; m0 += 16) {
+    cb_qdense_desc d = p->qd;
+    d.M = std::min<int64_t>(16, p->qd.M - m0);
+    const void* cin[3] = {(const uint8_t*)in[0] + (size_t)m0 * d.K * esz, in[1], d.has_bias ? in[2] : nullptr};
+    void* cout[1] = {(uint8_t*)out[0] + (size_t)m0 * d.N * esz};
+    CB_TRY(d.x_dtype == CB_BF16 ? gm_launch_t<__nv_bfloat16>(d, p->n_sm, cin, cout, ws, s) : gm_launch_t<float>(d, p->n_sm, cin, cout, ws, s));
+  }
+  return CB_OK;
 }
 
 }  // namespace cb

@@ -40,6 +40,12 @@ qdense_planes_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sc
                      uint16_t* __restrict__ planes, int64_t K, int64_t N, int layout, int64_t block, int rows_per_cta) {
   constexpr bool WUNSIGNED = WKIND == QP_U8 || WKIND == QP_U4;
   constexpr bool PACKED = WKIND == QP_U4 || WKIND == QP_I4;
+  // the table is read with a different index in every lane: from shared memory (16 banks), not from the constant cache
+  __shared__ float s_nf4[16];
+  if (NF4) {
+    if (threadIdx.x < 16) s_nf4[threadIdx.x] = kPrefillNf4[threadIdx.x];
+    __syncthreads();
+  }
   // the GEMM that consumes the planes may set itself up meanwhile; it waits for this grid before it loads
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t n = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
@@ -71,13 +77,13 @@ qdense_planes_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sc
 #pragma unroll
       for (int e = 0; e < 8; e++) {
         const uint32_t nib = (word >> (4 * e)) & 0xFu;
-        v[e] = NF4 ? kPrefillNf4[nib] : __uint_as_float(0x4B000000u | (WUNSIGNED ? nib : (nib ^ 8u))) - (WUNSIGNED ? 8388608.0f : 8388616.0f);
+        v[e] = NF4 ? s_nf4[nib] : __uint_as_float(0x4B000000u | (WUNSIGNED ? nib : (nib ^ 8u))) - (WUNSIGNED ? 8388608.0f : 8388616.0f);
       }
     } else {
       uint2 raw8 = *reinterpret_cast<const uint2*>(w + krow * N + n);
       if (NF4) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = kPrefillNf4[((e < 4 ? raw8.x : raw8.y) >> (8 * (e & 3))) & 0xFu];
+        for (int e = 0; e < 8; e++) v[e] = s_nf4[((e < 4 ? raw8.x : raw8.y) >> (8 * (e & 3))) & 0xFu];
       } else {
         if (!WUNSIGNED) { raw8.x ^= 0x80808080u; raw8.y ^= 0x80808080u; }
 #pragma unroll
