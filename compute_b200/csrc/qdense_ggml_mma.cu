@@ -6,7 +6,8 @@
 // scale, multiply-add), which is what bounds it.  Here the integers inside the blocks go to mma.sync m16n8k32 (s8) as
 // they are, against x in block fixed point:
 //   x[m, k] = unit[m] * (d0 + 128 d1 + 16384 d2),  signed base-128 digits, unit[m] a power of two from the largest |x| of
-//   the row (20 bits below it: an error of at most 2^-21 of the row's maximum per element);
+//   the row (20 bits below it: an error of at most 2^-21 of the row's maximum per element; bfloat16 x takes two digits,
+//   13 bits);
 // one MMA forms, for 16 weight rows and one 32-value block, the exact integer dot products with eight (digit plane, x
 // row) columns, and the block's own scale is applied to that integer in float32:
 //   Q8_0    d * sum(q x)                      Q4_0    (d / 16) * sum(16 (n - 8) x)    n = nibble
@@ -63,7 +64,11 @@ __host__ __device__ constexpr int gm_seg(int t) { return t == CB_GGML_Q4_K ? 144
 // apart.  Q8_0: the step's 272 bytes.
 __host__ __device__ constexpr int gm_pitch(int t) { return t == CB_GGML_Q4_K ? 160 : gm_seg(t); }
 __host__ __device__ constexpr int gm_stage_bytes(int t) { return 16 * gm_pitch(t); }
-__host__ __device__ constexpr int gm_tiles(int M) { return (3 * M + 7) / 8; }             // 8-column tiles of (plane, row) columns
+// Digit planes of x: three for float32 (20 bits below the row's largest value), two for bfloat16 (13 bits: its own
+// elements carry 8).
+template <typename XT> __host__ __device__ constexpr int gm_planes_of() { return sizeof(XT) == 2 ? 2 : 3; }
+__host__ inline int gm_planes(const cb_qdense_desc& d) { return d.x_dtype == CB_BF16 ? 2 : 3; }
+__host__ __device__ constexpr int gm_tiles(int M, int planes) { return (planes * M + 7) / 8; }   // 8-column tiles of (plane, row) columns
 
 __device__ __forceinline__ void gm_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
@@ -111,8 +116,8 @@ template <> __device__ __forceinline__ float4 gd_x4<__nv_bfloat16>(const __nv_bf
 }
 
 // digits [cols][K] int8 with column = plane * M + m; dsum [K / 32][cols] float = the sum of a block's digits (written
-// when the format has a per-block minimum); units [M] float.  `cols` is 3 M rounded up to whole 8-column tiles: the
-// columns past 3 M are never written and whatever they hold only reaches results that are dropped.
+// when the format has a per-block minimum); units [M] float.  `cols` is (planes x M) rounded up to whole 8-column tiles: the
+// columns past planes x M are never written and whatever they hold only reaches results that are dropped.
 template <typename XT>
 __global__ void __launch_bounds__(GD_THREADS)
 ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int8_t* __restrict__ digits, float* __restrict__ dsum, float* __restrict__ units) {
@@ -149,10 +154,11 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int
   __syncthreads();
   mx = 0;
   for (int w = 0; w < GD_THREADS / 32; w++) mx = max(mx, s_mx[w]);
-  // |x| < 2^ex; shift so that |x| * 2^shift <= 2^20 (three signed base-128 digits)
+  // |x| < 2^ex; shift so that |x| * 2^shift <= 2^QBITS (PL signed base-128 digits)
+  constexpr int PL = gm_planes_of<XT>(), QBITS = 7 * PL - 1;
   const int ef = (int)(mx >> 23);
   const int ex = ef > 0 ? ef - 126 : (32 - __clz(mx)) - 149;
-  const int shift = min(20 - ex, 149);
+  const int shift = min(QBITS - ex, 149);
   const int sh1 = shift / 2, sh2 = shift - sh1;
   const float p1 = __int_as_float((127 + sh1) << 23), p2 = __int_as_float((127 + sh2) << 23);
   if (threadIdx.x == 0) {
@@ -169,17 +175,17 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int
     for (int e = 0; e < 4; e++) {
       float v = vv[e];
       if ((__float_as_uint(v) & 0x7FFFFFFFu) >= 0x7F800000u) v = 0.0f;
-      const int q = (int)(__float_as_uint(fmaf(v * p1, p2, 12582912.0f)) - 0x4B400000u);     // round to nearest, |q| <= 2^20
+      const int q = (int)(__float_as_uint(fmaf(v * p1, p2, 12582912.0f)) - 0x4B400000u);     // round to nearest, |q| <= 2^QBITS
       const int a = ((q + 64) & 127) - 64;
       const int q1 = (q - a) >> 7;
-      const int b = ((q1 + 64) & 127) - 64;
-      const int c = (q1 - b) >> 7;
+      const int b = PL == 2 ? q1 : ((q1 + 64) & 127) - 64;    // two planes: |q1| <= 64 is the top digit
+      const int c = PL == 2 ? 0 : (q1 - b) >> 7;
       w0 |= (uint32_t)(a & 0xFF) << (8 * e); w1 |= (uint32_t)(b & 0xFF) << (8 * e); w2 |= (uint32_t)(c & 0xFF) << (8 * e);
       s0 += a; s1 += b; s2 += c;
     }
     *reinterpret_cast<uint32_t*>(digits + ((int64_t)0 * M + m) * K + k) = w0;
     *reinterpret_cast<uint32_t*>(digits + ((int64_t)1 * M + m) * K + k) = w1;
-    *reinterpret_cast<uint32_t*>(digits + ((int64_t)2 * M + m) * K + k) = w2;
+    if (PL == 3) *reinterpret_cast<uint32_t*>(digits + ((int64_t)2 * M + m) * K + k) = w2;
     if (dsum) {
 #pragma unroll
       for (int d = 1; d < 8; d <<= 1) {
@@ -187,7 +193,8 @@ ggml_row_digits_kernel(const XT* __restrict__ x, int M, int64_t K, int cols, int
       }
       if ((threadIdx.x & 7) == 0) {
         float* o = dsum + (k / 32) * cols;
-        o[0 * M + m] = (float)s0; o[1 * M + m] = (float)s1; o[2 * M + m] = (float)s2;
+        o[0 * M + m] = (float)s0; o[1 * M + m] = (float)s1;
+        if (PL == 3) o[2 * M + m] = (float)s2;
       }
     }
   };
@@ -229,7 +236,8 @@ ggml_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __rest
   uint64_t* bars = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + warp * GM_STAGES;
   uint64_t* bar_digits = reinterpret_cast<uint64_t*>(gm_smem + GM_WARPS * GM_STAGES * STAGE) + GM_WARPS * GM_STAGES;
   unsigned char* dsm = gm_smem + GM_WARPS * GM_STAGES * STAGE + GM_BAR_BYTES;     // [3 M columns][K + 32] when BSMEM
-  const int ncols = 3 * M;
+  constexpr int PL = gm_planes_of<XT>();
+  const int ncols = PL * M;
   const int64_t dpitch = K + GM_DPAD;
 
   // The ring: lane 0 asks for one tile per step - the warp's 16 rows by the step's bytes of each - and the stage's
@@ -431,7 +439,7 @@ ggml_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __rest
     if (r >= 16 * n_groups || n >= N) continue;
     float v = 0.0f;
 #pragma unroll
-    for (int pl = 2; pl >= 0; pl--) {                          // smallest plane last: unit * (A0 + 128 A1 + 16384 A2)
+    for (int pl = PL - 1; pl >= 0; pl--) {                     // smallest plane last: unit * (A0 + 128 A1 (+ 16384 A2))
       const int c = pl * M + m;
       const float a = part[(0 * GM_ROWS + r) * GM_MAX_COLS + c] + part[(1 * GM_ROWS + r) * GM_MAX_COLS + c];
       v = fmaf(v, 128.0f, a);
@@ -446,8 +454,8 @@ size_t gm_smem_bytes(int ggml) {      // the rings and their barriers; the excha
   static_assert((size_t)GM_WARPS * GM_STAGES * gm_stage_bytes(CB_GGML_Q4_0) >= (size_t)2 * GM_ROWS * GM_MAX_COLS * sizeof(float), "exchange buffer");
   return (size_t)GM_WARPS * GM_STAGES * gm_stage_bytes(ggml) + GM_BAR_BYTES;
 }
-size_t gm_digit_smem(int64_t M, int64_t K) { return (size_t)(3 * M) * (size_t)(K + GM_DPAD); }
-bool gm_digits_resident(int ggml, int64_t M, int64_t K) { return gm_smem_bytes(ggml) + gm_digit_smem(M, K) <= GM_SMEM_CTA; }
+size_t gm_digit_smem(int64_t M, int64_t K, int planes) { return (size_t)(planes * M) * (size_t)(K + GM_DPAD); }
+bool gm_digits_resident(int ggml, int64_t M, int64_t K, int planes) { return gm_smem_bytes(ggml) + gm_digit_smem(M, K, planes) <= GM_SMEM_CTA; }
 
 // The weights as a matrix of 32-bit words [N rows][bytes per row / 4], in boxes of 16 rows by one step (plus, for Q4_K,
 // four words of the next).  Encoding is a pure function of its arguments and a decode loop asks for the same few maps
@@ -478,8 +486,8 @@ static size_t gm_align(size_t b) { return (b + 255) & ~(size_t)255; }
 // The first 256 bytes hold the status words (zeroed when the workspace is prepared).
 constexpr size_t GM_HEADER = 256;
 struct GmLayout { size_t off_digits, off_dsum, off_units, total; };
-GmLayout gm_layout(int64_t M, int64_t K) {
-  const size_t cols = 8 * (size_t)gm_tiles((int)M);
+GmLayout gm_layout(int64_t M, int64_t K, int planes) {
+  const size_t cols = 8 * (size_t)gm_tiles((int)M, planes);
   GmLayout l;
   l.off_digits = GM_HEADER;
   l.off_dsum = l.off_digits + gm_align(cols * (size_t)K) + 256;
@@ -510,12 +518,12 @@ int gm_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
   static std::atomic<bool> configured[64];
   int dev = 0;
   CB_CUDA(cudaGetDevice(&dev));
-  const size_t smem = std::max(gm_smem_bytes(GGML) + (BSMEM ? gm_digit_smem(d.M, d.K) : 0), GM_SMEM_FLOOR);
+  const size_t smem = std::max(gm_smem_bytes(GGML) + (BSMEM ? gm_digit_smem(d.M, d.K, gm_planes(d)) : 0), GM_SMEM_FLOOR);
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
     CB_CUDA(cudaFuncSetAttribute(ggml_mma_kernel<XT, GGML, NT, BSMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM_CTA));
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  const GmLayout l = gm_layout(d.M, d.K);
+  const GmLayout l = gm_layout(d.M, d.K, gm_planes(d));
   CUtensorMap tmap;
   CB_TRY(gm_encode(&tmap, in[1], (uint64_t)(d.K / (GGML == CB_GGML_Q4_K ? 256 : 32) * gm_block_bytes(GGML)), (uint64_t)d.N, (uint32_t)gm_pitch(GGML)));
   uint8_t* w8 = (uint8_t*)ws;
@@ -533,8 +541,8 @@ int gm_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
 
 template <typename XT, int GGML>
 int gm_launch_n(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
-  const bool resident = gm_digits_resident(GGML, d.M, d.K);
-  switch (gm_tiles((int)d.M)) {
+  const bool resident = gm_digits_resident(GGML, d.M, d.K, gm_planes(d));
+  switch (gm_tiles((int)d.M, gm_planes(d))) {
     case 1: return resident ? gm_launch_k<XT, GGML, 1, true>(d, n_sm, in, out, ws, s) : gm_launch_k<XT, GGML, 1, false>(d, n_sm, in, out, ws, s);
     case 2: return resident ? gm_launch_k<XT, GGML, 2, true>(d, n_sm, in, out, ws, s) : gm_launch_k<XT, GGML, 2, false>(d, n_sm, in, out, ws, s);
     case 3: return gm_launch_k<XT, GGML, 3, false>(d, n_sm, in, out, ws, s);
@@ -567,9 +575,10 @@ void qdense_ggml_mma_plan(cb_plan* p, const char* type_name) {
   p->blocks = gm_grid(d.N, p->n_sm);
   p->threads = GM_WARPS * 32;
   const int64_t m16 = std::min<int64_t>(d.M, 16);
-  p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)m16) <= 2 && gm_digits_resident(d.ggml_type, m16, d.K) ? gm_digit_smem(m16, d.K) : 0),
+  const int pl = gm_planes(d);
+  p->dyn_smem = (int)std::max(gm_smem_bytes(d.ggml_type) + (gm_tiles((int)m16, pl) <= 2 && gm_digits_resident(d.ggml_type, m16, d.K, pl) ? gm_digit_smem(m16, d.K, pl) : 0),
                               GM_SMEM_FLOOR);
-  p->workspace_bytes = gm_layout(std::min<int64_t>(d.M, 16), d.K).total;
+  p->workspace_bytes = gm_layout(std::min<int64_t>(d.M, 16), d.K, gm_planes(d)).total;
   p->counter_bytes = GM_HEADER;
   p->has_status = true;
   p->name = std::string("qdense_ggml_mma_") + (d.x_dtype == CB_BF16 ? "bf16_" : "f32_") + type_name;
