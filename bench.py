@@ -209,6 +209,71 @@ def other_kernels(dv, dev, stream):
     return res
 
 
+def weight_format_legs(dv, dev, stream):
+    """The same 4096 x 14336 projection with the other weight formats of the op (GGML blocks, packed NF4 / Int4 with the
+    reference's [K, N/64] scales), float32 activations as the reference takes them: decode at M = 1 and 16 over eight
+    copies of the weights used in turn (more bytes than the L2 holds between two uses of a copy), and 2048 rows at once.
+    Random block bytes with a finite half-precision scale in every block."""
+    hpeak, _ = measured_peak()
+    rng = np.random.default_rng(17)
+    K, N, copies = K_DIM, N_DIM, 8
+    res = {}
+
+    def timed(plan, x, ws_list, extra, y, reps):
+        ws = plan.new_workspace()
+        e0, e1 = dv.Event(dev), dv.Event(dev)
+        for it in range(reps + 2):
+            if it == 2:
+                e0.record(stream)
+            for w in ws_list:
+                plan.launch([x.ptr, w.ptr] + extra, [y.ptr], ws.ptr if ws else None, stream)
+        e1.record(stream)
+        stream.sync()
+        plan.check_status(ws.ptr if ws else None)
+        if ws:
+            ws.free()
+        return e0.elapsed_ms(e1) * 1e3 / (reps * len(ws_list))
+
+    xs = {M: dv.DeviceMem.from_numpy(rng.standard_normal((M, K)).astype(np.float32), dev) for M in (1, 16, 2048)}
+    y = dv.DeviceMem(2048 * N * 4, dev)
+    formats = (("q4_0", dv.GGML_Q4_0, 32, 18, (0,)), ("q8_0", dv.GGML_Q8_0, 32, 34, (0,)), ("iq4_nl", dv.GGML_IQ4_NL, 32, 18, (0,)),
+               ("q4_k", dv.GGML_Q4_K, 256, 144, (0, 2)), ("q6_k", dv.GGML_Q6_K, 256, 210, (208,)))
+    for name, gt, values, bb, scale_at in formats:
+        blocks = rng.integers(0, 256, size=(N, K // values, bb), dtype=np.uint8)
+        for o in scale_at:
+            blocks[:, :, o:o + 2] = np.frombuffer(np.float16(0.03125).tobytes(), np.uint8)
+        wbufs = [dv.DeviceMem.from_numpy(blocks.reshape(N, -1), dev) for _ in range(copies)]
+        leg = {"weight_bytes": int(blocks.nbytes)}
+        for M in (1, 16, 2048):
+            plan = dv.Plan.qdense(M, K, N, dv.F32, dv.U8, scheme=dv.QUANT_GGML, ggml_type=gt, dev=dev)
+            us = timed(plan, xs[M], wbufs if M <= 16 else wbufs[:1], [], y, 5)
+            leg[f"M{M}"] = {"kernel": plan.kernel_name, "us": us}
+            if M <= 16:
+                leg[f"M{M}"]["frac_of_measured_hbm"] = blocks.nbytes / us / 1e3 / hpeak
+            else:
+                leg[f"M{M}"]["TFLOP/s"] = 2.0 * M * K * N / us / 1e6
+        res["ggml_" + name] = leg
+        for w in wbufs:
+            w.free()
+    nblk = N // 64
+    sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=K * nblk).astype(np.float32), dev)
+    wbufs = [dv.DeviceMem.from_numpy(rng.integers(0, 256, size=K * N // 2, dtype=np.uint8), dev) for _ in range(copies)]
+    for name, scheme, wd in (("nf4_packed", dv.QUANT_NF4, dv.U4), ("int4_packed", dv.QUANT_LINEAR, dv.I4)):
+        leg = {"weight_and_scale_bytes": K * N // 2 + K * nblk * 4}
+        for M in (1, 16, 2048):
+            plan = dv.Plan.qdense(M, K, N, dv.F32, wd, dv.SCALE_REF, 64, scheme=scheme, dev=dev)
+            us = timed(plan, xs[M], wbufs if M <= 16 else wbufs[:1], [sc.ptr], y, 5)
+            leg[f"M{M}"] = {"kernel": plan.kernel_name, "us": us}
+            if M <= 16:
+                leg[f"M{M}"]["frac_of_measured_hbm"] = leg["weight_and_scale_bytes"] / us / 1e3 / hpeak
+            else:
+                leg[f"M{M}"]["TFLOP/s"] = 2.0 * M * K * N / us / 1e6
+        res[name] = leg
+    for m in [sc, y] + wbufs + list(xs.values()):
+        m.free()
+    return res
+
+
 def sdpa_leg(dv, dev, stream, hq, hkv, tpeak, check=False):
     """Causal SDPA of the fourth configuration restricted to `hq` query heads / `hkv` KV heads (all of them on one GPU,
     a KV-head group per rank when sharded: attention of a (batch, KV head) pair reads no other head).  With `check`
@@ -803,6 +868,7 @@ def main():
                 p2.check_status(ws2.ptr)
             out["other_decode_batches"] = extra
             out["other_path_kernels"] = other_kernels(dv, dev, stream)
+            out["other_weight_formats"] = weight_format_legs(dv, dev, stream)
             out["decoder_block"] = decoder_block_legs()
         if not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(M)
