@@ -174,6 +174,28 @@ template <> struct Scalar<__half> {
   __device__ static void store(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
 };
 
+// A launch that may be scheduled while the kernel before it in the stream is still running (programmatic dependent
+// launch): the kernel must execute pdl_enter() before it reads or writes memory.  pdl_enter also lets the kernel after
+// this one be scheduled early, under the same condition.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // fusedDenseApplyActivation (internal/gobackend/fusedops/dense.go:176-205) in f32.
 __device__ inline float apply_activation(float x, int act) {
   switch (act) {

@@ -45,6 +45,7 @@ template <typename A> __device__ __forceinline__ A ew_unary_f(A x, int op) {
 template <typename T>
 __global__ void binary_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out, int rank,
                               Idx8 out_dims, Idx8 ls, Idx8 rs, int64_t n, int op, int same) {
+  pdl_enter();
   typedef typename EwT<T>::acc A;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     int64_t li = i, ri = i;
@@ -90,6 +91,7 @@ __global__ void binary_int_kernel(const T* __restrict__ lhs, const T* __restrict
 
 template <typename T>
 __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int op) {
+  pdl_enter();
   typedef typename EwT<T>::acc A;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     Scalar<T>::store(out, i, ew_unary_f<A>((A)Scalar<T>::load(x, i), op));
@@ -161,6 +163,7 @@ constexpr int RMS_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, int64_t rows, int64_t L, float eps) {
+  pdl_enter();
   __shared__ float s_part[RMS_THREADS / 32];
   __shared__ float s_inv;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -208,6 +211,7 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restri
 template <typename T, int NV, int WPR>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, int64_t rows, int64_t L, float eps) {
+  pdl_enter();
   constexpr int VEC = 16 / (int)sizeof(T);
   constexpr int RPB = RMS_THREADS / 32 / WPR;             // rows per block and pass
   __shared__ float s_part[RPB][WPR];
@@ -263,6 +267,7 @@ rmsnorm_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, T* __re
 template <>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel<double>(const double* __restrict__ x, const double* __restrict__ gamma, double* __restrict__ out, int64_t rows, int64_t L, float eps) {
+  pdl_enter();
   __shared__ double s_part[RMS_THREADS / 32];
   __shared__ double s_inv;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -408,7 +413,8 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
       else if (h.dtype == CB_I64) binary_int_kernel<int64_t><<<p->blocks, 256, 0, s>>>((const int64_t*)in[0], (const int64_t*)in[1], (int64_t*)out[0], h.rank, od, ls, rs, h.n, h.axis);
       else CB_TRY(by_float(h.dtype, "binary op", [&](auto* t) {
         typedef typename std::remove_pointer<decltype(t)>::type T;
-        binary_kernel<T><<<p->blocks, 256, 0, s>>>((const T*)in[0], (const T*)in[1], (T*)out[0], h.rank, od, ls, rs, h.n, h.axis, same ? 1 : 0);
+        CB_CUDA(launch_dependent(binary_kernel<T>, dim3(p->blocks), dim3(256), 0, s, (const T*)in[0], (const T*)in[1], (T*)out[0], (int)h.rank, od, ls, rs,
+                                 (int64_t)h.n, (int)h.axis, same ? 1 : 0));
         return (int)CB_OK;
       }));
       break;
@@ -416,7 +422,7 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
     case PLAN_UNARY:
       CB_TRY(by_float(h.dtype, "unary op", [&](auto* t) {
         typedef typename std::remove_pointer<decltype(t)>::type T;
-        unary_kernel<T><<<p->blocks, 256, 0, s>>>((const T*)in[0], (T*)out[0], h.n, h.axis);
+        CB_CUDA(launch_dependent(unary_kernel<T>, dim3(p->blocks), dim3(256), 0, s, (const T*)in[0], (T*)out[0], (int64_t)h.n, (int)h.axis));
         return (int)CB_OK;
       }));
       break;
@@ -469,7 +475,8 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
             const int64_t want = (h.dims[0] + rpb - 1) / rpb;
             const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)p->n_sm * 8));
             auto go = [&](auto nv, auto w) {
-              rmsnorm_vec_kernel<T, decltype(nv)::value, decltype(w)::value><<<grid, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], L, (float)h.eps);
+              launch_dependent(rmsnorm_vec_kernel<T, decltype(nv)::value, decltype(w)::value>, dim3(grid), dim3(RMS_THREADS), 0, s, (const T*)in[0], g, (T*)out[0],
+                               (int64_t)h.dims[0], L, (float)h.eps);
             };
             auto by_nv = [&](auto w) {
               if (per_lane <= 1) go(std::integral_constant<int, 1>(), w); else if (per_lane <= 2) go(std::integral_constant<int, 2>(), w);
@@ -479,7 +486,8 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
             return (int)CB_OK;
           }
         }
-        rmsnorm_kernel<T><<<p->blocks, RMS_THREADS, 0, s>>>((const T*)in[0], g, (T*)out[0], h.dims[0], h.dims[1], (float)h.eps);
+        CB_CUDA(launch_dependent(rmsnorm_kernel<T>, dim3(p->blocks), dim3(RMS_THREADS), 0, s, (const T*)in[0], g, (T*)out[0], (int64_t)h.dims[0], (int64_t)h.dims[1],
+                                 (float)h.eps));
         return (int)CB_OK;
       }));
       break;

@@ -76,6 +76,7 @@ __device__ __forceinline__ void sd_cp16(uint32_t dst, const void* src, bool vali
 template <typename T, int D, bool HI>
 __global__ void __launch_bounds__(SD_THREADS, 2)
 sdpa_decode_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const SdParams p) {
+  pdl_enter();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int ROWB = D * 2;                     // bytes per row
   constexpr int STAGE = 2 * SD_STEP * ROWB;       // K rows, then V rows
@@ -254,6 +255,7 @@ sdpa_decode_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
 // (sdpa.go:471-474).  One block of D threads per query row.
 template <typename T>
 __global__ void sdpa_decode_merge_kernel(T* __restrict__ out, const SdParams p) {
+  pdl_enter();
   const int r = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
   const long long base = (((long long)b * p.Hkv + kvh) * p.splits) * p.rows + r;
   float mm = -INFINITY;
@@ -351,8 +353,7 @@ static int sd_launch_k(const SdParams& s, const T* q, const T* k, const T* v, cu
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   dim3 grid((unsigned)s.splits, (unsigned)s.Hkv, (unsigned)s.B);
-  sdpa_decode_kernel<T, D, HI><<<grid, SD_THREADS, smem, st>>>(q, k, v, s);
-  CB_CUDA(cudaGetLastError());
+  CB_CUDA(launch_dependent(sdpa_decode_kernel<T, D, HI>, grid, dim3(SD_THREADS), smem, st, q, k, v, s));
   return CB_OK;
 }
 
@@ -360,8 +361,7 @@ template <typename T, int D>
 static int sd_launch_t(const SdParams& s, const T* q, const T* k, const T* v, T* out, cudaStream_t st) {
   const int rc = s.rows <= 8 ? sd_launch_k<T, D, false>(s, q, k, v, st) : sd_launch_k<T, D, true>(s, q, k, v, st);
   if (rc != CB_OK) return rc;
-  sdpa_decode_merge_kernel<T><<<dim3((unsigned)s.rows, (unsigned)s.Hkv, (unsigned)s.B), (unsigned)s.D, 0, st>>>(out, s);
-  CB_CUDA(cudaGetLastError());
+  CB_CUDA(launch_dependent(sdpa_decode_merge_kernel<T>, dim3((unsigned)s.rows, (unsigned)s.Hkv, (unsigned)s.B), dim3((unsigned)s.D), 0, st, out, s));
   return CB_OK;
 }
 
