@@ -63,6 +63,24 @@ __global__ void binary_kernel(const T* __restrict__ lhs, const T* __restrict__ r
     Scalar<T>::store(out, i, ew_binary<A>(a, b, op));
   }
 }
+// Both operands of the output's shape, 16-byte aligned, a whole number of 16-byte vectors: a thread takes whole vectors,
+// all its loads issued before the first use.  The arithmetic is the scalar kernel's (same conversions, same rounding).
+template <typename T>
+__global__ void __launch_bounds__(256)
+binary_vec_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out, int64_t n_vec, int op) {
+  pdl_enter();
+  typedef typename EwT<T>::acc A;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  union V { uint4 u; T e[VEC]; };
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    V a, b, r;
+    a.u = __ldg(reinterpret_cast<const uint4*>(lhs) + i);
+    b.u = __ldg(reinterpret_cast<const uint4*>(rhs) + i);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) Scalar<T>::store(r.e, e, ew_binary<A>((A)Scalar<T>::load(a.e, e), (A)Scalar<T>::load(b.e, e), op));
+    reinterpret_cast<uint4*>(out)[i] = r.u;
+  }
+}
 // integer flavour: no Scalar<> specialisations exist for the integer types
 template <typename T>
 __global__ void binary_int_kernel(const T* __restrict__ lhs, const T* __restrict__ rhs, T* __restrict__ out, int rank,
@@ -413,6 +431,14 @@ int elementwise_launch(const cb_plan* p, const void* const* in, void* const* out
       else if (h.dtype == CB_I64) binary_int_kernel<int64_t><<<p->blocks, 256, 0, s>>>((const int64_t*)in[0], (const int64_t*)in[1], (int64_t*)out[0], h.rank, od, ls, rs, h.n, h.axis);
       else CB_TRY(by_float(h.dtype, "binary op", [&](auto* t) {
         typedef typename std::remove_pointer<decltype(t)>::type T;
+        constexpr int VEC = 16 / (int)sizeof(T);
+        const bool aligned = !((reinterpret_cast<uintptr_t>(in[0]) | reinterpret_cast<uintptr_t>(in[1]) | reinterpret_cast<uintptr_t>(out[0])) & 15);
+        if (same && aligned && h.n % VEC == 0 && h.n > 0) {
+          const int64_t n_vec = h.n / VEC;
+          CB_CUDA(launch_dependent(binary_vec_kernel<T>, dim3((unsigned)ew_grid(n_vec)), dim3(256), 0, s, (const T*)in[0], (const T*)in[1], (T*)out[0], n_vec,
+                                   (int)h.axis));
+          return (int)CB_OK;
+        }
         CB_CUDA(launch_dependent(binary_kernel<T>, dim3(p->blocks), dim3(256), 0, s, (const T*)in[0], (const T*)in[1], (T*)out[0], (int)h.rank, od, ls, rs,
                                  (int64_t)h.n, (int)h.axis, same ? 1 : 0));
         return (int)CB_OK;
