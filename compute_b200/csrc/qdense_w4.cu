@@ -1,4 +1,6 @@
-// Packed 4-bit weights (Int4 / Uint4 Linear, NF4) for decode shapes: M <= 16, reference scales [K, N / block].
+// Weights with the reference's scale layout [K, N / block] for decode shapes: packed 4-bit (Int4 / Uint4 Linear, NF4)
+// and 8-bit (Int8 / Uint8 Linear, NF4 indices one per byte).  The 8-bit formats with compact scales have their own
+// tensor-core kernel; this one is what a caller of the reference's interface gets when the scales are per row of W.
 // Reference arithmetic: internal/gobackend/fusedops/quantizeddense.go:586-650 (per output column, k ascending:
 // x * w * scale, or x * (w * scale + zero point)); nibble order internal/gobackend/ops/convertdtype.go:199-226.
 //
@@ -9,6 +11,8 @@
 // registers; the rows of W go round the eight warps of a CTA, and the K range is cut over gridDim.z CTAs, so that
 // three to four CTAs fill every SM.  Partial sums meet in shared memory (fixed order), then in a workspace
 // [cut][M][N]; a second small kernel adds the cuts in order, the bias and the activation.
+//
+// With 8-bit weights a word holds four columns and a CTA owns 128; everything else is the same.
 //
 // A nibble becomes a float without a conversion: its four bits go to the top of the mantissa of 1.0, which is
 // 1 + n / 16 (for Int4 the nibble's top bit is flipped first: n ^ 8 = n + 8).  The sums run over those floats and the
@@ -29,9 +33,10 @@ constexpr size_t W4_HEADER = 256;          // status words at the start of the w
 // Up to this many rows of x the kernel runs once per 16 rows: two runs of 94 us beat expanding the weights to bf16
 // planes for the GEMM (about 265 us whatever M on the 4096 x 14336 projection).
 constexpr int W4_MAX_M = 32;
-constexpr int W4_COLS = 256;               // columns per CTA: 32 lanes x 8
 __host__ __device__ constexpr int w4_unroll(int mr) { return mr >= 8 ? 4 : 8; }   // rows of W a lane has in flight
-enum { W4_U4 = 0, W4_I4 = 1, W4_NF4 = 2 };
+enum { W4_U4 = 0, W4_I4 = 1, W4_NF4 = 2, W8_U8 = 3, W8_I8 = 4, W8_NF4 = 5 };
+__host__ __device__ constexpr int w4_vpw(int mode) { return mode >= W8_U8 ? 4 : 8; }         // weights per 32-bit word
+__host__ __device__ constexpr int w4_cols(int mode) { return 32 * w4_vpw(mode); }           // columns per CTA: a word per lane
 
 // NormalFloat4 (fused_ops.go:114-121)
 __constant__ float kW4Nf4[16] = {
@@ -41,14 +46,18 @@ __constant__ float kW4Nf4[16] = {
     0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
 
 // shared memory before the barriers: x of the cut, then the reduction buffer with, in the TMA form, the ring under it
-__host__ __device__ constexpr size_t w4_data_bytes(int mr, int rows_max, bool tma) {
-  const size_t xs = (size_t)mr * rows_max * 4, red = (size_t)W4_WARPS * mr * W4_COLS * 4, ring = (size_t)W4_STAGES * W4_WARPS * w4_unroll(mr) * 128;
+__host__ __device__ constexpr size_t w4_data_bytes(int mr, int rows_max, bool tma, int cols) {
+  const size_t xs = (size_t)mr * rows_max * 4, red = (size_t)W4_WARPS * mr * cols * 4, ring = (size_t)W4_STAGES * W4_WARPS * w4_unroll(mr) * 128;
   return xs + (tma && ring > red ? ring : red);
 }
 
 template <int MODE>
 __device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut) {
   if (MODE == W4_NF4) return lut[(word >> (4 * i)) & 0xFu];
+  if (MODE == W8_NF4) return lut[(word >> (8 * i)) & 0xFu];
+  // a byte under the exponent of 2^23 is 2^23 + b; signed bytes are biased by 128 first
+  if (MODE == W8_U8) return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650u | i)) - 8388608.0f;
+  if (MODE == W8_I8) return __uint_as_float(__byte_perm(word ^ 0x80808080u, 0x4B000000u, 0x7650u | i)) - 8388736.0f;
   const uint32_t at19 = 4 * i <= 19 ? word << (19 - 4 * i) : word >> (4 * i - 19);
   return __uint_as_float((at19 & 0x00780000u) ^ (MODE == W4_I4 ? 0x3FC00000u : 0x3F800000u));
 }
@@ -65,13 +74,15 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
                  const float* __restrict__ scales, const float* __restrict__ zps, float* __restrict__ partial, unsigned* __restrict__ status,
                  int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
   constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL, STAGE = GROUP * 128;
+  constexpr int VPW = w4_vpw(MODE), COLS = w4_cols(MODE);
+  constexpr bool TABLE = MODE == W4_NF4 || MODE == W8_NF4, DIRECT = MODE >= W4_NF4;          // DIRECT: w4_value is the weight itself
   // the kernel that adds the cuts may be scheduled now; it waits for this grid before it reads the partial sums
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(1024) unsigned char w4_smem[];
   float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_max]
-  float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][W4_COLS]; the ring lies under it
+  float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][COLS]; the ring lies under it
   const uint32_t* ring = reinterpret_cast<const uint32_t*>(red);               // [W4_STAGES][GROUP][32 words]
-  uint64_t* full = reinterpret_cast<uint64_t*>(w4_smem + w4_data_bytes(MR, rows_max, TMA));
+  uint64_t* full = reinterpret_cast<uint64_t*>(w4_smem + w4_data_bytes(MR, rows_max, TMA, COLS));
   uint64_t* empty = full + W4_STAGES;
   __shared__ float lut[16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -86,21 +97,21 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
   const int64_t k0 = g0 * GROUP;
   const int kc = (int)(min(K, g1 * GROUP) - k0);                               // rows of this cut
   const int n_groups = (int)(g1 - g0);
-  const int64_t n0 = (int64_t)blockIdx.y * W4_COLS + lane * 8;
+  const int64_t n0 = (int64_t)blockIdx.y * COLS + lane * VPW;
   const bool active = n0 < N;
-  if (MODE == W4_NF4 && threadIdx.x < 16) lut[threadIdx.x] = kW4Nf4[threadIdx.x];
+  if (TABLE && threadIdx.x < 16) lut[threadIdx.x] = kW4Nf4[threadIdx.x];
   for (int idx = threadIdx.x; idx < MR * rows_max; idx += blockDim.x) {
     const int m = idx / rows_max, kk = idx % rows_max;
     xs[idx] = (m0 + m < M && kk < kc) ? (float)Scalar<XT>::load(x, (int64_t)(m0 + m) * K + k0 + kk) : 0.0f;
   }
   __syncthreads();
 
-  float acc[MR][8], sx[MR], zacc[MR];
+  float acc[MR][VPW], sx[MR], zacc[MR];
 #pragma unroll
   for (int m = 0; m < MR; m++) {
     sx[m] = 0.0f; zacc[m] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) acc[m][i] = 0.0f;
+    for (int i = 0; i < VPW; i++) acc[m][i] = 0.0f;
   }
   bool failed = false;
   int issued = 0;                                                              // tiles asked for (thread 0 only)
@@ -110,7 +121,7 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
     const int slot = g % W4_STAGES, round = g / W4_STAGES;
     if (round > 0 && !tc::mbar_wait(&empty[slot], (uint32_t)((round - 1) & 1))) return false;
     tc::mbar_expect_tx(&full[slot], STAGE);
-    tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * (W4_COLS / 8)), (int)(k0 + (int64_t)g * GROUP),
+    tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * 32), (int)(k0 + (int64_t)g * GROUP),
                     &full[slot]);
     issued = g + 1;
     return true;
@@ -118,10 +129,10 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
   if (TMA && threadIdx.x == 0)
     for (int g = 0; g < min(n_groups, W4_STAGES - 1); g++) ask(g);
   if ((TMA || active) && n_groups > 0) {
-    const int64_t wrow = N / 8;                                                // words per row of W
+    const int64_t wrow = N / VPW;                                              // words per row of W
     const int64_t n0s = active ? n0 : 0;                                       // lanes past N (TMA form) work on zeros of column 0's scales
     // this warp's rows of a group: warp, warp + 8, ...; the next group is requested before this one is consumed
-    const uint32_t* wq = w + (k0 + warp) * wrow + n0s / 8;
+    const uint32_t* wq = w + (k0 + warp) * wrow + n0s / VPW;
     const float* sq = scales + (k0 + warp) * nblk + n0s / block;
     const float* zq = ZP ? zps + (k0 + warp) * nblk + n0s / block : nullptr;
     const int64_t w8 = W4_WARPS * wrow, s8 = W4_WARPS * nblk;
@@ -163,17 +174,17 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
       if (g + 1 < n_groups) request(g + 1);
 #pragma unroll
       for (int u = 0; u < W4_UNROLL; u++) {
-        float f[8];
+        float f[VPW];
 #pragma unroll
-        for (int i = 0; i < 8; i++) f[i] = w4_value<MODE>(wv[u], i, lut);
+        for (int i = 0; i < VPW; i++) f[i] = w4_value<MODE>(wv[u], i, lut);
 #pragma unroll
         for (int m = 0; m < MR; m++) {
           const float xv = xr[m * rows_max + u * W4_WARPS];                    // rows past K hold 0 here and scale 0
           const float xsv = xv * sv[u];
-          if (MODE != W4_NF4) sx[m] += xsv;
+          if (!DIRECT) sx[m] += xsv;
           if (ZP) zacc[m] = fmaf(xv, zv[u], zacc[m]);
 #pragma unroll
-          for (int i = 0; i < 8; i++) acc[m][i] = fmaf(xsv, f[i], acc[m][i]);
+          for (int i = 0; i < VPW; i++) acc[m][i] = fmaf(xsv, f[i], acc[m][i]);
         }
       }
       xr += GROUP;
@@ -191,26 +202,26 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
   // ---- the eight warps' sums, added in warp order
 #pragma unroll
   for (int m = 0; m < MR; m++) {
-    float v[8];
+    float v[VPW];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < VPW; i++) {
       // Uint4: n = 16 (f - 1); Int4: n = 16 (f - 1) - 8, f built from the nibble with its top bit flipped
-      v[i] = MODE == W4_NF4 ? acc[m][i] : MODE == W4_U4 ? 16.0f * (acc[m][i] - sx[m]) : fmaf(16.0f, acc[m][i], -24.0f * sx[m]);
+      v[i] = DIRECT ? acc[m][i] : MODE == W4_U4 ? 16.0f * (acc[m][i] - sx[m]) : fmaf(16.0f, acc[m][i], -24.0f * sx[m]);
       v[i] += zacc[m];
     }
-    float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * MR + m) * W4_COLS + lane * 8);
-    dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-    dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * MR + m) * COLS + lane * VPW);
+#pragma unroll
+    for (int q = 0; q < VPW / 4; q++) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
   }
   __syncthreads();
-  const int64_t n = (int64_t)blockIdx.y * W4_COLS + threadIdx.x;
-  if (n < N) {
+  const int64_t n = (int64_t)blockIdx.y * COLS + threadIdx.x;
+  if (n < N && threadIdx.x < COLS) {
 #pragma unroll
     for (int m = 0; m < MR; m++) {
       if (m0 + m >= M) break;
       float v = 0.0f;
 #pragma unroll
-      for (int wq = 0; wq < W4_WARPS; wq++) v += red[((size_t)wq * MR + m) * W4_COLS + threadIdx.x];
+      for (int wq = 0; wq < W4_WARPS; wq++) v += red[((size_t)wq * MR + m) * COLS + threadIdx.x];
       partial[((int64_t)blockIdx.z * M + m0 + m) * N + n] = v;
     }
   }
@@ -229,6 +240,9 @@ qdense_w4_finish_kernel(const float* __restrict__ partial, const float* __restri
 }
 
 int w4_rows(const cb_qdense_desc& d) { return d.M <= 1 ? 1 : d.M <= 2 ? 2 : d.M <= 4 ? 4 : 8; }
+bool w4_packed(const cb_qdense_desc& d) { return d.w_dtype == CB_I4 || d.w_dtype == CB_U4; }
+int w4_desc_vpw(const cb_qdense_desc& d) { return w4_packed(d) ? 8 : 4; }
+int w4_desc_cols(const cb_qdense_desc& d) { return 32 * w4_desc_vpw(d); }
 
 // How K is cut.  A CTA costs a fixed set-up and a reduction, so few long CTAs beat many short ones, but the CTAs must
 // fill whole waves: with `slots` CTAs resident on the GPU at once, the cut count that fills one wave best is taken when
@@ -237,7 +251,8 @@ void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   const int mr = w4_rows(d);
   const int group = W4_WARPS * w4_unroll(mr);
   const long long G = (d.K + group - 1) / group;
-  const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS);
+  const int cols = w4_desc_cols(d);
+  const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + cols - 1) / cols);
   const long long slots = (long long)std::max(n_sm, 1) * (mr >= 2 ? 2 : 3);
   const long long max_cuts = std::max(1LL, G / 2);
   long long best = 1;
@@ -252,10 +267,13 @@ void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   *rows_max = (int)(((G + best - 1) / best) * group);
 }
 
-size_t w4_smem_bytes(int mr, int rows_max, bool tma) { return w4_data_bytes(mr, rows_max, tma) + (tma ? 2 * W4_STAGES * sizeof(uint64_t) : 0); }
-// the packed rows as 32-bit words [K][N / 8], in boxes of one group of rows by the 32 words of a column tile
-bool w4_tma(const cb_qdense_desc& d) { return d.N % 32 == 0; }
-int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t group) {
+size_t w4_smem_bytes(int mr, int rows_max, bool tma, int cols) {
+  return w4_data_bytes(mr, rows_max, tma, cols) + (tma ? 2 * W4_STAGES * sizeof(uint64_t) : 0);
+}
+// the rows of W as 32-bit words [K][words per row], in boxes of one group of rows by the 32 words of a column tile;
+// a row must be a whole number of 16-byte units
+bool w4_tma(const cb_qdense_desc& d) { return (d.N / w4_desc_vpw(d)) % 4 == 0; }
+int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t group) {   // N: words per row
   struct Entry { const void* ptr; uint64_t K, N; uint32_t group; bool valid; CUtensorMap map; };
   constexpr int SLOTS = 64;
   static thread_local Entry cache[SLOTS];
@@ -264,9 +282,9 @@ int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t 
   if (e.valid && e.ptr == ptr && e.K == K && e.N == N && e.group == group) { *m = e.map; return CB_OK; }
   encode_tiled_fn enc = tensor_map_encoder();
   if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {N / 8, K};
-  cuuint64_t strides[1] = {N / 2};
-  cuuint32_t box[2] = {W4_COLS / 8, group};
+  cuuint64_t dims[2] = {N, K};
+  cuuint64_t strides[1] = {N * 4};
+  cuuint32_t box[2] = {32, group};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -279,10 +297,11 @@ template <typename XT, int MODE, int MR, bool ZP, bool TAIL, bool TMA>
 int w4_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   int cuts = 0, rows = 0;
   w4_cuts(d, n_sm, &cuts, &rows);
-  const size_t smem = w4_smem_bytes(MR, rows, TMA);
+  constexpr int COLS = w4_cols(MODE), VPW = w4_vpw(MODE);
+  const size_t smem = w4_smem_bytes(MR, rows, TMA, COLS);
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
-  if (TMA) CB_TRY(w4_encode(&tmap, in[1], (uint64_t)d.K, (uint64_t)d.N, (uint32_t)(W4_WARPS * w4_unroll(MR))));
+  if (TMA) CB_TRY(w4_encode(&tmap, in[1], (uint64_t)d.K, (uint64_t)(d.N / VPW), (uint32_t)(W4_WARPS * w4_unroll(MR))));
   float* partial = (float*)((uint8_t*)ws + W4_HEADER);
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -295,7 +314,7 @@ int w4_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
   const float* zp = d.has_zero_point ? (const float*)in[idx++] : nullptr;
   const float* bias = d.has_bias ? (const float*)in[idx++] : nullptr;
   const int64_t nblk = (d.N + d.block_size - 1) / d.block_size;
-  dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + W4_COLS - 1) / W4_COLS), (unsigned)cuts);
+  dim3 grid((unsigned)((d.M + MR - 1) / MR), (unsigned)((d.N + COLS - 1) / COLS), (unsigned)cuts);
   qdense_w4_kernel<XT, MODE, MR, ZP, TAIL, TMA><<<grid, W4_WARPS * 32, smem, s>>>(
       tmap, (const XT*)in[0], (const uint32_t*)in[1], (const float*)in[2], zp, partial, (unsigned*)ws, (int)d.M, d.K, d.N, d.block_size, nblk, rows);
   CB_CUDA(cudaGetLastError());
@@ -332,6 +351,11 @@ int w4_launch_m(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
 
 template <typename XT>
 int w4_launch_t(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
+  if (!w4_packed(d)) {
+    if (d.scheme == CB_QUANT_NF4) return w4_launch_m<XT, W8_NF4, false>(d, n_sm, in, out, ws, s);
+    if (d.w_dtype == CB_I8) return d.has_zero_point ? w4_launch_m<XT, W8_I8, true>(d, n_sm, in, out, ws, s) : w4_launch_m<XT, W8_I8, false>(d, n_sm, in, out, ws, s);
+    return d.has_zero_point ? w4_launch_m<XT, W8_U8, true>(d, n_sm, in, out, ws, s) : w4_launch_m<XT, W8_U8, false>(d, n_sm, in, out, ws, s);
+  }
   if (d.scheme == CB_QUANT_NF4) return w4_launch_m<XT, W4_NF4, false>(d, n_sm, in, out, ws, s);
   if (d.w_dtype == CB_I4) return d.has_zero_point ? w4_launch_m<XT, W4_I4, true>(d, n_sm, in, out, ws, s) : w4_launch_m<XT, W4_I4, false>(d, n_sm, in, out, ws, s);
   return d.has_zero_point ? w4_launch_m<XT, W4_U4, true>(d, n_sm, in, out, ws, s) : w4_launch_m<XT, W4_U4, false>(d, n_sm, in, out, ws, s);
@@ -339,16 +363,20 @@ int w4_launch_t(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
 
 }  // namespace
 
-// Decode shapes of the packed 4-bit formats with the reference's scale layout.  The generic kernel keeps everything
-// else, and these too when the plan asks for it by name (it sums in the reference's order).
+// Decode shapes of the 4-bit and 8-bit formats with the reference's scale layout (a column group must be whole words:
+// a multiple of 8 columns for packed 4-bit weights, of 4 for bytes).  The generic kernel keeps everything else, and
+// these too when the plan asks for it by name (it sums in the reference's order).
 bool qdense_w4_supports(const cb_qdense_desc& d) {
   if (d.variant != CB_QDENSE_AUTO) return false;
-  if (d.w_dtype != CB_I4 && d.w_dtype != CB_U4) return false;
+  if (d.w_dtype != CB_I4 && d.w_dtype != CB_U4 && d.w_dtype != CB_I8 && d.w_dtype != CB_U8) return false;
   if (d.scheme != CB_QUANT_LINEAR && d.scheme != CB_QUANT_NF4) return false;
-  if (d.scale_layout != CB_SCALE_REF || d.block_size < 8 || d.block_size % 8 != 0) return false;
+  const int vpw = w4_desc_vpw(d);
+  if (d.scale_layout != CB_SCALE_REF || d.block_size < vpw || d.block_size % vpw != 0) return false;
   if (d.gather_ranks > 1) return false;
   // below a few hundred thousand weights the launch of a second kernel costs more than the generic kernel's loop
-  return d.M >= 1 && d.M <= W4_MAX_M && d.N >= 8 && d.N % 8 == 0 && d.K >= 64 && d.K * d.N >= (1 << 18) && d.K < (1LL << 31) && d.N < (1LL << 31);
+  // bytes: a word holds four columns, so the per-word work (x, scale) weighs twice as much and 16 rows take 210 us on
+  // the 4096 x 14336 projection: beyond them the GEMM path (about 360 us whatever M) is the better one
+  return d.M >= 1 && d.M <= (w4_packed(d) ? W4_MAX_M : 16) && d.N >= vpw && d.N % vpw == 0 && d.K >= 64 && d.K * d.N >= (1 << 18) && d.K < (1LL << 31) && d.N < (1LL << 31);
 }
 
 void qdense_w4_plan(cb_plan* p) {
@@ -357,22 +385,23 @@ void qdense_w4_plan(cb_plan* p) {
   int cuts = 0, rows = 0;
   w4_cuts(d, p->n_sm, &cuts, &rows);
   const int mr = w4_rows(d);
-  p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS) * cuts);
+  const int cols = w4_desc_cols(d);
+  p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + cols - 1) / cols) * cuts);
   p->threads = W4_WARPS * 32;
-  p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d));
+  p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d), cols);
   p->workspace_bytes = W4_HEADER + (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
   p->counter_bytes = W4_HEADER;
   p->has_status = true;
-  p->name = std::string("qdense_w4_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") + (d.w_dtype == CB_U4 ? "_u4" : "_i4") +
-            (d.scheme == CB_QUANT_NF4 ? "_nf4" : "");
+  p->name = std::string(w4_packed(d) ? "qdense_w4_" : "qdense_w8_") + (d.x_dtype == CB_BF16 ? "bf16" : "f32") +
+            (d.w_dtype == CB_U4 ? "_u4" : d.w_dtype == CB_I4 ? "_i4" : d.w_dtype == CB_U8 ? "_u8" : "_i8") + (d.scheme == CB_QUANT_NF4 ? "_nf4" : "");
 }
 
 int qdense_w4_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   const cb_qdense_desc& d = p->qd;
   if (d.M == 0 || d.N == 0) return CB_OK;
-  if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (packed 4-bit): the plan needs its workspace (partial sums of the cuts of K)");
+  if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (reference scales, decode): the plan needs its workspace (partial sums of the cuts of K)");
   if ((reinterpret_cast<uintptr_t>(in[1]) & 3) || (reinterpret_cast<uintptr_t>(in[2]) & 3))
-    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (packed 4-bit): weights and scales must be 4-byte aligned");
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (reference scales, decode): weights and scales must be 4-byte aligned");
   // 16 rows of x per run; the runs follow each other on the stream and share the workspace
   const size_t esz = d.x_dtype == CB_BF16 ? 2 : 4;
   const int n_in = 3 + (d.has_zero_point ? 1 : 0) + (d.has_bias ? 1 : 0);

@@ -54,7 +54,7 @@ def test_plans_select_kernels_by_shape_and_dtype():
     assert dv.Plan.qdense(2048, 4096, 14336, dv.BF16, dv.I8, dv.SCALE_CHANNEL).kernel_name == "qdense_prefill_tcgen05_bf16_i8"
     assert dv.Plan.dot(1, 4096, 4096, 4096, dv.F32).kernel_name == "gemm_tcgen05_Float32_Float32_nn"
     # the reference's own scale layout and zero points go to the reference-order kernel
-    assert dv.Plan.qdense(1, 4096, 14336, dv.F32, dv.I8, dv.SCALE_REF, 128).kernel_name.startswith("qdense_generic")
+    assert dv.Plan.qdense(1, 4096, 14336, dv.F32, dv.I8, dv.SCALE_REF, 128).kernel_name == "qdense_w8_f32_i8"   # the reference's scale layout
     assert dv.Plan.qdense(4, 64, 64, dv.F32, dv.U8, dv.SCALE_CHANNEL, has_zero_point=True).kernel_name == "qdense_generic_f32_u8"
     assert dv.Plan.dot(1, 3, 5, 7, dv.F64).kernel_name.startswith("dot_generic_Float64")
     assert dv.Plan.sdpa(1, 4, 2, 5, 7, 8, dv.F32, causal=True).kernel_name.startswith("sdpa_")

@@ -153,6 +153,42 @@ def test_packed_4bit_decode_shapes(kind, M, K, N, block, x_dtype):
             break                                  # the generic kernel needs milliseconds per call on the full projection
 
 
+@pytest.mark.parametrize("kind", ["i8", "u8", "nf4_u8"])
+@pytest.mark.parametrize("M,K,N,block,x_dtype", [(1, 4096, 14336, 64, "f32"), (5, 520, 516, 4, "f32"), (16, 1024, 264, 24, "bf16"),
+                                                 (2, 300, 1000, 40, "f32"), (9, 2048, 136, 136, "f32")])
+def test_reference_scales_8bit_decode_shapes(kind, M, K, N, block, x_dtype):
+    """Int8 / Uint8 weights (and NF4 indices one per byte) with the reference's [K, N / block] scales, as a caller of the
+    reference's interface passes them, at decode shapes: the streaming kernel with four columns per lane, zero points,
+    bias and activation; every block size that is a multiple of 4."""
+    rng = np.random.default_rng(M * 1000 + N + 1)
+    nf4 = kind.startswith("nf4")
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if M >= 5:
+        x[1] = 0.0
+        x[2] *= 100.0
+    if nf4:
+        w = rng.integers(0, 16, size=(K, N)).astype(np.uint8)
+    elif kind == "i8":
+        w = rng.integers(-128, 128, size=(K, N)).astype(np.int8)
+    else:
+        w = rng.integers(0, 256, size=(K, N)).astype(np.uint8)
+    nblk = -(-N // block)
+    s = rng.uniform(0.001, 0.02, size=(K, nblk)).astype(np.float32)
+    zp = None if nf4 else rng.uniform(-0.05, 0.05, size=s.shape).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    xw = orc.bf16_to_f32(xin) if x_dtype == "bf16" else x
+    for z in ((None,) if nf4 else (None, zp)):
+        want = orc.qdense_nf4(xw, w, s, b, block, orc.ACT_GELU) if nf4 else orc.qdense_linear(xw, w, s, z, b, block, orc.ACT_GELU, threads=orc.max_threads())
+        got, plan = ops.quantized_dense(xin, w, s, z, b, x_dtype=code, block_size=block, activation=dv.ACT_GELU,
+                                        scheme=dv.QUANT_NF4 if nf4 else dv.QUANT_LINEAR, return_plan=True)
+        assert plan.kernel_name == f"qdense_w8_{x_dtype}_{'i8' if kind == 'i8' else 'u8'}{'_nf4' if nf4 else ''}" and plan.workspace_bytes > 0
+        gotf = orc.bf16_to_f32(got) if x_dtype == "bf16" else got
+        for m in range(M):
+            assert max_abs_normalised(gotf[m], want[m]) < (BF16_TOL if x_dtype == "bf16" else F32_TOL), (m, z is not None)
+
+
 def test_nf4_and_packed_validation():
     with pytest.raises(BackendError) as e:
         dv.Plan.qdense(2, 8, 8, dv.F32, dv.U8, dv.SCALE_REF, 8, has_zero_point=True, scheme=dv.QUANT_NF4)
