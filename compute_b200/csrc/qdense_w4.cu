@@ -12,7 +12,7 @@
 // three to four CTAs fill every SM.  Partial sums meet in shared memory (fixed order), then in a workspace
 // [cut][M][N]; a second small kernel adds the cuts in order, the bias and the activation.
 //
-// With 8-bit weights a word holds four columns and a CTA owns 128; everything else is the same.
+// With 8-bit weights a lane's eight columns are two words (one 64-bit read); everything else is the same.
 //
 // A nibble becomes a float without a conversion: its four bits go to the top of the mantissa of 1.0, which is
 // 1 + n / 16 (for Int4 the nibble's top bit is flipped first: n ^ 8 = n + 8).  The sums run over those floats and the
@@ -28,15 +28,15 @@ namespace cb {
 namespace {
 
 constexpr int W4_WARPS = 8;
-constexpr int W4_STAGES = 6;               // TMA form: groups of rows in flight or in use per CTA
+constexpr int W4_COLS = 256;               // columns per CTA: 32 lanes x 8
 constexpr size_t W4_HEADER = 256;          // status words at the start of the workspace
 // Up to this many rows of x the kernel runs once per 16 rows: two runs of 94 us beat expanding the weights to bf16
 // planes for the GEMM (about 265 us whatever M on the 4096 x 14336 projection).
 constexpr int W4_MAX_M = 32;
 __host__ __device__ constexpr int w4_unroll(int mr) { return mr >= 8 ? 4 : 8; }   // rows of W a lane has in flight
 enum { W4_U4 = 0, W4_I4 = 1, W4_NF4 = 2, W8_U8 = 3, W8_I8 = 4, W8_NF4 = 5 };
-__host__ __device__ constexpr int w4_vpw(int mode) { return mode >= W8_U8 ? 4 : 8; }         // weights per 32-bit word
-__host__ __device__ constexpr int w4_cols(int mode) { return 32 * w4_vpw(mode); }           // columns per CTA: a word per lane
+__host__ __device__ constexpr int w4_wpl(int mode) { return mode >= W8_U8 ? 2 : 1; }         // 32-bit words a lane's eight columns take
+__host__ __device__ constexpr int w4_stages(int wpl) { return wpl == 2 ? 4 : 6; }           // TMA form: groups of rows in flight or in use per CTA
 
 // NormalFloat4 (fused_ops.go:114-121)
 __constant__ float kW4Nf4[16] = {
@@ -46,18 +46,24 @@ __constant__ float kW4Nf4[16] = {
     0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
 
 // shared memory before the barriers: x of the cut, then the reduction buffer with, in the TMA form, the ring under it
-__host__ __device__ constexpr size_t w4_data_bytes(int mr, int rows_max, bool tma, int cols) {
-  const size_t xs = (size_t)mr * rows_max * 4, red = (size_t)W4_WARPS * mr * cols * 4, ring = (size_t)W4_STAGES * W4_WARPS * w4_unroll(mr) * 128;
+__host__ __device__ constexpr size_t w4_data_bytes(int mr, int rows_max, bool tma, int wpl) {
+  const size_t xs = (size_t)mr * rows_max * 4, red = (size_t)W4_WARPS * mr * W4_COLS * 4,
+               ring = (size_t)w4_stages(wpl) * W4_WARPS * w4_unroll(mr) * 128 * wpl;
   return xs + (tma && ring > red ? ring : red);
 }
 
 template <int MODE>
-__device__ __forceinline__ float w4_value(uint32_t word, int i, const float* lut) {
+__device__ __forceinline__ float w4_value(uint2 words, int i, const float* lut) {   // column i of the lane's eight
+  if (MODE >= W8_U8) {
+    const uint32_t wb = i < 4 ? words.x : words.y;
+    const int b = i & 3;
+    if (MODE == W8_NF4) return lut[(wb >> (8 * b)) & 0xFu];
+    // a byte under the exponent of 2^23 is 2^23 + b; signed bytes are biased by 128 first
+    if (MODE == W8_U8) return __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7650u | b)) - 8388608.0f;
+    return __uint_as_float(__byte_perm(wb ^ 0x80808080u, 0x4B000000u, 0x7650u | b)) - 8388736.0f;
+  }
+  const uint32_t word = words.x;
   if (MODE == W4_NF4) return lut[(word >> (4 * i)) & 0xFu];
-  if (MODE == W8_NF4) return lut[(word >> (8 * i)) & 0xFu];
-  // a byte under the exponent of 2^23 is 2^23 + b; signed bytes are biased by 128 first
-  if (MODE == W8_U8) return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650u | i)) - 8388608.0f;
-  if (MODE == W8_I8) return __uint_as_float(__byte_perm(word ^ 0x80808080u, 0x4B000000u, 0x7650u | i)) - 8388736.0f;
   const uint32_t at19 = 4 * i <= 19 ? word << (19 - 4 * i) : word >> (4 * i - 19);
   return __uint_as_float((at19 & 0x00780000u) ^ (MODE == W4_I4 ? 0x3FC00000u : 0x3F800000u));
 }
@@ -73,16 +79,17 @@ __global__ void __launch_bounds__(W4_WARPS * 32, MR >= 2 ? 2 : 3)
 qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restrict__ x, const uint32_t* __restrict__ w,
                  const float* __restrict__ scales, const float* __restrict__ zps, float* __restrict__ partial, unsigned* __restrict__ status,
                  int M, int64_t K, int64_t N, int64_t block, int64_t nblk, int rows_max) {
-  constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL, STAGE = GROUP * 128;
-  constexpr int VPW = w4_vpw(MODE), COLS = w4_cols(MODE);
+  constexpr int WPL = w4_wpl(MODE), W4_STAGES = w4_stages(WPL);
+  constexpr int W4_UNROLL = w4_unroll(MR), GROUP = W4_WARPS * W4_UNROLL, STAGE = GROUP * 128 * WPL;
+  constexpr int VPW = 8, COLS = W4_COLS;
   constexpr bool TABLE = MODE == W4_NF4 || MODE == W8_NF4, DIRECT = MODE >= W4_NF4;          // DIRECT: w4_value is the weight itself
   // the kernel that adds the cuts may be scheduled now; it waits for this grid before it reads the partial sums
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(1024) unsigned char w4_smem[];
   float* xs = reinterpret_cast<float*>(w4_smem);                               // [MR][rows_max]
   float* red = xs + (size_t)MR * rows_max;                                     // [W4_WARPS][MR][COLS]; the ring lies under it
-  const uint32_t* ring = reinterpret_cast<const uint32_t*>(red);               // [W4_STAGES][GROUP][32 words]
-  uint64_t* full = reinterpret_cast<uint64_t*>(w4_smem + w4_data_bytes(MR, rows_max, TMA, COLS));
+  const uint32_t* ring = reinterpret_cast<const uint32_t*>(red);               // [W4_STAGES][GROUP][32 WPL words]
+  uint64_t* full = reinterpret_cast<uint64_t*>(w4_smem + w4_data_bytes(MR, rows_max, TMA, WPL));
   uint64_t* empty = full + W4_STAGES;
   __shared__ float lut[16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -121,7 +128,7 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
     const int slot = g % W4_STAGES, round = g / W4_STAGES;
     if (round > 0 && !tc::mbar_wait(&empty[slot], (uint32_t)((round - 1) & 1))) return false;
     tc::mbar_expect_tx(&full[slot], STAGE);
-    tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * 32), (int)(k0 + (int64_t)g * GROUP),
+    tc::tma_load_2d(const_cast<uint32_t*>(ring) + (size_t)slot * (STAGE / 4), &tmap_w, (int)(blockIdx.y * 32 * WPL), (int)(k0 + (int64_t)g * GROUP),
                     &full[slot]);
     issued = g + 1;
     return true;
@@ -129,20 +136,24 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
   if (TMA && threadIdx.x == 0)
     for (int g = 0; g < min(n_groups, W4_STAGES - 1); g++) ask(g);
   if ((TMA || active) && n_groups > 0) {
-    const int64_t wrow = N / VPW;                                              // words per row of W
+    const int64_t wrow = N / VPW * WPL;                                        // words per row of W
     const int64_t n0s = active ? n0 : 0;                                       // lanes past N (TMA form) work on zeros of column 0's scales
     // this warp's rows of a group: warp, warp + 8, ...; the next group is requested before this one is consumed
-    const uint32_t* wq = w + (k0 + warp) * wrow + n0s / VPW;
+    const uint32_t* wq = w + (k0 + warp) * wrow + n0s / VPW * WPL;
     const float* sq = scales + (k0 + warp) * nblk + n0s / block;
     const float* zq = ZP ? zps + (k0 + warp) * nblk + n0s / block : nullptr;
     const int64_t w8 = W4_WARPS * wrow, s8 = W4_WARPS * nblk;
-    uint32_t wn[W4_UNROLL];
+    uint2 wn[W4_UNROLL];
     float sn[W4_UNROLL], zn[W4_UNROLL];
+    auto load_words = [&](const uint32_t* q) {                                 // the lane's one or two words of a row
+      if (WPL == 2) return __ldg(reinterpret_cast<const uint2*>(q));
+      return make_uint2(__ldg(q), 0u);
+    };
     auto request = [&](int g) {
 #pragma unroll
       for (int u = 0; u < W4_UNROLL; u++) {
         const bool in = !TAIL || g * GROUP + warp + u * W4_WARPS < kc;
-        if (!TMA) wn[u] = in ? __ldg(wq + u * w8) : 0u;
+        if (!TMA) wn[u] = in ? load_words(wq + u * w8) : make_uint2(0u, 0u);
         sn[u] = in ? __ldg(sq + u * s8) : 0.0f;
         zn[u] = (ZP && in) ? __ldg(zq + u * s8) : 0.0f;
       }
@@ -155,16 +166,19 @@ qdense_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const XT* __restric
     int slot = 0;
     uint32_t phase = 0;
     for (int g = 0; g < n_groups; g++) {
-      uint32_t wv[W4_UNROLL];
+      uint2 wv[W4_UNROLL];
       float sv[W4_UNROLL], zv[W4_UNROLL];
       if (TMA) {
         bool ok = true;
         if (threadIdx.x == 0 && g + W4_STAGES - 1 < n_groups) ok = ask(g + W4_STAGES - 1);
         ok = ok && tc::mbar_wait(&full[slot], phase);
         if (!__all_sync(0xFFFFFFFFu, ok)) { failed = true; break; }
-        const uint32_t* st = ring + (size_t)slot * (STAGE / 4) + warp * 32 + lane;
+        const uint32_t* st = ring + (size_t)slot * (STAGE / 4) + (warp * 32 + lane) * WPL;
 #pragma unroll
-        for (int u = 0; u < W4_UNROLL; u++) wv[u] = st[u * W4_WARPS * 32];
+        for (int u = 0; u < W4_UNROLL; u++) {
+          if (WPL == 2) wv[u] = *reinterpret_cast<const uint2*>(st + u * W4_WARPS * 32 * WPL);
+          else wv[u] = make_uint2(st[u * W4_WARPS * 32], 0u);
+        }
         __syncwarp();                                                          // every lane holds its words: the stage may be refilled
         if (lane == 0) tc::mbar_arrive(&empty[slot]);
         if (++slot == W4_STAGES) { slot = 0; phase ^= 1u; }
@@ -241,8 +255,7 @@ qdense_w4_finish_kernel(const float* __restrict__ partial, const float* __restri
 
 int w4_rows(const cb_qdense_desc& d) { return d.M <= 1 ? 1 : d.M <= 2 ? 2 : d.M <= 4 ? 4 : 8; }
 bool w4_packed(const cb_qdense_desc& d) { return d.w_dtype == CB_I4 || d.w_dtype == CB_U4; }
-int w4_desc_vpw(const cb_qdense_desc& d) { return w4_packed(d) ? 8 : 4; }
-int w4_desc_cols(const cb_qdense_desc& d) { return 32 * w4_desc_vpw(d); }
+int w4_desc_wpl(const cb_qdense_desc& d) { return w4_packed(d) ? 1 : 2; }
 
 // How K is cut.  A CTA costs a fixed set-up and a reduction, so few long CTAs beat many short ones, but the CTAs must
 // fill whole waves: with `slots` CTAs resident on the GPU at once, the cut count that fills one wave best is taken when
@@ -251,8 +264,7 @@ void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   const int mr = w4_rows(d);
   const int group = W4_WARPS * w4_unroll(mr);
   const long long G = (d.K + group - 1) / group;
-  const int cols = w4_desc_cols(d);
-  const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + cols - 1) / cols);
+  const long long tiles = ((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS);
   const long long slots = (long long)std::max(n_sm, 1) * (mr >= 2 ? 2 : 3);
   const long long max_cuts = std::max(1LL, G / 2);
   long long best = 1;
@@ -267,29 +279,29 @@ void w4_cuts(const cb_qdense_desc& d, int n_sm, int* cuts, int* rows_max) {
   *rows_max = (int)(((G + best - 1) / best) * group);
 }
 
-size_t w4_smem_bytes(int mr, int rows_max, bool tma, int cols) {
-  return w4_data_bytes(mr, rows_max, tma, cols) + (tma ? 2 * W4_STAGES * sizeof(uint64_t) : 0);
+size_t w4_smem_bytes(int mr, int rows_max, bool tma, int wpl) {
+  return w4_data_bytes(mr, rows_max, tma, wpl) + (tma ? 2 * w4_stages(wpl) * sizeof(uint64_t) : 0);
 }
 // the rows of W as 32-bit words [K][words per row], in boxes of one group of rows by the 32 words of a column tile;
 // a row must be a whole number of 16-byte units
-bool w4_tma(const cb_qdense_desc& d) { return (d.N / w4_desc_vpw(d)) % 4 == 0; }
-int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t group) {   // N: words per row
-  struct Entry { const void* ptr; uint64_t K, N; uint32_t group; bool valid; CUtensorMap map; };
+bool w4_tma(const cb_qdense_desc& d) { return (d.N / 8 * w4_desc_wpl(d)) % 4 == 0; }
+int w4_encode(CUtensorMap* m, const void* ptr, uint64_t K, uint64_t N, uint32_t group, uint32_t wpl) {   // N: words per row
+  struct Entry { const void* ptr; uint64_t K, N; uint32_t group, wpl; bool valid; CUtensorMap map; };
   constexpr int SLOTS = 64;
   static thread_local Entry cache[SLOTS];
   const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
   Entry& e = cache[(h >> 40) % SLOTS];
-  if (e.valid && e.ptr == ptr && e.K == K && e.N == N && e.group == group) { *m = e.map; return CB_OK; }
+  if (e.valid && e.ptr == ptr && e.K == K && e.N == N && e.group == group && e.wpl == wpl) { *m = e.map; return CB_OK; }
   encode_tiled_fn enc = tensor_map_encoder();
   if (!enc) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {N, K};
   cuuint64_t strides[1] = {N * 4};
-  cuuint32_t box[2] = {32, group};
+  cuuint32_t box[2] = {32 * wpl, group};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(CB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  e.ptr = ptr; e.K = K; e.N = N; e.group = group; e.map = *m; e.valid = true;
+  e.ptr = ptr; e.K = K; e.N = N; e.group = group; e.wpl = wpl; e.map = *m; e.valid = true;
   return CB_OK;
 }
 
@@ -297,11 +309,11 @@ template <typename XT, int MODE, int MR, bool ZP, bool TAIL, bool TMA>
 int w4_launch_k(const cb_qdense_desc& d, int n_sm, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   int cuts = 0, rows = 0;
   w4_cuts(d, n_sm, &cuts, &rows);
-  constexpr int COLS = w4_cols(MODE), VPW = w4_vpw(MODE);
-  const size_t smem = w4_smem_bytes(MR, rows, TMA, COLS);
+  constexpr int COLS = W4_COLS, WPL = w4_wpl(MODE);
+  const size_t smem = w4_smem_bytes(MR, rows, TMA, WPL);
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
-  if (TMA) CB_TRY(w4_encode(&tmap, in[1], (uint64_t)d.K, (uint64_t)(d.N / VPW), (uint32_t)(W4_WARPS * w4_unroll(MR))));
+  if (TMA) CB_TRY(w4_encode(&tmap, in[1], (uint64_t)d.K, (uint64_t)(d.N / 8 * WPL), (uint32_t)(W4_WARPS * w4_unroll(MR)), (uint32_t)WPL));
   float* partial = (float*)((uint8_t*)ws + W4_HEADER);
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -363,20 +375,18 @@ int w4_launch_t(const cb_qdense_desc& d, int n_sm, const void* const* in, void* 
 
 }  // namespace
 
-// Decode shapes of the 4-bit and 8-bit formats with the reference's scale layout (a column group must be whole words:
-// a multiple of 8 columns for packed 4-bit weights, of 4 for bytes).  The generic kernel keeps everything else, and
+// Decode shapes of the 4-bit and 8-bit formats with the reference's scale layout (a column group must be a multiple of
+// the eight columns a lane owns).  The generic kernel keeps everything else, and
 // these too when the plan asks for it by name (it sums in the reference's order).
 bool qdense_w4_supports(const cb_qdense_desc& d) {
   if (d.variant != CB_QDENSE_AUTO) return false;
   if (d.w_dtype != CB_I4 && d.w_dtype != CB_U4 && d.w_dtype != CB_I8 && d.w_dtype != CB_U8) return false;
   if (d.scheme != CB_QUANT_LINEAR && d.scheme != CB_QUANT_NF4) return false;
-  const int vpw = w4_desc_vpw(d);
+  const int vpw = 8;                       // a lane's eight columns share one scale
   if (d.scale_layout != CB_SCALE_REF || d.block_size < vpw || d.block_size % vpw != 0) return false;
   if (d.gather_ranks > 1) return false;
   // below a few hundred thousand weights the launch of a second kernel costs more than the generic kernel's loop
-  // bytes: a word holds four columns, so the per-word work (x, scale) weighs twice as much and 16 rows take 210 us on
-  // the 4096 x 14336 projection: beyond them the GEMM path (about 360 us whatever M) is the better one
-  return d.M >= 1 && d.M <= (w4_packed(d) ? W4_MAX_M : 16) && d.N >= vpw && d.N % vpw == 0 && d.K >= 64 && d.K * d.N >= (1 << 18) && d.K < (1LL << 31) && d.N < (1LL << 31);
+  return d.M >= 1 && d.M <= W4_MAX_M && d.N >= vpw && d.N % vpw == 0 && d.K >= 64 && d.K * d.N >= (1 << 18) && d.K < (1LL << 31) && d.N < (1LL << 31);
 }
 
 void qdense_w4_plan(cb_plan* p) {
@@ -385,10 +395,9 @@ void qdense_w4_plan(cb_plan* p) {
   int cuts = 0, rows = 0;
   w4_cuts(d, p->n_sm, &cuts, &rows);
   const int mr = w4_rows(d);
-  const int cols = w4_desc_cols(d);
-  p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + cols - 1) / cols) * cuts);
+  p->blocks = (int)(((d.M + mr - 1) / mr) * ((d.N + W4_COLS - 1) / W4_COLS) * cuts);
   p->threads = W4_WARPS * 32;
-  p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d), cols);
+  p->dyn_smem = (int)w4_smem_bytes(mr, rows, w4_tma(d), w4_desc_wpl(d));
   p->workspace_bytes = W4_HEADER + (size_t)cuts * (size_t)d.M * (size_t)d.N * sizeof(float);
   p->counter_bytes = W4_HEADER;
   p->has_status = true;
@@ -400,8 +409,8 @@ int qdense_w4_launch(const cb_plan* p, const void* const* in, void* const* out, 
   const cb_qdense_desc& d = p->qd;
   if (d.M == 0 || d.N == 0) return CB_OK;
   if (!ws) return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (reference scales, decode): the plan needs its workspace (partial sums of the cuts of K)");
-  if ((reinterpret_cast<uintptr_t>(in[1]) & 3) || (reinterpret_cast<uintptr_t>(in[2]) & 3))
-    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (reference scales, decode): weights and scales must be 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(in[1]) & (w4_packed(d) ? 3 : 7)) || (reinterpret_cast<uintptr_t>(in[2]) & 3))
+    return fail(CB_ERR_INVALID_ARG, "FusedQuantizedDense (reference scales, decode): weights must be 4-byte (bytes: 8-byte) and scales 4-byte aligned");
   // 16 rows of x per run; the runs follow each other on the stream and share the workspace
   const size_t esz = d.x_dtype == CB_BF16 ? 2 : 4;
   const int n_in = 3 + (d.has_zero_point ? 1 : 0) + (d.has_bias ? 1 : 0);

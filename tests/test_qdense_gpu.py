@@ -154,12 +154,12 @@ def test_packed_4bit_decode_shapes(kind, M, K, N, block, x_dtype):
 
 
 @pytest.mark.parametrize("kind", ["i8", "u8", "nf4_u8"])
-@pytest.mark.parametrize("M,K,N,block,x_dtype", [(1, 4096, 14336, 64, "f32"), (5, 520, 516, 4, "f32"), (16, 1024, 264, 24, "bf16"),
-                                                 (2, 300, 1000, 40, "f32"), (9, 2048, 136, 136, "f32")])
+@pytest.mark.parametrize("M,K,N,block,x_dtype", [(1, 4096, 14336, 64, "f32"), (5, 520, 520, 8, "f32"), (16, 1024, 264, 24, "bf16"),
+                                                 (2, 300, 1000, 40, "f32"), (21, 2048, 144, 144, "f32")])
 def test_reference_scales_8bit_decode_shapes(kind, M, K, N, block, x_dtype):
     """Int8 / Uint8 weights (and NF4 indices one per byte) with the reference's [K, N / block] scales, as a caller of the
-    reference's interface passes them, at decode shapes: the streaming kernel with four columns per lane, zero points,
-    bias and activation; every block size that is a multiple of 4."""
+    reference's interface passes them, at decode shapes: the streaming kernel with two words per lane, zero points,
+    bias and activation; with a TMA ring (N a multiple of 16) and without; 17 to 32 rows run once per 16 rows."""
     rng = np.random.default_rng(M * 1000 + N + 1)
     nf4 = kind.startswith("nf4")
     x = rng.standard_normal((M, K)).astype(np.float32)
