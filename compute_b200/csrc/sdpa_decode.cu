@@ -33,6 +33,10 @@ struct SdParams {
   int causal;
   float* part_o;        // [B, Hkv, splits, rows, D]
   float* part_ml;       // [B, Hkv, splits, rows, 2]  (max, sum)
+  // QuerySeqLen / KeyValueSeqLen [B] int32, or null: keys from kv_lens[b] on are not attended, query positions from
+  // q_lens[b] on give zero rows (sdpa.go:389-411)
+  const int* q_lens;
+  const int* kv_lens;
 };
 
 template <typename T> __device__ __forceinline__ void sd_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
@@ -89,7 +93,8 @@ sdpa_decode_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(sd_smem) + warp * SD_STAGES * STAGE;
 
   const int key0 = split * p.keys_per_split;
-  const int key1 = min(p.Skv, key0 + p.keys_per_split);
+  const int kv_limit = p.kv_lens ? min(p.Skv, __ldg(p.kv_lens + b)) : p.Skv;
+  const int key1 = min(kv_limit, key0 + p.keys_per_split);
   const T* kb = k + (long long)b * p.kv_b + (long long)kvh * p.kv_h;
   const T* vb = v + (long long)b * p.kv_b + (long long)kvh * p.kv_h;
   const int n_steps = key1 > key0 + warp * SD_STEP ? (key1 - key0 - warp * SD_STEP + SD_WARPS * SD_STEP - 1) / (SD_WARPS * SD_STEP) : 0;
@@ -269,7 +274,8 @@ __global__ void sdpa_decode_merge_kernel(T* __restrict__ out, const SdParams p) 
     oo = fmaf(p.part_o[pr * p.D + d], c, oo);
   }
   const int hg = r / p.S, s = r - hg * p.S;
-  const float res = ll != 0.0f ? oo / ll : 0.0f;
+  const bool padded = p.q_lens && s >= __ldg(p.q_lens + b);
+  const float res = (ll != 0.0f && !padded) ? oo / ll : 0.0f;
   Scalar<T>::store(out + (long long)b * p.q_b + (long long)(kvh * p.group + hg) * p.q_h + (long long)s * p.q_s, d, res);
 }
 
@@ -277,7 +283,7 @@ bool sdpa_decode_supports(const cb_sdpa_desc& d, std::string* why) {
   auto no = [&](const char* m) { if (why) *why = m; return false; };
   if (d.dtype != CB_BF16 && d.dtype != CB_F16) return no("bfloat16 / float16 only");
   if (d.D != 128 && d.D != 64) return no("head_dim must be 64 or 128");
-  if (d.mask_kind != CB_MASK_NONE || d.bias_rank > 0 || d.has_seq_lens) return no("mask, bias and sequence lengths go to the generic kernel");
+  if (d.mask_kind != CB_MASK_NONE || d.bias_rank > 0) return no("mask and bias tensors go to the generic kernel");
   if (d.Hkv <= 0 || d.Hq % d.Hkv != 0) return no("grouped heads");
   if (d.B < 1 || d.S < 1 || d.Skv < 1) return no("empty");
   if (d.S * (d.Hq / d.Hkv) > SD_MAX_ROWS) return no("more than 16 query rows per KV head");
@@ -370,6 +376,8 @@ int sdpa_decode_launch(const cb_plan* p, const void* const* in, void* const* out
   sd_fill(p, &s);
   s.part_o = (float*)ws;
   s.part_ml = s.part_o + (size_t)s.B * s.Hkv * s.splits * s.rows * s.D;
+  s.q_lens = p->sdpa.has_seq_lens ? (const int*)in[3] : nullptr;      // inputs: q, k, v, QuerySeqLen, KeyValueSeqLen
+  s.kv_lens = p->sdpa.has_seq_lens ? (const int*)in[4] : nullptr;
   if ((reinterpret_cast<uintptr_t>(in[0]) & 15) || (reinterpret_cast<uintptr_t>(in[1]) & 15) || (reinterpret_cast<uintptr_t>(in[2]) & 15))
     return fail(CB_ERR_INVALID_ARG, "FusedScaledDotProductAttention: query, key and value must be 16-byte aligned");
   if (p->sdpa.dtype == CB_BF16) {

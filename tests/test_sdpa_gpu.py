@@ -169,6 +169,34 @@ def test_sdpa_decode_kernel(B, Hq, Hkv, S, Skv, D, layout, dtype, causal):
     assert max_abs_normalised(orc.to_f32(got, code), orc.to_f32(gen, code)) < 2.0 ** -7
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,Skv,D,layout,dtype,causal", [
+    (16, 32, 8, 1, 2048, 128, "BSHD", "bf16", False),      # the benchmark's decode step with a different cache length per sequence
+    (5, 8, 2, 3, 1000, 64, "BHSD", "f16", True),           # three query tokens of which some are padding, causal
+])
+def test_sdpa_decode_kernel_with_sequence_lengths(B, Hq, Hkv, S, Skv, D, layout, dtype, causal):
+    """KeyValueSeqLen cuts each sequence's cache (a length inside a split, at a split boundary, the whole cache, one key,
+    none: that row is all zeros), QuerySeqLen zeroes the padded query positions (sdpa.go:389-411)."""
+    rng = np.random.default_rng(B * 77 + Skv)
+    code = DT[dtype]
+    shape = (lambda h, s: (B, s, h, D)) if layout == "BSHD" else (lambda h, s: (B, h, s, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shape(h, s), dtype=np.float32), code) for h, s in ((Hq, S), (Hkv, Skv), (Hkv, Skv)))
+    kv_len = rng.integers(1, Skv + 1, size=B).astype(np.int32)
+    kv_len[0], kv_len[1], kv_len[2] = Skv, 1, 0
+    if B > 3:
+        kv_len[3] = 512
+    q_len = rng.integers(0, S + 1, size=B).astype(np.int32)
+    q_len[0] = S
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, q_len=q_len, kv_len=kv_len, return_plan=True)
+    assert plan.kernel_name.startswith("sdpa_decode_"), plan.kernel_name
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), q_len=q_len, kv_len=kv_len, layout=layout, causal=causal)
+    gotf = orc.to_f32(got, code)
+    assert max_abs_normalised(gotf, want) < 2e-2
+    # rows the reference leaves at zero are zero here too, bit for bit
+    assert np.array_equal(gotf == 0.0, want == 0.0) or np.all(gotf[want == 0.0] == 0.0)
+    gen = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, q_len=q_len, kv_len=kv_len, variant=dv.SDPA_GENERIC)
+    assert max_abs_normalised(gotf, orc.to_f32(gen, code)) < 2.0 ** -7
+
+
 def test_sdpa_decode_kernel_is_refused_where_it_does_not_apply():
     with pytest.raises(ErrNotImplemented):      # float32 stays on the generic kernel
         dv.Plan.sdpa(2, 8, 2, 1, 1024, 128, dv.F32, variant=dv.SDPA_DECODE)
