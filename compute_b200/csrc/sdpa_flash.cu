@@ -43,6 +43,10 @@ struct FaParams {
   float scale_log2;        // scale * log2(e)
   int q_pairs;             // ceil(S / 256)
   int pair_heads;          // causal with an even GQA group: a CTA's two tiles are the same rows of two neighbouring heads
+  // QuerySeqLen / KeyValueSeqLen [B] int32, or null: keys from kv_lens[b] on are not attended (their blocks are not even
+  // loaded), query positions from q_lens[b] on give zero rows (sdpa.go:389-411)
+  const int* q_lens;
+  const int* kv_lens;
 };
 
 __device__ __forceinline__ void fa_fail(const FaParams& p, unsigned* s_failed, unsigned code, unsigned detail) {
@@ -159,7 +163,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tq0[0] = pair * 2 * FA_BM; tq0[1] = tq0[0] + FA_BM;
   }
   const int hk = th[0] / (p.Hq / p.Hkv);
-  const int nb_all = (p.Skv + FA_BN - 1) / FA_BN;
+  const int kvl = p.kv_lens ? max(0, min(p.Skv, __ldg(p.kv_lens + b))) : p.Skv;      // keys this sequence attends to
+  const int nb_all = (kvl + FA_BN - 1) / FA_BN;
   int nb[2];
 #pragma unroll
   for (int t = 0; t < 2; t++) {
@@ -207,6 +212,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         fa_load_tile(sV + s * FA_TILE_BYTES, &tm_v, p.bshd, j * FA_BN, hk, b, &v_full[s]);
         if (*(volatile unsigned*)&s_failed) break;
       }
+      // a sequence without keys: nobody else waits for the query tiles, so they are waited for here before the CTA ends
+      if (nb_max == 0) mbar_wait(q_full, 0);
     }
   } else if (warp == 9) {
     // ------------------------------ MMA issuer --------------------------------
@@ -295,8 +302,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (*(volatile unsigned*)&s_failed) { failed = true; break; }
       tc_fence_after();
       const int kv0 = j * FA_BN;
-      const bool need_mask = (p.causal && kv0 + FA_BN - 1 > row) || (kv0 + FA_BN > p.Skv);
-      const int kv_limit = p.causal ? min(p.Skv, row + 1) : p.Skv;   // first masked kv index
+      const bool need_mask = (p.causal && kv0 + FA_BN - 1 > row) || (kv0 + FA_BN > kvl);
+      const int kv_limit = p.causal ? min(kvl, row + 1) : kvl;       // first masked kv index
       // the whole score row of this block lives in registers: one TMEM read, one pass for the
       // maximum, one for the probabilities
       uint32_t sr[4][32];
@@ -386,7 +393,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     if (!failed && nb[t] > 0 && !*(volatile unsigned*)&s_failed) {
       tc_fence_after();
-      const float inv = l != 0.0f ? 1.0f / l : 0.0f;
+      const int ql = p.q_lens ? __ldg(p.q_lens + b) : p.S;           // query positions that are not padding
+      const float inv = (l != 0.0f && row < ql) ? 1.0f / l : 0.0f;    // nothing attended, or a padded query position: zeros
       OT* out = reinterpret_cast<OT*>(p.out);
       const int rr = min(row, p.S - 1);
       OT* orow = p.bshd ? out + (((size_t)b * p.S + rr) * p.Hq + h) * FA_D : out + (((size_t)b * p.Hq + h) * p.S + rr) * FA_D;
@@ -409,6 +417,13 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
     }
+    // a tile of a sequence without keys: its rows are zeros (sdpa.go:471-474)
+    if (nb[t] == 0 && row < p.S) {
+      OT* out = reinterpret_cast<OT*>(p.out);
+      OT* orow = p.bshd ? out + (((size_t)b * p.S + row) * p.Hq + h) * FA_D : out + (((size_t)b * p.Hq + h) * p.S + row) * FA_D;
+#pragma unroll
+      for (int c = 0; c < FA_D / 8; c++) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -426,7 +441,7 @@ bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why) {
   auto no = [&](const char* m) { if (why) *why = m; return false; };
   if (d.dtype != CB_BF16 && d.dtype != CB_F16) return no("dtype must be bfloat16 or float16");
   if (d.D != FA_D) return no("head_dim must be 128");
-  if (d.mask_kind != CB_MASK_NONE || d.bias_rank > 0 || d.has_seq_lens) return no("mask, bias and sequence lengths use the generic kernel");
+  if (d.mask_kind != CB_MASK_NONE || d.bias_rank > 0) return no("mask and bias tensors use the generic kernel");
   if (d.B < 1 || d.S < 1 || d.Skv < 1) return no("empty operand");
   if (d.S < 128 || d.Skv < 128) return no("sequence too short for the tensor-core tile");
   if (d.S > (1 << 24) || d.Skv > (1 << 24) || d.B * d.Hq * ((d.S + 255) / 256) > 0x7fffffffLL) return no("dimension too large");
@@ -500,6 +515,8 @@ int sdpa_flash_launch(const cb_plan* p, const void* const* in, void* const* out,
   prm.scale_log2 = (float)(scale * 1.4426950408889634);
   prm.q_pairs = (int)((d.S + 255) / 256);
   prm.pair_heads = (d.causal && d.Hkv > 0 && (d.Hq / d.Hkv) % 2 == 0) ? 1 : 0;
+  prm.q_lens = d.has_seq_lens ? (const int*)in[3] : nullptr;          // inputs: q, k, v, QuerySeqLen, KeyValueSeqLen
+  prm.kv_lens = d.has_seq_lens ? (const int*)in[4] : nullptr;
   return d.dtype == CB_BF16 ? launch_t<__nv_bfloat16>(p, tq, tk, tv, prm, s) : launch_t<__half>(p, tq, tk, tv, prm, s);
 }
 

@@ -141,6 +141,29 @@ def test_sdpa_flash_ragged_shapes(B, Hq, Hkv, S, Skv, layout, dtype, causal):
     assert max_abs_normalised(orc.to_f32(got, code), want) < 2e-2
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,layout,dtype,causal", [
+    (6, 8, 2, 512, 128, "BSHD", "bf16", True),       # a padded prefill batch: every sequence with its own length
+    (5, 4, 4, 300, 128, "BHSD", "f16", False),       # ragged S, no grouping, not causal
+])
+def test_sdpa_flash_kernel_with_sequence_lengths(B, Hq, Hkv, S, D, layout, dtype, causal):
+    """QuerySeqLen / KeyValueSeqLen on the tensor-core kernel: lengths inside a key block, at a block boundary, the
+    whole sequence, one key, none (zero rows); padded query positions are zero rows (sdpa.go:389-411, 471-474)."""
+    rng = np.random.default_rng(B * 31 + S)
+    code = DT[dtype]
+    shape = (lambda h, s: (B, s, h, D)) if layout == "BSHD" else (lambda h, s: (B, h, s, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shape(h, S), dtype=np.float32), code) for h in (Hq, Hkv, Hkv))
+    lens = rng.integers(1, S + 1, size=B).astype(np.int32)
+    lens[0], lens[1], lens[2], lens[3] = S, 1, 0, 128
+    q_len = lens.copy()
+    q_len[4] = max(1, int(lens[4]) // 2)              # fewer query positions than keys
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, q_len=q_len, kv_len=lens, return_plan=True)
+    assert plan.kernel_name.startswith("sdpa_flash_"), plan.kernel_name
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), q_len=q_len, kv_len=lens, layout=layout, causal=causal)
+    gotf = orc.to_f32(got, code)
+    assert max_abs_normalised(gotf, want) < 2e-2
+    assert np.all(gotf[want == 0.0] == 0.0)
+
+
 # ------------------------------------------------------------- decode shapes: a few query tokens over a long cache
 DECODE_CASES = [
     # B, Hq, Hkv, S, Skv, D, layout, dtype, causal
