@@ -7,6 +7,9 @@ namespace cb {
 struct SdpaParams;
 int sdpa_fill_params(const cb_sdpa_desc& d, SdpaParams* p);
 int sdpa_generic_plan(cb_plan* p);
+bool sdpa_tile_supports(const cb_sdpa_desc& d);
+int sdpa_tile_plan(cb_plan* p);
+int sdpa_tile_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s);
 int sdpa_generic_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s);
 bool sdpa_flash_supports(const cb_sdpa_desc& d, std::string* why);
 int sdpa_flash_plan(cb_plan* p);
@@ -38,7 +41,14 @@ int sdpa_plan(cb_plan* p) {
   std::string why_decode;
   const bool decode_ok = sdpa_decode_supports(d, &why_decode);
   // long query tiles go to the tensor-core kernel, a few query tokens over a long cache to the streaming kernel
-  if (variant == CB_SDPA_AUTO) variant = flash_ok ? CB_SDPA_FLASH : (decode_ok ? CB_SDPA_DECODE : CB_SDPA_GENERIC);
+  // everything else with at least half a tile of query rows to the tiled CUDA-core kernel, the rest to the row kernel
+  if (variant == CB_SDPA_AUTO)
+    variant = flash_ok ? CB_SDPA_FLASH : (decode_ok ? CB_SDPA_DECODE : (sdpa_tile_supports(d) ? CB_SDPA_TILE : CB_SDPA_GENERIC));
+  if (variant == CB_SDPA_TILE) {
+    if (!sdpa_tile_supports(d)) return fail(CB_ERR_NOT_IMPLEMENTED, "%s tiled kernel: float32 / bfloat16 / float16, head_dim 32, 64 or 128, at least 16 query rows", op);
+    p->variant = variant;
+    return sdpa_tile_plan(p);
+  }
   if (variant == CB_SDPA_DECODE) {
     if (!decode_ok) return fail(CB_ERR_NOT_IMPLEMENTED, "%s decode kernel: %s", op, why_decode.c_str());
     p->variant = variant;
@@ -56,6 +66,7 @@ int sdpa_plan(cb_plan* p) {
 int sdpa_launch(const cb_plan* p, const void* const* in, void* const* out, void* ws, cudaStream_t s) {
   if (p->variant == CB_SDPA_FLASH) return sdpa_flash_launch(p, in, out, ws, s);
   if (p->variant == CB_SDPA_DECODE) return sdpa_decode_launch(p, in, out, ws, s);
+  if (p->variant == CB_SDPA_TILE) return sdpa_tile_launch(p, in, out, s);
   return sdpa_generic_launch(p, in, out, s);
 }
 

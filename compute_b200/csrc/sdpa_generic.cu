@@ -190,6 +190,209 @@ int sdpa_validate_operands(const cb_sdpa_desc& d) {
   return sdpa_fill_params(d, &tmp);
 }
 
+// ---------------------------------------------------------------------------
+// Tiled kernel: the same operands and options as the row kernel above (any mask, bias, sequence lengths, GQA, both
+// layouts; float32 / bfloat16 / float16 with head_dim 32, 64 or 128) for query tiles of 32 rows — what a model built
+// on float32 attention with head_dim 64 and padding masks runs on, shapes the tensor-core kernels do not take.
+// A CTA of 128 threads owns 32 query rows of one head and walks the keys in blocks of 64: K and V blocks are staged in
+// shared memory as float32 (coalesced loads), thread (ty, tx) forms the scores of rows ty + 8 i and keys tx + 16 j
+// with 16-byte shared-memory reads along the head dimension, the streaming softmax state of a row is replicated in
+// the 16 threads that share it (reductions by shuffles), probabilities go through shared memory, and the same thread
+// accumulates rows ty + 8 i x dimensions tx + 16 c of the output.  All arithmetic is float32 FMA; the sums are not in
+// the reference's order, so results agree with it to rounding, not bit for bit (the row kernel keeps its order).
+constexpr int ST_BQ = 32, ST_BK = 64, ST_THREADS = 128, ST_PP = ST_BK + 4;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(ST_THREADS)
+sdpa_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                 const void* __restrict__ mask, const T* __restrict__ bias,
+                 const int32_t* __restrict__ q_len, const int32_t* __restrict__ kv_len,
+                 T* __restrict__ out, const SdpaParams p) {
+  pdl_enter();
+  constexpr int PD = D + 4, NC = D / 16;
+  extern __shared__ __align__(16) unsigned char sdpa_smem[];
+  float* Qs = reinterpret_cast<float*>(sdpa_smem);      // [ST_BQ][PD]
+  float* Ks = Qs + ST_BQ * PD;                           // [ST_BK][PD]
+  float* Vs = Ks + ST_BK * PD;                           // [ST_BK][PD]
+  float* Ps = Vs + ST_BK * PD;                           // [ST_BQ][ST_PP]
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int64_t nqt = (p.S + ST_BQ - 1) / ST_BQ;
+  const int64_t qt = blockIdx.x % nqt, h = (blockIdx.x / nqt) % p.Hq, b = blockIdx.x / (nqt * p.Hq);
+  const int64_t hk = h / (p.Hq / p.Hkv);
+  const int64_t q0 = qt * ST_BQ;
+  int64_t q_limit = p.S, kv_limit = p.Skv;
+  if (p.has_lens) {
+    const int64_t ql = q_len[b], kl = kv_len[b];
+    q_limit = ql < 0 ? 0 : (ql > p.S ? p.S : ql);
+    kv_limit = kl < 0 ? 0 : (kl > p.Skv ? p.Skv : kl);
+  }
+  const int64_t kv_end = p.causal ? min(kv_limit, q0 + ST_BQ) : kv_limit;        // no row of the tile sees keys from here on
+  const T* qb = q + b * p.q_b + h * p.q_h;
+  const T* kb_ = k + b * p.kv_b + hk * p.kv_h;
+  const T* vb = v + b * p.kv_b + hk * p.kv_h;
+  for (int idx = tid; idx < ST_BQ * D; idx += ST_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    Qs[r * PD + d] = q0 + r < p.S ? (float)Scalar<T>::load(qb, (q0 + r) * p.q_s + d) : 0.0f;
+  }
+  const uint8_t* bmask = p.mask_kind == CB_MASK_BOOL ? reinterpret_cast<const uint8_t*>(mask) : nullptr;
+  const T* amask = p.mask_kind == CB_MASK_ADDITIVE ? reinterpret_cast<const T*>(mask) : nullptr;
+  const float scale = (float)p.scale;
+  float m[4], l[4], o[4][NC];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    m[i] = -INFINITY; l[i] = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NC; c++) o[i][c] = 0.0f;
+  }
+  for (int64_t kb = 0; kb < kv_end; kb += ST_BK) {
+    __syncthreads();                                     // the previous block's K, V and P have been read (and Q is written)
+    for (int idx = tid; idx < ST_BK * D; idx += ST_THREADS) {
+      const int r = idx / D, d = idx - r * D;
+      const bool in = kb + r < kv_end;
+      Ks[r * PD + d] = in ? (float)Scalar<T>::load(kb_, (kb + r) * p.kv_s + d) : 0.0f;
+      Vs[r * PD + d] = in ? (float)Scalar<T>::load(vb, (kb + r) * p.kv_s + d) : 0.0f;
+    }
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) s[i][j] = 0.0f;
+#pragma unroll 4
+    for (int d4 = 0; d4 < D / 4; d4++) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 8 * i) * PD + 4 * d4);
+#pragma unroll
+      for (int j = 0; j < 4; j++) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * PD + 4 * d4);
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          s[i][j] = fmaf(qv[i].x, kv[j].x, fmaf(qv[i].y, kv[j].y, fmaf(qv[i].z, kv[j].z, fmaf(qv[i].w, kv[j].w, s[i][j]))));
+    }
+    // scale, bias, masks; the block's row maxima and sums across the 16 threads of a row
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t qi = q0 + ty + 8 * i;
+      const int64_t m_row = b * p.m_b + h * p.m_h + qi * p.m_s, b_row = b * p.b_b + h * p.b_h + qi * p.b_s;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int64_t key = kb + tx + 16 * j;
+        bool live = qi < p.S && key < kv_limit && (!p.causal || key <= qi);
+        if (live && bmask && !bmask[m_row + key * p.m_k]) live = false;
+        float sv = s[i][j] * scale;
+        if (live && p.has_bias) sv += (float)Scalar<T>::load(bias, b_row + key * p.b_k);
+        if (live && amask) sv += (float)Scalar<T>::load(amask, m_row + key * p.m_k);
+        s[i][j] = live ? sv : -INFINITY;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int w = 1; w < 16; w <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, w));
+      const float m_new = fmaxf(m[i], mx);
+      const float corr = m_new == -INFINITY ? 1.0f : expf(m[i] - m_new);
+      float sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float e = s[i][j] == -INFINITY ? 0.0f : expf(s[i][j] - m_new);
+        Ps[(ty + 8 * i) * ST_PP + tx + 16 * j] = e;
+        sum += e;
+      }
+#pragma unroll
+      for (int w = 1; w < 16; w <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, w);
+      l[i] = fmaf(l[i], corr, sum);
+      m[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < NC; c++) o[i][c] *= corr;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int k4 = 0; k4 < ST_BK / 4; k4++) {
+      float4 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) pv[i] = *reinterpret_cast<const float4*>(Ps + (ty + 8 * i) * ST_PP + 4 * k4);
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float vv[NC];
+#pragma unroll
+        for (int c = 0; c < NC; c++) vv[c] = Vs[(4 * k4 + e) * PD + tx + 16 * c];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float pe = e == 0 ? pv[i].x : e == 1 ? pv[i].y : e == 2 ? pv[i].z : pv[i].w;
+#pragma unroll
+          for (int c = 0; c < NC; c++) o[i][c] = fmaf(pe, vv[c], o[i][c]);
+        }
+      }
+    }
+  }
+  // rows without a live key and padded query positions are zeros (sdpa.go:389-398, 471-474)
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t qi = q0 + ty + 8 * i;
+    if (qi >= p.S) continue;
+    const float inv = (l[i] != 0.0f && qi < q_limit) ? 1.0f / l[i] : 0.0f;
+    T* orow = out + b * p.q_b + h * p.q_h + qi * p.q_s;
+#pragma unroll
+    for (int c = 0; c < NC; c++) Scalar<T>::store(orow, tx + 16 * c, o[i][c] * inv);
+  }
+}
+
+static size_t tile_smem(int64_t D) { return ((size_t)(ST_BQ + 2 * ST_BK) * (D + 4) + (size_t)ST_BQ * ST_PP) * sizeof(float); }
+
+// Shapes worth a tile: enough query rows to fill one, head_dim 32 / 64 / 128, a float type other than float64.  Tiny
+// problems (and anything asked for by name) stay on the row kernel, which sums in the reference's order.
+bool sdpa_tile_supports(const cb_sdpa_desc& d) {
+  if (d.dtype != CB_F32 && d.dtype != CB_BF16 && d.dtype != CB_F16) return false;
+  if (d.D != 32 && d.D != 64 && d.D != 128) return false;
+  if (d.S < 16 || d.S * d.Skv < 4096) return false;
+  return d.B * d.Hq * ((d.S + ST_BQ - 1) / ST_BQ) <= 0x7fffffffLL;
+}
+
+int sdpa_tile_plan(cb_plan* p) {
+  const cb_sdpa_desc& d = p->sdpa;
+  p->blocks = (int)(d.B * d.Hq * ((d.S + ST_BQ - 1) / ST_BQ));
+  p->threads = ST_THREADS;
+  p->dyn_smem = (int)tile_smem(d.D);
+  p->name = std::string("sdpa_tile_") + dtype_name(d.dtype);
+  return CB_OK;
+}
+
+template <typename T, int D>
+static int tile_launch_d(const cb_plan* p, const SdpaParams& prm, const void* const* in, void* const* out, cudaStream_t s) {
+  const cb_sdpa_desc& d = p->sdpa;
+  int idx = 3;
+  const void* mask = d.mask_kind != CB_MASK_NONE ? in[idx++] : nullptr;
+  const int32_t* ql = d.has_seq_lens ? (const int32_t*)in[idx++] : nullptr;
+  const int32_t* kl = d.has_seq_lens ? (const int32_t*)in[idx++] : nullptr;
+  const T* bias = d.bias_rank > 0 ? (const T*)in[idx++] : nullptr;
+  if (p->dyn_smem > 48 * 1024)
+    CB_CUDA(cudaFuncSetAttribute(sdpa_tile_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, p->dyn_smem));
+  CB_CUDA(launch_dependent(sdpa_tile_kernel<T, D>, dim3((unsigned)p->blocks), dim3(ST_THREADS), (size_t)p->dyn_smem, s, (const T*)in[0], (const T*)in[1],
+                           (const T*)in[2], mask, bias, ql, kl, (T*)out[0], prm));
+  return CB_OK;
+}
+template <typename T>
+static int tile_launch_t(const cb_plan* p, const SdpaParams& prm, const void* const* in, void* const* out, cudaStream_t s) {
+  switch (p->sdpa.D) {
+    case 32: return tile_launch_d<T, 32>(p, prm, in, out, s);
+    case 64: return tile_launch_d<T, 64>(p, prm, in, out, s);
+    default: return tile_launch_d<T, 128>(p, prm, in, out, s);
+  }
+}
+
+int sdpa_tile_launch(const cb_plan* p, const void* const* in, void* const* out, cudaStream_t s) {
+  const cb_sdpa_desc& d = p->sdpa;
+  if (p->blocks == 0) return CB_OK;
+  SdpaParams prm;
+  CB_TRY(sdpa_fill_params(d, &prm));
+  switch (d.dtype) {
+    case CB_F32: return tile_launch_t<float>(p, prm, in, out, s);
+    case CB_BF16: return tile_launch_t<__nv_bfloat16>(p, prm, in, out, s);
+    default: return tile_launch_t<__half>(p, prm, in, out, s);
+  }
+}
+
 static size_t generic_smem(const cb_sdpa_desc& d) {
   const size_t c = d.dtype == CB_F64 ? 8 : 4;
   return (size_t)(d.Skv + d.D + 8) * c;

@@ -26,7 +26,7 @@ QDENSE_AUTO, QDENSE_GENERIC, QDENSE_DECODE_MMA, QDENSE_PREFILL, QDENSE_DECODE_TC
 QUANT_LINEAR, QUANT_NF4, QUANT_GGML = 0, 1, 2
 GGML_Q4_0, GGML_Q8_0, GGML_IQ4_NL, GGML_Q4_K, GGML_Q6_K = 0, 1, 2, 5, 7       # compute.GGMLQuantType (fused_ops.go:132-145)
 DOT_AUTO, DOT_GENERIC, DOT_TCGEN05, DOT_TCGEN05_EXACT = range(4)
-SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH, SDPA_DECODE = range(4)
+SDPA_AUTO, SDPA_GENERIC, SDPA_FLASH, SDPA_DECODE, SDPA_TILE = range(5)
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
 MASK_NONE, MASK_BOOL, MASK_ADDITIVE = range(3)
 

@@ -199,7 +199,8 @@ int cb_plan_dot(int dev, const cb_dot_desc* desc, cb_plan** plan);
 typedef enum { CB_LAYOUT_BHSD = 0, CB_LAYOUT_BSHD = 1 } cb_attn_layout;
 typedef enum { CB_MASK_NONE = 0, CB_MASK_BOOL = 1, CB_MASK_ADDITIVE = 2 } cb_mask_kind;
 typedef enum { CB_SDPA_AUTO = 0, CB_SDPA_GENERIC = 1, CB_SDPA_FLASH = 2,
-               CB_SDPA_DECODE = 3   /* a few query tokens over a long key / value cache: split-KV streaming kernel */ } cb_sdpa_variant;
+               CB_SDPA_DECODE = 3,  /* a few query tokens over a long key / value cache: split-KV streaming kernel */
+               CB_SDPA_TILE = 4     /* 32-row query tiles on CUDA cores: float32, head_dim 32 / 64, masks, bias */ } cb_sdpa_variant;
 
 typedef struct {
   int64_t B, Hq, Hkv, S, Skv, D;

@@ -164,6 +164,67 @@ def test_sdpa_flash_kernel_with_sequence_lengths(B, Hq, Hkv, S, D, layout, dtype
     assert np.all(gotf[want == 0.0] == 0.0)
 
 
+# ------------------------------------------------------------- tiled CUDA-core kernel: float32, head_dim 32 / 64, masks, bias
+TILE_CASES = [
+    # B, Hq, Hkv, S, Skv, D, layout, dtype, causal, mask, bias, lens
+    (4, 12, 12, 128, 128, 64, "BHSD", "f32", False, "pad", None, False),     # an encoder layer: padding mask [B, 1, S, Skv]
+    (2, 8, 2, 100, 130, 64, "BSHD", "f32", True, None, None, False),         # ragged tiles, grouped heads, causal
+    (2, 4, 4, 96, 200, 32, "BHSD", "f32", False, "full", "full", True),      # boolean mask, bias and lengths together
+    (3, 6, 3, 64, 64, 128, "BSHD", "bf16", False, "additive", None, False),  # additive mask [S, Skv], bfloat16, head_dim 128
+    (2, 4, 2, 40, 512, 64, "BHSD", "f16", True, None, "head", True),         # bias [1, H, S, Skv], float16, lengths
+    (1, 2, 2, 33, 129, 64, "BHSD", "f32", False, "rows", None, False),       # some rows with every key masked: zero rows
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,Skv,D,layout,dtype,causal,mask_kind,bias_kind,lens", TILE_CASES)
+def test_sdpa_tiled_kernel(B, Hq, Hkv, S, Skv, D, layout, dtype, causal, mask_kind, bias_kind, lens):
+    rng = np.random.default_rng(B * 100 + S + Skv)
+    code = DT[dtype]
+    shape = (lambda h, s: (B, s, h, D)) if layout == "BSHD" else (lambda h, s: (B, h, s, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shape(h, s), dtype=np.float32), code) for h, s in ((Hq, S), (Hkv, Skv), (Hkv, Skv)))
+    mask = bias = q_len = kv_len = None
+    if mask_kind == "pad":
+        valid = rng.integers(Skv // 2, Skv + 1, size=B)
+        # the reference's masks are whole [S, Skv] planes, broadcast over batch and heads only (sdpa.go:309-329)
+        mask = np.ascontiguousarray(np.broadcast_to((np.arange(Skv)[None, :] < valid[:, None]).reshape(B, 1, 1, Skv), (B, 1, S, Skv)))
+    elif mask_kind == "full":
+        mask = rng.random((B, Hq, S, Skv)) < 0.8
+        if layout == "BSHD":
+            mask = np.ascontiguousarray(mask.transpose(0, 2, 1, 3))
+    elif mask_kind == "additive":
+        mask = orc.to_f32(orc.from_f32((rng.standard_normal((S, Skv)) * 2).astype(np.float32), code), code)
+    elif mask_kind == "rows":
+        mask = rng.random((S, Skv)) < 0.7
+        mask[5] = False
+        mask[32] = False
+    if bias_kind == "full":
+        bias = rng.standard_normal((B, Hq, S, Skv)).astype(np.float32)
+        if layout == "BSHD":
+            bias = np.ascontiguousarray(bias.transpose(0, 2, 1, 3))
+    elif bias_kind == "head":
+        bias = rng.standard_normal((1, Hq, S, Skv)).astype(np.float32)
+    if bias is not None:
+        bias = orc.to_f32(orc.from_f32(bias, code), code)
+    if lens:
+        kv_len = rng.integers(1, Skv + 1, size=B).astype(np.int32)
+        q_len = rng.integers(1, S + 1, size=B).astype(np.int32)
+        kv_len[0] = 0
+    dev_mask = mask if mask is None or mask.dtype == np.bool_ else orc.from_f32(mask, code)
+    dev_bias = None if bias is None else orc.from_f32(bias, code)
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, mask=dev_mask, bias=dev_bias, q_len=q_len, kv_len=kv_len,
+                         return_plan=True)
+    assert plan.kernel_name == f"sdpa_tile_{ {'f32': 'Float32', 'bf16': 'BFloat16', 'f16': 'Float16'}[dtype] }", plan.kernel_name
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), mask=mask, bias=bias, q_len=q_len, kv_len=kv_len,
+                    layout=layout, causal=causal)
+    gotf = orc.to_f32(got, code)
+    assert max_abs_normalised(gotf, want) < (2e-5 if dtype == "f32" else 2e-2)
+    assert np.all(gotf[want == 0.0] == 0.0)
+    # the row kernel (the reference's order of summation) on the same case
+    gen = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, mask=dev_mask, bias=dev_bias, q_len=q_len, kv_len=kv_len,
+                   variant=dv.SDPA_GENERIC)
+    assert max_abs_normalised(gotf, orc.to_f32(gen, code)) < (2e-5 if dtype == "f32" else 2.0 ** -7)
+
+
 # ------------------------------------------------------------- decode shapes: a few query tokens over a long cache
 DECODE_CASES = [
     # B, Hq, Hkv, S, Skv, D, layout, dtype, causal
