@@ -193,6 +193,15 @@ def other_kernels(dv, dev, stream):
     for m in (x, w, sc, y):
         m.free()
     res["sdpa_causal_b8_h32_8_s2048_d128_bf16"] = sdpa_leg(dv, dev, stream, 32, 8, tpeak)
+    # float32 attention with head_dim 64 (an encoder layer of a sentence-embedding model): the tiled CUDA-core kernel
+    Be, He, Se, De = 32, 12, 128, 64
+    qe, ke, ve = (dv.DeviceMem.from_numpy(rng.standard_normal(Be * He * Se * De, dtype=np.float32), dev) for _ in range(3))
+    oe = dv.DeviceMem(Be * He * Se * De * 4, dev)
+    plan = dv.Plan.sdpa(Be, He, He, Se, Se, De, dv.F32, dev=dev)
+    us = time_plan(dv, dev, stream, plan, [qe.ptr, ke.ptr, ve.ptr], [oe.ptr], 20)
+    res["sdpa_f32_b32_h12_s128_d64"] = {"kernel": plan.kernel_name, "us": us, "TFLOP/s": 4.0 * Be * He * Se * Se * De / us / 1e6}
+    for m in (qe, ke, ve, oe):
+        m.free()
     rows, L = 65536, 4096
     xf = dv.DeviceMem.from_numpy(rng.standard_normal(rows * L, dtype=np.float32), dev)
     gf = dv.DeviceMem.from_numpy(rng.standard_normal(L, dtype=np.float32), dev)

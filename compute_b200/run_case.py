@@ -82,16 +82,18 @@ def main() -> None:
         out.update(kernel=plan.kernel_name, us=us, tflops=2.0 * a.b * a.m * a.n * a.k / us / 1e6)
     elif a.case == "sdpa":
         sq = a.sq or a.s
-        q = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hq * sq * a.d, 1.0), dev)
-        k = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
-        v = dv.DeviceMem.from_numpy(_bf16(rng, a.b * a.hkv * a.s * a.d, 1.0), dev)
-        o = dv.DeviceMem(a.b * a.hq * sq * a.d * 2, dev)
-        plan = dv.Plan.sdpa(a.b, a.hq, a.hkv, sq, a.s, a.d, dv.BF16, causal=a.causal,
+        f32 = a.dtype == "f32"                      # float32 operands: the tiled CUDA-core kernel
+        mk = (lambda n: rng.standard_normal(n, dtype=np.float32)) if f32 else (lambda n: _bf16(rng, n, 1.0))
+        q = dv.DeviceMem.from_numpy(mk(a.b * a.hq * sq * a.d), dev)
+        k = dv.DeviceMem.from_numpy(mk(a.b * a.hkv * a.s * a.d), dev)
+        v = dv.DeviceMem.from_numpy(mk(a.b * a.hkv * a.s * a.d), dev)
+        o = dv.DeviceMem(a.b * a.hq * sq * a.d * (4 if f32 else 2), dev)
+        plan = dv.Plan.sdpa(a.b, a.hq, a.hkv, sq, a.s, a.d, dv.F32 if f32 else dv.BF16, causal=a.causal,
                             layout=dv.LAYOUT_BSHD if a.bshd else dv.LAYOUT_BHSD, dev=dev)
         us = _time(plan, [q.ptr, k.ptr, v.ptr], [o.ptr], dev, stream, a.reps, a.warmup)
         pairs = (a.s * (a.s + 1) / 2 if a.causal else a.s * a.s) if sq == a.s else sq * a.s
         out.update(kernel=plan.kernel_name, us=us, tflops=4.0 * a.b * a.hq * a.d * pairs / us / 1e6,
-                   kv_GBps=2.0 * a.b * a.hkv * a.s * a.d * 2 / us / 1e3)
+                   kv_GBps=2.0 * a.b * a.hkv * a.s * a.d * (4 if f32 else 2) / us / 1e3)
     elif a.case in ("softmax", "gelu", "layernorm"):
         code = dv.BF16 if a.dtype == "bf16" else dv.F32
         size = 2 if a.dtype == "bf16" else 4
