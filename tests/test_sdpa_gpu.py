@@ -225,6 +225,49 @@ def test_sdpa_tiled_kernel(B, Hq, Hkv, S, Skv, D, layout, dtype, causal, mask_ki
     assert max_abs_normalised(gotf, orc.to_f32(gen, code)) < (2e-5 if dtype == "f32" else 2.0 ** -7)
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_sdpa_tiled_kernel_random_sweep(seed):
+    """Seeded random shapes, head counts, layouts, dtypes, head dimensions and option combinations on the tiled kernel."""
+    rng = np.random.default_rng(9000 + seed)
+    dtype = ["f32", "f32", "bf16", "f16"][seed % 4]
+    code = DT[dtype]
+    D = [32, 64, 128][rng.integers(0, 3)]
+    Hkv = int(rng.integers(1, 4))
+    Hq = Hkv * int(rng.integers(1, 4))
+    B = int(rng.integers(1, 4))
+    S = int(rng.integers(16, 150))
+    Skv = int(rng.integers(max(16, -(-4096 // S)), 300))
+    layout = ["BHSD", "BSHD"][seed % 2]
+    causal = bool(rng.integers(0, 2))
+    shape = (lambda h, s: (B, s, h, D)) if layout == "BSHD" else (lambda h, s: (B, h, s, D))
+    q, k, v = (orc.from_f32(rng.standard_normal(shape(h, s), dtype=np.float32), code) for h, s in ((Hq, S), (Hkv, Skv), (Hkv, Skv)))
+    mask = bias = q_len = kv_len = None
+    mk = int(rng.integers(0, 4))
+    if mk == 1:
+        mask = rng.random((S, Skv)) < 0.85
+    elif mk == 2:
+        mask = rng.random((B, S, Skv)) < 0.85                     # rank 3 is [batch, seq, kv]
+    elif mk == 3:
+        mask = orc.to_f32(orc.from_f32(rng.standard_normal((B, Hq, S, Skv)).astype(np.float32), code), code)
+        if layout == "BSHD":
+            mask = np.ascontiguousarray(mask.transpose(0, 2, 1, 3))
+    if rng.integers(0, 2):
+        bias = orc.to_f32(orc.from_f32(rng.standard_normal((S, Skv)).astype(np.float32), code), code)
+    if rng.integers(0, 2):
+        q_len = rng.integers(0, S + 1, size=B).astype(np.int32)
+        kv_len = rng.integers(0, Skv + 1, size=B).astype(np.int32)
+    dev_mask = mask if mask is None or mask.dtype == np.bool_ else orc.from_f32(mask, code)
+    dev_bias = None if bias is None else orc.from_f32(bias, code)
+    got, plan = ops.sdpa(q, k, v, dtype=code, layout=LAYOUT[layout], causal=causal, mask=dev_mask, bias=dev_bias, q_len=q_len, kv_len=kv_len,
+                         return_plan=True)
+    assert plan.kernel_name.startswith("sdpa_tile_"), (plan.kernel_name, B, Hq, Hkv, S, Skv, D)
+    want = orc.sdpa(orc.to_f32(q, code), orc.to_f32(k, code), orc.to_f32(v, code), mask=mask, bias=bias, q_len=q_len, kv_len=kv_len,
+                    layout=layout, causal=causal)
+    gotf = orc.to_f32(got, code)
+    assert max_abs_normalised(gotf, want) < (2e-5 if dtype == "f32" else 2e-2), (B, Hq, Hkv, S, Skv, D, layout, causal, mk)
+    assert np.all(gotf[want == 0.0] == 0.0)
+
+
 # ------------------------------------------------------------- decode shapes: a few query tokens over a long cache
 DECODE_CASES = [
     # B, Hq, Hkv, S, Skv, D, layout, dtype, causal
