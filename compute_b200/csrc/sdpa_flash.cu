@@ -223,13 +223,19 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) fa_fail(p, &s_failed, 3, 0);
+      // Descriptors of the three tile kinds, built once: the address field sits in the low word in 16-byte units, so a
+      // tile, a stage or a k step is an add to the low word (shared-memory addresses stay below 2^18: no carry).
+      const uint64_t dq = smem_desc_sw128(q_addr, 16, 1024), dk = smem_desc_sw128(k_addr, 16, 1024);
+      const uint64_t dv = smem_desc_sw128(v_addr, FA_HALF_BYTES, 1024);
+      const uint32_t q_lo = (uint32_t)dq, q_hi = (uint32_t)(dq >> 32), k_lo = (uint32_t)dk, k_hi = (uint32_t)(dk >> 32);
+      const uint32_t v_lo = (uint32_t)dv, v_hi = (uint32_t)(dv >> 32);
       auto issue_qk = [&](int t, int s) {   // S_t = Q_t K_s^T
         const uint32_t d = tmem_base + (uint32_t)(t * 128);
+        const uint32_t a_lo = q_lo + (uint32_t)t * (FA_TILE_BYTES >> 4), b_lo = k_lo + (uint32_t)s * (FA_TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < FA_D / 16; kk++) {
-          const uint32_t off = (uint32_t)((kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32);
-          umma_f16(d, smem_desc_sw128(q_addr + t * FA_TILE_BYTES + off, 16, 1024),
-                   smem_desc_sw128(k_addr + s * FA_TILE_BYTES + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off = (uint32_t)(((kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32) >> 4);
+          umma_f16_lh(d, a_lo + off, q_hi, b_lo + off, k_hi, idesc_qk, kk > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[t]);
       };
@@ -238,10 +244,10 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_pv_chunk = [&](int t, int s, int c, bool accumulate) {
         const uint32_t d = tmem_base + (uint32_t)(256 + t * 128);
         const uint32_t a = tmem_base + (uint32_t)(t * 128);
+        const uint32_t b_lo = v_lo + (uint32_t)s * (FA_TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 2 * c; kk < 2 * c + 2; kk++)
-          umma_f16_ts(d, a + (uint32_t)(kk * 8), smem_desc_sw128(v_addr + s * FA_TILE_BYTES + kk * 16 * 128, FA_HALF_BYTES, 1024),
-                      idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          umma_f16_ts_lh(d, a + (uint32_t)(kk * 8), b_lo + (uint32_t)((kk * 16 * 128) >> 4), v_hi, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         if (c == 3) umma_commit(&o_done[t]);
       };
       if (ok) {
