@@ -89,6 +89,7 @@ struct cb_plan {
   bool has_status = false;        // kernel keeps a status word at workspace offset 0
   bool w4_stream = false;         // quantized dense on packed 4-bit weights: the streaming decode kernel, not the generic one
   bool whole_tiles = false;       // decode tensor-core plan: every CTA takes whole column tiles (nothing is split or parked)
+  int tile_cluster = 0;           // decode tensor-core plan: CTAs per column tile when these form a thread-block cluster (0: no clusters)
   std::string name;
   cb_qdense_desc qd{};
   std::vector<cb_qdense_member> group;   // members of a grouped decode plan (one entry for an ordinary plan)

@@ -41,7 +41,11 @@
 //       warps 0-7     epilogue as above, two groups of four warps; a tile whose units are split
 //                     between CTAs is finished by the CTA that arrives last, summing the parked
 //                     partial tiles in CTA order (deterministic: the result does not depend on
-//                     which CTA finishes)
+//                     which CTA finishes).  A launch of few column tiles instead gives every tile to a
+//                     thread-block cluster of two to four CTAs, each with an equal run of the tile's
+//                     units: the partial tiles stay in shared memory and the cluster's first CTA sums
+//                     them through distributed shared memory after one cluster barrier (no global
+//                     round trips: 17 -> 10.6 us per launch on a 4096 x 4096 projection)
 //     Every role comes in a pair, one thread (or group) for the even units and one for the odd ones,
 //     and both ring sizes are even: a stage, an accumulator and their barriers therefore always
 //     belong to the same member of each pair, which waits for every phase of those barriers in
@@ -117,6 +121,8 @@ struct QtParams {
   int units_per_tile;
   int tiles_total;
   int whole_tiles;          // 1: CTAs take whole tiles; 0: an equal share of the units, shared tiles fixed up
+  int cluster;              // > 1: every tile is shared by this many consecutive CTAs, launched as one thread-block cluster,
+                            // each with one run of the tile's units; the partial tiles are summed through shared memory
   long long total_units;
   int scale_group;          // 0: one scale per column; else rows of the K group
   int out_bf16;
@@ -569,7 +575,13 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
           const int n = tile_n0 + nl;
           const bool whole = tile_ends && (it >= g);          // the tile's first unit is ours too
           bool write = true;
-          if (!whole) {
+          if (!whole && p.cluster > 1) {
+            // the tile's CTAs are one cluster: the partial tile stays in this CTA's shared memory (s_merge is free again
+            // after the barrier above) and the cluster's first CTA sums all of them after the cluster barrier at the end
+#pragma unroll
+            for (int m = 0; m < MB; m++) s_merge[m * QT_TILE_N + nl] = tot[m];
+            write = false;
+          } else if (!whole) {
             // park the partial tile, count the arrival; the last CTA to arrive sums all of them in CTA order
             const int slot = (tile == tile0) ? 0 : 1;         // first or last share of this CTA's range
             float* mine = p.partials + ((size_t)(blockIdx.x * 2 + slot) * MB) * QT_TILE_N;
@@ -636,6 +648,44 @@ qdense_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     const unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
+  }
+  if (p.cluster > 1) {
+    // ---- the tile's partial sums, through distributed shared memory ----
+    // Every thread of every CTA of the cluster passes both barriers (no role returns early, and every wait above is
+    // bounded).  First barrier: all partial tiles are in place.  The first CTA's first epilogue group then reads them
+    // in CTA order (the sum does not depend on timing) and arrives at the second barrier, which keeps the other
+    // CTAs' shared memory alive until it has been read; the result is stored while the others leave.
+    cluster_arrive();
+    cluster_wait();
+    const bool leader = (blockIdx.x % (unsigned)p.cluster) == 0 && warp < 4;
+    float tot[MB];
+    if (leader) {
+      const uint32_t local = smem_u32(s_merge) + (uint32_t)tid * 4;
+#pragma unroll
+      for (int m = 0; m < MB; m++) tot[m] = s_merge[m * QT_TILE_N + tid];
+      for (int r = 1; r < p.cluster; r++) {
+        const uint32_t remote = cluster_map(local, (uint32_t)r);
+        float v[MB];
+#pragma unroll
+        for (int m = 0; m < MB; m++) v[m] = ld_cluster_f32(remote + (uint32_t)(m * QT_TILE_N * 4));
+#pragma unroll
+        for (int m = 0; m < MB; m++) tot[m] += v[m];
+      }
+    }
+    cluster_arrive();
+    if (leader) {
+      QtWalk w;
+      qt_walk_init(w, p, tile0, g0, tile_step);
+      const QtProblem* pp = &problems[w.pi];
+      const int tile_n0 = (tile0 - p.tile_start[w.pi]) * QT_TILE_N;
+      const int n = tile_n0 + tid;
+      const float bias = (pp->bias && n < pp->N) ? __ldg(pp->bias + n) : 0.0f;
+#pragma unroll
+      for (int m = 0; m < MB; m++) tot[m] += bias;
+      if (p.out_bf16) qt_store_rows<MB, true>(tot, p, pp, tile_n0, tid, s_stage);
+      else qt_store_rows<MB, false>(tot, p, pp, tile_n0, tid, s_stage);
+    }
+    cluster_wait();
   }
   if (warp == QT_MMA_WARP) {
     __syncwarp();
@@ -800,6 +850,33 @@ static QtLayout qt_layout(const cb_plan* p, int blocks) {
   return l;
 }
 
+// How many clusters of r CTAs of the main kernel the device holds at once: the CTAs of a cluster need r free SMs of one
+// GPC, so this is less than n_sm / r in general.  0 when it cannot be asked (a plan made without a device).  All
+// instances of the kernel have the same footprint (512 threads, all of an SM's shared memory), so one is asked.
+static int qt_resident_clusters(int dev, int r) {
+  static std::atomic<int> cache[64][5];
+  if (dev < 0 || r < 2 || r > 4 || sm_count(dev) <= 0) return 0;
+  if (dev < 64) { const int c = cache[dev][r].load(std::memory_order_acquire); if (c > 0) return c; }
+  int cur = 0, n = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  auto kernel = qdense_decode_tc_kernel<32, 2, 1>;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(r * 64));
+  cfg.blockDim = dim3(QT_THREADS);
+  cfg.dynamicSmemBytes = (size_t)qt_smem(32, 2);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)r; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qt_smem(32, 2)) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cudaSetDevice(cur);
+  if (n > 0 && dev < 64) cache[dev][r].store(n, std::memory_order_release);
+  return n;
+}
+
 static int qt_finish_plan(cb_plan* p) {
   const cb_qdense_desc& d = p->qd;
   long long tiles = 0;
@@ -829,10 +906,15 @@ static int qt_finish_plan(cb_plan* p) {
   // K = 14336, 32 tiles: 39.7 / 26.0 / 20.6 / 23.9 (148 CTAs).
   const long long units_per_tile = (d.K + QT_UNIT_K - 1) / QT_UNIT_K;
   if (waves == 1) {
+    // the most CTAs per tile (four at most: more did not pay) that still leave every CTA four units and let all
+    // clusters run at once (asked of the device; seven eighths of n_sm / r when there is none to ask)
     long long r = 0;
-    if (tiles * 4 <= p->n_sm && units_per_tile >= 16) r = 4;
-    else if (tiles * 16 <= (long long)p->n_sm * 7 && units_per_tile >= 8) r = 2;
-    if (r) { p->blocks = (int)(tiles * r); p->whole_tiles = false; }
+    for (long long c = 4; c >= 2 && r == 0; c--) {
+      const int resident = qt_resident_clusters(p->dev, (int)c);
+      const bool fits = resident > 0 ? tiles <= resident : tiles * c * 8 <= (long long)p->n_sm * 7;
+      if (fits && units_per_tile >= 4 * c) r = c;
+    }
+    if (r) { p->blocks = (int)(tiles * r); p->whole_tiles = false; p->tile_cluster = (int)r; }
   }
   const QtLayout l = qt_layout(p, p->blocks);
   p->threads = QT_THREADS;
@@ -981,6 +1063,7 @@ static int qt_fill_args(const cb_plan* p, const void* const* in, void* const* ou
   prm.units_per_tile = l.units_per_tile;
   prm.tiles_total = l.tiles_total;
   prm.whole_tiles = p->whole_tiles ? 1 : 0;
+  prm.cluster = p->tile_cluster;
   prm.total_units = l.total_units;
   prm.scale_group = d.scale_layout == CB_SCALE_KGROUP ? (int)d.block_size : 0;
   prm.out_bf16 = a->bf16 ? 1 : 0;
@@ -1009,11 +1092,18 @@ static int qt_launch_main_t(const cb_plan* p, const QtArgs& a, cudaStream_t s) {
   cfg.blockDim = dim3(QT_THREADS);
   cfg.dynamicSmemBytes = (size_t)qt_smem(NB, PLANES);
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p->tile_cluster > 1) {               // the CTAs of a column tile are co-scheduled and see each other's shared memory
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)p->tile_cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   // the first MAXP records of the table (QtTable<MAXP> is a prefix of QtTable<QT_MAX_PROBLEMS>)
   CB_CUDA(cudaLaunchKernelEx(&cfg, qdense_decode_tc_kernel<NB, PLANES, MAXP>, a.tmap_x, *reinterpret_cast<const QtTable<MAXP>*>(&a.table), a.prm));
   return CB_OK;
