@@ -522,6 +522,43 @@ def test_decode_uint8_no_bias_all_activations(variant, group):
         assert max_abs_normalised(got, want) < F32_TOL
 
 
+@pytest.mark.parametrize("x_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("M,K,N,ctas_per_tile", [
+    (16, 4096, 4096, (4,)),          # an o projection: 32 tiles
+    (1, 2048, 1008, (4,)),           # ragged last tile, 16 units per tile: four each
+    (7, 4096, 5120, (3, 2)),         # 40 tiles: three CTAs per tile where that many clusters are resident, else two
+    (16, 1024, 7168, (2,)),          # 56 tiles, 8 units per tile: two CTAs with four units each
+    (5, 1536, 2048, (3, 2)),         # 12 units per tile: three CTAs
+    (16, 512, 2048, (1, 9)),         # 4 units per tile are too few to share: no clusters
+])
+def test_decode_tc_few_tiles_on_cta_clusters(M, K, N, ctas_per_tile, x_dtype):
+    """A projection of few column tiles gives every tile to a cluster of CTAs that sum their partial tiles through
+    distributed shared memory: the grid is a whole number of CTAs per tile, the result matches the oracle, does not
+    change from launch to launch, and agrees with the kernel that keeps the reference's order of summation."""
+    x, w, s, b = qdense_inputs(31 * M + K + N, M, K, N, x_dtype=x_dtype, scale_layout="kgroup", group=128)
+    code = dv.BF16 if x_dtype == "bf16" else dv.F32
+    xin = orc.bf16_from_f32(x) if x_dtype == "bf16" else x
+    want = oracle_compact(x, w, s, b, "kgroup", 128, orc.ACT_GELU)
+    runs = []
+    for _ in range(3):
+        got, plan = ops.quantized_dense(xin, w, s, None, b, x_dtype=code, scale_layout=dv.SCALE_KGROUP, block_size=128,
+                                        activation=dv.ACT_GELU, variant=dv.QDENSE_DECODE_TC, return_plan=True)
+        runs.append(got)
+    tiles = (N + 127) // 128
+    assert plan.kernel_name.startswith("qdense_decode_tc_")
+    if ctas_per_tile != (1, 9):
+        assert plan.blocks % tiles == 0 and plan.blocks // tiles in ctas_per_tile, (plan.blocks, tiles)
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    if x_dtype == "bf16":
+        assert max_abs_normalised(orc.bf16_to_f32(runs[0]), want) < BF16_TOL
+        assert max_abs_normalised(orc.bf16_to_f32(runs[0]), orc.bf16_to_f32(orc.bf16_from_f32(want))) < 2.0 ** -7
+    else:
+        assert max_abs_normalised(runs[0], want) < 1e-5
+        gen = ops.quantized_dense(x, w, s, None, b, scale_layout=dv.SCALE_KGROUP, block_size=128, activation=dv.ACT_GELU,
+                                  variant=dv.QDENSE_GENERIC)
+        assert max_abs_normalised(runs[0], gen) < 1e-5
+
+
 @pytest.mark.parametrize("M", list(range(1, 17)))
 def test_decode_tc_every_batch_size(M):
     """M = 1..16 crosses the three digit-tile widths (5, 10 and 16 rows per digit plane)."""
