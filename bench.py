@@ -283,6 +283,45 @@ def weight_format_legs(dv, dev, stream):
     return res
 
 
+def block_projection_legs(dv, dev, stream):
+    """The four projection launches of the fifth configuration's decoder block on their own, one projection per launch in
+    a chain of launches (16 rows of bfloat16 x, int8 weights, per-channel scales), over distinct copies of the weights used
+    in turn (more bytes than the L2 holds between two uses of a copy).  The first three have few column tiles: their
+    tiles are shared by clusters of CTAs."""
+    hpeak, _ = measured_peak()
+    rng = np.random.default_rng(23)
+    res = {}
+    for name, K, N, copies in (("o_4096x4096", 4096, 4096, 10), ("qkv_4096x6144", 4096, 6144, 8), ("down_14336x4096", 14336, 4096, 4),
+                               ("gate_up_4096x28672", 4096, 28672, 2)):
+        M = 16
+        x = dv.DeviceMem.from_numpy((rng.standard_normal((M, K)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16), dev)
+        sc = dv.DeviceMem.from_numpy(rng.uniform(0.001, 0.02, size=N).astype(np.float32), dev)
+        wbufs = [dv.DeviceMem.from_numpy(rng.integers(-127, 128, size=(K, N), dtype=np.int8), dev) for _ in range(copies)]
+        y = dv.DeviceMem(M * N * 2, dev)
+        plan = dv.Plan.qdense(M, K, N, dv.BF16, dv.I8, dv.SCALE_CHANNEL, 0, False, False, dv.ACT_NONE, dev=dev)
+        wss = [plan.new_workspace() for _ in range(copies)]
+        seq = dv.BoundSequence([plan.bind([x.ptr, w.ptr, sc.ptr], [y.ptr], ws.ptr) for w, ws in zip(wbufs, wss)])
+        reps = 20
+        e0, e1 = dv.Event(dev), dv.Event(dev)
+        for it in range(reps + 3):
+            if it == 3:
+                e0.record(stream)
+            seq.launch(stream)
+        e1.record(stream)
+        stream.sync()
+        for ws in wss:
+            plan.check_status(ws.ptr)
+        us = e0.elapsed_ms(e1) * 1e3 / (reps * copies)
+        tiles = (N + 127) // 128
+        bts = K * N + 4 * N + 2 * M * K + 2 * M * N
+        res[name] = {"kernel": plan.kernel_name, "grid": plan.blocks, "column_tiles": tiles,
+                     "ctas_per_tile": plan.blocks // tiles if plan.blocks % tiles == 0 and plan.blocks >= tiles else None,
+                     "us_per_launch": us, "GB/s": bts / us / 1e3, "frac_of_measured_hbm": bts / us / 1e3 / hpeak}
+        for m in [x, sc, y] + wbufs + wss:
+            m.free()
+    return res
+
+
 def sdpa_leg(dv, dev, stream, hq, hkv, tpeak, check=False):
     """Causal SDPA of the fourth configuration restricted to `hq` query heads / `hkv` KV heads (all of them on one GPU,
     a KV-head group per rank when sharded: attention of a (batch, KV head) pair reads no other head).  With `check`
@@ -879,6 +918,7 @@ def main():
             out["other_path_kernels"] = other_kernels(dv, dev, stream)
             out["other_weight_formats"] = weight_format_legs(dv, dev, stream)
             out["decoder_block"] = decoder_block_legs()
+            out["decoder_block_projections"] = block_projection_legs(dv, dev, stream)
         if not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(M)
             if not args.no_extra:
