@@ -45,6 +45,11 @@ def test_plans_select_kernels_by_shape_and_dtype():
     assert g.kernel_name == "qdense_decode_tc_bf16_n32p2_i8_x8" and g.blocks == 128
     # an 8-way column shard of the same step: 8 x 14 tiles, one whole tile per CTA
     assert dv.Plan.qdense_group(16, 4096, [(1792, False, dv.ACT_SILU)] * 8, dv.BF16, dv.I8, dv.SCALE_KGROUP, 128).blocks == 112
+    # few column tiles are shared by clusters of CTAs, each with an equal run of the tile's 128-row units: four CTAs per
+    # tile (32 tiles), two (56 tiles), none when a tile has too few units to share (K = 512: four units)
+    assert dv.Plan.qdense(16, 4096, 4096, dv.BF16, dv.I8, dv.SCALE_CHANNEL).blocks == 128
+    assert dv.Plan.qdense(16, 4096, 7168, dv.BF16, dv.I8, dv.SCALE_CHANNEL).blocks == 112
+    assert dv.Plan.qdense(16, 512, 2048, dv.BF16, dv.I8, dv.SCALE_CHANNEL).blocks in (16, 64)
     with pytest.raises(cb.ErrNotImplemented):      # members must suit the tensor-core decode kernel
         dv.Plan.qdense_group(16, 4096, [(14336, False, 0)], dv.BF16, dv.I8, dv.SCALE_KGROUP, 64)
     with pytest.raises(cb.BackendError):
