@@ -154,6 +154,15 @@ class Shape:
     def size(self) -> int:
         return int(np.prod(self.dimensions, dtype=np.int64)) if self.dimensions else 1
 
+    def _c_dims(self):
+        """(element count, dimensions as a C int64 array), built once per Shape: BufferFromFlatData is on the per-step
+        path of a decode loop and a Shape is immutable in use."""
+        c = self.__dict__.get("_c_cache")
+        if c is None or c[2] != self.dimensions:
+            c = (self.size(), _i64(self.dimensions), self.dimensions)
+            self.__dict__["_c_cache"] = c
+        return c
+
 
 def make_shape(dtype: int, *dims: int) -> Shape:
     return Shape(dtype, tuple(int(d) for d in dims))
@@ -278,9 +287,9 @@ class Buffer:
 
     def ToFlatData(self, flat: np.ndarray) -> None:
         """Copies the buffer into `flat` (exact size), like Buffer.ToFlatData."""
-        if not flat.flags["C_CONTIGUOUS"]:
+        if not flat.flags.c_contiguous:
             raise BackendError(_lib.ERR_INVALID_ARG, "Buffer.ToFlatData: flat must be contiguous")
-        check(_g().cbg_buffer_to_flat(self.handle, flat.ctypes.data, flat.nbytes))
+        check(_g().cbg_buffer_to_flat(self.handle, flat.__array_interface__["data"][0], flat.nbytes))
 
     def ToNumpy(self) -> np.ndarray:
         s = self.Shape()
@@ -614,7 +623,9 @@ class Executable:
             if len(donate) != n_in:
                 raise BackendError(_lib.ERR_INVALID_ARG, f"Execute: donate has {len(donate)} entries for {n_in} inputs")
             don = (C.c_uint8 * max(n_in, 1))(*[1 if d else 0 for d in donate])
-        n_out_max = max(_g().cbg_exec_num_outputs(self.handle) * max(self._backend.NumDevices(), 1), 1)
+        n_out_max = self.__dict__.get("_n_out_max")
+        if n_out_max is None:          # fixed for the life of the executable
+            n_out_max = self._n_out_max = max(_g().cbg_exec_num_outputs(self.handle) * max(self._backend.NumDevices(), 1), 1)
         outs = (C.c_void_p * n_out_max)()
         check(_g().cbg_exec_execute(self.handle, ins, n_in, don, defaultDevice, outs, n_out_max))
         if donate is not None:
@@ -721,12 +732,13 @@ class Backend:
             if a.size != (shape.size() + 1) // 2:
                 raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} bytes, packed shape needs {(shape.size() + 1) // 2}")
         else:
-            a = np.ascontiguousarray(flat, dv.NP_CARRIER.get(shape.dtype))
-            if a.size != shape.size():
+            carrier = dv.NP_CARRIER.get(shape.dtype)
+            a = flat if (isinstance(flat, np.ndarray) and flat.dtype == carrier and flat.flags.c_contiguous) else np.ascontiguousarray(flat, carrier)
+            if a.size != shape._c_dims()[0]:
                 raise BackendError(_lib.ERR_INVALID_ARG, f"BufferFromFlatData: flat has {a.size} elements, shape needs {shape.size()}")
         h = C.c_void_p()
-        check(_g().cbg_buffer_from_flat(self.handle, deviceNum, a.ctypes.data, shape.dtype, shape.rank(),
-                                        _i64(shape.dimensions), C.byref(h)))
+        check(_g().cbg_buffer_from_flat(self.handle, deviceNum, a.__array_interface__["data"][0], shape.dtype, len(shape.dimensions),
+                                        shape._c_dims()[1], C.byref(h)))
         return Buffer(h, self)
 
     def HasSharedBuffers(self) -> bool:

@@ -40,6 +40,10 @@ void clear_error();
 // Makes `dev` current for the calling thread (cgo calls may land on any OS thread).
 int set_device(int dev);
 int sm_count(int dev);
+bool host_range_is_page_locked(const void* p, size_t bytes);   // inside a range cb_host_alloc returned
+// several same-device copies as one kernel launch (elementwise.cu): pointers and sizes multiples of 16 bytes
+int copy_many_max();
+int copy_many(int n_sm, int n, void* const* dst, const void* const* src, const size_t* bytes, cudaStream_t s);
 
 // cuTensorMapEncodeTiled resolved through the runtime (no link-time libcuda dependency).
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,

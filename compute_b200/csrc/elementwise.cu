@@ -535,4 +535,52 @@ int stacked_reduce_launch(int dtype, int op, const void* stacked, int g, int64_t
   return CB_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// several device-to-device copies as one launch
+// ---------------------------------------------------------------------------
+// The results of a replayed graph live in the graph's own memory and are handed to the caller as fresh buffers: one
+// launch copies all of them (16-byte vectors, every pointer 16-byte aligned) instead of one copy engine call each.
+constexpr int COPY_MANY_MAX = 16;
+struct CopyMany {
+  const uint4* src[COPY_MANY_MAX];
+  uint4* dst[COPY_MANY_MAX];
+  unsigned long long vecs[COPY_MANY_MAX];      // 16-byte vectors per copy
+  int n;
+};
+__global__ void __launch_bounds__(256) copy_many_kernel(const CopyMany c) {
+  for (int k = 0; k < c.n; k++) {
+    const uint4* s = c.src[k];
+    uint4* d = c.dst[k];
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < c.vecs[k]; i += (unsigned long long)gridDim.x * blockDim.x)
+      d[i] = s[i];
+  }
+}
+
+int copy_many_max() { return COPY_MANY_MAX; }
+
+// n <= copy_many_max() copies of bytes[k] from src[k] to dst[k] on one device; every pointer and size a multiple of 16
+int copy_many(int n_sm, int n, void* const* dst, const void* const* src, const size_t* bytes, cudaStream_t s) {
+  if (n <= 0) return CB_OK;
+  if (n > COPY_MANY_MAX) return fail(CB_ERR_INVALID_ARG, "copy_many: %d copies, at most %d", n, COPY_MANY_MAX);
+  CopyMany c;
+  memset(&c, 0, sizeof(c));
+  c.n = n;
+  unsigned long long total = 0;
+  for (int k = 0; k < n; k++) {
+    if ((reinterpret_cast<uintptr_t>(dst[k]) | reinterpret_cast<uintptr_t>(src[k]) | bytes[k]) & 15)
+      return fail(CB_ERR_INVALID_ARG, "copy_many: pointers and sizes must be multiples of 16 bytes");
+    c.src[k] = reinterpret_cast<const uint4*>(src[k]);
+    c.dst[k] = reinterpret_cast<uint4*>(dst[k]);
+    c.vecs[k] = bytes[k] / 16;
+    total += c.vecs[k];
+  }
+  if (total == 0) return CB_OK;
+  const unsigned long long want = (total + 256 * 4 - 1) / (256 * 4);          // about four vectors per thread
+  const unsigned blocks = (unsigned)std::min<unsigned long long>(std::max<unsigned long long>(want, 1), (unsigned long long)(n_sm > 0 ? n_sm : 148) * 8);
+  copy_many_kernel<<<blocks, 256, 0, s>>>(c);        // an ordinary launch: it may follow a graph launch
+  CB_CUDA(cudaGetLastError());
+  return CB_OK;
+}
+
 }  // namespace cb

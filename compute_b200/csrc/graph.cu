@@ -310,7 +310,7 @@ int staged_copy(cbg_backend* be, int dev, void* dptr, void* host, size_t bytes, 
   if (bytes == 0) return CB_OK;
   // The caller's memory is itself page-locked (from cb_host_alloc, or registered): no staging copy is needed.
   cudaPointerAttributes attr;
-  if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost) {
+  if (cb::host_range_is_page_locked(host, bytes) || (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost)) {
     cb_stream s = nullptr;
     CB_TRY(be->get_stream(dev, &s));
     int st = to_device ? cb_h2d(dev, dptr, host, bytes, s) : cb_d2h(dev, host, dptr, bytes, s);
@@ -1918,6 +1918,20 @@ int launch_node(cbg_exec* e, Replica& r, size_t i) {
 
 int collect_outputs(cbg_exec* e, Replica& r) {
   cbg_function* f = e->fn.get();
+  // results that must be copied (a replayed graph keeps its own memory; an output that is also a parameter) leave
+  // together in one launch when there are several and their sizes allow 16-byte vectors
+  std::vector<void*> cp_dst;
+  std::vector<const void*> cp_src;
+  std::vector<size_t> cp_bytes;
+  int n_copies = 0;
+  bool vectors = true;
+  for (size_t o = 0; o < f->outputs.size(); o++) {
+    const cbg_value* root = f->outputs[o];
+    while (root->kind == N_RESHAPE) root = root->inputs[0];
+    const bool donated_param = root->kind == N_PARAM && r.donate && r.donate[root->param_index];
+    if (!(r.owned[root->index] || donated_param)) { n_copies++; vectors = vectors && f->outputs[o]->shape.bytes() % 16 == 0; }
+  }
+  const bool batch = n_copies >= 2 && n_copies <= cb::copy_many_max() && vectors;
   for (size_t o = 0; o < f->outputs.size(); o++) {
     cbg_value* n = f->outputs[o];
     // root of the aliasing chain (Reshape shares memory with its operand)
@@ -1934,10 +1948,18 @@ int collect_outputs(cbg_exec* e, Replica& r) {
       r.taken[ri] = 1;
     } else {
       CB_TRY(r.pool->get(r.dev, n->shape.bytes(), &buf->ptr));
-      int st = cb_d2d(r.dev, buf->ptr, r.dev, r.mem[ri], n->shape.bytes(), r.stream);
-      if (st != CB_OK) { r.pool->put(n->shape.bytes(), buf->ptr); return st; }
+      if (batch && n->shape.bytes() > 0 && (int)cp_dst.size() < cb::copy_many_max() && !((reinterpret_cast<uintptr_t>(buf->ptr) | reinterpret_cast<uintptr_t>(r.mem[ri])) & 15)) {
+        cp_dst.push_back(buf->ptr); cp_src.push_back(r.mem[ri]); cp_bytes.push_back(n->shape.bytes());
+      } else {
+        int st = cb_d2d(r.dev, buf->ptr, r.dev, r.mem[ri], n->shape.bytes(), r.stream);
+        if (st != CB_OK) { r.pool->put(n->shape.bytes(), buf->ptr); return st; }
+      }
     }
     r.outs.push_back(buf.release());
+  }
+  if (!cp_dst.empty()) {
+    CB_TRY(cb::set_device(r.dev));
+    CB_TRY(cb::copy_many(cb::sm_count(r.dev), (int)cp_dst.size(), cp_dst.data(), cp_src.data(), cp_bytes.data(), (cudaStream_t)r.stream));
   }
   return CB_OK;
 }

@@ -5,6 +5,7 @@
 
 #include <stdarg.h>
 #include <string.h>
+#include <map>
 #include <mutex>
 #include <vector>
 
@@ -75,6 +76,26 @@ const char* dtype_name(int d) {
     case CB_I4: return "Int4"; case CB_U4: return "Uint4";
     default: return "InvalidDType";
   }
+}
+
+// The page-locked ranges this library handed out, so that a transfer from one of them needs no query of the driver.
+static std::mutex g_host_mu;
+static std::map<uintptr_t, size_t> g_host_ranges;      // base -> bytes
+void host_range_add(const void* p, size_t bytes) {
+  std::lock_guard<std::mutex> l(g_host_mu);
+  g_host_ranges[reinterpret_cast<uintptr_t>(p)] = bytes;
+}
+void host_range_remove(const void* p) {
+  std::lock_guard<std::mutex> l(g_host_mu);
+  g_host_ranges.erase(reinterpret_cast<uintptr_t>(p));
+}
+bool host_range_is_page_locked(const void* p, size_t bytes) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  std::lock_guard<std::mutex> l(g_host_mu);
+  auto it = g_host_ranges.upper_bound(a);
+  if (it == g_host_ranges.begin()) return false;
+  --it;
+  return a >= it->first && a + bytes <= it->first + it->second;
 }
 
 }  // namespace cb
@@ -182,12 +203,15 @@ int cb_d2d(int dst_dev, void* dst, int src_dev, const void* src, size_t bytes, c
 
 int cb_host_alloc(size_t bytes, void** host_ptr) {
   clear_error();
-  CB_CUDA(cudaMallocHost(host_ptr, bytes ? bytes : 16));
+  const size_t n = bytes ? bytes : 16;
+  CB_CUDA(cudaMallocHost(host_ptr, n));
+  cb::host_range_add(*host_ptr, n);
   return CB_OK;
 }
 
 int cb_host_free(void* host_ptr) {
   if (!host_ptr) return CB_OK;
+  cb::host_range_remove(host_ptr);
   CB_CUDA(cudaFreeHost(host_ptr));
   return CB_OK;
 }
